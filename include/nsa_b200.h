@@ -1,0 +1,153 @@
+/*
+ * nsa_b200.h - C ABI of the B200 (sm_100a) Native Sparse Attention kernels.
+ *
+ * Every entry point takes raw DEVICE pointers, explicit element strides, sizes, a dtype code and a
+ * CUDA stream handle (cudaStream_t passed as void*), launches asynchronously on that stream and
+ * returns 0 on success or a negative NSA_ERR_* code (nsa_last_error() then holds a message).
+ * Nothing here allocates device memory unless stated; scratch memory is passed in by the caller and
+ * sized by the matching *_workspace_bytes() query.  No entry point has a CPU fallback.
+ *
+ * Layout conventions (those of the reference project's kernel-call contract, README.md:55-101 of
+ * Noumena-Network/NSA-Test):
+ *   Q   [B,H,T,dk]          strides (z,h,m,k)
+ *   K   [B,G,dk,T] in memory; its strides are passed in the order (z,g,n=time,k=dk)
+ *   V   [B,G,T,dv]          strides (z,g,n,k)
+ *   Out [B,H,T,dv]          strides (z,h,m,k); dOut uses Out's strides
+ *   L,M [B,H,T] fp32        L = log(sum exp(s - M)), M = row max of the scaled logits
+ *   dQ  like Q (overwritten); dK is [B,G,T,dk] (time-major!) and dV [B,G,T,dv]: both must be
+ *   zero-initialised by the caller, the kernels add into them (nsa/kernels.py:1146-1148).
+ * Kernels honour whatever strides they are given (tests/test_kernel_contracts.py:68-90 of the
+ * reference passes wrong K strides on purpose and expects a different answer, not a fault).
+ */
+#ifndef NSA_B200_H
+#define NSA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define NSA_API __attribute__((visibility("default")))
+#else
+#define NSA_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { NSA_F32 = 0, NSA_BF16 = 1 };
+enum { NSA_GATE_SIGMOID = 0, NSA_GATE_SOFTMAX = 1 };
+enum {
+  NSA_OK = 0,
+  NSA_ERR_ARG = -1,        /* bad size / dtype / null pointer */
+  NSA_ERR_LAUNCH = -2,     /* CUDA reported a launch error */
+  NSA_ERR_WORKSPACE = -3,  /* scratch buffer missing or too small */
+  NSA_ERR_UNSUPPORTED = -4 /* shape outside what the requested kernel family covers */
+};
+
+/* Message for the last non-zero status returned on the calling thread. */
+NSA_API const char* nsa_last_error(void);
+/* Library / build identification: "nsa_b200 <version> sm_100a". */
+NSA_API const char* nsa_version(void);
+
+/* Strides block shared by the attention entry points, in elements:
+ *   [0..3] q (z,h,m,k)   [4..7] k (z,g,n,k)   [8..11] v (z,g,n,k)   [12..15] out (z,h,m,k)
+ *   [16..18] L (z,h,m)   [19..21] M (z,h,m)
+ * backward adds [22..25] dq (z,h,m,k)  [26..29] dk (z,g,n,k)  [30..33] dv (z,g,n,k)
+ * selection adds, after those of its direction, 4 strides of the index tensor (z,g,m,n).      */
+
+/* Sliding-window attention, query t sees keys [max(0,t-window+1), t].
+ * Replaces _nsa_sliding_window_fwd_kernel / _bwd_kernel (nsa/kernels.py:1151-1300, 1303-1530). */
+NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void* v, void* out, float* L, float* M,
+                    const int64_t* strides22, int B, int H, int G, int T, int dk, int dv, int window,
+                    float scale, int dtype, void* stream);
+NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                    const float* L, const float* M, void* dq, void* dkey, void* dval,
+                    const int64_t* strides34, int B, int H, int G, int T, int dk, int dv, int window,
+                    float scale, int dtype, void* stream);
+
+/* Attention over compressed tokens, block i visible iff block_ends[i] <= t; a row that sees no block
+ * gets out = 0, L = M = -inf.  k_cmp is [B,G,dk,NB] with strides passed (z,g,n=block,k), v_cmp
+ * [B,G,NB,dv]; dk_cmp is written [B,G,NB,dk].
+ * Replaces _nsa_compression_fwd_kernel / _bwd_kernel (nsa/kernels.py:1533-1687, 1690-1917). */
+NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
+                     void* out, float* L, float* M, const int64_t* strides22, int B, int H, int G,
+                     int T, int NB, int dk, int dv, float scale, int dtype, void* stream);
+NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
+                     const void* out, const void* dout, const float* L, const float* M, void* dq,
+                     void* dk_cmp, void* dv_cmp, const int64_t* strides34, int B, int H, int G, int T,
+                     int NB, int dk, int dv, float scale, int dtype, void* stream);
+
+/* Selected-block attention: query t of group g sees the union of blocks indices[b,g,t,:] (ids < 0
+ * and blocks starting at or beyond Tkv ignored, a repeated id counts once) intersected with
+ * keys <= t.  indices is int32.
+ * Replaces _nsa_sparse_selection_fwd_kernel / _bwd_kernel (nsa/kernels.py:594-833, 836-1148). */
+NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, const int32_t* indices, void* out,
+                float* L, float* M, const int64_t* strides26, int B, int H, int G, int Tq, int Tkv,
+                int n_slots, int l_prime, int dk, int dv, float scale, int dtype, void* stream);
+/* Backward; dK/dV are reduced per key block over the queries that selected it in a fixed order (an
+ * inverse index "block -> queries" is built in the workspace), so results are run-to-run identical. */
+NSA_API size_t nsa_slc_bwd_workspace_bytes(int B, int G, int Tq, int Tkv, int n_slots, int l_prime);
+NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, const int32_t* indices, const void* out,
+                const void* dout, const float* L, const float* M, void* dq, void* dkey, void* dval,
+                const int64_t* strides38, int B, int H, int G, int Tq, int Tkv, int n_slots,
+                int l_prime, int dk, int dv, float scale, int dtype, void* workspace,
+                size_t workspace_bytes, void* stream);
+
+/* Pooling half of the block-compression MLP phi (NSAAttention.compress_tokens, nsa/kernels.py:
+ * 2119-2208).  With A[t,:] = W1[:, :dk] k_t (a plain GEMM done by the caller) and the table
+ * C[j,:] = W1[:, dk:] pos_embed[j] + b1, computes hbar[i,:] = mean_{j<l} relu(A[i*d+j,:] + C[j,:])
+ * and v_cmp[i,:] = mean_{j<l} v[i*d+j,:] for i < n_blocks; the caller finishes with
+ * k_cmp[i] = W2 hbar[i] + b2.  a [BG,T,U] fp32, c [l,U] fp32, v [B,G,T,dv] (strides z,g,n,k; dtype),
+ * hbar [BG,n_blocks,U] fp32, v_cmp [B,G,nbp,dv] contiguous in dtype (rows >= n_blocks untouched). */
+NSA_API int nsa_phi_pool_fwd(const float* a, const float* c, const void* v, const int64_t* v_strides4,
+                     float* hbar, void* v_cmp, int B, int G, int T, int U, int dv, int l, int d,
+                     int n_blocks, int nbp, int dtype, void* stream);
+/* Backward of the pooling: da[t,u] = sum over blocks i holding t of [A[t,u]+C[j,u] > 0] dhbar[i,u]/l,
+ * dc_part[bg,j,u] = sum_i of the same terms (the caller sums dc_part over bg), and
+ * dv[t,:] = sum over blocks holding t of dv_cmp[i,:]/l (fp32 [B,G,T,dv] contiguous, overwritten);
+ * dhbar [BG,n_blocks,U], dv_cmp [BG,nbp,dv] fp32. */
+NSA_API int nsa_phi_pool_bwd(const float* a, const float* c, const float* dhbar, const float* dv_cmp,
+                     float* da, float* dc_part, float* dv, int B, int G, int T, int U, int dv_dim,
+                     int l, int d, int n_blocks, int nbp, void* stream);
+
+/* Eq. 8 -> 9 -> 10/11 in one pass (nsa/kernels.py:2304-2343, 1920-1962, 1965-2040): softmax of
+ * q k_cmp over visible blocks (fallback: block 0 alone), the (l/d x l'/d) stencil onto selection
+ * blocks, the sum over the heads of each group in head order, a stable top-min(n,n_sel) (ties to the
+ * lower block id), then the fixed blocks [0, max(0,(t-l')/l'), t/l'] prepended, repeats dropped,
+ * cut to n and padded with -1.  q [B,H,T,dk] (dtype, strides z,h,m,k), k_cmp fp32 [B,G,dk,nbp]
+ * contiguous, block_ends [nbp], indices_out int32 [B,G,T,n] contiguous. */
+NSA_API int nsa_score_topn(const void* q, const int64_t* q_strides4, const float* k_cmp,
+                   const int32_t* block_ends, int32_t* indices_out, int B, int H, int G, int T, int dk,
+                   int nbp, int l, int d, int l_prime, int n, int n_fixed, float scale, int dtype,
+                   void* stream);
+/* Eq. 10/11 alone on a given score tensor [B,H,T,n_sel] fp32 contiguous
+ * (select_top_k_blocks_per_query_with_gqa, nsa/kernels.py:1965-2040). */
+NSA_API int nsa_topn_from_scores(const float* scores, int32_t* indices_out, int B, int H, int G, int T,
+                         int n_sel, int l_prime, int n, int n_fixed, void* stream);
+
+/* Diagnostics behind the module's output_attentions=True report (nsa/kernels.py:2481-2488), never
+ * on the training path: Eq. 8 probabilities materialised as out [B,H,T,nbp] fp32, and Eq. 9 applied
+ * to a materialised probability tensor of `rows` rows (derive_selection_from_compression_per_timestep,
+ * nsa/kernels.py:1920-1962), out [rows, ceil(n_cmp/(l'/d))] fp32. */
+NSA_API int nsa_cmp_probs(const void* q, const int64_t* q_strides4, const float* k_cmp,
+                          const int32_t* block_ends, float* out, int B, int H, int G, int T, int dk,
+                          int nbp, float scale, int dtype, void* stream);
+NSA_API int nsa_eq9_scores(const float* p_cmp, float* out, int64_t rows, int n_cmp, int l, int d,
+                           int l_prime, void* stream);
+
+/* Gate + mix (nsa/kernels.py:2446-2463): gates = sigmoid | softmax-over-3 of logits[b,t,3h+i],
+ * out = g0*o_cmp + g1*o_slc + g2*o_win.  logits [B,T,3H] fp32, branch outputs and out [B,H,T,dv]
+ * contiguous in dtype, gates_out [B,H,T,3] fp32 (saved for backward / diagnostics). */
+NSA_API int nsa_gate_mix_fwd(const float* logits, const void* o_cmp, const void* o_slc, const void* o_win,
+                     void* out, float* gates_out, int B, int H, int T, int dv, int gate_mode,
+                     int dtype, void* stream);
+/* Backward: d_branch_i = g_i * dout (three tensors in dtype), dlogits [B,T,3H] fp32. */
+NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
+                     const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits,
+                     int B, int H, int T, int dv, int gate_mode, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NSA_B200_H */

@@ -1,0 +1,148 @@
+// C ABI of the attention entry points declared in include/nsa_b200.h, plus error reporting.
+// Argument checking happens here; kernels never see a null pointer or an inconsistent size.
+#include "attn_args.cuh"
+#include "common.cuh"
+
+namespace nsa {
+
+char* error_buffer() {
+  static thread_local char buf[512] = "";
+  return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(NSA_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  return NSA_OK;
+}
+
+static void fill_fwd_strides(AttnArgs& a, const int64_t* s) {
+  for (int i = 0; i < 4; ++i) { a.sq[i] = s[i]; a.sk[i] = s[4 + i]; a.sv[i] = s[8 + i]; a.so[i] = s[12 + i]; }
+  for (int i = 0; i < 3; ++i) { a.sL[i] = s[16 + i]; a.sM[i] = s[19 + i]; }
+}
+static void fill_bwd_strides(AttnArgs& a, const int64_t* s) {
+  fill_fwd_strides(a, s);
+  for (int i = 0; i < 4; ++i) { a.sdq[i] = s[22 + i]; a.sdk[i] = s[26 + i]; a.sdv[i] = s[30 + i]; }
+}
+
+static int check_common(const char* who, int B, int H, int G, int Tq, int Tk, int dk, int dv, int dtype) {
+  NSA_REQUIRE(B >= 0 && H > 0 && G > 0 && H % G == 0, "%s: bad B/H/G = %d/%d/%d", who, B, H, G);
+  NSA_REQUIRE(Tq >= 0 && Tk >= 0, "%s: negative sequence length", who);
+  NSA_REQUIRE(dk > 0 && dk <= kMaxHeadDim && dv > 0 && dv <= kMaxHeadDim, "%s: head dims %d/%d outside 1..%d", who, dk,
+              dv, kMaxHeadDim);
+  NSA_REQUIRE(dtype == NSA_F32 || dtype == NSA_BF16, "%s: unsupported dtype %d", who, dtype);
+  NSA_REQUIRE((int64_t)B * H <= 65535, "%s: B*H = %lld exceeds 65535", who, (long long)B * H);
+  return NSA_OK;
+}
+
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" NSA_API const char* nsa_last_error(void) { return error_buffer(); }
+extern "C" NSA_API const char* nsa_version(void) { return "nsa_b200 0.1.0 sm_100a"; }
+
+extern "C" NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void* v, void* out, float* L, float* M,
+                               const int64_t* strides, int B, int H, int G, int T, int dk, int dv, int window,
+                               float scale, int dtype, void* stream) {
+  if (int rc = check_common("sliding_fwd", B, H, G, T, T, dk, dv, dtype)) return rc;
+  NSA_REQUIRE(q && k && v && out && strides, "sliding_fwd: null pointer");
+  NSA_REQUIRE(window > 0, "sliding_fwd: window must be positive");
+  AttnArgs a = {};
+  a.q = q; a.k = k; a.v = v; a.o = out; a.L = L; a.M = M;
+  fill_fwd_strides(a, strides);
+  a.B = B; a.H = H; a.G = G; a.Tq = T; a.Tk = T; a.dk = dk; a.dv = dv; a.window = window; a.scale = scale; a.causal = 1;
+  return launch_attn_generic(a, kWin, dtype, false, (cudaStream_t)stream);
+}
+
+extern "C" NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                               const float* L, const float* M, void* dq, void* dkey, void* dval,
+                               const int64_t* strides, int B, int H, int G, int T, int dk, int dv, int window,
+                               float scale, int dtype, void* stream) {
+  if (int rc = check_common("sliding_bwd", B, H, G, T, T, dk, dv, dtype)) return rc;
+  NSA_REQUIRE(q && k && v && out && dout && L && M && dq && dkey && dval && strides, "sliding_bwd: null pointer");
+  NSA_REQUIRE(window > 0, "sliding_bwd: window must be positive");
+  AttnArgs a = {};
+  a.q = q; a.k = k; a.v = v; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.dq = dq; a.dk_out = dkey; a.dv_out = dval;
+  fill_bwd_strides(a, strides);
+  a.B = B; a.H = H; a.G = G; a.Tq = T; a.Tk = T; a.dk = dk; a.dv = dv; a.window = window; a.scale = scale; a.causal = 1;
+  return launch_attn_generic(a, kWin, dtype, true, (cudaStream_t)stream);
+}
+
+extern "C" NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
+                                void* out, float* L, float* M, const int64_t* strides, int B, int H, int G, int T,
+                                int NB, int dk, int dv, float scale, int dtype, void* stream) {
+  if (int rc = check_common("cmp_attn_fwd", B, H, G, T, NB, dk, dv, dtype)) return rc;
+  NSA_REQUIRE(q && k_cmp && v_cmp && block_ends && out && strides, "cmp_attn_fwd: null pointer");
+  AttnArgs a = {};
+  a.q = q; a.k = k_cmp; a.v = v_cmp; a.o = out; a.L = L; a.M = M; a.block_ends = block_ends;
+  fill_fwd_strides(a, strides);
+  a.B = B; a.H = H; a.G = G; a.Tq = T; a.Tk = NB; a.dk = dk; a.dv = dv; a.scale = scale; a.causal = 1;
+  return launch_attn_generic(a, kCmp, dtype, false, (cudaStream_t)stream);
+}
+
+extern "C" NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
+                                const void* out, const void* dout, const float* L, const float* M, void* dq,
+                                void* dk_cmp, void* dv_cmp, const int64_t* strides, int B, int H, int G, int T, int NB,
+                                int dk, int dv, float scale, int dtype, void* stream) {
+  if (int rc = check_common("cmp_attn_bwd", B, H, G, T, NB, dk, dv, dtype)) return rc;
+  NSA_REQUIRE(q && k_cmp && v_cmp && block_ends && out && dout && L && M && dq && dk_cmp && dv_cmp && strides,
+              "cmp_attn_bwd: null pointer");
+  AttnArgs a = {};
+  a.q = q; a.k = k_cmp; a.v = v_cmp; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.block_ends = block_ends;
+  a.dq = dq; a.dk_out = dk_cmp; a.dv_out = dv_cmp;
+  fill_bwd_strides(a, strides);
+  a.B = B; a.H = H; a.G = G; a.Tq = T; a.Tk = NB; a.dk = dk; a.dv = dv; a.scale = scale; a.causal = 1;
+  return launch_attn_generic(a, kCmp, dtype, true, (cudaStream_t)stream);
+}
+
+extern "C" NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, const int32_t* indices, void* out, float* L,
+                           float* M, const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots,
+                           int l_prime, int dk, int dv, float scale, int dtype, void* stream) {
+  if (int rc = check_common("slc_fwd", B, H, G, Tq, Tkv, dk, dv, dtype)) return rc;
+  NSA_REQUIRE(q && k && v && indices && out && strides, "slc_fwd: null pointer");
+  NSA_REQUIRE(l_prime > 0 && n_slots >= 0, "slc_fwd: bad block size / slot count");
+  AttnArgs a = {};
+  a.q = q; a.k = k; a.v = v; a.o = out; a.L = L; a.M = M; a.indices = indices;
+  fill_fwd_strides(a, strides);
+  for (int i = 0; i < 4; ++i) a.sidx[i] = strides[22 + i];
+  a.B = B; a.H = H; a.G = G; a.Tq = Tq; a.Tk = Tkv; a.dk = dk; a.dv = dv; a.scale = scale; a.causal = 1;
+  a.nslots = n_slots; a.lprime = l_prime; a.nblk = (Tkv + l_prime - 1) / l_prime;
+  return launch_attn_generic(a, kSlc, dtype, false, (cudaStream_t)stream);
+}
+
+extern "C" NSA_API size_t nsa_slc_bwd_workspace_bytes(int B, int G, int Tq, int Tkv, int n_slots, int l_prime) {
+  if (B <= 0 || G <= 0 || Tq <= 0 || Tkv <= 0 || n_slots <= 0 || l_prime <= 0) return 256;
+  return slc_csr_workspace_bytes(B, G, Tq, Tkv, n_slots, l_prime);
+}
+
+extern "C" NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, const int32_t* indices, const void* out,
+                           const void* dout, const float* L, const float* M, void* dq, void* dkey, void* dval,
+                           const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots, int l_prime,
+                           int dk, int dv, float scale, int dtype, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  if (int rc = check_common("slc_bwd", B, H, G, Tq, Tkv, dk, dv, dtype)) return rc;
+  NSA_REQUIRE(q && k && v && indices && out && dout && L && M && dq && dkey && dval && strides, "slc_bwd: null pointer");
+  NSA_REQUIRE(l_prime > 0 && n_slots > 0, "slc_bwd: bad block size / slot count");
+  if (B == 0 || Tq == 0 || Tkv == 0) return NSA_OK;
+  AttnArgs a = {};
+  a.q = q; a.k = k; a.v = v; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.indices = indices;
+  a.dq = dq; a.dk_out = dkey; a.dv_out = dval;
+  fill_bwd_strides(a, strides);
+  for (int i = 0; i < 4; ++i) a.sidx[i] = strides[34 + i];
+  a.B = B; a.H = H; a.G = G; a.Tq = Tq; a.Tk = Tkv; a.dk = dk; a.dv = dv; a.scale = scale; a.causal = 1;
+  a.nslots = n_slots; a.lprime = l_prime; a.nblk = (Tkv + l_prime - 1) / l_prime;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (int rc = build_slc_csr(indices, a.sidx, B, G, Tq, Tkv, n_slots, l_prime, 1, workspace, workspace_bytes,
+                             &a.csr_off, &a.csr_t, st))
+    return rc;
+  return launch_attn_generic(a, kSlc, dtype, true, st);
+}

@@ -1,0 +1,39 @@
+// Argument block shared by the attention kernels of the three NSA branches.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nsa {
+
+enum AttnMode { kWin = 0, kCmp = 1, kSlc = 2 };
+
+struct AttnArgs {
+  // forward
+  const void *q, *k, *v;
+  void* o;
+  float *L, *M;
+  // backward
+  const void *o_in, *dout;
+  const float *Lc, *Mc;
+  void *dq, *dk_out, *dv_out;
+  // masks
+  const int* block_ends;  // kCmp: [Tk]
+  const int* indices;     // kSlc: [B,G,Tq,nslots] with strides sidx
+  const int* csr_off;     // kSlc backward: [B*G, nblk+1] offsets into csr_t
+  const int* csr_t;       // kSlc backward: [B*G, Tq*nslots] query positions grouped by key block
+  // element strides; sk/sdk are ordered (z, g, n = key position, k = head dim)
+  int64_t sq[4], sk[4], sv[4], so[4], sL[3], sM[3], sdq[4], sdk[4], sdv[4], sidx[4];
+  int B, H, G, Tq, Tk, dk, dv;
+  int window, nslots, lprime, nblk, causal;
+  float scale;
+};
+
+int launch_attn_generic(const AttnArgs& a, int mode, int dtype, bool backward, cudaStream_t st);
+
+// Inverse index "key block -> queries that selected it" for the selection backward.
+size_t slc_csr_workspace_bytes(int B, int G, int Tq, int Tkv, int nslots, int lprime);
+int build_slc_csr(const int* indices, const int64_t* sidx, int B, int G, int Tq, int Tkv, int nslots,
+                  int lprime, int causal, void* workspace, size_t workspace_bytes, const int** csr_off,
+                  const int** csr_t, cudaStream_t st);
+
+}  // namespace nsa

@@ -1,0 +1,117 @@
+// Branch gates and mix (Eq. 5; nsa/kernels.py:2446-2463): gates = sigmoid (or softmax over the three
+// branches) of logits[b,t,3h+i], out = g0*o_cmp + g1*o_slc + g2*o_win.  HBM-bound: three reads and
+// one write of [B,H,T,dv] forward; backward reads four tensors and writes three.
+#include "common.cuh"
+
+namespace nsa {
+
+__device__ __forceinline__ void gates3(const float* lg, int mode, float g[3]) {
+  if (mode == NSA_GATE_SOFTMAX) {
+    const float m = fmaxf(lg[0], fmaxf(lg[1], lg[2]));
+    const float e0 = expf(lg[0] - m), e1 = expf(lg[1] - m), e2 = expf(lg[2] - m);
+    const float inv = 1.f / (e0 + e1 + e2);
+    g[0] = e0 * inv; g[1] = e1 * inv; g[2] = e2 * inv;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 3; ++i) g[i] = 1.f / (1.f + expf(-lg[i]));
+  }
+}
+
+// one warp per (b,h,t) row
+template <typename T>
+__global__ void gate_mix_fwd_kernel(const float* __restrict__ logits, const T* __restrict__ oc, const T* __restrict__ os,
+                                    const T* __restrict__ ow, T* __restrict__ out, float* __restrict__ gates, int B,
+                                    int H, int T_, int dv, int mode) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)B * H * T_) return;
+  const int t = row % T_, h = (row / T_) % H, b = row / ((int64_t)T_ * H);
+  float g[3];
+  gates3(logits + ((int64_t)b * T_ + t) * 3 * H + 3 * h, mode, g);
+  if (lane < 3) gates[row * 3 + lane] = g[lane];
+  const int64_t base = row * dv;
+  for (int c = lane; c < dv; c += 32) {
+    const float x = Elem<T>::ld(oc + base + c) * g[0];
+    const float y = x + Elem<T>::ld(os + base + c) * g[1];
+    Elem<T>::st(out + base + c, y + Elem<T>::ld(ow + base + c) * g[2]);
+  }
+}
+
+template <typename T>
+__global__ void gate_mix_bwd_kernel(const float* __restrict__ gates, const T* __restrict__ oc, const T* __restrict__ os,
+                                    const T* __restrict__ ow, const T* __restrict__ dout, T* __restrict__ doc,
+                                    T* __restrict__ dos, T* __restrict__ dow, float* __restrict__ dlogits, int B, int H,
+                                    int T_, int dv, int mode) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)B * H * T_) return;
+  const int t = row % T_, h = (row / T_) % H, b = row / ((int64_t)T_ * H);
+  const float g0 = gates[row * 3], g1 = gates[row * 3 + 1], g2 = gates[row * 3 + 2];
+  const int64_t base = row * dv;
+  float d0 = 0.f, d1 = 0.f, d2 = 0.f;
+  for (int c = lane; c < dv; c += 32) {
+    const float dy = Elem<T>::ld(dout + base + c);
+    d0 = fmaf(dy, Elem<T>::ld(oc + base + c), d0);
+    d1 = fmaf(dy, Elem<T>::ld(os + base + c), d1);
+    d2 = fmaf(dy, Elem<T>::ld(ow + base + c), d2);
+    Elem<T>::st(doc + base + c, dy * g0);
+    Elem<T>::st(dos + base + c, dy * g1);
+    Elem<T>::st(dow + base + c, dy * g2);
+  }
+  d0 = warp_sum(d0); d1 = warp_sum(d1); d2 = warp_sum(d2);
+  if (lane == 0) {
+    float* dl = dlogits + ((int64_t)b * T_ + t) * 3 * H + 3 * h;
+    if (mode == NSA_GATE_SOFTMAX) {
+      const float dot = g0 * d0 + g1 * d1 + g2 * d2;
+      dl[0] = g0 * (d0 - dot); dl[1] = g1 * (d1 - dot); dl[2] = g2 * (d2 - dot);
+    } else {
+      dl[0] = d0 * g0 * (1.f - g0); dl[1] = d1 * g1 * (1.f - g1); dl[2] = d2 * g2 * (1.f - g2);
+    }
+  }
+}
+
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" NSA_API int nsa_gate_mix_fwd(const float* logits, const void* o_cmp, const void* o_slc, const void* o_win, void* out,
+                                float* gates_out, int B, int H, int T, int dv, int gate_mode, int dtype, void* stream) {
+  NSA_REQUIRE(logits && o_cmp && o_slc && o_win && out && gates_out, "gate_mix_fwd: null pointer");
+  NSA_REQUIRE(gate_mode == NSA_GATE_SIGMOID || gate_mode == NSA_GATE_SOFTMAX, "gate_mix_fwd: bad gate mode %d", gate_mode);
+  const int64_t rows = (int64_t)B * H * T;
+  if (rows == 0) return NSA_OK;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == NSA_F32)
+    gate_mix_fwd_kernel<float><<<grid, 256, 0, st>>>(logits, (const float*)o_cmp, (const float*)o_slc, (const float*)o_win,
+                                                      (float*)out, gates_out, B, H, T, dv, gate_mode);
+  else if (dtype == NSA_BF16)
+    gate_mix_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(logits, (const __nv_bfloat16*)o_cmp,
+                                                              (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win,
+                                                              (__nv_bfloat16*)out, gates_out, B, H, T, dv, gate_mode);
+  else
+    return fail(NSA_ERR_ARG, "gate_mix_fwd: unsupported dtype %d", dtype);
+  return check_launch("gate_mix_fwd");
+}
+
+extern "C" NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
+                                const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits, int B, int H,
+                                int T, int dv, int gate_mode, int dtype, void* stream) {
+  NSA_REQUIRE(gates && o_cmp && o_slc && o_win && dout && do_cmp && do_slc && do_win && dlogits, "gate_mix_bwd: null pointer");
+  const int64_t rows = (int64_t)B * H * T;
+  if (rows == 0) return NSA_OK;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == NSA_F32)
+    gate_mix_bwd_kernel<float><<<grid, 256, 0, st>>>(gates, (const float*)o_cmp, (const float*)o_slc, (const float*)o_win,
+                                                      (const float*)dout, (float*)do_cmp, (float*)do_slc, (float*)do_win,
+                                                      dlogits, B, H, T, dv, gate_mode);
+  else if (dtype == NSA_BF16)
+    gate_mix_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        gates, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win,
+        (const __nv_bfloat16*)dout, (__nv_bfloat16*)do_cmp, (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, dlogits, B, H,
+        T, dv, gate_mode);
+  else
+    return fail(NSA_ERR_ARG, "gate_mix_bwd: unsupported dtype %d", dtype);
+  return check_launch("gate_mix_bwd");
+}

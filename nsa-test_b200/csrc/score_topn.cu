@@ -1,0 +1,305 @@
+// Selection scoring: Eq. 8 (compressed-attention probabilities) -> Eq. 9 (stencil onto selection
+// blocks) -> Eq. 10 (sum over the heads of a GQA group) -> Eq. 11 (top-n with forced blocks).
+//
+// Semantics pinned to the reference's torch code: p_cmp (nsa/kernels.py:2316-2343, rows that see no
+// compressed block use block 0 alone), derive_selection_from_compression_per_timestep
+// (nsa/kernels.py:1943-1960: adds in (m outer, n inner) order from zero, n_sel from the padded block
+// count), select_top_k_blocks_per_query_with_gqa (nsa/kernels.py:1986-2040: heads summed in order,
+// stable descending sort so ties go to the lower block id, fixed blocks first, repeats dropped,
+// -1 padding).  Nothing of size [B,H,T,n_cmp] ever reaches HBM: one CTA owns one (b,g,t).
+#include "common.cuh"
+
+namespace nsa {
+
+constexpr int kThreads = 256;
+constexpr int kMaxN = 64;
+
+__device__ __forceinline__ float block_max(float x, float* red) {
+  x = warp_max(x);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = x;
+  __syncthreads();
+  float r = red[0];
+  for (int w = 1; w < kThreads / 32; ++w) r = fmaxf(r, red[w]);
+  return r;
+}
+__device__ __forceinline__ float block_sum(float x, float* red) {
+  x = warp_sum(x);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = x;
+  __syncthreads();
+  float r = red[0];
+  for (int w = 1; w < kThreads / 32; ++w) r += red[w];
+  return r;
+}
+
+// Stable top-k of agg[0..n_sel) (value descending, index ascending), fixed-block merge, -1 padding.
+// Destroys agg.  All threads of the CTA must call it.
+__device__ void topn_and_merge(float* agg, int n_sel, int t, int l_prime, int n, int n_fixed, int* top,
+                               float* redv, int* redi, int32_t* out) {
+  const int k_actual = min(n, n_sel);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int r = 0; r < k_actual; ++r) {
+    float bv = -CUDART_INF_F;
+    int bi = 0x7fffffff;
+    for (int j = threadIdx.x; j < n_sel; j += kThreads) {
+      const float v = agg[j];
+      if (v > bv || (v == bv && j < bi)) { bv = v; bi = j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { redv[warp] = bv; redi[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < kThreads / 32; ++w)
+        if (redv[w] > bv || (redv[w] == bv && redi[w] < bi)) { bv = redv[w]; bi = redi[w]; }
+      top[r] = bi;
+      if (bi < n_sel) agg[bi] = -CUDART_INF_F;  // taken; scores are >= 0
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    int cnt = 0;
+    int res[kMaxN];
+    auto push = [&](int id) {
+      if (cnt >= n) return;
+      for (int i = 0; i < cnt; ++i)
+        if (res[i] == id) return;
+      res[cnt++] = id;
+    };
+    if (n_fixed > 0) {
+      push(0);
+      push(t < l_prime ? 0 : (t - l_prime) / l_prime);
+      push(t / l_prime);
+    }
+    for (int r = 0; r < k_actual; ++r) push(top[r]);
+    for (int i = 0; i < n; ++i) out[i] = i < cnt ? res[i] : -1;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+score_topn_kernel(const T* __restrict__ q, int64_t sqz, int64_t sqh, int64_t sqm, int64_t sqk,
+                  const float* __restrict__ kc, const int* __restrict__ block_ends, int32_t* __restrict__ out, int H,
+                  int G, int T_, int dk, int nbp, int a_, int s_, int n_sel, int l_prime, int n, int n_fixed,
+                  float scale) {
+  extern __shared__ float sm[];
+  const int t = blockIdx.x, bg = blockIdx.y, b = bg / G, g = bg % G, hpg = H / G;
+  float* qs = sm;                       // [hpg][dk]
+  float* p = qs + hpg * dk;             // [nbp + a_ + s_]
+  float* agg = p + nbp + a_ + s_;       // [n_sel]
+  float* redv = agg + n_sel;            // [8]
+  int* redi = (int*)(redv + 8);         // [8]
+  int* top = redi + 8;                  // [kMaxN]
+  for (int i = threadIdx.x; i < hpg * dk; i += kThreads) {
+    const int hh = i / dk, d = i % dk;
+    qs[i] = Elem<T>::ld(q + b * sqz + (int64_t)(g * hpg + hh) * sqh + (int64_t)t * sqm + d * sqk);
+  }
+  for (int j = threadIdx.x; j < n_sel; j += kThreads) agg[j] = 0.f;
+  for (int i = nbp + threadIdx.x; i < nbp + a_ + s_; i += kThreads) p[i] = 0.f;
+  __syncthreads();
+  const float* kb = kc + (int64_t)bg * dk * nbp;
+  for (int hh = 0; hh < hpg; ++hh) {
+    const float* qh = qs + hh * dk;
+    float mx = -CUDART_INF_F;
+    for (int i = threadIdx.x; i < nbp; i += kThreads) {
+      float s = -CUDART_INF_F;
+      if (block_ends[i] <= t) {
+        float acc = 0.f;
+        for (int d = 0; d < dk; ++d) acc = fmaf(qh[d], kb[(int64_t)d * nbp + i], acc);
+        s = acc * scale;
+      }
+      p[i] = s;
+      mx = fmaxf(mx, s);
+    }
+    mx = block_max(mx, redv);
+    if (mx == -CUDART_INF_F) {  // nothing visible: block 0 alone
+      for (int i = threadIdx.x; i < nbp; i += kThreads) p[i] = i == 0 ? 1.f : 0.f;
+    } else {
+      float sum = 0.f;
+      for (int i = threadIdx.x; i < nbp; i += kThreads) {
+        const float e = expf(p[i] - mx);  // exp(-inf) = 0 for hidden blocks
+        p[i] = e;
+        sum += e;
+      }
+      sum = block_sum(sum, redv);
+      const float inv = 1.f / sum;
+      for (int i = threadIdx.x; i < nbp; i += kThreads) p[i] *= inv;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < n_sel; j += kThreads) {
+      float sel = 0.f;
+      for (int m = 0; m < s_; ++m)
+        for (int nn = 0; nn < a_; ++nn) sel += p[s_ * j + m + nn];  // zero padding stands for skipped terms
+      agg[j] += sel;
+    }
+    __syncthreads();
+  }
+  topn_and_merge(agg, n_sel, t, l_prime, n, n_fixed, top, redv, redi,
+                 out + ((int64_t)bg * T_ + t) * n);
+}
+
+__global__ void __launch_bounds__(kThreads)
+topn_from_scores_kernel(const float* __restrict__ scores, int32_t* __restrict__ out, int H, int G, int T_, int n_sel,
+                        int l_prime, int n, int n_fixed) {
+  extern __shared__ float sm[];
+  const int t = blockIdx.x, bg = blockIdx.y, b = bg / G, g = bg % G, hpg = H / G;
+  float* agg = sm;
+  float* redv = agg + n_sel;
+  int* redi = (int*)(redv + 8);
+  int* top = redi + 8;
+  for (int j = threadIdx.x; j < n_sel; j += kThreads) {
+    float acc = 0.f;
+    for (int hh = 0; hh < hpg; ++hh)
+      acc += scores[(((int64_t)b * H + g * hpg + hh) * T_ + t) * n_sel + j];
+    agg[j] = acc;
+  }
+  __syncthreads();
+  topn_and_merge(agg, n_sel, t, l_prime, n, n_fixed, top, redv, redi, out + ((int64_t)bg * T_ + t) * n);
+}
+
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const float* k_cmp, const int32_t* block_ends,
+                              int32_t* indices_out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
+                              int l_prime, int n, int n_fixed, float scale, int dtype, void* stream) {
+  NSA_REQUIRE(q && qs && k_cmp && block_ends && indices_out, "score_topn: null pointer");
+  NSA_REQUIRE(G > 0 && H % G == 0 && d > 0 && l % d == 0 && l_prime % d == 0 && l > 0 && l_prime > 0,
+              "score_topn: bad block parameters");
+  NSA_REQUIRE(n > 0 && n <= kMaxN, "score_topn: n=%d outside 1..%d", n, kMaxN);
+  NSA_REQUIRE(nbp > 0, "score_topn: no compressed blocks");
+  if (B * G == 0 || T == 0) return NSA_OK;
+  const int a_ = l / d, s_ = l_prime / d, n_sel = (nbp + s_ - 1) / s_, hpg = H / G;
+  const size_t sm = ((size_t)hpg * dk + nbp + a_ + s_ + n_sel + 16 + kMaxN) * sizeof(float);
+  if (sm > 200 * 1024) return fail(NSA_ERR_UNSUPPORTED, "score_topn: %zu bytes of shared memory needed", sm);
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid(T, B * G);
+  if (dtype == NSA_F32) {
+    cudaFuncSetAttribute(score_topn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    score_topn_kernel<float><<<grid, kThreads, sm, st>>>((const float*)q, qs[0], qs[1], qs[2], qs[3], k_cmp, block_ends,
+                                                          indices_out, H, G, T, dk, nbp, a_, s_, n_sel, l_prime, n,
+                                                          n_fixed, scale);
+  } else if (dtype == NSA_BF16) {
+    cudaFuncSetAttribute(score_topn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    score_topn_kernel<__nv_bfloat16><<<grid, kThreads, sm, st>>>((const __nv_bfloat16*)q, qs[0], qs[1], qs[2], qs[3],
+                                                                  k_cmp, block_ends, indices_out, H, G, T, dk, nbp, a_,
+                                                                  s_, n_sel, l_prime, n, n_fixed, scale);
+  } else {
+    return fail(NSA_ERR_ARG, "score_topn: unsupported dtype %d", dtype);
+  }
+  return check_launch("score_topn");
+}
+
+extern "C" NSA_API int nsa_topn_from_scores(const float* scores, int32_t* indices_out, int B, int H, int G, int T, int n_sel,
+                                    int l_prime, int n, int n_fixed, void* stream) {
+  NSA_REQUIRE(scores && indices_out, "topn_from_scores: null pointer");
+  NSA_REQUIRE(G > 0 && H % G == 0 && l_prime > 0 && n > 0 && n <= kMaxN && n_sel > 0, "topn_from_scores: bad sizes");
+  if (B * G == 0 || T == 0) return NSA_OK;
+  const size_t sm = ((size_t)n_sel + 16 + kMaxN) * sizeof(float);
+  if (sm > 200 * 1024) return fail(NSA_ERR_UNSUPPORTED, "topn_from_scores: n_sel too large");
+  cudaFuncSetAttribute(topn_from_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  topn_from_scores_kernel<<<dim3(T, B * G), kThreads, sm, (cudaStream_t)stream>>>(scores, indices_out, H, G, T, n_sel,
+                                                                                 l_prime, n, n_fixed);
+  return check_launch("topn_from_scores");
+}
+
+// ------------------------------------------------------------------------------------------------
+// diagnostics: materialised Eq. 8 probabilities and Eq. 9 scores (the layer never needs them in HBM;
+// they back the module's output_attentions=True report, nsa/kernels.py:2481-2488)
+// ------------------------------------------------------------------------------------------------
+namespace nsa {
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+cmp_probs_kernel(const T* __restrict__ q, int64_t sqz, int64_t sqh, int64_t sqm, int64_t sqk,
+                 const float* __restrict__ kc, const int* __restrict__ block_ends, float* __restrict__ out, int H, int G,
+                 int T_, int dk, int nbp, float scale) {
+  extern __shared__ float sm[];
+  const int t = blockIdx.x, bh = blockIdx.y, b = bh / H, h = bh % H, g = h / (H / G);
+  float* qs = sm;
+  float* red = qs + dk;
+  for (int d = threadIdx.x; d < dk; d += kThreads) qs[d] = Elem<T>::ld(q + b * sqz + h * sqh + (int64_t)t * sqm + d * sqk);
+  __syncthreads();
+  const float* kb = kc + (int64_t)(b * G + g) * dk * nbp;
+  float* orow = out + ((int64_t)bh * T_ + t) * nbp;
+  float mx = -CUDART_INF_F;
+  for (int i = threadIdx.x; i < nbp; i += kThreads) {
+    float s = -CUDART_INF_F;
+    if (block_ends[i] <= t) {
+      float acc = 0.f;
+      for (int d = 0; d < dk; ++d) acc = fmaf(qs[d], kb[(int64_t)d * nbp + i], acc);
+      s = acc * scale;
+    }
+    orow[i] = s;
+    mx = fmaxf(mx, s);
+  }
+  mx = block_max(mx, red);
+  if (mx == -CUDART_INF_F) {
+    for (int i = threadIdx.x; i < nbp; i += kThreads) orow[i] = i == 0 ? 1.f : 0.f;
+    return;
+  }
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < nbp; i += kThreads) {
+    const float e = expf(orow[i] - mx);
+    orow[i] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, red);
+  const float inv = 1.f / sum;
+  for (int i = threadIdx.x; i < nbp; i += kThreads) orow[i] *= inv;
+}
+
+__global__ void eq9_kernel(const float* __restrict__ p, float* __restrict__ out, int64_t rows, int n_cmp, int n_sel,
+                           int a_, int s_) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * n_sel) return;
+  const int64_t r = i / n_sel;
+  const int j = i % n_sel;
+  const float* pr = p + r * n_cmp;
+  float sel = 0.f;
+  for (int m = 0; m < s_; ++m)
+    for (int nn = 0; nn < a_; ++nn) {
+      const int idx = s_ * j + m + nn;
+      if (idx < n_cmp) sel += pr[idx];
+    }
+  out[i] = sel;
+}
+
+}  // namespace nsa
+
+extern "C" NSA_API int nsa_cmp_probs(const void* q, const int64_t* qs, const float* k_cmp, const int32_t* block_ends,
+                                     float* out, int B, int H, int G, int T, int dk, int nbp, float scale, int dtype,
+                                     void* stream) {
+  NSA_REQUIRE(q && qs && k_cmp && block_ends && out, "cmp_probs: null pointer");
+  NSA_REQUIRE(G > 0 && H % G == 0 && nbp > 0 && dk > 0 && (int64_t)B * H <= 65535, "cmp_probs: bad sizes");
+  if (B == 0 || T == 0) return NSA_OK;
+  const size_t sm = ((size_t)dk + 8) * sizeof(float);
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid(T, B * H);
+  if (dtype == NSA_F32)
+    cmp_probs_kernel<float><<<grid, kThreads, sm, st>>>((const float*)q, qs[0], qs[1], qs[2], qs[3], k_cmp, block_ends, out,
+                                                         H, G, T, dk, nbp, scale);
+  else if (dtype == NSA_BF16)
+    cmp_probs_kernel<__nv_bfloat16><<<grid, kThreads, sm, st>>>((const __nv_bfloat16*)q, qs[0], qs[1], qs[2], qs[3], k_cmp,
+                                                                 block_ends, out, H, G, T, dk, nbp, scale);
+  else
+    return fail(NSA_ERR_ARG, "cmp_probs: unsupported dtype %d", dtype);
+  return check_launch("cmp_probs");
+}
+
+extern "C" NSA_API int nsa_eq9_scores(const float* p_cmp, float* out, int64_t rows, int n_cmp, int l, int d, int l_prime,
+                                      void* stream) {
+  NSA_REQUIRE(p_cmp && out, "eq9_scores: null pointer");
+  NSA_REQUIRE(d > 0 && l > 0 && l_prime > 0 && l % d == 0 && l_prime % d == 0 && n_cmp > 0, "eq9_scores: bad block parameters");
+  const int a_ = l / d, s_ = l_prime / d, n_sel = (n_cmp + s_ - 1) / s_;
+  const int64_t total = rows * n_sel;
+  if (total == 0) return NSA_OK;
+  eq9_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p_cmp, out, rows, n_cmp, n_sel, a_, s_);
+  return check_launch("eq9_scores");
+}

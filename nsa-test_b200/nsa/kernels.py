@@ -1,0 +1,497 @@
+"""Host-side mirror of the reference project's ``nsa.kernels`` module, backed by sm_100a CUDA kernels.
+
+Same names and call signatures as Noumena-Network/NSA-Test ``nsa/kernels.py``: ``NSAConfig``
+(:516-591), the autograd wrappers ``CompressionAttention`` / ``SelectionAttention`` /
+``SlidingWindowAttention`` (:34-513), the scoring functions (:1920-2040), the ``NSAAttention`` module
+(:2043-2507) and the six ``_nsa_*_kernel`` objects, which here are launcher shims that accept the
+reference's ``kernel[grid](*positional, **constexpr)`` call and forward it to the C ABI.
+
+Deliberate differences from the reference:
+* every path runs on the GPU; eval mode uses the same (deterministic) kernels as training instead of
+  a float64 CPU detour (nsa/kernels.py:2366-2398), and CPU tensors raise;
+* the [B,H,T,n_cmp] probability tensor is never materialised on the training path; it is produced
+  only for ``output_attentions=True``;
+* dK/dV are reduced in a fixed order (no atomics), so backward is bit-reproducible.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import ops
+
+__all__ = [
+    "NSAConfig", "NSAAttention", "CompressionAttention", "SelectionAttention", "SlidingWindowAttention",
+    "derive_selection_from_compression_per_timestep", "select_top_k_blocks_per_query_with_gqa",
+    "_nsa_sliding_window_fwd_kernel", "_nsa_sliding_window_bwd_kernel", "_nsa_compression_fwd_kernel",
+    "_nsa_compression_bwd_kernel", "_nsa_sparse_selection_fwd_kernel", "_nsa_sparse_selection_bwd_kernel",
+]
+
+PAD_BLOCK_END = 999999  # block end of the padding blocks (nsa/kernels.py:2190)
+
+
+def _next_pow2(n: int) -> int:
+    p = 1
+    while p < n:
+        p *= 2
+    return p
+
+
+# --------------------------------------------------------------------------------------------------
+# configuration (nsa/kernels.py:516-591)
+# --------------------------------------------------------------------------------------------------
+
+@dataclass
+class NSAConfig:
+    """NSA layer configuration; field names and defaults are those of the reference (paper Sec. 4.1)."""
+
+    d_model: int = 2560
+    head_dim_qk: int = 192
+    head_dim_v: int = 128
+    l: int = 32           # compression block size
+    d: int = 16           # compression stride
+    l_prime: int = 64     # selection block size
+    n: int = 16           # blocks selected per query
+    include_fixed_in_selection: bool = True
+    n_fixed: int = 3      # 1 initial + 2 local
+    n_dynamic: int = 13
+    w: int = 512          # sliding window
+    n_heads: int = 64
+    n_kv_groups: int = 4
+    dropout_p: float = 0.0
+    use_bias: bool = False
+    block_m: int = 32     # accepted for compatibility; tile sizes are chosen by the CUDA kernels
+    block_n: int = 32
+    gate_mode: str = "sigmoid"
+
+    def __post_init__(self):
+        # The reference accepts l=0 / l_prime=0 by accident (0 % d == 0) although its own contract test
+        # expects a rejection (tests/test_kernel_contracts.py:372-382); reject them explicitly.
+        assert self.d > 0, "compression stride d must be positive"
+        assert self.l > 0 and self.l_prime > 0, "block sizes l and l_prime must be positive"
+        assert self.n > 0, "n must be positive"
+        assert self.n_kv_groups > 0 and self.n_heads % self.n_kv_groups == 0
+        assert self.l % self.d == 0
+        assert self.l_prime % self.d == 0
+        assert self.w > 0
+        if not self.include_fixed_in_selection:
+            self.n_fixed = 0
+        self.n_dynamic = max(0, self.n - self.n_fixed)
+        assert self.n_fixed + self.n_dynamic == self.n
+        assert self.gate_mode in ("sigmoid", "softmax")
+
+    @property
+    def heads_per_group(self) -> int:
+        return self.n_heads // self.n_kv_groups
+
+    @property
+    def head_dim_qk_padded(self) -> int:
+        return _next_pow2(self.head_dim_qk)
+
+    @property
+    def head_dim_v_padded(self) -> int:
+        return _next_pow2(self.head_dim_v)
+
+
+# --------------------------------------------------------------------------------------------------
+# autograd wrappers (nsa/kernels.py:34-513)
+# --------------------------------------------------------------------------------------------------
+
+class SlidingWindowAttention(torch.autograd.Function):
+    """``apply(q [B,H,T,dk], k [B,G,dk,T], v [B,G,T,dv], scale, window_size, config) -> o [B,H,T,dv]``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, window_size, config=None):
+        o, L, M = ops.sliding_fwd(q, k, v, window_size, scale)
+        ctx.save_for_backward(q, k, v, o, L, M)
+        ctx.scale, ctx.window_size = scale, window_size
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, L, M = ctx.saved_tensors
+        dq, dkey, dval = ops.sliding_bwd(q, k, v, o, do, L, M, ctx.window_size, ctx.scale)
+        return dq, dkey.transpose(-1, -2), dval, None, None, None
+
+
+class CompressionAttention(torch.autograd.Function):
+    """``apply(q, k_compressed [B,G,dk,NB], v_compressed [B,G,NB,dv], block_ends [NB], scale, config)``."""
+
+    @staticmethod
+    def forward(ctx, q, k_compressed, v_compressed, block_ends, scale, config=None):
+        o, L, M = ops.cmp_attn_fwd(q, k_compressed, v_compressed, block_ends, scale)
+        ctx.save_for_backward(q, k_compressed, v_compressed, block_ends, o, L, M)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, kc, vc, block_ends, o, L, M = ctx.saved_tensors
+        dq, dkc, dvc = ops.cmp_attn_bwd(q, kc, vc, block_ends, o, do, L, M, ctx.scale)
+        return dq, dkc.transpose(-1, -2), dvc, None, None, None
+
+
+def _selection_fallback(indices: torch.Tensor, l_prime: int) -> torch.Tensor:
+    """Rows whose slots are all -1 attend the block holding the query (nsa/kernels.py:199-205)."""
+    if indices.numel() == 0:
+        return indices
+    T = indices.shape[2]
+    t_blocks = (torch.arange(T, device=indices.device, dtype=indices.dtype) // l_prime).view(1, 1, T, 1)
+    none_valid = (indices < 0).all(dim=-1, keepdim=True)
+    return torch.where(none_valid, t_blocks, indices)
+
+
+class SelectionAttention(torch.autograd.Function):
+    """``apply(q, k [B,G,dk,T], v [B,G,T,dv], indices [B,G,T,n], scale, config) -> o``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, indices, scale, config):
+        idx = _selection_fallback(indices, config.l_prime).to(torch.int32).contiguous()
+        o, L, M = ops.slc_fwd(q, k, v, idx, config.l_prime, scale)
+        ctx.save_for_backward(q, k, v, idx, o, L, M)
+        ctx.scale, ctx.l_prime = scale, config.l_prime
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, idx, o, L, M = ctx.saved_tensors
+        dq, dkey, dval = ops.slc_bwd(q, k, v, idx, o, do, L, M, ctx.l_prime, ctx.scale)
+        return dq, dkey.transpose(-1, -2), dval, None, None, None
+
+
+# --------------------------------------------------------------------------------------------------
+# scoring functions (nsa/kernels.py:1920-2040)
+# --------------------------------------------------------------------------------------------------
+
+def derive_selection_from_compression_per_timestep(compression_scores: torch.Tensor, config: NSAConfig) -> torch.Tensor:
+    """Eq. 9 on a materialised probability tensor [B,H,T,n_cmp] -> [B,H,T,n_sel]."""
+    assert config.l % config.d == 0 and config.l_prime % config.d == 0
+    out = ops.eq9_scores(compression_scores, config.l, config.d, config.l_prime)
+    return out.to(compression_scores.dtype)
+
+
+def select_top_k_blocks_per_query_with_gqa(selection_scores: torch.Tensor, config: NSAConfig,
+                                           always_include_blocks: Optional[List[int]] = None) -> torch.Tensor:
+    """Eq. 10/11: [B,H,T,n_blocks] scores -> int64 block ids [B,G,T,n] (-1 = empty slot).
+
+    ``always_include_blocks`` is accepted and ignored, as in the reference."""
+    n_fixed = config.n_fixed if config.include_fixed_in_selection else 0
+    idx = ops.topn_from_scores(selection_scores, config.n_kv_groups, config.l_prime, config.n, n_fixed)
+    return idx.to(torch.int64)
+
+
+# --------------------------------------------------------------------------------------------------
+# phi compression and gate/mix as autograd functions
+# --------------------------------------------------------------------------------------------------
+
+class _PhiCompress(torch.autograd.Function):
+    """Block compression phi (nsa/kernels.py:2119-2208) with fp32 outputs.
+
+    k_cmp[i] = W2 mean_j relu(W1k k_{id+j} + W1p pos_j + b1) + b2, which equals the reference's
+    mean_j MLP([k_j || pos_j]) because the second linear layer commutes with the mean.  The two dense
+    products are plain GEMMs (cuBLAS through torch, fp32); the relu + positional table + pooling in
+    between is one fused streaming kernel.
+    """
+
+    @staticmethod
+    def forward(ctx, keys, values, pos_embed, w1, b1, w2, b2, l, d):
+        B, G, T, dk = keys.shape
+        nb = (T - l) // d + 1
+        assert nb >= 1, f"sequence length {T} shorter than one compression block ({l})"
+        nbp = _next_pow2(nb)
+        w1k, w1p = w1[:, :dk].float(), w1[:, dk:].float()
+        c = torch.addmm(b1.float(), pos_embed.float(), w1p.t())                     # [l,U]
+        a = torch.matmul(keys.float(), w1k.t())                                     # [B,G,T,U]
+        hbar, v_cmp = ops.phi_pool_fwd(a, c, values, l, d, nb, nbp)
+        kc = torch.matmul(hbar, w2.float().t()) + b2.float()                        # [B,G,nb,dk]
+        k_cmp = torch.zeros(B, G, dk, nbp, device=keys.device, dtype=torch.float32)
+        k_cmp[..., :nb] = kc.transpose(-1, -2)
+        ctx.save_for_backward(keys, a, c, hbar, pos_embed, w1, w2)
+        ctx.cfg = (l, d, nb, nbp, values.dtype)
+        return k_cmp, v_cmp
+
+    @staticmethod
+    def backward(ctx, dk_cmp, dv_cmp):
+        keys, a, c, hbar, pos_embed, w1, w2 = ctx.saved_tensors
+        l, d, nb, nbp, vdtype = ctx.cfg
+        B, G, T, dk = keys.shape
+        U = w1.shape[0]
+        dkc = dk_cmp[..., :nb].transpose(-1, -2).float().contiguous()              # [B,G,nb,dk]
+        dw2 = dkc.reshape(-1, dk).t() @ hbar.reshape(-1, U)
+        db2 = dkc.reshape(-1, dk).sum(0)
+        dhbar = torch.matmul(dkc, w2.float())                                       # [B,G,nb,U]
+        da, dc, dvals = ops.phi_pool_bwd(a, c, dhbar, dv_cmp, l, d, nb)
+        w1k, w1p = w1[:, :dk].float(), w1[:, dk:].float()
+        dkeys = torch.matmul(da, w1k)                                               # [B,G,T,dk]
+        dw1k = da.reshape(-1, U).t() @ keys.float().reshape(-1, dk)
+        dw1p = dc.t() @ pos_embed.float()
+        dpos = dc @ w1p
+        dw1 = torch.cat([dw1k, dw1p], dim=1)
+        return (dkeys.to(keys.dtype), dvals.to(vdtype), dpos.to(pos_embed.dtype), dw1.to(w1.dtype),
+                dc.sum(0).to(w1.dtype), dw2.to(w2.dtype), db2.to(w2.dtype), None, None)
+
+
+class _GateMix(torch.autograd.Function):
+    """out = g0*o_cmp + g1*o_slc + g2*o_win with gates from logits [B,T,3H] (nsa/kernels.py:2446-2463)."""
+
+    @staticmethod
+    def forward(ctx, logits, o_cmp, o_slc, o_win, gate_mode):
+        out, gates = ops.gate_mix_fwd(logits, o_cmp, o_slc, o_win, gate_mode)
+        ctx.save_for_backward(gates, o_cmp, o_slc, o_win)
+        ctx.gate_mode, ctx.ldtype = gate_mode, logits.dtype
+        ctx.mark_non_differentiable(gates)
+        return out, gates
+
+    @staticmethod
+    def backward(ctx, dout, _dgates):
+        gates, o_cmp, o_slc, o_win = ctx.saved_tensors
+        d0, d1, d2, dlogits = ops.gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, ctx.gate_mode)
+        return dlogits.to(ctx.ldtype), d0, d1, d2, None
+
+
+def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv_compress=None, kv_sliding=None,
+              scale: Optional[float] = None, return_info: bool = False):
+    """The NSA hot path between the q/k/v projections and o_proj (nsa/kernels.py:2298-2463).
+
+    q [B,H,T,dk]; k_* [B,G,dk,T]; v_* [B,G,T,dv]; gate_logits [B,T,3H]; phi_params =
+    (pos_embed [l,l], w1 [2dk,dk+l], b1, w2 [dk,2dk], b2).  One (k,v) feeds all branches unless
+    ``kv_compress`` / ``kv_sliding`` are given.  Returns the mixed output [B,H,T,dv] (and a dict with
+    indices, gates, k_cmp, v_cmp, block_ends when ``return_info``).
+    """
+    cfg = config
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    kc_src, vc_src = kv_compress if kv_compress is not None else (k_slc, v_slc)
+    kw, vw = kv_sliding if kv_sliding is not None else (k_slc, v_slc)
+    T = q.shape[2]
+    pos_embed, w1, b1, w2, b2 = phi_params
+    k_cmp, v_cmp = _PhiCompress.apply(kc_src.transpose(-1, -2), vc_src, pos_embed, w1, b1, w2, b2, cfg.l, cfg.d)
+    nb = (T - cfg.l) // cfg.d + 1
+    block_ends = torch.full((k_cmp.shape[-1],), PAD_BLOCK_END, device=q.device, dtype=torch.int32)
+    block_ends[:nb] = torch.arange(nb, device=q.device, dtype=torch.int32) * cfg.d + (cfg.l - 1)
+    n_fixed = cfg.n_fixed if cfg.include_fixed_in_selection else 0
+    indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale)
+    o_cmp = CompressionAttention.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, scale, cfg)
+    o_slc = SelectionAttention.apply(q, k_slc, v_slc, indices, scale, cfg)
+    o_win = SlidingWindowAttention.apply(q, kw, vw, scale, cfg.w, cfg)
+    out, gates = _GateMix.apply(gate_logits, o_cmp, o_slc, o_win, cfg.gate_mode)
+    if return_info:
+        return out, dict(indices=indices, gates=gates, k_cmp=k_cmp, v_cmp=v_cmp, block_ends=block_ends,
+                         o_cmp=o_cmp, o_slc=o_slc, o_win=o_win)
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# module (nsa/kernels.py:2043-2507)
+# --------------------------------------------------------------------------------------------------
+
+class NSAAttention(torch.nn.Module):
+    """Drop-in for the reference's ``NSAAttention``: same parameter names (so its state_dicts load),
+    same ``forward(hidden_states, attention_mask=None, output_attentions=False) -> (out, info)``."""
+
+    def __init__(self, config: NSAConfig):
+        super().__init__()
+        self.config = config
+        c = config
+        lin = torch.nn.Linear
+        self.q_proj = lin(c.d_model, c.n_heads * c.head_dim_qk, bias=c.use_bias)
+        self.k_compress = lin(c.d_model, c.n_kv_groups * c.head_dim_qk, bias=c.use_bias)
+        self.v_compress = lin(c.d_model, c.n_kv_groups * c.head_dim_v, bias=c.use_bias)
+        self.k_select = lin(c.d_model, c.n_kv_groups * c.head_dim_qk, bias=c.use_bias)
+        self.v_select = lin(c.d_model, c.n_kv_groups * c.head_dim_v, bias=c.use_bias)
+        self.k_sliding = lin(c.d_model, c.n_kv_groups * c.head_dim_qk, bias=c.use_bias)
+        self.v_sliding = lin(c.d_model, c.n_kv_groups * c.head_dim_v, bias=c.use_bias)
+        self.pos_embed = torch.nn.Embedding(c.l, c.l)
+        self.compress_mlp = torch.nn.Sequential(lin(c.head_dim_qk + c.l, c.head_dim_qk * 2), torch.nn.ReLU(),
+                                                lin(c.head_dim_qk * 2, c.head_dim_qk))
+        self.gate_mlp = torch.nn.Sequential(lin(c.d_model, c.d_model // 2), torch.nn.ReLU(),
+                                            lin(c.d_model // 2, 3 * c.n_heads))
+        self.o_proj = lin(c.n_heads * c.head_dim_v, c.d_model, bias=c.use_bias)
+        self.dropout = torch.nn.Dropout(c.dropout_p)
+        self.scale = 1.0 / math.sqrt(c.head_dim_qk)
+
+    def _phi_params(self):
+        m = self.compress_mlp
+        return (self.pos_embed.weight, m[0].weight, m[0].bias, m[2].weight, m[2].bias)
+
+    def compress_tokens(self, keys: torch.Tensor, values: torch.Tensor):
+        """keys [B,G,T,dk], values [B,G,T,dv] -> (k_cmp [B,G,dk,nbp], v_cmp [B,G,nbp,dv],
+        block_ends [nbp] int32, n_blocks_actual); nbp = block count padded to a power of two with zero
+        blocks whose block end is 999999."""
+        c = self.config
+        T = keys.shape[2]
+        nb = (T - c.l) // c.d + 1
+        k_cmp, v_cmp = _PhiCompress.apply(keys, values, *self._phi_params(), c.l, c.d)
+        block_ends = torch.full((k_cmp.shape[-1],), PAD_BLOCK_END, device=keys.device, dtype=torch.int32)
+        block_ends[:nb] = torch.arange(nb, device=keys.device, dtype=torch.int32) * c.d + (c.l - 1)
+        return k_cmp.to(keys.dtype), v_cmp, block_ends, nb
+
+    def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                output_attentions: bool = False) -> Tuple[torch.Tensor, Optional[Dict]]:
+        c = self.config
+        B, T, _ = hidden_states.shape
+        H, G, dk, dv = c.n_heads, c.n_kv_groups, c.head_dim_qk, c.head_dim_v
+        q = self.q_proj(hidden_states).view(B, T, H, dk).transpose(1, 2).contiguous()           # [B,H,T,dk]
+
+        def kv(kp, vp):
+            k = kp(hidden_states).view(B, T, G, dk).permute(0, 2, 3, 1).contiguous()             # [B,G,dk,T]
+            v = vp(hidden_states).view(B, T, G, dv).transpose(1, 2).contiguous()                 # [B,G,T,dv]
+            return k, v
+
+        k_sel, v_sel = kv(self.k_select, self.v_select)
+        gate_logits = self.gate_mlp(hidden_states)                                               # [B,T,3H]
+        out, info = nsa_layer(q, k_sel, v_sel, gate_logits, self._phi_params(), c,
+                              kv_compress=kv(self.k_compress, self.v_compress),
+                              kv_sliding=kv(self.k_sliding, self.v_sliding), scale=self.scale, return_info=True)
+        y = self.o_proj(out.transpose(1, 2).reshape(B, T, H * dv))
+        y = self.dropout(y)
+        attn_info = None
+        if output_attentions:
+            with torch.no_grad():
+                p_cmp = ops.cmp_probs(q, info["k_cmp"], info["block_ends"], self.scale)
+                sel = ops.eq9_scores(p_cmp, c.l, c.d, c.l_prime)
+            attn_info = {
+                "compression_scores": p_cmp.to(q.dtype),
+                "selection_scores": sel.to(q.dtype),
+                "selected_indices": info["indices"].to(torch.int64),
+                "gates": info["gates"].permute(0, 2, 1, 3).to(q.dtype),                         # [B,T,H,3]
+            }
+        return y, attn_info
+
+
+# --------------------------------------------------------------------------------------------------
+# launcher shims for the raw kernel-call contract (README.md:55-101, examples/basic_usage.py:48-114)
+# --------------------------------------------------------------------------------------------------
+
+def _names(prefix, dims):
+    return [f"stride_{prefix}{d}" for d in dims]
+
+
+_Q, _K, _V, _O = _names("q", "zhmk"), _names("k", "zgnk"), _names("v", "zgnk"), _names("o", "zhmk")
+_BI = _names("b", "zgmn")
+_LM = _names("l", "zhm") + _names("m", "zhm")
+_DG = _names("dq", "zhmk") + _names("dk", "zgnk") + _names("dv", "zgnk")
+
+
+class _Launcher:
+    """``launcher[grid](*positional, **constexpr)`` with the reference kernel's parameter order.
+
+    ``grid`` is accepted and ignored (the CUDA kernels size their own grids), as are BLOCK_M/BLOCK_N.
+    The strides passed by the caller are honoured as given; if they address memory beyond a tensor's
+    storage (the contract tests pass wrong strides on purpose), the tensor is first copied into a
+    zero-padded buffer so that nothing is read out of bounds.
+    """
+
+    def __init__(self, name: str, positional: List[str], kind: str, backward: bool):
+        self.__name__ = name
+        self.positional, self.kind, self.backward = positional, kind, backward
+
+    def __getitem__(self, grid):
+        def launch(*args, **kwargs):
+            if len(args) > len(self.positional):
+                raise TypeError(f"{self.__name__}: too many positional arguments")
+            named = dict(zip(self.positional, args))
+            dup = set(named) & set(kwargs)
+            if dup:
+                raise TypeError(f"{self.__name__}: got multiple values for {sorted(dup)}")
+            named.update(kwargs)
+            return self._run(named)
+        return launch
+
+    @staticmethod
+    def _safe(t: torch.Tensor, strides, dims):
+        need = 1 + sum((int(n) - 1) * int(s) for n, s in zip(dims, strides) if n > 0)
+        have = t.untyped_storage().nbytes() // t.element_size() - t.storage_offset()
+        if need <= have:
+            return t
+        buf = torch.zeros(need, device=t.device, dtype=t.dtype)
+        flat = torch.as_strided(t, (have,), (1,))
+        buf[:have] = flat
+        return buf
+
+    def _run(self, a):
+        from ._lib import check, dtype_code, i64, lib, ptr, require_cuda, stream_ptr
+        kind = self.kind
+        Q, V, Out = a["Q"], a["V"], a["Out"]
+        K = a["K"] if kind != "cmp" else a.get("K_compressed", a.get("K_blocks"))
+        if kind == "cmp":
+            V = a.get("V_compressed", a.get("V_blocks"))
+        B, H, G = int(a["Z"]), int(a["H"]), int(a["N_KV_GROUPS"])
+        dk, dv = Q.shape[-1], V.shape[-1]
+        if kind == "win":
+            Tq = Tk = int(a["N_CTX"])
+        elif kind == "cmp":
+            Tq, Tk = int(a["N_CTX_Q"]), int(a["N_BLOCKS"])
+        else:
+            Tq, Tk = int(a["N_CTX_Q"]), int(a["N_CTX_KV"])
+        scale = float(a["sm_scale"])
+        dev = require_cuda(Q, K, V, Out)
+        sq, sk, sv, so = ([a[n] for n in names] for names in (_Q, _K, _V, _O))
+        Q = self._safe(Q, sq, (B, H, Tq, dk))
+        K = self._safe(K, sk, (B, G, Tk, dk))
+        V = self._safe(V, sv, (B, G, Tk, dv))
+        L, M = a["L"], a["M"]
+        strides = sq + sk + sv + so + [a[n] for n in _LM]
+        tail = []
+        idx = None
+        if self.backward:
+            strides += [a[n] for n in _DG]
+        if kind == "slc":
+            idx = a["Block_indices"]
+            if idx.dtype != torch.int32:
+                raise TypeError("Block_indices must be int32")
+            strides += [a[n] for n in _BI]
+            if not bool(a.get("IS_CAUSAL", True)):
+                raise NotImplementedError("selection kernels are causal")
+        code = dtype_code(Q)
+        st = stream_ptr(dev)
+        with torch.cuda.device(dev):
+            if not self.backward:
+                if kind == "win":
+                    rc = lib.nsa_sliding_fwd(ptr(Q), ptr(K), ptr(V), ptr(Out), ptr(L), ptr(M), i64(strides), B, H, G, Tq,
+                                             dk, dv, int(a["WINDOW_SIZE"]), scale, code, st)
+                elif kind == "cmp":
+                    be = a["Block_ends"].to(torch.int32).contiguous()
+                    rc = lib.nsa_cmp_attn_fwd(ptr(Q), ptr(K), ptr(V), ptr(be), ptr(Out), ptr(L), ptr(M), i64(strides), B, H,
+                                              G, Tq, Tk, dk, dv, scale, code, st)
+                else:
+                    rc = lib.nsa_slc_fwd(ptr(Q), ptr(K), ptr(V), ptr(idx), ptr(Out), ptr(L), ptr(M), i64(strides), B, H, G,
+                                         Tq, Tk, int(a["N_BLOCKS"]), int(a["BLOCK_SIZE_SELECTION"]), dk, dv, scale, code, st)
+            else:
+                dO, dQ, dK, dV = a["dOut"], a["dQ"], a["dK"], a["dV"]
+                if kind == "win":
+                    rc = lib.nsa_sliding_bwd(ptr(Q), ptr(K), ptr(V), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ), ptr(dK),
+                                             ptr(dV), i64(strides), B, H, G, Tq, dk, dv, int(a["WINDOW_SIZE"]), scale, code, st)
+                elif kind == "cmp":
+                    be = a["Block_ends"].to(torch.int32).contiguous()
+                    rc = lib.nsa_cmp_attn_bwd(ptr(Q), ptr(K), ptr(V), ptr(be), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ),
+                                              ptr(dK), ptr(dV), i64(strides), B, H, G, Tq, Tk, dk, dv, scale, code, st)
+                else:
+                    n = int(a["N_BLOCKS"])
+                    lp = int(a["BLOCK_SIZE_SELECTION"])
+                    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, G, Tq, Tk, n, lp)
+                    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+                    rc = lib.nsa_slc_bwd(ptr(Q), ptr(K), ptr(V), ptr(idx), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ),
+                                         ptr(dK), ptr(dV), i64(strides), B, H, G, Tq, Tk, n, lp, dk, dv, scale, code,
+                                         ptr(ws), nbytes, st)
+        check(rc, self.__name__)
+
+
+def _sig(kind: str, backward: bool) -> List[str]:
+    kv = {"win": ["K", "V"], "cmp": ["K_compressed" if not backward else "K_blocks",
+                                     "V_compressed" if not backward else "V_blocks", "Block_ends"],
+          "slc": ["K", "V", "Block_indices"]}[kind]
+    head = ["Q"] + kv + ["Out"] + (["dOut"] if backward else []) + ["sm_scale", "L", "M"]
+    strides = _Q + _K + _V + _O + (_BI if kind == "slc" else []) + _LM
+    tail = (["dQ", "dK", "dV"] + _DG) if backward else []
+    return head + strides + tail
+
+
+_nsa_sliding_window_fwd_kernel = _Launcher("_nsa_sliding_window_fwd_kernel", _sig("win", False), "win", False)
+_nsa_sliding_window_bwd_kernel = _Launcher("_nsa_sliding_window_bwd_kernel", _sig("win", True), "win", True)
+_nsa_compression_fwd_kernel = _Launcher("_nsa_compression_fwd_kernel", _sig("cmp", False), "cmp", False)
+_nsa_compression_bwd_kernel = _Launcher("_nsa_compression_bwd_kernel", _sig("cmp", True), "cmp", True)
+_nsa_sparse_selection_fwd_kernel = _Launcher("_nsa_sparse_selection_fwd_kernel", _sig("slc", False), "slc", False)
+_nsa_sparse_selection_bwd_kernel = _Launcher("_nsa_sparse_selection_bwd_kernel", _sig("slc", True), "slc", True)

@@ -1,0 +1,252 @@
+"""Tensor-level wrappers of the C-ABI entry points: compute strides, pick the stream, check status.
+
+Each function launches asynchronously on the current CUDA stream of the tensors' device and returns
+nothing but its outputs; shapes follow the reference project's kernel-call contract
+(K is [B,G,dk,T] in memory, dK comes back time-major [B,G,T,dk]).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check, dtype_code, i64, lib, ptr, require_cuda, stream_ptr
+
+
+def _k_strides(k: torch.Tensor):
+    """Strides of a [B,G,dk,T] key tensor in the contract's (z, g, n=time, k=dk) order."""
+    return [k.stride(0), k.stride(1), k.stride(3), k.stride(2)]
+
+
+def _fwd_strides(q, k, v, o, L, M):
+    return list(q.stride()) + _k_strides(k) + list(v.stride()) + list(o.stride()) + list(L.stride()) + list(M.stride())
+
+
+def _stats(q, o_dv):
+    B, H, T, _ = q.shape
+    o = torch.empty(B, H, T, o_dv, device=q.device, dtype=q.dtype)
+    L = torch.empty(B, H, T, device=q.device, dtype=torch.float32)
+    M = torch.empty(B, H, T, device=q.device, dtype=torch.float32)
+    return o, L, M
+
+
+# ------------------------------------------------------------------------------------------------
+# the three branches
+# ------------------------------------------------------------------------------------------------
+
+def sliding_fwd(q, k, v, window: int, scale: float):
+    dev = require_cuda(q, k, v)
+    B, H, T, dk = q.shape
+    G, dv = k.shape[1], v.shape[-1]
+    o, L, M = _stats(q, dv)
+    with torch.cuda.device(dev):
+        check(lib.nsa_sliding_fwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(L), ptr(M), i64(_fwd_strides(q, k, v, o, L, M)),
+                                  B, H, G, T, dk, dv, int(window), float(scale), dtype_code(q), stream_ptr(dev)),
+              "nsa_sliding_fwd")
+    return o, L, M
+
+
+def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float):
+    dev = require_cuda(q, k, v, o, do, L, M)
+    B, H, T, dk = q.shape
+    G, dv = k.shape[1], v.shape[-1]
+    if do.stride() != o.stride():
+        do = do.contiguous()
+        o = o.contiguous()
+    dq = torch.empty_like(q)
+    dkey = torch.zeros(B, G, T, dk, device=dev, dtype=q.dtype)
+    dval = torch.zeros(B, G, T, dv, device=dev, dtype=q.dtype)
+    s = _fwd_strides(q, k, v, o, L, M) + list(dq.stride()) + list(dkey.stride()) + list(dval.stride())
+    with torch.cuda.device(dev):
+        check(lib.nsa_sliding_bwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq), ptr(dkey), ptr(dval),
+                                  i64(s), B, H, G, T, dk, dv, int(window), float(scale), dtype_code(q), stream_ptr(dev)),
+              "nsa_sliding_bwd")
+    return dq, dkey, dval
+
+
+def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float):
+    dev = require_cuda(q, k_cmp, v_cmp, block_ends)
+    B, H, T, dk = q.shape
+    G, NB, dv = k_cmp.shape[1], k_cmp.shape[-1], v_cmp.shape[-1]
+    be = block_ends.to(torch.int32).contiguous()
+    o, L, M = _stats(q, dv)
+    with torch.cuda.device(dev):
+        check(lib.nsa_cmp_attn_fwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(L), ptr(M),
+                                   i64(_fwd_strides(q, k_cmp, v_cmp, o, L, M)), B, H, G, T, NB, dk, dv, float(scale),
+                                   dtype_code(q), stream_ptr(dev)), "nsa_cmp_attn_fwd")
+    return o, L, M
+
+
+def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float):
+    dev = require_cuda(q, k_cmp, v_cmp, block_ends, o, do, L, M)
+    B, H, T, dk = q.shape
+    G, NB, dv = k_cmp.shape[1], k_cmp.shape[-1], v_cmp.shape[-1]
+    be = block_ends.to(torch.int32).contiguous()
+    if do.stride() != o.stride():
+        do = do.contiguous()
+        o = o.contiguous()
+    dq = torch.empty_like(q)
+    dkc = torch.zeros(B, G, NB, dk, device=dev, dtype=q.dtype)
+    dvc = torch.zeros(B, G, NB, dv, device=dev, dtype=q.dtype)
+    s = _fwd_strides(q, k_cmp, v_cmp, o, L, M) + list(dq.stride()) + list(dkc.stride()) + list(dvc.stride())
+    with torch.cuda.device(dev):
+        check(lib.nsa_cmp_attn_bwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq),
+                                   ptr(dkc), ptr(dvc), i64(s), B, H, G, T, NB, dk, dv, float(scale), dtype_code(q),
+                                   stream_ptr(dev)), "nsa_cmp_attn_bwd")
+    return dq, dkc, dvc
+
+
+def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float):
+    dev = require_cuda(q, k, v, indices_i32)
+    B, H, Tq, dk = q.shape
+    G, Tkv, dv = k.shape[1], k.shape[-1], v.shape[-1]
+    assert indices_i32.dtype == torch.int32
+    o, L, M = _stats(q, dv)
+    s = _fwd_strides(q, k, v, o, L, M) + list(indices_i32.stride())
+    with torch.cuda.device(dev):
+        check(lib.nsa_slc_fwd(ptr(q), ptr(k), ptr(v), ptr(indices_i32), ptr(o), ptr(L), ptr(M), i64(s), B, H, G, Tq, Tkv,
+                              indices_i32.shape[-1], int(l_prime), dk, dv, float(scale), dtype_code(q), stream_ptr(dev)),
+              "nsa_slc_fwd")
+    return o, L, M
+
+
+def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float):
+    dev = require_cuda(q, k, v, indices_i32, o, do, L, M)
+    B, H, Tq, dk = q.shape
+    G, Tkv, dv = k.shape[1], k.shape[-1], v.shape[-1]
+    n = indices_i32.shape[-1]
+    if do.stride() != o.stride():
+        do = do.contiguous()
+        o = o.contiguous()
+    dq = torch.empty_like(q)
+    dkey = torch.zeros(B, G, Tkv, dk, device=dev, dtype=q.dtype)
+    dval = torch.zeros(B, G, Tkv, dv, device=dev, dtype=q.dtype)
+    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, G, Tq, Tkv, n, int(l_prime))
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    s = (_fwd_strides(q, k, v, o, L, M) + list(dq.stride()) + list(dkey.stride()) + list(dval.stride())
+         + list(indices_i32.stride()))
+    with torch.cuda.device(dev):
+        check(lib.nsa_slc_bwd(ptr(q), ptr(k), ptr(v), ptr(indices_i32), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq),
+                              ptr(dkey), ptr(dval), i64(s), B, H, G, Tq, Tkv, n, int(l_prime), dk, dv, float(scale),
+                              dtype_code(q), ptr(ws), nbytes, stream_ptr(dev)), "nsa_slc_bwd")
+    return dq, dkey, dval
+
+
+# ------------------------------------------------------------------------------------------------
+# phi pooling, scoring, gates
+# ------------------------------------------------------------------------------------------------
+
+def phi_pool_fwd(a, c, v, l: int, d: int, n_blocks: int, nbp: int):
+    """a [B,G,T,U] fp32, c [l,U] fp32, v [B,G,T,dv] -> hbar [B,G,n_blocks,U] fp32, v_cmp [B,G,nbp,dv] (zero padded)."""
+    dev = require_cuda(a, c, v)
+    B, G, T, U = a.shape
+    dv = v.shape[-1]
+    a, c = a.contiguous(), c.contiguous()
+    hbar = torch.empty(B, G, n_blocks, U, device=dev, dtype=torch.float32)
+    v_cmp = torch.zeros(B, G, nbp, dv, device=dev, dtype=v.dtype)
+    with torch.cuda.device(dev):
+        check(lib.nsa_phi_pool_fwd(ptr(a), ptr(c), ptr(v), i64(v.stride()), ptr(hbar), ptr(v_cmp), B, G, T, U, dv, int(l),
+                                   int(d), int(n_blocks), int(nbp), dtype_code(v), stream_ptr(dev)), "nsa_phi_pool_fwd")
+    return hbar, v_cmp
+
+
+def phi_pool_bwd(a, c, dhbar, dv_cmp, l: int, d: int, n_blocks: int):
+    """-> da [B,G,T,U], dc [l,U] (summed over batch and group), dv [B,G,T,dv]; all fp32."""
+    dev = require_cuda(a, c, dhbar, dv_cmp)
+    B, G, T, U = a.shape
+    nbp, dvd = dv_cmp.shape[2], dv_cmp.shape[3]
+    a, c, dhbar, dv_cmp = a.contiguous(), c.contiguous(), dhbar.float().contiguous(), dv_cmp.float().contiguous()
+    da = torch.empty_like(a)
+    dc_part = torch.empty(B * G, int(l), U, device=dev, dtype=torch.float32)
+    dv = torch.empty(B, G, T, dvd, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.nsa_phi_pool_bwd(ptr(a), ptr(c), ptr(dhbar), ptr(dv_cmp), ptr(da), ptr(dc_part), ptr(dv), B, G, T, U,
+                                   dvd, int(l), int(d), int(n_blocks), nbp, stream_ptr(dev)), "nsa_phi_pool_bwd")
+    return da, dc_part.sum(0), dv
+
+
+def score_topn(q, k_cmp_f32, block_ends, l: int, d: int, l_prime: int, n: int, n_fixed: int, scale: float):
+    """q [B,H,T,dk], k_cmp fp32 [B,G,dk,nbp] -> int32 indices [B,G,T,n]."""
+    dev = require_cuda(q, k_cmp_f32, block_ends)
+    B, H, T, dk = q.shape
+    G, nbp = k_cmp_f32.shape[1], k_cmp_f32.shape[-1]
+    kc = k_cmp_f32.float().contiguous()
+    be = block_ends.to(torch.int32).contiguous()
+    out = torch.empty(B, G, T, n, device=dev, dtype=torch.int32)
+    with torch.cuda.device(dev):
+        check(lib.nsa_score_topn(ptr(q), i64(q.stride()), ptr(kc), ptr(be), ptr(out), B, H, G, T, dk, nbp, int(l), int(d),
+                                 int(l_prime), int(n), int(n_fixed), float(scale), dtype_code(q), stream_ptr(dev)),
+              "nsa_score_topn")
+    return out
+
+
+def topn_from_scores(scores, G: int, l_prime: int, n: int, n_fixed: int):
+    """scores [B,H,T,n_sel] -> int32 indices [B,G,T,n]."""
+    dev = require_cuda(scores)
+    B, H, T, n_sel = scores.shape
+    sc = scores.float().contiguous()
+    out = torch.empty(B, G, T, n, device=dev, dtype=torch.int32)
+    with torch.cuda.device(dev):
+        check(lib.nsa_topn_from_scores(ptr(sc), ptr(out), B, H, G, T, n_sel, int(l_prime), int(n), int(n_fixed),
+                                       stream_ptr(dev)), "nsa_topn_from_scores")
+    return out
+
+
+def cmp_probs(q, k_cmp_f32, block_ends, scale: float):
+    """Eq. 8 probabilities materialised: [B,H,T,nbp] fp32 (diagnostics only)."""
+    dev = require_cuda(q, k_cmp_f32, block_ends)
+    B, H, T, dk = q.shape
+    G, nbp = k_cmp_f32.shape[1], k_cmp_f32.shape[-1]
+    kc = k_cmp_f32.float().contiguous()
+    be = block_ends.to(torch.int32).contiguous()
+    out = torch.empty(B, H, T, nbp, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.nsa_cmp_probs(ptr(q), i64(q.stride()), ptr(kc), ptr(be), ptr(out), B, H, G, T, dk, nbp, float(scale),
+                                dtype_code(q), stream_ptr(dev)), "nsa_cmp_probs")
+    return out
+
+
+def eq9_scores(p_cmp, l: int, d: int, l_prime: int):
+    """[..., n_cmp] -> [..., ceil(n_cmp/(l'/d))] fp32."""
+    dev = require_cuda(p_cmp)
+    n_cmp = p_cmp.shape[-1]
+    s_ = l_prime // d
+    n_sel = (n_cmp + s_ - 1) // s_
+    p = p_cmp.float().contiguous()
+    out = torch.empty(*p.shape[:-1], n_sel, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.nsa_eq9_scores(ptr(p), ptr(out), p.numel() // n_cmp, n_cmp, int(l), int(d), int(l_prime),
+                                 stream_ptr(dev)), "nsa_eq9_scores")
+    return out
+
+
+def gate_mix_fwd(logits, o_cmp, o_slc, o_win, gate_mode: str):
+    """logits [B,T,3H]; branch outputs [B,H,T,dv] -> out [B,H,T,dv], gates [B,H,T,3] fp32."""
+    dev = require_cuda(logits, o_cmp, o_slc, o_win)
+    B, H, T, dv = o_cmp.shape
+    lg = logits.float().contiguous()
+    o_cmp, o_slc, o_win = o_cmp.contiguous(), o_slc.contiguous(), o_win.contiguous()
+    out = torch.empty_like(o_cmp)
+    gates = torch.empty(B, H, T, 3, device=dev, dtype=torch.float32)
+    mode = _lib.GATE_SOFTMAX if gate_mode == "softmax" else _lib.GATE_SIGMOID
+    with torch.cuda.device(dev):
+        check(lib.nsa_gate_mix_fwd(ptr(lg), ptr(o_cmp), ptr(o_slc), ptr(o_win), ptr(out), ptr(gates), B, H, T, dv, mode,
+                                   dtype_code(o_cmp), stream_ptr(dev)), "nsa_gate_mix_fwd")
+    return out, gates
+
+
+def gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, gate_mode: str):
+    """-> (do_cmp, do_slc, do_win, dlogits [B,T,3H] fp32)."""
+    dev = require_cuda(gates, o_cmp, o_slc, o_win, dout)
+    B, H, T, dv = o_cmp.shape
+    dout = dout.contiguous()
+    o_cmp, o_slc, o_win = o_cmp.contiguous(), o_slc.contiguous(), o_win.contiguous()
+    d0, d1, d2 = torch.empty_like(o_cmp), torch.empty_like(o_cmp), torch.empty_like(o_cmp)
+    dlogits = torch.empty(B, T, 3 * H, device=dev, dtype=torch.float32)
+    mode = _lib.GATE_SOFTMAX if gate_mode == "softmax" else _lib.GATE_SIGMOID
+    with torch.cuda.device(dev):
+        check(lib.nsa_gate_mix_bwd(ptr(gates), ptr(o_cmp), ptr(o_slc), ptr(o_win), ptr(dout), ptr(d0), ptr(d1), ptr(d2),
+                                   ptr(dlogits), B, H, T, dv, mode, dtype_code(o_cmp), stream_ptr(dev)), "nsa_gate_mix_bwd")
+    return d0, d1, d2, dlogits
