@@ -45,6 +45,15 @@ enum {
   NSA_ERR_UNSUPPORTED = -4 /* shape outside what the requested kernel family covers */
 };
 
+/* Kernel-family switch for testing: 0 (default) uses the tensor-core (tcgen05) kernels wherever a call
+ * qualifies (bf16, canonical contiguous layouts, supported head dims, T multiple of 128) and the
+ * stride-generic kernels elsewhere; 1 forces the stride-generic kernels.  Process-wide. */
+NSA_API int nsa_set_kernel_family(int family);
+/* Number of thread blocks of the tensor-core kernels that ever gave up on a bounded barrier wait
+ * (0 in a healthy run; their output is then invalid).  Synchronises the device.  reset != 0 clears
+ * the counter.  Negative = error. */
+NSA_API int nsa_device_timeouts(int reset);
+
 /* Message for the last non-zero status returned on the calling thread. */
 NSA_API const char* nsa_last_error(void);
 /* Library / build identification: "nsa_b200 <version> sm_100a". */
@@ -68,11 +77,14 @@ NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void* v, const v
 
 /* Attention over compressed tokens, block i visible iff block_ends[i] <= t; a row that sees no block
  * gets out = 0, L = M = -inf.  k_cmp is [B,G,dk,NB] with strides passed (z,g,n=block,k), v_cmp
- * [B,G,NB,dv]; dk_cmp is written [B,G,NB,dk].
+ * [B,G,NB,dv]; dk_cmp is written [B,G,NB,dk].  Layout hint (forward): blocks_d > 0 asserts that
+ * block_ends[i] == i*blocks_d + blocks_l - 1 for i < blocks_n and that later blocks are never
+ * visible, which lets the tensor-core kernel skip tiles; blocks_d == 0 makes no assumption.
  * Replaces _nsa_compression_fwd_kernel / _bwd_kernel (nsa/kernels.py:1533-1687, 1690-1917). */
 NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                      void* out, float* L, float* M, const int64_t* strides22, int B, int H, int G,
-                     int T, int NB, int dk, int dv, float scale, int dtype, void* stream);
+                     int T, int NB, int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d,
+                     int blocks_n, void* stream);
 NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                      const void* out, const void* dout, const float* L, const float* M, void* dq,
                      void* dk_cmp, void* dv_cmp, const int64_t* strides34, int B, int H, int G, int T,

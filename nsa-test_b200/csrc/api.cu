@@ -2,6 +2,7 @@
 // Argument checking happens here; kernels never see a null pointer or an inconsistent size.
 #include "attn_args.cuh"
 #include "common.cuh"
+#include "fa_sm100.cuh"
 
 namespace nsa {
 
@@ -43,9 +44,38 @@ static int check_common(const char* who, int B, int H, int G, int Tq, int Tk, in
   return NSA_OK;
 }
 
+static int g_kernel_family = 0;  // 0: tensor-core kernels where they apply, 1: stride-generic kernels only
+
+// canonical contiguous layouts: q [B,H,T,dk], k [B,G,dk,Tk] (strides given as z,g,n,k), v [B,G,Tk,dv], o [B,H,T,dv]
+static bool canonical_fwd(const int64_t* s, int H, int G, int Tq, int Tk, int dk, int dv) {
+  const int64_t q[4] = {(int64_t)H * Tq * dk, (int64_t)Tq * dk, dk, 1};
+  const int64_t k[4] = {(int64_t)G * dk * Tk, (int64_t)dk * Tk, 1, Tk};
+  const int64_t v[4] = {(int64_t)G * Tk * dv, (int64_t)Tk * dv, dv, 1};
+  const int64_t o[4] = {(int64_t)H * Tq * dv, (int64_t)Tq * dv, dv, 1};
+  const int64_t lm[3] = {(int64_t)H * Tq, Tq, 1};
+  for (int i = 0; i < 4; ++i)
+    if (s[i] != q[i] || s[4 + i] != k[i] || s[8 + i] != v[i] || s[12 + i] != o[i]) return false;
+  for (int i = 0; i < 3; ++i)
+    if (s[16 + i] != lm[i] || s[19 + i] != lm[i]) return false;
+  return true;
+}
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 }  // namespace nsa
 
 using namespace nsa;
+
+extern "C" NSA_API int nsa_set_kernel_family(int family) {
+  NSA_REQUIRE(family == 0 || family == 1, "kernel family must be 0 (auto) or 1 (generic)");
+  g_kernel_family = family;
+  return NSA_OK;
+}
+
+extern "C" NSA_API int nsa_device_timeouts(int reset) {
+  int n = 0;
+  if (int rc = fa_fwd_sm100_timeouts(&n, reset != 0)) return rc;
+  return n;
+}
 
 extern "C" NSA_API const char* nsa_last_error(void) { return error_buffer(); }
 extern "C" NSA_API const char* nsa_version(void) { return "nsa_b200 0.1.0 sm_100a"; }
@@ -56,6 +86,10 @@ extern "C" NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void*
   if (int rc = check_common("sliding_fwd", B, H, G, T, T, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && out && strides, "sliding_fwd: null pointer");
   NSA_REQUIRE(window > 0, "sliding_fwd: window must be positive");
+  if (g_kernel_family == 0 && dtype == NSA_BF16 && L && M && fa_fwd_sm100_supported(H, G, T, T, dk, dv) &&
+      canonical_fwd(strides, H, G, T, T, dk, dv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
+      (int64_t)B * (H / 2) <= 65535)
+    return fa_fwd_sm100(q, k, v, out, L, M, B, H, G, T, T, dk, dv, kWin, window, 0, 0, 0, scale, (cudaStream_t)stream);
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o = out; a.L = L; a.M = M;
   fill_fwd_strides(a, strides);
@@ -79,9 +113,17 @@ extern "C" NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void*
 
 extern "C" NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                                 void* out, float* L, float* M, const int64_t* strides, int B, int H, int G, int T,
-                                int NB, int dk, int dv, float scale, int dtype, void* stream) {
+                                int NB, int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d,
+                                int blocks_n, void* stream) {
   if (int rc = check_common("cmp_attn_fwd", B, H, G, T, NB, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k_cmp && v_cmp && block_ends && out && strides, "cmp_attn_fwd: null pointer");
+  NSA_REQUIRE(blocks_d >= 0 && (blocks_d == 0 || (blocks_l > 0 && blocks_n >= 0 && blocks_n <= NB)),
+              "cmp_attn_fwd: bad block layout hint (l=%d, d=%d, n=%d)", blocks_l, blocks_d, blocks_n);
+  if (g_kernel_family == 0 && blocks_d > 0 && dtype == NSA_BF16 && L && M && fa_fwd_sm100_supported(H, G, T, NB, dk, dv) &&
+      canonical_fwd(strides, H, G, T, NB, dk, dv) && aligned16(q) && aligned16(k_cmp) && aligned16(v_cmp) &&
+      aligned16(out) && (int64_t)B * (H / 2) <= 65535)
+    return fa_fwd_sm100(q, k_cmp, v_cmp, out, L, M, B, H, G, T, NB, dk, dv, kCmp, 0, blocks_l, blocks_d, blocks_n, scale,
+                        (cudaStream_t)stream);
   AttnArgs a = {};
   a.q = q; a.k = k_cmp; a.v = v_cmp; a.o = out; a.L = L; a.M = M; a.block_ends = block_ends;
   fill_fwd_strides(a, strides);

@@ -1,0 +1,427 @@
+// Dense-range flash-attention forward on 5th-generation tensor cores (tcgen05 + TMEM + TMA), used by
+// the sliding-window branch and the compressed-token branch of NSA
+// (replaces _nsa_sliding_window_fwd_kernel / _nsa_compression_fwd_kernel, nsa/kernels.py:1151-1300,
+// 1533-1687, for bf16 tensors in their canonical layouts).
+//
+// One CTA owns 128 consecutive queries of TWO heads of the same KV group, so every K/V tile staged in
+// shared memory feeds two 128-row MMA tiles.  Roles (warp-specialised, 320 threads):
+//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: one thread per query row, fp32 online softmax in the
+//                    log2 domain, lazy rescaling of O (only when the row maximum grows by > 2^8)
+//   warp 8           TMA producer: Q once, then a 2-deep ring of K tiles and a 1-deep V buffer
+//   warp 9           UMMA issuer: S_i = Q_i K^T (SS form, K is MN-major in smem), O_i += P_i V
+//                    (TS form: P is read straight from tensor memory where it aliases S_i)
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i = bf16 pairs in S_i[0,64).
+// Issue order PV0(j) QK0(j+1) PV1(j) QK1(j+1) keeps the tensor pipe busy while the other tile's
+// softmax runs.  All waits are bounded; a timeout raises a device flag readable from the host.
+#include <cuda.h>
+
+#include "attn_args.cuh"
+#include "common.cuh"
+#include "fa_sm100.cuh"
+#include "sm100_ptx.cuh"
+
+namespace nsa {
+
+using namespace ptx;
+
+static __device__ int g_fa_fwd_timeouts;  // CTAs that gave up on a barrier (0 in every healthy run)
+
+constexpr int kBM = 128;  // queries per MMA tile
+constexpr int kBN = 128;  // keys per tile
+constexpr int kFaThreads = 320;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.f;  // log2 units
+
+template <int DK, int DV>
+struct FaSmem {
+  static constexpr int kQBytes = kBM * DK * 2;
+  static constexpr int kKBytes = kBN * DK * 2;
+  static constexpr int kVBytes = kBN * DV * 2;
+  static constexpr int kKStages = 2;
+  static constexpr int oQ = 0;
+  static constexpr int oK = oQ + 2 * kQBytes;
+  static constexpr int oV = oK + kKStages * kKBytes;
+  static constexpr int oBar = oV + kVBytes;
+  static constexpr int kTotal = oBar + 256;
+  static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024 B (swizzle atom)
+};
+
+struct FaBarriers {
+  uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full[2], pv_done[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+// visible columns of a row inside the current key tile: clo < c <= chi
+template <int MODE>
+__device__ __forceinline__ void row_bounds(const FaFwdParams& p, int t, int n0, int& clo, int& chi) {
+  if (MODE == kWin) {
+    chi = t - n0;
+    clo = t - p.window - n0;
+  } else {
+    const int vis = t >= p.cmp_l - 1 ? min(p.cmp_nb - 1, (t - p.cmp_l + 1) / p.cmp_d) : -1;
+    chi = vis - n0;
+    clo = -0x40000000;
+  }
+}
+
+template <int DK, int DV, int MODE>
+__global__ void __launch_bounds__(kFaThreads, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const FaFwdParams p) {
+  using SM = FaSmem<DK, DV>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sQ = smem + SM::oQ;
+  uint8_t* sK = smem + SM::oK;
+  uint8_t* sV = smem + SM::oV;
+  FaBarriers* bar = reinterpret_cast<FaBarriers*>(smem + SM::oBar);
+  volatile int* abort = &bar->abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hpg = p.H / p.G;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) query tiles first
+  const int m0 = qt * kBM;
+  const int pairs = p.H / 2;
+  const int b = blockIdx.y / pairs, h0 = (blockIdx.y % pairs) * 2, g = h0 / hpg;
+
+  // key-tile range visited by this query tile
+  int jlo, jhi;
+  if (MODE == kWin) {
+    jlo = max(0, m0 - p.window + 1) / kBN;
+    jhi = min(m0 + kBM - 1, p.Tk - 1) / kBN;
+  } else {
+    const int tl = m0 + kBM - 1;
+    const int kmax = tl >= p.cmp_l - 1 ? min(p.cmp_nb - 1, (tl - p.cmp_l + 1) / p.cmp_d) : -1;
+    jlo = 0;
+    jhi = kmax >= 0 ? kmax / kBN : -1;
+  }
+  const int ntiles = jhi - jlo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->k_full[i], 1);
+      mbar_init(&bar->k_empty[i], 1);
+      mbar_init(&bar->s_full[i], 1);
+      mbar_init(&bar->p_full[i], 128);
+      mbar_init(&bar->pv_done[i], 1);
+    }
+    mbar_init(&bar->v_full, 1);
+    mbar_init(&bar->v_empty, 1);
+    bar->abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 9) tmem_alloc(&bar->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && ntiles > 0) {
+      prefetch_tensormap(&tmQ);
+      prefetch_tensormap(&tmK);
+      prefetch_tensormap(&tmV);
+      mbar_arrive_expect_tx(&bar->q_full, 2 * SM::kQBytes);
+      for (int i = 0; i < 2; ++i)
+        for (int c = 0; c < DK / 64; ++c)
+          tma_load_2d(&tmQ, &bar->q_full, sQ + i * SM::kQBytes + c * (kBM * 128), c * 64,
+                      (b * p.H + h0 + i) * p.Tq + m0);
+      bool ok = true;
+      int issued = 0;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int n0 = (jlo + j) * kBN, ks = j & 1;
+        ok = mbar_wait(&bar->k_empty[ks], ((j >> 1) & 1) ^ 1, abort);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bar->k_full[ks], SM::kKBytes);
+        for (int hf = 0; hf < 2; ++hf)
+          tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kKBytes + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
+        ok = mbar_wait(&bar->v_empty, (j & 1) ^ 1, abort);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bar->v_full, SM::kVBytes);
+        for (int c = 0; c < DV / 64; ++c)
+          tma_load_2d(&tmV, &bar->v_full, sV + c * (kBN * 128), c * 64, (b * p.G + g) * p.Tk + n0);
+        issued = j + 1;
+      }
+      if (!ok) {
+        // let copies already in flight land before the CTA gives its shared memory back
+        mbar_wait(&bar->q_full, 0, abort);
+        for (int j = max(0, issued - 2); j < issued; ++j) mbar_wait(&bar->k_full[j & 1], (j >> 1) & 1, abort);
+        if (issued > 0) mbar_wait(&bar->v_full, (issued - 1) & 1, abort);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ UMMA issuer (one thread)
+    if (lane == 0 && ntiles > 0) {
+      constexpr uint32_t idQK = idesc_bf16(kBM, kBN, 0, 1);
+      constexpr uint32_t idPV = idesc_bf16(kBM, DV, 0, 1);
+      const uint64_t dQ[2] = {smem_desc_sw128(smem_u32(sQ), 16, 1024), smem_desc_sw128(smem_u32(sQ + SM::kQBytes), 16, 1024)};
+      const uint64_t dK[2] = {smem_desc_sw128(smem_u32(sK), DK * 128, 1024),
+                              smem_desc_sw128(smem_u32(sK + SM::kKBytes), DK * 128, 1024)};
+      const uint64_t dV = smem_desc_sw128(smem_u32(sV), kBN * 128, 1024);
+      auto issue_qk = [&](int i, int ks) {
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + i * 128, desc_advance(dQ[i], (kk >> 2) * (kBM * 128) + (kk & 3) * 32),
+                  desc_advance(dK[ks], kk * 2048), idQK, kk > 0);
+        umma_commit(&bar->s_full[i]);
+      };
+      bool ok = mbar_wait(&bar->q_full, 0, abort) && mbar_wait(&bar->k_full[0], 0, abort);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0, 0);
+        issue_qk(1, 0);
+        umma_commit(&bar->k_empty[0]);
+      }
+      for (int j = 0; j < ntiles && ok; ++j) {
+        ok = mbar_wait(&bar->v_full, j & 1, abort);
+        for (int i = 0; i < 2 && ok; ++i) {
+          ok = mbar_wait(&bar->p_full[i], j & 1, abort);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < kBN / 16; ++kk)
+            umma_ts(tmem + 256 + i * 128, tmem + i * 128 + kk * 8, desc_advance(dV, kk * 2048), idPV, (j > 0) || (kk > 0));
+          umma_commit(&bar->pv_done[i]);
+          if (i == 1) umma_commit(&bar->v_empty);
+          if (j + 1 < ntiles) {
+            const int ks = (j + 1) & 1;
+            if (i == 0) {
+              ok = mbar_wait(&bar->k_full[ks], ((j + 1) >> 1) & 1, abort);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            issue_qk(i, ks);
+            if (i == 1) umma_commit(&bar->k_empty[ks]);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax + epilogue, one row per thread
+    const int i = warp >> 2;                   // which MMA tile / head
+    const int r = (warp & 3) * 32 + lane;      // row inside the tile == TMEM lane
+    const int t = m0 + r;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_base + i * 128;
+    const uint32_t tO = tmem + lane_base + 256 + i * 128;
+    float m_true = -CUDART_INF_F, m_ref = -CUDART_INF_F, l = 0.f;
+    bool ok = true;
+    uint32_t sv[4][32];
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int n0 = (jlo + j) * kBN;
+      ok = mbar_wait(&bar->s_full[i], j & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sv[c]);
+      tc_wait_ld();
+      // does this tile need element masks?
+      bool full;
+      if (MODE == kWin) {
+        full = (n0 + kBN - 1 <= m0) && (n0 > m0 + kBM - 1 - p.window);
+      } else {
+        full = (n0 + kBN - 1 < p.cmp_nb) && ((n0 + kBN - 1) * p.cmp_d + p.cmp_l - 1 <= m0);
+      }
+      float mx = -CUDART_INF_F;
+      if (full) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float x = __uint_as_float(sv[c][e]) * p.scale_log2;
+            sv[c][e] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
+          }
+      } else {
+        int clo, chi;
+        row_bounds<MODE>(p, t, n0, clo, chi);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int col = c * 32 + e;
+            const float x = (col > clo && col <= chi) ? __uint_as_float(sv[c][e]) * p.scale_log2 : -CUDART_INF_F;
+            sv[c][e] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
+          }
+      }
+      m_true = fmaxf(m_true, mx);
+      // lazy rescale: move the reference maximum only when the true one ran away from it
+      const bool grow = m_true > m_ref + kRescaleThreshold;  // also true on the first finite maximum
+      const bool need_o = grow && m_ref != -CUDART_INF_F;
+      if (__any_sync(0xffffffffu, need_o)) {
+        ok = mbar_wait(&bar->pv_done[i], (j - 1) & 1, abort);  // O_i must hold PV(j-1) before it is scaled
+        if (!ok) break;
+        tc_fence_after();
+        const float f = need_o ? exp2f(m_ref - m_true) : 1.f;
+        l *= f;
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld32(tO + c * 32, ov);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * f);
+          tmem_st32(tO + c * 32, ov);
+        }
+        tc_wait_st();
+      }
+      if (grow) m_ref = m_true;
+      const float mref_use = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int cc = c * 2 + (e >> 4), ee = (e & 15) * 2;
+          const float p0 = exp2f(__uint_as_float(sv[cc][ee]) - mref_use);
+          const float p1 = exp2f(__uint_as_float(sv[cc][ee + 1]) - mref_use);
+          rs += p0 + p1;
+          __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);  // .x (low half) = even key
+          pk[e] = *reinterpret_cast<uint32_t*>(&v2);
+        }
+        tmem_st32(tS + c * 32, pk);
+      }
+      l += rs;
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->p_full[i]);
+    }
+    // epilogue
+    const int h = h0 + i;
+    const int64_t row = ((int64_t)b * p.H + h) * p.Tq + t;
+    __nv_bfloat16* orow = p.o + row * DV;
+    if (ok && ntiles > 0) ok = mbar_wait(&bar->pv_done[i], (ntiles - 1) & 1, abort);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < DV / 32; ++c) {
+        uint32_t ov[32];
+        if (ntiles > 0) {
+          tmem_ld32(tO + c * 32, ov);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[e] = 0;
+        }
+#pragma unroll
+        for (int e = 0; e < 32; e += 8) {
+          uint4 w;
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[e]) * inv, __uint_as_float(ov[e + 1]) * inv);
+          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2]) * inv, __uint_as_float(ov[e + 3]) * inv);
+          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 4]) * inv, __uint_as_float(ov[e + 5]) * inv);
+          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[e + 6]) * inv, __uint_as_float(ov[e + 7]) * inv);
+          w.x = *reinterpret_cast<uint32_t*>(&a0);
+          w.y = *reinterpret_cast<uint32_t*>(&a1);
+          w.z = *reinterpret_cast<uint32_t*>(&a2);
+          w.w = *reinterpret_cast<uint32_t*>(&a3);
+          *reinterpret_cast<uint4*>(orow + c * 32 + e) = w;
+        }
+      }
+      if (p.L) p.L[row] = l > 0.f ? logf(l) + (m_ref - m_true) * kLn2 : -CUDART_INF_F;
+      if (p.M) p.M[row] = m_true * kLn2;  // back from log2 units to the natural-log scale of the logits
+    }
+  }
+
+  // ------------------------------------------------------------ teardown (every thread gets here)
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bar->abort) atomicAdd(&g_fa_fwd_timeouts, 1);
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// bf16 row-major [rows, cols] matrix, box [box_rows, 64 cols] (128 B inner extent), 128-byte swizzle
+int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(NSA_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(NSA_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return NSA_OK;
+}
+
+template <int DK, int DV, int MODE>
+static int launch_fa_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaFwdParams& p,
+                           cudaStream_t st) {
+  using SM = FaSmem<DK, DV>;
+  auto kern = fa_fwd_kernel<DK, DV, MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kDynamic);
+  if (e != cudaSuccess) return fail(NSA_ERR_LAUNCH, "fa_fwd: cannot reserve %d bytes of shared memory: %s", SM::kDynamic, cudaGetErrorString(e));
+  dim3 grid(p.Tq / kBM, p.B * (p.H / 2));
+  kern<<<grid, kFaThreads, SM::kDynamic, st>>>(tq, tk, tv, p);
+  return check_launch("fa_fwd_sm100");
+}
+
+bool fa_fwd_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv) {
+  const bool dims = (dk == 192 && dv == 128) || (dk == 128 && dv == 128) || (dk == 64 && dv == 64);
+  return dims && G > 0 && H % G == 0 && (H / G) % 2 == 0 && Tq % kBM == 0 && Tk % kBN == 0 && Tq > 0 && Tk > 0;
+}
+
+int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L, float* M, int B, int H, int G, int Tq,
+                 int Tk, int dk, int dv, int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale,
+                 cudaStream_t st) {
+  if (!fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: unsupported shape");
+  if ((int64_t)B * (H / 2) > 65535) return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: too many (batch, head) pairs");
+  CUtensorMap tq, tk, tv;
+  if (int rc = make_tmap_bf16_2d(&tq, q, (uint64_t)B * H * Tq, dk, kBM)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, kBN)) return rc;
+  FaFwdParams p;
+  p.o = (__nv_bfloat16*)o; p.L = L; p.M = M;
+  p.B = B; p.H = H; p.G = G; p.Tq = Tq; p.Tk = Tk;
+  p.window = window; p.cmp_l = cmp_l; p.cmp_d = cmp_d; p.cmp_nb = cmp_nb;
+  p.scale_log2 = scale * 1.4426950408889634f;
+#define NSA_FA_CASE(DK_, DV_)                                                                   \
+  if (dk == DK_ && dv == DV_)                                                                   \
+    return mode == kWin ? launch_fa_fwd_t<DK_, DV_, kWin>(tq, tk, tv, p, st) : launch_fa_fwd_t<DK_, DV_, kCmp>(tq, tk, tv, p, st);
+  NSA_FA_CASE(192, 128)
+  NSA_FA_CASE(128, 128)
+  NSA_FA_CASE(64, 64)
+#undef NSA_FA_CASE
+  return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: unsupported head dims");
+}
+
+int fa_fwd_sm100_timeouts(int* count, bool reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(count, g_fa_fwd_timeouts, sizeof(int));
+  if (e != cudaSuccess) return fail(NSA_ERR_LAUNCH, "cannot read the timeout counter: %s", cudaGetErrorString(e));
+  if (reset) {
+    const int z = 0;
+    cudaMemcpyToSymbol(g_fa_fwd_timeouts, &z, sizeof(int));
+  }
+  return NSA_OK;
+}
+
+}  // namespace nsa

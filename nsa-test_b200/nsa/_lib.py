@@ -32,9 +32,11 @@ _I64P = POINTER(c_int64)
 PROTOTYPES = {
     "nsa_last_error": (c_char_p, []),
     "nsa_version": (c_char_p, []),
+    "nsa_set_kernel_family": (c_int, [c_int]),
+    "nsa_device_timeouts": (c_int, [c_int]),
     "nsa_sliding_fwd": (c_int, [_P] * 6 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P]),
     "nsa_sliding_bwd": (c_int, [_P] * 10 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P]),
-    "nsa_cmp_attn_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P]),
+    "nsa_cmp_attn_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 7 + [c_float, c_int, c_int, c_int, c_int, _P]),
     "nsa_cmp_attn_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P]),
     "nsa_slc_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 9 + [c_float, c_int, _P]),
     "nsa_slc_bwd_workspace_bytes": (c_size_t, [c_int] * 6),

@@ -121,8 +121,8 @@ class CompressionAttention(torch.autograd.Function):
     """``apply(q, k_compressed [B,G,dk,NB], v_compressed [B,G,NB,dv], block_ends [NB], scale, config)``."""
 
     @staticmethod
-    def forward(ctx, q, k_compressed, v_compressed, block_ends, scale, config=None):
-        o, L, M = ops.cmp_attn_fwd(q, k_compressed, v_compressed, block_ends, scale)
+    def forward(ctx, q, k_compressed, v_compressed, block_ends, scale, config=None, blocks=None):
+        o, L, M = ops.cmp_attn_fwd(q, k_compressed, v_compressed, block_ends, scale, blocks)
         ctx.save_for_backward(q, k_compressed, v_compressed, block_ends, o, L, M)
         ctx.scale = scale
         return o
@@ -131,7 +131,7 @@ class CompressionAttention(torch.autograd.Function):
     def backward(ctx, do):
         q, kc, vc, block_ends, o, L, M = ctx.saved_tensors
         dq, dkc, dvc = ops.cmp_attn_bwd(q, kc, vc, block_ends, o, do, L, M, ctx.scale)
-        return dq, dkc.transpose(-1, -2), dvc, None, None, None
+        return dq, dkc.transpose(-1, -2), dvc, None, None, None, None
 
 
 def _selection_fallback(indices: torch.Tensor, l_prime: int) -> torch.Tensor:
@@ -273,7 +273,7 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
     block_ends[:nb] = torch.arange(nb, device=q.device, dtype=torch.int32) * cfg.d + (cfg.l - 1)
     n_fixed = cfg.n_fixed if cfg.include_fixed_in_selection else 0
     indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale)
-    o_cmp = CompressionAttention.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, scale, cfg)
+    o_cmp = CompressionAttention.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, scale, cfg, (cfg.l, cfg.d, nb))
     o_slc = SelectionAttention.apply(q, k_slc, v_slc, indices, scale, cfg)
     o_win = SlidingWindowAttention.apply(q, kw, vw, scale, cfg.w, cfg)
     out, gates = _GateMix.apply(gate_logits, o_cmp, o_slc, o_win, cfg.gate_mode)
@@ -414,10 +414,12 @@ class _Launcher:
     def _run(self, a):
         from ._lib import check, dtype_code, i64, lib, ptr, require_cuda, stream_ptr
         kind = self.kind
-        Q, V, Out = a["Q"], a["V"], a["Out"]
-        K = a["K"] if kind != "cmp" else a.get("K_compressed", a.get("K_blocks"))
+        Q, Out = a["Q"], a["Out"]
         if kind == "cmp":
-            V = a.get("V_compressed", a.get("V_blocks"))
+            K = a["K_compressed"] if "K_compressed" in a else a["K_blocks"]
+            V = a["V_compressed"] if "V_compressed" in a else a["V_blocks"]
+        else:
+            K, V = a["K"], a["V"]
         B, H, G = int(a["Z"]), int(a["H"]), int(a["N_KV_GROUPS"])
         dk, dv = Q.shape[-1], V.shape[-1]
         if kind == "win":
@@ -455,7 +457,7 @@ class _Launcher:
                 elif kind == "cmp":
                     be = a["Block_ends"].to(torch.int32).contiguous()
                     rc = lib.nsa_cmp_attn_fwd(ptr(Q), ptr(K), ptr(V), ptr(be), ptr(Out), ptr(L), ptr(M), i64(strides), B, H,
-                                              G, Tq, Tk, dk, dv, scale, code, st)
+                                              G, Tq, Tk, dk, dv, scale, code, 0, 0, 0, st)
                 else:
                     rc = lib.nsa_slc_fwd(ptr(Q), ptr(K), ptr(V), ptr(idx), ptr(Out), ptr(L), ptr(M), i64(strides), B, H, G,
                                          Tq, Tk, int(a["N_BLOCKS"]), int(a["BLOCK_SIZE_SELECTION"]), dk, dv, scale, code, st)

@@ -66,7 +66,10 @@ def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float):
     return dq, dkey, dval
 
 
-def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float):
+def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None):
+    """``blocks=(l, d, n_blocks)`` asserts block_ends[i] == i*d + l - 1 for i < n_blocks and no later block
+    ever visible; it lets the tensor-core kernel bound its key loop."""
+    bl, bd, bn = blocks if blocks is not None else (0, 0, 0)
     dev = require_cuda(q, k_cmp, v_cmp, block_ends)
     B, H, T, dk = q.shape
     G, NB, dv = k_cmp.shape[1], k_cmp.shape[-1], v_cmp.shape[-1]
@@ -75,7 +78,7 @@ def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float):
     with torch.cuda.device(dev):
         check(lib.nsa_cmp_attn_fwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(L), ptr(M),
                                    i64(_fwd_strides(q, k_cmp, v_cmp, o, L, M)), B, H, G, T, NB, dk, dv, float(scale),
-                                   dtype_code(q), stream_ptr(dev)), "nsa_cmp_attn_fwd")
+                                   dtype_code(q), int(bl), int(bd), int(bn), stream_ptr(dev)), "nsa_cmp_attn_fwd")
     return o, L, M
 
 

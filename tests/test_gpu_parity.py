@@ -395,8 +395,14 @@ def test_layer_fp32_forward_backward(nsa_mod, name, gate_mode):
         assert rel_err(info[key], r[key]) < 1e-3
     assert rel_err(out, r["out"]) < 1e-3
     names = ["dq", "dk", "dv", "dpos", "dw1", "db1", "dw2", "db2", "dgw1", "dgb1", "dgw2", "dgb2"]
+    ref = dict(zip(names, gref))
     for nme, a, b in zip(names, grads, gref):
-        assert rel_err(a, b) < 1e-3, nme
+        if nme == "db2":
+            # a constant added to every compressed key leaves the softmax unchanged: the true gradient is
+            # zero and both sides hold rounding noise; compare on the scale of the weight gradient
+            assert max_abs(a, b) < 1e-3 * ref["dw2"].abs().max().item(), nme
+        else:
+            assert rel_err(a, b) < 1e-3, nme
 
 
 def test_layer_bf16_forward_backward(nsa_mod):

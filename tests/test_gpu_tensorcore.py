@@ -1,0 +1,101 @@
+"""Tensor-core (tcgen05) kernels against the CPU oracle at small sizes and against the stride-generic
+CUDA kernels at sizes the oracle cannot reach.  bf16 I/O: 2e-2 max-abs on outputs."""
+import pytest
+import torch
+
+from oracle import nsa_oracle as O
+from tests.util import max_abs
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _inputs(B, H, G, T, dk, dv, Tk=None, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    Tk = T if Tk is None else Tk
+    rnd = lambda *s: torch.randn(*s, generator=gen).bfloat16()
+    return rnd(B, H, T, dk), rnd(B, G, dk, Tk), rnd(B, G, Tk, dv), rnd(B, H, T, dv)
+
+
+def _generic(fn):
+    from nsa._lib import lib
+    lib.nsa_set_kernel_family(1)
+    try:
+        return fn()
+    finally:
+        lib.nsa_set_kernel_family(0)
+
+
+def _no_timeouts():
+    from nsa._lib import lib
+    assert lib.nsa_device_timeouts(1) == 0, "a tensor-core CTA gave up on a barrier wait"
+
+
+def _check_stats(L, M, L_ref, M_ref):
+    fin = torch.isfinite(M_ref)
+    assert torch.equal(torch.isfinite(M.cpu()), fin) and torch.equal(torch.isfinite(L.cpu()), fin)
+    lse, lse_ref = (M + L).cpu()[fin], (M_ref + L_ref)[fin]
+    assert (lse - lse_ref).abs().max() < 2e-2
+    assert (M.cpu()[fin] - M_ref[fin]).abs().max() < 2e-2 * (1 + M_ref[fin].abs().max())
+
+
+@pytest.mark.parametrize("dk,dv,H,G,T,w", [(64, 64, 4, 2, 512, 200), (192, 128, 4, 1, 1024, 512),
+                                           (128, 128, 2, 1, 384, 128), (192, 128, 2, 1, 256, 1000)])
+def test_sliding_forward_tensorcore_vs_oracle(dk, dv, H, G, T, w):
+    from nsa import ops
+    q, k, v, _ = _inputs(2, H, G, T, dk, dv, seed=1)
+    scale = dk ** -0.5
+    o, L, M = ops.sliding_fwd(q.to(DEV), k.to(DEV), v.to(DEV), w, scale)
+    torch.cuda.synchronize()
+    _no_timeouts()
+    o_ref, M_ref, L_ref = O.sliding_window_attention(q.float(), k.float(), v.float(), w, scale, return_stats=True)
+    assert max_abs(o.float(), o_ref) < 2e-2
+    _check_stats(L, M, L_ref, M_ref)
+
+
+@pytest.mark.parametrize("dk,dv,H,G,T", [(64, 64, 4, 2, 2048), (192, 128, 2, 1, 4096 + 2048)])
+def test_compression_forward_tensorcore_vs_oracle(dk, dv, H, G, T):
+    from nsa import ops
+    l, d = 32, 16
+    nb = (T - l) // d + 1
+    nbp = O.next_pow2(nb)
+    q, kc, vc, _ = _inputs(1, H, G, T, dk, dv, Tk=nbp, seed=2)
+    kc[..., nb:] = 0
+    vc[:, :, nb:] = 0
+    be = torch.full((nbp,), 999999, dtype=torch.int32)
+    be[:nb] = torch.arange(nb, dtype=torch.int32) * d + l - 1
+    scale = dk ** -0.5
+    o, L, M = ops.cmp_attn_fwd(q.to(DEV), kc.to(DEV), vc.to(DEV), be.to(DEV), scale, blocks=(l, d, nb))
+    torch.cuda.synchronize()
+    _no_timeouts()
+    o_ref, M_ref, L_ref = O.compression_attention(q.float(), kc.float(), vc.float(), be, scale, return_stats=True)
+    assert max_abs(o.float(), o_ref) < 2e-2
+    assert (o[:, :, : l - 1] == 0).all()
+    _check_stats(L, M, L_ref, M_ref)
+
+
+def test_forward_tensorcore_vs_generic_at_scale():
+    """Paper head dims at T=8192 (16 heads of one group): tensor-core vs stride-generic kernels."""
+    from nsa import ops
+    B, H, G, T, dk, dv = 1, 16, 1, 8192, 192, 128
+    q, k, v, _ = (t.to(DEV) for t in _inputs(B, H, G, T, dk, dv, seed=3))
+    scale = dk ** -0.5
+    o, L, M = ops.sliding_fwd(q, k, v, 512, scale)
+    og, Lg, Mg = _generic(lambda: ops.sliding_fwd(q, k, v, 512, scale))
+    assert max_abs(o.float(), og.float()) < 2e-2 and max_abs(M + L, Mg + Lg) < 2e-2
+    l, d = 32, 16
+    nb = (T - l) // d + 1
+    nbp = O.next_pow2(nb)
+    kc = torch.zeros(B, G, dk, nbp, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros(B, G, nbp, dv, device=DEV, dtype=torch.bfloat16)
+    kc[..., :nb] = torch.randn(B, G, dk, nb, device=DEV).bfloat16()
+    vc[:, :, :nb] = torch.randn(B, G, nb, dv, device=DEV).bfloat16()
+    be = torch.full((nbp,), 999999, dtype=torch.int32, device=DEV)
+    be[:nb] = torch.arange(nb, dtype=torch.int32, device=DEV) * d + l - 1
+    o, L, M = ops.cmp_attn_fwd(q, kc, vc, be, scale, blocks=(l, d, nb))
+    og, Lg, Mg = _generic(lambda: ops.cmp_attn_fwd(q, kc, vc, be, scale))
+    torch.cuda.synchronize()
+    _no_timeouts()
+    assert max_abs(o.float(), og.float()) < 2e-2
+    fin = torch.isfinite(Mg)
+    assert torch.equal(torch.isfinite(M), fin) and max_abs((M + L)[fin], (Mg + Lg)[fin]) < 2e-2
