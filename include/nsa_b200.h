@@ -70,16 +70,21 @@ NSA_API const char* nsa_version(void);
 NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void* v, void* out, float* L, float* M,
                     const int64_t* strides22, int B, int H, int G, int T, int dk, int dv, int window,
                     float scale, int dtype, void* stream);
+/* The backward entry points of the sliding and compression branches take scratch memory of
+ * nsa_attn_bwd_workspace_bytes() bytes (used by the tensor-core kernels: per-row statistics and, for
+ * the compression branch, per-head-chunk partial dK/dV sums that are then added in a fixed order). */
+NSA_API size_t nsa_attn_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv,
+                                            int is_compression);
 NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                     const float* L, const float* M, void* dq, void* dkey, void* dval,
                     const int64_t* strides34, int B, int H, int G, int T, int dk, int dv, int window,
-                    float scale, int dtype, void* stream);
+                    float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Attention over compressed tokens, block i visible iff block_ends[i] <= t; a row that sees no block
  * gets out = 0, L = M = -inf.  k_cmp is [B,G,dk,NB] with strides passed (z,g,n=block,k), v_cmp
  * [B,G,NB,dv]; dk_cmp is written [B,G,NB,dk].  Layout hint (forward): blocks_d > 0 asserts that
  * block_ends[i] == i*blocks_d + blocks_l - 1 for i < blocks_n and that later blocks are never
- * visible, which lets the tensor-core kernel skip tiles; blocks_d == 0 makes no assumption.
+ * visible, which lets the tensor-core kernels skip tiles; blocks_d == 0 makes no assumption.
  * Replaces _nsa_compression_fwd_kernel / _bwd_kernel (nsa/kernels.py:1533-1687, 1690-1917). */
 NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                      void* out, float* L, float* M, const int64_t* strides22, int B, int H, int G,
@@ -88,7 +93,8 @@ NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp
 NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                      const void* out, const void* dout, const float* L, const float* M, void* dq,
                      void* dk_cmp, void* dv_cmp, const int64_t* strides34, int B, int H, int G, int T,
-                     int NB, int dk, int dv, float scale, int dtype, void* stream);
+                     int NB, int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d,
+                     int blocks_n, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Selected-block attention: query t of group g sees the union of blocks indices[b,g,t,:] (ids < 0
  * and blocks starting at or beyond Tkv ignored, a repeated id counts once) intersected with

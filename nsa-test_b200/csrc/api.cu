@@ -61,6 +61,21 @@ static bool canonical_fwd(const int64_t* s, int H, int G, int Tq, int Tk, int dk
 }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// canonical contiguous gradients: dq like q, dk [B,G,Tk,dk], dv [B,G,Tk,dv]
+static bool tensor_core_bwd_ok(const int64_t* s, int dtype, int B, int H, int G, int Tq, int Tk, int dk, int dv,
+                               const void* q, const void* k, const void* v, const void* o, const void* dout, const void* dq,
+                               const void* dkey, const void* dval) {
+  if (g_kernel_family != 0 || dtype != NSA_BF16 || !fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return false;
+  if (!canonical_fwd(s, H, G, Tq, Tk, dk, dv) || (int64_t)B * H > 65535) return false;
+  const int64_t gq[4] = {(int64_t)H * Tq * dk, (int64_t)Tq * dk, dk, 1};
+  const int64_t gk[4] = {(int64_t)G * Tk * dk, (int64_t)Tk * dk, dk, 1};
+  const int64_t gv[4] = {(int64_t)G * Tk * dv, (int64_t)Tk * dv, dv, 1};
+  for (int i = 0; i < 4; ++i)
+    if (s[22 + i] != gq[i] || s[26 + i] != gk[i] || s[30 + i] != gv[i]) return false;
+  return aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && aligned16(dout) && aligned16(dq) &&
+         aligned16(dkey) && aligned16(dval);
+}
+
 }  // namespace nsa
 
 using namespace nsa;
@@ -69,6 +84,11 @@ extern "C" NSA_API int nsa_set_kernel_family(int family) {
   NSA_REQUIRE(family == 0 || family == 1, "kernel family must be 0 (auto) or 1 (generic)");
   g_kernel_family = family;
   return NSA_OK;
+}
+
+extern "C" NSA_API size_t nsa_attn_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int is_compression) {
+  if (B <= 0 || H <= 0 || G <= 0 || Tq <= 0 || Tk <= 0 || H % G != 0) return 256;
+  return fa_bwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, is_compression ? kCmp : kWin);
 }
 
 extern "C" NSA_API int nsa_device_timeouts(int reset) {
@@ -100,10 +120,13 @@ extern "C" NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void*
 extern "C" NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                                const float* L, const float* M, void* dq, void* dkey, void* dval,
                                const int64_t* strides, int B, int H, int G, int T, int dk, int dv, int window,
-                               float scale, int dtype, void* stream) {
+                               float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
   if (int rc = check_common("sliding_bwd", B, H, G, T, T, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && out && dout && L && M && dq && dkey && dval && strides, "sliding_bwd: null pointer");
   NSA_REQUIRE(window > 0, "sliding_bwd: window must be positive");
+  if (tensor_core_bwd_ok(strides, dtype, B, H, G, T, T, dk, dv, q, k, v, out, dout, dq, dkey, dval))
+    return fa_bwd_sm100(q, k, v, out, dout, L, M, dq, dkey, dval, B, H, G, T, T, dk, dv, kWin, window, 0, 0, 0, scale,
+                        workspace, workspace_bytes, (cudaStream_t)stream);
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.dq = dq; a.dk_out = dkey; a.dv_out = dval;
   fill_bwd_strides(a, strides);
@@ -134,10 +157,16 @@ extern "C" NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const 
 extern "C" NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                                 const void* out, const void* dout, const float* L, const float* M, void* dq,
                                 void* dk_cmp, void* dv_cmp, const int64_t* strides, int B, int H, int G, int T, int NB,
-                                int dk, int dv, float scale, int dtype, void* stream) {
+                                int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d, int blocks_n,
+                                void* workspace, size_t workspace_bytes, void* stream) {
   if (int rc = check_common("cmp_attn_bwd", B, H, G, T, NB, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k_cmp && v_cmp && block_ends && out && dout && L && M && dq && dk_cmp && dv_cmp && strides,
               "cmp_attn_bwd: null pointer");
+  NSA_REQUIRE(blocks_d >= 0 && (blocks_d == 0 || (blocks_l > 0 && blocks_n >= 0 && blocks_n <= NB)),
+              "cmp_attn_bwd: bad block layout hint (l=%d, d=%d, n=%d)", blocks_l, blocks_d, blocks_n);
+  if (blocks_d > 0 && tensor_core_bwd_ok(strides, dtype, B, H, G, T, NB, dk, dv, q, k_cmp, v_cmp, out, dout, dq, dk_cmp, dv_cmp))
+    return fa_bwd_sm100(q, k_cmp, v_cmp, out, dout, L, M, dq, dk_cmp, dv_cmp, B, H, G, T, NB, dk, dv, kCmp, 0, blocks_l,
+                        blocks_d, blocks_n, scale, workspace, workspace_bytes, (cudaStream_t)stream);
   AttnArgs a = {};
   a.q = q; a.k = k_cmp; a.v = v_cmp; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.block_ends = block_ends;
   a.dq = dq; a.dk_out = dk_cmp; a.dv_out = dv_cmp;

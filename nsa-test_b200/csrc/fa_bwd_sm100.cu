@@ -1,0 +1,613 @@
+// Dense-range flash-attention backward on tcgen05 tensor cores for the sliding-window and compressed
+// branches (replaces _nsa_sliding_window_bwd_kernel / _nsa_compression_bwd_kernel,
+// nsa/kernels.py:1303-1530, 1690-1917, for bf16 tensors in canonical layouts).
+//
+// The reference accumulates dK/dV with atomics from every query tile.  Here gradients are produced by
+// two stationary kernels, so every output element has one writer and a fixed summation order:
+//   prep   D[t] = sum_c O[t,c] dO[t,c] and lse2[t] = (M+L) log2(e)           (HBM-bound, one pass)
+//   dQ     query-stationary: S = Q K^T, dP = dO V^T, dS = P*(dP-D) written to tensor memory as bf16,
+//          dQ += dS K   (A operand read straight from TMEM)
+//   dK/dV  key-stationary, transposed: S^T = K Q^T, dP^T = V dO^T over 64-query sub-tiles of every
+//          head of the group; P^T and dS^T stay in TMEM as A operands of dV += P^T dO, dK += dS^T Q.
+//          TMEM: dK 192 + dV 128 + S^T 64 + dP^T 64 columns.  Heads may be split over several CTAs
+//          (compressed branch, few key tiles): partial sums go to scratch and are added in head order.
+#include <cuda.h>
+
+#include "attn_args.cuh"
+#include "common.cuh"
+#include "fa_sm100.cuh"
+#include "sm100_ptx.cuh"
+
+namespace nsa {
+
+using namespace ptx;
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct FaBwdParams {
+  const float *D, *lse2;  // [B,H,Tq] from the prep kernel
+  __nv_bfloat16 *dq, *dk, *dv;
+  float *dk_part, *dv_part;  // [hsplit, B, G, Tk, dk|dv] when hsplit > 1
+  int B, H, G, Tq, Tk;
+  int window, cmp_l, cmp_d, cmp_nb;
+  int hsplit;
+  float scale, scale_log2;
+  int* timeouts;
+};
+
+// ------------------------------------------------------------------------------------------------
+// prep: one warp per (b,h,t)
+// ------------------------------------------------------------------------------------------------
+__global__ void fa_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                   const float* __restrict__ L, const float* __restrict__ M, float* __restrict__ D,
+                                   float* __restrict__ lse2, int64_t rows, int dv) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float acc = 0.f;
+  for (int c = lane * 2; c < dv; c += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + row * dv + c));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dout + row * dv + c));
+    acc = fmaf(a.x, b.x, fmaf(a.y, b.y, acc));
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    D[row] = acc;
+    const float lse = M[row] + L[row];
+    lse2[row] = isfinite(lse) ? lse * kLog2e : CUDART_INF_F;  // +inf: exp2(x - inf) = 0 for rows that saw nothing
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dQ kernel: 128 queries of one head per CTA; warps 0-3 compute, warp 4 TMA, warp 5 UMMA
+// ------------------------------------------------------------------------------------------------
+template <int DK, int DV>
+struct DqSmem {
+  static constexpr int kQ = 128 * DK * 2, kdO = 128 * DV * 2, kK = 128 * DK * 2, kV = 128 * DV * 2;
+  static constexpr int oQ = 0, odO = oQ + kQ, oK = odO + kdO, oV = oK + 2 * kK, oBar = oV + kV;
+  static constexpr int kDynamic = oBar + 256 + 1024;
+};
+struct DqBarriers {
+  uint64_t qdo_full, k_full[2], k_empty[2], v_full, v_empty, sdp_full, ds_full, dq_done;
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int DK, int DV, int MODE>
+__global__ void __launch_bounds__(192, 1)
+fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FaBwdParams p) {
+  using SM = DqSmem<DK, DV>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t *sQ = smem + SM::oQ, *sdO = smem + SM::odO, *sK = smem + SM::oK, *sV = smem + SM::oV;
+  DqBarriers* bar = reinterpret_cast<DqBarriers*>(smem + SM::oBar);
+  volatile int* abort = &bar->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * 128;
+  const int b = blockIdx.y / p.H, h = blockIdx.y % p.H, g = h / (p.H / p.G);
+  int jlo, jhi;
+  if (MODE == kWin) {
+    jlo = max(0, m0 - p.window + 1) / 128;
+    jhi = min(m0 + 127, p.Tk - 1) / 128;
+  } else {
+    const int tl = m0 + 127;
+    const int kmax = tl >= p.cmp_l - 1 ? min(p.cmp_nb - 1, (tl - p.cmp_l + 1) / p.cmp_d) : -1;
+    jlo = 0;
+    jhi = kmax >= 0 ? kmax / 128 : -1;
+  }
+  const int ntiles = jhi - jlo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->qdo_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar->k_full[i], 1); mbar_init(&bar->k_empty[i], 1); }
+    mbar_init(&bar->v_full, 1);
+    mbar_init(&bar->v_empty, 1);
+    mbar_init(&bar->sdp_full, 1);
+    mbar_init(&bar->ds_full, 128);
+    mbar_init(&bar->dq_done, 1);
+    bar->abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) tmem_alloc(&bar->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  constexpr uint32_t cS = 0, cdP = 128, cdQ = 256;
+
+  if (warp == 4) {
+    if (lane == 0 && ntiles > 0) {
+      mbar_arrive_expect_tx(&bar->qdo_full, SM::kQ + SM::kdO);
+      const int qrow = (b * p.H + h) * p.Tq + m0;
+      for (int c = 0; c < DK / 64; ++c) tma_load_2d(&tmQ, &bar->qdo_full, sQ + c * 16384, c * 64, qrow);
+      for (int c = 0; c < DV / 64; ++c) tma_load_2d(&tmdO, &bar->qdo_full, sdO + c * 16384, c * 64, qrow);
+      bool ok = true;
+      int issued = 0;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int n0 = (jlo + j) * 128, ks = j & 1;
+        ok = mbar_wait(&bar->k_empty[ks], ((j >> 1) & 1) ^ 1, abort);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bar->k_full[ks], SM::kK);
+        for (int hf = 0; hf < 2; ++hf)
+          tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kK + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
+        ok = mbar_wait(&bar->v_empty, (j & 1) ^ 1, abort);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bar->v_full, SM::kV);
+        for (int c = 0; c < DV / 64; ++c)
+          tma_load_2d(&tmV, &bar->v_full, sV + c * 16384, c * 64, (b * p.G + g) * p.Tk + n0);
+        issued = j + 1;
+      }
+      if (!ok) {
+        mbar_wait(&bar->qdo_full, 0, abort);
+        for (int j = max(0, issued - 2); j < issued; ++j) mbar_wait(&bar->k_full[j & 1], (j >> 1) & 1, abort);
+        if (issued > 0) mbar_wait(&bar->v_full, (issued - 1) & 1, abort);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && ntiles > 0) {
+      constexpr uint32_t idS = idesc_bf16(128, 128, 0, 1);    // Q (K-major) x K tile (MN-major: keys contiguous)
+      constexpr uint32_t iddP = idesc_bf16(128, 128, 0, 0);   // dO (K-major) x V tile (K-major: dv contiguous)
+      constexpr uint32_t iddQ = idesc_bf16(128, DK, 0, 0);    // dS (TMEM) x K tile read K-major (keys = K dim)
+      const uint64_t dQd = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t ddO = smem_desc_sw128(smem_u32(sdO), 16, 1024);
+      const uint64_t dVd = smem_desc_sw128(smem_u32(sV), 16, 1024);
+      bool ok = mbar_wait(&bar->qdo_full, 0, abort);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int ks = j & 1;
+        const uint64_t dK_mn = smem_desc_sw128(smem_u32(sK + ks * SM::kK), DK * 128, 1024);
+        const uint64_t dK_k = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);
+        ok = mbar_wait(&bar->k_full[ks], (j >> 1) & 1, abort) && mbar_wait(&bar->v_full, j & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + cS, desc_advance(dQd, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dK_mn, kk * 2048), idS, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < DV / 16; ++kk)
+          umma_ss(tmem + cdP, desc_advance(ddO, (kk >> 2) * 16384 + (kk & 3) * 32),
+                  desc_advance(dVd, (kk >> 2) * 16384 + (kk & 3) * 32), iddP, kk > 0);
+        umma_commit(&bar->sdp_full);
+        umma_commit(&bar->v_empty);
+        ok = mbar_wait(&bar->ds_full, j & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts(tmem + cdQ, tmem + cS + kk * 8, desc_advance(dK_k, (kk >> 2) * (DK * 128) + (kk & 3) * 32), iddQ,
+                  (j > 0) || (kk > 0));
+        umma_commit(&bar->k_empty[ks]);
+      }
+      if (ok) umma_commit(&bar->dq_done);
+    }
+  } else {
+    const int r = warp * 32 + lane, t = m0 + r;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const int64_t row = ((int64_t)b * p.H + h) * p.Tq + t;
+    const float lse2 = p.lse2[row], Dr = p.D[row];
+    bool ok = true;
+    uint32_t sv[4][32];
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int n0 = (jlo + j) * 128;
+      ok = mbar_wait(&bar->sdp_full, j & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + cS + c * 32, sv[c]);
+      tc_wait_ld();
+      int clo, chi;
+      if (MODE == kWin) {
+        chi = t - n0;
+        clo = t - p.window - n0;
+      } else {
+        const int vis = t >= p.cmp_l - 1 ? min(p.cmp_nb - 1, (t - p.cmp_l + 1) / p.cmp_d) : -1;
+        chi = vis - n0;
+        clo = -0x40000000;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int col = c * 32 + e;
+          const float pr = (col > clo && col <= chi) ? exp2f(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -lse2)) : 0.f;
+          sv[c][e] = __float_as_uint(pr);
+        }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t dp0[32], dp1[32], pk[32];
+        tmem_ld32(tmem + lane_base + cdP + c * 64, dp0);
+        tmem_ld32(tmem + lane_base + cdP + c * 64 + 32, dp1);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float a0 = __uint_as_float(sv[c * 2][2 * e]) * (__uint_as_float(dp0[2 * e]) - Dr);
+          const float a1 = __uint_as_float(sv[c * 2][2 * e + 1]) * (__uint_as_float(dp0[2 * e + 1]) - Dr);
+          const float b0 = __uint_as_float(sv[c * 2 + 1][2 * e]) * (__uint_as_float(dp1[2 * e]) - Dr);
+          const float b1 = __uint_as_float(sv[c * 2 + 1][2 * e + 1]) * (__uint_as_float(dp1[2 * e + 1]) - Dr);
+          __nv_bfloat162 x = __floats2bfloat162_rn(a0, a1), y = __floats2bfloat162_rn(b0, b1);
+          pk[e] = *reinterpret_cast<uint32_t*>(&x);
+          pk[16 + e] = *reinterpret_cast<uint32_t*>(&y);
+        }
+        tmem_st32(tmem + lane_base + cS + c * 32, pk);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->ds_full);
+    }
+    if (ok && ntiles > 0) ok = mbar_wait(&bar->dq_done, 0, abort);
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* dst = p.dq + row * DK;
+#pragma unroll
+      for (int c = 0; c < DK / 32; ++c) {
+        uint32_t ov[32];
+        if (ntiles > 0) {
+          tmem_ld32(tmem + lane_base + cdQ + c * 32, ov);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[e] = 0;
+        }
+#pragma unroll
+        for (int e = 0; e < 32; e += 8) {
+          uint4 w;
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[e]) * p.scale, __uint_as_float(ov[e + 1]) * p.scale);
+          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2]) * p.scale, __uint_as_float(ov[e + 3]) * p.scale);
+          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 4]) * p.scale, __uint_as_float(ov[e + 5]) * p.scale);
+          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[e + 6]) * p.scale, __uint_as_float(ov[e + 7]) * p.scale);
+          w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
+          w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
+          *reinterpret_cast<uint4*>(dst + c * 32 + e) = w;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dK/dV kernel: 128 keys per CTA, loops over (head, 64-query sub-tile); transposed tiles in TMEM
+// ------------------------------------------------------------------------------------------------
+template <int DK, int DV>
+struct DkvSmem {
+  static constexpr int kK = 128 * DK * 2, kV = 128 * DV * 2, kQs = 64 * DK * 2, kdOs = 64 * DV * 2;
+  static constexpr int kStage = kQs + kdOs + 1024;  // + lse2[64], D[64] (512 B, padded to keep 1024 B alignment)
+  static constexpr int kStages = 3;
+  static constexpr int oK = 0, oV = oK + kK, oStage = oV + kV, oBar = oStage + kStages * kStage;
+  static constexpr int kDynamic = oBar + 256 + 1024;
+};
+struct DkvBarriers {
+  uint64_t kv_full, full[3], empty[3], stp_full, pds_full, acc_done;
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int DK, int DV, int MODE>
+__global__ void __launch_bounds__(192, 1)
+fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FaBwdParams p) {
+  using SM = DkvSmem<DK, DV>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sSt = smem + SM::oStage;
+  DkvBarriers* bar = reinterpret_cast<DkvBarriers*>(smem + SM::oBar);
+  volatile int* abort = &bar->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * 128;
+  const int hc = blockIdx.y;
+  const int b = blockIdx.z / p.G, g = blockIdx.z % p.G;
+  const int hpg = p.H / p.G, hper = hpg / p.hsplit;
+  const int hbeg = g * hpg + hc * hper;
+
+  // 64-query sub-tiles that can see this key tile
+  int qs_lo, qs_hi;
+  if (MODE == kWin) {
+    qs_lo = n0 / 64;
+    qs_hi = min(p.Tq - 1, n0 + 126 + p.window) / 64;
+  } else {
+    const int64_t tfirst = (int64_t)n0 * p.cmp_d + p.cmp_l - 1;
+    qs_lo = (n0 < p.cmp_nb && tfirst < p.Tq) ? (int)(tfirst / 64) : 1;
+    qs_hi = (n0 < p.cmp_nb && tfirst < p.Tq) ? (p.Tq - 1) / 64 : 0;
+  }
+  const int nq = max(0, qs_hi - qs_lo + 1);
+  const int n_it = nq * hper;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->kv_full, 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(&bar->full[i], 2); mbar_init(&bar->empty[i], 1); }
+    mbar_init(&bar->stp_full, 1);
+    mbar_init(&bar->pds_full, 128);
+    mbar_init(&bar->acc_done, 1);
+    bar->abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) tmem_alloc(&bar->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  constexpr uint32_t cdK = 0, cdV = DK, cST = DK + DV, cdPT = DK + DV + 64;
+
+  if (warp == 4) {
+    // producer: the whole warp takes part (lanes fill the per-query statistics), lane 0 drives TMA
+    if (n_it > 0) {
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
+        for (int hf = 0; hf < 2; ++hf) tma_load_2d(&tmK, &bar->kv_full, sK + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
+        for (int c = 0; c < DV / 64; ++c) tma_load_2d(&tmV, &bar->kv_full, sV + c * 16384, c * 64, (b * p.G + g) * p.Tk + n0);
+      }
+      bool ok = true;
+      int issued = 0;
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it % 3, h = hbeg + it / nq, tq0 = (qs_lo + it % nq) * 64;
+        if (lane == 0) ok = mbar_wait(&bar->empty[s], ((it / 3) & 1) ^ 1, abort);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        uint8_t* st = sSt + s * SM::kStage;
+        const int64_t qrow = ((int64_t)b * p.H + h) * p.Tq + tq0;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&bar->full[s], SM::kQs + SM::kdOs);
+          for (int c = 0; c < DK / 64; ++c) tma_load_2d(&tmQ, &bar->full[s], st + c * 8192, c * 64, (int)qrow);
+          for (int c = 0; c < DV / 64; ++c) tma_load_2d(&tmdO, &bar->full[s], st + SM::kQs + c * 8192, c * 64, (int)qrow);
+        }
+        float* stat = reinterpret_cast<float*>(st + SM::kQs + SM::kdOs);
+        for (int c = lane; c < 64; c += 32) {
+          stat[c] = p.lse2[qrow + c];
+          stat[64 + c] = p.D[qrow + c];
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->full[s]);
+        issued = it + 1;
+      }
+      if (!ok && lane == 0) {
+        mbar_wait(&bar->kv_full, 0, abort);
+        for (int it = max(0, issued - 3); it < issued; ++it) mbar_wait(&bar->full[it % 3], (it / 3) & 1, abort);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idST = idesc_bf16(128, 64, 1, 0);    // K tile as A (MN-major: keys contiguous) x Q sub-tile (K-major)
+      constexpr uint32_t iddPT = idesc_bf16(128, 64, 0, 0);   // V tile as A (K-major) x dO sub-tile (K-major)
+      constexpr uint32_t iddV = idesc_bf16(128, DV, 0, 1);    // P^T (TMEM) x dO sub-tile (MN-major: dv contiguous)
+      constexpr uint32_t iddK = idesc_bf16(128, DK, 0, 1);    // dS^T (TMEM) x Q sub-tile (MN-major: dk contiguous)
+      const uint64_t dKa = smem_desc_sw128(smem_u32(sK), DK * 128, 1024);
+      const uint64_t dVa = smem_desc_sw128(smem_u32(sV), 16, 1024);
+      bool ok = mbar_wait(&bar->kv_full, 0, abort);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it % 3;
+        const uint32_t st = smem_u32(sSt + s * SM::kStage);
+        const uint64_t dQk = smem_desc_sw128(st, 16, 1024), dQmn = smem_desc_sw128(st, 8192, 1024);
+        const uint64_t dOk = smem_desc_sw128(st + SM::kQs, 16, 1024), dOmn = smem_desc_sw128(st + SM::kQs, 8192, 1024);
+        ok = mbar_wait(&bar->full[s], (it / 3) & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + cST, desc_advance(dKa, kk * 2048), desc_advance(dQk, (kk >> 2) * 8192 + (kk & 3) * 32), idST, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < DV / 16; ++kk)
+          umma_ss(tmem + cdPT, desc_advance(dVa, (kk >> 2) * 16384 + (kk & 3) * 32),
+                  desc_advance(dOk, (kk >> 2) * 8192 + (kk & 3) * 32), iddPT, kk > 0);
+        umma_commit(&bar->stp_full);
+        ok = mbar_wait(&bar->pds_full, it & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ts(tmem + cdV, tmem + cST + kk * 8, desc_advance(dOmn, kk * 2048), iddV, (it > 0) || (kk > 0));
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ts(tmem + cdK, tmem + cdPT + kk * 8, desc_advance(dQmn, kk * 2048), iddK, (it > 0) || (kk > 0));
+        umma_commit(&bar->empty[s]);
+      }
+      if (ok) umma_commit(&bar->acc_done);
+    }
+  } else {
+    const int r = warp * 32 + lane, key = n0 + r;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int s = it % 3, tq0 = (qs_lo + it % nq) * 64;
+      ok = mbar_wait(&bar->full[s], (it / 3) & 1, abort) && mbar_wait(&bar->stp_full, it & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      const float* stat = reinterpret_cast<const float*>(sSt + s * SM::kStage + SM::kQs + SM::kdOs);
+      // visible columns (queries) for this key: clo <= c <= chi
+      int clo, chi;
+      if (MODE == kWin) {
+        clo = key - tq0;
+        chi = key + p.window - 1 - tq0;
+      } else {
+        clo = key < p.cmp_nb ? key * p.cmp_d + p.cmp_l - 1 - tq0 : 0x40000000;
+        chi = 0x40000000;
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sT[32], dpT[32], pk[16], dk_[16];
+        tmem_ld32(tmem + lane_base + cST + c * 32, sT);
+        tmem_ld32(tmem + lane_base + cdPT + c * 32, dpT);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int c0 = c * 32 + 2 * e;
+          const float l0 = stat[c0], l1 = stat[c0 + 1], D0 = stat[64 + c0], D1 = stat[64 + c0 + 1];
+          const float p0 = (c0 >= clo && c0 <= chi) ? exp2f(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0)) : 0.f;
+          const float p1 = (c0 + 1 >= clo && c0 + 1 <= chi) ? exp2f(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1)) : 0.f;
+          const float s0 = p0 * (__uint_as_float(dpT[2 * e]) - D0), s1 = p1 * (__uint_as_float(dpT[2 * e + 1]) - D1);
+          __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1), y = __floats2bfloat162_rn(s0, s1);
+          pk[e] = *reinterpret_cast<uint32_t*>(&x);
+          dk_[e] = *reinterpret_cast<uint32_t*>(&y);
+        }
+        // 16 packed columns each: P^T over S^T, dS^T over dP^T (the fp32 values were consumed above)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::
+                     "r"(tmem + lane_base + cST + c * 16), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
+                     "r"(pk[6]), "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]),
+                     "r"(pk[15]) : "memory");
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::
+                     "r"(tmem + lane_base + cdPT + c * 16), "r"(dk_[0]), "r"(dk_[1]), "r"(dk_[2]), "r"(dk_[3]), "r"(dk_[4]),
+                     "r"(dk_[5]), "r"(dk_[6]), "r"(dk_[7]), "r"(dk_[8]), "r"(dk_[9]), "r"(dk_[10]), "r"(dk_[11]), "r"(dk_[12]),
+                     "r"(dk_[13]), "r"(dk_[14]), "r"(dk_[15]) : "memory");
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->pds_full);
+    }
+    if (ok && n_it > 0) ok = mbar_wait(&bar->acc_done, 0, abort);
+    if (ok) {
+      tc_fence_after();
+      const int64_t krow = ((int64_t)b * p.G + g) * p.Tk + key;
+      auto flush = [&](uint32_t col0, int width, float mul, __nv_bfloat16* out_bf, float* out_part) {
+        for (int c = 0; c < width / 32; ++c) {
+          uint32_t ov[32];
+          if (n_it > 0) {
+            tmem_ld32(tmem + lane_base + col0 + c * 32, ov);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ov[e] = 0;
+          }
+          if (out_part) {
+            float* dst = out_part + ((int64_t)hc * p.B * p.G * p.Tk + krow) * width + c * 32;
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              *reinterpret_cast<float4*>(dst + e) = make_float4(__uint_as_float(ov[e]) * mul, __uint_as_float(ov[e + 1]) * mul,
+                                                                __uint_as_float(ov[e + 2]) * mul, __uint_as_float(ov[e + 3]) * mul);
+          } else if (n_it > 0) {
+            __nv_bfloat16* dst = out_bf + krow * width + c * 32;
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              __nv_bfloat162 cur = *reinterpret_cast<__nv_bfloat162*>(dst + e);
+              const float2 f = __bfloat1622float2(cur);
+              cur = __floats2bfloat162_rn(f.x + __uint_as_float(ov[e]) * mul, f.y + __uint_as_float(ov[e + 1]) * mul);
+              *reinterpret_cast<__nv_bfloat162*>(dst + e) = cur;
+            }
+          }
+        }
+      };
+      flush(cdK, DK, p.scale, p.dk, p.hsplit > 1 ? p.dk_part : nullptr);
+      flush(cdV, DV, 1.f, p.dv, p.hsplit > 1 ? p.dv_part : nullptr);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// out[i] += sum_{c < hsplit} part[c][i], partial sums taken in chunk order
+__global__ void dkv_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int64_t n, int hsplit) {
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (i >= n) return;
+  float a0 = 0.f, a1 = 0.f;
+  for (int c = 0; c < hsplit; ++c) {
+    const float2 v = *reinterpret_cast<const float2*>(part + (int64_t)c * n + i);
+    a0 += v.x;
+    a1 += v.y;
+  }
+  const float2 cur = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(out + i));
+  *reinterpret_cast<__nv_bfloat162*>(out + i) = __floats2bfloat162_rn(cur.x + a0, cur.y + a1);
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+static size_t al256(size_t x) { return (x + 255) & ~size_t(255); }
+
+static int pick_hsplit(int B, int G, int H, int Tk, int mode) {
+  if (mode == kWin) return 1;
+  const int hpg = H / G;
+  const long ctas = (long)B * G * (Tk / 128);
+  int hs = 1;
+  while (hs < hpg && ctas * hs < 4 * 148 && hpg % (hs * 2) == 0) hs *= 2;
+  return hs;
+}
+
+size_t fa_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int mode) {
+  const int hs = pick_hsplit(B, G, H, Tk, mode);
+  size_t n = 2 * al256((size_t)B * H * Tq * sizeof(float));
+  if (hs > 1) n += al256((size_t)hs * B * G * Tk * dk * sizeof(float)) + al256((size_t)hs * B * G * Tk * dv * sizeof(float));
+  return n;
+}
+
+template <int DK, int DV, int MODE>
+static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, const CUtensorMap& tq64,
+                        const CUtensorMap& tdo64, const CUtensorMap& tk, const CUtensorMap& tv, const FaBwdParams& p,
+                        cudaStream_t st) {
+  auto kq = fa_bwd_dq_kernel<DK, DV, MODE>;
+  auto kkv = fa_bwd_dkv_kernel<DK, DV, MODE>;
+  if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<DK, DV>::kDynamic) != cudaSuccess ||
+      cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<DK, DV>::kDynamic) != cudaSuccess)
+    return fail(NSA_ERR_LAUNCH, "fa_bwd: cannot reserve shared memory");
+  kq<<<dim3(p.Tq / 128, p.B * p.H), 192, DqSmem<DK, DV>::kDynamic, st>>>(tq128, tdo128, tk, tv, p);
+  if (int rc = check_launch("fa_bwd_dq_sm100")) return rc;
+  kkv<<<dim3(p.Tk / 128, p.hsplit, p.B * p.G), 192, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, p);
+  return check_launch("fa_bwd_dkv_sm100");
+}
+
+int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* L,
+                 const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G, int Tq, int Tk, int dk, int dv,
+                 int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale, void* workspace,
+                 size_t workspace_bytes, cudaStream_t st) {
+  if (!fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return fail(NSA_ERR_UNSUPPORTED, "fa_bwd_sm100: unsupported shape");
+  if ((int64_t)B * H > 65535) return fail(NSA_ERR_UNSUPPORTED, "fa_bwd_sm100: B*H too large");
+  const size_t need = fa_bwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, mode);
+  if (!workspace || workspace_bytes < need)
+    return fail(NSA_ERR_WORKSPACE, "attention backward needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  FaBwdParams p;
+  char* w = (char*)workspace;
+  const size_t rows = (size_t)B * H * Tq;
+  float* D = (float*)w;
+  float* lse2 = (float*)(w + al256(rows * sizeof(float)));
+  p.D = D; p.lse2 = lse2;
+  p.hsplit = pick_hsplit(B, G, H, Tk, mode);
+  p.dk_part = p.dv_part = nullptr;
+  if (p.hsplit > 1) {
+    p.dk_part = (float*)(w + 2 * al256(rows * sizeof(float)));
+    p.dv_part = (float*)((char*)p.dk_part + al256((size_t)p.hsplit * B * G * Tk * dk * sizeof(float)));
+  }
+  p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk_out; p.dv = (__nv_bfloat16*)dv_out;
+  p.B = B; p.H = H; p.G = G; p.Tq = Tq; p.Tk = Tk;
+  p.window = window; p.cmp_l = cmp_l; p.cmp_d = cmp_d; p.cmp_nb = cmp_nb;
+  p.scale = scale; p.scale_log2 = scale * kLog2e;
+  p.timeouts = fa_timeout_counter();
+  fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, L, M, D,
+                                                               lse2, (int64_t)rows, dv);
+  if (int rc = check_launch("fa_bwd_prep")) return rc;
+  CUtensorMap tq128, tdo128, tq64, tdo64, tk, tv;
+  if (int rc = make_tmap_bf16_2d(&tq128, q, (uint64_t)B * H * Tq, dk, 128)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tdo128, dout, (uint64_t)B * H * Tq, dv, 128)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tq64, q, (uint64_t)B * H * Tq, dk, 64)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tdo64, dout, (uint64_t)B * H * Tq, dv, 64)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, 128)) return rc;
+  int rc = NSA_ERR_UNSUPPORTED;
+#define NSA_BWD_CASE(DK_, DV_)                                                                               \
+  if (dk == DK_ && dv == DV_)                                                                                \
+    rc = mode == kWin ? launch_bwd_t<DK_, DV_, kWin>(tq128, tdo128, tq64, tdo64, tk, tv, p, st)              \
+                      : launch_bwd_t<DK_, DV_, kCmp>(tq128, tdo128, tq64, tdo64, tk, tv, p, st);
+  NSA_BWD_CASE(192, 128)
+  NSA_BWD_CASE(128, 128)
+  NSA_BWD_CASE(64, 64)
+#undef NSA_BWD_CASE
+  if (rc) return rc == NSA_ERR_UNSUPPORTED ? fail(rc, "fa_bwd_sm100: unsupported head dims") : rc;
+  if (p.hsplit > 1) {
+    const int64_t nk = (int64_t)B * G * Tk * dk, nv = (int64_t)B * G * Tk * dv;
+    dkv_reduce_kernel<<<(unsigned)((nk / 2 + 255) / 256), 256, 0, st>>>(p.dk_part, p.dk, nk, p.hsplit);
+    dkv_reduce_kernel<<<(unsigned)((nv / 2 + 255) / 256), 256, 0, st>>>(p.dv_part, p.dv, nv, p.hsplit);
+    return check_launch("dkv_reduce");
+  }
+  return NSA_OK;
+}
+
+}  // namespace nsa

@@ -414,6 +414,12 @@ int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L,
   return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: unsupported head dims");
 }
 
+int* fa_timeout_counter() {
+  int* ptr = nullptr;
+  if (cudaGetSymbolAddress((void**)&ptr, g_fa_fwd_timeouts) != cudaSuccess) return nullptr;
+  return ptr;
+}
+
 int fa_fwd_sm100_timeouts(int* count, bool reset) {
   cudaError_t e = cudaMemcpyFromSymbol(count, g_fa_fwd_timeouts, sizeof(int));
   if (e != cudaSuccess) return fail(NSA_ERR_LAUNCH, "cannot read the timeout counter: %s", cudaGetErrorString(e));

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+struct CUtensorMap_st;
+
 namespace nsa {
 
 struct FaFwdParams {
@@ -22,6 +24,21 @@ bool fa_fwd_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv);
 int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L, float* M, int B, int H, int G, int Tq,
                  int Tk, int dk, int dv, int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale,
                  cudaStream_t st);
+
+// Backward of the same two branches.  Adds into dk [B,G,Tk,dk] and dv [B,G,Tk,dv] (time-major, bf16),
+// overwrites dq [B,H,Tq,dk].  Three launches: delta/lse preparation, a query-stationary dQ kernel and
+// a key-stationary dK/dV kernel whose per-head-chunk partial sums are combined in a fixed order.
+size_t fa_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int mode);
+int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* L,
+                 const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G, int Tq, int Tk, int dk, int dv,
+                 int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale, void* workspace,
+                 size_t workspace_bytes, cudaStream_t st);
+
+// bf16 row-major [rows, cols] matrix -> tensor map with box [box_rows, 64 columns], 128-byte swizzle
+int make_tmap_bf16_2d(::CUtensorMap_st* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+
+// Device address (on the current device) of the counter of CTAs that gave up on a barrier wait.
+int* fa_timeout_counter();
 
 // Number of CTAs that ever gave up on a barrier wait (0 in a healthy run); optionally reset.
 int fa_fwd_sm100_timeouts(int* count, bool reset);

@@ -124,13 +124,13 @@ class CompressionAttention(torch.autograd.Function):
     def forward(ctx, q, k_compressed, v_compressed, block_ends, scale, config=None, blocks=None):
         o, L, M = ops.cmp_attn_fwd(q, k_compressed, v_compressed, block_ends, scale, blocks)
         ctx.save_for_backward(q, k_compressed, v_compressed, block_ends, o, L, M)
-        ctx.scale = scale
+        ctx.scale, ctx.blocks = scale, blocks
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, kc, vc, block_ends, o, L, M = ctx.saved_tensors
-        dq, dkc, dvc = ops.cmp_attn_bwd(q, kc, vc, block_ends, o, do, L, M, ctx.scale)
+        dq, dkc, dvc = ops.cmp_attn_bwd(q, kc, vc, block_ends, o, do, L, M, ctx.scale, ctx.blocks)
         return dq, dkc.transpose(-1, -2), dvc, None, None, None, None
 
 
@@ -464,12 +464,16 @@ class _Launcher:
             else:
                 dO, dQ, dK, dV = a["dOut"], a["dQ"], a["dK"], a["dV"]
                 if kind == "win":
+                    nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, 0)
+                    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
                     rc = lib.nsa_sliding_bwd(ptr(Q), ptr(K), ptr(V), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ), ptr(dK),
-                                             ptr(dV), i64(strides), B, H, G, Tq, dk, dv, int(a["WINDOW_SIZE"]), scale, code, st)
+                                             ptr(dV), i64(strides), B, H, G, Tq, dk, dv, int(a["WINDOW_SIZE"]), scale, code,
+                                             ptr(ws), nbytes, st)
                 elif kind == "cmp":
                     be = a["Block_ends"].to(torch.int32).contiguous()
                     rc = lib.nsa_cmp_attn_bwd(ptr(Q), ptr(K), ptr(V), ptr(be), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ),
-                                              ptr(dK), ptr(dV), i64(strides), B, H, G, Tq, Tk, dk, dv, scale, code, st)
+                                              ptr(dK), ptr(dV), i64(strides), B, H, G, Tq, Tk, dk, dv, scale, code, 0, 0, 0,
+                                              None, 0, st)
                 else:
                     n = int(a["N_BLOCKS"])
                     lp = int(a["BLOCK_SIZE_SELECTION"])

@@ -59,10 +59,12 @@ def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float):
     dkey = torch.zeros(B, G, T, dk, device=dev, dtype=q.dtype)
     dval = torch.zeros(B, G, T, dv, device=dev, dtype=q.dtype)
     s = _fwd_strides(q, k, v, o, L, M) + list(dq.stride()) + list(dkey.stride()) + list(dval.stride())
+    nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, T, T, dk, dv, 0)
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
         check(lib.nsa_sliding_bwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq), ptr(dkey), ptr(dval),
-                                  i64(s), B, H, G, T, dk, dv, int(window), float(scale), dtype_code(q), stream_ptr(dev)),
-              "nsa_sliding_bwd")
+                                  i64(s), B, H, G, T, dk, dv, int(window), float(scale), dtype_code(q), ptr(ws), nbytes,
+                                  stream_ptr(dev)), "nsa_sliding_bwd")
     return dq, dkey, dval
 
 
@@ -82,7 +84,8 @@ def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None):
     return o, L, M
 
 
-def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float):
+def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=None):
+    bl, bd, bn = blocks if blocks is not None else (0, 0, 0)
     dev = require_cuda(q, k_cmp, v_cmp, block_ends, o, do, L, M)
     B, H, T, dk = q.shape
     G, NB, dv = k_cmp.shape[1], k_cmp.shape[-1], v_cmp.shape[-1]
@@ -94,10 +97,12 @@ def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float):
     dkc = torch.zeros(B, G, NB, dk, device=dev, dtype=q.dtype)
     dvc = torch.zeros(B, G, NB, dv, device=dev, dtype=q.dtype)
     s = _fwd_strides(q, k_cmp, v_cmp, o, L, M) + list(dq.stride()) + list(dkc.stride()) + list(dvc.stride())
+    nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, T, NB, dk, dv, 1)
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
         check(lib.nsa_cmp_attn_bwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq),
                                    ptr(dkc), ptr(dvc), i64(s), B, H, G, T, NB, dk, dv, float(scale), dtype_code(q),
-                                   stream_ptr(dev)), "nsa_cmp_attn_bwd")
+                                   int(bl), int(bd), int(bn), ptr(ws), nbytes, stream_ptr(dev)), "nsa_cmp_attn_bwd")
     return dq, dkc, dvc
 
 

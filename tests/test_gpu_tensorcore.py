@@ -99,3 +99,82 @@ def test_forward_tensorcore_vs_generic_at_scale():
     assert max_abs(o.float(), og.float()) < 2e-2
     fin = torch.isfinite(Mg)
     assert torch.equal(torch.isfinite(M), fin) and max_abs((M + L)[fin], (Mg + Lg)[fin]) < 2e-2
+
+
+def _grad_close(a, ref, what):
+    tol = 2e-2 * max(1.0, ref.abs().max().item())
+    err = max_abs(a.float(), ref)
+    assert err < tol, f"{what}: max-abs {err:.4g} > {tol:.4g}"
+
+
+@pytest.mark.parametrize("dk,dv,H,G,T,w", [(64, 64, 4, 2, 512, 200), (192, 128, 4, 1, 1024, 512),
+                                           (128, 128, 2, 1, 384, 128), (192, 128, 2, 1, 256, 1000)])
+def test_sliding_backward_tensorcore_vs_oracle(dk, dv, H, G, T, w):
+    from nsa import ops
+    q, k, v, do = _inputs(2, H, G, T, dk, dv, seed=4)
+    scale = dk ** -0.5
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
+    o, L, M = ops.sliding_fwd(qd, kd, vd, w, scale)
+    dq, dkey, dval = ops.sliding_bwd(qd, kd, vd, o, dod, L, M, w, scale)
+    dq2, dkey2, dval2 = ops.sliding_bwd(qd, kd, vd, o, dod, L, M, w, scale)
+    torch.cuda.synchronize()
+    _no_timeouts()
+    assert torch.equal(dq, dq2) and torch.equal(dkey, dkey2) and torch.equal(dval, dval2)   # fixed summation order
+    qo, ko, vo = (t.float().requires_grad_(True) for t in (q, k, v))
+    g = torch.autograd.grad(O.sliding_window_attention(qo, ko, vo, w, scale), (qo, ko, vo), do.float())
+    _grad_close(dq, g[0], "dq")
+    _grad_close(dkey.transpose(-1, -2), g[1], "dk")
+    _grad_close(dval, g[2], "dv")
+
+
+@pytest.mark.parametrize("dk,dv,H,G,T", [(64, 64, 4, 2, 2048), (192, 128, 2, 1, 4096 + 2048)])
+def test_compression_backward_tensorcore_vs_oracle(dk, dv, H, G, T):
+    from nsa import ops
+    l, d = 32, 16
+    nb = (T - l) // d + 1
+    nbp = O.next_pow2(nb)
+    q, kc, vc, do = _inputs(1, H, G, T, dk, dv, Tk=nbp, seed=5)
+    kc[..., nb:] = 0
+    vc[:, :, nb:] = 0
+    be = torch.full((nbp,), 999999, dtype=torch.int32)
+    be[:nb] = torch.arange(nb, dtype=torch.int32) * d + l - 1
+    scale = dk ** -0.5
+    qd, kd, vd, dod, bed = (t.to(DEV) for t in (q, kc, vc, do, be))
+    o, L, M = ops.cmp_attn_fwd(qd, kd, vd, bed, scale, blocks=(l, d, nb))
+    dq, dkc, dvc = ops.cmp_attn_bwd(qd, kd, vd, bed, o, dod, L, M, scale, blocks=(l, d, nb))
+    torch.cuda.synchronize()
+    _no_timeouts()
+    qo, ko, vo = (t.float().requires_grad_(True) for t in (q, kc, vc))
+    g = torch.autograd.grad(O.compression_attention(qo, ko, vo, be, scale), (qo, ko, vo), do.float())
+    _grad_close(dq, g[0], "dq")
+    _grad_close(dkc.transpose(-1, -2), g[1], "dk_cmp")
+    _grad_close(dvc, g[2], "dv_cmp")
+    assert (dkc[:, :, nb:] == 0).all() and (dvc[:, :, nb:] == 0).all()
+
+
+def test_backward_tensorcore_vs_generic_at_scale():
+    from nsa import ops
+    B, H, G, T, dk, dv = 1, 16, 1, 4096, 192, 128
+    q, k, v, do = (t.to(DEV) for t in _inputs(B, H, G, T, dk, dv, seed=6))
+    scale = dk ** -0.5
+    o, L, M = ops.sliding_fwd(q, k, v, 512, scale)
+    tc = ops.sliding_bwd(q, k, v, o, do, L, M, 512, scale)
+    gen = _generic(lambda: ops.sliding_bwd(q, k, v, o, do, L, M, 512, scale))
+    for a, b_, n in zip(tc, gen, ("dq", "dk", "dv")):
+        _grad_close(a, b_.float().cpu(), "sliding " + n)
+    l, d = 32, 16
+    nb = (T - l) // d + 1
+    nbp = O.next_pow2(nb)
+    kc = torch.zeros(B, G, dk, nbp, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros(B, G, nbp, dv, device=DEV, dtype=torch.bfloat16)
+    kc[..., :nb] = torch.randn(B, G, dk, nb, device=DEV).bfloat16()
+    vc[:, :, :nb] = torch.randn(B, G, nb, dv, device=DEV).bfloat16()
+    be = torch.full((nbp,), 999999, dtype=torch.int32, device=DEV)
+    be[:nb] = torch.arange(nb, dtype=torch.int32, device=DEV) * d + l - 1
+    o, L, M = ops.cmp_attn_fwd(q, kc, vc, be, scale, blocks=(l, d, nb))
+    tc = ops.cmp_attn_bwd(q, kc, vc, be, o, do, L, M, scale, blocks=(l, d, nb))
+    gen = _generic(lambda: ops.cmp_attn_bwd(q, kc, vc, be, o, do, L, M, scale))
+    torch.cuda.synchronize()
+    _no_timeouts()
+    for a, b_, n in zip(tc, gen, ("dq", "dk", "dv")):
+        _grad_close(a, b_.float().cpu(), "compression " + n)
