@@ -1,0 +1,341 @@
+#!/usr/bin/env python3
+"""Benchmark of the NSA layer hot path (forward + backward) on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --gpus N ...            # the reference algorithm on the host CPU
+
+Workload (BASELINE.json's metric): one NSA layer forward + backward at T = 65536, H = 64 query heads,
+G = 4 KV groups, dk = 192, dv = 128, window 512, l = 32, d = 16, l' = 64, n = 16 (3 forced blocks),
+sigmoid gates, d_model = 2560, bf16, synthetic seeded inputs (keys carry a per-64-token-block offset).
+One sequence per GPU (weak scaling); with N > 1 the only collective is the NCCL all-reduce of the
+compression-MLP and gate-MLP weight gradients, inside the timed step.
+
+Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM; `e2e` = the same step
+fed from pinned host buffers each step (host->device copies and a device->host read of the result
+inside the timed region); `roofline` = the dominant kernel against the measured bf16 tensor peak;
+`cpu_baseline` = the CPU oracle (a restatement of the reference's algorithm) on a bounded sample.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "nsa-test_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+CFG = dict(H=64, G=4, dk=192, dv=128, w=512, l=32, d=16, l_prime=64, n=16, d_model=2560)
+METRIC = "NSA layer fwd+bwd tokens/s at T=64K"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(tflops=d.get("bf16_tflops", 1590.0), tflops_sustained=d.get("bf16_tflops_sustained", 1400.0),
+                    hbm_gbs=d.get("hbm_gbs", 6650.0), source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi SM clock / throttle-reason samples while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for nme, val in zip(names, f[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nme)
+        sm.sort()
+        busy = sm[len(sm) // 2:] if sm else []          # upper half = samples taken under load
+        med = busy[len(busy) // 2] if busy else None
+        return dict(sm_mhz=med, sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+
+
+# --------------------------------------------------------------------------------------------------
+# workload
+# --------------------------------------------------------------------------------------------------
+
+def make_device_inputs(T, dev, seed, B=1):
+    c = CFG
+    g = torch.Generator(device=dev).manual_seed(seed)
+    rn = lambda *s, std=1.0: torch.randn(*s, generator=g, device=dev) * std
+    q = rn(B, c["H"], T, c["dk"]).bfloat16()
+    k = rn(B, c["G"], c["dk"], T)
+    off = rn(B, c["G"], c["dk"], T // c["l_prime"], std=0.5)
+    k = (k + off.repeat_interleave(c["l_prime"], dim=-1)).bfloat16()
+    v = rn(B, c["G"], T, c["dv"]).bfloat16()
+    do = rn(B, c["H"], T, c["dv"]).bfloat16()
+    x = rn(B, T, c["d_model"]).bfloat16()
+    dk, l = c["dk"], c["l"]
+    params = dict(pos_embed=rn(l, l, std=0.02), w1=rn(2 * dk, dk + l, std=0.02), b1=torch.zeros(2 * dk, device=dev),
+                  w2=rn(dk, 2 * dk, std=0.02), b2=torch.zeros(dk, device=dev),
+                  gw1=rn(c["d_model"] // 2, c["d_model"], std=0.02).bfloat16(), gb1=torch.zeros(c["d_model"] // 2, device=dev).bfloat16(),
+                  gw2=rn(3 * c["H"], c["d_model"] // 2, std=0.02).bfloat16(), gb2=torch.zeros(3 * c["H"], device=dev).bfloat16())
+    for p_ in params.values():
+        p_.requires_grad_(True)
+    return dict(q=q, k=k, v=v, do=do, x=x), params
+
+
+def layer_step(inp, params, cfg, world):
+    """One forward + backward of the layer; returns a scalar tensor summarising the result."""
+    from nsa.kernels import nsa_layer
+    lin = torch.nn.functional.linear
+    q = inp["q"].detach().requires_grad_(True)
+    k = inp["k"].detach().requires_grad_(True)
+    v = inp["v"].detach().requires_grad_(True)
+    logits = lin(torch.relu(lin(inp["x"], params["gw1"], params["gb1"])), params["gw2"], params["gb2"])
+    phi = (params["pos_embed"], params["w1"], params["b1"], params["w2"], params["b2"])
+    out = nsa_layer(q, k, v, logits, phi, cfg)
+    plist = list(params.values())
+    grads = torch.autograd.grad(out, [q, k, v] + plist, inp["do"])
+    if world > 1:
+        import torch.distributed as dist
+        flat = torch.cat([g_.float().reshape(-1) for g_ in grads[3:]])
+        dist.all_reduce(flat)
+    return out[0, 0, -1, :8].float().sum() + grads[0][0, 0, -1, :8].float().sum()
+
+
+def attention_flops(T):
+    """Algorithmic attention FLOPs per sequence (masked-out keys do not count): forward 2(dk+dv)N,
+    backward 2(3dk+2dv)N per (head, query) with N valid keys; selection counted at n full blocks minus
+    the causal clipping of the block holding the query."""
+    c = CFG
+    H, dk, dv, w, l, d, lp, n = c["H"], c["dk"], c["dv"], c["w"], c["l"], c["d"], c["l_prime"], c["n"]
+    t = torch.arange(T, dtype=torch.float64)
+    n_win = torch.clamp(t + 1, max=w).sum().item()
+    n_cmp = torch.clamp(torch.floor((t - l + 1) / d) + 1, min=0).sum().item()
+    blocks_visible = torch.floor(t / lp) + 1
+    full = torch.clamp(blocks_visible - 1, max=n - 1)                 # earlier blocks, fully visible
+    n_slc = (full * lp + (t % lp) + 1).sum().item()
+    per_key = dict(fwd=2 * (dk + dv), bwd=2 * (3 * dk + 2 * dv))
+    return {br: {ph: per_key[ph] * cnt * H for ph in per_key} for br, cnt in (("win", n_win), ("cmp", n_cmp), ("slc", n_slc))}
+
+
+def kernel_flops(T):
+    """Algorithmic FLOPs of one launch of each tensor-core kernel family (what that kernel's role requires)."""
+    c = CFG
+    dk, dv = c["dk"], c["dv"]
+    a = attention_flops(T)
+    unit = {br: a[br]["fwd"] / (2 * (dk + dv)) for br in a}            # (head, query, key) triples
+    f = {}
+    for br in ("win", "cmp"):
+        f[f"fa_fwd_{br}"] = unit[br] * 2 * (dk + dv)
+        f[f"fa_bwd_dq_{br}"] = unit[br] * 2 * (2 * dk + dv)             # S, dP, dQ
+        f[f"fa_bwd_dkv_{br}"] = unit[br] * 2 * (2 * dk + 2 * dv)        # S^T, dP^T, dV, dK
+    f["slc_fwd"] = unit["slc"] * 2 * (dk + dv)
+    f["slc_bwd_dq"] = unit["slc"] * 2 * (2 * dk + dv)
+    f["slc_bwd_dkv"] = unit["slc"] * 2 * (2 * dk + 2 * dv)
+    return f
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm: the oracle (port of the reference's algorithm) on a bounded sample of the workload
+# --------------------------------------------------------------------------------------------------
+
+def cpu_oracle_tokens_per_s(T_sample, steps, threads):
+    from oracle import nsa_oracle as O
+    c = CFG
+    torch.set_num_threads(threads)
+    inp = O.make_inputs(1, c["H"], c["G"], T_sample, c["dk"], c["dv"], c["d_model"], c["l"], seed=0, block_offset_std=0.5,
+                        l_prime=c["l_prime"], dtype=torch.bfloat16)
+    times = []
+    for _ in range(steps):
+        q, k, v = (inp[n_].clone().requires_grad_(True) for n_ in ("q", "k", "v"))
+        t0 = time.perf_counter()
+        r = O.nsa_layer(q, k, v, inp["x"], inp["phi"], inp["gate"], l=c["l"], d=c["d"], l_prime=c["l_prime"], n=c["n"], w=c["w"])
+        torch.autograd.grad(r["out"], (q, k, v), inp["do"])
+        times.append(time.perf_counter() - t0)
+    return T_sample / (sum(times) / len(times)), sum(times) / len(times)
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's CPU path.  The reference is a Python package that cannot be
+    installed on the benchmark box, so its algorithm runs as the committed CPU oracle (kind "port")."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    T_sample = args.cpu_sample
+    for _ in range(min(args.warmup, 1)):
+        cpu_oracle_tokens_per_s(T_sample, 1, threads)
+    tps, sec = cpu_oracle_tokens_per_s(T_sample, max(1, args.steps), threads)
+    value = tps * args.gpus  # N independent sequences would take N times as long on the same host
+    value = tps
+    sample = f"full layer fwd+bwd, fp32 on bf16-rounded inputs, one sequence of T={T_sample} (same heads/dims as the workload)"
+    line = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                ms_per_step=sec * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+                impl="reference", config=dict(workload=f"NSA layer fwd+bwd, B=1 per GPU, T={T_sample} sample of T={args.T}", **CFG),
+                cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind="port", sample=sample),
+                e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--T", type=int, default=65536)
+    ap.add_argument("--cpu-sample", type=int, default=2048, help="sequence length of the CPU-oracle sample")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import nsa
+    from nsa import _lib
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    T = args.T
+    c = CFG
+    cfg = nsa.NSAConfig(d_model=c["d_model"], head_dim_qk=c["dk"], head_dim_v=c["dv"], l=c["l"], d=c["d"], l_prime=c["l_prime"],
+                        n=c["n"], w=c["w"], n_heads=c["H"], n_kv_groups=c["G"])
+    inp, params = make_device_inputs(T, dev, seed=rank)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput -------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        layer_step(inp, params, cfg, world)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        layer_step(inp, params, cfg, world)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t_ms = torch.tensor([ms], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t_ms, op=torch.distributed.ReduceOp.MAX)
+    ms_per_step = t_ms.item() / args.steps
+    value = world * T / (ms_per_step * 1e-3)
+
+    # ---- end to end: inputs come from pinned host memory every step, result read back -----------
+    host = {k_: torch.empty(v_.shape, dtype=v_.dtype, pin_memory=True).copy_(v_) for k_, v_ in inp.items()}
+    h2d = sum(t_.numel() * t_.element_size() for t_ in host.values())
+    res_host = torch.empty(1, dtype=torch.float32, pin_memory=True)
+
+    def e2e_step():
+        dinp = {k_: v_.to(dev, non_blocking=True) for k_, v_ in host.items()}
+        res = layer_step(dinp, params, cfg, world)
+        res_host.copy_(res.reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_step()
+    barrier()
+    e2e_steps = max(1, min(args.steps, 3))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t_e2e = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t_e2e, op=torch.distributed.ReduceOp.MAX)
+    e2e_value = world * T / (t_e2e.item() / e2e_steps * 1e-3)
+
+    # ---- per-kernel times (CUDA events around every launch, outside the timed region) -----------
+    prof = _lib.profile_kernels(lambda: layer_step(inp, params, cfg, world))
+    launches = sum(n_ for n_, _ in prof.values())
+    kflops = kernel_flops(T)
+    peaks = measured_peaks()
+    timeouts = _lib.lib.nsa_device_timeouts(0)
+    if rank == 0:
+        cand = {k_: v_ for k_, v_ in prof.items() if k_ in kflops}
+        top = max(cand, key=lambda k_: cand[k_][1]) if cand else None
+        roofline = None
+        if top:
+            n_l, tot = cand[top]
+            achieved = kflops[top] / (tot / n_l * 1e-3) / 1e12
+            roofline = dict(bound="tensor", kernel=top, achieved=round(achieved, 1), peak=peaks["tflops_sustained"], unit="TFLOP/s",
+                            frac=round(achieved / peaks["tflops_sustained"], 4), traffic=None, peak_source=peaks["source"] + " (sustained bf16)",
+                            ms_per_launch=round(tot / n_l, 4))
+        att = attention_flops(T)
+        att_total = sum(att[b_][p_] for b_ in att for p_ in att[b_])
+        kern_ms = sum(ms_ for _, ms_ in prof.values())
+        breakdown = {k_: round(v_[1], 3) for k_, v_ in sorted(prof.items(), key=lambda kv: -kv[1][1])}
+        cpu = None
+        if not args.no_cpu:
+            threads = os.cpu_count() or 1
+            tps, sec = cpu_oracle_tokens_per_s(args.cpu_sample, 1, threads)
+            cpu = dict(value=round(tps, 2), unit="tokens/s", cores=threads, kind="port",
+                       sample=f"one full-layer fwd+bwd of the CPU oracle (fp32) at T={args.cpu_sample}, same heads/dims, {sec:.1f} s")
+        line = dict(metric=METRIC, value=round(value, 1), unit="tokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                    ms_per_step=round(ms_per_step, 3), higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                    data="synthetic", impl="ours",
+                    config=dict(workload=f"NSA layer fwd+bwd, one sequence per GPU, T={T}", l2="inputs (>= 1.6 GB per tensor) exceed the 126 MB L2",
+                                parallelism=f"dp{world}", **c),
+                    e2e=dict(value=round(e2e_value, 1), unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=4),
+                    gpu_launches=launches * args.steps, roofline=roofline, cpu_baseline=cpu, clocks=clocks,
+                    attention_tflops_per_s=round(att_total / (ms_per_step * 1e-3) / 1e12, 1),
+                    attention_frac_of_peak=round(att_total / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"], 4),
+                    kernel_ms=breakdown, kernel_ms_total=round(kern_ms, 3), device_timeouts=timeouts)
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -54,6 +54,13 @@ NSA_API int nsa_set_kernel_family(int family);
  * the counter.  Negative = error. */
 NSA_API int nsa_device_timeouts(int reset);
 
+/* Per-kernel timing for benchmarks: while enabled, every kernel launch of this library is bracketed
+ * by a CUDA event pair on its stream.  nsa_profile_report() synchronises the device and writes one
+ * line per kernel family, "name launches total_ms", in first-launch order.  Enabling clears old
+ * records.  Leave it off in timed regions (two extra event records per launch). */
+NSA_API int nsa_profile_enable(int on);
+NSA_API int nsa_profile_report(char* buf, size_t buf_bytes);
+
 /* Message for the last non-zero status returned on the calling thread. */
 NSA_API const char* nsa_last_error(void);
 /* Library / build identification: "nsa_b200 <version> sm_100a". */
@@ -100,12 +107,20 @@ NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp
  * and blocks starting at or beyond Tkv ignored, a repeated id counts once) intersected with
  * keys <= t.  indices is int32.
  * Replaces _nsa_sparse_selection_fwd_kernel / _bwd_kernel (nsa/kernels.py:594-833, 836-1148). */
+/* The tensor-core path works key-block-major (each KV block is staged once and shared by all queries
+ * and heads that selected it) and needs scratch for the inverse index and per-(query, slot) partial
+ * results: nsa_slc_fwd_workspace_bytes() bytes (256 when the stride-generic kernels will run). */
+NSA_API size_t nsa_slc_fwd_workspace_bytes(int B, int H, int G, int Tq, int Tkv, int dk, int dv,
+                                           int n_slots, int l_prime, int dtype);
 NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, const int32_t* indices, void* out,
                 float* L, float* M, const int64_t* strides26, int B, int H, int G, int Tq, int Tkv,
-                int n_slots, int l_prime, int dk, int dv, float scale, int dtype, void* stream);
+                int n_slots, int l_prime, int dk, int dv, float scale, int dtype, void* workspace,
+                size_t workspace_bytes, void* stream);
 /* Backward; dK/dV are reduced per key block over the queries that selected it in a fixed order (an
- * inverse index "block -> queries" is built in the workspace), so results are run-to-run identical. */
-NSA_API size_t nsa_slc_bwd_workspace_bytes(int B, int G, int Tq, int Tkv, int n_slots, int l_prime);
+ * inverse index "block -> queries" is built in the workspace; the tensor-core path also keeps per-
+ * (query, slot) dQ partials and per-block dK/dV partials there), so results are run-to-run identical. */
+NSA_API size_t nsa_slc_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tkv, int dk, int dv,
+                                           int n_slots, int l_prime, int dtype);
 NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, const int32_t* indices, const void* out,
                 const void* dout, const float* L, const float* M, void* dq, void* dkey, void* dval,
                 const int64_t* strides38, int B, int H, int G, int Tq, int Tkv, int n_slots,

@@ -1,8 +1,15 @@
 // C ABI of the attention entry points declared in include/nsa_b200.h, plus error reporting.
 // Argument checking happens here; kernels never see a null pointer or an inconsistent size.
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
 #include "attn_args.cuh"
 #include "common.cuh"
 #include "fa_sm100.cuh"
+#include "slc_sm100.cuh"
 
 namespace nsa {
 
@@ -17,6 +24,29 @@ int fail(int code, const char* fmt, ...) {
   vsnprintf(error_buffer(), 512, fmt, ap);
   va_end(ap);
   return code;
+}
+
+namespace {
+struct ProfRecord { const char* name; cudaEvent_t a, b; };
+std::mutex g_prof_mu;
+std::vector<ProfRecord> g_prof;
+std::atomic<int> g_prof_on{0};
+}  // namespace
+
+KernelTimer::KernelTimer(const char* name, cudaStream_t st) : st_(st), slot_(-1) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  ProfRecord r;
+  r.name = name;
+  if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+  cudaEventRecord(r.a, st);
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  slot_ = (int)g_prof.size();
+  g_prof.push_back(r);
+}
+KernelTimer::~KernelTimer() {
+  if (slot_ < 0) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  cudaEventRecord(g_prof[slot_].b, st_);
 }
 
 int check_launch(const char* what) {
@@ -44,6 +74,9 @@ static int check_common(const char* who, int B, int H, int G, int Tq, int Tk, in
   return NSA_OK;
 }
 
+static bool tensor_core_bwd_ok_slc(const int64_t* s, int dtype, int H, int G, int Tq, int Tk, int dk, int dv, const void* q,
+                                   const void* k, const void* v, const void* o, const void* dout, const void* dq,
+                                   const void* dkey, const void* dval);
 static int g_kernel_family = 0;  // 0: tensor-core kernels where they apply, 1: stride-generic kernels only
 
 // canonical contiguous layouts: q [B,H,T,dk], k [B,G,dk,Tk] (strides given as z,g,n,k), v [B,G,Tk,dv], o [B,H,T,dv]
@@ -76,9 +109,53 @@ static bool tensor_core_bwd_ok(const int64_t* s, int dtype, int B, int H, int G,
          aligned16(dkey) && aligned16(dval);
 }
 
+static bool tensor_core_bwd_ok_slc(const int64_t* s, int dtype, int H, int G, int Tq, int Tk, int dk, int dv, const void* q,
+                                   const void* k, const void* v, const void* o, const void* dout, const void* dq,
+                                   const void* dkey, const void* dval) {
+  if (g_kernel_family != 0 || dtype != NSA_BF16 || !canonical_fwd(s, H, G, Tq, Tk, dk, dv)) return false;
+  const int64_t gq[4] = {(int64_t)H * Tq * dk, (int64_t)Tq * dk, dk, 1};
+  const int64_t gk[4] = {(int64_t)G * Tk * dk, (int64_t)Tk * dk, dk, 1};
+  const int64_t gv[4] = {(int64_t)G * Tk * dv, (int64_t)Tk * dv, dv, 1};
+  for (int i = 0; i < 4; ++i)
+    if (s[22 + i] != gq[i] || s[26 + i] != gk[i] || s[30 + i] != gv[i]) return false;
+  return aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && aligned16(dout) && aligned16(dq) &&
+         aligned16(dkey) && aligned16(dval);
+}
+
 }  // namespace nsa
 
 using namespace nsa;
+
+extern "C" NSA_API int nsa_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (auto& r : g_prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  g_prof.clear();
+  g_prof_on.store(on ? 1 : 0);
+  return NSA_OK;
+}
+
+extern "C" NSA_API int nsa_profile_report(char* buf, size_t buf_bytes) {
+  NSA_REQUIRE(buf && buf_bytes > 0, "profile_report: no buffer");
+  if (cudaDeviceSynchronize() != cudaSuccess) return fail(NSA_ERR_LAUNCH, "profile_report: device error");
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  std::map<std::string, std::pair<int, double>> agg;
+  std::vector<std::string> order;
+  for (auto& r : g_prof) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, r.a, r.b) != cudaSuccess) continue;
+    auto it = agg.find(r.name);
+    if (it == agg.end()) { agg[r.name] = {1, ms}; order.push_back(r.name); }
+    else { it->second.first += 1; it->second.second += ms; }
+  }
+  size_t off = 0;
+  buf[0] = 0;
+  for (auto& n : order) {
+    const int w = snprintf(buf + off, buf_bytes - off, "%s %d %.6f\n", n.c_str(), agg[n].first, agg[n].second);
+    if (w < 0 || (size_t)w >= buf_bytes - off) break;
+    off += (size_t)w;
+  }
+  return NSA_OK;
+}
 
 extern "C" NSA_API int nsa_set_kernel_family(int family) {
   NSA_REQUIRE(family == 0 || family == 1, "kernel family must be 0 (auto) or 1 (generic)");
@@ -177,10 +254,15 @@ extern "C" NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const 
 
 extern "C" NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, const int32_t* indices, void* out, float* L,
                            float* M, const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots,
-                           int l_prime, int dk, int dv, float scale, int dtype, void* stream) {
+                           int l_prime, int dk, int dv, float scale, int dtype, void* workspace, size_t workspace_bytes,
+                           void* stream) {
   if (int rc = check_common("slc_fwd", B, H, G, Tq, Tkv, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && indices && out && strides, "slc_fwd: null pointer");
   NSA_REQUIRE(l_prime > 0 && n_slots >= 0, "slc_fwd: bad block size / slot count");
+  if (g_kernel_family == 0 && dtype == NSA_BF16 && L && M && B > 0 && slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime) &&
+      canonical_fwd(strides, H, G, Tq, Tkv, dk, dv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out))
+    return slc_fwd_sm100(q, k, v, indices, strides + 22, out, L, M, B, H, G, Tq, Tkv, dk, dv, n_slots, l_prime, scale,
+                         workspace, workspace_bytes, (cudaStream_t)stream);
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o = out; a.L = L; a.M = M; a.indices = indices;
   fill_fwd_strides(a, strides);
@@ -190,8 +272,17 @@ extern "C" NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, 
   return launch_attn_generic(a, kSlc, dtype, false, (cudaStream_t)stream);
 }
 
-extern "C" NSA_API size_t nsa_slc_bwd_workspace_bytes(int B, int G, int Tq, int Tkv, int n_slots, int l_prime) {
+extern "C" NSA_API size_t nsa_slc_fwd_workspace_bytes(int B, int H, int G, int Tq, int Tkv, int dk, int dv, int n_slots,
+                                                      int l_prime, int dtype) {
+  if (g_kernel_family != 0 || dtype != NSA_BF16 || B <= 0 || !slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime)) return 256;
+  return slc_fwd_sm100_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n_slots, l_prime);
+}
+
+extern "C" NSA_API size_t nsa_slc_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tkv, int dk, int dv, int n_slots,
+                                                      int l_prime, int dtype) {
   if (B <= 0 || G <= 0 || Tq <= 0 || Tkv <= 0 || n_slots <= 0 || l_prime <= 0) return 256;
+  if (g_kernel_family == 0 && dtype == NSA_BF16 && slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime))
+    return slc_bwd_sm100_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n_slots, l_prime);
   return slc_csr_workspace_bytes(B, G, Tq, Tkv, n_slots, l_prime);
 }
 
@@ -204,6 +295,10 @@ extern "C" NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, 
   NSA_REQUIRE(q && k && v && indices && out && dout && L && M && dq && dkey && dval && strides, "slc_bwd: null pointer");
   NSA_REQUIRE(l_prime > 0 && n_slots > 0, "slc_bwd: bad block size / slot count");
   if (B == 0 || Tq == 0 || Tkv == 0) return NSA_OK;
+  if (slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime) &&
+      tensor_core_bwd_ok_slc(strides, dtype, H, G, Tq, Tkv, dk, dv, q, k, v, out, dout, dq, dkey, dval))
+    return slc_bwd_sm100(q, k, v, indices, strides + 34, out, dout, L, M, dq, dkey, dval, B, H, G, Tq, Tkv, dk, dv, n_slots,
+                         l_prime, scale, workspace, workspace_bytes, (cudaStream_t)stream);
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.indices = indices;
   a.dq = dq; a.dk_out = dkey; a.dv_out = dval;

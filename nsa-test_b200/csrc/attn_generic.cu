@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn_bwd_dkv_generic(const __grid
       const int e = e0 + lane;
       int t = -1;
       if (e < tend) {
-        t = (MODE == kSlc) ? tl[e] : e;
+        t = (MODE == kSlc) ? (tl[e] & 0xFFFFFF) : e;
         if (MODE == kSlc && a.causal && t < key) t = -1;
       }
       float p = 0.f, ds = 0.f;
@@ -271,12 +271,14 @@ __global__ void __launch_bounds__(kWarps * 32) attn_bwd_dkv_generic(const __grid
 // ------------------------------------------------------------------------------------------------
 template <typename T, int MODE>
 static int launch_fwd_t(const AttnArgs& a, cudaStream_t st) {
+  KernelTimer kt("attn_fwd_generic", st);
   dim3 grid((a.Tq + kWarps - 1) / kWarps, a.B * a.H);
   attn_fwd_generic<T, MODE><<<grid, kWarps * 32, kWarps * a.dk * sizeof(float), st>>>(a);
   return check_launch("attn_fwd_generic");
 }
 template <typename T, int MODE>
 static int launch_bwd_t(const AttnArgs& a, cudaStream_t st) {
+  KernelTimer kt("attn_bwd_generic", st);
   const size_t sm = kWarps * (a.dk + a.dv) * sizeof(float);
   dim3 gq((a.Tq + kWarps - 1) / kWarps, a.B * a.H);
   attn_bwd_dq_generic<T, MODE><<<gq, kWarps * 32, sm, st>>>(a);

@@ -17,6 +17,15 @@ char* error_buffer();
 int fail(int code, const char* fmt, ...);
 int check_launch(const char* what);
 
+// Optional per-kernel timing (nsa_profile_enable): records a CUDA event pair around a launch on the
+// launching stream.  Costs nothing while profiling is off.
+struct KernelTimer {
+  KernelTimer(const char* name, cudaStream_t st);
+  ~KernelTimer();
+  cudaStream_t st_;
+  int slot_;
+};
+
 #define NSA_REQUIRE(cond, ...)                                  \
   do {                                                          \
     if (!(cond)) return ::nsa::fail(NSA_ERR_ARG, __VA_ARGS__);  \

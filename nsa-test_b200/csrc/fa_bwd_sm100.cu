@@ -58,6 +58,13 @@ __global__ void fa_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __
   }
 }
 
+void launch_bwd_prep(const void* o, const void* dout, const float* L, const float* M, float* D, float* lse2, int64_t rows, int dv,
+                     cudaStream_t st) {
+  KernelTimer kt("bwd_prep", st);
+  fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, L, M, D, lse2,
+                                                               rows, dv);
+}
+
 // ------------------------------------------------------------------------------------------------
 // dQ kernel: 128 queries of one head per CTA; warps 0-3 compute, warp 4 TMA, warp 5 UMMA
 // ------------------------------------------------------------------------------------------------
@@ -549,8 +556,12 @@ static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, con
   if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<DK, DV>::kDynamic) != cudaSuccess ||
       cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<DK, DV>::kDynamic) != cudaSuccess)
     return fail(NSA_ERR_LAUNCH, "fa_bwd: cannot reserve shared memory");
-  kq<<<dim3(p.Tq / 128, p.B * p.H), 192, DqSmem<DK, DV>::kDynamic, st>>>(tq128, tdo128, tk, tv, p);
+  {
+    KernelTimer kt(MODE == kWin ? "fa_bwd_dq_win" : "fa_bwd_dq_cmp", st);
+    kq<<<dim3(p.Tq / 128, p.B * p.H), 192, DqSmem<DK, DV>::kDynamic, st>>>(tq128, tdo128, tk, tv, p);
+  }
   if (int rc = check_launch("fa_bwd_dq_sm100")) return rc;
+  KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);
   kkv<<<dim3(p.Tk / 128, p.hsplit, p.B * p.G), 192, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, p);
   return check_launch("fa_bwd_dkv_sm100");
 }
@@ -603,6 +614,7 @@ int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, con
   if (rc) return rc == NSA_ERR_UNSUPPORTED ? fail(rc, "fa_bwd_sm100: unsupported head dims") : rc;
   if (p.hsplit > 1) {
     const int64_t nk = (int64_t)B * G * Tk * dk, nv = (int64_t)B * G * Tk * dv;
+    KernelTimer kt("fa_dkv_reduce", st);
     dkv_reduce_kernel<<<(unsigned)((nk / 2 + 255) / 256), 256, 0, st>>>(p.dk_part, p.dk, nk, p.hsplit);
     dkv_reduce_kernel<<<(unsigned)((nv / 2 + 255) / 256), 256, 0, st>>>(p.dv_part, p.dv, nv, p.hsplit);
     return check_launch("dkv_reduce");

@@ -381,6 +381,7 @@ static int launch_fa_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const C
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kDynamic);
   if (e != cudaSuccess) return fail(NSA_ERR_LAUNCH, "fa_fwd: cannot reserve %d bytes of shared memory: %s", SM::kDynamic, cudaGetErrorString(e));
   dim3 grid(p.Tq / kBM, p.B * (p.H / 2));
+  KernelTimer kt(MODE == kWin ? "fa_fwd_win" : "fa_fwd_cmp", st);
   kern<<<grid, kFaThreads, SM::kDynamic, st>>>(tq, tk, tv, p);
   return check_launch("fa_fwd_sm100");
 }

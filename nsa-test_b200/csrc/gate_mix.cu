@@ -82,6 +82,7 @@ extern "C" NSA_API int nsa_gate_mix_fwd(const float* logits, const void* o_cmp, 
   if (rows == 0) return NSA_OK;
   const unsigned grid = (unsigned)((rows + 7) / 8);
   cudaStream_t st = (cudaStream_t)stream;
+  KernelTimer kt("gate_mix_fwd", st);
   if (dtype == NSA_F32)
     gate_mix_fwd_kernel<float><<<grid, 256, 0, st>>>(logits, (const float*)o_cmp, (const float*)o_slc, (const float*)o_win,
                                                       (float*)out, gates_out, B, H, T, dv, gate_mode);
@@ -102,6 +103,7 @@ extern "C" NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, c
   if (rows == 0) return NSA_OK;
   const unsigned grid = (unsigned)((rows + 7) / 8);
   cudaStream_t st = (cudaStream_t)stream;
+  KernelTimer kt("gate_mix_bwd", st);
   if (dtype == NSA_F32)
     gate_mix_bwd_kernel<float><<<grid, 256, 0, st>>>(gates, (const float*)o_cmp, (const float*)o_slc, (const float*)o_win,
                                                       (const float*)dout, (float*)do_cmp, (float*)do_slc, (float*)do_win,

@@ -79,6 +79,7 @@ extern "C" NSA_API int nsa_phi_pool_fwd(const float* a, const float* c, const vo
   if (n_blocks == 0 || B * G == 0) return NSA_OK;
   dim3 grid(n_blocks, B * G);
   cudaStream_t st = (cudaStream_t)stream;
+  KernelTimer kt("phi_pool_fwd", st);
   if (dtype == NSA_F32)
     phi_pool_fwd_kernel<float><<<grid, 128, 0, st>>>(a, c, (const float*)v, vs[0], vs[1], vs[2], vs[3], hbar,
                                                       (float*)v_cmp, G, T, U, dv, l, d, n_blocks, nbp);
@@ -98,6 +99,7 @@ extern "C" NSA_API int nsa_phi_pool_bwd(const float* a, const float* c, const fl
   NSA_REQUIRE(l > 0 && d > 0 && n_blocks >= 0 && (int64_t)(n_blocks - 1) * d + l <= T, "phi_pool_bwd: bad blocks");
   if (B * G == 0 || T == 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  KernelTimer kt("phi_pool_bwd", st);
   phi_pool_bwd_tok_kernel<<<dim3(T, B * G), 128, 0, st>>>(a, c, dhbar, dv_cmp, da, dv, T, U, dv_dim, l, d, n_blocks,
                                                           nbp);
   if (int rc = check_launch("phi_pool_bwd_tok")) return rc;

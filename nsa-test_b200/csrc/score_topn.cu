@@ -179,6 +179,7 @@ extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const fl
   const size_t sm = ((size_t)hpg * dk + nbp + a_ + s_ + n_sel + 16 + kMaxN) * sizeof(float);
   if (sm > 200 * 1024) return fail(NSA_ERR_UNSUPPORTED, "score_topn: %zu bytes of shared memory needed", sm);
   cudaStream_t st = (cudaStream_t)stream;
+  KernelTimer kt("score_topn", st);
   dim3 grid(T, B * G);
   if (dtype == NSA_F32) {
     cudaFuncSetAttribute(score_topn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);

@@ -1,5 +1,6 @@
 // Inverse index for the selected-block attention backward: for every (batch, group, key block) the
-// list of query positions that selected the block, in ascending query order.
+// list of (query position | slot << 24) entries of the queries that selected the block, in ascending
+// query order.
 //
 // The reference accumulates dK/dV of selected blocks with atomics from every query tile
 // (nsa/kernels.py:1111-1115, 1140-1144); here each key block instead walks its own query list in a
@@ -11,18 +12,7 @@
 
 namespace nsa {
 
-constexpr int kChunk = 1024;  // queries per histogram chunk
-
-__device__ __forceinline__ int slot_block(const int* row, int64_t sn, int s, int t, int Tkv, int lprime,
-                                          int causal) {
-  const int id = row[s * sn];
-  if (id < 0) return -1;
-  const int64_t beg = (int64_t)id * lprime;
-  if (beg >= Tkv || (causal && beg > t)) return -1;
-  for (int s2 = 0; s2 < s; ++s2)
-    if (row[s2 * sn] == id) return -1;  // a repeated id counts once
-  return id;
-}
+constexpr int kChunk = 128;  // queries per histogram chunk (one warp orders the entries of a chunk)
 
 struct CsrArgs {
   const int* indices;
@@ -108,7 +98,7 @@ __global__ void csr_fill(const CsrArgs a, int slots_pad) {
     }
     const unsigned peers = __match_any_sync(0xffffffffu, id >= 0 ? id : -1 - lane);
     const int rank = __popc(peers & ((1u << lane) - 1u));
-    if (id >= 0) out[cur[id] + rank] = t;
+    if (id >= 0) out[cur[id] + rank] = t | (s << 24);  // query position and its slot
     __syncwarp();
     if (id >= 0 && rank == 0) cur[id] += __popc(peers);
     __syncwarp();
@@ -143,7 +133,8 @@ int build_slc_csr(const int* indices, const int64_t* sidx, int B, int G, int Tq,
   csr_layout(B, G, Tq, Tkv, nslots, lprime, &a.nblk, &a.nchunks, &o_hist, &o_off, &o_t, &total);
   if (!workspace || workspace_bytes < total)
     return fail(NSA_ERR_WORKSPACE, "selection backward needs %zu workspace bytes, got %zu", total, workspace_bytes);
-  if (nslots > 32) return fail(NSA_ERR_UNSUPPORTED, "selection backward supports at most 32 slots per query");
+  if (nslots > 32) return fail(NSA_ERR_UNSUPPORTED, "selection supports at most 32 slots per query here");
+  if (Tq >= (1 << 24)) return fail(NSA_ERR_UNSUPPORTED, "selection inverse index supports fewer than 2^24 queries");
   if ((size_t)a.nblk * sizeof(int) > 160 * 1024) return fail(NSA_ERR_UNSUPPORTED, "too many key blocks (%d)", a.nblk);
   a.indices = indices;
   for (int i = 0; i < 4; ++i) a.sidx[i] = sidx[i];
@@ -157,6 +148,7 @@ int build_slc_csr(const int* indices, const int64_t* sidx, int B, int G, int Tq,
     cudaFuncSetAttribute(csr_count, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     cudaFuncSetAttribute(csr_fill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
   }
+  KernelTimer kt("slc_inverse_index", st);
   dim3 grid(a.nchunks, B * G);
   csr_count<<<grid, 256, sm, st>>>(a);
   if (int rc = check_launch("csr_count")) return rc;

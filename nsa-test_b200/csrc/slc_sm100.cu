@@ -1,0 +1,1115 @@
+// Selected-block attention on tcgen05 tensor cores, key-block-major
+// (replaces _nsa_sparse_selection_fwd_kernel / _bwd_kernel, nsa/kernels.py:594-833, 836-1148, for bf16
+// tensors in canonical layouts with a 64-key selection block).
+//
+// The reference walks queries and, for each, gathers its selected blocks: every KV block is fetched once
+// per (query, head).  Here the work is turned around with the inverse index "block -> (query, slot)"
+// (select_csr.cu): a CTA keeps one KV block in shared memory and streams the queries that selected it
+// past it, 128 MMA rows at a time (128/heads_per_group queries x all heads of the GQA group), so a block
+// is read once per group of queries and shared by all their heads.  Each (query, slot) pair yields a
+// partial result; partials of a query are merged afterwards in slot order, which keeps everything
+// deterministic:
+//   forward   partial O (normalised, bf16) + (max, sum) per (query, slot, head) -> slc_combine_fwd
+//   backward  dQ partials per (query, slot, head) -> slc_combine_dq; dK/dV accumulate inside the CTA
+//             that owns the block (transposed tiles, M = 64 keys) and are flushed once per CTA.
+// CTAs own fixed-size ranges of the inverse index (not whole blocks), so a block selected by every
+// query (block 0) is spread over many CTAs.
+#include <cuda.h>
+
+#include "attn_args.cuh"
+#include "common.cuh"
+#include "fa_sm100.cuh"
+#include "slc_sm100.cuh"
+#include "sm100_ptx.cuh"
+
+namespace nsa {
+
+using namespace ptx;
+
+constexpr int kEntriesPerCta = 1024;  // inverse-index entries handled by one CTA
+constexpr float kLn2f = 0.6931471805599453f;
+constexpr float kLog2ef = 1.4426950408889634f;
+
+struct SlcParams {
+  const __nv_bfloat16* q;      // [B,H,Tq,dk]
+  const __nv_bfloat16* dout;   // [B,H,Tq,dv] (backward)
+  const int* csr_off;          // [BG, nblk+1]
+  const int* csr_t;            // [BG, Tq*nslots]
+  __nv_bfloat16* o_part;       // [BG,Tq,nslots,hpg,dv]  normalised partial outputs
+  float2* st_part;             // [BG,Tq,nslots,hpg]     (row max in log2 units, sum of exp2)
+  const float *D, *lse2;       // [B,H,Tq] backward statistics
+  __nv_bfloat16* dq_part;      // [BG,Tq,nslots,hpg,dk]
+  float *dk_part, *dv_part;    // [BG, nparts+nblk, 64, dk|dv] per-(CTA, block) partial sums (backward)
+  __nv_bfloat16 *dk_out, *dv_out;  // [B,G,Tk,dk|dv] gradients the reduced partials are added into
+  int B, H, G, Tq, Tk, nslots, nblk, hpg;
+  float scale, scale_log2;
+  int* timeouts;
+};
+
+// Walks the chunk schedule of a CTA: chunks of up to `qpc` consecutive entries that stay inside one block.
+struct ChunkWalker {
+  const int* off;
+  int e, e1, blk, blk_end, nblk, qpc;
+  __device__ ChunkWalker(const int* off_, int nblk_, int e0, int e1_, int qpc_) : off(off_), e(e0), e1(e1_), nblk(nblk_), qpc(qpc_) {
+    const int total = off[nblk];
+    e1 = min(e1, total);
+    // block holding entry e0: largest blk with off[blk] <= e0
+    int lo = 0, hi = nblk;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (off[mid] <= e) lo = mid; else hi = mid;
+    }
+    blk = lo;
+    blk_end = off[blk + 1];
+    skip_empty();
+  }
+  __device__ void skip_empty() {
+    while (e < e1 && e >= blk_end && blk + 1 < nblk) {
+      ++blk;
+      blk_end = off[blk + 1];
+    }
+  }
+  __device__ bool done() const { return e >= e1; }
+  __device__ int count() const { return min(qpc, min(blk_end, e1) - e); }
+  __device__ void next() {
+    e += count();
+    skip_empty();
+  }
+};
+
+// ------------------------------------------------------------------------------------------------
+// forward: partial attention of every (query, slot) against its block
+// ------------------------------------------------------------------------------------------------
+template <int DK, int DV>
+struct SlcFwdSmem {
+  static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2;
+  static constexpr int oK = 0, oV = oK + 2 * kK, oQ = oV + 2 * kV, oBar = oQ + 2 * kQ;
+  static constexpr int kDynamic = oBar + 256 + 1024;
+};
+struct SlcFwdBarriers {
+  uint64_t kv_full[2], kv_empty[2], q_full[2], q_empty[2], s_full[2], p_full[2], o_full[2], o_read[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+// gather 128 rows (qpc queries x hpg heads) of `width` bf16 into the K-major 128-byte-swizzled tile layout
+// (row r of the tile = query r / hpg of the chunk, head r % hpg; one row per producer thread)
+template <int WIDTH>
+__device__ __forceinline__ void gather_row(const __nv_bfloat16* base, uint8_t* dst, const int* entries, int cnt,
+                                           int b, int g, int H, int hpg, int T, int r) {
+  const int qi = r / hpg, hh = r % hpg;
+  const bool valid = qi < cnt;
+  const int t = valid ? (entries[qi] & 0xFFFFFF) : 0;
+  const __nv_bfloat16* src = base + (((int64_t)b * H + g * hpg + hh) * T + t) * WIDTH;
+  const uint32_t d0 = smem_u32(dst) + r * 128;
+  const int nbytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+#pragma unroll
+  for (int c = 0; c < WIDTH / 8; ++c) {
+    const uint32_t d = d0 + (c >> 3) * 16384 + (((c & 7) ^ (r & 7)) << 4);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src + c * 8), "r"(nbytes) : "memory");
+  }
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(416, 1)
+slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SlcParams p) {
+  using SM = SlcFwdSmem<DK, DV>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sQ = smem + SM::oQ;
+  SlcFwdBarriers* bar = reinterpret_cast<SlcFwdBarriers*>(smem + SM::oBar);
+  volatile int* abort = &bar->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bg = blockIdx.y, b = bg / p.G, g = bg % p.G;
+  const int* off = p.csr_off + (int64_t)bg * (p.nblk + 1);
+  const int* ent = p.csr_t + (int64_t)bg * p.Tq * p.nslots;
+  const int e0 = blockIdx.x * kEntriesPerCta;
+  const int qpc = 128 / p.hpg;
+  const bool has_work = e0 < off[p.nblk];
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->kv_full[i], 1);
+      mbar_init(&bar->kv_empty[i], 1);
+      mbar_init(&bar->q_full[i], 128);
+      mbar_init(&bar->q_empty[i], 1);
+      mbar_init(&bar->s_full[i], 1);
+      mbar_init(&bar->p_full[i], 128);
+      mbar_init(&bar->o_full[i], 1);
+      mbar_init(&bar->o_read[i], 128);
+    }
+    bar->abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 8) tmem_alloc(&bar->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (!has_work) {
+    // nothing to do for this CTA
+  } else if (warp >= 9) {
+    // ------------------------------------------------------------ producers (4 warps): K/V by TMA, Q rows by cp.async
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    const int prow = (warp - 9) * 32 + lane;
+    bool ok = true;
+    int c = 0, kvidx = -1, last_blk = -1;
+    int pending_stage = -1;
+    for (; !w.done() && ok; w.next(), ++c) {
+      if (w.blk != last_blk) {
+        // hand over the chunk still in flight first: the K/V slot is only released after that chunk was consumed
+        if (pending_stage >= 0) {
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          fence_proxy_async();
+          mbar_arrive(&bar->q_full[pending_stage]);
+          pending_stage = -1;
+        }
+        last_blk = w.blk;
+        ++kvidx;
+        if (prow == 0) {
+          const int ks = kvidx & 1;
+          ok = mbar_wait(&bar->kv_empty[ks], ((kvidx >> 1) & 1) ^ 1, abort);
+          if (ok) {
+            mbar_arrive_expect_tx(&bar->kv_full[ks], SM::kK + SM::kV);
+            tma_load_2d(&tmK, &bar->kv_full[ks], sK + ks * SM::kK, w.blk * 64, (b * p.G + g) * DK);
+            for (int cc = 0; cc < DV / 64; ++cc)
+              tma_load_2d(&tmV, &bar->kv_full[ks], sV + ks * SM::kV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
+          }
+        }
+        if (!ok) break;
+      }
+      const int s = c & 1;
+      ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
+      if (!ok) break;
+      gather_row<DK>(p.q, sQ + s * SM::kQ, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (pending_stage >= 0) {
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        fence_proxy_async();
+        mbar_arrive(&bar->q_full[pending_stage]);
+      }
+      pending_stage = s;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (pending_stage >= 0 && ok) {
+      fence_proxy_async();
+      mbar_arrive(&bar->q_full[pending_stage]);
+    }
+    if (!ok && prow == 0 && kvidx >= 0) mbar_wait(&bar->kv_full[kvidx & 1], (kvidx >> 1) & 1, abort);
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);   // Q rows (K-major) x K block (MN-major: keys contiguous)
+      constexpr uint32_t idO = idesc_bf16(128, DV, 0, 1);   // P (TMEM) x V block (MN-major: dv contiguous)
+      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+      bool ok = true;
+      int c = 0, kvidx = -1, last_blk = -1, prev_ks = -1;
+      auto issue_s = [&](int cc, int ks) -> bool {
+        const int s = cc & 1, buf = cc & 1;
+        if (!mbar_wait(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
+        if (!mbar_wait(&bar->o_read[buf], ((cc >> 1) & 1) ^ 1, abort)) return false;
+        tc_fence_after();
+        const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * SM::kQ), 16, 1024);
+        const uint64_t dK = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);  // one 64-key MN block: LBO unused
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + buf * 192, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dK, kk * 2048), idS, kk > 0);
+        umma_commit(&bar->s_full[buf]);
+        umma_commit(&bar->q_empty[s]);
+        return true;
+      };
+      // the block (and K/V slot) of every chunk is needed twice: when S is issued and when PV is issued
+      int ks_of[2] = {0, 0};
+      bool last_of_block[2] = {false, false};
+      // prologue: S(0)
+      if (!w.done()) {
+        last_blk = w.blk;
+        kvidx = 0;
+        ok = mbar_wait(&bar->kv_full[0], 0, abort);
+        ks_of[0] = 0;
+        if (ok) ok = issue_s(0, 0);
+      }
+      while (ok && !w.done()) {
+        const int cur = c;
+        w.next();
+        // look ahead: S(c+1) before PV(c)
+        if (!w.done()) {
+          int ks = kvidx & 1;
+          if (w.blk != last_blk) {
+            last_blk = w.blk;
+            ++kvidx;
+            ks = kvidx & 1;
+            ok = mbar_wait(&bar->kv_full[ks], (kvidx >> 1) & 1, abort);
+            if (!ok) break;
+            last_of_block[cur & 1] = true;
+          } else {
+            last_of_block[cur & 1] = false;
+          }
+          ks_of[(cur + 1) & 1] = ks;
+          ok = issue_s(cur + 1, ks);
+          if (!ok) break;
+        } else {
+          last_of_block[cur & 1] = true;
+        }
+        const int buf = cur & 1, ks = ks_of[cur & 1];
+        ok = mbar_wait(&bar->p_full[buf], (cur >> 1) & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t dV = smem_desc_sw128(smem_u32(sV + ks * SM::kV), 8192, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ts(tmem + buf * 192 + 64, tmem + buf * 192 + kk * 8, desc_advance(dV, kk * 2048), idO, kk > 0);
+        umma_commit(&bar->o_full[buf]);
+        if (last_of_block[cur & 1]) umma_commit(&bar->kv_empty[ks]);
+        ++c;
+      }
+      (void)prev_ks;
+    }
+  } else {
+    // ------------------------------------------------------------ softmax + partial epilogue (two groups alternate chunks)
+    const int grp = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const int qi = r / p.hpg, hh = r % p.hpg;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    bool ok = true;
+    int c = 0;
+    for (; !w.done() && ok; w.next(), ++c) {
+      if ((c & 1) != grp) continue;
+      const int buf = grp, it = c >> 1;
+      const bool valid = qi < w.count();
+      const int entry = valid ? ent[w.e + qi] : 0;
+      const int t = entry & 0xFFFFFF, slot = entry >> 24;
+      const int key0 = w.blk * 64;
+      ok = mbar_wait(&bar->s_full[buf], it & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[2][32];
+      tmem_ld32(tmem + lane_base + buf * 192, sv[0]);
+      tmem_ld32(tmem + lane_base + buf * 192 + 32, sv[1]);
+      tc_wait_ld();
+      const int chi = valid ? t - key0 : 63;  // causal: keys key0 + c <= t
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float x = (cc * 32 + e <= chi) ? __uint_as_float(sv[cc][e]) * p.scale_log2 : -CUDART_INF_F;
+          sv[cc][e] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+      float l = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int cc = e >> 4, ee = (e & 15) * 2;
+        const float p0 = exp2f(__uint_as_float(sv[cc][ee]) - mx), p1 = exp2f(__uint_as_float(sv[cc][ee + 1]) - mx);
+        l += p0 + p1;
+        __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);
+        pk[e] = *reinterpret_cast<uint32_t*>(&v2);
+      }
+      tmem_st32(tmem + lane_base + buf * 192, pk);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->p_full[buf]);
+      ok = mbar_wait(&bar->o_full[buf], it & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      const float inv = 1.f / l;
+      const int64_t prow = (((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh;
+      __nv_bfloat16* dst = p.o_part + prow * DV;
+#pragma unroll
+      for (int cc = 0; cc < DV / 32; ++cc) {
+        uint32_t ov[32];
+        tmem_ld32(tmem + lane_base + buf * 192 + 64 + cc * 32, ov);
+        tc_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 wv;
+            __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[e]) * inv, __uint_as_float(ov[e + 1]) * inv);
+            __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2]) * inv, __uint_as_float(ov[e + 3]) * inv);
+            __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 4]) * inv, __uint_as_float(ov[e + 5]) * inv);
+            __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[e + 6]) * inv, __uint_as_float(ov[e + 7]) * inv);
+            wv.x = *reinterpret_cast<uint32_t*>(&a0); wv.y = *reinterpret_cast<uint32_t*>(&a1);
+            wv.z = *reinterpret_cast<uint32_t*>(&a2); wv.w = *reinterpret_cast<uint32_t*>(&a3);
+            *reinterpret_cast<uint4*>(dst + cc * 32 + e) = wv;
+          }
+        }
+      }
+      if (valid) p.st_part[prow] = make_float2(mx, l);
+      tc_fence_before();
+      mbar_arrive(&bar->o_read[buf]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// merge the partials of a query in slot order: one warp per (b,h,t); lane s first fetches slot s
+template <int DV>
+__global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part, const float2* __restrict__ st_part,
+                                       const int* __restrict__ indices, int64_t s0, int64_t s1, int64_t s2, int64_t s3,
+                                       __nv_bfloat16* __restrict__ out, float* __restrict__ L, float* __restrict__ M, int B,
+                                       int H, int G, int Tq, int Tk, int nslots, int lprime) {
+  static_assert(DV % 64 == 0, "lanes own 2 or 4 consecutive output columns");
+  constexpr int VPL = DV / 32;  // values per lane
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)B * H * Tq) return;
+  const int t = row % Tq, h = (row / Tq) % H, b = row / ((int64_t)Tq * H);
+  const int hpg = H / G, g = h / hpg, hh = h % hpg;
+  const int* irow = indices + b * s0 + g * s1 + (int64_t)t * s2;
+  const int64_t base = (((int64_t)(b * G + g) * Tq + t) * nslots) * hpg + hh;
+  float2 st = make_float2(-CUDART_INF_F, 0.f);
+  const bool mine = lane < nslots && slot_block(irow, s3, lane, t, Tk, lprime, 1) >= 0;
+  if (mine) st = st_part[base + (int64_t)lane * hpg];
+  const unsigned validmask = __ballot_sync(0xffffffffu, mine);
+  const float mx = warp_max(st.x);
+  const float wmine = mine ? st.y * exp2f(st.x - mx) : 0.f;
+  float lsum = 0.f, acc[VPL];
+#pragma unroll
+  for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
+  for (int s = 0; s < nslots; ++s) {
+    const float wgt = __shfl_sync(0xffffffffu, wmine, s);
+    if (!((validmask >> s) & 1)) continue;
+    lsum += wgt;
+    const __nv_bfloat16* src = o_part + (base + (int64_t)s * hpg) * DV + lane * VPL;
+    if (VPL == 4) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(src);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      const float2 c2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      acc[0] = fmaf(wgt, a.x, acc[0]); acc[1] = fmaf(wgt, a.y, acc[1]);
+      acc[2 % VPL] = fmaf(wgt, c2.x, acc[2 % VPL]); acc[3 % VPL] = fmaf(wgt, c2.y, acc[3 % VPL]);
+    } else {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src));
+      acc[0] = fmaf(wgt, a.x, acc[0]); acc[1] = fmaf(wgt, a.y, acc[1]);
+    }
+  }
+  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+  __nv_bfloat16* dst = out + row * DV + lane * VPL;
+#pragma unroll
+  for (int c = 0; c < VPL; c += 2)
+    *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+  if (lane == 0) {
+    L[row] = lsum > 0.f ? logf(lsum) : -CUDART_INF_F;
+    M[row] = lsum > 0.f ? mx * kLn2f : -CUDART_INF_F;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward, part 1: dQ partials.  Per chunk: S = Q K^T, dP = dO V^T, dS = P*(dP - D) -> TMEM (bf16),
+// dQ_part = dS K.  One K/V slot (a block change drains the pipe), two S/dP buffers, one dQ buffer.
+// ------------------------------------------------------------------------------------------------
+template <int DK, int DV>
+struct SlcDqSmem {
+  static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2, kdO = 128 * DV * 2;
+  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, kStage = kQ + kdO, oBar = oSt + 2 * kStage;
+  static constexpr int kDynamic = oBar + 256 + 1024;
+};
+struct SlcDqBarriers {
+  uint64_t kv_full, kv_empty, q_full[2], q_empty[2], sdp_full[2], ds_full[2], dq_full[2], dq_read[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(416, 1)
+slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SlcParams p) {
+  using SM = SlcDqSmem<DK, DV>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sSt = smem + SM::oSt;
+  SlcDqBarriers* bar = reinterpret_cast<SlcDqBarriers*>(smem + SM::oBar);
+  volatile int* abort = &bar->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bg = blockIdx.y, b = bg / p.G, g = bg % p.G;
+  const int* off = p.csr_off + (int64_t)bg * (p.nblk + 1);
+  const int* ent = p.csr_t + (int64_t)bg * p.Tq * p.nslots;
+  const int e0 = blockIdx.x * kEntriesPerCta;
+  const int qpc = 128 / p.hpg;
+  const bool has_work = e0 < off[p.nblk];
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->kv_full, 1);
+    mbar_init(&bar->kv_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->q_full[i], 128);
+      mbar_init(&bar->q_empty[i], 1);
+      mbar_init(&bar->sdp_full[i], 1);
+      mbar_init(&bar->ds_full[i], 128);
+      mbar_init(&bar->dq_full[i], 1);   // per compute group: a group only ever sees its own chunks' phases
+      mbar_init(&bar->dq_read[i], 128);
+    }
+    bar->abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 8) tmem_alloc(&bar->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  constexpr uint32_t cdQ = 256;
+
+  if (!has_work) {
+  } else if (warp >= 9) {
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    const int prow = (warp - 9) * 32 + lane;
+    bool ok = true;
+    int c = 0, kvidx = -1, last_blk = -1, pending_stage = -1;
+    for (; !w.done() && ok; w.next(), ++c) {
+      if (w.blk != last_blk) {
+        // hand over the chunk still in flight first: the K/V slot is only released after that chunk was consumed
+        if (pending_stage >= 0) {
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          fence_proxy_async();
+          mbar_arrive(&bar->q_full[pending_stage]);
+          pending_stage = -1;
+        }
+        last_blk = w.blk;
+        ++kvidx;
+        if (prow == 0) {
+          ok = mbar_wait(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
+          if (ok) {
+            mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
+            tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
+            for (int cc = 0; cc < DV / 64; ++cc)
+              tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
+          }
+        }
+        if (!ok) break;
+      }
+      const int s = c & 1;
+      ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
+      if (!ok) break;
+      gather_row<DK>(p.q, sSt + s * SM::kStage, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
+      gather_row<DV>(p.dout, sSt + s * SM::kStage + SM::kQ, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (pending_stage >= 0) {
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        fence_proxy_async();
+        mbar_arrive(&bar->q_full[pending_stage]);
+      }
+      pending_stage = s;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (pending_stage >= 0 && ok) {
+      fence_proxy_async();
+      mbar_arrive(&bar->q_full[pending_stage]);
+    }
+    if (!ok && prow == 0 && kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
+  } else if (warp == 8) {
+    if (lane == 0) {
+      constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);    // Q rows x K block (keys contiguous)
+      constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);   // dO rows x V block read K-major (dv contiguous)
+      constexpr uint32_t iddQ = idesc_bf16(128, DK, 0, 0);   // dS (TMEM) x K block read K-major (keys = K dim)
+      const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024), dKk = dKmn;
+      const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
+      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+      bool ok = true;
+      int c = 0, kvidx = 0, last_blk = w.blk;
+      auto issue_sdp = [&](int cc) -> bool {
+        const int s = cc & 1;
+        if (!mbar_wait(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
+        tc_fence_after();
+        const uint64_t dQ = smem_desc_sw128(smem_u32(sSt + s * SM::kStage), 16, 1024);
+        const uint64_t ddO = smem_desc_sw128(smem_u32(sSt + s * SM::kStage + SM::kQ), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < DV / 16; ++kk)
+          umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * 16384 + (kk & 3) * 32),
+                  desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP, kk > 0);
+        umma_commit(&bar->sdp_full[s]);
+        umma_commit(&bar->q_empty[s]);
+        return true;
+      };
+      ok = mbar_wait(&bar->kv_full, 0, abort) && issue_sdp(0);
+      while (ok && !w.done()) {
+        const int cur = c;
+        w.next();
+        const bool more = !w.done();
+        const bool same_blk = more && w.blk == last_blk;
+        if (same_blk) ok = issue_sdp(cur + 1);  // look ahead while this chunk's dS is being computed
+        if (!ok) break;
+        ok = mbar_wait(&bar->ds_full[cur & 1], (cur >> 1) & 1, abort);
+        // the single dQ accumulator must have been drained by the epilogue of the previous chunk (other group)
+        if (ok && cur > 0) ok = mbar_wait(&bar->dq_read[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ts(tmem + cdQ, tmem + (cur & 1) * 128 + kk * 8, desc_advance(dKk, kk * 32), iddQ, kk > 0);
+        umma_commit(&bar->dq_full[cur & 1]);
+        if (more && !same_blk) {
+          // the single K/V slot is reloaded: everything issued so far must have finished with it
+          umma_commit(&bar->kv_empty);
+          last_blk = w.blk;
+          ++kvidx;
+          ok = mbar_wait(&bar->kv_full, kvidx & 1, abort) && issue_sdp(cur + 1);
+        }
+        ++c;
+      }
+    }
+  } else {
+    const int grp = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const int qi = r / p.hpg, hh = r % p.hpg;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    bool ok = true;
+    int c = 0;
+    for (; !w.done() && ok; w.next(), ++c) {
+      if ((c & 1) != grp) continue;
+      const int buf = grp, it = c >> 1;
+      const bool valid = qi < w.count();
+      const int entry = valid ? ent[w.e + qi] : 0;
+      const int t = entry & 0xFFFFFF, slot = entry >> 24;
+      const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + t;
+      const float lse2 = valid ? p.lse2[srow] : CUDART_INF_F, Dr = valid ? p.D[srow] : 0.f;
+      const int chi = t - w.blk * 64;
+      ok = mbar_wait(&bar->sdp_full[buf], it & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t pk[32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sv[32], dp[32];
+        tmem_ld32(tmem + lane_base + buf * 128 + cc * 32, sv);
+        tmem_ld32(tmem + lane_base + buf * 128 + 64 + cc * 32, dp);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int c0 = cc * 32 + 2 * e;
+          const float p0 = c0 <= chi ? exp2f(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse2)) : 0.f;
+          const float p1 = c0 + 1 <= chi ? exp2f(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse2)) : 0.f;
+          __nv_bfloat162 x = __floats2bfloat162_rn(p0 * (__uint_as_float(dp[2 * e]) - Dr), p1 * (__uint_as_float(dp[2 * e + 1]) - Dr));
+          pk[cc * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
+        }
+      }
+      tmem_st32(tmem + lane_base + buf * 128, pk);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->ds_full[buf]);
+      ok = mbar_wait(&bar->dq_full[buf], it & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t prow = (((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh;
+      __nv_bfloat16* dst = p.dq_part + prow * DK;
+#pragma unroll
+      for (int cc = 0; cc < DK / 32; ++cc) {
+        uint32_t ov[32];
+        tmem_ld32(tmem + lane_base + cdQ + cc * 32, ov);
+        tc_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 wv;
+            __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[e]), __uint_as_float(ov[e + 1]));
+            __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2]), __uint_as_float(ov[e + 3]));
+            __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 4]), __uint_as_float(ov[e + 5]));
+            __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[e + 6]), __uint_as_float(ov[e + 7]));
+            wv.x = *reinterpret_cast<uint32_t*>(&a0); wv.y = *reinterpret_cast<uint32_t*>(&a1);
+            wv.z = *reinterpret_cast<uint32_t*>(&a2); wv.w = *reinterpret_cast<uint32_t*>(&a3);
+            *reinterpret_cast<uint4*>(dst + cc * 32 + e) = wv;
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bar->dq_read[buf]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// dQ[b,h,t,:] = scale * sum of the valid slots' partials, slot order: one warp per row
+template <int DK>
+__global__ void slc_combine_dq_kernel(const __nv_bfloat16* __restrict__ dq_part, const int* __restrict__ indices, int64_t s0,
+                                      int64_t s1, int64_t s2, int64_t s3, __nv_bfloat16* __restrict__ dq, int B, int H, int G,
+                                      int Tq, int Tk, int nslots, int lprime, float scale) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)B * H * Tq) return;
+  const int t = row % Tq, h = (row / Tq) % H, b = row / ((int64_t)Tq * H);
+  const int hpg = H / G, g = h / hpg, hh = h % hpg;
+  const int* irow = indices + b * s0 + g * s1 + (int64_t)t * s2;
+  const int64_t base = (((int64_t)(b * G + g) * Tq + t) * nslots) * hpg + hh;
+  const bool mine = lane < nslots && slot_block(irow, s3, lane, t, Tk, lprime, 1) >= 0;
+  const unsigned validmask = __ballot_sync(0xffffffffu, mine);
+  float acc[DK / 32];
+#pragma unroll
+  for (int c = 0; c < DK / 32; ++c) acc[c] = 0.f;
+  for (int s = 0; s < nslots; ++s) {
+    if (!((validmask >> s) & 1)) continue;
+    const __nv_bfloat16* src = dq_part + (base + (int64_t)s * hpg) * DK;
+#pragma unroll
+    for (int c = 0; c < DK / 64; ++c) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + c * 64 + lane * 2));
+      acc[2 * c] += a.x;
+      acc[2 * c + 1] += a.y;
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < DK / 64; ++c)
+    *reinterpret_cast<__nv_bfloat162*>(dq + row * DK + c * 64 + lane * 2) = __floats2bfloat162_rn(acc[2 * c] * scale, acc[2 * c + 1] * scale);
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward, part 2: dK/dV of each block, transposed tiles with the 64 keys on the M axis.  Per half
+// chunk (64 rows): S^T = K Q^T, dP^T = V dO^T, P^T and dS^T -> TMEM (bf16), dV += P^T dO, dK += dS^T Q.
+// The accumulators live in TMEM for as long as the CTA stays on a block and are then written as one
+// fp32 partial; slc_reduce_dkv adds the partials of a block in a fixed order.
+// ------------------------------------------------------------------------------------------------
+template <int DK, int DV>
+struct SlcDkvSmem {
+  static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2, kdO = 128 * DV * 2;
+  static constexpr int kStage = kQ + kdO + 2048;  // + lse2[128], D[128], t[128]
+  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, oBar = oSt + 2 * kStage;
+  static constexpr int kDynamic = oBar + 256 + 1024;
+};
+struct SlcDkvBarriers {
+  uint64_t kv_full, kv_empty, q_full[2], q_empty[2], stp_full, pds_full, acc_full, acc_read;
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(288, 1)
+slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SlcParams p) {
+  using SM = SlcDkvSmem<DK, DV>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sSt = smem + SM::oSt;
+  SlcDkvBarriers* bar = reinterpret_cast<SlcDkvBarriers*>(smem + SM::oBar);
+  volatile int* abort = &bar->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bg = blockIdx.y, b = bg / p.G, g = bg % p.G;
+  const int* off = p.csr_off + (int64_t)bg * (p.nblk + 1);
+  const int* ent = p.csr_t + (int64_t)bg * p.Tq * p.nslots;
+  const int e0 = blockIdx.x * kEntriesPerCta;
+  const int qpc = 128 / p.hpg;
+  const bool has_work = e0 < off[p.nblk];
+  const int nseg = gridDim.x + p.nblk;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->kv_full, 1);
+    mbar_init(&bar->kv_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->q_full[i], 128);
+      mbar_init(&bar->q_empty[i], 1);
+    }
+    mbar_init(&bar->stp_full, 1);
+    mbar_init(&bar->pds_full, 128);
+    mbar_init(&bar->acc_full, 1);
+    mbar_init(&bar->acc_read, 128);
+    bar->abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 4) tmem_alloc(&bar->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  constexpr uint32_t cdK = 0, cdV = DK, cST = DK + DV, cdPT = DK + DV + 64;
+
+  if (!has_work) {
+  } else if (warp >= 5) {
+    // producers (4 warps): one gathered row of Q and dO per thread, plus that row's statistics
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    const int prow = (warp - 5) * 32 + lane;
+    const int qi = prow / p.hpg, hh = prow % p.hpg;
+    bool ok = true;
+    int c = 0, kvidx = -1, last_blk = -1, pending_stage = -1;
+    for (; !w.done() && ok; w.next(), ++c) {
+      if (w.blk != last_blk) {
+        // hand over the chunk still in flight first: the K/V slot is only released after that chunk was consumed
+        if (pending_stage >= 0) {
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          fence_proxy_async();
+          mbar_arrive(&bar->q_full[pending_stage]);
+          pending_stage = -1;
+        }
+        last_blk = w.blk;
+        ++kvidx;
+        if (prow == 0) {
+          ok = mbar_wait(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
+          if (ok) {
+            mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
+            tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
+            for (int cc = 0; cc < DV / 64; ++cc)
+              tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
+          }
+        }
+        if (!ok) break;
+      }
+      const int s = c & 1;
+      ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
+      if (!ok) break;
+      uint8_t* st = sSt + s * SM::kStage;
+      gather_row<DK>(p.q, st, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
+      gather_row<DV>(p.dout, st + SM::kQ, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      {
+        float* stat = reinterpret_cast<float*>(st + SM::kQ + SM::kdO);
+        const bool valid = qi < w.count();
+        const int t = valid ? (ent[w.e + qi] & 0xFFFFFF) : -1;
+        const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + max(t, 0);
+        stat[prow] = valid ? p.lse2[srow] : CUDART_INF_F;
+        stat[128 + prow] = valid ? p.D[srow] : 0.f;
+        reinterpret_cast<int*>(stat)[256 + prow] = t;  // -1: row not in use
+      }
+      if (pending_stage >= 0) {
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        fence_proxy_async();
+        mbar_arrive(&bar->q_full[pending_stage]);
+      }
+      pending_stage = s;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (pending_stage >= 0 && ok) {
+      fence_proxy_async();
+      mbar_arrive(&bar->q_full[pending_stage]);
+    }
+    if (!ok && prow == 0 && kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
+  } else if (warp == 4) {
+    if (lane == 0) {
+      constexpr uint32_t idST = idesc_bf16(64, 64, 1, 0);    // K block as A (keys contiguous) x Q rows (K-major)
+      constexpr uint32_t iddPT = idesc_bf16(64, 64, 0, 0);   // V block as A (K-major) x dO rows (K-major)
+      constexpr uint32_t iddV = idesc_bf16(64, DV, 0, 1);    // P^T (TMEM) x dO rows (dv contiguous)
+      constexpr uint32_t iddK = idesc_bf16(64, DK, 0, 1);    // dS^T (TMEM) x Q rows (dk contiguous)
+      const uint64_t dKa = smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t dVa = smem_desc_sw128(smem_u32(sV), 16, 1024);
+      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+      bool ok = true;
+      int c = 0, kvidx = -1, last_blk = -1, seg = 0, half_idx = 0;
+      bool fresh = true;  // next accumulation MMA starts a new segment
+      for (; !w.done() && ok; w.next(), ++c) {
+        if (w.blk != last_blk) {
+          if (last_blk >= 0) {
+            // finish the segment of the previous block: hand the accumulators over, wait until they are read
+            umma_commit(&bar->acc_full);
+            umma_commit(&bar->kv_empty);
+            ok = mbar_wait(&bar->acc_read, seg & 1, abort);
+            if (!ok) break;
+            ++seg;
+            fresh = true;
+          }
+          last_blk = w.blk;
+          ++kvidx;
+          ok = mbar_wait(&bar->kv_full, kvidx & 1, abort);
+          if (!ok) break;
+        }
+        const int s = c & 1;
+        ok = mbar_wait(&bar->q_full[s], (c >> 1) & 1, abort);
+        if (!ok) break;
+        const uint32_t st = smem_u32(sSt + s * SM::kStage);
+        for (int hf = 0; hf < 2 && ok; ++hf, ++half_idx) {
+          const uint64_t dQk = smem_desc_sw128(st + hf * 8192, 16, 1024), dQmn = smem_desc_sw128(st + hf * 8192, 16384, 1024);
+          const uint64_t dOk = smem_desc_sw128(st + SM::kQ + hf * 8192, 16, 1024), dOmn = smem_desc_sw128(st + SM::kQ + hf * 8192, 16384, 1024);
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < DK / 16; ++kk)
+            umma_ss(tmem + cST, desc_advance(dKa, kk * 2048), desc_advance(dQk, (kk >> 2) * 16384 + (kk & 3) * 32), idST, kk > 0);
+#pragma unroll
+          for (int kk = 0; kk < DV / 16; ++kk)
+            umma_ss(tmem + cdPT, desc_advance(dVa, (kk >> 2) * 8192 + (kk & 3) * 32),
+                    desc_advance(dOk, (kk >> 2) * 16384 + (kk & 3) * 32), iddPT, kk > 0);
+          umma_commit(&bar->stp_full);
+          ok = mbar_wait(&bar->pds_full, half_idx & 1, abort);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ts(tmem + cdV, tmem + cST + kk * 8, desc_advance(dOmn, kk * 2048), iddV, !(fresh && kk == 0));
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ts(tmem + cdK, tmem + cdPT + kk * 8, desc_advance(dQmn, kk * 2048), iddK, !(fresh && kk == 0));
+          fresh = false;
+        }
+        if (ok) umma_commit(&bar->q_empty[s]);
+      }
+      if (ok && last_blk >= 0) umma_commit(&bar->acc_full);
+    }
+  } else {
+    // compute: warp w owns key rows 16w .. 16w+15 in its first 16 lanes (M = 64 accumulator layout)
+    const int kr = warp * 16 + (lane & 15);
+    const bool rowlane = lane < 16;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    bool ok = true;
+    int c = 0, last_blk = -1, seg = 0, half_idx = 0;
+    auto flush = [&](int blk) -> bool {
+      if (!mbar_wait(&bar->acc_full, seg & 1, abort)) return false;
+      tc_fence_after();
+      const int64_t sidx = ((int64_t)bg * nseg + blockIdx.x + blk) * 64 + kr;
+      for (int cc = 0; cc < (DK + DV) / 32; ++cc) {
+        uint32_t ov[32];
+        tmem_ld32(tmem + lane_base + cc * 32, ov);
+        tc_wait_ld();
+        if (rowlane) {
+          float* dst = cc < DK / 32 ? p.dk_part + sidx * DK + cc * 32 : p.dv_part + sidx * DV + (cc - DK / 32) * 32;
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            *reinterpret_cast<float4*>(dst + e) = make_float4(__uint_as_float(ov[e]), __uint_as_float(ov[e + 1]),
+                                                              __uint_as_float(ov[e + 2]), __uint_as_float(ov[e + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bar->acc_read);
+      ++seg;
+      return true;
+    };
+    for (; !w.done() && ok; w.next(), ++c) {
+      if (w.blk != last_blk) {
+        if (last_blk >= 0) ok = flush(last_blk);
+        if (!ok) break;
+        last_blk = w.blk;
+      }
+      const int s = c & 1;
+      ok = mbar_wait(&bar->q_full[s], (c >> 1) & 1, abort);
+      if (!ok) break;
+      const float* stat = reinterpret_cast<const float*>(sSt + s * SM::kStage + SM::kQ + SM::kdO);
+      const int* tcol = reinterpret_cast<const int*>(stat) + 256;
+      const int key = w.blk * 64 + kr;
+      for (int hf = 0; hf < 2 && ok; ++hf, ++half_idx) {
+        ok = mbar_wait(&bar->stp_full, half_idx & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t sT[32], dpT[32], pk[16], dk_[16];
+          tmem_ld32(tmem + lane_base + cST + cc * 32, sT);
+          tmem_ld32(tmem + lane_base + cdPT + cc * 32, dpT);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int j0 = hf * 64 + cc * 32 + 2 * e;  // row of the gathered tile = column here
+            const float l0 = stat[j0], l1 = stat[j0 + 1], D0 = stat[128 + j0], D1 = stat[128 + j0 + 1];
+            const int t0 = tcol[j0], t1 = tcol[j0 + 1];
+            const float p0 = key <= t0 ? exp2f(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0)) : 0.f;
+            const float p1 = key <= t1 ? exp2f(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1)) : 0.f;
+            __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1);
+            __nv_bfloat162 y = __floats2bfloat162_rn(p0 * (__uint_as_float(dpT[2 * e]) - D0), p1 * (__uint_as_float(dpT[2 * e + 1]) - D1));
+            pk[e] = *reinterpret_cast<uint32_t*>(&x);
+            dk_[e] = *reinterpret_cast<uint32_t*>(&y);
+          }
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::
+                       "r"(tmem + lane_base + cST + cc * 16), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
+                       "r"(pk[6]), "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]),
+                       "r"(pk[15]) : "memory");
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::
+                       "r"(tmem + lane_base + cdPT + cc * 16), "r"(dk_[0]), "r"(dk_[1]), "r"(dk_[2]), "r"(dk_[3]), "r"(dk_[4]),
+                       "r"(dk_[5]), "r"(dk_[6]), "r"(dk_[7]), "r"(dk_[8]), "r"(dk_[9]), "r"(dk_[10]), "r"(dk_[11]), "r"(dk_[12]),
+                       "r"(dk_[13]), "r"(dk_[14]), "r"(dk_[15]) : "memory");
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bar->pds_full);
+      }
+    }
+    if (ok && last_blk >= 0) flush(last_blk);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// dK/dV of block `blk` += sum of its segment partials in segment order
+__global__ void slc_reduce_dkv_kernel(const float* __restrict__ dk_part, const float* __restrict__ dv_part,
+                                      const int* __restrict__ csr_off, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
+                                      int G, int Tk, int nblk, int nparts, int DK, int DV, float scale) {
+  const int blk = blockIdx.x, bg = blockIdx.y;
+  const int* off = csr_off + (int64_t)bg * (nblk + 1);
+  const int lo = off[blk], hi = off[blk + 1];
+  if (hi <= lo) return;
+  const int p_lo = lo / kEntriesPerCta, p_hi = (hi - 1) / kEntriesPerCta;
+  const int nseg = nparts + nblk;
+  const int W = DK + DV;
+  for (int i = threadIdx.x; i < 64 * W; i += blockDim.x) {
+    const int r = i / W, c = i % W;
+    float acc = 0.f;
+    for (int pp = p_lo; pp <= p_hi; ++pp) {
+      const int64_t sidx = ((int64_t)bg * nseg + pp + blk) * 64 + r;
+      acc += c < DK ? dk_part[sidx * DK + c] : dv_part[sidx * DV + (c - DK)];
+    }
+    const int64_t krow = (int64_t)bg * Tk + blk * 64 + r;
+    __nv_bfloat16* dst = c < DK ? dk + krow * DK + c : dv + krow * DV + (c - DK);
+    *dst = __float2bfloat16_rn(__bfloat162float(*dst) + (c < DK ? acc * scale : acc));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+static size_t al256(size_t x) { return (x + 255) & ~size_t(255); }
+
+bool slc_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime) {
+  const bool dims = (dk == 192 && dv == 128) || (dk == 128 && dv == 128) || (dk == 64 && dv == 64);
+  if (!dims || G <= 0 || H % G != 0) return false;
+  const int hpg = H / G;
+  return hpg <= 128 && 128 % hpg == 0 && lprime == 64 && Tk % 64 == 0 && Tk > 0 && Tq > 0 && Tq < (1 << 24) &&
+         nslots > 0 && nslots <= 32;
+}
+
+size_t slc_fwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime) {
+  const size_t rows = (size_t)B * H * Tq * nslots;
+  return al256(slc_csr_workspace_bytes(B, G, Tq, Tk, nslots, lprime)) + al256(rows * dv * 2) + al256(rows * sizeof(float2));
+}
+
+template <int DK, int DV>
+static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const SlcParams& p, const int* indices,
+                            const int64_t* sidx, __nv_bfloat16* out, float* L, float* M, cudaStream_t st) {
+  using SM = SlcFwdSmem<DK, DV>;
+  auto kern = slc_fwd_kernel<DK, DV>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kDynamic) != cudaSuccess)
+    return fail(NSA_ERR_LAUNCH, "slc_fwd: cannot reserve shared memory");
+  const int nparts = (int)(((int64_t)p.Tq * p.nslots + kEntriesPerCta - 1) / kEntriesPerCta);
+  {
+    KernelTimer kt("slc_fwd", st);
+    kern<<<dim3(nparts, p.B * p.G), 416, SM::kDynamic, st>>>(tk, tv, p);
+  }
+  if (int rc = check_launch("slc_fwd_sm100")) return rc;
+  const int64_t rows = (int64_t)p.B * p.H * p.Tq;
+  KernelTimer kt("slc_combine_fwd", st);
+  slc_combine_fwd_kernel<DV><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.o_part, p.st_part, indices, sidx[0], sidx[1], sidx[2],
+                                                                         sidx[3], out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64);
+  return check_launch("slc_combine_fwd");
+}
+
+int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, void* out, float* L,
+                  float* M, int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale,
+                  void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!slc_sm100_supported(H, G, Tq, Tk, dk, dv, nslots, lprime)) return fail(NSA_ERR_UNSUPPORTED, "slc_fwd_sm100: unsupported shape");
+  const size_t need = slc_fwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, nslots, lprime);
+  if (!workspace || workspace_bytes < need)
+    return fail(NSA_ERR_WORKSPACE, "selection forward needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  SlcParams p = {};
+  char* w = (char*)workspace;
+  const size_t csr_bytes = al256(slc_csr_workspace_bytes(B, G, Tq, Tk, nslots, lprime));
+  if (int rc = build_slc_csr(indices, sidx, B, G, Tq, Tk, nslots, lprime, 1, w, csr_bytes, &p.csr_off, &p.csr_t, st)) return rc;
+  const size_t rows = (size_t)B * H * Tq * nslots;
+  p.o_part = (__nv_bfloat16*)(w + csr_bytes);
+  p.st_part = (float2*)(w + csr_bytes + al256(rows * dv * 2));
+  p.q = (const __nv_bfloat16*)q;
+  p.B = B; p.H = H; p.G = G; p.Tq = Tq; p.Tk = Tk; p.nslots = nslots; p.nblk = (Tk + 63) / 64; p.hpg = H / G;
+  p.scale = scale; p.scale_log2 = scale * kLog2ef;
+  p.timeouts = fa_timeout_counter();
+  CUtensorMap tk, tv;
+  if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, 64)) return rc;
+  if (dk == 192 && dv == 128) return launch_slc_fwd_t<192, 128>(tk, tv, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  if (dk == 128 && dv == 128) return launch_slc_fwd_t<128, 128>(tk, tv, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  if (dk == 64 && dv == 64) return launch_slc_fwd_t<64, 64>(tk, tv, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  return fail(NSA_ERR_UNSUPPORTED, "slc_fwd_sm100: unsupported head dims");
+}
+
+// prep kernel shared with the dense backward (defined in fa_bwd_sm100.cu)
+void launch_bwd_prep(const void* o, const void* dout, const float* L, const float* M, float* D, float* lse2, int64_t rows, int dv,
+                     cudaStream_t st);
+
+static void slc_bwd_layout(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, size_t* o_stat,
+                           size_t* o_dq, size_t* o_dk, size_t* o_dv, size_t* total) {
+  const size_t rows = (size_t)B * H * Tq;
+  const size_t nparts = ((size_t)Tq * nslots + kEntriesPerCta - 1) / kEntriesPerCta;
+  const size_t nseg = nparts + (size_t)(Tk + 63) / 64;
+  size_t o = al256(slc_csr_workspace_bytes(B, G, Tq, Tk, nslots, lprime));
+  *o_stat = o; o += 2 * al256(rows * sizeof(float));
+  *o_dq = o;   o += al256(rows * nslots * dk * 2);
+  *o_dk = o;   o += al256((size_t)B * G * nseg * 64 * dk * sizeof(float));
+  *o_dv = o;   o += al256((size_t)B * G * nseg * 64 * dv * sizeof(float));
+  *total = o;
+}
+
+size_t slc_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime) {
+  size_t a, b, c, d, total;
+  slc_bwd_layout(B, H, G, Tq, Tk, dk, dv, nslots, lprime, &a, &b, &c, &d, &total);
+  return total;
+}
+
+template <int DK, int DV>
+static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const SlcParams& p, const int* indices,
+                            const int64_t* sidx, __nv_bfloat16* dq, cudaStream_t st) {
+  auto kq = slc_bwd_dq_kernel<DK, DV>;
+  auto kkv = slc_bwd_dkv_kernel<DK, DV>;
+  if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, SlcDqSmem<DK, DV>::kDynamic) != cudaSuccess ||
+      cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, SlcDkvSmem<DK, DV>::kDynamic) != cudaSuccess)
+    return fail(NSA_ERR_LAUNCH, "slc_bwd: cannot reserve shared memory");
+  const int nparts = (int)(((int64_t)p.Tq * p.nslots + kEntriesPerCta - 1) / kEntriesPerCta);
+  {
+    KernelTimer kt("slc_bwd_dq", st);
+    kq<<<dim3(nparts, p.B * p.G), 416, SlcDqSmem<DK, DV>::kDynamic, st>>>(tk, tv, p);
+  }
+  if (int rc = check_launch("slc_bwd_dq_sm100")) return rc;
+  const int64_t rows = (int64_t)p.B * p.H * p.Tq;
+  {
+    KernelTimer kt("slc_combine_dq", st);
+    slc_combine_dq_kernel<DK><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.dq_part, indices, sidx[0], sidx[1], sidx[2], sidx[3], dq,
+                                                                          p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale);
+  }
+  if (int rc = check_launch("slc_combine_dq")) return rc;
+  {
+    KernelTimer kt("slc_bwd_dkv", st);
+    kkv<<<dim3(nparts, p.B * p.G), 288, SlcDkvSmem<DK, DV>::kDynamic, st>>>(tk, tv, p);
+  }
+  if (int rc = check_launch("slc_bwd_dkv_sm100")) return rc;
+  KernelTimer kt("slc_reduce_dkv", st);
+  slc_reduce_dkv_kernel<<<dim3(p.nblk, p.B * p.G), 256, 0, st>>>(p.dk_part, p.dv_part, p.csr_off, p.dk_out, p.dv_out, p.G, p.Tk,
+                                                                 p.nblk, nparts, DK, DV, p.scale);
+  return check_launch("slc_reduce_dkv");
+}
+
+int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, const void* out,
+                  const void* dout, const float* L, const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G,
+                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, void* workspace,
+                  size_t workspace_bytes, cudaStream_t st) {
+  if (!slc_sm100_supported(H, G, Tq, Tk, dk, dv, nslots, lprime)) return fail(NSA_ERR_UNSUPPORTED, "slc_bwd_sm100: unsupported shape");
+  size_t o_stat, o_dq, o_dk, o_dv, need;
+  slc_bwd_layout(B, H, G, Tq, Tk, dk, dv, nslots, lprime, &o_stat, &o_dq, &o_dk, &o_dv, &need);
+  if (!workspace || workspace_bytes < need)
+    return fail(NSA_ERR_WORKSPACE, "selection backward needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  SlcParams p = {};
+  char* w = (char*)workspace;
+  if (int rc = build_slc_csr(indices, sidx, B, G, Tq, Tk, nslots, lprime, 1, w, o_stat, &p.csr_off, &p.csr_t, st)) return rc;
+  const size_t rows = (size_t)B * H * Tq;
+  float* D = (float*)(w + o_stat);
+  float* lse2 = (float*)(w + o_stat + al256(rows * sizeof(float)));
+  launch_bwd_prep(out, dout, L, M, D, lse2, (int64_t)rows, dv, st);
+  if (int rc = check_launch("fa_bwd_prep")) return rc;
+  p.q = (const __nv_bfloat16*)q; p.dout = (const __nv_bfloat16*)dout;
+  p.D = D; p.lse2 = lse2;
+  p.dq_part = (__nv_bfloat16*)(w + o_dq);
+  p.dk_part = (float*)(w + o_dk); p.dv_part = (float*)(w + o_dv);
+  p.dk_out = (__nv_bfloat16*)dk_out; p.dv_out = (__nv_bfloat16*)dv_out;
+  p.B = B; p.H = H; p.G = G; p.Tq = Tq; p.Tk = Tk; p.nslots = nslots; p.nblk = (Tk + 63) / 64; p.hpg = H / G;
+  p.scale = scale; p.scale_log2 = scale * kLog2ef;
+  p.timeouts = fa_timeout_counter();
+  CUtensorMap tk, tv;
+  if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, 64)) return rc;
+  if (dk == 192 && dv == 128) return launch_slc_bwd_t<192, 128>(tk, tv, p, indices, sidx, (__nv_bfloat16*)dq, st);
+  if (dk == 128 && dv == 128) return launch_slc_bwd_t<128, 128>(tk, tv, p, indices, sidx, (__nv_bfloat16*)dq, st);
+  if (dk == 64 && dv == 64) return launch_slc_bwd_t<64, 64>(tk, tv, p, indices, sidx, (__nv_bfloat16*)dq, st);
+  return fail(NSA_ERR_UNSUPPORTED, "slc_bwd_sm100: unsupported head dims");
+}
+
+}  // namespace nsa

@@ -1,0 +1,23 @@
+// Selected-block attention, tensor-core (tcgen05) key-block-major kernels: host entry points.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nsa {
+
+// bf16, canonical contiguous layouts, 64-key selection blocks, heads-per-group dividing 128
+bool slc_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime);
+
+size_t slc_fwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime);
+int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, void* out, float* L,
+                  float* M, int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale,
+                  void* workspace, size_t workspace_bytes, cudaStream_t st);
+
+
+size_t slc_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime);
+int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, const void* out,
+                  const void* dout, const float* L, const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G,
+                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, void* workspace,
+                  size_t workspace_bytes, cudaStream_t st);
+
+}  // namespace nsa

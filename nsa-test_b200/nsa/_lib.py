@@ -33,14 +33,17 @@ PROTOTYPES = {
     "nsa_last_error": (c_char_p, []),
     "nsa_version": (c_char_p, []),
     "nsa_set_kernel_family": (c_int, [c_int]),
+    "nsa_profile_enable": (c_int, [c_int]),
+    "nsa_profile_report": (c_int, [ctypes.c_char_p, c_size_t]),
     "nsa_device_timeouts": (c_int, [c_int]),
     "nsa_sliding_fwd": (c_int, [_P] * 6 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P]),
     "nsa_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 8),
     "nsa_sliding_bwd": (c_int, [_P] * 10 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P, c_size_t, _P]),
     "nsa_cmp_attn_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 7 + [c_float, c_int, c_int, c_int, c_int, _P]),
     "nsa_cmp_attn_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 7 + [c_float, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
-    "nsa_slc_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 9 + [c_float, c_int, _P]),
-    "nsa_slc_bwd_workspace_bytes": (c_size_t, [c_int] * 6),
+    "nsa_slc_fwd_workspace_bytes": (c_size_t, [c_int] * 10),
+    "nsa_slc_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 9 + [c_float, c_int, _P, c_size_t, _P]),
+    "nsa_slc_bwd_workspace_bytes": (c_size_t, [c_int] * 10),
     "nsa_slc_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 9 + [c_float, c_int, _P, c_size_t, _P]),
     "nsa_phi_pool_fwd": (c_int, [_P, _P, _P, _I64P, _P, _P] + [c_int] * 10 + [_P]),
     "nsa_phi_pool_bwd": (c_int, [_P] * 7 + [c_int] * 9 + [_P]),
@@ -101,3 +104,19 @@ def i64(vals):
 
 def stream_ptr(dev: torch.device):
     return c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def profile_kernels(fn):
+    """Run fn() with per-kernel event timing on; returns {kernel family: (launches, total_ms)}."""
+    lib.nsa_profile_enable(1)
+    try:
+        fn()
+        buf = ctypes.create_string_buffer(1 << 16)
+        check(lib.nsa_profile_report(buf, len(buf)), "nsa_profile_report")
+    finally:
+        lib.nsa_profile_enable(0)
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, n, ms = line.split()
+        out[name] = (int(n), float(ms))
+    return out

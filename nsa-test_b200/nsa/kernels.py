@@ -459,8 +459,11 @@ class _Launcher:
                     rc = lib.nsa_cmp_attn_fwd(ptr(Q), ptr(K), ptr(V), ptr(be), ptr(Out), ptr(L), ptr(M), i64(strides), B, H,
                                               G, Tq, Tk, dk, dv, scale, code, 0, 0, 0, st)
                 else:
+                    n, lp = int(a["N_BLOCKS"]), int(a["BLOCK_SIZE_SELECTION"])
+                    nbytes = lib.nsa_slc_fwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, n, lp, code)
+                    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
                     rc = lib.nsa_slc_fwd(ptr(Q), ptr(K), ptr(V), ptr(idx), ptr(Out), ptr(L), ptr(M), i64(strides), B, H, G,
-                                         Tq, Tk, int(a["N_BLOCKS"]), int(a["BLOCK_SIZE_SELECTION"]), dk, dv, scale, code, st)
+                                         Tq, Tk, n, lp, dk, dv, scale, code, ptr(ws), nbytes, st)
             else:
                 dO, dQ, dK, dV = a["dOut"], a["dQ"], a["dK"], a["dV"]
                 if kind == "win":
@@ -477,7 +480,7 @@ class _Launcher:
                 else:
                     n = int(a["N_BLOCKS"])
                     lp = int(a["BLOCK_SIZE_SELECTION"])
-                    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, G, Tq, Tk, n, lp)
+                    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, n, lp, code)
                     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
                     rc = lib.nsa_slc_bwd(ptr(Q), ptr(K), ptr(V), ptr(idx), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ),
                                          ptr(dK), ptr(dV), i64(strides), B, H, G, Tq, Tk, n, lp, dk, dv, scale, code,

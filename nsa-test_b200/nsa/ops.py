@@ -113,9 +113,12 @@ def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float):
     assert indices_i32.dtype == torch.int32
     o, L, M = _stats(q, dv)
     s = _fwd_strides(q, k, v, o, L, M) + list(indices_i32.stride())
+    n = indices_i32.shape[-1]
+    nbytes = lib.nsa_slc_fwd_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n, int(l_prime), dtype_code(q))
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
         check(lib.nsa_slc_fwd(ptr(q), ptr(k), ptr(v), ptr(indices_i32), ptr(o), ptr(L), ptr(M), i64(s), B, H, G, Tq, Tkv,
-                              indices_i32.shape[-1], int(l_prime), dk, dv, float(scale), dtype_code(q), stream_ptr(dev)),
+                              n, int(l_prime), dk, dv, float(scale), dtype_code(q), ptr(ws), nbytes, stream_ptr(dev)),
               "nsa_slc_fwd")
     return o, L, M
 
@@ -131,7 +134,7 @@ def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float):
     dq = torch.empty_like(q)
     dkey = torch.zeros(B, G, Tkv, dk, device=dev, dtype=q.dtype)
     dval = torch.zeros(B, G, Tkv, dv, device=dev, dtype=q.dtype)
-    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, G, Tq, Tkv, n, int(l_prime))
+    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n, int(l_prime), dtype_code(q))
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     s = (_fwd_strides(q, k, v, o, L, M) + list(dq.stride()) + list(dkey.stride()) + list(dval.stride())
          + list(indices_i32.stride()))

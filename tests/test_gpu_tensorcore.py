@@ -178,3 +178,86 @@ def test_backward_tensorcore_vs_generic_at_scale():
     _no_timeouts()
     for a, b_, n in zip(tc, gen, ("dq", "dk", "dv")):
         _grad_close(a, b_.float().cpu(), "compression " + n)
+
+
+def _random_indices(B, G, T, n, lp, gen, with_holes=True):
+    """Per-query block ids like the layer produces (block 0, the local blocks, random earlier blocks),
+    plus -1 slots, repeated ids and ids of future blocks when with_holes."""
+    nblk = (T + lp - 1) // lp
+    idx = torch.randint(0, nblk, (B, G, T, n), generator=gen)
+    t = torch.arange(T)
+    idx = torch.minimum(idx, (t // lp).view(1, 1, T, 1).expand_as(idx) + (1 if with_holes else 0))
+    idx[..., 0] = 0
+    idx[..., 1] = (t // lp).view(1, 1, T)
+    if with_holes:
+        idx[..., -1] = -1
+        idx[:, :, 7::13, 2] = idx[:, :, 7::13, 3]      # repeated ids
+        idx[:, :, 5] = -1                               # an empty row
+    return idx.to(torch.int32)
+
+
+@pytest.mark.parametrize("dk,dv,H,G,T,n", [(64, 64, 8, 2, 512, 6), (192, 128, 16, 1, 1024, 16), (128, 128, 32, 1, 256, 4)])
+def test_selection_forward_tensorcore_vs_oracle(dk, dv, H, G, T, n):
+    from nsa import ops
+    gen = torch.Generator().manual_seed(7)
+    q, k, v, _ = _inputs(2, H, G, T, dk, dv, seed=7)
+    idx = _random_indices(2, G, T, n, 64, gen)
+    scale = dk ** -0.5
+    o, L, M = ops.slc_fwd(q.to(DEV), k.to(DEV), v.to(DEV), idx.to(DEV), 64, scale)
+    torch.cuda.synchronize()
+    _no_timeouts()
+    o_ref, M_ref, L_ref = O.selection_attention(q.float(), k.float(), v.float(), idx.long(), 64, scale, return_stats=True)
+    assert max_abs(o.float(), o_ref) < 2e-2
+    _check_stats(L, M, L_ref, M_ref)
+    assert (o[:, :, 5] == 0).all()
+
+
+def test_selection_forward_tensorcore_vs_generic_at_scale():
+    from nsa import ops
+    B, H, G, T, dk, dv, n = 1, 32, 2, 8192, 192, 128, 16
+    gen = torch.Generator().manual_seed(8)
+    q, k, v, _ = (t.to(DEV) for t in _inputs(B, H, G, T, dk, dv, seed=8))
+    idx = _random_indices(B, G, T, n, 64, gen, with_holes=False).to(DEV)
+    scale = dk ** -0.5
+    o, L, M = ops.slc_fwd(q, k, v, idx, 64, scale)
+    og, Lg, Mg = _generic(lambda: ops.slc_fwd(q, k, v, idx, 64, scale))
+    torch.cuda.synchronize()
+    _no_timeouts()
+    assert max_abs(o.float(), og.float()) < 2e-2 and max_abs(M + L, Mg + Lg) < 2e-2
+
+
+@pytest.mark.parametrize("dk,dv,H,G,T,n", [(64, 64, 8, 2, 512, 6), (192, 128, 16, 1, 1024, 16), (128, 128, 32, 1, 256, 4)])
+def test_selection_backward_tensorcore_vs_oracle(dk, dv, H, G, T, n):
+    from nsa import ops
+    gen = torch.Generator().manual_seed(9)
+    q, k, v, do = _inputs(2, H, G, T, dk, dv, seed=9)
+    idx = _random_indices(2, G, T, n, 64, gen)
+    scale = dk ** -0.5
+    qd, kd, vd, dod, idd = (t.to(DEV) for t in (q, k, v, do, idx))
+    o, L, M = ops.slc_fwd(qd, kd, vd, idd, 64, scale)
+    r1 = ops.slc_bwd(qd, kd, vd, idd, o, dod, L, M, 64, scale)
+    r2 = ops.slc_bwd(qd, kd, vd, idd, o, dod, L, M, 64, scale)
+    torch.cuda.synchronize()
+    _no_timeouts()
+    assert all(torch.equal(a, b_) for a, b_ in zip(r1, r2))          # fixed summation order
+    qo, ko, vo = (t.float().requires_grad_(True) for t in (q, k, v))
+    g = torch.autograd.grad(O.selection_attention(qo, ko, vo, idx.long(), 64, scale), (qo, ko, vo), do.float())
+    _grad_close(r1[0], g[0], "dq")
+    _grad_close(r1[1].transpose(-1, -2), g[1], "dk")
+    _grad_close(r1[2], g[2], "dv")
+
+
+def test_selection_backward_tensorcore_vs_generic_at_scale():
+    from nsa import ops
+    B, H, G, T, dk, dv, n = 1, 32, 2, 4096, 192, 128, 16
+    gen = torch.Generator().manual_seed(10)
+    q, k, v, do = (t.to(DEV) for t in _inputs(B, H, G, T, dk, dv, seed=10))
+    idx = _random_indices(B, G, T, n, 64, gen, with_holes=False).to(DEV)
+    scale = dk ** -0.5
+    o, L, M = ops.slc_fwd(q, k, v, idx, 64, scale)
+    tc = ops.slc_bwd(q, k, v, idx, o, do, L, M, 64, scale)
+    gen_ = _generic(lambda: ops.slc_bwd(q, k, v, idx, o, do, L, M, 64, scale))
+    torch.cuda.synchronize()
+    _no_timeouts()
+    for a, b_, nme in zip(tc, gen_, ("dq", "dk", "dv")):
+        _grad_close(a, b_.float().cpu(), "selection " + nme)

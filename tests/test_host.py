@@ -29,7 +29,7 @@ def test_argument_errors_without_a_gpu():
     assert rc == -1 and b"null" in L.lib.nsa_last_error()
     rc = L.lib.nsa_topn_from_scores(None, None, 1, 4, 2, 8, 8, 2, 100, 0, None)
     assert rc == -1
-    assert L.lib.nsa_slc_bwd_workspace_bytes(1, 4, 65536, 65536, 16, 64) > 4 * 65536 * 16 * 4
+    assert L.lib.nsa_slc_bwd_workspace_bytes(1, 64, 4, 65536, 65536, 192, 128, 16, 64, 1) > 4 * 65536 * 16 * 4
 
 
 def test_config_defaults_and_validation():
