@@ -149,11 +149,16 @@ NSA_API int nsa_phi_pool_bwd(const float* a, const float* c, const float* dhbar,
  * blocks, the sum over the heads of each group in head order, a stable top-min(n,n_sel) (ties to the
  * lower block id), then the fixed blocks [0, max(0,(t-l')/l'), t/l'] prepended, repeats dropped,
  * cut to n and padded with -1.  q [B,H,T,dk] (dtype, strides z,h,m,k), k_cmp fp32 [B,G,dk,nbp]
- * contiguous, block_ends [nbp], indices_out int32 [B,G,T,n] contiguous. */
+ * contiguous, block_ends [nbp], indices_out int32 [B,G,T,n] contiguous.
+ * n_real_blocks >= 0 asserts block_ends[i] == i*d + l - 1 for i < n_real_blocks and no later block ever
+ * visible, which admits the tensor-core kernel (fp32 keys split into bf16 hi + lo parts held in the
+ * workspace of nsa_score_topn_workspace_bytes() bytes); -1 makes no assumption. */
+NSA_API size_t nsa_score_topn_workspace_bytes(int B, int H, int G, int T, int dk, int nbp, int l, int d,
+                                              int l_prime, int n, int dtype);
 NSA_API int nsa_score_topn(const void* q, const int64_t* q_strides4, const float* k_cmp,
                    const int32_t* block_ends, int32_t* indices_out, int B, int H, int G, int T, int dk,
                    int nbp, int l, int d, int l_prime, int n, int n_fixed, float scale, int dtype,
-                   void* stream);
+                   int n_real_blocks, void* workspace, size_t workspace_bytes, void* stream);
 /* Eq. 10/11 alone on a given score tensor [B,H,T,n_sel] fp32 contiguous
  * (select_top_k_blocks_per_query_with_gqa, nsa/kernels.py:1965-2040). */
 NSA_API int nsa_topn_from_scores(const float* scores, int32_t* indices_out, int B, int H, int G, int T,

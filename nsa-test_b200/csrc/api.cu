@@ -77,7 +77,8 @@ static int check_common(const char* who, int B, int H, int G, int Tq, int Tk, in
 static bool tensor_core_bwd_ok_slc(const int64_t* s, int dtype, int H, int G, int Tq, int Tk, int dk, int dv, const void* q,
                                    const void* k, const void* v, const void* o, const void* dout, const void* dq,
                                    const void* dkey, const void* dval);
-static int g_kernel_family = 0;  // 0: tensor-core kernels where they apply, 1: stride-generic kernels only
+static int g_kernel_family = 0;
+int kernel_family() { return g_kernel_family; }  // 0: tensor-core kernels where they apply, 1: stride-generic kernels only
 
 // canonical contiguous layouts: q [B,H,T,dk], k [B,G,dk,Tk] (strides given as z,g,n,k), v [B,G,Tk,dv], o [B,H,T,dv]
 static bool canonical_fwd(const int64_t* s, int H, int G, int Tq, int Tk, int dk, int dv) {

@@ -1,0 +1,344 @@
+// Selection scoring on tcgen05 tensor cores: Eq. 8 -> 9 -> 10/11 fused, nothing of size [B,H,T,n_cmp]
+// leaves the SM (replaces the torch code of nsa/kernels.py:2304-2343, 1920-1962, 1965-2040 for bf16
+// queries in the canonical layout, l = 2d, block counts that are multiples of 128).
+//
+// Bit-exact top-n against an fp32 oracle needs logits far more accurate than bf16 keys give, so the fp32
+// compressed keys are split into bf16 hi + lo parts and every logit tile is S = Q K_hi^T + Q K_lo^T
+// accumulated in fp32 by the tensor core (16 mantissa bits of K, exact bf16 Q).
+// One CTA owns 128 queries of one KV group and makes two passes over (key tile, head):
+//   pass A  online (max, sum) of every (query, head) row -> logsumexp
+//   pass B  p = exp2(x - lse); per-key sums over the heads of the group (head order, fp32, registers);
+//           after the last head the l/d x l'/d stencil maps 128 keys to 128/(l'/d) selection blocks,
+//           which stream into a per-query sorted top-n list (score descending, ties to the lower id).
+// Then the forced blocks are merged in, repeats dropped, the list cut to n and padded with -1.
+#include <cuda.h>
+
+#include "attn_args.cuh"
+#include "common.cuh"
+#include "fa_sm100.cuh"
+#include "sm100_ptx.cuh"
+
+namespace nsa {
+
+using namespace ptx;
+
+constexpr int kScoreMaxN = 32;
+
+struct ScoreParams {
+  int32_t* out;  // [B,G,T,n]
+  int B, H, G, T, nbp;
+  int l, d, lprime, nb, n, n_fixed;
+  float scale_log2;
+  int* timeouts;
+};
+
+__global__ void split_hi_lo_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                   int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = x[i];
+  const __nv_bfloat16 h = __float2bfloat16_rn(v);
+  hi[i] = h;
+  lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+}
+
+struct ScoreBarriers {
+  uint64_t k_full, k_empty, q_full[2], q_empty[2], s_full[2], s_free[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+// Sorted insert into a per-thread top-k list kept in shared memory ([slot][128 rows]); score descending,
+// candidates arrive in ascending id order so an equal score never displaces an earlier entry.
+__device__ __noinline__ void topn_insert(float* lst_s, int* lst_i, int r, int& cnt, int k_actual, float sc, int j) {
+  if (cnt == k_actual) {
+    if (!(sc > lst_s[(cnt - 1) * 128 + r])) return;
+  } else {
+    ++cnt;
+  }
+  int pos = cnt - 1;
+  while (pos > 0 && lst_s[(pos - 1) * 128 + r] < sc) {
+    lst_s[pos * 128 + r] = lst_s[(pos - 1) * 128 + r];
+    lst_i[pos * 128 + r] = lst_i[(pos - 1) * 128 + r];
+    --pos;
+  }
+  lst_s[pos * 128 + r] = sc;
+  lst_i[pos * 128 + r] = j;
+}
+
+template <int DK>
+__global__ void __launch_bounds__(192, 1)
+score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKhi,
+                     const __grid_constant__ CUtensorMap tmKlo, const ScoreParams p, int hpg, int smem_state_off,
+                     int smem_list_off, int smem_bar_off) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  constexpr int kK = 128 * DK * 2, kQ = 128 * DK * 2;
+  uint8_t *sKhi = smem, *sKlo = smem + kK, *sQ = smem + 2 * kK;
+  float* st_m = reinterpret_cast<float*>(smem + smem_state_off);  // [hpg][128]
+  float* st_l = st_m + hpg * 128;                                   // [hpg][128]
+  float* lst_s = reinterpret_cast<float*>(smem + smem_list_off);   // [n][128]
+  int* lst_i = reinterpret_cast<int*>(lst_s + p.n * 128);           // [n][128]
+  ScoreBarriers* bar = reinterpret_cast<ScoreBarriers*>(smem + smem_bar_off);
+  volatile int* abort = &bar->abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * 128;
+  const int bg = blockIdx.y, b = bg / p.G, g = bg % p.G;
+  const int tl = m0 + 127;
+  const int kmax = tl >= p.l - 1 ? min(p.nb - 1, (tl - p.l + 1) / p.d) : -1;
+  const int ntiles = max(1, kmax / 128 + 1);
+  const int steps_per_pass = ntiles * hpg;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->k_full, 1);
+    mbar_init(&bar->k_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->q_full[i], 1);
+      mbar_init(&bar->q_empty[i], 1);
+      mbar_init(&bar->s_full[i], 1);
+      mbar_init(&bar->s_free[i], 128);
+    }
+    bar->abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) tmem_alloc(&bar->tmem_base, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      bool ok = true;
+      int kissued = 0, qissued = 0;
+      for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
+        const int within = step % steps_per_pass, kt = within / hpg, hh = within % hpg;
+        if (hh == 0) {
+          const int kidx = step / hpg;  // K tile loads so far
+          ok = mbar_wait(&bar->k_empty, (kidx & 1) ^ 1, abort);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bar->k_full, 2 * kK);
+          for (int hf = 0; hf < 2; ++hf) {
+            tma_load_2d(&tmKhi, &bar->k_full, sKhi + hf * (DK * 128), kt * 128 + hf * 64, bg * DK);
+            tma_load_2d(&tmKlo, &bar->k_full, sKlo + hf * (DK * 128), kt * 128 + hf * 64, bg * DK);
+          }
+          kissued = kidx + 1;
+        }
+        const int s = step & 1;
+        ok = mbar_wait(&bar->q_empty[s], ((step >> 1) & 1) ^ 1, abort);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bar->q_full[s], kQ);
+        for (int c = 0; c < DK / 64; ++c)
+          tma_load_2d(&tmQ, &bar->q_full[s], sQ + s * kQ + c * 16384, c * 64, (b * p.H + g * hpg + hh) * p.T + m0);
+        qissued = step + 1;
+      }
+      if (!ok) {
+        if (kissued > 0) mbar_wait(&bar->k_full, (kissued - 1) & 1, abort);
+        for (int st = max(0, qissued - 2); st < qissued; ++st) mbar_wait(&bar->q_full[st & 1], (st >> 1) & 1, abort);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idS = idesc_bf16(128, 128, 0, 1);
+      const uint64_t dKhi = smem_desc_sw128(smem_u32(sKhi), DK * 128, 1024);
+      const uint64_t dKlo = smem_desc_sw128(smem_u32(sKlo), DK * 128, 1024);
+      bool ok = true;
+      for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
+        const int hh = step % hpg, s = step & 1;
+        if (hh == 0) ok = mbar_wait(&bar->k_full, (step / hpg) & 1, abort);
+        ok = ok && mbar_wait(&bar->q_full[s], (step >> 1) & 1, abort) && mbar_wait(&bar->s_free[s], ((step >> 1) & 1) ^ 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * kQ), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dKhi, kk * 2048), idS, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dKlo, kk * 2048), idS, 1);
+        umma_commit(&bar->s_full[s]);
+        umma_commit(&bar->q_empty[s]);
+        if (hh == hpg - 1) umma_commit(&bar->k_empty);
+      }
+    }
+  } else {
+    const int r = warp * 32 + lane, t = m0 + r;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const int vis = t >= p.l - 1 ? min(p.nb - 1, (t - p.l + 1) / p.d) : -1;  // last visible compressed block
+    const int a_ = p.l / p.d, s_ = p.lprime / p.d;                          // a_ == 2 on this path
+    const int per_tile = 128 / s_;
+    const int n_sel = (p.nbp + s_ - 1) / s_;
+    const int k_actual = min(p.n, n_sel);
+    bool ok = true;
+    for (int hh = 0; hh < hpg; ++hh) {
+      st_m[hh * 128 + r] = -CUDART_INF_F;
+      st_l[hh * 128 + r] = 0.f;
+    }
+    int cnt = 0;
+    auto insert = [&](float sc, int j) { topn_insert(lst_s, lst_i, r, cnt, k_actual, sc, j); };
+    float agg[128];     // pass A: scaled logits of the current tile; pass B: per-key probability sums over heads
+    float cur = 0.f;    // running stencil sum of the selection block being assembled
+    (void)a_;
+    for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
+      const int pass = step / steps_per_pass, within = step % steps_per_pass, kt = within / hpg, hh = within % hpg, s = step & 1;
+      const int n0 = kt * 128;
+      const int chi = vis - n0;
+      if (pass == 1 && hh == 0) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) agg[i] = 0.f;
+      }
+      ok = mbar_wait(&bar->s_full[s], (step >> 1) & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      if (pass == 0) {
+        const float m_old = st_m[hh * 128 + r];
+        float mx = m_old;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sv[32];
+          tmem_ld32(tmem + lane_base + s * 128 + c * 32, sv);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float x = (c * 32 + e <= chi) ? __uint_as_float(sv[e]) * p.scale_log2 : -CUDART_INF_F;
+            agg[c * 32 + e] = x;
+            mx = fmaxf(mx, x);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&bar->s_free[s]);
+        if (mx != -CUDART_INF_F) {
+          float sum = 0.f;
+#pragma unroll
+          for (int i = 0; i < 128; ++i) sum += exp2f(agg[i] - mx);
+          st_l[hh * 128 + r] = st_l[hh * 128 + r] * exp2f(m_old - mx) + sum;  // m_old = -inf -> factor 0
+          st_m[hh * 128 + r] = mx;
+        }
+      } else {
+        const float m_h = st_m[hh * 128 + r], l_h = st_l[hh * 128 + r];
+        const float lse2 = l_h > 0.f ? m_h + log2f(l_h) : CUDART_INF_F;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sv[32];
+          tmem_ld32(tmem + lane_base + s * 128 + c * 32, sv);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float pr = (c * 32 + e <= chi) ? exp2f(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2)) : 0.f;
+            agg[c * 32 + e] += pr;
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&bar->s_free[s]);
+        if (vis < 0 && kt == 0) agg[0] += 1.f;  // a row that sees no block puts all its mass on block 0
+        if (hh == hpg - 1) {
+          // Eq. 9 with l = 2d: sel[j] = sum_{m<s_} (A[s_ j + m] + A[s_ j + m + 1]), adds issued in that order.
+          // Streaming over the keys: key i ends the previous block when i % s_ == 0 and otherwise enters the
+          // current block twice in a row; the block that straddles the tile end is finished by the next tile.
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            const float av = agg[i];
+            if (i % s_ == 0) {
+              if (kt > 0 || i > 0) insert(cur + av, (n0 + i) / s_ - 1);
+              cur = av;
+            } else {
+              cur = (cur + av) + av;
+            }
+          }
+        }
+      }
+    }
+    if (ok) {
+      insert(cur, ntiles * per_tile - 1);  // the last block's final term lies beyond every visible key: + 0
+      for (int j = ntiles * per_tile; j < n_sel && cnt < k_actual; ++j) insert(0.f, j);  // never-visible blocks, id order
+      int res[kScoreMaxN];
+      int nres = 0;
+      auto push = [&](int id) {
+        if (nres >= p.n) return;
+        for (int i = 0; i < nres; ++i)
+          if (res[i] == id) return;
+        res[nres++] = id;
+      };
+      if (p.n_fixed > 0) {
+        push(0);
+        push(t < p.lprime ? 0 : (t - p.lprime) / p.lprime);
+        push(t / p.lprime);
+      }
+      for (int i = 0; i < cnt; ++i) push(lst_i[i * 128 + r]);
+      int32_t* dst = p.out + ((int64_t)bg * p.T + t) * p.n;
+      for (int i = 0; i < p.n; ++i) dst[i] = i < nres ? res[i] : -1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+bool score_sm100_supported(int H, int G, int T, int dk, int nbp, int l, int d, int lprime, int n) {
+  if (!(dk == 192 || dk == 128 || dk == 64) || G <= 0 || H % G != 0) return false;
+  const int hpg = H / G;
+  if (d <= 0 || l != 2 * d || lprime % d != 0) return false;
+  const int s_ = lprime / d;
+  const size_t smem = 4 * (size_t)128 * dk * 2 + 2 * (size_t)hpg * 512 + 2 * (size_t)n * 512 + 256 + 1024;
+  return smem <= 227 * 1024 && T % 128 == 0 && nbp % 128 == 0 && 128 % s_ == 0 && n >= 1 && n <= kScoreMaxN;
+}
+
+size_t score_sm100_workspace_bytes(int B, int G, int dk, int nbp) { return 2 * (((size_t)B * G * dk * nbp * 2 + 255) & ~size_t(255)); }
+
+template <int DK>
+static int launch_score_t(const CUtensorMap& tq, const CUtensorMap& thi, const CUtensorMap& tlo, const ScoreParams& p,
+                          cudaStream_t st) {
+  const int hpg = p.H / p.G;
+  const int tiles = 2 * 128 * DK * 2 + 2 * 128 * DK * 2;
+  const int state_off = tiles, state_bytes = 2 * hpg * 128 * 4;
+  const int list_off = state_off + state_bytes, list_bytes = 2 * p.n * 128 * 4;
+  const int bar_off = list_off + list_bytes;
+  const int dyn = bar_off + 256 + 1024;
+  if (dyn > 227 * 1024) return fail(NSA_ERR_UNSUPPORTED, "score_topn: %d bytes of shared memory needed", dyn);
+  auto kern = score_topn_tc_kernel<DK>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess)
+    return fail(NSA_ERR_LAUNCH, "score_topn: cannot reserve shared memory");
+  KernelTimer kt("score_topn_tc", st);
+  kern<<<dim3(p.T / 128, p.B * p.G), 192, dyn, st>>>(tq, thi, tlo, p, hpg, state_off, list_off, bar_off);
+  return check_launch("score_topn_tc");
+}
+
+int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
+                     int lprime, int nb, int n, int n_fixed, float scale, void* workspace, size_t workspace_bytes,
+                     cudaStream_t st) {
+  if (!score_sm100_supported(H, G, T, dk, nbp, l, d, lprime, n)) return fail(NSA_ERR_UNSUPPORTED, "score_topn_sm100: unsupported shape");
+  const size_t need = score_sm100_workspace_bytes(B, G, dk, nbp);
+  if (!workspace || workspace_bytes < need)
+    return fail(NSA_ERR_WORKSPACE, "scoring needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  __nv_bfloat16* hi = (__nv_bfloat16*)workspace;
+  __nv_bfloat16* lo = (__nv_bfloat16*)((char*)workspace + need / 2);
+  const int64_t nk = (int64_t)B * G * dk * nbp;
+  {
+    KernelTimer kt("score_split_keys", st);
+    split_hi_lo_kernel<<<(unsigned)((nk + 255) / 256), 256, 0, st>>>(k_cmp, hi, lo, nk);
+  }
+  if (int rc = check_launch("split_hi_lo")) return rc;
+  CUtensorMap tq, thi, tlo;
+  if (int rc = make_tmap_bf16_2d(&tq, q, (uint64_t)B * H * T, dk, 128)) return rc;
+  if (int rc = make_tmap_bf16_2d(&thi, hi, (uint64_t)B * G * dk, nbp, dk)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tlo, lo, (uint64_t)B * G * dk, nbp, dk)) return rc;
+  ScoreParams p;
+  p.out = out;
+  p.B = B; p.H = H; p.G = G; p.T = T; p.nbp = nbp; p.l = l; p.d = d; p.lprime = lprime; p.nb = nb; p.n = n; p.n_fixed = n_fixed;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.timeouts = fa_timeout_counter();
+  if (dk == 192) return launch_score_t<192>(tq, thi, tlo, p, st);
+  if (dk == 128) return launch_score_t<128>(tq, thi, tlo, p, st);
+  return launch_score_t<64>(tq, thi, tlo, p, st);
+}
+
+}  // namespace nsa

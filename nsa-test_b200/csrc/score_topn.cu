@@ -8,6 +8,7 @@
 // stable descending sort so ties go to the lower block id, fixed blocks first, repeats dropped,
 // -1 padding).  Nothing of size [B,H,T,n_cmp] ever reaches HBM: one CTA owns one (b,g,t).
 #include "common.cuh"
+#include "fa_sm100.cuh"
 
 namespace nsa {
 
@@ -166,10 +167,33 @@ topn_from_scores_kernel(const float* __restrict__ scores, int32_t* __restrict__ 
 
 using namespace nsa;
 
+namespace nsa { int kernel_family(); }
+
+static bool score_tc_ok(const void* q, const int64_t* qs, int B, int H, int G, int T, int dk, int nbp, int l, int d, int l_prime,
+                        int n, int n_real_blocks, int dtype) {
+  if (nsa::kernel_family() != 0 || dtype != NSA_BF16 || n_real_blocks < 0 || n_real_blocks > nbp) return false;
+  if (!score_sm100_supported(H, G, T, dk, nbp, l, d, l_prime, n) || (int64_t)B * G > 65535) return false;
+  const int64_t cq[4] = {(int64_t)H * T * dk, (int64_t)T * dk, dk, 1};
+  for (int i = 0; i < 4; ++i)
+    if (qs[i] != cq[i]) return false;
+  return (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+}
+
+extern "C" NSA_API size_t nsa_score_topn_workspace_bytes(int B, int H, int G, int T, int dk, int nbp, int l, int d, int l_prime,
+                                                         int n, int dtype) {
+  if (B <= 0 || G <= 0 || dtype != NSA_BF16 || nsa::kernel_family() != 0 || !score_sm100_supported(H, G, T, dk, nbp, l, d, l_prime, n))
+    return 256;
+  return score_sm100_workspace_bytes(B, G, dk, nbp);
+}
+
 extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const float* k_cmp, const int32_t* block_ends,
                               int32_t* indices_out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
-                              int l_prime, int n, int n_fixed, float scale, int dtype, void* stream) {
+                              int l_prime, int n, int n_fixed, float scale, int dtype, int n_real_blocks, void* workspace,
+                              size_t workspace_bytes, void* stream) {
   NSA_REQUIRE(q && qs && k_cmp && block_ends && indices_out, "score_topn: null pointer");
+  if (B > 0 && T > 0 && score_tc_ok(q, qs, B, H, G, T, dk, nbp, l, d, l_prime, n, n_real_blocks, dtype))
+    return score_topn_sm100(q, k_cmp, indices_out, B, H, G, T, dk, nbp, l, d, l_prime, n_real_blocks, n, n_fixed, scale, workspace,
+                            workspace_bytes, (cudaStream_t)stream);
   NSA_REQUIRE(G > 0 && H % G == 0 && d > 0 && l % d == 0 && l_prime % d == 0 && l > 0 && l_prime > 0,
               "score_topn: bad block parameters");
   NSA_REQUIRE(n > 0 && n <= kMaxN, "score_topn: n=%d outside 1..%d", n, kMaxN);

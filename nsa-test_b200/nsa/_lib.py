@@ -47,7 +47,8 @@ PROTOTYPES = {
     "nsa_slc_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 9 + [c_float, c_int, _P, c_size_t, _P]),
     "nsa_phi_pool_fwd": (c_int, [_P, _P, _P, _I64P, _P, _P] + [c_int] * 10 + [_P]),
     "nsa_phi_pool_bwd": (c_int, [_P] * 7 + [c_int] * 9 + [_P]),
-    "nsa_score_topn": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 11 + [c_float, c_int, _P]),
+    "nsa_score_topn_workspace_bytes": (c_size_t, [c_int] * 11),
+    "nsa_score_topn": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 11 + [c_float, c_int, c_int, _P, c_size_t, _P]),
     "nsa_topn_from_scores": (c_int, [_P, _P] + [c_int] * 8 + [_P]),
     "nsa_cmp_probs": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 6 + [c_float, c_int, _P]),
     "nsa_eq9_scores": (c_int, [_P, _P, c_int64] + [c_int] * 4 + [_P]),

@@ -272,7 +272,7 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
     block_ends = torch.full((k_cmp.shape[-1],), PAD_BLOCK_END, device=q.device, dtype=torch.int32)
     block_ends[:nb] = torch.arange(nb, device=q.device, dtype=torch.int32) * cfg.d + (cfg.l - 1)
     n_fixed = cfg.n_fixed if cfg.include_fixed_in_selection else 0
-    indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale)
+    indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale, nb)
     o_cmp = CompressionAttention.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, scale, cfg, (cfg.l, cfg.d, nb))
     o_slc = SelectionAttention.apply(q, k_slc, v_slc, indices, scale, cfg)
     o_win = SlidingWindowAttention.apply(q, kw, vw, scale, cfg.w, cfg)

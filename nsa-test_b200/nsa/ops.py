@@ -178,18 +178,22 @@ def phi_pool_bwd(a, c, dhbar, dv_cmp, l: int, d: int, n_blocks: int):
     return da, dc_part.sum(0), dv
 
 
-def score_topn(q, k_cmp_f32, block_ends, l: int, d: int, l_prime: int, n: int, n_fixed: int, scale: float):
-    """q [B,H,T,dk], k_cmp fp32 [B,G,dk,nbp] -> int32 indices [B,G,T,n]."""
+def score_topn(q, k_cmp_f32, block_ends, l: int, d: int, l_prime: int, n: int, n_fixed: int, scale: float,
+               n_real_blocks: int = -1):
+    """q [B,H,T,dk], k_cmp fp32 [B,G,dk,nbp] -> int32 indices [B,G,T,n].  ``n_real_blocks >= 0`` asserts the
+    canonical block ends (block i ends at i*d + l - 1 for i < n_real_blocks, later blocks never visible)."""
     dev = require_cuda(q, k_cmp_f32, block_ends)
     B, H, T, dk = q.shape
     G, nbp = k_cmp_f32.shape[1], k_cmp_f32.shape[-1]
     kc = k_cmp_f32.float().contiguous()
     be = block_ends.to(torch.int32).contiguous()
     out = torch.empty(B, G, T, n, device=dev, dtype=torch.int32)
+    nbytes = lib.nsa_score_topn_workspace_bytes(B, H, G, T, dk, nbp, int(l), int(d), int(l_prime), int(n), dtype_code(q))
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
         check(lib.nsa_score_topn(ptr(q), i64(q.stride()), ptr(kc), ptr(be), ptr(out), B, H, G, T, dk, nbp, int(l), int(d),
-                                 int(l_prime), int(n), int(n_fixed), float(scale), dtype_code(q), stream_ptr(dev)),
-              "nsa_score_topn")
+                                 int(l_prime), int(n), int(n_fixed), float(scale), dtype_code(q), int(n_real_blocks), ptr(ws),
+                                 nbytes, stream_ptr(dev)), "nsa_score_topn")
     return out
 
 

@@ -261,3 +261,33 @@ def test_selection_backward_tensorcore_vs_generic_at_scale():
     _no_timeouts()
     for a, b_, nme in zip(tc, gen_, ("dq", "dk", "dv")):
         _grad_close(a, b_.float().cpu(), "selection " + nme)
+
+
+@pytest.mark.parametrize("dk,H,G,T", [(64, 8, 2, 2048), (192, 16, 1, 4096)])
+def test_score_topn_tensorcore_bit_exact_outside_ambiguity(dk, H, G, T):
+    """Fused Eq. 8-11 on tensor cores (bf16 hi + lo split of the fp32 keys) against the fp32 CPU oracle:
+    identical block ids on every row whose ranking does not hinge on rounding, and identical to the
+    stride-generic CUDA kernel under the same rule."""
+    from nsa import ops
+    from tests.util import ambiguous_rows
+    l, d, lp, n = 32, 16, 64, 16
+    inp = O.make_inputs(1, H, G, T, dk, 64, 64, l, seed=11, block_offset_std=0.5, dtype=torch.bfloat16)
+    k_cmp, _, be, nb = O.compress_tokens(inp["k"].transpose(-1, -2), inp["v"], inp["phi"], l, d)
+    scale = dk ** -0.5
+    p = O.compression_probabilities(inp["q"], k_cmp, be, scale)
+    sel = O.selection_scores_from_compression(p, l, d, lp)
+    ref = O.select_top_n(sel, G, n, lp)
+    agg = sel.view(1, G, H // G, T, -1).sum(2)
+    amb = ambiguous_rows(agg, n)
+    qd = inp["q"].bfloat16().to(DEV)
+    tc = ops.score_topn(qd, k_cmp.to(DEV), be.to(DEV), l, d, lp, n, 3, scale, n_real_blocks=nb).cpu().long()
+    gen = _generic(lambda: ops.score_topn(qd, k_cmp.to(DEV), be.to(DEV), l, d, lp, n, 3, scale)).cpu().long()
+    torch.cuda.synchronize()
+    _no_timeouts()
+    bad_tc = (tc != ref).any(-1) & ~amb
+    bad_gen = (gen != ref).any(-1) & ~amb
+    assert not bad_gen.any(), f"generic kernel: {int(bad_gen.sum())} unambiguous rows differ"
+    assert not bad_tc.any(), f"tensor-core kernel: {int(bad_tc.sum())} unambiguous rows differ, first {bad_tc.nonzero()[:3].tolist()}"
+    assert amb.float().mean() < 0.1
+    # early rows: forced blocks first, never-visible blocks listed in id order, -1 padding only when blocks run out
+    assert tc[0, 0, 0].tolist()[:3] == [0, 1, 2] and (tc >= -1).all() and (tc < (T + lp - 1) // lp).all()
