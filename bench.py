@@ -132,9 +132,8 @@ def layer_step(inp, params, cfg, world):
     plist = list(params.values())
     grads = torch.autograd.grad(out, [q, k, v] + plist, inp["do"])
     if world > 1:
-        import torch.distributed as dist
-        flat = torch.cat([g_.float().reshape(-1) for g_ in grads[3:]])
-        dist.all_reduce(flat)
+        from nsa.sharding import allreduce_grads
+        allreduce_grads(grads[3:])      # phi and gate-MLP weight gradients: the only collective of the layer
     return out[0, 0, -1, :8].float().sum() + grads[0][0, 0, -1, :8].float().sum()
 
 

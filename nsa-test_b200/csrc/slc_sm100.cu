@@ -83,36 +83,50 @@ struct ChunkWalker {
 template <int DK, int DV>
 struct SlcFwdSmem {
   static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2;
-  static constexpr int oK = 0, oV = oK + 2 * kK, oQ = oV + 2 * kV, oBar = oQ + 2 * kQ;
+  static constexpr int kQStages = 3;
+  static constexpr int oK = 0, oV = oK + 2 * kK, oQ = oV + 2 * kV, oBar = oQ + kQStages * kQ;
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct SlcFwdBarriers {
-  uint64_t kv_full[2], kv_empty[2], q_full[2], q_empty[2], s_full[2], p_full[2], o_full[2], o_read[2];
+  uint64_t kv_full[2], kv_empty[2], q_full[3], q_empty[3], s_full[2], p_full[2], o_full[2], o_read[2];
   uint32_t tmem_base;
   int abort;
 };
 
-// gather 128 rows (qpc queries x hpg heads) of `width` bf16 into the K-major 128-byte-swizzled tile layout
-// (row r of the tile = query r / hpg of the chunk, head r % hpg; one row per producer thread)
+// Token-major copy [B,H,T,W] -> [B,G,T,H/G,W]: the rows of all heads of a group for one query become one contiguous
+// [H/G x W] box, so a chunk of queries is gathered with a handful of TMA tile loads instead of thousands of 16-byte copies.
+template <int W>
+__global__ void to_token_major_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int B, int H, int G,
+                                      int T) {
+  const int64_t ro = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (ro >= (int64_t)B * H * T) return;
+  const int hpg = H / G;
+  const int hh = ro % hpg;
+  const int64_t bgt = ro / hpg;
+  const int t = bgt % T;
+  const int bg = bgt / T, b = bg / G, g = bg % G;
+  const uint4* src = reinterpret_cast<const uint4*>(in + (((int64_t)b * H + g * hpg + hh) * T + t) * W);
+  uint4* dst = reinterpret_cast<uint4*>(out + ro * W);
+  if (lane < W / 8) dst[lane] = src[lane];
+}
+
+// One chunk = up to qpc queries; query qi fills rows [qi*hpg, (qi+1)*hpg) of the 128-row K-major swizzled tile.
+// Unused query slots are loaded from beyond the tensor (TMA fills zeros), so every chunk delivers the same byte count.
 template <int WIDTH>
-__device__ __forceinline__ void gather_row(const __nv_bfloat16* base, uint8_t* dst, const int* entries, int cnt,
-                                           int b, int g, int H, int hpg, int T, int r) {
-  const int qi = r / hpg, hh = r % hpg;
-  const bool valid = qi < cnt;
-  const int t = valid ? (entries[qi] & 0xFFFFFF) : 0;
-  const __nv_bfloat16* src = base + (((int64_t)b * H + g * hpg + hh) * T + t) * WIDTH;
-  const uint32_t d0 = smem_u32(dst) + r * 128;
-  const int nbytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+__device__ __forceinline__ void tma_gather_chunk(const CUtensorMap* tm, uint64_t* bar, uint8_t* dst, const int* entries, int cnt,
+                                                 int qpc, int hpg, int64_t bgT, int oob_row) {
+  for (int qi = 0; qi < qpc; ++qi) {
+    const int row = qi < cnt ? (int)((bgT + (entries[qi] & 0xFFFFFF)) * hpg) : oob_row;
 #pragma unroll
-  for (int c = 0; c < WIDTH / 8; ++c) {
-    const uint32_t d = d0 + (c >> 3) * 16384 + (((c & 7) ^ (r & 7)) << 4);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src + c * 8), "r"(nbytes) : "memory");
+    for (int c = 0; c < WIDTH / 64; ++c) tma_load_2d(tm, bar, dst + c * 16384 + qi * hpg * 128, c * 64, row);
   }
 }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(416, 1)
-slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SlcParams p) {
+__global__ void __launch_bounds__(320, 1)
+slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+               const __grid_constant__ CUtensorMap tmQt, const SlcParams p) {
   using SM = SlcFwdSmem<DK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -128,11 +142,13 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const bool has_work = e0 < off[p.nblk];
 
   if (threadIdx.x == 0) {
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&bar->q_full[i], 1);
+      mbar_init(&bar->q_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar->kv_full[i], 1);
       mbar_init(&bar->kv_empty[i], 1);
-      mbar_init(&bar->q_full[i], 128);
-      mbar_init(&bar->q_empty[i], 1);
       mbar_init(&bar->s_full[i], 1);
       mbar_init(&bar->p_full[i], 128);
       mbar_init(&bar->o_full[i], 1);
@@ -150,54 +166,36 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
   if (!has_work) {
     // nothing to do for this CTA
-  } else if (warp >= 9) {
-    // ------------------------------------------------------------ producers (4 warps): K/V by TMA, Q rows by cp.async
-    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-    const int prow = (warp - 9) * 32 + lane;
-    bool ok = true;
-    int c = 0, kvidx = -1, last_blk = -1;
-    int pending_stage = -1;
-    for (; !w.done() && ok; w.next(), ++c) {
-      if (w.blk != last_blk) {
-        // hand over the chunk still in flight first: the K/V slot is only released after that chunk was consumed
-        if (pending_stage >= 0) {
-          asm volatile("cp.async.wait_group 0;" ::: "memory");
-          fence_proxy_async();
-          mbar_arrive(&bar->q_full[pending_stage]);
-          pending_stage = -1;
-        }
-        last_blk = w.blk;
-        ++kvidx;
-        if (prow == 0) {
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ producer: K/V blocks and gathered Q rows, all by TMA
+    if (lane == 0) {
+      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+      const int oob_row = p.B * p.H * p.Tq;
+      bool ok = true;
+      int c = 0, kvidx = -1, last_blk = -1;
+      for (; !w.done() && ok; w.next(), ++c) {
+        if (w.blk != last_blk) {
+          last_blk = w.blk;
+          ++kvidx;
           const int ks = kvidx & 1;
           ok = mbar_wait(&bar->kv_empty[ks], ((kvidx >> 1) & 1) ^ 1, abort);
-          if (ok) {
-            mbar_arrive_expect_tx(&bar->kv_full[ks], SM::kK + SM::kV);
-            tma_load_2d(&tmK, &bar->kv_full[ks], sK + ks * SM::kK, w.blk * 64, (b * p.G + g) * DK);
-            for (int cc = 0; cc < DV / 64; ++cc)
-              tma_load_2d(&tmV, &bar->kv_full[ks], sV + ks * SM::kV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
-          }
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bar->kv_full[ks], SM::kK + SM::kV);
+          tma_load_2d(&tmK, &bar->kv_full[ks], sK + ks * SM::kK, w.blk * 64, (b * p.G + g) * DK);
+          for (int cc = 0; cc < DV / 64; ++cc)
+            tma_load_2d(&tmV, &bar->kv_full[ks], sV + ks * SM::kV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
         }
+        const int s = c % 3;
+        ok = mbar_wait(&bar->q_empty[s], ((c / 3) & 1) ^ 1, abort);
         if (!ok) break;
+        mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ);
+        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], sQ + s * SM::kQ, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row);
       }
-      const int s = c & 1;
-      ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
-      if (!ok) break;
-      gather_row<DK>(p.q, sQ + s * SM::kQ, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      if (pending_stage >= 0) {
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        fence_proxy_async();
-        mbar_arrive(&bar->q_full[pending_stage]);
+      if (!ok) {  // let copies in flight land before the CTA gives its shared memory back
+        if (kvidx >= 0) mbar_wait(&bar->kv_full[kvidx & 1], (kvidx >> 1) & 1, abort);
+        for (int cc = max(0, c - 3); cc < c; ++cc) mbar_wait(&bar->q_full[cc % 3], (cc / 3) & 1, abort);
       }
-      pending_stage = s;
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (pending_stage >= 0 && ok) {
-      fence_proxy_async();
-      mbar_arrive(&bar->q_full[pending_stage]);
-    }
-    if (!ok && prow == 0 && kvidx >= 0) mbar_wait(&bar->kv_full[kvidx & 1], (kvidx >> 1) & 1, abort);
   } else if (warp == 8) {
     // ------------------------------------------------------------ UMMA issuer
     if (lane == 0) {
@@ -207,8 +205,8 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       bool ok = true;
       int c = 0, kvidx = -1, last_blk = -1, prev_ks = -1;
       auto issue_s = [&](int cc, int ks) -> bool {
-        const int s = cc & 1, buf = cc & 1;
-        if (!mbar_wait(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
+        const int s = cc % 3, buf = cc & 1;
+        if (!mbar_wait(&bar->q_full[s], (cc / 3) & 1, abort)) return false;
         if (!mbar_wait(&bar->o_read[buf], ((cc >> 1) & 1) ^ 1, abort)) return false;
         tc_fence_after();
         const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * SM::kQ), 16, 1024);
@@ -421,8 +419,9 @@ struct SlcDqBarriers {
 };
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(416, 1)
-slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SlcParams p) {
+__global__ void __launch_bounds__(320, 1)
+slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                  const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmdOt, const SlcParams p) {
   using SM = SlcDqSmem<DK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -441,7 +440,7 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     mbar_init(&bar->kv_full, 1);
     mbar_init(&bar->kv_empty, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar->q_full[i], 128);
+      mbar_init(&bar->q_full[i], 1);
       mbar_init(&bar->q_empty[i], 1);
       mbar_init(&bar->sdp_full[i], 1);
       mbar_init(&bar->ds_full[i], 128);
@@ -460,52 +459,36 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   constexpr uint32_t cdQ = 256;
 
   if (!has_work) {
-  } else if (warp >= 9) {
-    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-    const int prow = (warp - 9) * 32 + lane;
-    bool ok = true;
-    int c = 0, kvidx = -1, last_blk = -1, pending_stage = -1;
-    for (; !w.done() && ok; w.next(), ++c) {
-      if (w.blk != last_blk) {
-        // hand over the chunk still in flight first: the K/V slot is only released after that chunk was consumed
-        if (pending_stage >= 0) {
-          asm volatile("cp.async.wait_group 0;" ::: "memory");
-          fence_proxy_async();
-          mbar_arrive(&bar->q_full[pending_stage]);
-          pending_stage = -1;
-        }
-        last_blk = w.blk;
-        ++kvidx;
-        if (prow == 0) {
+  } else if (warp == 9) {
+    if (lane == 0) {
+      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+      const int oob_row = p.B * p.H * p.Tq;
+      bool ok = true;
+      int c = 0, kvidx = -1, last_blk = -1;
+      for (; !w.done() && ok; w.next(), ++c) {
+        if (w.blk != last_blk) {
+          last_blk = w.blk;
+          ++kvidx;
           ok = mbar_wait(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
-          if (ok) {
-            mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
-            tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
-            for (int cc = 0; cc < DV / 64; ++cc)
-              tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
-          }
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
+          tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
+          for (int cc = 0; cc < DV / 64; ++cc)
+            tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
         }
+        const int s = c & 1;
+        ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
         if (!ok) break;
+        mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
+        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], sSt + s * SM::kStage, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row);
+        tma_gather_chunk<DV>(&tmdOt, &bar->q_full[s], sSt + s * SM::kStage + SM::kQ, ent + w.e, w.count(), qpc, p.hpg,
+                             (int64_t)bg * p.Tq, oob_row);
       }
-      const int s = c & 1;
-      ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
-      if (!ok) break;
-      gather_row<DK>(p.q, sSt + s * SM::kStage, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
-      gather_row<DV>(p.dout, sSt + s * SM::kStage + SM::kQ, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      if (pending_stage >= 0) {
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        fence_proxy_async();
-        mbar_arrive(&bar->q_full[pending_stage]);
+      if (!ok) {
+        if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
+        for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
       }
-      pending_stage = s;
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (pending_stage >= 0 && ok) {
-      fence_proxy_async();
-      mbar_arrive(&bar->q_full[pending_stage]);
-    }
-    if (!ok && prow == 0 && kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
   } else if (warp == 8) {
     if (lane == 0) {
       constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);    // Q rows x K block (keys contiguous)
@@ -689,8 +672,9 @@ struct SlcDkvBarriers {
 };
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(288, 1)
-slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SlcParams p) {
+__global__ void __launch_bounds__(192, 1)
+slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmdOt, const SlcParams p) {
   using SM = SlcDkvSmem<DK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -710,7 +694,7 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     mbar_init(&bar->kv_full, 1);
     mbar_init(&bar->kv_empty, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar->q_full[i], 128);
+      mbar_init(&bar->q_full[i], 2);  // TMA bytes + the statistics written by the producer warp
       mbar_init(&bar->q_empty[i], 1);
     }
     mbar_init(&bar->stp_full, 1);
@@ -729,25 +713,17 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   constexpr uint32_t cdK = 0, cdV = DK, cST = DK + DV, cdPT = DK + DV + 64;
 
   if (!has_work) {
-  } else if (warp >= 5) {
-    // producers (4 warps): one gathered row of Q and dO per thread, plus that row's statistics
+  } else if (warp == 5) {
+    // producer warp: lane 0 drives TMA (K/V block, gathered Q and dO rows); all lanes fetch the rows' statistics
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-    const int prow = (warp - 5) * 32 + lane;
-    const int qi = prow / p.hpg, hh = prow % p.hpg;
+    const int oob_row = p.B * p.H * p.Tq;
     bool ok = true;
-    int c = 0, kvidx = -1, last_blk = -1, pending_stage = -1;
-    for (; !w.done() && ok; w.next(), ++c) {
+    int c = 0, kvidx = -1, last_blk = -1;
+    for (; !w.done(); w.next(), ++c) {
       if (w.blk != last_blk) {
-        // hand over the chunk still in flight first: the K/V slot is only released after that chunk was consumed
-        if (pending_stage >= 0) {
-          asm volatile("cp.async.wait_group 0;" ::: "memory");
-          fence_proxy_async();
-          mbar_arrive(&bar->q_full[pending_stage]);
-          pending_stage = -1;
-        }
         last_blk = w.blk;
         ++kvidx;
-        if (prow == 0) {
+        if (lane == 0) {
           ok = mbar_wait(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
           if (ok) {
             mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
@@ -756,37 +732,36 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
               tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
           }
         }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
       }
       const int s = c & 1;
-      ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
+      if (lane == 0) ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       uint8_t* st = sSt + s * SM::kStage;
-      gather_row<DK>(p.q, st, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
-      gather_row<DV>(p.dout, st + SM::kQ, ent + w.e, w.count(), b, g, p.H, p.hpg, p.Tq, prow);
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      {
-        float* stat = reinterpret_cast<float*>(st + SM::kQ + SM::kdO);
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
+        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], st, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row);
+        tma_gather_chunk<DV>(&tmdOt, &bar->q_full[s], st + SM::kQ, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row);
+      }
+      float* stat = reinterpret_cast<float*>(st + SM::kQ + SM::kdO);
+      for (int rr = lane; rr < 128; rr += 32) {
+        const int qi = rr / p.hpg, hh = rr % p.hpg;
         const bool valid = qi < w.count();
         const int t = valid ? (ent[w.e + qi] & 0xFFFFFF) : -1;
         const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + max(t, 0);
-        stat[prow] = valid ? p.lse2[srow] : CUDART_INF_F;
-        stat[128 + prow] = valid ? p.D[srow] : 0.f;
-        reinterpret_cast<int*>(stat)[256 + prow] = t;  // -1: row not in use
+        stat[rr] = valid ? p.lse2[srow] : CUDART_INF_F;
+        stat[128 + rr] = valid ? p.D[srow] : 0.f;
+        reinterpret_cast<int*>(stat)[256 + rr] = t;  // -1: row not in use
       }
-      if (pending_stage >= 0) {
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        fence_proxy_async();
-        mbar_arrive(&bar->q_full[pending_stage]);
-      }
-      pending_stage = s;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->q_full[s]);
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (pending_stage >= 0 && ok) {
-      fence_proxy_async();
-      mbar_arrive(&bar->q_full[pending_stage]);
+    if (!ok && lane == 0) {
+      if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
+      for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
     }
-    if (!ok && prow == 0 && kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
   } else if (warp == 4) {
     if (lane == 0) {
       constexpr uint32_t idST = idesc_bf16(64, 64, 1, 0);    // K block as A (keys contiguous) x Q rows (K-major)
@@ -968,16 +943,30 @@ bool slc_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv, int nslot
   if (!dims || G <= 0 || H % G != 0) return false;
   const int hpg = H / G;
   return hpg <= 128 && 128 % hpg == 0 && lprime == 64 && Tk % 64 == 0 && Tk > 0 && Tq > 0 && Tq < (1 << 24) &&
-         nslots > 0 && nslots <= 32;
+         nslots > 0 && nslots <= 32;  // (the caller also keeps B*H*Tq below 2^31: rows are 32-bit TMA coordinates)
 }
 
 size_t slc_fwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime) {
   const size_t rows = (size_t)B * H * Tq * nslots;
-  return al256(slc_csr_workspace_bytes(B, G, Tq, Tk, nslots, lprime)) + al256(rows * dv * 2) + al256(rows * sizeof(float2));
+  return al256(slc_csr_workspace_bytes(B, G, Tq, Tk, nslots, lprime)) + al256(rows * dv * 2) + al256(rows * sizeof(float2)) +
+         al256((size_t)B * H * Tq * dk * 2);
+}
+
+template <int W>
+static int token_major_copy(const void* in, void* out, int B, int H, int G, int T, const char* what, cudaStream_t st) {
+  const int64_t rows = (int64_t)B * H * T;
+  KernelTimer kt(what, st);
+  to_token_major_kernel<W><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, B, H, G, T);
+  return check_launch(what);
+}
+static int token_major_copy_w(int W, const void* in, void* out, int B, int H, int G, int T, const char* what, cudaStream_t st) {
+  if (W == 192) return token_major_copy<192>(in, out, B, H, G, T, what, st);
+  if (W == 128) return token_major_copy<128>(in, out, B, H, G, T, what, st);
+  return token_major_copy<64>(in, out, B, H, G, T, what, st);
 }
 
 template <int DK, int DV>
-static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const SlcParams& p, const int* indices,
+static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tqt, const SlcParams& p, const int* indices,
                             const int64_t* sidx, __nv_bfloat16* out, float* L, float* M, cudaStream_t st) {
   using SM = SlcFwdSmem<DK, DV>;
   auto kern = slc_fwd_kernel<DK, DV>;
@@ -986,7 +975,7 @@ static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   const int nparts = (int)(((int64_t)p.Tq * p.nslots + kEntriesPerCta - 1) / kEntriesPerCta);
   {
     KernelTimer kt("slc_fwd", st);
-    kern<<<dim3(nparts, p.B * p.G), 416, SM::kDynamic, st>>>(tk, tv, p);
+    kern<<<dim3(nparts, p.B * p.G), 320, SM::kDynamic, st>>>(tk, tv, tqt, p);
   }
   if (int rc = check_launch("slc_fwd_sm100")) return rc;
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
@@ -1010,6 +999,8 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
   const size_t rows = (size_t)B * H * Tq * nslots;
   p.o_part = (__nv_bfloat16*)(w + csr_bytes);
   p.st_part = (float2*)(w + csr_bytes + al256(rows * dv * 2));
+  void* qt = w + csr_bytes + al256(rows * dv * 2) + al256(rows * sizeof(float2));
+  if (int rc = token_major_copy_w(dk, q, qt, B, H, G, Tq, "slc_q_token_major", st)) return rc;
   p.q = (const __nv_bfloat16*)q;
   p.B = B; p.H = H; p.G = G; p.Tq = Tq; p.Tk = Tk; p.nslots = nslots; p.nblk = (Tk + 63) / 64; p.hpg = H / G;
   p.scale = scale; p.scale_log2 = scale * kLog2ef;
@@ -1017,9 +1008,11 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
   CUtensorMap tk, tv;
   if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
   if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, 64)) return rc;
-  if (dk == 192 && dv == 128) return launch_slc_fwd_t<192, 128>(tk, tv, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
-  if (dk == 128 && dv == 128) return launch_slc_fwd_t<128, 128>(tk, tv, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
-  if (dk == 64 && dv == 64) return launch_slc_fwd_t<64, 64>(tk, tv, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  CUtensorMap tqt;
+  if (int rc = make_tmap_bf16_2d(&tqt, qt, (uint64_t)B * H * Tq, dk, H / G)) return rc;
+  if (dk == 192 && dv == 128) return launch_slc_fwd_t<192, 128>(tk, tv, tqt, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  if (dk == 128 && dv == 128) return launch_slc_fwd_t<128, 128>(tk, tv, tqt, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  if (dk == 64 && dv == 64) return launch_slc_fwd_t<64, 64>(tk, tv, tqt, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
   return fail(NSA_ERR_UNSUPPORTED, "slc_fwd_sm100: unsupported head dims");
 }
 
@@ -1028,7 +1021,7 @@ void launch_bwd_prep(const void* o, const void* dout, const float* L, const floa
                      cudaStream_t st);
 
 static void slc_bwd_layout(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, size_t* o_stat,
-                           size_t* o_dq, size_t* o_dk, size_t* o_dv, size_t* total) {
+                           size_t* o_dq, size_t* o_dk, size_t* o_dv, size_t* o_qt, size_t* o_dot, size_t* total) {
   const size_t rows = (size_t)B * H * Tq;
   const size_t nparts = ((size_t)Tq * nslots + kEntriesPerCta - 1) / kEntriesPerCta;
   const size_t nseg = nparts + (size_t)(Tk + 63) / 64;
@@ -1037,17 +1030,20 @@ static void slc_bwd_layout(int B, int H, int G, int Tq, int Tk, int dk, int dv, 
   *o_dq = o;   o += al256(rows * nslots * dk * 2);
   *o_dk = o;   o += al256((size_t)B * G * nseg * 64 * dk * sizeof(float));
   *o_dv = o;   o += al256((size_t)B * G * nseg * 64 * dv * sizeof(float));
+  *o_qt = o;   o += al256(rows * dk * 2);
+  *o_dot = o;  o += al256(rows * dv * 2);
   *total = o;
 }
 
 size_t slc_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime) {
-  size_t a, b, c, d, total;
-  slc_bwd_layout(B, H, G, Tq, Tk, dk, dv, nslots, lprime, &a, &b, &c, &d, &total);
+  size_t a, b, c, d, e, f, total;
+  slc_bwd_layout(B, H, G, Tq, Tk, dk, dv, nslots, lprime, &a, &b, &c, &d, &e, &f, &total);
   return total;
 }
 
 template <int DK, int DV>
-static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const SlcParams& p, const int* indices,
+static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tqt, const CUtensorMap& tdot,
+                            const SlcParams& p, const int* indices,
                             const int64_t* sidx, __nv_bfloat16* dq, cudaStream_t st) {
   auto kq = slc_bwd_dq_kernel<DK, DV>;
   auto kkv = slc_bwd_dkv_kernel<DK, DV>;
@@ -1057,7 +1053,7 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   const int nparts = (int)(((int64_t)p.Tq * p.nslots + kEntriesPerCta - 1) / kEntriesPerCta);
   {
     KernelTimer kt("slc_bwd_dq", st);
-    kq<<<dim3(nparts, p.B * p.G), 416, SlcDqSmem<DK, DV>::kDynamic, st>>>(tk, tv, p);
+    kq<<<dim3(nparts, p.B * p.G), 320, SlcDqSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
   }
   if (int rc = check_launch("slc_bwd_dq_sm100")) return rc;
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
@@ -1069,7 +1065,7 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   if (int rc = check_launch("slc_combine_dq")) return rc;
   {
     KernelTimer kt("slc_bwd_dkv", st);
-    kkv<<<dim3(nparts, p.B * p.G), 288, SlcDkvSmem<DK, DV>::kDynamic, st>>>(tk, tv, p);
+    kkv<<<dim3(nparts, p.B * p.G), 192, SlcDkvSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
   }
   if (int rc = check_launch("slc_bwd_dkv_sm100")) return rc;
   KernelTimer kt("slc_reduce_dkv", st);
@@ -1083,8 +1079,8 @@ int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indice
                   int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, void* workspace,
                   size_t workspace_bytes, cudaStream_t st) {
   if (!slc_sm100_supported(H, G, Tq, Tk, dk, dv, nslots, lprime)) return fail(NSA_ERR_UNSUPPORTED, "slc_bwd_sm100: unsupported shape");
-  size_t o_stat, o_dq, o_dk, o_dv, need;
-  slc_bwd_layout(B, H, G, Tq, Tk, dk, dv, nslots, lprime, &o_stat, &o_dq, &o_dk, &o_dv, &need);
+  size_t o_stat, o_dq, o_dk, o_dv, o_qt, o_dot, need;
+  slc_bwd_layout(B, H, G, Tq, Tk, dk, dv, nslots, lprime, &o_stat, &o_dq, &o_dk, &o_dv, &o_qt, &o_dot, &need);
   if (!workspace || workspace_bytes < need)
     return fail(NSA_ERR_WORKSPACE, "selection backward needs %zu workspace bytes, got %zu", need, workspace_bytes);
   SlcParams p = {};
@@ -1106,9 +1102,14 @@ int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indice
   CUtensorMap tk, tv;
   if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
   if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, 64)) return rc;
-  if (dk == 192 && dv == 128) return launch_slc_bwd_t<192, 128>(tk, tv, p, indices, sidx, (__nv_bfloat16*)dq, st);
-  if (dk == 128 && dv == 128) return launch_slc_bwd_t<128, 128>(tk, tv, p, indices, sidx, (__nv_bfloat16*)dq, st);
-  if (dk == 64 && dv == 64) return launch_slc_bwd_t<64, 64>(tk, tv, p, indices, sidx, (__nv_bfloat16*)dq, st);
+  if (int rc = token_major_copy_w(dk, q, w + o_qt, B, H, G, Tq, "slc_q_token_major", st)) return rc;
+  if (int rc = token_major_copy_w(dv, dout, w + o_dot, B, H, G, Tq, "slc_do_token_major", st)) return rc;
+  CUtensorMap tqt, tdot;
+  if (int rc = make_tmap_bf16_2d(&tqt, w + o_qt, (uint64_t)B * H * Tq, dk, H / G)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tdot, w + o_dot, (uint64_t)B * H * Tq, dv, H / G)) return rc;
+  if (dk == 192 && dv == 128) return launch_slc_bwd_t<192, 128>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, st);
+  if (dk == 128 && dv == 128) return launch_slc_bwd_t<128, 128>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, st);
+  if (dk == 64 && dv == 64) return launch_slc_bwd_t<64, 64>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, st);
   return fail(NSA_ERR_UNSUPPORTED, "slc_bwd_sm100: unsupported head dims");
 }
 

@@ -288,6 +288,9 @@ def test_score_topn_tensorcore_bit_exact_outside_ambiguity(dk, H, G, T):
     bad_gen = (gen != ref).any(-1) & ~amb
     assert not bad_gen.any(), f"generic kernel: {int(bad_gen.sum())} unambiguous rows differ"
     assert not bad_tc.any(), f"tensor-core kernel: {int(bad_tc.sum())} unambiguous rows differ, first {bad_tc.nonzero()[:3].tolist()}"
-    assert amb.float().mean() < 0.1
+    # the ambiguity set is a property of the data (near-uniform scores); what must stay small is the number
+    # of rows that actually differ, inside the set included
+    assert amb.float().mean() < 0.5
+    assert (tc != ref).any(-1).float().mean() < 0.01 and (gen != ref).any(-1).float().mean() < 0.01
     # early rows: forced blocks first, never-visible blocks listed in id order, -1 padding only when blocks run out
     assert tc[0, 0, 0].tolist()[:3] == [0, 1, 2] and (tc >= -1).all() and (tc < (T + lp - 1) // lp).all()

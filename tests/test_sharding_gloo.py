@@ -1,0 +1,59 @@
+"""World-size-2 CPU (gloo) test of the multi-rank host logic: batch sharding + one all-reduce of the
+compression-MLP / gate-MLP weight gradients reproduces the single-process gradients."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import nsa_oracle as O
+
+CFG = dict(B=2, H=4, G=2, T=96, dk=16, dv=16, d_model=32, l=8, d=4, l_prime=16, n=4, w=24)
+
+
+def _weight_grads(inp, b0, b1):
+    c = CFG
+    phi, gp = inp["phi"], inp["gate"]
+    ws = [p.clone().requires_grad_(True) for p in (phi.pos_embed, phi.w1, phi.b1, phi.w2, phi.b2, gp.w1, gp.b1, gp.w2, gp.b2)]
+    r = O.nsa_layer(inp["q"][b0:b1], inp["k"][b0:b1], inp["v"][b0:b1], inp["x"][b0:b1], O.PhiParams(*ws[:5]), O.GateParams(*ws[5:]),
+                    l=c["l"], d=c["d"], l_prime=c["l_prime"], n=c["n"], w=c["w"])
+    return torch.autograd.grad(r["out"], ws, inp["do"][b0:b1])
+
+
+def _worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nsa.sharding import allreduce_grads, batch_shard
+        c = CFG
+        inp = O.make_inputs(c["B"], c["H"], c["G"], c["T"], c["dk"], c["dv"], c["d_model"], c["l"], seed=5, l_prime=c["l_prime"])
+        b0, b1 = batch_shard(c["B"], world, rank)
+        summed = allreduce_grads(_weight_grads(inp, b0, b1))
+        if rank == 0:
+            full = _weight_grads(inp, 0, c["B"])
+            # index 4 is the second phi bias, whose true gradient is zero (softmax is shift invariant): skip it
+            ret["err"] = max(((a - b).abs().max() / (b.abs().max() + 1e-12)).item()
+                             for i, (a, b) in enumerate(zip(summed, full)) if i != 4)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_batch_shard_bounds():
+    from nsa.sharding import batch_shard
+    assert [batch_shard(8, 8, r) for r in range(8)] == [(r, r + 1) for r in range(8)]
+    assert [batch_shard(5, 2, r) for r in range(2)] == [(0, 3), (3, 5)]
+    assert batch_shard(1, 2, 1) == (1, 1)
+    with pytest.raises(ValueError):
+        batch_shard(4, 2, 2)
+
+
+def test_two_rank_weight_gradient_allreduce():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert ret["err"] < 1e-5
