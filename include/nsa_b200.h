@@ -87,6 +87,30 @@ NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void* v, const v
                     const int64_t* strides34, int B, int H, int G, int T, int dk, int dv, int window,
                     float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Sliding-window backward for callers that cannot allocate device memory.  (No counterpart in the reference
+ * project: its wrappers allocate freely through torch.)
+ * Some hosts of this library may not call cudaMalloc at the point where they need the backward pass: code
+ * running inside a CUDA-graph capture, a runtime that handed out all device memory up front, a real-time
+ * loop that must not touch the allocator.  This variant of nsa_sliding_bwd takes no workspace: its scratch
+ * (two floats per (batch, head, query) row) is a device array built into the library, 8 MiB that every GPU
+ * loading the library holds until the process exits.
+ *   - Tensors: bf16, the canonical contiguous layouts (q [B,H,T,dk], k [B,G,dk,T], v [B,G,T,dv], out/dout
+ *     [B,H,T,dv], L/M [B,H,T], dq like q, dkey [B,G,T,dk], dval [B,G,T,dv]), 16-byte aligned, shapes the
+ *     tensor-core kernels cover; anything else returns NSA_ERR_UNSUPPORTED (nsa_sliding_bwd serves it, and its
+ *     stride-generic kernels need no scratch anyway).
+ *   - Limit: B*H*T <= 1,048,576 rows; larger calls are rejected with NSA_ERR_UNSUPPORTED and a message.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, no
+ *     allocation); make that first call before any stream capture begins.
+ *   - No cudaMalloc, cudaFree or other allocating routine is called.  Nothing in the scratch needs clearing
+ *     between calls (each call overwrites the rows it reads).
+ *   - All calls on a device share the one array: two calls whose kernels may overlap on the GPU (different
+ *     streams, no dependency) race on it.  Serialise them.
+ * dkey/dval are added into (zero them first), dq is overwritten, as with nsa_sliding_bwd. */
+NSA_API int nsa_sliding_bwd_noalloc(const void* q, const void* k, const void* v, const void* out,
+                                    const void* dout, const float* L, const float* M, void* dq, void* dkey,
+                                    void* dval, int B, int H, int G, int T, int dk, int dv, int window,
+                                    float scale, void* stream);
+
 /* Attention over compressed tokens, block i visible iff block_ends[i] <= t; a row that sees no block
  * gets out = 0, L = M = -inf.  k_cmp is [B,G,dk,NB] with strides passed (z,g,n=block,k), v_cmp
  * [B,G,NB,dv]; dk_cmp is written [B,G,NB,dk].  Layout hint (forward): blocks_d > 0 asserts that

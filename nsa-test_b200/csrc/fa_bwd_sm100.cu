@@ -13,6 +13,8 @@
 //          (compressed branch, few key tiles): partial sums go to scratch and are added in head order.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "attn_args.cuh"
 #include "common.cuh"
 #include "fa_sm100.cuh"
@@ -622,4 +624,59 @@ int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, con
   return NSA_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Sliding-window backward for callers that cannot allocate device memory.
+//
+// The scratch of the sliding-window backward (per-row D = sum(O*dO) and logsumexp*log2e, two floats per
+// (batch, head, query) row) lives in the file-scope device array below instead of a caller-provided
+// workspace.  Every GPU that loads this library carries the array (8 MiB) until the process exits.
+// ------------------------------------------------------------------------------------------------
+constexpr int64_t kNoAllocMaxRows = 1 << 20;  // B*H*T rows the static scratch can hold
+static __device__ __align__(256) float g_sliding_bwd_scratch[2 * kNoAllocMaxRows];
+
+// In host code the array's name is only a stand-in; the device address has to be asked for, once per device,
+// while that device is current.  Cached per device ordinal.
+static int sliding_bwd_scratch_address(float** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static float* cached[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(NSA_ERR_LAUNCH, "sliding_bwd_noalloc: cannot identify the current device");
+  std::lock_guard<std::mutex> lk(mu);
+  if (!cached[dev]) {
+    float* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_sliding_bwd_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(NSA_ERR_LAUNCH, "sliding_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return NSA_OK;
+}
+
 }  // namespace nsa
+
+extern "C" NSA_API int nsa_sliding_bwd_noalloc(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                               const float* L, const float* M, void* dq, void* dkey, void* dval, int B, int H,
+                                               int G, int T, int dk, int dv, int window, float scale, void* stream) {
+  using namespace nsa;
+  NSA_REQUIRE(q && k && v && out && dout && L && M && dq && dkey && dval, "sliding_bwd_noalloc: null pointer");
+  NSA_REQUIRE(B > 0 && H > 0 && G > 0 && H % G == 0 && T > 0 && window > 0, "sliding_bwd_noalloc: bad sizes");
+  if (!fa_fwd_sm100_supported(H, G, T, T, dk, dv))
+    return fail(NSA_ERR_UNSUPPORTED,
+                "sliding_bwd_noalloc covers bf16 tensors with head dims (192,128), (128,128) or (64,64), an even number of heads per "
+                "group and T a multiple of 128; other shapes run through nsa_sliding_bwd, whose stride-generic kernels need no scratch");
+  const int64_t rows = (int64_t)B * H * T;
+  if (rows > kNoAllocMaxRows)
+    return fail(NSA_ERR_UNSUPPORTED, "sliding_bwd_noalloc: B*H*T = %lld rows exceed the built-in scratch of %lld rows; use "
+                "nsa_sliding_bwd with a caller-provided workspace", (long long)rows, (long long)kNoAllocMaxRows);
+  const uintptr_t all = (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out | (uintptr_t)dout | (uintptr_t)dq |
+                        (uintptr_t)dkey | (uintptr_t)dval;
+  NSA_REQUIRE((all & 15) == 0, "sliding_bwd_noalloc: tensors must be 16-byte aligned");
+  float* scratch = nullptr;
+  if (int rc = sliding_bwd_scratch_address(&scratch)) return rc;
+  // Nothing in the scratch has to start at zero: the preparation kernel overwrites every row this call reads.
+  return fa_bwd_sm100(q, k, v, out, dout, L, M, dq, dkey, dval, B, H, G, T, T, dk, dv, kWin, window, 0, 0, 0, scale, scratch,
+                      sizeof(float) * 2 * kNoAllocMaxRows, (cudaStream_t)stream);
+}

@@ -39,6 +39,7 @@ PROTOTYPES = {
     "nsa_sliding_fwd": (c_int, [_P] * 6 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P]),
     "nsa_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 8),
     "nsa_sliding_bwd": (c_int, [_P] * 10 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P, c_size_t, _P]),
+    "nsa_sliding_bwd_noalloc": (c_int, [_P] * 10 + [c_int] * 7 + [c_float, _P]),
     "nsa_cmp_attn_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 7 + [c_float, c_int, c_int, c_int, c_int, _P]),
     "nsa_cmp_attn_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 7 + [c_float, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "nsa_slc_fwd_workspace_bytes": (c_size_t, [c_int] * 10),
