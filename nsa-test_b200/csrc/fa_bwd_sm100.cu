@@ -214,14 +214,21 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         chi = vis - n0;
         clo = -0x40000000;
       }
+      if (clo < 0 && chi >= 127) {  // every key of the tile is visible to this row
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int col = c * 32 + e;
-          const float pr = (col > clo && col <= chi) ? exp2f(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -lse2)) : 0.f;
-          sv[c][e] = __float_as_uint(pr);
-        }
+          for (int e = 0; e < 32; ++e) sv[c][e] = __float_as_uint(ex2(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -lse2)));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int col = c * 32 + e;
+            const float pr = (col > clo && col <= chi) ? ex2(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -lse2)) : 0.f;
+            sv[c][e] = __float_as_uint(pr);
+          }
+      }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t dp0[32], dp1[32], pk[32];
@@ -438,6 +445,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         clo = key < p.cmp_nb ? key * p.cmp_d + p.cmp_l - 1 - tq0 : 0x40000000;
         chi = 0x40000000;
       }
+      const bool allvis = clo <= 0 && chi >= 63;  // this key sees all 64 queries of the sub-tile
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t sT[32], dpT[32], pk[16], dk_[16];
@@ -448,8 +456,8 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int e = 0; e < 16; ++e) {
           const int c0 = c * 32 + 2 * e;
           const float l0 = stat[c0], l1 = stat[c0 + 1], D0 = stat[64 + c0], D1 = stat[64 + c0 + 1];
-          const float p0 = (c0 >= clo && c0 <= chi) ? exp2f(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0)) : 0.f;
-          const float p1 = (c0 + 1 >= clo && c0 + 1 <= chi) ? exp2f(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1)) : 0.f;
+          const float p0 = (allvis || (c0 >= clo && c0 <= chi)) ? ex2(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0)) : 0.f;
+          const float p1 = (allvis || (c0 + 1 >= clo && c0 + 1 <= chi)) ? ex2(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1)) : 0.f;
           const float s0 = p0 * (__uint_as_float(dpT[2 * e]) - D0), s1 = p1 * (__uint_as_float(dpT[2 * e + 1]) - D1);
           __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1), y = __floats2bfloat162_rn(s0, s1);
           pk[e] = *reinterpret_cast<uint32_t*>(&x);

@@ -257,7 +257,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         ok = mbar_wait(&bar->pv_done[i], (j - 1) & 1, abort);  // O_i must hold PV(j-1) before it is scaled
         if (!ok) break;
         tc_fence_after();
-        const float f = need_o ? exp2f(m_ref - m_true) : 1.f;
+        const float f = need_o ? ex2(m_ref - m_true) : 1.f;
         l *= f;
 #pragma unroll
         for (int c = 0; c < DV / 32; ++c) {
@@ -279,8 +279,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const int cc = c * 2 + (e >> 4), ee = (e & 15) * 2;
-          const float p0 = exp2f(__uint_as_float(sv[cc][ee]) - mref_use);
-          const float p1 = exp2f(__uint_as_float(sv[cc][ee + 1]) - mref_use);
+          const float p0 = ex2(__uint_as_float(sv[cc][ee]) - mref_use);
+          const float p1 = ex2(__uint_as_float(sv[cc][ee + 1]) - mref_use);
           rs += p0 + p1;
           __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);  // .x (low half) = even key
           pk[e] = *reinterpret_cast<uint32_t*>(&v2);

@@ -192,9 +192,11 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       ok = mbar_wait(&bar->s_full[s], (step >> 1) & 1, abort);
       if (!ok) break;
       tc_fence_after();
+      const bool full = chi >= 127;  // every key of this tile is visible to this row: no per-element mask
       if (pass == 0) {
+        // raw logits into agg[], running maximum in scaled (log2) units
         const float m_old = st_m[hh * 128 + r];
-        float mx = m_old;
+        float raw_mx = -CUDART_INF_F;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t sv[32];
@@ -202,18 +204,22 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tc_wait_ld();
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            const float x = (c * 32 + e <= chi) ? __uint_as_float(sv[e]) * p.scale_log2 : -CUDART_INF_F;
+            const float x = (full || c * 32 + e <= chi) ? __uint_as_float(sv[e]) : -CUDART_INF_F;
             agg[c * 32 + e] = x;
-            mx = fmaxf(mx, x);
+            raw_mx = fmaxf(raw_mx, x);
           }
         }
         tc_fence_before();
         mbar_arrive(&bar->s_free[s]);
-        if (mx != -CUDART_INF_F) {
-          float sum = 0.f;
+        if (raw_mx != -CUDART_INF_F) {
+          const float mx = fmaxf(m_old, raw_mx * p.scale_log2);
+          float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-          for (int i = 0; i < 128; ++i) sum += exp2f(agg[i] - mx);
-          st_l[hh * 128 + r] = st_l[hh * 128 + r] * exp2f(m_old - mx) + sum;  // m_old = -inf -> factor 0
+          for (int i = 0; i < 128; i += 2) {
+            sum0 += ex2(fmaf(agg[i], p.scale_log2, -mx));
+            sum1 += ex2(fmaf(agg[i + 1], p.scale_log2, -mx));
+          }
+          st_l[hh * 128 + r] = st_l[hh * 128 + r] * ex2(m_old - mx) + (sum0 + sum1);  // m_old = -inf -> factor 0
           st_m[hh * 128 + r] = mx;
         }
       } else {
@@ -224,10 +230,13 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           uint32_t sv[32];
           tmem_ld32(tmem + lane_base + s * 128 + c * 32, sv);
           tc_wait_ld();
+          if (full) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float pr = (c * 32 + e <= chi) ? exp2f(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2)) : 0.f;
-            agg[c * 32 + e] += pr;
+            for (int e = 0; e < 32; ++e) agg[c * 32 + e] += ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              agg[c * 32 + e] += (c * 32 + e <= chi) ? ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2)) : 0.f;
           }
         }
         tc_fence_before();

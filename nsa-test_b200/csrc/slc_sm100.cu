@@ -113,10 +113,12 @@ __global__ void to_token_major_kernel(const __nv_bfloat16* __restrict__ in, __nv
 
 // One chunk = up to qpc queries; query qi fills rows [qi*hpg, (qi+1)*hpg) of the 128-row K-major swizzled tile.
 // Unused query slots are loaded from beyond the tensor (TMA fills zeros), so every chunk delivers the same byte count.
+// Called by a whole warp: lane qi fetches its query's inverse-index entry and issues that query's tile loads, so the
+// entry loads of a chunk are one coalesced request instead of a chain of dependent ones.
 template <int WIDTH>
 __device__ __forceinline__ void tma_gather_chunk(const CUtensorMap* tm, uint64_t* bar, uint8_t* dst, const int* entries, int cnt,
-                                                 int qpc, int hpg, int64_t bgT, int oob_row) {
-  for (int qi = 0; qi < qpc; ++qi) {
+                                                 int qpc, int hpg, int64_t bgT, int oob_row, int lane) {
+  for (int qi = lane; qi < qpc; qi += 32) {
     const int row = qi < cnt ? (int)((bgT + (entries[qi] & 0xFFFFFF)) * hpg) : oob_row;
 #pragma unroll
     for (int c = 0; c < WIDTH / 64; ++c) tma_load_2d(tm, bar, dst + c * 16384 + qi * hpg * 128, c * 64, row);
@@ -167,31 +169,34 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   if (!has_work) {
     // nothing to do for this CTA
   } else if (warp == 9) {
-    // ------------------------------------------------------------ producer: K/V blocks and gathered Q rows, all by TMA
-    if (lane == 0) {
+    // ------------------------------------------------------------ producer warp: K/V blocks and gathered Q rows, all by TMA
+    {
       ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
       const int oob_row = p.B * p.H * p.Tq;
       bool ok = true;
       int c = 0, kvidx = -1, last_blk = -1;
-      for (; !w.done() && ok; w.next(), ++c) {
-        if (w.blk != last_blk) {
-          last_blk = w.blk;
-          ++kvidx;
-          const int ks = kvidx & 1;
-          ok = mbar_wait(&bar->kv_empty[ks], ((kvidx >> 1) & 1) ^ 1, abort);
-          if (!ok) break;
-          mbar_arrive_expect_tx(&bar->kv_full[ks], SM::kK + SM::kV);
-          tma_load_2d(&tmK, &bar->kv_full[ks], sK + ks * SM::kK, w.blk * 64, (b * p.G + g) * DK);
-          for (int cc = 0; cc < DV / 64; ++cc)
-            tma_load_2d(&tmV, &bar->kv_full[ks], sV + ks * SM::kV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
-        }
+      for (; !w.done(); w.next(), ++c) {
         const int s = c % 3;
-        ok = mbar_wait(&bar->q_empty[s], ((c / 3) & 1) ^ 1, abort);
+        if (lane == 0) {
+          if (w.blk != last_blk) {
+            const int ks = (kvidx + 1) & 1;
+            ok = mbar_wait(&bar->kv_empty[ks], (((kvidx + 1) >> 1) & 1) ^ 1, abort);
+            if (ok) {
+              mbar_arrive_expect_tx(&bar->kv_full[ks], SM::kK + SM::kV);
+              tma_load_2d(&tmK, &bar->kv_full[ks], sK + ks * SM::kK, w.blk * 64, (b * p.G + g) * DK);
+              for (int cc = 0; cc < DV / 64; ++cc)
+                tma_load_2d(&tmV, &bar->kv_full[ks], sV + ks * SM::kV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
+            }
+          }
+          if (ok) ok = mbar_wait(&bar->q_empty[s], ((c / 3) & 1) ^ 1, abort);
+          if (ok) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ);
+        }
+        if (w.blk != last_blk) { last_blk = w.blk; ++kvidx; }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
-        mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ);
-        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], sQ + s * SM::kQ, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row);
+        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], sQ + s * SM::kQ, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row, lane);
       }
-      if (!ok) {  // let copies in flight land before the CTA gives its shared memory back
+      if (!ok && lane == 0) {  // let copies in flight land before the CTA gives its shared memory back
         if (kvidx >= 0) mbar_wait(&bar->kv_full[kvidx & 1], (kvidx >> 1) & 1, abort);
         for (int cc = max(0, c - 3); cc < c; ++cc) mbar_wait(&bar->q_full[cc % 3], (cc / 3) & 1, abort);
       }
@@ -303,7 +308,7 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
         const int cc = e >> 4, ee = (e & 15) * 2;
-        const float p0 = exp2f(__uint_as_float(sv[cc][ee]) - mx), p1 = exp2f(__uint_as_float(sv[cc][ee + 1]) - mx);
+        const float p0 = ex2(__uint_as_float(sv[cc][ee]) - mx), p1 = ex2(__uint_as_float(sv[cc][ee + 1]) - mx);
         l += p0 + p1;
         __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);
         pk[e] = *reinterpret_cast<uint32_t*>(&v2);
@@ -371,7 +376,7 @@ __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part,
   if (mine) st = st_part[base + (int64_t)lane * hpg];
   const unsigned validmask = __ballot_sync(0xffffffffu, mine);
   const float mx = warp_max(st.x);
-  const float wmine = mine ? st.y * exp2f(st.x - mx) : 0.f;
+  const float wmine = mine ? st.y * ex2(st.x - mx) : 0.f;
   float lsum = 0.f, acc[VPL];
 #pragma unroll
   for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
@@ -460,31 +465,34 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
   if (!has_work) {
   } else if (warp == 9) {
-    if (lane == 0) {
+    {
       ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
       const int oob_row = p.B * p.H * p.Tq;
       bool ok = true;
       int c = 0, kvidx = -1, last_blk = -1;
-      for (; !w.done() && ok; w.next(), ++c) {
-        if (w.blk != last_blk) {
-          last_blk = w.blk;
-          ++kvidx;
-          ok = mbar_wait(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
-          if (!ok) break;
-          mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
-          tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
-          for (int cc = 0; cc < DV / 64; ++cc)
-            tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
-        }
+      for (; !w.done(); w.next(), ++c) {
         const int s = c & 1;
-        ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
+        if (lane == 0) {
+          if (w.blk != last_blk) {
+            ok = mbar_wait(&bar->kv_empty, ((kvidx + 1) & 1) ^ 1, abort);
+            if (ok) {
+              mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
+              tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
+              for (int cc = 0; cc < DV / 64; ++cc)
+                tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
+            }
+          }
+          if (ok) ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
+          if (ok) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
+        }
+        if (w.blk != last_blk) { last_blk = w.blk; ++kvidx; }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
-        mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
-        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], sSt + s * SM::kStage, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row);
+        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], sSt + s * SM::kStage, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row, lane);
         tma_gather_chunk<DV>(&tmdOt, &bar->q_full[s], sSt + s * SM::kStage + SM::kQ, ent + w.e, w.count(), qpc, p.hpg,
-                             (int64_t)bg * p.Tq, oob_row);
+                             (int64_t)bg * p.Tq, oob_row, lane);
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
         for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
       }
@@ -573,8 +581,8 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const int c0 = cc * 32 + 2 * e;
-          const float p0 = c0 <= chi ? exp2f(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse2)) : 0.f;
-          const float p1 = c0 + 1 <= chi ? exp2f(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse2)) : 0.f;
+          const float p0 = c0 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse2)) : 0.f;
+          const float p1 = c0 + 1 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse2)) : 0.f;
           __nv_bfloat162 x = __floats2bfloat162_rn(p0 * (__uint_as_float(dp[2 * e]) - Dr), p1 * (__uint_as_float(dp[2 * e + 1]) - Dr));
           pk[cc * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
         }
@@ -740,11 +748,10 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       uint8_t* st = sSt + s * SM::kStage;
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
-        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], st, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row);
-        tma_gather_chunk<DV>(&tmdOt, &bar->q_full[s], st + SM::kQ, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row);
-      }
+      if (lane == 0) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
+      __syncwarp();
+      tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], st, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row, lane);
+      tma_gather_chunk<DV>(&tmdOt, &bar->q_full[s], st + SM::kQ, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row, lane);
       float* stat = reinterpret_cast<float*>(st + SM::kQ + SM::kdO);
       for (int rr = lane; rr < 128; rr += 32) {
         const int qi = rr / p.hpg, hh = rr % p.hpg;
@@ -877,8 +884,8 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             const int j0 = hf * 64 + cc * 32 + 2 * e;  // row of the gathered tile = column here
             const float l0 = stat[j0], l1 = stat[j0 + 1], D0 = stat[128 + j0], D1 = stat[128 + j0 + 1];
             const int t0 = tcol[j0], t1 = tcol[j0 + 1];
-            const float p0 = key <= t0 ? exp2f(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0)) : 0.f;
-            const float p1 = key <= t1 ? exp2f(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1)) : 0.f;
+            const float p0 = key <= t0 ? ex2(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0)) : 0.f;
+            const float p1 = key <= t1 ? ex2(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1)) : 0.f;
             __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1);
             __nv_bfloat162 y = __floats2bfloat162_rn(p0 * (__uint_as_float(dpT[2 * e]) - D0), p1 * (__uint_as_float(dpT[2 * e + 1]) - D1));
             pk[e] = *reinterpret_cast<uint32_t*>(&x);

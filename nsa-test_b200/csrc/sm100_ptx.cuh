@@ -127,6 +127,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
+// 2^x on the special-function unit (max relative error 2^-22; -inf -> +0)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor, 128-byte swizzle.  K-major operand: rows of 128 B, 8-row groups
 // `sbo` bytes apart (lbo unused, encoded as 16 B).  MN-major operand: 64-element (128 B) runs along
