@@ -68,7 +68,7 @@ void launch_bwd_prep(const void* o, const void* dout, const float* L, const floa
 }
 
 // ------------------------------------------------------------------------------------------------
-// dQ kernel: 128 queries of one head per CTA; warps 0-3 compute, warp 4 TMA, warp 5 UMMA
+// dQ kernel: 128 queries of one head per CTA
 // ------------------------------------------------------------------------------------------------
 template <int DK, int DV>
 struct DqSmem {
@@ -77,13 +77,16 @@ struct DqSmem {
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct DqBarriers {
-  uint64_t qdo_full, k_full[2], k_empty[2], v_full, v_empty, sdp_full, ds_full, dq_done;
+  uint64_t qdo_full, k_full[2], k_empty[2], v_full, v_empty, sdp_full, sdp_free, ds_full, ds_free, dq_done;
   uint32_t tmem_base;
   int abort;
 };
 
+// warps 0-3 / 4-7: compute, key columns [0,64) / [64,128) of every tile (same query rows); warp 8 TMA; warp 9 UMMA.
+// TMEM: S [0,128) dP [128,256) dQ [256,256+DK) dS (bf16) [256+DK, 320+DK): S/dP of tile j+1 are produced while the
+// compute warps turn tile j into dS, and dQ += dS K of tile j runs while they work on tile j+1.
 template <int DK, int DV, int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __maxnreg__(200)
 fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FaBwdParams p) {
   using SM = DqSmem<DK, DV>;
@@ -113,20 +116,22 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(&bar->v_full, 1);
     mbar_init(&bar->v_empty, 1);
     mbar_init(&bar->sdp_full, 1);
-    mbar_init(&bar->ds_full, 128);
+    mbar_init(&bar->sdp_free, 256);
+    mbar_init(&bar->ds_full, 256);
+    mbar_init(&bar->ds_free, 1);
     mbar_init(&bar->dq_done, 1);
     bar->abort = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 5) tmem_alloc(&bar->tmem_base, 512);
+  if (warp == 9) tmem_alloc(&bar->tmem_base, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
-  constexpr uint32_t cS = 0, cdP = 128, cdQ = 256;
+  constexpr uint32_t cS = 0, cdP = 128, cdQ = 256, cdS = 256 + DK;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0 && ntiles > 0) {
       mbar_arrive_expect_tx(&bar->qdo_full, SM::kQ + SM::kdO);
       const int qrow = (b * p.H + h) * p.Tq + m0;
@@ -154,7 +159,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (issued > 0) mbar_wait(&bar->v_full, (issued - 1) & 1, abort);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0 && ntiles > 0) {
       constexpr uint32_t idS = idesc_bf16(128, 128, 0, 1);    // Q (K-major) x K tile (MN-major: keys contiguous)
       constexpr uint32_t iddP = idesc_bf16(128, 128, 0, 0);   // dO (K-major) x V tile (K-major: dv contiguous)
@@ -162,13 +167,11 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint64_t dQd = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t ddO = smem_desc_sw128(smem_u32(sdO), 16, 1024);
       const uint64_t dVd = smem_desc_sw128(smem_u32(sV), 16, 1024);
-      bool ok = mbar_wait(&bar->qdo_full, 0, abort);
-      for (int j = 0; j < ntiles && ok; ++j) {
+      auto issue_sdp = [&](int j) -> bool {
         const int ks = j & 1;
         const uint64_t dK_mn = smem_desc_sw128(smem_u32(sK + ks * SM::kK), DK * 128, 1024);
-        const uint64_t dK_k = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);
-        ok = mbar_wait(&bar->k_full[ks], (j >> 1) & 1, abort) && mbar_wait(&bar->v_full, j & 1, abort);
-        if (!ok) break;
+        if (!(mbar_wait(&bar->k_full[ks], (j >> 1) & 1, abort) && mbar_wait(&bar->v_full, j & 1, abort))) return false;
+        if (j > 0 && !mbar_wait(&bar->sdp_free, (j - 1) & 1, abort)) return false;  // S/dP of tile j-1 are in registers
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
@@ -179,32 +182,46 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                   desc_advance(dVd, (kk >> 2) * 16384 + (kk & 3) * 32), iddP, kk > 0);
         umma_commit(&bar->sdp_full);
         umma_commit(&bar->v_empty);
+        return true;
+      };
+      bool ok = mbar_wait(&bar->qdo_full, 0, abort) && issue_sdp(0);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int ks = j & 1;
+        const uint64_t dK_k = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);
+        if (j + 1 < ntiles) ok = issue_sdp(j + 1);
+        if (!ok) break;
         ok = mbar_wait(&bar->ds_full, j & 1, abort);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tmem + cdQ, tmem + cS + kk * 8, desc_advance(dK_k, (kk >> 2) * (DK * 128) + (kk & 3) * 32), iddQ,
+          umma_ts(tmem + cdQ, tmem + cdS + kk * 8, desc_advance(dK_k, (kk >> 2) * (DK * 128) + (kk & 3) * 32), iddQ,
                   (j > 0) || (kk > 0));
         umma_commit(&bar->k_empty[ks]);
+        umma_commit(&bar->ds_free);
       }
       if (ok) umma_commit(&bar->dq_done);
     }
   } else {
-    const int r = warp * 32 + lane, t = m0 + r;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const int gsel = warp >> 2;                 // which half of the key columns this thread handles
+    const int r = (warp & 3) * 32 + lane, t = m0 + r;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int64_t row = ((int64_t)b * p.H + h) * p.Tq + t;
     const float lse2 = p.lse2[row], Dr = p.D[row];
     bool ok = true;
-    uint32_t sv[4][32];
     for (int j = 0; j < ntiles && ok; ++j) {
-      const int n0 = (jlo + j) * 128;
+      const int n0 = (jlo + j) * 128 + gsel * 64;   // first key of this thread's columns
       ok = mbar_wait(&bar->sdp_full, j & 1, abort);
       if (!ok) break;
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + cS + c * 32, sv[c]);
+      uint32_t sv[2][32], dp[2][32], pk[32];
+      tmem_ld32(tmem + lane_base + cS + gsel * 64, sv[0]);
+      tmem_ld32(tmem + lane_base + cS + gsel * 64 + 32, sv[1]);
+      tmem_ld32(tmem + lane_base + cdP + gsel * 64, dp[0]);
+      tmem_ld32(tmem + lane_base + cdP + gsel * 64 + 32, dp[1]);
       tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&bar->sdp_free);
       int clo, chi;
       if (MODE == kWin) {
         chi = t - n0;
@@ -214,39 +231,27 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         chi = vis - n0;
         clo = -0x40000000;
       }
-      if (clo < 0 && chi >= 127) {  // every key of the tile is visible to this row
+      const bool allvis = clo < 0 && chi >= 63;
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e) sv[c][e] = __float_as_uint(ex2(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -lse2)));
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = c * 32 + e;
-            const float pr = (col > clo && col <= chi) ? ex2(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -lse2)) : 0.f;
-            sv[c][e] = __float_as_uint(pr);
-          }
-      }
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t dp0[32], dp1[32], pk[32];
-        tmem_ld32(tmem + lane_base + cdP + c * 64, dp0);
-        tmem_ld32(tmem + lane_base + cdP + c * 64 + 32, dp1);
-        tc_wait_ld();
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float a0 = __uint_as_float(sv[c * 2][2 * e]) * (__uint_as_float(dp0[2 * e]) - Dr);
-          const float a1 = __uint_as_float(sv[c * 2][2 * e + 1]) * (__uint_as_float(dp0[2 * e + 1]) - Dr);
-          const float b0 = __uint_as_float(sv[c * 2 + 1][2 * e]) * (__uint_as_float(dp1[2 * e]) - Dr);
-          const float b1 = __uint_as_float(sv[c * 2 + 1][2 * e + 1]) * (__uint_as_float(dp1[2 * e + 1]) - Dr);
-          __nv_bfloat162 x = __floats2bfloat162_rn(a0, a1), y = __floats2bfloat162_rn(b0, b1);
-          pk[e] = *reinterpret_cast<uint32_t*>(&x);
-          pk[16 + e] = *reinterpret_cast<uint32_t*>(&y);
+          const int c0 = c * 32 + 2 * e;
+          float p0 = ex2(fmaf(__uint_as_float(sv[c][2 * e]), p.scale_log2, -lse2));
+          float p1 = ex2(fmaf(__uint_as_float(sv[c][2 * e + 1]), p.scale_log2, -lse2));
+          if (!allvis) {
+            p0 = (c0 > clo && c0 <= chi) ? p0 : 0.f;
+            p1 = (c0 + 1 > clo && c0 + 1 <= chi) ? p1 : 0.f;
+          }
+          __nv_bfloat162 x = __floats2bfloat162_rn(p0 * (__uint_as_float(dp[c][2 * e]) - Dr), p1 * (__uint_as_float(dp[c][2 * e + 1]) - Dr));
+          pk[c * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
         }
-        tmem_st32(tmem + lane_base + cS + c * 32, pk);
+      if (j > 0) {  // dS of the previous tile must have been consumed by its dQ MMAs
+        ok = mbar_wait(&bar->ds_free, (j - 1) & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
       }
+      tmem_st32(tmem + lane_base + cdS + gsel * 32, pk);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bar->ds_full);
@@ -254,12 +259,12 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok && ntiles > 0) ok = mbar_wait(&bar->dq_done, 0, abort);
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* dst = p.dq + row * DK;
+      __nv_bfloat16* dst = p.dq + row * DK + gsel * (DK / 2);
 #pragma unroll
-      for (int c = 0; c < DK / 32; ++c) {
+      for (int c = 0; c < DK / 64; ++c) {
         uint32_t ov[32];
         if (ntiles > 0) {
-          tmem_ld32(tmem + lane_base + cdQ + c * 32, ov);
+          tmem_ld32(tmem + lane_base + cdQ + gsel * (DK / 2) + c * 32, ov);
           tc_wait_ld();
         } else {
 #pragma unroll
@@ -282,7 +287,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -300,7 +305,7 @@ struct DkvSmem {
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct DkvBarriers {
-  uint64_t kv_full, full[3], empty[3], stp_full, pds_full, acc_done;
+  uint64_t kv_full, full[3], empty[3], stp_full, st_free, pds_full, pds_free, acc_done;
   uint32_t tmem_base;
   int abort;
 };
@@ -339,7 +344,9 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(&bar->kv_full, 1);
     for (int i = 0; i < 3; ++i) { mbar_init(&bar->full[i], 2); mbar_init(&bar->empty[i], 1); }
     mbar_init(&bar->stp_full, 1);
+    mbar_init(&bar->st_free, 128);
     mbar_init(&bar->pds_full, 128);
+    mbar_init(&bar->pds_free, 1);
     mbar_init(&bar->acc_done, 1);
     bar->abort = 0;
     fence_barrier_init();
@@ -350,7 +357,9 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
-  constexpr uint32_t cdK = 0, cdV = DK, cST = DK + DV, cdPT = DK + DV + 64;
+  // fp32 S^T / dP^T tiles and their bf16 successors P^T / dS^T have separate columns, so the next tile's
+  // S^T / dP^T can be produced while this tile's P^T / dS^T are still being consumed
+  constexpr uint32_t cdK = 0, cdV = DK, cST = DK + DV, cdPT = DK + DV + 64, cP = DK + DV + 128, cdS = DK + DV + 160;
 
   if (warp == 4) {
     // producer: the whole warp takes part (lanes fill the per-query statistics), lane 0 drives TMA
@@ -396,14 +405,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       constexpr uint32_t iddK = idesc_bf16(128, DK, 0, 1);    // dS^T (TMEM) x Q sub-tile (MN-major: dk contiguous)
       const uint64_t dKa = smem_desc_sw128(smem_u32(sK), DK * 128, 1024);
       const uint64_t dVa = smem_desc_sw128(smem_u32(sV), 16, 1024);
-      bool ok = mbar_wait(&bar->kv_full, 0, abort);
-      for (int it = 0; it < n_it && ok; ++it) {
+      auto issue_st = [&](int it) -> bool {   // S^T = K Q^T and dP^T = V dO^T of iteration `it`
         const int s = it % 3;
         const uint32_t st = smem_u32(sSt + s * SM::kStage);
-        const uint64_t dQk = smem_desc_sw128(st, 16, 1024), dQmn = smem_desc_sw128(st, 8192, 1024);
-        const uint64_t dOk = smem_desc_sw128(st + SM::kQs, 16, 1024), dOmn = smem_desc_sw128(st + SM::kQs, 8192, 1024);
-        ok = mbar_wait(&bar->full[s], (it / 3) & 1, abort);
-        if (!ok) break;
+        const uint64_t dQk = smem_desc_sw128(st, 16, 1024), dOk = smem_desc_sw128(st + SM::kQs, 16, 1024);
+        if (!mbar_wait(&bar->full[s], (it / 3) & 1, abort)) return false;
+        if (it > 0 && !mbar_wait(&bar->st_free, (it - 1) & 1, abort)) return false;  // fp32 tiles of it-1 are in registers
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
@@ -413,16 +420,26 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           umma_ss(tmem + cdPT, desc_advance(dVa, (kk >> 2) * 16384 + (kk & 3) * 32),
                   desc_advance(dOk, (kk >> 2) * 8192 + (kk & 3) * 32), iddPT, kk > 0);
         umma_commit(&bar->stp_full);
+        return true;
+      };
+      bool ok = mbar_wait(&bar->kv_full, 0, abort) && issue_st(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it % 3;
+        const uint32_t st = smem_u32(sSt + s * SM::kStage);
+        const uint64_t dQmn = smem_desc_sw128(st, 8192, 1024), dOmn = smem_desc_sw128(st + SM::kQs, 8192, 1024);
+        if (it + 1 < n_it) ok = issue_st(it + 1);   // runs on the tensor pipe while the compute warps work on `it`
+        if (!ok) break;
         ok = mbar_wait(&bar->pds_full, it & 1, abort);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem + cdV, tmem + cST + kk * 8, desc_advance(dOmn, kk * 2048), iddV, (it > 0) || (kk > 0));
+          umma_ts(tmem + cdV, tmem + cP + kk * 8, desc_advance(dOmn, kk * 2048), iddV, (it > 0) || (kk > 0));
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem + cdK, tmem + cdPT + kk * 8, desc_advance(dQmn, kk * 2048), iddK, (it > 0) || (kk > 0));
+          umma_ts(tmem + cdK, tmem + cdS + kk * 8, desc_advance(dQmn, kk * 2048), iddK, (it > 0) || (kk > 0));
         umma_commit(&bar->empty[s]);
+        umma_commit(&bar->pds_free);
       }
       if (ok) umma_commit(&bar->acc_done);
     }
@@ -446,33 +463,40 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         chi = 0x40000000;
       }
       const bool allvis = clo <= 0 && chi >= 63;  // this key sees all 64 queries of the sub-tile
+      uint32_t sT[2][32], dpT[2][32];
+      tmem_ld32(tmem + lane_base + cST, sT[0]);
+      tmem_ld32(tmem + lane_base + cST + 32, sT[1]);
+      tmem_ld32(tmem + lane_base + cdPT, dpT[0]);
+      tmem_ld32(tmem + lane_base + cdPT + 32, dpT[1]);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&bar->st_free);   // the fp32 tiles may be overwritten by the next iteration's MMAs
+      uint32_t pk[32], dk_[32];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sT[32], dpT[32], pk[16], dk_[16];
-        tmem_ld32(tmem + lane_base + cST + c * 32, sT);
-        tmem_ld32(tmem + lane_base + cdPT + c * 32, dpT);
-        tc_wait_ld();
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const int c0 = c * 32 + 2 * e;
           const float l0 = stat[c0], l1 = stat[c0 + 1], D0 = stat[64 + c0], D1 = stat[64 + c0 + 1];
-          const float p0 = (allvis || (c0 >= clo && c0 <= chi)) ? ex2(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0)) : 0.f;
-          const float p1 = (allvis || (c0 + 1 >= clo && c0 + 1 <= chi)) ? ex2(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1)) : 0.f;
-          const float s0 = p0 * (__uint_as_float(dpT[2 * e]) - D0), s1 = p1 * (__uint_as_float(dpT[2 * e + 1]) - D1);
+          float p0 = ex2(fmaf(__uint_as_float(sT[c][2 * e]), p.scale_log2, -l0));
+          float p1 = ex2(fmaf(__uint_as_float(sT[c][2 * e + 1]), p.scale_log2, -l1));
+          if (!allvis) {
+            p0 = (c0 >= clo && c0 <= chi) ? p0 : 0.f;
+            p1 = (c0 + 1 >= clo && c0 + 1 <= chi) ? p1 : 0.f;
+          }
+          const float s0 = p0 * (__uint_as_float(dpT[c][2 * e]) - D0), s1 = p1 * (__uint_as_float(dpT[c][2 * e + 1]) - D1);
           __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1), y = __floats2bfloat162_rn(s0, s1);
-          pk[e] = *reinterpret_cast<uint32_t*>(&x);
-          dk_[e] = *reinterpret_cast<uint32_t*>(&y);
+          pk[c * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
+          dk_[c * 16 + e] = *reinterpret_cast<uint32_t*>(&y);
         }
-        // 16 packed columns each: P^T over S^T, dS^T over dP^T (the fp32 values were consumed above)
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::
-                     "r"(tmem + lane_base + cST + c * 16), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
-                     "r"(pk[6]), "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]),
-                     "r"(pk[15]) : "memory");
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::
-                     "r"(tmem + lane_base + cdPT + c * 16), "r"(dk_[0]), "r"(dk_[1]), "r"(dk_[2]), "r"(dk_[3]), "r"(dk_[4]),
-                     "r"(dk_[5]), "r"(dk_[6]), "r"(dk_[7]), "r"(dk_[8]), "r"(dk_[9]), "r"(dk_[10]), "r"(dk_[11]), "r"(dk_[12]),
-                     "r"(dk_[13]), "r"(dk_[14]), "r"(dk_[15]) : "memory");
+      // P^T / dS^T of the previous iteration must have been consumed before they are overwritten
+      if (it > 0) {
+        ok = mbar_wait(&bar->pds_free, (it - 1) & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
       }
+      tmem_st32(tmem + lane_base + cP, pk);
+      tmem_st32(tmem + lane_base + cdS, dk_);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bar->pds_full);
@@ -568,7 +592,7 @@ static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, con
     return fail(NSA_ERR_LAUNCH, "fa_bwd: cannot reserve shared memory");
   {
     KernelTimer kt(MODE == kWin ? "fa_bwd_dq_win" : "fa_bwd_dq_cmp", st);
-    kq<<<dim3(p.Tq / 128, p.B * p.H), 192, DqSmem<DK, DV>::kDynamic, st>>>(tq128, tdo128, tk, tv, p);
+    kq<<<dim3(p.Tq / 128, p.B * p.H), 320, DqSmem<DK, DV>::kDynamic, st>>>(tq128, tdo128, tk, tv, p);
   }
   if (int rc = check_launch("fa_bwd_dq_sm100")) return rc;
   KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);

@@ -70,6 +70,79 @@ __global__ void gate_mix_bwd_kernel(const float* __restrict__ gates, const T* __
   }
 }
 
+// bf16, dv a multiple of 128: each lane owns 4 consecutive values (8-byte accesses, 256 B per warp and row segment)
+__device__ __forceinline__ void unpack4(const uint2 r, float (&f)[4]) {
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ uint2 pack4(const float (&f)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  return make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+
+__global__ void gate_mix_fwd_bf16x4_kernel(const float* __restrict__ logits, const __nv_bfloat16* __restrict__ oc,
+                                           const __nv_bfloat16* __restrict__ os, const __nv_bfloat16* __restrict__ ow,
+                                           __nv_bfloat16* __restrict__ out, float* __restrict__ gates, int B, int H, int T_, int dv,
+                                           int mode) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)B * H * T_) return;
+  const int t = row % T_, h = (row / T_) % H, b = row / ((int64_t)T_ * H);
+  float g[3];
+  gates3(logits + ((int64_t)b * T_ + t) * 3 * H + 3 * h, mode, g);
+  if (lane < 3) gates[row * 3 + lane] = g[lane];
+  const int64_t base = row * dv;
+  for (int c = lane * 4; c < dv; c += 128) {
+    float a[4], s_[4], w[4], y[4];
+    unpack4(*reinterpret_cast<const uint2*>(oc + base + c), a);
+    unpack4(*reinterpret_cast<const uint2*>(os + base + c), s_);
+    unpack4(*reinterpret_cast<const uint2*>(ow + base + c), w);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) y[i] = (a[i] * g[0] + s_[i] * g[1]) + w[i] * g[2];
+    *reinterpret_cast<uint2*>(out + base + c) = pack4(y);
+  }
+}
+
+__global__ void gate_mix_bwd_bf16x4_kernel(const float* __restrict__ gates, const __nv_bfloat16* __restrict__ oc,
+                                           const __nv_bfloat16* __restrict__ os, const __nv_bfloat16* __restrict__ ow,
+                                           const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ doc,
+                                           __nv_bfloat16* __restrict__ dos, __nv_bfloat16* __restrict__ dow, float* __restrict__ dlogits,
+                                           int B, int H, int T_, int dv, int mode) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)B * H * T_) return;
+  const int t = row % T_, h = (row / T_) % H, b = row / ((int64_t)T_ * H);
+  const float g0 = gates[row * 3], g1 = gates[row * 3 + 1], g2 = gates[row * 3 + 2];
+  const int64_t base = row * dv;
+  float d0 = 0.f, d1 = 0.f, d2 = 0.f;
+  for (int c = lane * 4; c < dv; c += 128) {
+    float dy[4], a[4], s_[4], w[4], r0[4], r1[4], r2[4];
+    unpack4(*reinterpret_cast<const uint2*>(dout + base + c), dy);
+    unpack4(*reinterpret_cast<const uint2*>(oc + base + c), a);
+    unpack4(*reinterpret_cast<const uint2*>(os + base + c), s_);
+    unpack4(*reinterpret_cast<const uint2*>(ow + base + c), w);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      d0 = fmaf(dy[i], a[i], d0); d1 = fmaf(dy[i], s_[i], d1); d2 = fmaf(dy[i], w[i], d2);
+      r0[i] = dy[i] * g0; r1[i] = dy[i] * g1; r2[i] = dy[i] * g2;
+    }
+    *reinterpret_cast<uint2*>(doc + base + c) = pack4(r0);
+    *reinterpret_cast<uint2*>(dos + base + c) = pack4(r1);
+    *reinterpret_cast<uint2*>(dow + base + c) = pack4(r2);
+  }
+  d0 = warp_sum(d0); d1 = warp_sum(d1); d2 = warp_sum(d2);
+  if (lane == 0) {
+    float* dl = dlogits + ((int64_t)b * T_ + t) * 3 * H + 3 * h;
+    if (mode == NSA_GATE_SOFTMAX) {
+      const float dot = g0 * d0 + g1 * d1 + g2 * d2;
+      dl[0] = g0 * (d0 - dot); dl[1] = g1 * (d1 - dot); dl[2] = g2 * (d2 - dot);
+    } else {
+      dl[0] = d0 * g0 * (1.f - g0); dl[1] = d1 * g1 * (1.f - g1); dl[2] = d2 * g2 * (1.f - g2);
+    }
+  }
+}
+
 }  // namespace nsa
 
 using namespace nsa;
@@ -86,6 +159,9 @@ extern "C" NSA_API int nsa_gate_mix_fwd(const float* logits, const void* o_cmp, 
   if (dtype == NSA_F32)
     gate_mix_fwd_kernel<float><<<grid, 256, 0, st>>>(logits, (const float*)o_cmp, (const float*)o_slc, (const float*)o_win,
                                                       (float*)out, gates_out, B, H, T, dv, gate_mode);
+  else if (dtype == NSA_BF16 && dv % 128 == 0)
+    gate_mix_fwd_bf16x4_kernel<<<grid, 256, 0, st>>>(logits, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc,
+                                                     (const __nv_bfloat16*)o_win, (__nv_bfloat16*)out, gates_out, B, H, T, dv, gate_mode);
   else if (dtype == NSA_BF16)
     gate_mix_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(logits, (const __nv_bfloat16*)o_cmp,
                                                               (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win,
@@ -108,6 +184,10 @@ extern "C" NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, c
     gate_mix_bwd_kernel<float><<<grid, 256, 0, st>>>(gates, (const float*)o_cmp, (const float*)o_slc, (const float*)o_win,
                                                       (const float*)dout, (float*)do_cmp, (float*)do_slc, (float*)do_win,
                                                       dlogits, B, H, T, dv, gate_mode);
+  else if (dtype == NSA_BF16 && dv % 128 == 0)
+    gate_mix_bwd_bf16x4_kernel<<<grid, 256, 0, st>>>(gates, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc,
+                                                     (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)dout, (__nv_bfloat16*)do_cmp,
+                                                     (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, dlogits, B, H, T, dv, gate_mode);
   else if (dtype == NSA_BF16)
     gate_mix_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
         gates, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win,

@@ -7,7 +7,8 @@
 // accumulated in fp32 by the tensor core (16 mantissa bits of K, exact bf16 Q).
 // One CTA owns 128 queries of one KV group and makes two passes over (key tile, head):
 //   pass A  online (max, sum) of every (query, head) row -> logsumexp
-//   pass B  p = exp2(x - lse); per-key sums over the heads of the group (head order, fp32, registers);
+//   pass B  p = exp2(x - lse); per-key sums over the heads of the group (fp32, registers; two compute warpgroups
+//           take the even and the odd heads and their sums are added once per key tile);
 //           after the last head the l/d x l'/d stencil maps 128 keys to 128/(l'/d) selection blocks,
 //           which stream into a per-query sorted top-n list (score descending, ties to the lower id).
 // Then the forced blocks are merged in, repeats dropped, the list cut to n and padded with -1.
@@ -43,7 +44,7 @@ __global__ void split_hi_lo_kernel(const float* __restrict__ x, __nv_bfloat16* _
 }
 
 struct ScoreBarriers {
-  uint64_t k_full, k_empty, q_full[2], q_empty[2], s_full[2], s_free[2];
+  uint64_t k_full, k_empty, q_full[2], q_empty[2], s_full[2], s_free[2], xchg_full, xchg_free;
   uint32_t tmem_base;
   int abort;
 };
@@ -67,7 +68,7 @@ __device__ __noinline__ void topn_insert(float* lst_s, int* lst_i, int r, int& c
 }
 
 template <int DK>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(384, 1)
 score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKhi,
                      const __grid_constant__ CUtensorMap tmKlo, const ScoreParams p, int hpg, int smem_state_off,
                      int smem_list_off, int smem_bar_off) {
@@ -99,17 +100,24 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(&bar->s_full[i], 1);
       mbar_init(&bar->s_free[i], 128);
     }
+    mbar_init(&bar->xchg_full, 128);
+    mbar_init(&bar->xchg_free, 128);
     bar->abort = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 5) tmem_alloc(&bar->tmem_base, 256);
+  if (warp == 9) tmem_alloc(&bar->tmem_base, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
+  // three warpgroups: 0 and 1 compute (even / odd steps), 2 holds the TMA and UMMA warps.  The compute groups need
+  // far more registers than the launch-time split gives them, the third group far fewer.
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
 
-  if (warp == 4) {
+  if (warp >= 10) {
+    // idle half of the third warpgroup
+  } else if (warp == 8) {
     if (lane == 0) {
       bool ok = true;
       int kissued = 0, qissued = 0;
@@ -139,7 +147,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int st = max(0, qissued - 2); st < qissued; ++st) mbar_wait(&bar->q_full[st & 1], (st >> 1) & 1, abort);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       constexpr uint32_t idS = idesc_bf16(128, 128, 0, 1);
       const uint64_t dKhi = smem_desc_sw128(smem_u32(sKhi), DK * 128, 1024);
@@ -164,15 +172,20 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     }
   } else {
-    const int r = warp * 32 + lane, t = m0 + r;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // Group 0 takes the even steps (even heads), group 1 the odd ones; each sums the probabilities of its heads.
+    // After its last head of a key tile group 1 parks its sums in TMEM columns [256,384); group 0 adds them to its
+    // own, applies the stencil and feeds the top-n list, while group 1 is already on the next tile.
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int wg = warp >> 2;
+    const int r = (warp & 3) * 32 + lane, t = m0 + r;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int vis = t >= p.l - 1 ? min(p.nb - 1, (t - p.l + 1) / p.d) : -1;  // last visible compressed block
     const int a_ = p.l / p.d, s_ = p.lprime / p.d;                          // a_ == 2 on this path
     const int per_tile = 128 / s_;
     const int n_sel = (p.nbp + s_ - 1) / s_;
     const int k_actual = min(p.n, n_sel);
     bool ok = true;
-    for (int hh = 0; hh < hpg; ++hh) {
+    for (int hh = wg; hh < hpg; hh += 2) {
       st_m[hh * 128 + r] = -CUDART_INF_F;
       st_l[hh * 128 + r] = 0.f;
     }
@@ -183,9 +196,10 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     (void)a_;
     for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
       const int pass = step / steps_per_pass, within = step % steps_per_pass, kt = within / hpg, hh = within % hpg, s = step & 1;
+      if ((step & 1) != wg) continue;
       const int n0 = kt * 128;
       const int chi = vis - n0;
-      if (pass == 1 && hh == 0) {
+      if (pass == 1 && hh == wg) {
 #pragma unroll
         for (int i = 0; i < 128; ++i) agg[i] = 0.f;
       }
@@ -242,7 +256,38 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tc_fence_before();
         mbar_arrive(&bar->s_free[s]);
         if (vis < 0 && kt == 0) agg[0] += 1.f;  // a row that sees no block puts all its mass on block 0
-        if (hh == hpg - 1) {
+        if (wg == 1 && hh == hpg - 1) {
+          // park this group's sums for group 0 (the previous tile's must have been picked up)
+          if (kt > 0) {
+            ok = mbar_wait(&bar->xchg_free, (kt - 1) & 1, abort);
+            if (!ok) break;
+            tc_fence_after();
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t sv[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sv[e] = __float_as_uint(agg[c * 32 + e]);
+            tmem_st32(tmem + lane_base + 256 + c * 32, sv);
+          }
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(&bar->xchg_full);
+        }
+        if (wg == 0 && hh == hpg - 2) {
+          ok = mbar_wait(&bar->xchg_full, kt & 1, abort);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t sv[32];
+            tmem_ld32(tmem + lane_base + 256 + c * 32, sv);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) agg[c * 32 + e] += __uint_as_float(sv[e]);
+          }
+          tc_fence_before();
+          mbar_arrive(&bar->xchg_free);
           // Eq. 9 with l = 2d: sel[j] = sum_{m<s_} (A[s_ j + m] + A[s_ j + m + 1]), adds issued in that order.
           // Streaming over the keys: key i ends the previous block when i % s_ == 0 and otherwise enters the
           // current block twice in a row; the block that straddles the tile end is finished by the next tile.
@@ -259,7 +304,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
       }
     }
-    if (ok) {
+    if (ok && wg == 0) {
       insert(cur, ntiles * per_tile - 1);  // the last block's final term lies beyond every visible key: + 0
       for (int j = ntiles * per_tile; j < n_sel && cnt < k_actual; ++j) insert(0.f, j);  // never-visible blocks, id order
       int res[kScoreMaxN];
@@ -283,9 +328,9 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
-    tmem_dealloc(tmem, 256);
+    tmem_dealloc(tmem, 512);
   }
 }
 
@@ -295,7 +340,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 bool score_sm100_supported(int H, int G, int T, int dk, int nbp, int l, int d, int lprime, int n) {
   if (!(dk == 192 || dk == 128 || dk == 64) || G <= 0 || H % G != 0) return false;
   const int hpg = H / G;
-  if (d <= 0 || l != 2 * d || lprime % d != 0) return false;
+  if (d <= 0 || l != 2 * d || lprime % d != 0 || hpg % 2 != 0) return false;
   const int s_ = lprime / d;
   const size_t smem = 4 * (size_t)128 * dk * 2 + 2 * (size_t)hpg * 512 + 2 * (size_t)n * 512 + 256 + 1024;
   return smem <= 227 * 1024 && T % 128 == 0 && nbp % 128 == 0 && 128 % s_ == 0 && n >= 1 && n <= kScoreMaxN;
@@ -317,7 +362,7 @@ static int launch_score_t(const CUtensorMap& tq, const CUtensorMap& thi, const C
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess)
     return fail(NSA_ERR_LAUNCH, "score_topn: cannot reserve shared memory");
   KernelTimer kt("score_topn_tc", st);
-  kern<<<dim3(p.T / 128, p.B * p.G), 192, dyn, st>>>(tq, thi, tlo, p, hpg, state_off, list_off, bar_off);
+  kern<<<dim3(p.T / 128, p.B * p.G), 384, dyn, st>>>(tq, thi, tlo, p, hpg, state_off, list_off, bar_off);
   return check_launch("score_topn_tc");
 }
 

@@ -380,20 +380,31 @@ __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part,
   float lsum = 0.f, acc[VPL];
 #pragma unroll
   for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
-  for (int s = 0; s < nslots; ++s) {
-    const float wgt = __shfl_sync(0xffffffffu, wmine, s);
-    if (!((validmask >> s) & 1)) continue;
-    lsum += wgt;
-    const __nv_bfloat16* src = o_part + (base + (int64_t)s * hpg) * DV + lane * VPL;
-    if (VPL == 4) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(src);
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-      const float2 c2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  // slots in groups of 8: all loads of a group are issued before the first value is used
+  for (int s8 = 0; s8 < nslots; s8 += 8) {
+    uint2 raw[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int s = s8 + u;
+      raw[u] = make_uint2(0u, 0u);
+      if (s < nslots && ((validmask >> s) & 1)) {
+        const __nv_bfloat16* src = o_part + (base + (int64_t)s * hpg) * DV + lane * VPL;
+        if (VPL == 4) raw[u] = *reinterpret_cast<const uint2*>(src);
+        else raw[u].x = *reinterpret_cast<const uint32_t*>(src);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int s = s8 + u;
+      const float wgt = __shfl_sync(0xffffffffu, wmine, s & 31);
+      if (s >= nslots || !((validmask >> s) & 1)) continue;
+      lsum += wgt;
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u].x));
       acc[0] = fmaf(wgt, a.x, acc[0]); acc[1] = fmaf(wgt, a.y, acc[1]);
-      acc[2 % VPL] = fmaf(wgt, c2.x, acc[2 % VPL]); acc[3 % VPL] = fmaf(wgt, c2.y, acc[3 % VPL]);
-    } else {
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src));
-      acc[0] = fmaf(wgt, a.x, acc[0]); acc[1] = fmaf(wgt, a.y, acc[1]);
+      if (VPL == 4) {
+        const float2 c2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u].y));
+        acc[2 % VPL] = fmaf(wgt, c2.x, acc[2 % VPL]); acc[3 % VPL] = fmaf(wgt, c2.y, acc[3 % VPL]);
+      }
     }
   }
   const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
@@ -418,7 +429,7 @@ struct SlcDqSmem {
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct SlcDqBarriers {
-  uint64_t kv_full, kv_empty, q_full[2], q_empty[2], sdp_full[2], ds_full[2], dq_full[2], dq_read[2];
+  uint64_t kv_full, kv_empty, q_full[2], q_empty[2], sdp_full[2], ds_full[2], dq_full[2], dq_read_lo[2], dq_read_hi[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -450,7 +461,8 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       mbar_init(&bar->sdp_full[i], 1);
       mbar_init(&bar->ds_full[i], 128);
       mbar_init(&bar->dq_full[i], 1);   // per compute group: a group only ever sees its own chunks' phases
-      mbar_init(&bar->dq_read[i], 128);
+      mbar_init(&bar->dq_read_lo[i], 128);  // the dQ accumulator is handed back in two column halves
+      mbar_init(&bar->dq_read_hi[i], 128);
     }
     bar->abort = 0;
     fence_barrier_init();
@@ -501,7 +513,7 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     if (lane == 0) {
       constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);    // Q rows x K block (keys contiguous)
       constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);   // dO rows x V block read K-major (dv contiguous)
-      constexpr uint32_t iddQ = idesc_bf16(128, DK, 0, 0);   // dS (TMEM) x K block read K-major (keys = K dim)
+      constexpr uint32_t iddQh = idesc_bf16(128, DK / 2, 0, 0);   // dS (TMEM) x half of the K block's dk rows, read K-major
       const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024), dKk = dKmn;
       const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
       ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
@@ -533,13 +545,20 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         if (same_blk) ok = issue_sdp(cur + 1);  // look ahead while this chunk's dS is being computed
         if (!ok) break;
         ok = mbar_wait(&bar->ds_full[cur & 1], (cur >> 1) & 1, abort);
-        // the single dQ accumulator must have been drained by the epilogue of the previous chunk (other group)
-        if (ok && cur > 0) ok = mbar_wait(&bar->dq_read[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
+        // the single dQ accumulator is drained by the epilogue of the previous chunk (other group) one column half at
+        // a time; each half is refilled as soon as it has been read
+        if (ok && cur > 0) ok = mbar_wait(&bar->dq_read_lo[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem + cdQ, tmem + (cur & 1) * 128 + kk * 8, desc_advance(dKk, kk * 32), iddQ, kk > 0);
+          umma_ts(tmem + cdQ, tmem + (cur & 1) * 128 + kk * 8, desc_advance(dKk, kk * 32), iddQh, kk > 0);
+        if (cur > 0) ok = mbar_wait(&bar->dq_read_hi[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ts(tmem + cdQ + DK / 2, tmem + (cur & 1) * 128 + kk * 8, desc_advance(dKk, (DK / 2) * 128 + kk * 32), iddQh, kk > 0);
         umma_commit(&bar->dq_full[cur & 1]);
         if (more && !same_blk) {
           // the single K/V slot is reloaded: everything issued so far must have finished with it
@@ -614,9 +633,13 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             *reinterpret_cast<uint4*>(dst + cc * 32 + e) = wv;
           }
         }
+        if (cc == DK / 64 - 1) {
+          tc_fence_before();
+          mbar_arrive(&bar->dq_read_lo[buf]);
+        }
       }
       tc_fence_before();
-      mbar_arrive(&bar->dq_read[buf]);
+      mbar_arrive(&bar->dq_read_hi[buf]);
     }
   }
   tc_fence_before();
@@ -645,15 +668,24 @@ __global__ void slc_combine_dq_kernel(const __nv_bfloat16* __restrict__ dq_part,
   float acc[DK / 32];
 #pragma unroll
   for (int c = 0; c < DK / 32; ++c) acc[c] = 0.f;
-  for (int s = 0; s < nslots; ++s) {
-    if (!((validmask >> s) & 1)) continue;
-    const __nv_bfloat16* src = dq_part + (base + (int64_t)s * hpg) * DK;
+  for (int s4 = 0; s4 < nslots; s4 += 4) {   // 4 slots x DK/64 loads in flight per lane
+    uint32_t raw[4][DK / 64];
 #pragma unroll
-    for (int c = 0; c < DK / 64; ++c) {
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + c * 64 + lane * 2));
-      acc[2 * c] += a.x;
-      acc[2 * c + 1] += a.y;
+    for (int u = 0; u < 4; ++u) {
+      const int s = s4 + u;
+      const bool on = s < nslots && ((validmask >> s) & 1);
+      const __nv_bfloat16* src = dq_part + (base + (int64_t)s * hpg) * DK;
+#pragma unroll
+      for (int c = 0; c < DK / 64; ++c) raw[u][c] = on ? *reinterpret_cast<const uint32_t*>(src + c * 64 + lane * 2) : 0u;
     }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)   // a skipped slot adds exact zeros: the sum is unchanged
+#pragma unroll
+      for (int c = 0; c < DK / 64; ++c) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u][c]));
+        acc[2 * c] += a.x;
+        acc[2 * c + 1] += a.y;
+      }
   }
 #pragma unroll
   for (int c = 0; c < DK / 64; ++c)
@@ -881,6 +913,7 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           tc_wait_ld();
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
+            if (!rowlane) { pk[e] = 0u; dk_[e] = 0u; continue; }  // lanes 16-31 hold no row of an M = 64 tile
             const int j0 = hf * 64 + cc * 32 + 2 * e;  // row of the gathered tile = column here
             const float l0 = stat[j0], l1 = stat[j0 + 1], D0 = stat[128 + j0], D1 = stat[128 + j0 + 1];
             const int t0 = tcol[j0], t1 = tcol[j0 + 1];

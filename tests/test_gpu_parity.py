@@ -345,10 +345,10 @@ def test_top_n_known_answers_on_gpu(nsa_mod):
 
 
 @pytest.mark.parametrize("mode", ["sigmoid", "softmax"])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gate_mix(nsa_mod, mode, dtype):
+@pytest.mark.parametrize("dtype,dv", [(torch.float32, 80), (torch.bfloat16, 80), (torch.bfloat16, 128)])
+def test_gate_mix(nsa_mod, mode, dtype, dv):
     from nsa.kernels import _GateMix
-    B, H, T, dv = 2, 6, 37, 80
+    B, H, T = 2, 6, 37
     gen = torch.Generator().manual_seed(3)
     rnd = lambda *s: torch.randn(*s, generator=gen).to(dtype).float()
     lg, oc, os_, ow, do = rnd(B, T, 3 * H), rnd(B, H, T, dv), rnd(B, H, T, dv), rnd(B, H, T, dv), rnd(B, H, T, dv)
