@@ -30,6 +30,17 @@ constexpr int kEntriesPerCta = 1024;  // inverse-index entries handled by one CT
 constexpr float kLn2f = 0.6931471805599453f;
 constexpr float kLog2ef = 1.4426950408889634f;
 
+// Optional timeline probe for development builds (-DNSA_TRACE): one CTA records clock64() at role hand-offs.
+#ifdef NSA_TRACE
+__device__ long long g_trace[4][128][8];
+#define NSA_TR(role, c, ev)                                                              \
+  do {                                                                                   \
+    if (blockIdx.x == 3 && blockIdx.y == 0 && (c) < 128) g_trace[role][c][ev] = clock64(); \
+  } while (0)
+#else
+#define NSA_TR(role, c, ev)
+#endif
+
 struct SlcParams {
   const __nv_bfloat16* q;      // [B,H,Tq,dk]
   const __nv_bfloat16* dout;   // [B,H,Tq,dv] (backward)
@@ -188,13 +199,16 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 tma_load_2d(&tmV, &bar->kv_full[ks], sV + ks * SM::kV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
             }
           }
+          if (lane == 0) NSA_TR(0, c, 0);
           if (ok) ok = mbar_wait(&bar->q_empty[s], ((c / 3) & 1) ^ 1, abort);
+          if (lane == 0) NSA_TR(0, c, 1);
           if (ok) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ);
         }
         if (w.blk != last_blk) { last_blk = w.blk; ++kvidx; }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], sQ + s * SM::kQ, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row, lane);
+        if (lane == 0) NSA_TR(0, c, 2);
       }
       if (!ok && lane == 0) {  // let copies in flight land before the CTA gives its shared memory back
         if (kvidx >= 0) mbar_wait(&bar->kv_full[kvidx & 1], (kvidx >> 1) & 1, abort);
@@ -211,8 +225,11 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       int c = 0, kvidx = -1, last_blk = -1, prev_ks = -1;
       auto issue_s = [&](int cc, int ks) -> bool {
         const int s = cc % 3, buf = cc & 1;
+        NSA_TR(1, cc, 0);
         if (!mbar_wait(&bar->q_full[s], (cc / 3) & 1, abort)) return false;
+        NSA_TR(1, cc, 1);
         if (!mbar_wait(&bar->o_read[buf], ((cc >> 1) & 1) ^ 1, abort)) return false;
+        NSA_TR(1, cc, 2);
         tc_fence_after();
         const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * SM::kQ), 16, 1024);
         const uint64_t dK = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);  // one 64-key MN block: LBO unused
@@ -221,6 +238,7 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           umma_ss(tmem + buf * 192, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dK, kk * 2048), idS, kk > 0);
         umma_commit(&bar->s_full[buf]);
         umma_commit(&bar->q_empty[s]);
+        NSA_TR(1, cc, 3);
         return true;
       };
       // the block (and K/V slot) of every chunk is needed twice: when S is issued and when PV is issued
@@ -257,8 +275,10 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           last_of_block[cur & 1] = true;
         }
         const int buf = cur & 1, ks = ks_of[cur & 1];
+        NSA_TR(1, cur, 4);
         ok = mbar_wait(&bar->p_full[buf], (cur >> 1) & 1, abort);
         if (!ok) break;
+        NSA_TR(1, cur, 5);
         tc_fence_after();
         const uint64_t dV = smem_desc_sw128(smem_u32(sV + ks * SM::kV), 8192, 1024);
 #pragma unroll
@@ -266,6 +286,7 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           umma_ts(tmem + buf * 192 + 64, tmem + buf * 192 + kk * 8, desc_advance(dV, kk * 2048), idO, kk > 0);
         umma_commit(&bar->o_full[buf]);
         if (last_of_block[cur & 1]) umma_commit(&bar->kv_empty[ks]);
+        NSA_TR(1, cur, 6);
         ++c;
       }
       (void)prev_ks;
@@ -286,8 +307,10 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const int entry = valid ? ent[w.e + qi] : 0;
       const int t = entry & 0xFFFFFF, slot = entry >> 24;
       const int key0 = w.blk * 64;
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 0);
       ok = mbar_wait(&bar->s_full[buf], it & 1, abort);
       if (!ok) break;
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 1);
       tc_fence_after();
       uint32_t sv[2][32];
       tmem_ld32(tmem + lane_base + buf * 192, sv[0]);
@@ -317,8 +340,10 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bar->p_full[buf]);
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 2);
       ok = mbar_wait(&bar->o_full[buf], it & 1, abort);
       if (!ok) break;
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 3);
       tc_fence_after();
       const float inv = 1.f / l;
       const int64_t prow = (((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh;
@@ -345,6 +370,7 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (valid) p.st_part[prow] = make_float2(mx, l);
       tc_fence_before();
       mbar_arrive(&bar->o_read[buf]);
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 4);
     }
   }
   tc_fence_before();
@@ -913,7 +939,6 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           tc_wait_ld();
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            if (!rowlane) { pk[e] = 0u; dk_[e] = 0u; continue; }  // lanes 16-31 hold no row of an M = 64 tile
             const int j0 = hf * 64 + cc * 32 + 2 * e;  // row of the gathered tile = column here
             const float l0 = stat[j0], l1 = stat[j0 + 1], D0 = stat[128 + j0], D1 = stat[128 + j0 + 1];
             const int t0 = tcol[j0], t1 = tcol[j0 + 1];
@@ -1154,3 +1179,9 @@ int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indice
 }
 
 }  // namespace nsa
+
+#ifdef NSA_TRACE
+extern "C" __attribute__((visibility("default"))) int nsa_trace_read(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, nsa::g_trace, sizeof(nsa::g_trace));
+}
+#endif
