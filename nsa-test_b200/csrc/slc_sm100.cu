@@ -32,7 +32,7 @@ constexpr float kLog2ef = 1.4426950408889634f;
 
 // Optional timeline probe for development builds (-DNSA_TRACE): one CTA records clock64() at role hand-offs.
 #ifdef NSA_TRACE
-__device__ long long g_trace[4][128][8];
+__device__ long long g_trace[4][128][16];
 #define NSA_TR(role, c, ev)                                                              \
   do {                                                                                   \
     if (blockIdx.x == 3 && blockIdx.y == 0 && (c) < 128) g_trace[role][c][ev] = clock64(); \
@@ -94,12 +94,13 @@ struct ChunkWalker {
 template <int DK, int DV>
 struct SlcFwdSmem {
   static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2;
-  static constexpr int kQStages = 3;
-  static constexpr int oK = 0, oV = oK + 2 * kK, oQ = oV + 2 * kV, oBar = oQ + kQStages * kQ;
+  static constexpr int kQStages = 2;
+  static constexpr int kStage = 8 * 4096;  // per compute warp: 32 rows x 64 bf16 columns on their way to global memory
+  static constexpr int oK = 0, oV = oK + 2 * kK, oQ = oV + 2 * kV, oStage = oQ + kQStages * kQ, oBar = oStage + kStage;
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct SlcFwdBarriers {
-  uint64_t kv_full[2], kv_empty[2], q_full[3], q_empty[3], s_full[2], p_full[2], o_full[2], o_read[2];
+  uint64_t kv_full[2], kv_empty[2], q_full[2], q_empty[2], s_full[2], p_full[2], o_full[2], o_read[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -139,8 +140,9 @@ __device__ __forceinline__ void tma_gather_chunk(const CUtensorMap* tm, uint64_t
 template <int DK, int DV>
 __global__ void __launch_bounds__(320, 1)
 slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-               const __grid_constant__ CUtensorMap tmQt, const SlcParams p) {
+               const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmOp, const SlcParams p) {
   using SM = SlcFwdSmem<DK, DV>;
+  constexpr int NQ = SM::kQStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sQ = smem + SM::oQ;
@@ -155,11 +157,9 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const bool has_work = e0 < off[p.nblk];
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 3; ++i) {
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&bar->q_full[i], 1);
       mbar_init(&bar->q_empty[i], 1);
-    }
-    for (int i = 0; i < 2; ++i) {
       mbar_init(&bar->kv_full[i], 1);
       mbar_init(&bar->kv_empty[i], 1);
       mbar_init(&bar->s_full[i], 1);
@@ -181,115 +181,117 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // nothing to do for this CTA
   } else if (warp == 9) {
     // ------------------------------------------------------------ producer warp: K/V blocks and gathered Q rows, all by TMA
-    {
-      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-      const int oob_row = p.B * p.H * p.Tq;
-      bool ok = true;
-      int c = 0, kvidx = -1, last_blk = -1;
-      for (; !w.done(); w.next(), ++c) {
-        const int s = c % 3;
-        if (lane == 0) {
-          if (w.blk != last_blk) {
-            const int ks = (kvidx + 1) & 1;
-            ok = mbar_wait(&bar->kv_empty[ks], (((kvidx + 1) >> 1) & 1) ^ 1, abort);
-            if (ok) {
-              mbar_arrive_expect_tx(&bar->kv_full[ks], SM::kK + SM::kV);
-              tma_load_2d(&tmK, &bar->kv_full[ks], sK + ks * SM::kK, w.blk * 64, (b * p.G + g) * DK);
-              for (int cc = 0; cc < DV / 64; ++cc)
-                tma_load_2d(&tmV, &bar->kv_full[ks], sV + ks * SM::kV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
-            }
-          }
-          if (lane == 0) NSA_TR(0, c, 0);
-          if (ok) ok = mbar_wait(&bar->q_empty[s], ((c / 3) & 1) ^ 1, abort);
-          if (lane == 0) NSA_TR(0, c, 1);
-          if (ok) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ);
-        }
-        if (w.blk != last_blk) { last_blk = w.blk; ++kvidx; }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    const int oob_row = p.B * p.H * p.Tq;
+    bool ok = true;
+    int c = 0, kvidx = -1, last_blk = -1;
+    for (; !w.done(); w.next(), ++c) {
+      const int s = c % NQ;
+      if (w.blk != last_blk) {
+        last_blk = w.blk;
+        ++kvidx;
+        const int ks = kvidx & 1;
+        ok = mbar_wait_warp(&bar->kv_empty[ks], ((kvidx >> 1) & 1) ^ 1, abort);
         if (!ok) break;
-        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], sQ + s * SM::kQ, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row, lane);
-        if (lane == 0) NSA_TR(0, c, 2);
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&bar->kv_full[ks], SM::kK + SM::kV);
+          tma_load_2d(&tmK, &bar->kv_full[ks], sK + ks * SM::kK, w.blk * 64, (b * p.G + g) * DK);
+          for (int cc = 0; cc < DV / 64; ++cc)
+            tma_load_2d(&tmV, &bar->kv_full[ks], sV + ks * SM::kV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
+        }
       }
-      if (!ok && lane == 0) {  // let copies in flight land before the CTA gives its shared memory back
-        if (kvidx >= 0) mbar_wait(&bar->kv_full[kvidx & 1], (kvidx >> 1) & 1, abort);
-        for (int cc = max(0, c - 3); cc < c; ++cc) mbar_wait(&bar->q_full[cc % 3], (cc / 3) & 1, abort);
+      // this chunk's entries are fetched while the stage is still busy
+      const int cnt = w.count();
+      int row = oob_row;
+      if (lane < cnt) row = (int)(((int64_t)bg * p.Tq + (ent[w.e + lane] & 0xFFFFFF)) * p.hpg);
+      if (lane == 0) NSA_TR(0, c, 0);
+      ok = mbar_wait_warp(&bar->q_empty[s], ((c / NQ) & 1) ^ 1, abort);
+      if (!ok) break;
+      if (lane == 0) {
+        NSA_TR(0, c, 1);
+        mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ);
       }
+      __syncwarp();
+      for (int qi = lane; qi < qpc; qi += 32) {
+        const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
+#pragma unroll
+        for (int cc = 0; cc < DK / 64; ++cc)
+          tma_load_2d(&tmQt, &bar->q_full[s], sQ + s * SM::kQ + cc * 16384 + qi * p.hpg * 128, cc * 64, r2);
+      }
+      if (lane == 0) NSA_TR(0, c, 2);
+    }
+    if (!ok && lane == 0) {  // let copies in flight land before the CTA gives its shared memory back
+      if (kvidx >= 0) mbar_wait(&bar->kv_full[kvidx & 1], (kvidx >> 1) & 1, abort);
+      for (int cc = max(0, c - NQ); cc < c; ++cc) mbar_wait(&bar->q_full[cc % NQ], (cc / NQ) & 1, abort);
     }
   } else if (warp == 8) {
-    // ------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);   // Q rows (K-major) x K block (MN-major: keys contiguous)
-      constexpr uint32_t idO = idesc_bf16(128, DV, 0, 1);   // P (TMEM) x V block (MN-major: dv contiguous)
-      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-      bool ok = true;
-      int c = 0, kvidx = -1, last_blk = -1, prev_ks = -1;
-      auto issue_s = [&](int cc, int ks) -> bool {
-        const int s = cc % 3, buf = cc & 1;
-        NSA_TR(1, cc, 0);
-        if (!mbar_wait(&bar->q_full[s], (cc / 3) & 1, abort)) return false;
-        NSA_TR(1, cc, 1);
-        if (!mbar_wait(&bar->o_read[buf], ((cc >> 1) & 1) ^ 1, abort)) return false;
-        NSA_TR(1, cc, 2);
-        tc_fence_after();
-        const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * SM::kQ), 16, 1024);
-        const uint64_t dK = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);  // one 64-key MN block: LBO unused
+    // ------------------------------------------------------------ UMMA issuer: the warp runs the schedule uniformly, one
+    // elected lane issues the tensor-core instructions
+    constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);   // Q rows (K-major) x K block (MN-major: keys contiguous)
+    constexpr uint32_t idO = idesc_bf16(128, DV, 0, 1);   // P (TMEM) x V block (MN-major: dv contiguous)
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    bool ok = true;
+    int c = 0, kvidx = 0, ks_cur = 0, cur_blk = w.blk;
+    auto issue_s = [&](int cc, int ks) -> bool {
+      const int s = cc % NQ, buf = cc & 1;
+      if (lane == 0) NSA_TR(1, cc, 0);
+      if (!mbar_wait_warp(&bar->q_full[s], (cc / NQ) & 1, abort)) return false;
+      if (lane == 0) NSA_TR(1, cc, 1);
+      if (!mbar_wait_warp(&bar->o_read[buf], ((cc >> 1) & 1) ^ 1, abort)) return false;
+      if (lane == 0) NSA_TR(1, cc, 2);
+      tc_fence_after();
+      const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * SM::kQ), 16, 1024);
+      const uint64_t dK = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);  // one 64-key MN block: LBO unused
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
           umma_ss(tmem + buf * 192, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dK, kk * 2048), idS, kk > 0);
         umma_commit(&bar->s_full[buf]);
         umma_commit(&bar->q_empty[s]);
-        NSA_TR(1, cc, 3);
-        return true;
-      };
-      // the block (and K/V slot) of every chunk is needed twice: when S is issued and when PV is issued
-      int ks_of[2] = {0, 0};
-      bool last_of_block[2] = {false, false};
-      // prologue: S(0)
-      if (!w.done()) {
-        last_blk = w.blk;
-        kvidx = 0;
-        ok = mbar_wait(&bar->kv_full[0], 0, abort);
-        ks_of[0] = 0;
-        if (ok) ok = issue_s(0, 0);
       }
-      while (ok && !w.done()) {
-        const int cur = c;
-        w.next();
-        // look ahead: S(c+1) before PV(c)
-        if (!w.done()) {
-          int ks = kvidx & 1;
-          if (w.blk != last_blk) {
-            last_blk = w.blk;
-            ++kvidx;
-            ks = kvidx & 1;
-            ok = mbar_wait(&bar->kv_full[ks], (kvidx >> 1) & 1, abort);
-            if (!ok) break;
-            last_of_block[cur & 1] = true;
-          } else {
-            last_of_block[cur & 1] = false;
-          }
-          ks_of[(cur + 1) & 1] = ks;
-          ok = issue_s(cur + 1, ks);
+      __syncwarp();
+      if (lane == 0) NSA_TR(1, cc, 3);
+      return true;
+    };
+    // prologue: S(0)
+    ok = mbar_wait_warp(&bar->kv_full[0], 0, abort);
+    if (ok) ok = issue_s(0, 0);
+    while (ok && !w.done()) {
+      w.next();
+      // look ahead: S(c+1) is issued before PV(c)
+      bool last_of_block = true;
+      int ks_next = ks_cur;
+      if (!w.done()) {
+        if (w.blk != cur_blk) {
+          cur_blk = w.blk;
+          ++kvidx;
+          ks_next = kvidx & 1;
+          ok = mbar_wait_warp(&bar->kv_full[ks_next], (kvidx >> 1) & 1, abort);
           if (!ok) break;
         } else {
-          last_of_block[cur & 1] = true;
+          last_of_block = false;
         }
-        const int buf = cur & 1, ks = ks_of[cur & 1];
-        NSA_TR(1, cur, 4);
-        ok = mbar_wait(&bar->p_full[buf], (cur >> 1) & 1, abort);
+        ok = issue_s(c + 1, ks_next);
         if (!ok) break;
-        NSA_TR(1, cur, 5);
-        tc_fence_after();
-        const uint64_t dV = smem_desc_sw128(smem_u32(sV + ks * SM::kV), 8192, 1024);
+      }
+      const int buf = c & 1;
+      if (lane == 0) NSA_TR(1, c, 4);
+      ok = mbar_wait_warp(&bar->p_full[buf], (c >> 1) & 1, abort);
+      if (!ok) break;
+      if (lane == 0) NSA_TR(1, c, 5);
+      tc_fence_after();
+      const uint64_t dV = smem_desc_sw128(smem_u32(sV + ks_cur * SM::kV), 8192, 1024);
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ts(tmem + buf * 192 + 64, tmem + buf * 192 + kk * 8, desc_advance(dV, kk * 2048), idO, kk > 0);
         umma_commit(&bar->o_full[buf]);
-        if (last_of_block[cur & 1]) umma_commit(&bar->kv_empty[ks]);
-        NSA_TR(1, cur, 6);
-        ++c;
+        if (last_of_block) umma_commit(&bar->kv_empty[ks_cur]);
       }
-      (void)prev_ks;
+      __syncwarp();
+      if (lane == 0) NSA_TR(1, c, 6);
+      ks_cur = ks_next;
+      ++c;
     }
   } else {
     // ------------------------------------------------------------ softmax + partial epilogue (two groups alternate chunks)
@@ -297,16 +299,26 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const int r = (warp & 3) * 32 + lane;
     const int qi = r / p.hpg, hh = r % p.hpg;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    // partial outputs leave through a per-warp staging area (128-byte swizzle) and TMA tile stores: one box per query
+    // (or per 32 rows of it), so global memory sees whole lines instead of one 16-byte piece per row
+    uint8_t* stage = smem + SM::oStage + warp * 4096;
+    const int boxrows = min(p.hpg, 32), nbox = 32 / boxrows;
+    const int box_lane = (lane * boxrows) & 31;  // lane owning the first row of the box this lane would store
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     bool ok = true;
-    int c = 0;
-    for (; !w.done() && ok; w.next(), ++c) {
-      if ((c & 1) != grp) continue;
+    if (grp == 1 && !w.done()) w.next();
+    int entry_next = 0;
+    if (!w.done() && qi < w.count()) entry_next = ent[w.e + qi];
+    for (int c = grp; !w.done() && ok; c += 2) {
       const int buf = grp, it = c >> 1;
       const bool valid = qi < w.count();
-      const int entry = valid ? ent[w.e + qi] : 0;
+      const int entry = entry_next;
       const int t = entry & 0xFFFFFF, slot = entry >> 24;
       const int key0 = w.blk * 64;
+      // move on to this group's next chunk and fetch its entry early
+      w.next();
+      if (!w.done()) w.next();
+      if (!w.done() && qi < w.count()) entry_next = ent[w.e + qi];
       if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 0);
       ok = mbar_wait(&bar->s_full[buf], it & 1, abort);
       if (!ok) break;
@@ -341,37 +353,47 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       tc_fence_before();
       mbar_arrive(&bar->p_full[buf]);
       if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 2);
+      const float inv = 1.f / l;
+      const int64_t prow = (((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh;
+      if (valid) p.st_part[prow] = make_float2(mx, l);
+      // the lane that stores a box needs the global row of the box's first row
+      const int box_row = __shfl_sync(0xffffffffu, valid ? (int)prow : -1, box_lane);
       ok = mbar_wait(&bar->o_full[buf], it & 1, abort);
       if (!ok) break;
       if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 3);
       tc_fence_after();
-      const float inv = 1.f / l;
-      const int64_t prow = (((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh;
-      __nv_bfloat16* dst = p.o_part + prow * DV;
 #pragma unroll
-      for (int cc = 0; cc < DV / 32; ++cc) {
-        uint32_t ov[32];
-        tmem_ld32(tmem + lane_base + buf * 192 + 64 + cc * 32, ov);
+      for (int half = 0; half < DV / 64; ++half) {
+        uint32_t ov[2][32];
+        tmem_ld32(tmem + lane_base + buf * 192 + 64 + half * 64, ov[0]);
+        tmem_ld32(tmem + lane_base + buf * 192 + 64 + half * 64 + 32, ov[1]);
         tc_wait_ld();
-        if (valid) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            uint4 wv;
-            __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[e]) * inv, __uint_as_float(ov[e + 1]) * inv);
-            __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2]) * inv, __uint_as_float(ov[e + 3]) * inv);
-            __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 4]) * inv, __uint_as_float(ov[e + 5]) * inv);
-            __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[e + 6]) * inv, __uint_as_float(ov[e + 7]) * inv);
-            wv.x = *reinterpret_cast<uint32_t*>(&a0); wv.y = *reinterpret_cast<uint32_t*>(&a1);
-            wv.z = *reinterpret_cast<uint32_t*>(&a2); wv.w = *reinterpret_cast<uint32_t*>(&a3);
-            *reinterpret_cast<uint4*>(dst + cc * 32 + e) = wv;
-          }
+        if (half == DV / 64 - 1) {  // the accumulator is free again as soon as it sits in registers
+          tc_fence_before();
+          mbar_arrive(&bar->o_read[buf]);
         }
+        bulk_wait_read<0>();  // the staging area is no longer being read by the previous store
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t* src = &ov[j >> 2][(j & 3) * 8];
+          uint4 wv;
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
+          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
+          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
+          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
+          wv.x = *reinterpret_cast<uint32_t*>(&a0); wv.y = *reinterpret_cast<uint32_t*>(&a1);
+          wv.z = *reinterpret_cast<uint32_t*>(&a2); wv.w = *reinterpret_cast<uint32_t*>(&a3);
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = wv;
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane < nbox && box_row >= 0) tma_store_2d(&tmOp, stage + lane * boxrows * 128, half * 64, box_row);
+        bulk_commit();
       }
-      if (valid) p.st_part[prow] = make_float2(mx, l);
-      tc_fence_before();
-      mbar_arrive(&bar->o_read[buf]);
       if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 4);
     }
+    bulk_wait_read<0>();
   }
   tc_fence_before();
   __syncthreads();
@@ -1031,7 +1053,8 @@ static int token_major_copy_w(int W, const void* in, void* out, int B, int H, in
 }
 
 template <int DK, int DV>
-static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tqt, const SlcParams& p, const int* indices,
+static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tqt, const CUtensorMap& top,
+                            const SlcParams& p, const int* indices,
                             const int64_t* sidx, __nv_bfloat16* out, float* L, float* M, cudaStream_t st) {
   using SM = SlcFwdSmem<DK, DV>;
   auto kern = slc_fwd_kernel<DK, DV>;
@@ -1040,7 +1063,7 @@ static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   const int nparts = (int)(((int64_t)p.Tq * p.nslots + kEntriesPerCta - 1) / kEntriesPerCta);
   {
     KernelTimer kt("slc_fwd", st);
-    kern<<<dim3(nparts, p.B * p.G), 320, SM::kDynamic, st>>>(tk, tv, tqt, p);
+    kern<<<dim3(nparts, p.B * p.G), 320, SM::kDynamic, st>>>(tk, tv, tqt, top, p);
   }
   if (int rc = check_launch("slc_fwd_sm100")) return rc;
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
@@ -1075,9 +1098,11 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
   if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, 64)) return rc;
   CUtensorMap tqt;
   if (int rc = make_tmap_bf16_2d(&tqt, qt, (uint64_t)B * H * Tq, dk, H / G)) return rc;
-  if (dk == 192 && dv == 128) return launch_slc_fwd_t<192, 128>(tk, tv, tqt, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
-  if (dk == 128 && dv == 128) return launch_slc_fwd_t<128, 128>(tk, tv, tqt, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
-  if (dk == 64 && dv == 64) return launch_slc_fwd_t<64, 64>(tk, tv, tqt, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  CUtensorMap top;  // partial outputs as rows of dv values; one box = the heads of a group for one (query, slot)
+  if (int rc = make_tmap_bf16_2d(&top, p.o_part, (uint64_t)rows, dv, (uint32_t)(H / G < 32 ? H / G : 32))) return rc;
+  if (dk == 192 && dv == 128) return launch_slc_fwd_t<192, 128>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  if (dk == 128 && dv == 128) return launch_slc_fwd_t<128, 128>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  if (dk == 64 && dv == 64) return launch_slc_fwd_t<64, 64>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
   return fail(NSA_ERR_UNSUPPORTED, "slc_fwd_sm100: unsupported head dims");
 }
 
