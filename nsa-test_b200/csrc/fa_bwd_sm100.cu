@@ -108,7 +108,9 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     jlo = 0;
     jhi = kmax >= 0 ? kmax / 128 : -1;
   }
-  const int ntiles = jhi - jlo + 1;
+  // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
+  const bool poisoned = p.timeouts && *(volatile const int*)p.timeouts != 0;
+  const int ntiles = poisoned ? 0 : jhi - jlo + 1;
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->qdo_full, 1);
@@ -132,35 +134,49 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr uint32_t cS = 0, cdP = 128, cdQ = 256, cdS = 256 + DK;
 
   if (warp == 8) {
-    if (lane == 0 && ntiles > 0) {
-      mbar_arrive_expect_tx(&bar->qdo_full, SM::kQ + SM::kdO);
-      const int qrow = (b * p.H + h) * p.Tq + m0;
-      for (int c = 0; c < DK / 64; ++c) tma_load_2d(&tmQ, &bar->qdo_full, sQ + c * 16384, c * 64, qrow);
-      for (int c = 0; c < DV / 64; ++c) tma_load_2d(&tmdO, &bar->qdo_full, sdO + c * 16384, c * 64, qrow);
+    // TMA producer: warp-uniform loop, one elected lane issues
+    if (ntiles > 0) {
+      if (elect_one()) {
+        mbar_arrive_expect_tx(&bar->qdo_full, SM::kQ + SM::kdO);
+        const int qrow = (b * p.H + h) * p.Tq + m0;
+        for (int c = 0; c < DK / 64; ++c) tma_load_2d(&tmQ, &bar->qdo_full, sQ + c * 16384, c * 64, qrow);
+        for (int c = 0; c < DV / 64; ++c) tma_load_2d(&tmdO, &bar->qdo_full, sdO + c * 16384, c * 64, qrow);
+      }
+      __syncwarp();
       bool ok = true;
       int issued = 0;
       for (int j = 0; j < ntiles && ok; ++j) {
         const int n0 = (jlo + j) * 128, ks = j & 1;
-        ok = mbar_wait(&bar->k_empty[ks], ((j >> 1) & 1) ^ 1, abort);
+        ok = mbar_wait_warp(&bar->k_empty[ks], ((j >> 1) & 1) ^ 1, abort);
         if (!ok) break;
-        mbar_arrive_expect_tx(&bar->k_full[ks], SM::kK);
-        for (int hf = 0; hf < 2; ++hf)
-          tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kK + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
-        ok = mbar_wait(&bar->v_empty, (j & 1) ^ 1, abort);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&bar->v_full, SM::kV);
-        for (int c = 0; c < DV / 64; ++c)
-          tma_load_2d(&tmV, &bar->v_full, sV + c * 16384, c * 64, (b * p.G + g) * p.Tk + n0);
+        if (elect_one()) {
+          mbar_arrive_expect_tx(&bar->k_full[ks], SM::kK);
+          for (int hf = 0; hf < 2; ++hf)
+            tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kK + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
+        }
+        __syncwarp();
+        ok = mbar_wait_warp(&bar->v_empty, (j & 1) ^ 1, abort);
+        if (!ok) {
+          if (lane == 0) mbar_wait(&bar->k_full[ks], (j >> 1) & 1, abort);
+          break;
+        }
+        if (elect_one()) {
+          mbar_arrive_expect_tx(&bar->v_full, SM::kV);
+          for (int c = 0; c < DV / 64; ++c)
+            tma_load_2d(&tmV, &bar->v_full, sV + c * 16384, c * 64, (b * p.G + g) * p.Tk + n0);
+        }
+        __syncwarp();
         issued = j + 1;
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         mbar_wait(&bar->qdo_full, 0, abort);
         for (int j = max(0, issued - 2); j < issued; ++j) mbar_wait(&bar->k_full[j & 1], (j >> 1) & 1, abort);
         if (issued > 0) mbar_wait(&bar->v_full, (issued - 1) & 1, abort);
       }
     }
   } else if (warp == 9) {
-    if (lane == 0 && ntiles > 0) {
+    // UMMA issuer: warp-uniform loop, one elected lane issues
+    if (ntiles > 0) {
       constexpr uint32_t idS = idesc_bf16(128, 128, 0, 1);    // Q (K-major) x K tile (MN-major: keys contiguous)
       constexpr uint32_t iddP = idesc_bf16(128, 128, 0, 0);   // dO (K-major) x V tile (K-major: dv contiguous)
       constexpr uint32_t iddQ = idesc_bf16(128, DK, 0, 0);    // dS (TMEM) x K tile read K-major (keys = K dim)
@@ -170,37 +186,46 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       auto issue_sdp = [&](int j) -> bool {
         const int ks = j & 1;
         const uint64_t dK_mn = smem_desc_sw128(smem_u32(sK + ks * SM::kK), DK * 128, 1024);
-        if (!(mbar_wait(&bar->k_full[ks], (j >> 1) & 1, abort) && mbar_wait(&bar->v_full, j & 1, abort))) return false;
-        if (j > 0 && !mbar_wait(&bar->sdp_free, (j - 1) & 1, abort)) return false;  // S/dP of tile j-1 are in registers
+        if (!(mbar_wait_warp(&bar->k_full[ks], (j >> 1) & 1, abort) && mbar_wait_warp(&bar->v_full, j & 1, abort))) return false;
+        if (j > 0 && !mbar_wait_warp(&bar->sdp_free, (j - 1) & 1, abort)) return false;  // S/dP of tile j-1 are in registers
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < DK / 16; ++kk)
-          umma_ss(tmem + cS, desc_advance(dQd, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dK_mn, kk * 2048), idS, kk > 0);
+          for (int kk = 0; kk < DK / 16; ++kk)
+            umma_ss(tmem + cS, desc_advance(dQd, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dK_mn, kk * 2048), idS, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < DV / 16; ++kk)
-          umma_ss(tmem + cdP, desc_advance(ddO, (kk >> 2) * 16384 + (kk & 3) * 32),
-                  desc_advance(dVd, (kk >> 2) * 16384 + (kk & 3) * 32), iddP, kk > 0);
-        umma_commit(&bar->sdp_full);
-        umma_commit(&bar->v_empty);
+          for (int kk = 0; kk < DV / 16; ++kk)
+            umma_ss(tmem + cdP, desc_advance(ddO, (kk >> 2) * 16384 + (kk & 3) * 32),
+                    desc_advance(dVd, (kk >> 2) * 16384 + (kk & 3) * 32), iddP, kk > 0);
+          umma_commit(&bar->sdp_full);
+          umma_commit(&bar->v_empty);
+        }
+        __syncwarp();
         return true;
       };
-      bool ok = mbar_wait(&bar->qdo_full, 0, abort) && issue_sdp(0);
+      bool ok = mbar_wait_warp(&bar->qdo_full, 0, abort) && issue_sdp(0);
       for (int j = 0; j < ntiles && ok; ++j) {
         const int ks = j & 1;
         const uint64_t dK_k = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);
         if (j + 1 < ntiles) ok = issue_sdp(j + 1);
         if (!ok) break;
-        ok = mbar_wait(&bar->ds_full, j & 1, abort);
+        ok = mbar_wait_warp(&bar->ds_full, j & 1, abort);
         if (!ok) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tmem + cdQ, tmem + cdS + kk * 8, desc_advance(dK_k, (kk >> 2) * (DK * 128) + (kk & 3) * 32), iddQ,
-                  (j > 0) || (kk > 0));
-        umma_commit(&bar->k_empty[ks]);
-        umma_commit(&bar->ds_free);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ts(tmem + cdQ, tmem + cdS + kk * 8, desc_advance(dK_k, (kk >> 2) * (DK * 128) + (kk & 3) * 32), iddQ,
+                    (j > 0) || (kk > 0));
+          umma_commit(&bar->k_empty[ks]);
+          umma_commit(&bar->ds_free);
+        }
+        __syncwarp();
       }
-      if (ok) umma_commit(&bar->dq_done);
+      if (ok) {
+        if (elect_one()) umma_commit(&bar->dq_done);
+        __syncwarp();
+      }
     }
   } else {
     const int gsel = warp >> 2;                 // which half of the key columns this thread handles
@@ -337,7 +362,8 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     qs_lo = (n0 < p.cmp_nb && tfirst < p.Tq) ? (int)(tfirst / 64) : 1;
     qs_hi = (n0 < p.cmp_nb && tfirst < p.Tq) ? (p.Tq - 1) / 64 : 0;
   }
-  const int nq = max(0, qs_hi - qs_lo + 1);
+  const bool poisoned = p.timeouts && *(volatile const int*)p.timeouts != 0;  // a block gave up on a wait earlier: skip
+  const int nq = poisoned ? 0 : max(0, qs_hi - qs_lo + 1);
   const int n_it = nq * hper;
 
   if (threadIdx.x == 0) {
@@ -362,35 +388,40 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   constexpr uint32_t cdK = 0, cdV = DK, cST = DK + DV, cdPT = DK + DV + 64, cP = DK + DV + 128, cdS = DK + DV + 160;
 
   if (warp == 4) {
-    // producer: the whole warp takes part (lanes fill the per-query statistics), lane 0 drives TMA
+    // producer: the whole warp takes part (lanes fill the per-query statistics), one elected lane drives TMA
     if (n_it > 0) {
-      if (lane == 0) {
+      if (elect_one()) {
         mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
         for (int hf = 0; hf < 2; ++hf) tma_load_2d(&tmK, &bar->kv_full, sK + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
         for (int c = 0; c < DV / 64; ++c) tma_load_2d(&tmV, &bar->kv_full, sV + c * 16384, c * 64, (b * p.G + g) * p.Tk + n0);
       }
+      __syncwarp();
       bool ok = true;
-      int issued = 0;
+      int issued = 0, s = 0, ph = 0, h = hbeg, qs = qs_lo;
       for (int it = 0; it < n_it; ++it) {
-        const int s = it % 3, h = hbeg + it / nq, tq0 = (qs_lo + it % nq) * 64;
-        if (lane == 0) ok = mbar_wait(&bar->empty[s], ((it / 3) & 1) ^ 1, abort);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        const int tq0 = qs * 64;
+        const int64_t qrow = ((int64_t)b * p.H + h) * p.Tq + tq0;
+        // the statistics are fetched before the stage is free
+        const float s_l0 = p.lse2[qrow + lane], s_l1 = p.lse2[qrow + 32 + lane];
+        const float s_d0 = p.D[qrow + lane], s_d1 = p.D[qrow + 32 + lane];
+        ok = mbar_wait_warp(&bar->empty[s], ph ^ 1, abort);
         if (!ok) break;
         uint8_t* st = sSt + s * SM::kStage;
-        const int64_t qrow = ((int64_t)b * p.H + h) * p.Tq + tq0;
-        if (lane == 0) {
+        if (elect_one()) {
           mbar_arrive_expect_tx(&bar->full[s], SM::kQs + SM::kdOs);
           for (int c = 0; c < DK / 64; ++c) tma_load_2d(&tmQ, &bar->full[s], st + c * 8192, c * 64, (int)qrow);
           for (int c = 0; c < DV / 64; ++c) tma_load_2d(&tmdO, &bar->full[s], st + SM::kQs + c * 8192, c * 64, (int)qrow);
         }
         float* stat = reinterpret_cast<float*>(st + SM::kQs + SM::kdOs);
-        for (int c = lane; c < 64; c += 32) {
-          stat[c] = p.lse2[qrow + c];
-          stat[64 + c] = p.D[qrow + c];
-        }
+        stat[lane] = s_l0;
+        stat[32 + lane] = s_l1;
+        stat[64 + lane] = s_d0;
+        stat[96 + lane] = s_d1;
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar->full[s]);
         issued = it + 1;
+        if (++s == 3) { s = 0; ph ^= 1; }
+        if (++qs > qs_hi) { qs = qs_lo; ++h; }
       }
       if (!ok && lane == 0) {
         mbar_wait(&bar->kv_full, 0, abort);
@@ -398,58 +429,73 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
     }
   } else if (warp == 5) {
-    if (lane == 0 && n_it > 0) {
+    // UMMA issuer: warp-uniform loop, one elected lane issues
+    if (n_it > 0) {
       constexpr uint32_t idST = idesc_bf16(128, 64, 1, 0);    // K tile as A (MN-major: keys contiguous) x Q sub-tile (K-major)
       constexpr uint32_t iddPT = idesc_bf16(128, 64, 0, 0);   // V tile as A (K-major) x dO sub-tile (K-major)
       constexpr uint32_t iddV = idesc_bf16(128, DV, 0, 1);    // P^T (TMEM) x dO sub-tile (MN-major: dv contiguous)
       constexpr uint32_t iddK = idesc_bf16(128, DK, 0, 1);    // dS^T (TMEM) x Q sub-tile (MN-major: dk contiguous)
       const uint64_t dKa = smem_desc_sw128(smem_u32(sK), DK * 128, 1024);
       const uint64_t dVa = smem_desc_sw128(smem_u32(sV), 16, 1024);
-      auto issue_st = [&](int it) -> bool {   // S^T = K Q^T and dP^T = V dO^T of iteration `it`
-        const int s = it % 3;
+      // S^T = K Q^T and dP^T = V dO^T of iteration `it`, whose stage is s (phase ph)
+      auto issue_st = [&](int it, int s, int ph) -> bool {
         const uint32_t st = smem_u32(sSt + s * SM::kStage);
         const uint64_t dQk = smem_desc_sw128(st, 16, 1024), dOk = smem_desc_sw128(st + SM::kQs, 16, 1024);
-        if (!mbar_wait(&bar->full[s], (it / 3) & 1, abort)) return false;
-        if (it > 0 && !mbar_wait(&bar->st_free, (it - 1) & 1, abort)) return false;  // fp32 tiles of it-1 are in registers
+        if (!mbar_wait_warp(&bar->full[s], ph, abort)) return false;
+        if (it > 0 && !mbar_wait_warp(&bar->st_free, (it - 1) & 1, abort)) return false;  // fp32 tiles of it-1 are in registers
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < DK / 16; ++kk)
-          umma_ss(tmem + cST, desc_advance(dKa, kk * 2048), desc_advance(dQk, (kk >> 2) * 8192 + (kk & 3) * 32), idST, kk > 0);
+          for (int kk = 0; kk < DK / 16; ++kk)
+            umma_ss(tmem + cST, desc_advance(dKa, kk * 2048), desc_advance(dQk, (kk >> 2) * 8192 + (kk & 3) * 32), idST, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < DV / 16; ++kk)
-          umma_ss(tmem + cdPT, desc_advance(dVa, (kk >> 2) * 16384 + (kk & 3) * 32),
-                  desc_advance(dOk, (kk >> 2) * 8192 + (kk & 3) * 32), iddPT, kk > 0);
-        umma_commit(&bar->stp_full);
+          for (int kk = 0; kk < DV / 16; ++kk)
+            umma_ss(tmem + cdPT, desc_advance(dVa, (kk >> 2) * 16384 + (kk & 3) * 32),
+                    desc_advance(dOk, (kk >> 2) * 8192 + (kk & 3) * 32), iddPT, kk > 0);
+          umma_commit(&bar->stp_full);
+        }
+        __syncwarp();
         return true;
       };
-      bool ok = mbar_wait(&bar->kv_full, 0, abort) && issue_st(0);
+      bool ok = mbar_wait_warp(&bar->kv_full, 0, abort) && issue_st(0, 0, 0);
+      int s = 0, s1 = 1, ph1 = 0;  // stage of `it`, stage and phase of `it + 1`
       for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it % 3;
         const uint32_t st = smem_u32(sSt + s * SM::kStage);
         const uint64_t dQmn = smem_desc_sw128(st, 8192, 1024), dOmn = smem_desc_sw128(st + SM::kQs, 8192, 1024);
-        if (it + 1 < n_it) ok = issue_st(it + 1);   // runs on the tensor pipe while the compute warps work on `it`
+        if (it + 1 < n_it) ok = issue_st(it + 1, s1, ph1);   // runs on the tensor pipe while the compute warps work on `it`
         if (!ok) break;
-        ok = mbar_wait(&bar->pds_full, it & 1, abort);
+        ok = mbar_wait_warp(&bar->pds_full, it & 1, abort);
         if (!ok) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem + cdV, tmem + cP + kk * 8, desc_advance(dOmn, kk * 2048), iddV, (it > 0) || (kk > 0));
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ts(tmem + cdV, tmem + cP + kk * 8, desc_advance(dOmn, kk * 2048), iddV, (it > 0) || (kk > 0));
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem + cdK, tmem + cdS + kk * 8, desc_advance(dQmn, kk * 2048), iddK, (it > 0) || (kk > 0));
-        umma_commit(&bar->empty[s]);
-        umma_commit(&bar->pds_free);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ts(tmem + cdK, tmem + cdS + kk * 8, desc_advance(dQmn, kk * 2048), iddK, (it > 0) || (kk > 0));
+          umma_commit(&bar->empty[s]);
+          umma_commit(&bar->pds_free);
+        }
+        __syncwarp();
+        s = s1;
+        if (++s1 == 3) { s1 = 0; ph1 ^= 1; }
       }
-      if (ok) umma_commit(&bar->acc_done);
+      if (ok) {
+        if (elect_one()) umma_commit(&bar->acc_done);
+        __syncwarp();
+      }
     }
   } else {
     const int r = warp * 32 + lane, key = n0 + r;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     bool ok = true;
+    int s = -1, ph = 0, qs = qs_lo - 1;
     for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it % 3, tq0 = (qs_lo + it % nq) * 64;
-      ok = mbar_wait(&bar->full[s], (it / 3) & 1, abort) && mbar_wait(&bar->stp_full, it & 1, abort);
+      if (++s == 3) { s = 0; ph ^= 1; }
+      if (++qs > qs_hi) qs = qs_lo;
+      const int tq0 = qs * 64;
+      ok = mbar_wait(&bar->full[s], ph, abort) && mbar_wait(&bar->stp_full, it & 1, abort);
       if (!ok) break;
       tc_fence_after();
       const float* stat = reinterpret_cast<const float*>(sSt + s * SM::kStage + SM::kQs + SM::kdOs);

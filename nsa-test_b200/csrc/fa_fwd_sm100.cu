@@ -28,7 +28,7 @@ static __device__ int g_fa_fwd_timeouts;  // CTAs that gave up on a barrier (0 i
 
 constexpr int kBM = 128;  // queries per MMA tile
 constexpr int kBN = 128;  // keys per tile
-constexpr int kFaThreads = 320;
+constexpr int kFaThreads = 384;  // 8 softmax warps, producer, UMMA issuer, 2 idle warps completing the third warpgroup
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
@@ -96,7 +96,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     jlo = 0;
     jhi = kmax >= 0 ? kmax / kBN : -1;
   }
-  const int ntiles = jhi - jlo + 1;
+  // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
+  const int ntiles = *(volatile const int*)&g_fa_fwd_timeouts != 0 ? 0 : jhi - jlo + 1;
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->q_full, 1);
@@ -118,35 +119,51 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
+  // the softmax warpgroups need more registers than an even split gives them, the third warpgroup far fewer
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
 
-  if (warp == 8) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0 && ntiles > 0) {
-      prefetch_tensormap(&tmQ);
-      prefetch_tensormap(&tmK);
-      prefetch_tensormap(&tmV);
-      mbar_arrive_expect_tx(&bar->q_full, 2 * SM::kQBytes);
-      for (int i = 0; i < 2; ++i)
-        for (int c = 0; c < DK / 64; ++c)
-          tma_load_2d(&tmQ, &bar->q_full, sQ + i * SM::kQBytes + c * (kBM * 128), c * 64,
-                      (b * p.H + h0 + i) * p.Tq + m0);
+  if (warp >= 10) {
+    // idle half of the third warpgroup
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer (warp-uniform loop, one elected lane issues)
+    if (ntiles > 0) {
+      if (elect_one()) {
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+        mbar_arrive_expect_tx(&bar->q_full, 2 * SM::kQBytes);
+        for (int i = 0; i < 2; ++i)
+          for (int c = 0; c < DK / 64; ++c)
+            tma_load_2d(&tmQ, &bar->q_full, sQ + i * SM::kQBytes + c * (kBM * 128), c * 64,
+                        (b * p.H + h0 + i) * p.Tq + m0);
+      }
+      __syncwarp();
       bool ok = true;
       int issued = 0;
       for (int j = 0; j < ntiles && ok; ++j) {
         const int n0 = (jlo + j) * kBN, ks = j & 1;
-        ok = mbar_wait(&bar->k_empty[ks], ((j >> 1) & 1) ^ 1, abort);
+        ok = mbar_wait_warp(&bar->k_empty[ks], ((j >> 1) & 1) ^ 1, abort);
         if (!ok) break;
-        mbar_arrive_expect_tx(&bar->k_full[ks], SM::kKBytes);
-        for (int hf = 0; hf < 2; ++hf)
-          tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kKBytes + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
-        ok = mbar_wait(&bar->v_empty, (j & 1) ^ 1, abort);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&bar->v_full, SM::kVBytes);
-        for (int c = 0; c < DV / 64; ++c)
-          tma_load_2d(&tmV, &bar->v_full, sV + c * (kBN * 128), c * 64, (b * p.G + g) * p.Tk + n0);
+        if (elect_one()) {
+          mbar_arrive_expect_tx(&bar->k_full[ks], SM::kKBytes);
+          for (int hf = 0; hf < 2; ++hf)
+            tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kKBytes + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
+        }
+        __syncwarp();
+        ok = mbar_wait_warp(&bar->v_empty, (j & 1) ^ 1, abort);
+        if (!ok) {
+          if (lane == 0) mbar_wait(&bar->k_full[ks], (j >> 1) & 1, abort);
+          break;
+        }
+        if (elect_one()) {
+          mbar_arrive_expect_tx(&bar->v_full, SM::kVBytes);
+          for (int c = 0; c < DV / 64; ++c)
+            tma_load_2d(&tmV, &bar->v_full, sV + c * (kBN * 128), c * 64, (b * p.G + g) * p.Tk + n0);
+        }
+        __syncwarp();
         issued = j + 1;
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         // let copies already in flight land before the CTA gives its shared memory back
         mbar_wait(&bar->q_full, 0, abort);
         for (int j = max(0, issued - 2); j < issued; ++j) mbar_wait(&bar->k_full[j & 1], (j >> 1) & 1, abort);
@@ -154,54 +171,66 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
     }
   } else if (warp == 9) {
-    // ------------------------------------------------------------ UMMA issuer (one thread)
-    if (lane == 0 && ntiles > 0) {
+    // ------------------------------------------------------------ UMMA issuer (warp-uniform loop, one elected lane issues)
+    if (ntiles > 0) {
       constexpr uint32_t idQK = idesc_bf16(kBM, kBN, 0, 1);
       constexpr uint32_t idPV = idesc_bf16(kBM, DV, 0, 1);
-      const uint64_t dQ[2] = {smem_desc_sw128(smem_u32(sQ), 16, 1024), smem_desc_sw128(smem_u32(sQ + SM::kQBytes), 16, 1024)};
-      const uint64_t dK[2] = {smem_desc_sw128(smem_u32(sK), DK * 128, 1024),
-                              smem_desc_sw128(smem_u32(sK + SM::kKBytes), DK * 128, 1024)};
+      const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t dK0 = smem_desc_sw128(smem_u32(sK), DK * 128, 1024);
       const uint64_t dV = smem_desc_sw128(smem_u32(sV), kBN * 128, 1024);
+      // issue S_i = Q_i K^T for key slot ks; called by the elected lane only
       auto issue_qk = [&](int i, int ks) {
+        const uint64_t dQ = desc_advance(dQ0, i * SM::kQBytes), dK = desc_advance(dK0, ks * SM::kKBytes);
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
-          umma_ss(tmem + i * 128, desc_advance(dQ[i], (kk >> 2) * (kBM * 128) + (kk & 3) * 32),
-                  desc_advance(dK[ks], kk * 2048), idQK, kk > 0);
+          umma_ss(tmem + i * 128, desc_advance(dQ, (kk >> 2) * (kBM * 128) + (kk & 3) * 32), desc_advance(dK, kk * 2048), idQK,
+                  kk > 0);
         umma_commit(&bar->s_full[i]);
       };
-      bool ok = mbar_wait(&bar->q_full, 0, abort) && mbar_wait(&bar->k_full[0], 0, abort);
+      bool ok = mbar_wait_warp(&bar->q_full, 0, abort) && mbar_wait_warp(&bar->k_full[0], 0, abort);
       if (ok) {
         tc_fence_after();
-        issue_qk(0, 0);
-        issue_qk(1, 0);
-        umma_commit(&bar->k_empty[0]);
+        if (elect_one()) {
+          issue_qk(0, 0);
+          issue_qk(1, 0);
+          umma_commit(&bar->k_empty[0]);
+        }
+        __syncwarp();
       }
       for (int j = 0; j < ntiles && ok; ++j) {
-        ok = mbar_wait(&bar->v_full, j & 1, abort);
+        ok = mbar_wait_warp(&bar->v_full, j & 1, abort);
         for (int i = 0; i < 2 && ok; ++i) {
-          ok = mbar_wait(&bar->p_full[i], j & 1, abort);
+          ok = mbar_wait_warp(&bar->p_full[i], j & 1, abort);
           if (!ok) break;
+          const bool more = j + 1 < ntiles;
+          const int ks = (j + 1) & 1;
           tc_fence_after();
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk)
-            umma_ts(tmem + 256 + i * 128, tmem + i * 128 + kk * 8, desc_advance(dV, kk * 2048), idPV, (j > 0) || (kk > 0));
-          umma_commit(&bar->pv_done[i]);
-          if (i == 1) umma_commit(&bar->v_empty);
-          if (j + 1 < ntiles) {
-            const int ks = (j + 1) & 1;
+            for (int kk = 0; kk < kBN / 16; ++kk)
+              umma_ts(tmem + 256 + i * 128, tmem + i * 128 + kk * 8, desc_advance(dV, kk * 2048), idPV, (j > 0) || (kk > 0));
+            umma_commit(&bar->pv_done[i]);
+            if (i == 1) umma_commit(&bar->v_empty);
+          }
+          __syncwarp();
+          if (more) {
             if (i == 0) {
-              ok = mbar_wait(&bar->k_full[ks], ((j + 1) >> 1) & 1, abort);
+              ok = mbar_wait_warp(&bar->k_full[ks], ((j + 1) >> 1) & 1, abort);
               if (!ok) break;
               tc_fence_after();
             }
-            issue_qk(i, ks);
-            if (i == 1) umma_commit(&bar->k_empty[ks]);
+            if (elect_one()) {
+              issue_qk(i, ks);
+              if (i == 1) umma_commit(&bar->k_empty[ks]);
+            }
+            __syncwarp();
           }
         }
       }
     }
   } else {
     // ------------------------------------------------------------ softmax + epilogue, one row per thread
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int i = warp >> 2;                   // which MMA tile / head
     const int r = (warp & 3) * 32 + lane;      // row inside the tile == TMEM lane
     const int t = m0 + r;

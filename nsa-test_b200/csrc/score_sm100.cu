@@ -113,53 +113,66 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tmem = bar->tmem_base;
   // three warpgroups: 0 and 1 compute (even / odd steps), 2 holds the TMA and UMMA warps.  The compute groups need
   // far more registers than the launch-time split gives them, the third group far fewer.
-  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
 
-  if (warp >= 10) {
+  const bool poisoned = p.timeouts && *(volatile const int*)p.timeouts != 0;  // a block gave up on a wait earlier: skip
+  if (warp >= 10 || poisoned) {
     // idle half of the third warpgroup
   } else if (warp == 8) {
-    if (lane == 0) {
-      bool ok = true;
-      int kissued = 0, qissued = 0;
-      for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
-        const int within = step % steps_per_pass, kt = within / hpg, hh = within % hpg;
-        if (hh == 0) {
-          const int kidx = step / hpg;  // K tile loads so far
-          ok = mbar_wait(&bar->k_empty, (kidx & 1) ^ 1, abort);
-          if (!ok) break;
+    // producer: the warp walks the schedule uniformly, one elected lane issues the copies
+    bool ok = true;
+    int kissued = 0, qissued = 0;
+    int kt = 0, hh = 0;
+    for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
+      if (hh == 0) {
+        const int kidx = kissued;  // K tile loads so far
+        ok = mbar_wait_warp(&bar->k_empty, (kidx & 1) ^ 1, abort);
+        if (!ok) break;
+        if (elect_one()) {
           mbar_arrive_expect_tx(&bar->k_full, 2 * kK);
           for (int hf = 0; hf < 2; ++hf) {
             tma_load_2d(&tmKhi, &bar->k_full, sKhi + hf * (DK * 128), kt * 128 + hf * 64, bg * DK);
             tma_load_2d(&tmKlo, &bar->k_full, sKlo + hf * (DK * 128), kt * 128 + hf * 64, bg * DK);
           }
-          kissued = kidx + 1;
         }
-        const int s = step & 1;
-        ok = mbar_wait(&bar->q_empty[s], ((step >> 1) & 1) ^ 1, abort);
-        if (!ok) break;
+        __syncwarp();
+        kissued = kidx + 1;
+      }
+      const int s = step & 1;
+      ok = mbar_wait_warp(&bar->q_empty[s], ((step >> 1) & 1) ^ 1, abort);
+      if (!ok) break;
+      if (elect_one()) {
         mbar_arrive_expect_tx(&bar->q_full[s], kQ);
         for (int c = 0; c < DK / 64; ++c)
           tma_load_2d(&tmQ, &bar->q_full[s], sQ + s * kQ + c * 16384, c * 64, (b * p.H + g * hpg + hh) * p.T + m0);
-        qissued = step + 1;
       }
-      if (!ok) {
-        if (kissued > 0) mbar_wait(&bar->k_full, (kissued - 1) & 1, abort);
-        for (int st = max(0, qissued - 2); st < qissued; ++st) mbar_wait(&bar->q_full[st & 1], (st >> 1) & 1, abort);
+      __syncwarp();
+      qissued = step + 1;
+      if (++hh == hpg) {
+        hh = 0;
+        if (++kt == ntiles) kt = 0;  // second pass starts over
       }
     }
+    if (!ok && lane == 0) {
+      if (kissued > 0) mbar_wait(&bar->k_full, (kissued - 1) & 1, abort);
+      for (int st = max(0, qissued - 2); st < qissued; ++st) mbar_wait(&bar->q_full[st & 1], (st >> 1) & 1, abort);
+    }
   } else if (warp == 9) {
-    if (lane == 0) {
-      constexpr uint32_t idS = idesc_bf16(128, 128, 0, 1);
-      const uint64_t dKhi = smem_desc_sw128(smem_u32(sKhi), DK * 128, 1024);
-      const uint64_t dKlo = smem_desc_sw128(smem_u32(sKlo), DK * 128, 1024);
-      bool ok = true;
-      for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
-        const int hh = step % hpg, s = step & 1;
-        if (hh == 0) ok = mbar_wait(&bar->k_full, (step / hpg) & 1, abort);
-        ok = ok && mbar_wait(&bar->q_full[s], (step >> 1) & 1, abort) && mbar_wait(&bar->s_free[s], ((step >> 1) & 1) ^ 1, abort);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * kQ), 16, 1024);
+    // UMMA issuer: warp-uniform loop, one elected lane issues
+    constexpr uint32_t idS = idesc_bf16(128, 128, 0, 1);
+    const uint64_t dKhi = smem_desc_sw128(smem_u32(sKhi), DK * 128, 1024);
+    const uint64_t dKlo = smem_desc_sw128(smem_u32(sKlo), DK * 128, 1024);
+    bool ok = true;
+    int hh = 0, ktiles = 0;
+    for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
+      const int s = step & 1;
+      if (hh == 0) ok = mbar_wait_warp(&bar->k_full, ktiles & 1, abort);
+      ok = ok && mbar_wait_warp(&bar->q_full[s], (step >> 1) & 1, abort) &&
+           mbar_wait_warp(&bar->s_free[s], ((step >> 1) & 1) ^ 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * kQ), 16, 1024);
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
           umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dKhi, kk * 2048), idS, kk > 0);
@@ -170,12 +183,17 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         umma_commit(&bar->q_empty[s]);
         if (hh == hpg - 1) umma_commit(&bar->k_empty);
       }
+      __syncwarp();
+      if (++hh == hpg) {
+        hh = 0;
+        ++ktiles;
+      }
     }
   } else {
     // Group 0 takes the even steps (even heads), group 1 the odd ones; each sums the probabilities of its heads.
     // After its last head of a key tile group 1 parks its sums in TMEM columns [256,384); group 0 adds them to its
     // own, applies the stencil and feeds the top-n list, while group 1 is already on the next tile.
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane, t = m0 + r;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;

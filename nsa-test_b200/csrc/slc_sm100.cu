@@ -123,19 +123,10 @@ __global__ void to_token_major_kernel(const __nv_bfloat16* __restrict__ in, __nv
   if (lane < W / 8) dst[lane] = src[lane];
 }
 
-// One chunk = up to qpc queries; query qi fills rows [qi*hpg, (qi+1)*hpg) of the 128-row K-major swizzled tile.
+// One chunk = up to qpc queries; query qi fills rows [qi*hpg, (qi+1)*hpg) of the 128-row K-major swizzled tiles.
 // Unused query slots are loaded from beyond the tensor (TMA fills zeros), so every chunk delivers the same byte count.
-// Called by a whole warp: lane qi fetches its query's inverse-index entry and issues that query's tile loads, so the
-// entry loads of a chunk are one coalesced request instead of a chain of dependent ones.
-template <int WIDTH>
-__device__ __forceinline__ void tma_gather_chunk(const CUtensorMap* tm, uint64_t* bar, uint8_t* dst, const int* entries, int cnt,
-                                                 int qpc, int hpg, int64_t bgT, int oob_row, int lane) {
-  for (int qi = lane; qi < qpc; qi += 32) {
-    const int row = qi < cnt ? (int)((bgT + (entries[qi] & 0xFFFFFF)) * hpg) : oob_row;
-#pragma unroll
-    for (int c = 0; c < WIDTH / 64; ++c) tma_load_2d(tm, bar, dst + c * 16384 + qi * hpg * 128, c * 64, row);
-  }
-}
+// Lane qi of the producer warp fetches its query's inverse-index entry and issues that query's tile loads, so the entry
+// loads of a chunk are one coalesced request instead of a chain of dependent ones.
 
 template <int DK, int DV>
 __global__ void __launch_bounds__(320, 1)
@@ -154,7 +145,8 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const int* ent = p.csr_t + (int64_t)bg * p.Tq * p.nslots;
   const int e0 = blockIdx.x * kEntriesPerCta;
   const int qpc = 128 / p.hpg;
-  const bool has_work = e0 < off[p.nblk];
+  // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
+  const bool has_work = e0 < off[p.nblk] && !(p.timeouts && *(volatile const int*)p.timeouts != 0);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -473,7 +465,8 @@ __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part,
 template <int DK, int DV>
 struct SlcDqSmem {
   static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2, kdO = 128 * DV * 2;
-  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, kStage = kQ + kdO, oBar = oSt + 2 * kStage;
+  static constexpr int kOut = 8 * 2048;  // per compute warp: 32 rows x 32 bf16 columns being transposed for coalesced stores
+  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, kStage = kQ + kdO, oOut = oSt + 2 * kStage, oBar = oOut + kOut;
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct SlcDqBarriers {
@@ -498,7 +491,8 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   const int* ent = p.csr_t + (int64_t)bg * p.Tq * p.nslots;
   const int e0 = blockIdx.x * kEntriesPerCta;
   const int qpc = 128 / p.hpg;
-  const bool has_work = e0 < off[p.nblk];
+  // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
+  const bool has_work = e0 < off[p.nblk] && !(p.timeouts && *(volatile const int*)p.timeouts != 0);
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->kv_full, 1);
@@ -525,54 +519,62 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
   if (!has_work) {
   } else if (warp == 9) {
-    {
-      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-      const int oob_row = p.B * p.H * p.Tq;
-      bool ok = true;
-      int c = 0, kvidx = -1, last_blk = -1;
-      for (; !w.done(); w.next(), ++c) {
-        const int s = c & 1;
-        if (lane == 0) {
-          if (w.blk != last_blk) {
-            ok = mbar_wait(&bar->kv_empty, ((kvidx + 1) & 1) ^ 1, abort);
-            if (ok) {
-              mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
-              tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
-              for (int cc = 0; cc < DV / 64; ++cc)
-                tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
-            }
-          }
-          if (ok) ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
-          if (ok) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
-        }
-        if (w.blk != last_blk) { last_blk = w.blk; ++kvidx; }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+    // producer warp: K/V block and gathered Q / dO rows by TMA; lane qi fetches and issues query qi of the chunk
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    const int oob_row = p.B * p.H * p.Tq;
+    bool ok = true;
+    int c = 0, kvidx = -1, last_blk = -1;
+    for (; !w.done(); w.next(), ++c) {
+      const int s = c & 1;
+      const int cnt = w.count();
+      int row = oob_row;
+      if (lane < cnt) row = (int)(((int64_t)bg * p.Tq + (ent[w.e + lane] & 0xFFFFFF)) * p.hpg);
+      if (w.blk != last_blk) {
+        last_blk = w.blk;
+        ++kvidx;
+        ok = mbar_wait_warp(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
         if (!ok) break;
-        tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], sSt + s * SM::kStage, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row, lane);
-        tma_gather_chunk<DV>(&tmdOt, &bar->q_full[s], sSt + s * SM::kStage + SM::kQ, ent + w.e, w.count(), qpc, p.hpg,
-                             (int64_t)bg * p.Tq, oob_row, lane);
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
+          tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
+          for (int cc = 0; cc < DV / 64; ++cc)
+            tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
+        }
       }
-      if (!ok && lane == 0) {
-        if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
-        for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
+      ok = mbar_wait_warp(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
+      if (!ok) break;
+      if (lane == 0) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
+      __syncwarp();
+      for (int qi = lane; qi < qpc; qi += 32) {
+        const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
+        uint8_t* dst = sSt + s * SM::kStage + qi * p.hpg * 128;
+#pragma unroll
+        for (int cc = 0; cc < DK / 64; ++cc) tma_load_2d(&tmQt, &bar->q_full[s], dst + cc * 16384, cc * 64, r2);
+#pragma unroll
+        for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
       }
     }
+    if (!ok && lane == 0) {
+      if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
+      for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
+    }
   } else if (warp == 8) {
-    if (lane == 0) {
-      constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);    // Q rows x K block (keys contiguous)
-      constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);   // dO rows x V block read K-major (dv contiguous)
-      constexpr uint32_t iddQh = idesc_bf16(128, DK / 2, 0, 0);   // dS (TMEM) x half of the K block's dk rows, read K-major
-      const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024), dKk = dKmn;
-      const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
-      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-      bool ok = true;
-      int c = 0, kvidx = 0, last_blk = w.blk;
-      auto issue_sdp = [&](int cc) -> bool {
-        const int s = cc & 1;
-        if (!mbar_wait(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
-        tc_fence_after();
-        const uint64_t dQ = smem_desc_sw128(smem_u32(sSt + s * SM::kStage), 16, 1024);
-        const uint64_t ddO = smem_desc_sw128(smem_u32(sSt + s * SM::kStage + SM::kQ), 16, 1024);
+    // UMMA issuer: warp-uniform loop, one elected lane issues
+    constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);    // Q rows x K block (keys contiguous)
+    constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);   // dO rows x V block read K-major (dv contiguous)
+    constexpr uint32_t iddQh = idesc_bf16(128, DK / 2, 0, 0);   // dS (TMEM) x half of the K block's dk rows, read K-major
+    const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024), dKk = dKmn;
+    const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    bool ok = true;
+    int c = 0, kvidx = 0, last_blk = w.blk;
+    auto issue_sdp = [&](int cc) -> bool {
+      const int s = cc & 1;
+      if (!mbar_wait_warp(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
+      tc_fence_after();
+      const uint64_t dQ = smem_desc_sw128(smem_u32(sSt + s * SM::kStage), 16, 1024);
+      const uint64_t ddO = smem_desc_sw128(smem_u32(sSt + s * SM::kStage + SM::kQ), 16, 1024);
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
           umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
@@ -582,59 +584,84 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                   desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP, kk > 0);
         umma_commit(&bar->sdp_full[s]);
         umma_commit(&bar->q_empty[s]);
-        return true;
-      };
-      ok = mbar_wait(&bar->kv_full, 0, abort) && issue_sdp(0);
-      while (ok && !w.done()) {
-        const int cur = c;
-        w.next();
-        const bool more = !w.done();
-        const bool same_blk = more && w.blk == last_blk;
-        if (same_blk) ok = issue_sdp(cur + 1);  // look ahead while this chunk's dS is being computed
-        if (!ok) break;
-        ok = mbar_wait(&bar->ds_full[cur & 1], (cur >> 1) & 1, abort);
-        // the single dQ accumulator is drained by the epilogue of the previous chunk (other group) one column half at
-        // a time; each half is refilled as soon as it has been read
-        if (ok && cur > 0) ok = mbar_wait(&bar->dq_read_lo[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
-        if (!ok) break;
-        tc_fence_after();
+      }
+      __syncwarp();
+      return true;
+    };
+    ok = mbar_wait_warp(&bar->kv_full, 0, abort) && issue_sdp(0);
+    while (ok && !w.done()) {
+      const int cur = c;
+      w.next();
+      const bool more = !w.done();
+      const bool same_blk = more && w.blk == last_blk;
+      if (same_blk) ok = issue_sdp(cur + 1);  // look ahead while this chunk's dS is being computed
+      if (!ok) break;
+      ok = mbar_wait_warp(&bar->ds_full[cur & 1], (cur >> 1) & 1, abort);
+      // the single dQ accumulator is drained by the epilogue of the previous chunk (other group) one column half at
+      // a time; each half is refilled as soon as it has been read
+      if (ok && cur > 0) ok = mbar_wait_warp(&bar->dq_read_lo[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ts(tmem + cdQ, tmem + (cur & 1) * 128 + kk * 8, desc_advance(dKk, kk * 32), iddQh, kk > 0);
-        if (cur > 0) ok = mbar_wait(&bar->dq_read_hi[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
-        if (!ok) break;
-        tc_fence_after();
+      }
+      __syncwarp();
+      if (cur > 0) ok = mbar_wait_warp(&bar->dq_read_hi[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ts(tmem + cdQ + DK / 2, tmem + (cur & 1) * 128 + kk * 8, desc_advance(dKk, (DK / 2) * 128 + kk * 32), iddQh, kk > 0);
         umma_commit(&bar->dq_full[cur & 1]);
-        if (more && !same_blk) {
-          // the single K/V slot is reloaded: everything issued so far must have finished with it
-          umma_commit(&bar->kv_empty);
-          last_blk = w.blk;
-          ++kvidx;
-          ok = mbar_wait(&bar->kv_full, kvidx & 1, abort) && issue_sdp(cur + 1);
-        }
-        ++c;
+        // when the single K/V slot is reloaded, everything issued so far must have finished with it
+        if (more && !same_blk) umma_commit(&bar->kv_empty);
       }
+      __syncwarp();
+      if (more && !same_blk) {
+        last_blk = w.blk;
+        ++kvidx;
+        ok = mbar_wait_warp(&bar->kv_full, kvidx & 1, abort) && issue_sdp(cur + 1);
+      }
+      ++c;
     }
   } else {
     const int grp = warp >> 2;
     const int r = (warp & 3) * 32 + lane;
     const int qi = r / p.hpg, hh = r % p.hpg;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    // dQ partials go through a per-warp staging area (32 rows x 64 bytes, 16-byte pieces rotated by the row) so that
+    // a store instruction writes whole 64-byte runs of 8 rows instead of one 16-byte piece of 32 rows
+    uint8_t* stage = smem + SM::oOut + warp * 2048;
+    const int srow_l = lane >> 2, spiece = lane & 3;  // read-back role: row within a group of 8, 16-byte piece
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     bool ok = true;
-    int c = 0;
-    for (; !w.done() && ok; w.next(), ++c) {
-      if ((c & 1) != grp) continue;
+    if (grp == 1 && !w.done()) w.next();
+    // this group's next chunk: entry and backward statistics are fetched one chunk ahead
+    int entry_next = 0;
+    float lse_next = CUDART_INF_F, D_next = 0.f;
+    auto fetch = [&]() {
+      entry_next = 0; lse_next = CUDART_INF_F; D_next = 0.f;
+      if (!w.done() && qi < w.count()) {
+        entry_next = ent[w.e + qi];
+        const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + (entry_next & 0xFFFFFF);
+        lse_next = p.lse2[srow];
+        D_next = p.D[srow];
+      }
+    };
+    fetch();
+    for (int c = grp; !w.done() && ok; c += 2) {
       const int buf = grp, it = c >> 1;
       const bool valid = qi < w.count();
-      const int entry = valid ? ent[w.e + qi] : 0;
+      const int entry = entry_next;
+      const float lse2 = lse_next, Dr = D_next;
       const int t = entry & 0xFFFFFF, slot = entry >> 24;
-      const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + t;
-      const float lse2 = valid ? p.lse2[srow] : CUDART_INF_F, Dr = valid ? p.D[srow] : 0.f;
       const int chi = t - w.blk * 64;
+      w.next();
+      if (!w.done()) w.next();
+      fetch();
       ok = mbar_wait(&bar->sdp_full[buf], it & 1, abort);
       if (!ok) break;
       tc_fence_after();
@@ -658,36 +685,44 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bar->ds_full[buf]);
+      const int prow = valid ? (int)((((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh) : -1;
       ok = mbar_wait(&bar->dq_full[buf], it & 1, abort);
       if (!ok) break;
       tc_fence_after();
-      const int64_t prow = (((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh;
-      __nv_bfloat16* dst = p.dq_part + prow * DK;
 #pragma unroll
       for (int cc = 0; cc < DK / 32; ++cc) {
         uint32_t ov[32];
         tmem_ld32(tmem + lane_base + cdQ + cc * 32, ov);
         tc_wait_ld();
-        if (valid) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            uint4 wv;
-            __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[e]), __uint_as_float(ov[e + 1]));
-            __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2]), __uint_as_float(ov[e + 3]));
-            __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 4]), __uint_as_float(ov[e + 5]));
-            __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[e + 6]), __uint_as_float(ov[e + 7]));
-            wv.x = *reinterpret_cast<uint32_t*>(&a0); wv.y = *reinterpret_cast<uint32_t*>(&a1);
-            wv.z = *reinterpret_cast<uint32_t*>(&a2); wv.w = *reinterpret_cast<uint32_t*>(&a3);
-            *reinterpret_cast<uint4*>(dst + cc * 32 + e) = wv;
-          }
-        }
         if (cc == DK / 64 - 1) {
           tc_fence_before();
           mbar_arrive(&bar->dq_read_lo[buf]);
         }
+        if (cc == DK / 32 - 1) {
+          tc_fence_before();
+          mbar_arrive(&bar->dq_read_hi[buf]);
+        }
+        __syncwarp();  // the previous 32 columns have been read back
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 wv;
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[8 * j]), __uint_as_float(ov[8 * j + 1]));
+          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[8 * j + 2]), __uint_as_float(ov[8 * j + 3]));
+          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[8 * j + 4]), __uint_as_float(ov[8 * j + 5]));
+          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[8 * j + 6]), __uint_as_float(ov[8 * j + 7]));
+          wv.x = *reinterpret_cast<uint32_t*>(&a0); wv.y = *reinterpret_cast<uint32_t*>(&a1);
+          wv.z = *reinterpret_cast<uint32_t*>(&a2); wv.w = *reinterpret_cast<uint32_t*>(&a3);
+          *reinterpret_cast<uint4*>(stage + lane * 64 + (((j + (lane >> 1)) & 3) << 4)) = wv;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rr = i * 8 + srow_l;  // row of this warp whose piece this lane forwards
+          const int grow = __shfl_sync(0xffffffffu, prow, rr);
+          const uint4 wv = *reinterpret_cast<const uint4*>(stage + rr * 64 + (((spiece + (rr >> 1)) & 3) << 4));
+          if (grow >= 0) *reinterpret_cast<uint4*>(p.dq_part + (int64_t)grow * DK + cc * 32 + spiece * 8) = wv;
+        }
       }
-      tc_fence_before();
-      mbar_arrive(&bar->dq_read_hi[buf]);
     }
   }
   tc_fence_before();
@@ -775,7 +810,8 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const int* ent = p.csr_t + (int64_t)bg * p.Tq * p.nslots;
   const int e0 = blockIdx.x * kEntriesPerCta;
   const int qpc = 128 / p.hpg;
-  const bool has_work = e0 < off[p.nblk];
+  // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
+  const bool has_work = e0 < off[p.nblk] && !(p.timeouts && *(volatile const int*)p.timeouts != 0);
   const int nseg = gridDim.x + p.nblk;
 
   if (threadIdx.x == 0) {
@@ -802,45 +838,60 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 
   if (!has_work) {
   } else if (warp == 5) {
-    // producer warp: lane 0 drives TMA (K/V block, gathered Q and dO rows); all lanes fetch the rows' statistics
+    // producer warp: K/V block and gathered Q / dO rows by TMA (lane qi issues query qi); all lanes fetch the rows' statistics
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     const int oob_row = p.B * p.H * p.Tq;
     bool ok = true;
     int c = 0, kvidx = -1, last_blk = -1;
     for (; !w.done(); w.next(), ++c) {
+      const int cnt = w.count();
+      // entries and statistics of this chunk are fetched before the stage is free
+      int row = oob_row;
+      if (lane < cnt) row = (int)(((int64_t)bg * p.Tq + (ent[w.e + lane] & 0xFFFFFF)) * p.hpg);
+      float st_l[4], st_d[4];
+      int st_t[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rr = lane + 32 * i, qi = rr / p.hpg, hh = rr % p.hpg;
+        const bool valid = qi < cnt;
+        st_t[i] = valid ? (ent[w.e + qi] & 0xFFFFFF) : -1;  // -1: row not in use
+        const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + max(st_t[i], 0);
+        st_l[i] = valid ? p.lse2[srow] : CUDART_INF_F;
+        st_d[i] = valid ? p.D[srow] : 0.f;
+      }
       if (w.blk != last_blk) {
         last_blk = w.blk;
         ++kvidx;
-        if (lane == 0) {
-          ok = mbar_wait(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
-          if (ok) {
-            mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
-            tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
-            for (int cc = 0; cc < DV / 64; ++cc)
-              tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        ok = mbar_wait_warp(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
         if (!ok) break;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
+          tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
+          for (int cc = 0; cc < DV / 64; ++cc)
+            tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
+        }
       }
       const int s = c & 1;
-      if (lane == 0) ok = mbar_wait(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = mbar_wait_warp(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
       if (!ok) break;
       uint8_t* st = sSt + s * SM::kStage;
       if (lane == 0) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
       __syncwarp();
-      tma_gather_chunk<DK>(&tmQt, &bar->q_full[s], st, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row, lane);
-      tma_gather_chunk<DV>(&tmdOt, &bar->q_full[s], st + SM::kQ, ent + w.e, w.count(), qpc, p.hpg, (int64_t)bg * p.Tq, oob_row, lane);
+      for (int qi = lane; qi < qpc; qi += 32) {
+        const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
+        uint8_t* dst = st + qi * p.hpg * 128;
+#pragma unroll
+        for (int cc = 0; cc < DK / 64; ++cc) tma_load_2d(&tmQt, &bar->q_full[s], dst + cc * 16384, cc * 64, r2);
+#pragma unroll
+        for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
+      }
       float* stat = reinterpret_cast<float*>(st + SM::kQ + SM::kdO);
-      for (int rr = lane; rr < 128; rr += 32) {
-        const int qi = rr / p.hpg, hh = rr % p.hpg;
-        const bool valid = qi < w.count();
-        const int t = valid ? (ent[w.e + qi] & 0xFFFFFF) : -1;
-        const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + max(t, 0);
-        stat[rr] = valid ? p.lse2[srow] : CUDART_INF_F;
-        stat[128 + rr] = valid ? p.D[srow] : 0.f;
-        reinterpret_cast<int*>(stat)[256 + rr] = t;  // -1: row not in use
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rr = lane + 32 * i;
+        stat[rr] = st_l[i];
+        stat[128 + rr] = st_d[i];
+        reinterpret_cast<int*>(stat)[256 + rr] = st_t[i];
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar->q_full[s]);
@@ -850,41 +901,45 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
     }
   } else if (warp == 4) {
-    if (lane == 0) {
-      constexpr uint32_t idST = idesc_bf16(64, 64, 1, 0);    // K block as A (keys contiguous) x Q rows (K-major)
-      constexpr uint32_t iddPT = idesc_bf16(64, 64, 0, 0);   // V block as A (K-major) x dO rows (K-major)
-      constexpr uint32_t iddV = idesc_bf16(64, DV, 0, 1);    // P^T (TMEM) x dO rows (dv contiguous)
-      constexpr uint32_t iddK = idesc_bf16(64, DK, 0, 1);    // dS^T (TMEM) x Q rows (dk contiguous)
-      const uint64_t dKa = smem_desc_sw128(smem_u32(sK), 16, 1024);
-      const uint64_t dVa = smem_desc_sw128(smem_u32(sV), 16, 1024);
-      ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-      bool ok = true;
-      int c = 0, kvidx = -1, last_blk = -1, seg = 0, half_idx = 0;
-      bool fresh = true;  // next accumulation MMA starts a new segment
-      for (; !w.done() && ok; w.next(), ++c) {
-        if (w.blk != last_blk) {
-          if (last_blk >= 0) {
-            // finish the segment of the previous block: hand the accumulators over, wait until they are read
+    // UMMA issuer: warp-uniform loop, one elected lane issues
+    constexpr uint32_t idST = idesc_bf16(64, 64, 1, 0);    // K block as A (keys contiguous) x Q rows (K-major)
+    constexpr uint32_t iddPT = idesc_bf16(64, 64, 0, 0);   // V block as A (K-major) x dO rows (K-major)
+    constexpr uint32_t iddV = idesc_bf16(64, DV, 0, 1);    // P^T (TMEM) x dO rows (dv contiguous)
+    constexpr uint32_t iddK = idesc_bf16(64, DK, 0, 1);    // dS^T (TMEM) x Q rows (dk contiguous)
+    const uint64_t dKa = smem_desc_sw128(smem_u32(sK), 16, 1024);
+    const uint64_t dVa = smem_desc_sw128(smem_u32(sV), 16, 1024);
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    bool ok = true;
+    int c = 0, kvidx = -1, last_blk = -1, seg = 0, half_idx = 0;
+    bool fresh = true;  // next accumulation MMA starts a new segment
+    for (; !w.done() && ok; w.next(), ++c) {
+      if (w.blk != last_blk) {
+        if (last_blk >= 0) {
+          // finish the segment of the previous block: hand the accumulators over, wait until they are read
+          if (elect_one()) {
             umma_commit(&bar->acc_full);
             umma_commit(&bar->kv_empty);
-            ok = mbar_wait(&bar->acc_read, seg & 1, abort);
-            if (!ok) break;
-            ++seg;
-            fresh = true;
           }
-          last_blk = w.blk;
-          ++kvidx;
-          ok = mbar_wait(&bar->kv_full, kvidx & 1, abort);
+          __syncwarp();
+          ok = mbar_wait_warp(&bar->acc_read, seg & 1, abort);
           if (!ok) break;
+          ++seg;
+          fresh = true;
         }
-        const int s = c & 1;
-        ok = mbar_wait(&bar->q_full[s], (c >> 1) & 1, abort);
+        last_blk = w.blk;
+        ++kvidx;
+        ok = mbar_wait_warp(&bar->kv_full, kvidx & 1, abort);
         if (!ok) break;
-        const uint32_t st = smem_u32(sSt + s * SM::kStage);
-        for (int hf = 0; hf < 2 && ok; ++hf, ++half_idx) {
-          const uint64_t dQk = smem_desc_sw128(st + hf * 8192, 16, 1024), dQmn = smem_desc_sw128(st + hf * 8192, 16384, 1024);
-          const uint64_t dOk = smem_desc_sw128(st + SM::kQ + hf * 8192, 16, 1024), dOmn = smem_desc_sw128(st + SM::kQ + hf * 8192, 16384, 1024);
-          tc_fence_after();
+      }
+      const int s = c & 1;
+      ok = mbar_wait_warp(&bar->q_full[s], (c >> 1) & 1, abort);
+      if (!ok) break;
+      const uint32_t st = smem_u32(sSt + s * SM::kStage);
+      for (int hf = 0; hf < 2 && ok; ++hf, ++half_idx) {
+        const uint64_t dQk = smem_desc_sw128(st + hf * 8192, 16, 1024), dQmn = smem_desc_sw128(st + hf * 8192, 16384, 1024);
+        const uint64_t dOk = smem_desc_sw128(st + SM::kQ + hf * 8192, 16, 1024), dOmn = smem_desc_sw128(st + SM::kQ + hf * 8192, 16384, 1024);
+        tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < DK / 16; ++kk)
             umma_ss(tmem + cST, desc_advance(dKa, kk * 2048), desc_advance(dQk, (kk >> 2) * 16384 + (kk & 3) * 32), idST, kk > 0);
@@ -893,20 +948,27 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             umma_ss(tmem + cdPT, desc_advance(dVa, (kk >> 2) * 8192 + (kk & 3) * 32),
                     desc_advance(dOk, (kk >> 2) * 16384 + (kk & 3) * 32), iddPT, kk > 0);
           umma_commit(&bar->stp_full);
-          ok = mbar_wait(&bar->pds_full, half_idx & 1, abort);
-          if (!ok) break;
-          tc_fence_after();
+        }
+        __syncwarp();
+        ok = mbar_wait_warp(&bar->pds_full, half_idx & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_ts(tmem + cdV, tmem + cST + kk * 8, desc_advance(dOmn, kk * 2048), iddV, !(fresh && kk == 0));
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_ts(tmem + cdK, tmem + cdPT + kk * 8, desc_advance(dQmn, kk * 2048), iddK, !(fresh && kk == 0));
-          fresh = false;
+          if (hf == 1) umma_commit(&bar->q_empty[s]);
         }
-        if (ok) umma_commit(&bar->q_empty[s]);
+        __syncwarp();
+        fresh = false;
       }
-      if (ok && last_blk >= 0) umma_commit(&bar->acc_full);
+    }
+    if (ok && last_blk >= 0) {
+      if (elect_one()) umma_commit(&bar->acc_full);
+      __syncwarp();
     }
   } else {
     // compute: warp w owns key rows 16w .. 16w+15 in its first 16 lanes (M = 64 accumulator layout)

@@ -36,7 +36,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Gives up after ~2^31 clock ticks (about a second) or as soon as another role of the
+// Bounded wait.  Gives up after ~2^28 clock ticks (over a tenth of a second; a healthy wait lasts microseconds)
+// or as soon as another role of the
 // CTA has raised *abort; on giving up it raises *abort itself and returns false.  Callers then skip
 // their remaining work and fall through to the common teardown, so the kernel always terminates.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
@@ -47,7 +48,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
-    if (clock64() - t0 > (1ll << 31)) {
+    if (clock64() - t0 > (1ll << 28)) {
       *abort = 1;
       return false;
     }
@@ -177,7 +178,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
   d |= (uint64_t)2 << 61;  // 128-byte swizzle
   return d;
 }
-__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
+// Move the start address of a descriptor.  Only the low word changes (the 14-bit address field cannot carry out
+// for any shared-memory address), so successive descriptors of an unrolled loop share their high word.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) {
+  const uint32_t lo = (uint32_t)desc + (bytes >> 4);
+  return (desc & 0xFFFFFFFF00000000ull) | (uint64_t)lo;
+}
 
 // Instruction descriptor for kind::f16, bf16 x bf16 -> fp32, dense.
 __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
