@@ -40,7 +40,7 @@ int make_tmap_bf16_2d(::CUtensorMap_st* map, const void* base, uint64_t rows, ui
 // Fused selection scoring (Eq. 8-11) on tensor cores; see score_sm100.cu.  k_cmp fp32 [B,G,dk,nbp] contiguous,
 // q bf16 [B,H,T,dk] contiguous, compressed block i ends at i*d + l - 1 for i < nb and is never visible beyond.
 bool score_sm100_supported(int H, int G, int T, int dk, int nbp, int l, int d, int lprime, int n);
-size_t score_sm100_workspace_bytes(int B, int G, int dk, int nbp);
+size_t score_sm100_workspace_bytes(int B, int G, int T, int dk, int nbp, int d, int lprime);
 int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
                      int lprime, int nb, int n, int n_fixed, float scale, void* workspace, size_t workspace_bytes,
                      cudaStream_t st);

@@ -9,15 +9,17 @@
 //   pass A  online (max, sum) of every (query, head) row -> logsumexp
 //   pass B  p = exp2(x - lse); per-key sums over the heads of the group (fp32, registers; two compute warpgroups
 //           take the even and the odd heads and their sums are added once per key tile);
-//           after the last head the l/d x l'/d stencil maps 128 keys to 128/(l'/d) selection blocks,
-//           which stream into a per-query sorted top-n list (score descending, ties to the lower id).
-// Then the forced blocks are merged in, repeats dropped, the list cut to n and padded with -1.
+//           after the last head the l/d x l'/d stencil maps 128 keys to 128/(l'/d) selection-block scores,
+//           which go to a [B,G,T,n_sel] scratch buffer (4 bytes per query and block: the only per-block data leaving the SM).
+// A second kernel (one warp per query) takes the top n of every row (score descending, ties to the lower id), merges the
+// forced blocks in, drops repeats, cuts the list to n and pads it with -1.
 #include <cuda.h>
 
 #include "attn_args.cuh"
 #include "common.cuh"
 #include "fa_sm100.cuh"
 #include "sm100_ptx.cuh"
+#include "trace.cuh"
 
 namespace nsa {
 
@@ -25,10 +27,14 @@ using namespace ptx;
 
 constexpr int kScoreMaxN = 32;
 
+NSA_TRACE_STORAGE
+// trace slot of a step: the first 64 steps of each pass
+#define NSA_TRC(step, spp) (((step) % (spp)) < 64 ? ((step) / (spp)) * 64 + ((step) % (spp)) : 128)
+
 struct ScoreParams {
-  int32_t* out;  // [B,G,T,n]
+  float* sel;    // [B,G,T,n_sel] selection-block scores (blocks beyond a query tile's last key tile are not written)
   int B, H, G, T, nbp;
-  int l, d, lprime, nb, n, n_fixed;
+  int l, d, lprime, nb, n_sel;
   float scale_log2;
   int* timeouts;
 };
@@ -49,37 +55,17 @@ struct ScoreBarriers {
   int abort;
 };
 
-// Sorted insert into a per-thread top-k list kept in shared memory ([slot][128 rows]); score descending,
-// candidates arrive in ascending id order so an equal score never displaces an earlier entry.
-__device__ __noinline__ void topn_insert(float* lst_s, int* lst_i, int r, int& cnt, int k_actual, float sc, int j) {
-  if (cnt == k_actual) {
-    if (!(sc > lst_s[(cnt - 1) * 128 + r])) return;
-  } else {
-    ++cnt;
-  }
-  int pos = cnt - 1;
-  while (pos > 0 && lst_s[(pos - 1) * 128 + r] < sc) {
-    lst_s[pos * 128 + r] = lst_s[(pos - 1) * 128 + r];
-    lst_i[pos * 128 + r] = lst_i[(pos - 1) * 128 + r];
-    --pos;
-  }
-  lst_s[pos * 128 + r] = sc;
-  lst_i[pos * 128 + r] = j;
-}
-
 template <int DK>
 __global__ void __launch_bounds__(384, 1)
 score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKhi,
                      const __grid_constant__ CUtensorMap tmKlo, const ScoreParams p, int hpg, int smem_state_off,
-                     int smem_list_off, int smem_bar_off) {
+                     int smem_bar_off) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   constexpr int kK = 128 * DK * 2, kQ = 128 * DK * 2;
   uint8_t *sKhi = smem, *sKlo = smem + kK, *sQ = smem + 2 * kK;
   float* st_m = reinterpret_cast<float*>(smem + smem_state_off);  // [hpg][128]
   float* st_l = st_m + hpg * 128;                                   // [hpg][128]
-  float* lst_s = reinterpret_cast<float*>(smem + smem_list_off);   // [n][128]
-  int* lst_i = reinterpret_cast<int*>(lst_s + p.n * 128);           // [n][128]
   ScoreBarriers* bar = reinterpret_cast<ScoreBarriers*>(smem + smem_bar_off);
   volatile int* abort = &bar->abort;
 
@@ -139,8 +125,10 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         kissued = kidx + 1;
       }
       const int s = step & 1;
+      if (lane == 0) NSA_TR(0, NSA_TRC(step, steps_per_pass), 0);
       ok = mbar_wait_warp(&bar->q_empty[s], ((step >> 1) & 1) ^ 1, abort);
       if (!ok) break;
+      if (lane == 0) NSA_TR(0, NSA_TRC(step, steps_per_pass), 1);
       if (elect_one()) {
         mbar_arrive_expect_tx(&bar->q_full[s], kQ);
         for (int c = 0; c < DK / 64; ++c)
@@ -166,10 +154,14 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     int hh = 0, ktiles = 0;
     for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
       const int s = step & 1;
+      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 0);
       if (hh == 0) ok = mbar_wait_warp(&bar->k_full, ktiles & 1, abort);
-      ok = ok && mbar_wait_warp(&bar->q_full[s], (step >> 1) & 1, abort) &&
-           mbar_wait_warp(&bar->s_free[s], ((step >> 1) & 1) ^ 1, abort);
+      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 1);
+      ok = ok && mbar_wait_warp(&bar->q_full[s], (step >> 1) & 1, abort);
+      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 2);
+      ok = ok && mbar_wait_warp(&bar->s_free[s], ((step >> 1) & 1) ^ 1, abort);
       if (!ok) break;
+      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 3);
       tc_fence_after();
       const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * kQ), 16, 1024);
       if (elect_one()) {
@@ -184,6 +176,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (hh == hpg - 1) umma_commit(&bar->k_empty);
       }
       __syncwarp();
+      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 4);
       if (++hh == hpg) {
         hh = 0;
         ++ktiles;
@@ -198,20 +191,17 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int r = (warp & 3) * 32 + lane, t = m0 + r;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int vis = t >= p.l - 1 ? min(p.nb - 1, (t - p.l + 1) / p.d) : -1;  // last visible compressed block
-    const int a_ = p.l / p.d, s_ = p.lprime / p.d;                          // a_ == 2 on this path
-    const int per_tile = 128 / s_;
-    const int n_sel = (p.nbp + s_ - 1) / s_;
-    const int k_actual = min(p.n, n_sel);
+    const int s_ = p.lprime / p.d;   // keys per selection block (a power of two on this path); l / d == 2
+    const int smask = s_ - 1, sshift = 31 - __clz(s_);
+    const int per_tile = 128 >> sshift;
+    float* srow = p.sel + ((int64_t)bg * p.T + t) * p.n_sel;
     bool ok = true;
     for (int hh = wg; hh < hpg; hh += 2) {
       st_m[hh * 128 + r] = -CUDART_INF_F;
       st_l[hh * 128 + r] = 0.f;
     }
-    int cnt = 0;
-    auto insert = [&](float sc, int j) { topn_insert(lst_s, lst_i, r, cnt, k_actual, sc, j); };
     float agg[128];     // pass A: scaled logits of the current tile; pass B: per-key probability sums over heads
     float cur = 0.f;    // running stencil sum of the selection block being assembled
-    (void)a_;
     for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
       const int pass = step / steps_per_pass, within = step % steps_per_pass, kt = within / hpg, hh = within % hpg, s = step & 1;
       if ((step & 1) != wg) continue;
@@ -221,8 +211,10 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int i = 0; i < 128; ++i) agg[i] = 0.f;
       }
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 0);
       ok = mbar_wait(&bar->s_full[s], (step >> 1) & 1, abort);
       if (!ok) break;
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 1);
       tc_fence_after();
       const bool full = chi >= 127;  // every key of this tile is visible to this row: no per-element mask
       if (pass == 0) {
@@ -243,6 +235,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         tc_fence_before();
         mbar_arrive(&bar->s_free[s]);
+        if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 2);
         if (raw_mx != -CUDART_INF_F) {
           const float mx = fmaxf(m_old, raw_mx * p.scale_log2);
           float sum0 = 0.f, sum1 = 0.f;
@@ -273,6 +266,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         tc_fence_before();
         mbar_arrive(&bar->s_free[s]);
+        if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 2);
         if (vis < 0 && kt == 0) agg[0] += 1.f;  // a row that sees no block puts all its mass on block 0
         if (wg == 1 && hh == hpg - 1) {
           // park this group's sums for group 0 (the previous tile's must have been picked up)
@@ -309,11 +303,12 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           // Eq. 9 with l = 2d: sel[j] = sum_{m<s_} (A[s_ j + m] + A[s_ j + m + 1]), adds issued in that order.
           // Streaming over the keys: key i ends the previous block when i % s_ == 0 and otherwise enters the
           // current block twice in a row; the block that straddles the tile end is finished by the next tile.
+          float* sdst = srow + (n0 >> sshift) - 1;
 #pragma unroll
           for (int i = 0; i < 128; ++i) {
             const float av = agg[i];
-            if (i % s_ == 0) {
-              if (kt > 0 || i > 0) insert(cur + av, (n0 + i) / s_ - 1);
+            if ((i & smask) == 0) {
+              if (kt > 0 || i > 0) sdst[i >> sshift] = cur + av;
               cur = av;
             } else {
               cur = (cur + av) + av;
@@ -321,27 +316,10 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
         }
       }
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 3);
     }
-    if (ok && wg == 0) {
-      insert(cur, ntiles * per_tile - 1);  // the last block's final term lies beyond every visible key: + 0
-      for (int j = ntiles * per_tile; j < n_sel && cnt < k_actual; ++j) insert(0.f, j);  // never-visible blocks, id order
-      int res[kScoreMaxN];
-      int nres = 0;
-      auto push = [&](int id) {
-        if (nres >= p.n) return;
-        for (int i = 0; i < nres; ++i)
-          if (res[i] == id) return;
-        res[nres++] = id;
-      };
-      if (p.n_fixed > 0) {
-        push(0);
-        push(t < p.lprime ? 0 : (t - p.lprime) / p.lprime);
-        push(t / p.lprime);
-      }
-      for (int i = 0; i < cnt; ++i) push(lst_i[i * 128 + r]);
-      int32_t* dst = p.out + ((int64_t)bg * p.T + t) * p.n;
-      for (int i = 0; i < p.n; ++i) dst[i] = i < nres ? res[i] : -1;
-    }
+    // the last block's final term lies beyond every visible key: + 0
+    if (ok && wg == 0) srow[ntiles * per_tile - 1] = cur;
   }
   tc_fence_before();
   __syncthreads();
@@ -349,6 +327,76 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
+  }
+}
+
+// One warp per query row: top-k of the row's n_sel block scores (score descending, ties to the lower id), then the
+// forced blocks first, repeats dropped, cut to n, padded with -1.  Scores of blocks past the last key tile of the
+// row's query tile were never written and count as 0.
+__global__ void __launch_bounds__(128)
+topn_rows_kernel(const float* __restrict__ sel, int32_t* __restrict__ out, int64_t rows, int T, int n_sel, int per_tile, int l,
+                 int d, int nb, int lprime, int n, int n_fixed) {
+  extern __shared__ float sm_rows[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + warp;
+  if (row >= rows) return;  // warps are independent: no block-wide barrier below
+  const int t = (int)(row % T);
+  const int tl = (t / 128) * 128 + 127;
+  const int kmax = tl >= l - 1 ? min(nb - 1, (tl - l + 1) / d) : -1;
+  const int lim = min(n_sel, max(1, kmax / 128 + 1) * per_tile);
+  float* v = sm_rows + warp * n_sel;
+  const float* src = sel + row * n_sel;
+  float bv = -CUDART_INF_F;
+  int bi = 0x7fffffff;
+  for (int j = lane; j < n_sel; j += 32) {
+    const float x = j < lim ? src[j] : 0.f;
+    v[j] = x;
+    if (x > bv) { bv = x; bi = j; }  // ascending j: an equal score never displaces an earlier id
+  }
+  __syncwarp();
+  const int k_actual = min(n, n_sel);
+  int mytop = -1;  // lane r keeps the r-th pick
+  for (int r = 0; r < k_actual; ++r) {
+    float wv = bv;
+    int wi = bi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+      if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
+    }
+    if (lane == r) mytop = wi;
+    if ((wi & 31) == lane) {  // the owner retires the pick and looks for its next best
+      v[wi] = -CUDART_INF_F;
+      bv = -CUDART_INF_F;
+      bi = 0x7fffffff;
+      for (int j = lane; j < n_sel; j += 32) {
+        const float x = v[j];
+        if (x > bv) { bv = x; bi = j; }
+      }
+    }
+    __syncwarp();
+  }
+  int res[kScoreMaxN];
+  int nres = 0;
+  auto push = [&](int id) {
+    if (nres >= n) return;
+    for (int i = 0; i < nres; ++i)
+      if (res[i] == id) return;
+    res[nres++] = id;
+  };
+  if (n_fixed > 0) {
+    push(0);
+    push(t < lprime ? 0 : (t - lprime) / lprime);
+    push(t / lprime);
+  }
+  for (int i = 0; i < k_actual; ++i) {
+    const int id = __shfl_sync(0xffffffffu, mytop, i);
+    push(id);
+  }
+  if (lane == 0) {
+    int32_t* dst = out + row * n;
+    for (int i = 0; i < n; ++i) dst[i] = i < nres ? res[i] : -1;
   }
 }
 
@@ -360,11 +408,19 @@ bool score_sm100_supported(int H, int G, int T, int dk, int nbp, int l, int d, i
   const int hpg = H / G;
   if (d <= 0 || l != 2 * d || lprime % d != 0 || hpg % 2 != 0) return false;
   const int s_ = lprime / d;
-  const size_t smem = 4 * (size_t)128 * dk * 2 + 2 * (size_t)hpg * 512 + 2 * (size_t)n * 512 + 256 + 1024;
-  return smem <= 227 * 1024 && T % 128 == 0 && nbp % 128 == 0 && 128 % s_ == 0 && n >= 1 && n <= kScoreMaxN;
+  const size_t smem = 4 * (size_t)128 * dk * 2 + 2 * (size_t)hpg * 512 + 256 + 1024;
+  const size_t rows_smem = 4 * (size_t)(nbp / (s_ > 0 ? s_ : 1)) * sizeof(float);
+  return smem <= 227 * 1024 && rows_smem <= 200 * 1024 && T % 128 == 0 && nbp % 128 == 0 && 128 % s_ == 0 && n >= 1 &&
+         n <= kScoreMaxN;
 }
 
-size_t score_sm100_workspace_bytes(int B, int G, int dk, int nbp) { return 2 * (((size_t)B * G * dk * nbp * 2 + 255) & ~size_t(255)); }
+static size_t al256s(size_t x) { return (x + 255) & ~size_t(255); }
+
+// bf16 hi and lo copies of the compressed keys + the [B,G,T,n_sel] block scores
+size_t score_sm100_workspace_bytes(int B, int G, int T, int dk, int nbp, int d, int lprime) {
+  const size_t n_sel = (size_t)nbp / (size_t)(lprime / d);
+  return 2 * al256s((size_t)B * G * dk * nbp * 2) + al256s((size_t)B * G * T * n_sel * sizeof(float));
+}
 
 template <int DK>
 static int launch_score_t(const CUtensorMap& tq, const CUtensorMap& thi, const CUtensorMap& tlo, const ScoreParams& p,
@@ -372,15 +428,14 @@ static int launch_score_t(const CUtensorMap& tq, const CUtensorMap& thi, const C
   const int hpg = p.H / p.G;
   const int tiles = 2 * 128 * DK * 2 + 2 * 128 * DK * 2;
   const int state_off = tiles, state_bytes = 2 * hpg * 128 * 4;
-  const int list_off = state_off + state_bytes, list_bytes = 2 * p.n * 128 * 4;
-  const int bar_off = list_off + list_bytes;
+  const int bar_off = state_off + state_bytes;
   const int dyn = bar_off + 256 + 1024;
   if (dyn > 227 * 1024) return fail(NSA_ERR_UNSUPPORTED, "score_topn: %d bytes of shared memory needed", dyn);
   auto kern = score_topn_tc_kernel<DK>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess)
     return fail(NSA_ERR_LAUNCH, "score_topn: cannot reserve shared memory");
   KernelTimer kt("score_topn_tc", st);
-  kern<<<dim3(p.T / 128, p.B * p.G), 384, dyn, st>>>(tq, thi, tlo, p, hpg, state_off, list_off, bar_off);
+  kern<<<dim3(p.T / 128, p.B * p.G), 384, dyn, st>>>(tq, thi, tlo, p, hpg, state_off, bar_off);
   return check_launch("score_topn_tc");
 }
 
@@ -388,11 +443,13 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
                      int lprime, int nb, int n, int n_fixed, float scale, void* workspace, size_t workspace_bytes,
                      cudaStream_t st) {
   if (!score_sm100_supported(H, G, T, dk, nbp, l, d, lprime, n)) return fail(NSA_ERR_UNSUPPORTED, "score_topn_sm100: unsupported shape");
-  const size_t need = score_sm100_workspace_bytes(B, G, dk, nbp);
+  const size_t need = score_sm100_workspace_bytes(B, G, T, dk, nbp, d, lprime);
   if (!workspace || workspace_bytes < need)
     return fail(NSA_ERR_WORKSPACE, "scoring needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  const size_t key_bytes = al256s((size_t)B * G * dk * nbp * 2);
   __nv_bfloat16* hi = (__nv_bfloat16*)workspace;
-  __nv_bfloat16* lo = (__nv_bfloat16*)((char*)workspace + need / 2);
+  __nv_bfloat16* lo = (__nv_bfloat16*)((char*)workspace + key_bytes);
+  float* sel = (float*)((char*)workspace + 2 * key_bytes);
   const int64_t nk = (int64_t)B * G * dk * nbp;
   {
     KernelTimer kt("score_split_keys", st);
@@ -403,14 +460,26 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
   if (int rc = make_tmap_bf16_2d(&tq, q, (uint64_t)B * H * T, dk, 128)) return rc;
   if (int rc = make_tmap_bf16_2d(&thi, hi, (uint64_t)B * G * dk, nbp, dk)) return rc;
   if (int rc = make_tmap_bf16_2d(&tlo, lo, (uint64_t)B * G * dk, nbp, dk)) return rc;
+  const int s_ = lprime / d, n_sel = nbp / s_;
   ScoreParams p;
-  p.out = out;
-  p.B = B; p.H = H; p.G = G; p.T = T; p.nbp = nbp; p.l = l; p.d = d; p.lprime = lprime; p.nb = nb; p.n = n; p.n_fixed = n_fixed;
+  p.sel = sel;
+  p.B = B; p.H = H; p.G = G; p.T = T; p.nbp = nbp; p.l = l; p.d = d; p.lprime = lprime; p.nb = nb; p.n_sel = n_sel;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.timeouts = fa_timeout_counter();
-  if (dk == 192) return launch_score_t<192>(tq, thi, tlo, p, st);
-  if (dk == 128) return launch_score_t<128>(tq, thi, tlo, p, st);
-  return launch_score_t<64>(tq, thi, tlo, p, st);
+  int rc;
+  if (dk == 192) rc = launch_score_t<192>(tq, thi, tlo, p, st);
+  else if (dk == 128) rc = launch_score_t<128>(tq, thi, tlo, p, st);
+  else rc = launch_score_t<64>(tq, thi, tlo, p, st);
+  if (rc) return rc;
+  const int64_t rows = (int64_t)B * G * T;
+  const size_t sm = 4 * (size_t)n_sel * sizeof(float);
+  if (cudaFuncSetAttribute(topn_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
+    return fail(NSA_ERR_LAUNCH, "score_topn: cannot reserve shared memory for the row selection");
+  KernelTimer kt("score_topn_rows", st);
+  topn_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, sm, st>>>(sel, out, rows, T, n_sel, 128 / s_, l, d, nb, lprime, n, n_fixed);
+  return check_launch("score_topn_rows");
 }
 
 }  // namespace nsa
+
+NSA_TRACE_READER(nsa_trace_read_score)

@@ -183,7 +183,7 @@ extern "C" NSA_API size_t nsa_score_topn_workspace_bytes(int B, int H, int G, in
                                                          int n, int dtype) {
   if (B <= 0 || G <= 0 || dtype != NSA_BF16 || nsa::kernel_family() != 0 || !score_sm100_supported(H, G, T, dk, nbp, l, d, l_prime, n))
     return 256;
-  return score_sm100_workspace_bytes(B, G, dk, nbp);
+  return score_sm100_workspace_bytes(B, G, T, dk, nbp, d, l_prime);
 }
 
 extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const float* k_cmp, const int32_t* block_ends,

@@ -21,6 +21,7 @@
 #include "fa_sm100.cuh"
 #include "slc_sm100.cuh"
 #include "sm100_ptx.cuh"
+#include "trace.cuh"
 
 namespace nsa {
 
@@ -30,16 +31,7 @@ constexpr int kEntriesPerCta = 1024;  // inverse-index entries handled by one CT
 constexpr float kLn2f = 0.6931471805599453f;
 constexpr float kLog2ef = 1.4426950408889634f;
 
-// Optional timeline probe for development builds (-DNSA_TRACE): one CTA records clock64() at role hand-offs.
-#ifdef NSA_TRACE
-__device__ long long g_trace[4][128][16];
-#define NSA_TR(role, c, ev)                                                              \
-  do {                                                                                   \
-    if (blockIdx.x == 3 && blockIdx.y == 0 && (c) < 128) g_trace[role][c][ev] = clock64(); \
-  } while (0)
-#else
-#define NSA_TR(role, c, ev)
-#endif
+NSA_TRACE_STORAGE
 
 struct SlcParams {
   const __nv_bfloat16* q;      // [B,H,Tq,dk]
@@ -1267,8 +1259,4 @@ int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indice
 
 }  // namespace nsa
 
-#ifdef NSA_TRACE
-extern "C" __attribute__((visibility("default"))) int nsa_trace_read(long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, nsa::g_trace, sizeof(nsa::g_trace));
-}
-#endif
+NSA_TRACE_READER(nsa_trace_read)
