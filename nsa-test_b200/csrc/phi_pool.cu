@@ -51,18 +51,34 @@ __global__ void phi_pool_bwd_tok_kernel(const float* __restrict__ a, const float
   }
 }
 
-// dc_part[bg,j,u] = sum_i [A[i*d+j,u] + C[j,u] > 0] * dhbar[i,u] / l, blocks in ascending order.
-__global__ void phi_pool_bwd_tab_kernel(const float* __restrict__ a, const float* __restrict__ c,
-                                        const float* __restrict__ dhbar, float* __restrict__ dc_part, int T_, int U,
-                                        int l, int d, int nb) {
+// dc_part[bg,j,u] = sum_i [A[i*d+j,u] + C[j,u] > 0] * dhbar[i,u] / l.  The blocks are dealt round-robin to kTabGroups
+// thread groups whose sums are added in group order, so the result does not depend on scheduling.
+constexpr int kTabGroups = 8, kTabLanes = 128;
+__global__ void __launch_bounds__(kTabGroups * kTabLanes)
+phi_pool_bwd_tab_kernel(const float* __restrict__ a, const float* __restrict__ c, const float* __restrict__ dhbar,
+                        float* __restrict__ dc_part, int T_, int U, int l, int d, int nb) {
+  __shared__ float part[kTabGroups][kTabLanes];
   const int j = blockIdx.x, bg = blockIdx.y;
+  const int ul = threadIdx.x % kTabLanes, grp = threadIdx.x / kTabLanes;
   const float inv = 1.f / (float)l;
-  for (int u = threadIdx.x; u < U; u += blockDim.x) {
-    const float cv = c[j * U + u];
+  for (int u0 = 0; u0 < U; u0 += kTabLanes) {
+    const int u = u0 + ul;
     float acc = 0.f;
-    for (int i = 0; i < nb; ++i)
-      if (a[((int64_t)bg * T_ + (int64_t)i * d + j) * U + u] + cv > 0.f) acc += dhbar[((int64_t)bg * nb + i) * U + u];
-    dc_part[((int64_t)bg * l + j) * U + u] = acc * inv;
+    if (u < U) {
+      const float cv = c[j * U + u];
+#pragma unroll 4
+      for (int i = grp; i < nb; i += kTabGroups)
+        if (a[((int64_t)bg * T_ + (int64_t)i * d + j) * U + u] + cv > 0.f) acc += dhbar[((int64_t)bg * nb + i) * U + u];
+    }
+    part[grp][ul] = acc;
+    __syncthreads();
+    if (grp == 0 && u < U) {
+      float tot = 0.f;
+#pragma unroll
+      for (int g2 = 0; g2 < kTabGroups; ++g2) tot += part[g2][ul];
+      dc_part[((int64_t)bg * l + j) * U + u] = tot * inv;
+    }
+    __syncthreads();
   }
 }
 
@@ -103,6 +119,6 @@ extern "C" NSA_API int nsa_phi_pool_bwd(const float* a, const float* c, const fl
   phi_pool_bwd_tok_kernel<<<dim3(T, B * G), 128, 0, st>>>(a, c, dhbar, dv_cmp, da, dv, T, U, dv_dim, l, d, n_blocks,
                                                           nbp);
   if (int rc = check_launch("phi_pool_bwd_tok")) return rc;
-  phi_pool_bwd_tab_kernel<<<dim3(l, B * G), 128, 0, st>>>(a, c, dhbar, dc_part, T, U, l, d, n_blocks);
+  phi_pool_bwd_tab_kernel<<<dim3(l, B * G), kTabGroups * kTabLanes, 0, st>>>(a, c, dhbar, dc_part, T, U, l, d, n_blocks);
   return check_launch("phi_pool_bwd_tab");
 }

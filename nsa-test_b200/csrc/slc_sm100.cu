@@ -388,7 +388,21 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   }
 }
 
-// merge the partials of a query in slot order: one warp per (b,h,t); lane s first fetches slot s
+// Which slots of a query's index row contribute (see slot_block): lane s decides for slot s from one load per lane,
+// repeats are found with shuffles.  Returns the ballot of contributing slots.
+__device__ __forceinline__ unsigned valid_slot_mask(const int* irow, int64_t s3, int nslots, int t, int Tk, int lprime, int lane) {
+  const int id = lane < nslots ? irow[lane * s3] : -1;
+  bool ok = id >= 0 && (int64_t)id * lprime < Tk && (int64_t)id * lprime <= t;
+  for (int s2 = 0; s2 < nslots; ++s2) {
+    const int other = __shfl_sync(0xffffffffu, id, s2);
+    if (s2 < lane && other == id) ok = false;
+  }
+  return __ballot_sync(0xffffffffu, ok);
+}
+
+// merge the partials of a query in slot order: one warp per (b,h,t).  Every load of the row (index row, statistics,
+// all slots' partial outputs) is issued before the first value is used; slots that turn out not to contribute were
+// never written and their loads are discarded.
 template <int DV>
 __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part, const float2* __restrict__ st_part,
                                        const int* __restrict__ indices, int64_t s0, int64_t s1, int64_t s2, int64_t s3,
@@ -396,38 +410,43 @@ __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part,
                                        int H, int G, int Tq, int Tk, int nslots, int lprime) {
   static_assert(DV % 64 == 0, "lanes own 2 or 4 consecutive output columns");
   constexpr int VPL = DV / 32;  // values per lane
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // consecutive warps take the heads of one (group, query): together they stream that query's contiguous block of partials
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (row >= (int64_t)B * H * Tq) return;
-  const int t = row % Tq, h = (row / Tq) % H, b = row / ((int64_t)Tq * H);
-  const int hpg = H / G, g = h / hpg, hh = h % hpg;
+  if (wid >= (int64_t)B * H * Tq) return;
+  const int hpg = H / G;
+  const int hh = wid % hpg, t = (wid / hpg) % Tq, bgi = wid / ((int64_t)hpg * Tq);
+  const int b = bgi / G, g = bgi % G, h = g * hpg + hh;
+  const int64_t row = ((int64_t)b * H + h) * Tq + t;
   const int* irow = indices + b * s0 + g * s1 + (int64_t)t * s2;
   const int64_t base = (((int64_t)(b * G + g) * Tq + t) * nslots) * hpg + hh;
   float2 st = make_float2(-CUDART_INF_F, 0.f);
-  const bool mine = lane < nslots && slot_block(irow, s3, lane, t, Tk, lprime, 1) >= 0;
-  if (mine) st = st_part[base + (int64_t)lane * hpg];
-  const unsigned validmask = __ballot_sync(0xffffffffu, mine);
-  const float mx = warp_max(st.x);
-  const float wmine = mine ? st.y * ex2(st.x - mx) : 0.f;
-  float lsum = 0.f, acc[VPL];
+  if (lane < nslots) st = st_part[base + (int64_t)lane * hpg];
+  float lsum = 0.f, mx = 0.f, wmine = 0.f, acc[VPL];
+  unsigned validmask = 0;
 #pragma unroll
   for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
-  // slots in groups of 8: all loads of a group are issued before the first value is used
-  for (int s8 = 0; s8 < nslots; s8 += 8) {
-    uint2 raw[8];
+  for (int s16 = 0; s16 < nslots; s16 += 16) {
+    uint2 raw[16];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int s = s8 + u;
+    for (int u = 0; u < 16; ++u) {
       raw[u] = make_uint2(0u, 0u);
-      if (s < nslots && ((validmask >> s) & 1)) {
-        const __nv_bfloat16* src = o_part + (base + (int64_t)s * hpg) * DV + lane * VPL;
+      if (s16 + u < nslots) {
+        const __nv_bfloat16* src = o_part + (base + (int64_t)(s16 + u) * hpg) * DV + lane * VPL;
         if (VPL == 4) raw[u] = *reinterpret_cast<const uint2*>(src);
         else raw[u].x = *reinterpret_cast<const uint32_t*>(src);
       }
     }
+    if (s16 == 0) {
+      validmask = valid_slot_mask(irow, s3, nslots, t, Tk, lprime, lane);
+      const bool mine = (validmask >> lane) & 1;
+      if (!mine) st = make_float2(-CUDART_INF_F, 0.f);
+      mx = warp_max(st.x);
+      wmine = mine ? st.y * ex2(st.x - mx) : 0.f;
+    }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int s = s8 + u;
+    for (int u = 0; u < 16; ++u) {
+      const int s = s16 + u;
       const float wgt = __shfl_sync(0xffffffffu, wmine, s & 31);
       if (s >= nslots || !((validmask >> s) & 1)) continue;
       lsum += wgt;
@@ -448,6 +467,76 @@ __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part,
     L[row] = lsum > 0.f ? logf(lsum) : -CUDART_INF_F;
     M[row] = lsum > 0.f ? mx * kLn2f : -CUDART_INF_F;
   }
+}
+
+// Same merge with the whole contiguous block of a query's partials ([slots][heads][dv]) brought into shared memory by
+// one bulk copy: one thread block per (group, query), one warp per head.  No registers are spent on loads in flight,
+// so several blocks per SM keep enough bytes on their way to saturate HBM.
+template <int DV>
+__global__ void slc_combine_fwd_bulk_kernel(const __nv_bfloat16* __restrict__ o_part, const float2* __restrict__ st_part,
+                                            const int* __restrict__ indices, int64_t s0, int64_t s1, int64_t s2, int64_t s3,
+                                            __nv_bfloat16* __restrict__ out, float* __restrict__ L, float* __restrict__ M, int B,
+                                            int H, int G, int Tq, int Tk, int nslots, int lprime, int* timeouts) {
+  constexpr int VPL = DV / 32;
+  extern __shared__ __align__(128) uint8_t sm_part[];
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  const int hpg = H / G, hh = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t q = blockIdx.x;  // (batch, group, query)
+  const int t = q % Tq, bgi = q / Tq, b = bgi / G, g = bgi % G, h = g * hpg + hh;
+  const uint32_t bytes = (uint32_t)nslots * hpg * DV * 2;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(&bar, bytes);
+    bulk_load_1d(sm_part, o_part + q * (int64_t)nslots * hpg * DV, bytes, &bar);
+  }
+  const int64_t row = ((int64_t)b * H + h) * Tq + t;
+  const int* irow = indices + b * s0 + g * s1 + (int64_t)t * s2;
+  const int64_t base = (q * nslots) * hpg + hh;
+  float2 st = make_float2(-CUDART_INF_F, 0.f);
+  if (lane < nslots) st = st_part[base + (int64_t)lane * hpg];
+  const unsigned validmask = valid_slot_mask(irow, s3, nslots, t, Tk, lprime, lane);
+  const bool mine = (validmask >> lane) & 1;
+  if (!mine) st = make_float2(-CUDART_INF_F, 0.f);
+  const float mx = warp_max(st.x);
+  const float wmine = mine ? st.y * ex2(st.x - mx) : 0.f;
+  float lsum = 0.f, acc[VPL];
+#pragma unroll
+  for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
+  const bool ok = mbar_wait_warp(&bar, 0, &abort_flag);
+  if (ok) {
+    for (int s = 0; s < nslots; ++s) {
+      const float wgt = __shfl_sync(0xffffffffu, wmine, s);
+      if (!((validmask >> s) & 1)) continue;  // never written: skip
+      lsum += wgt;
+      const uint8_t* src = sm_part + ((size_t)(s * hpg + hh) * DV + lane * VPL) * 2;
+      uint2 raw = make_uint2(0u, 0u);
+      if (VPL == 4) raw = *reinterpret_cast<const uint2*>(src);
+      else raw.x = *reinterpret_cast<const uint32_t*>(src);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      acc[0] = fmaf(wgt, a.x, acc[0]); acc[1] = fmaf(wgt, a.y, acc[1]);
+      if (VPL == 4) {
+        const float2 c2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        acc[2 % VPL] = fmaf(wgt, c2.x, acc[2 % VPL]); acc[3 % VPL] = fmaf(wgt, c2.y, acc[3 % VPL]);
+      }
+    }
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    __nv_bfloat16* dst = out + row * DV + lane * VPL;
+#pragma unroll
+    for (int c = 0; c < VPL; c += 2)
+      *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+    if (lane == 0) {
+      L[row] = lsum > 0.f ? logf(lsum) : -CUDART_INF_F;
+      M[row] = lsum > 0.f ? mx * kLn2f : -CUDART_INF_F;
+    }
+  }
+  __syncthreads();  // the copy has landed (or was given up on) before shared memory is handed back
+  if (threadIdx.x == 0 && abort_flag && timeouts) atomicAdd(timeouts, 1);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -726,45 +815,98 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   }
 }
 
-// dQ[b,h,t,:] = scale * sum of the valid slots' partials, slot order: one warp per row
+// dQ[b,h,t,:] = scale * sum of the contributing slots' partials, slot order: one warp per row; the loads of 8 slots
+// are in flight together and do not wait for the index row
 template <int DK>
 __global__ void slc_combine_dq_kernel(const __nv_bfloat16* __restrict__ dq_part, const int* __restrict__ indices, int64_t s0,
                                       int64_t s1, int64_t s2, int64_t s3, __nv_bfloat16* __restrict__ dq, int B, int H, int G,
                                       int Tq, int Tk, int nslots, int lprime, float scale) {
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // consecutive warps take the heads of one (group, query): together they stream that query's contiguous block of partials
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (row >= (int64_t)B * H * Tq) return;
-  const int t = row % Tq, h = (row / Tq) % H, b = row / ((int64_t)Tq * H);
-  const int hpg = H / G, g = h / hpg, hh = h % hpg;
+  if (wid >= (int64_t)B * H * Tq) return;
+  const int hpg = H / G;
+  const int hh = wid % hpg, t = (wid / hpg) % Tq, bgi = wid / ((int64_t)hpg * Tq);
+  const int b = bgi / G, g = bgi % G, h = g * hpg + hh;
+  const int64_t row = ((int64_t)b * H + h) * Tq + t;
   const int* irow = indices + b * s0 + g * s1 + (int64_t)t * s2;
   const int64_t base = (((int64_t)(b * G + g) * Tq + t) * nslots) * hpg + hh;
-  const bool mine = lane < nslots && slot_block(irow, s3, lane, t, Tk, lprime, 1) >= 0;
-  const unsigned validmask = __ballot_sync(0xffffffffu, mine);
+  unsigned validmask = 0;
   float acc[DK / 32];
 #pragma unroll
   for (int c = 0; c < DK / 32; ++c) acc[c] = 0.f;
-  for (int s4 = 0; s4 < nslots; s4 += 4) {   // 4 slots x DK/64 loads in flight per lane
-    uint32_t raw[4][DK / 64];
+  for (int s8 = 0; s8 < nslots; s8 += 8) {
+    uint32_t raw[8][DK / 64];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int s = s4 + u;
-      const bool on = s < nslots && ((validmask >> s) & 1);
-      const __nv_bfloat16* src = dq_part + (base + (int64_t)s * hpg) * DK;
+    for (int u = 0; u < 8; ++u) {
+      const __nv_bfloat16* src = dq_part + (base + (int64_t)(s8 + u) * hpg) * DK;
 #pragma unroll
-      for (int c = 0; c < DK / 64; ++c) raw[u][c] = on ? *reinterpret_cast<const uint32_t*>(src + c * 64 + lane * 2) : 0u;
+      for (int c = 0; c < DK / 64; ++c) raw[u][c] = s8 + u < nslots ? *reinterpret_cast<const uint32_t*>(src + c * 64 + lane * 2) : 0u;
     }
+    if (s8 == 0) validmask = valid_slot_mask(irow, s3, nslots, t, Tk, lprime, lane);
 #pragma unroll
-    for (int u = 0; u < 4; ++u)   // a skipped slot adds exact zeros: the sum is unchanged
+    for (int u = 0; u < 8; ++u) {
+      if (s8 + u >= nslots || !((validmask >> (s8 + u)) & 1)) continue;  // never written: discard
 #pragma unroll
       for (int c = 0; c < DK / 64; ++c) {
         const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u][c]));
         acc[2 * c] += a.x;
         acc[2 * c + 1] += a.y;
       }
+    }
   }
 #pragma unroll
   for (int c = 0; c < DK / 64; ++c)
     *reinterpret_cast<__nv_bfloat162*>(dq + row * DK + c * 64 + lane * 2) = __floats2bfloat162_rn(acc[2 * c] * scale, acc[2 * c + 1] * scale);
+}
+
+// Same sum with the query's contiguous block of partials ([slots][heads][dk]) brought in by one bulk copy:
+// one thread block per (group, query), one warp per head.
+template <int DK>
+__global__ void slc_combine_dq_bulk_kernel(const __nv_bfloat16* __restrict__ dq_part, const int* __restrict__ indices, int64_t s0,
+                                           int64_t s1, int64_t s2, int64_t s3, __nv_bfloat16* __restrict__ dq, int B, int H, int G,
+                                           int Tq, int Tk, int nslots, int lprime, float scale, int* timeouts) {
+  extern __shared__ __align__(128) uint8_t sm_part[];
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  const int hpg = H / G, hh = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t q = blockIdx.x;
+  const int t = q % Tq, bgi = q / Tq, b = bgi / G, g = bgi % G, h = g * hpg + hh;
+  const uint32_t bytes = (uint32_t)nslots * hpg * DK * 2;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(&bar, bytes);
+    bulk_load_1d(sm_part, dq_part + q * (int64_t)nslots * hpg * DK, bytes, &bar);
+  }
+  const int64_t row = ((int64_t)b * H + h) * Tq + t;
+  const int* irow = indices + b * s0 + g * s1 + (int64_t)t * s2;
+  const unsigned validmask = valid_slot_mask(irow, s3, nslots, t, Tk, lprime, lane);
+  float acc[DK / 32];
+#pragma unroll
+  for (int c = 0; c < DK / 32; ++c) acc[c] = 0.f;
+  const bool ok = mbar_wait_warp(&bar, 0, &abort_flag);
+  if (ok) {
+    for (int s = 0; s < nslots; ++s) {
+      if (!((validmask >> s) & 1)) continue;
+      const uint8_t* src = sm_part + (size_t)(s * hpg + hh) * DK * 2;
+#pragma unroll
+      for (int c = 0; c < DK / 64; ++c) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + (c * 64 + lane * 2) * 2));
+        acc[2 * c] += a.x;
+        acc[2 * c + 1] += a.y;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < DK / 64; ++c)
+      *reinterpret_cast<__nv_bfloat162*>(dq + row * DK + c * 64 + lane * 2) = __floats2bfloat162_rn(acc[2 * c] * scale, acc[2 * c + 1] * scale);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag && timeouts) atomicAdd(timeouts, 1);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1121,9 +1263,18 @@ static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   }
   if (int rc = check_launch("slc_fwd_sm100")) return rc;
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
+  const size_t qbytes = (size_t)p.nslots * p.hpg * DV * 2;  // one query's partials
   KernelTimer kt("slc_combine_fwd", st);
-  slc_combine_fwd_kernel<DV><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.o_part, p.st_part, indices, sidx[0], sidx[1], sidx[2],
-                                                                         sidx[3], out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64);
+  if (p.hpg <= 32 && qbytes <= 100 * 1024 && (int64_t)p.B * p.G * p.Tq < (1ll << 31)) {
+    auto kc = slc_combine_fwd_bulk_kernel<DV>;
+    if (cudaFuncSetAttribute(kc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qbytes) != cudaSuccess)
+      return fail(NSA_ERR_LAUNCH, "slc_combine_fwd: cannot reserve shared memory");
+    kc<<<(unsigned)((int64_t)p.B * p.G * p.Tq), p.hpg * 32, qbytes, st>>>(p.o_part, p.st_part, indices, sidx[0], sidx[1], sidx[2], sidx[3],
+                                                                      out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.timeouts);
+  } else {
+    slc_combine_fwd_kernel<DV><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.o_part, p.st_part, indices, sidx[0], sidx[1], sidx[2],
+                                                                           sidx[3], out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64);
+  }
   return check_launch("slc_combine_fwd");
 }
 
@@ -1203,8 +1354,17 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
   {
     KernelTimer kt("slc_combine_dq", st);
-    slc_combine_dq_kernel<DK><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.dq_part, indices, sidx[0], sidx[1], sidx[2], sidx[3], dq,
-                                                                          p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale);
+    const size_t qbytes = (size_t)p.nslots * p.hpg * DK * 2;  // one query's partials
+    if (p.hpg <= 32 && qbytes <= 100 * 1024 && (int64_t)p.B * p.G * p.Tq < (1ll << 31)) {
+      auto kc = slc_combine_dq_bulk_kernel<DK>;
+      if (cudaFuncSetAttribute(kc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qbytes) != cudaSuccess)
+        return fail(NSA_ERR_LAUNCH, "slc_combine_dq: cannot reserve shared memory");
+      kc<<<(unsigned)((int64_t)p.B * p.G * p.Tq), p.hpg * 32, qbytes, st>>>(p.dq_part, indices, sidx[0], sidx[1], sidx[2], sidx[3], dq, p.B,
+                                                                        p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale, p.timeouts);
+    } else {
+      slc_combine_dq_kernel<DK><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.dq_part, indices, sidx[0], sidx[1], sidx[2], sidx[3], dq,
+                                                                            p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale);
+    }
   }
   if (int rc = check_launch("slc_combine_dq")) return rc;
   {
