@@ -910,32 +910,62 @@ __global__ void slc_combine_dq_bulk_kernel(const __nv_bfloat16* __restrict__ dq_
 }
 
 // ------------------------------------------------------------------------------------------------
-// backward, part 2: dK/dV of each block, transposed tiles with the 64 keys on the M axis.  Per half
-// chunk (64 rows): S^T = K Q^T, dP^T = V dO^T, P^T and dS^T -> TMEM (bf16), dV += P^T dO, dK += dS^T Q.
-// The accumulators live in TMEM for as long as the CTA stays on a block and are then written as one
-// fp32 partial; slc_reduce_dkv adds the partials of a block in a fixed order.
+// backward, part 2: dK/dV of each block.  Per chunk (128 gathered rows): S = Q K^T and dP = dO V^T with the
+// rows on the M axis (one row per compute thread, statistics in registers), P and dS (bf16) are handed to
+// the tensor core through shared memory, 64 rows at a time, and the accumulators are kept transposed:
+//   dV^T [dv x 64 keys] += dO^T P,   dK^T [dk x 64 keys] += Q^T dS     (dk = 192 as an M = 128 and an M = 64 part).
+// They live in TMEM for as long as the CTA stays on a block and are then written as one fp32 partial
+// ([64 keys][dk|dv], coalesced: a warp's lanes are consecutive dk / dv indices); slc_reduce_dkv adds the
+// partials of a block in a fixed order.
 // ------------------------------------------------------------------------------------------------
 template <int DK, int DV>
 struct SlcDkvSmem {
   static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2, kdO = 128 * DV * 2;
   static constexpr int kStage = kQ + kdO + 2048;  // + lse2[128], D[128], t[128]
-  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, oBar = oSt + 2 * kStage;
+  static constexpr int kHalf = 64 * 128;          // 64 rows x 64 keys of bf16 P (or dS), 128-byte swizzle
+  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, oP = oSt + 2 * kStage, odS = oP + kHalf, oBar = odS + kHalf;
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct SlcDkvBarriers {
-  uint64_t kv_full, kv_empty, q_full[2], q_empty[2], stp_full, pds_full, acc_full, acc_read;
+  // p_free / ds_free are rings of four: a writer may arrive several hand-overs early, and a parity wait tells apart only
+  // the last two completions of one barrier
+  uint64_t kv_full, kv_empty, q_full[2], q_empty[2], sdp_full[2], sdp_free[2], p_full, p_free[4], ds_full, ds_free[4], acc_full, acc_read;
   uint32_t tmem_base;
   int abort;
 };
 
+// accumulator rows [M x 64 keys] in TMEM -> part[(key_base + key) * W + off + row]; M = 128: row = TMEM lane,
+// M = 64: 16 rows per warp in its first 16 lanes
+template <int M>
+__device__ __forceinline__ void slc_flush_rows(uint32_t taddr, float* __restrict__ part, int64_t key_base, int W, int off, int warp4,
+                                               int lane) {
+  const int row = M == 128 ? warp4 * 32 + lane : warp4 * 16 + (lane & 15);
+  const bool active = M == 128 || lane < 16;
+  const uint32_t lane_base = (uint32_t)(warp4 * 32) << 16;
+#pragma unroll
+  for (int cc = 0; cc < 2; ++cc) {
+    uint32_t ov[32];
+    tmem_ld32(taddr + lane_base + cc * 32, ov);
+    tc_wait_ld();
+    if (active) {
+      float* dst = part + (key_base + cc * 32) * W + off + row;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) dst[(int64_t)e * W] = __uint_as_float(ov[e]);
+    }
+  }
+}
+
 template <int DK, int DV>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(384, 1)
 slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmdOt, const SlcParams p) {
   using SM = SlcDkvSmem<DK, DV>;
+  constexpr int MK1 = DK >= 128 ? 128 : 64, MK2 = DK - MK1;  // dK^T as one or two accumulators
+  static_assert(MK2 == 0 || MK2 == 64, "dk is 64, 128 or 192");
+  static_assert(DV == 64 || DV == 128, "dv is 64 or 128");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sSt = smem + SM::oSt;
+  uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sSt = smem + SM::oSt, *sP = smem + SM::oP, *sdS = smem + SM::odS;
   SlcDkvBarriers* bar = reinterpret_cast<SlcDkvBarriers*>(smem + SM::oBar);
   volatile int* abort = &bar->abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -954,24 +984,35 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar->q_full[i], 2);  // TMA bytes + the statistics written by the producer warp
       mbar_init(&bar->q_empty[i], 1);
+      mbar_init(&bar->sdp_full[i], 1);
+      mbar_init(&bar->sdp_free[i], 128);
     }
-    mbar_init(&bar->stp_full, 1);
-    mbar_init(&bar->pds_full, 128);
+    mbar_init(&bar->p_full, 64);
+    mbar_init(&bar->ds_full, 64);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&bar->p_free[i], 1);
+      mbar_init(&bar->ds_free[i], 1);
+    }
     mbar_init(&bar->acc_full, 1);
-    mbar_init(&bar->acc_read, 128);
+    mbar_init(&bar->acc_read, 256);
     bar->abort = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 4) tmem_alloc(&bar->tmem_base, 512);
+  if (warp == 8) tmem_alloc(&bar->tmem_base, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
-  constexpr uint32_t cdK = 0, cdV = DK, cST = DK + DV, cdPT = DK + DV + 64;
+  // S / dP of chunk c in columns (c & 1) * 128 + {0, 64}; then the transposed accumulators
+  constexpr uint32_t cdV = 256, cdK1 = 320, cdK2 = 384;
+  // 12 warps: 8 compute, UMMA issuer, producer, 2 idle ones completing the third warpgroup, whose registers go to the
+  // compute warpgroups
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
 
-  if (!has_work) {
-  } else if (warp == 5) {
+  if (warp >= 10) {
+  } else if (!has_work) {
+  } else if (warp == 9) {
     // producer warp: K/V block and gathered Q / dO rows by TMA (lane qi issues query qi); all lanes fetch the rows' statistics
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     const int oob_row = p.B * p.H * p.Tq;
@@ -1034,99 +1075,126 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
       for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // UMMA issuer: warp-uniform loop, one elected lane issues
-    constexpr uint32_t idST = idesc_bf16(64, 64, 1, 0);    // K block as A (keys contiguous) x Q rows (K-major)
-    constexpr uint32_t iddPT = idesc_bf16(64, 64, 0, 0);   // V block as A (K-major) x dO rows (K-major)
-    constexpr uint32_t iddV = idesc_bf16(64, DV, 0, 1);    // P^T (TMEM) x dO rows (dv contiguous)
-    constexpr uint32_t iddK = idesc_bf16(64, DK, 0, 1);    // dS^T (TMEM) x Q rows (dk contiguous)
-    const uint64_t dKa = smem_desc_sw128(smem_u32(sK), 16, 1024);
-    const uint64_t dVa = smem_desc_sw128(smem_u32(sV), 16, 1024);
+    constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);     // Q rows (K-major) x K block (keys contiguous)
+    constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);    // dO rows (K-major) x V block read K-major (dv contiguous)
+    constexpr uint32_t iddV = idesc_bf16(DV, 64, 1, 1);     // dO^T (dv contiguous) x P (keys contiguous), K = gathered rows
+    constexpr uint32_t iddK1 = idesc_bf16(MK1, 64, 1, 1);   // Q^T (dk contiguous) x dS (keys contiguous)
+    constexpr uint32_t iddK2 = idesc_bf16(64, 64, 1, 1);
+    const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024);
+    const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
+    const uint64_t dPb = smem_desc_sw128(smem_u32(sP), 16, 1024);    // one 64-key MN block: LBO unused
+    const uint64_t dSb = smem_desc_sw128(smem_u32(sdS), 16, 1024);
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     bool ok = true;
-    int c = 0, kvidx = -1, last_blk = -1, seg = 0, half_idx = 0;
-    bool fresh = true;  // next accumulation MMA starts a new segment
-    for (; !w.done() && ok; w.next(), ++c) {
-      if (w.blk != last_blk) {
-        if (last_blk >= 0) {
-          // finish the segment of the previous block: hand the accumulators over, wait until they are read
-          if (elect_one()) {
-            umma_commit(&bar->acc_full);
-            umma_commit(&bar->kv_empty);
-          }
-          __syncwarp();
-          ok = mbar_wait_warp(&bar->acc_read, seg & 1, abort);
-          if (!ok) break;
-          ++seg;
-          fresh = true;
-        }
-        last_blk = w.blk;
-        ++kvidx;
-        ok = mbar_wait_warp(&bar->kv_full, kvidx & 1, abort);
-        if (!ok) break;
-      }
-      const int s = c & 1;
-      ok = mbar_wait_warp(&bar->q_full[s], (c >> 1) & 1, abort);
-      if (!ok) break;
+    int c = 0, kvidx = 0, last_blk = w.blk, seg = 0, u = 0;
+    bool fresh = true;  // the next accumulation starts a new segment
+    auto issue_sdp = [&](int cc) -> bool {
+      const int s = cc & 1;
+      if (!mbar_wait_warp(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
+      if (!mbar_wait_warp(&bar->sdp_free[s], ((cc >> 1) & 1) ^ 1, abort)) return false;  // S/dP of chunk cc-2 are in registers
+      tc_fence_after();
       const uint32_t st = smem_u32(sSt + s * SM::kStage);
-      for (int hf = 0; hf < 2 && ok; ++hf, ++half_idx) {
-        const uint64_t dQk = smem_desc_sw128(st + hf * 8192, 16, 1024), dQmn = smem_desc_sw128(st + hf * 8192, 16384, 1024);
-        const uint64_t dOk = smem_desc_sw128(st + SM::kQ + hf * 8192, 16, 1024), dOmn = smem_desc_sw128(st + SM::kQ + hf * 8192, 16384, 1024);
-        tc_fence_after();
-        if (elect_one()) {
+      const uint64_t dQ = smem_desc_sw128(st, 16, 1024), ddO = smem_desc_sw128(st + SM::kQ, 16, 1024);
+      if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < DK / 16; ++kk)
-            umma_ss(tmem + cST, desc_advance(dKa, kk * 2048), desc_advance(dQk, (kk >> 2) * 16384 + (kk & 3) * 32), idST, kk > 0);
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
 #pragma unroll
-          for (int kk = 0; kk < DV / 16; ++kk)
-            umma_ss(tmem + cdPT, desc_advance(dVa, (kk >> 2) * 8192 + (kk & 3) * 32),
-                    desc_advance(dOk, (kk >> 2) * 16384 + (kk & 3) * 32), iddPT, kk > 0);
-          umma_commit(&bar->stp_full);
-        }
+        for (int kk = 0; kk < DV / 16; ++kk)
+          umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * 16384 + (kk & 3) * 32),
+                  desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP, kk > 0);
+        umma_commit(&bar->sdp_full[s]);
+      }
+      __syncwarp();
+      return true;
+    };
+    ok = mbar_wait_warp(&bar->kv_full, 0, abort) && issue_sdp(0);
+    while (ok && !w.done()) {
+      const int cur = c;
+      w.next();
+      const bool more = !w.done();
+      const bool same_blk = more && w.blk == last_blk;
+      if (same_blk) {
+        ok = issue_sdp(cur + 1);  // look ahead while this chunk's P / dS are being computed
+        if (!ok) break;
+      } else if (more) {
+        // the single K/V slot is refilled once everything issued so far has finished with it
+        if (elect_one()) umma_commit(&bar->kv_empty);
         __syncwarp();
-        ok = mbar_wait_warp(&bar->pds_full, half_idx & 1, abort);
+      }
+      if (fresh && seg > 0) {  // the previous segment's sums must have been read out of the accumulators
+        ok = mbar_wait_warp(&bar->acc_read, (seg - 1) & 1, abort);
+        if (!ok) break;
+      }
+      const uint32_t st = smem_u32(sSt + (cur & 1) * SM::kStage);
+      // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart, column blocks 16 KB apart
+      const uint64_t dQt = smem_desc_sw128(st, 16384, 1024), dOt = smem_desc_sw128(st + SM::kQ, 16384, 1024);
+      for (int h = 0; h < 2 && ok; ++h, ++u) {
+        ok = mbar_wait_warp(&bar->p_full, u & 1, abort);
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ts(tmem + cdV, tmem + cST + kk * 8, desc_advance(dOmn, kk * 2048), iddV, !(fresh && kk == 0));
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ts(tmem + cdK, tmem + cdPT + kk * 8, desc_advance(dQmn, kk * 2048), iddK, !(fresh && kk == 0));
-          if (hf == 1) umma_commit(&bar->q_empty[s]);
+            umma_ss(tmem + cdV, desc_advance(dOt, h * 8192 + kk * 2048), desc_advance(dPb, kk * 2048), iddV,
+                    !(fresh && h == 0 && kk == 0));
+          umma_commit(&bar->p_free[u & 3]);
         }
         __syncwarp();
-        fresh = false;
+        ok = mbar_wait_warp(&bar->ds_full, u & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            umma_ss(tmem + cdK1, desc_advance(dQt, h * 8192 + kk * 2048), desc_advance(dSb, kk * 2048), iddK1,
+                    !(fresh && h == 0 && kk == 0));
+            if (MK2)
+              umma_ss(tmem + cdK2, desc_advance(dQt, 2 * 16384 + h * 8192 + kk * 2048), desc_advance(dSb, kk * 2048), iddK2,
+                      !(fresh && h == 0 && kk == 0));
+          }
+          umma_commit(&bar->ds_free[u & 3]);
+          if (h == 1) umma_commit(&bar->q_empty[cur & 1]);
+        }
+        __syncwarp();
       }
-    }
-    if (ok && last_blk >= 0) {
-      if (elect_one()) umma_commit(&bar->acc_full);
-      __syncwarp();
+      if (!ok) break;
+      fresh = false;
+      if (!same_blk) {
+        // last chunk of the block (or of the CTA): hand the accumulators over
+        if (elect_one()) umma_commit(&bar->acc_full);
+        __syncwarp();
+        ++seg;
+        fresh = true;
+        if (more) {
+          last_blk = w.blk;
+          ++kvidx;
+          ok = mbar_wait_warp(&bar->kv_full, kvidx & 1, abort) && issue_sdp(cur + 1);
+        }
+      }
+      ++c;
     }
   } else {
-    // compute: warp w owns key rows 16w .. 16w+15 in its first 16 lanes (M = 64 accumulator layout)
-    const int kr = warp * 16 + (lane & 15);
-    const bool rowlane = lane < 16;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // compute: one gathered row per thread; groups alternate chunks; both groups take part in every flush
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const int grp = warp >> 2, warp4 = warp & 3;
+    const int r = warp4 * 32 + lane;
+    const int half = warp4 >> 1, rr = r & 63;  // which 64-row half of the chunk this row is handed over in
+    const uint32_t lane_base = (uint32_t)(warp4 * 32) << 16;
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     bool ok = true;
-    int c = 0, last_blk = -1, seg = 0, half_idx = 0;
+    int c = 0, last_blk = -1, seg = 0;
     auto flush = [&](int blk) -> bool {
       if (!mbar_wait(&bar->acc_full, seg & 1, abort)) return false;
       tc_fence_after();
-      const int64_t sidx = ((int64_t)bg * nseg + blockIdx.x + blk) * 64 + kr;
-      for (int cc = 0; cc < (DK + DV) / 32; ++cc) {
-        uint32_t ov[32];
-        tmem_ld32(tmem + lane_base + cc * 32, ov);
-        tc_wait_ld();
-        if (rowlane) {
-          float* dst = cc < DK / 32 ? p.dk_part + sidx * DK + cc * 32 : p.dv_part + sidx * DV + (cc - DK / 32) * 32;
-#pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            *reinterpret_cast<float4*>(dst + e) = make_float4(__uint_as_float(ov[e]), __uint_as_float(ov[e + 1]),
-                                                              __uint_as_float(ov[e + 2]), __uint_as_float(ov[e + 3]));
-        }
+      const int64_t key_base = ((int64_t)bg * nseg + blockIdx.x + blk) * 64;
+      if (grp == 0) {
+        slc_flush_rows<MK1>(tmem + cdK1, p.dk_part, key_base, DK, 0, warp4, lane);
+        if (MK2) slc_flush_rows<64>(tmem + cdK2, p.dk_part, key_base, DK, MK1, warp4, lane);
+      } else {
+        slc_flush_rows<DV>(tmem + cdV, p.dv_part, key_base, DV, 0, warp4, lane);
       }
       tc_fence_before();
       mbar_arrive(&bar->acc_read);
@@ -1139,54 +1207,66 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         if (!ok) break;
         last_blk = w.blk;
       }
-      const int s = c & 1;
-      ok = mbar_wait(&bar->q_full[s], (c >> 1) & 1, abort);
+      if ((c & 1) != grp) continue;
+      const int buf = grp, it = c >> 1;
+      ok = mbar_wait(&bar->q_full[buf], it & 1, abort);
       if (!ok) break;
-      const float* stat = reinterpret_cast<const float*>(sSt + s * SM::kStage + SM::kQ + SM::kdO);
-      const int* tcol = reinterpret_cast<const int*>(stat) + 256;
-      const int key = w.blk * 64 + kr;
-      for (int hf = 0; hf < 2 && ok; ++hf, ++half_idx) {
-        ok = mbar_wait(&bar->stp_full, half_idx & 1, abort);
-        if (!ok) break;
-        tc_fence_after();
+      const float* stat = reinterpret_cast<const float*>(sSt + buf * SM::kStage + SM::kQ + SM::kdO);
+      const float lse2 = stat[r], Dr = stat[128 + r];
+      const int t = reinterpret_cast<const int*>(stat)[256 + r];  // -1: row not in use (lse2 = +inf, so P = 0)
+      const int chi = t - w.blk * 64;
+      ok = mbar_wait(&bar->sdp_full[buf], it & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t pP[32], pS[32];
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t sT[32], dpT[32], pk[16], dk_[16];
-          tmem_ld32(tmem + lane_base + cST + cc * 32, sT);
-          tmem_ld32(tmem + lane_base + cdPT + cc * 32, dpT);
-          tc_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int j0 = hf * 64 + cc * 32 + 2 * e;  // row of the gathered tile = column here
-            const float l0 = stat[j0], l1 = stat[j0 + 1], D0 = stat[128 + j0], D1 = stat[128 + j0 + 1];
-            const int t0 = tcol[j0], t1 = tcol[j0 + 1];
-            const float p0 = key <= t0 ? ex2(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0)) : 0.f;
-            const float p1 = key <= t1 ? ex2(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1)) : 0.f;
-            __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1);
-            __nv_bfloat162 y = __floats2bfloat162_rn(p0 * (__uint_as_float(dpT[2 * e]) - D0), p1 * (__uint_as_float(dpT[2 * e + 1]) - D1));
-            pk[e] = *reinterpret_cast<uint32_t*>(&x);
-            dk_[e] = *reinterpret_cast<uint32_t*>(&y);
-          }
-          asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::
-                       "r"(tmem + lane_base + cST + cc * 16), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
-                       "r"(pk[6]), "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]),
-                       "r"(pk[15]) : "memory");
-          asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::
-                       "r"(tmem + lane_base + cdPT + cc * 16), "r"(dk_[0]), "r"(dk_[1]), "r"(dk_[2]), "r"(dk_[3]), "r"(dk_[4]),
-                       "r"(dk_[5]), "r"(dk_[6]), "r"(dk_[7]), "r"(dk_[8]), "r"(dk_[9]), "r"(dk_[10]), "r"(dk_[11]), "r"(dk_[12]),
-                       "r"(dk_[13]), "r"(dk_[14]), "r"(dk_[15]) : "memory");
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sv[32], dp[32];
+        tmem_ld32(tmem + lane_base + buf * 128 + cc * 32, sv);
+        tmem_ld32(tmem + lane_base + buf * 128 + 64 + cc * 32, dp);
+        tc_wait_ld();
+        if (cc == 1) {  // both tiles are in registers: the tensor core may overwrite them
+          tc_fence_before();
+          mbar_arrive(&bar->sdp_free[buf]);
         }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(&bar->pds_full);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int c0 = cc * 32 + 2 * e;
+          const float p0 = c0 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse2)) : 0.f;
+          const float p1 = c0 + 1 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse2)) : 0.f;
+          __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1);
+          __nv_bfloat162 y = __floats2bfloat162_rn(p0 * (__uint_as_float(dp[2 * e]) - Dr), p1 * (__uint_as_float(dp[2 * e + 1]) - Dr));
+          pP[cc * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
+          pS[cc * 16 + e] = *reinterpret_cast<uint32_t*>(&y);
+        }
       }
+      // hand-over: the staging tiles are used by (chunk, half) in order; use u waits for the MMAs of use u - 1
+      const int u = 2 * c + half;
+      if (u > 0) {
+        ok = mbar_wait(&bar->p_free[(u - 1) & 3], ((u - 1) >> 2) & 1, abort);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(sP + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pP[4 * j], pP[4 * j + 1], pP[4 * j + 2], pP[4 * j + 3]);
+      fence_proxy_async();
+      mbar_arrive(&bar->p_full);
+      if (u > 0) {
+        ok = mbar_wait(&bar->ds_free[(u - 1) & 3], ((u - 1) >> 2) & 1, abort);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(sdS + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pS[4 * j], pS[4 * j + 1], pS[4 * j + 2], pS[4 * j + 3]);
+      fence_proxy_async();
+      mbar_arrive(&bar->ds_full);
     }
     if (ok && last_blk >= 0) flush(last_blk);
   }
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -1369,7 +1449,7 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   if (int rc = check_launch("slc_combine_dq")) return rc;
   {
     KernelTimer kt("slc_bwd_dkv", st);
-    kkv<<<dim3(nparts, p.B * p.G), 192, SlcDkvSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
+    kkv<<<dim3(nparts, p.B * p.G), 384, SlcDkvSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
   }
   if (int rc = check_launch("slc_bwd_dkv_sm100")) return rc;
   KernelTimer kt("slc_reduce_dkv", st);
