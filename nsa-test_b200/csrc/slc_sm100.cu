@@ -45,6 +45,7 @@ struct SlcParams {
   float *dk_part, *dv_part;    // [BG, nparts+nblk, 64, dk|dv] per-(CTA, block) partial sums (backward)
   __nv_bfloat16 *dk_out, *dv_out;  // [B,G,Tk,dk|dv] gradients the reduced partials are added into
   int B, H, G, Tq, Tk, nslots, nblk, hpg;
+  int g5;  // gathered rows arrive as one rank-5 tile per query ([heads/8][width/64][8 rows][64 columns]) instead of one tile per 64 columns
   float scale, scale_log2;
   int* timeouts;
 };
@@ -116,6 +117,9 @@ __global__ void to_token_major_kernel(const __nv_bfloat16* __restrict__ in, __nv
 }
 
 // One chunk = up to qpc queries; query qi fills rows [qi*hpg, (qi+1)*hpg) of the 128-row K-major swizzled tiles.
+// Two tile layouts: one 64-column block after the other ([width/64][128 rows][128 B], a 2-D tile load per query and
+// column block), or, when the heads of a group fill whole 8-row swizzle atoms, [128/8 row groups][width/64][8 rows][128 B]
+// with ONE rank-5 tile load per query.  The UMMA descriptors take the layout as (row-group stride, column-block stride).
 // Unused query slots are loaded from beyond the tensor (TMA fills zeros), so every chunk delivers the same byte count.
 // Lane qi of the producer warp fetches its query's inverse-index entry and issues that query's tile loads, so the entry
 // loads of a chunk are one coalesced request instead of a chain of dependent ones.
@@ -198,9 +202,13 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       __syncwarp();
       for (int qi = lane; qi < qpc; qi += 32) {
         const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
+        if (p.g5) {
+          tma_load_5d_outer(&tmQt, &bar->q_full[s], sQ + s * SM::kQ + qi * p.hpg * (DK * 2), r2 / p.hpg);
+        } else {
 #pragma unroll
-        for (int cc = 0; cc < DK / 64; ++cc)
-          tma_load_2d(&tmQt, &bar->q_full[s], sQ + s * SM::kQ + cc * 16384 + qi * p.hpg * 128, cc * 64, r2);
+          for (int cc = 0; cc < DK / 64; ++cc)
+            tma_load_2d(&tmQt, &bar->q_full[s], sQ + s * SM::kQ + cc * 16384 + qi * p.hpg * 128, cc * 64, r2);
+        }
       }
       if (lane == 0) NSA_TR(0, c, 2);
     }
@@ -213,6 +221,7 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // elected lane issues the tensor-core instructions
     constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);   // Q rows (K-major) x K block (MN-major: keys contiguous)
     constexpr uint32_t idO = idesc_bf16(128, DV, 0, 1);   // P (TMEM) x V block (MN-major: dv contiguous)
+    const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;  // Q tile: row-group / column-block strides
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     bool ok = true;
     int c = 0, kvidx = 0, ks_cur = 0, cur_blk = w.blk;
@@ -224,12 +233,12 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (!mbar_wait_warp(&bar->o_read[buf], ((cc >> 1) & 1) ^ 1, abort)) return false;
       if (lane == 0) NSA_TR(1, cc, 2);
       tc_fence_after();
-      const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * SM::kQ), 16, 1024);
+      const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * SM::kQ), 16, sboQ);
       const uint64_t dK = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);  // one 64-key MN block: LBO unused
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
-          umma_ss(tmem + buf * 192, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dK, kk * 2048), idS, kk > 0);
+          umma_ss(tmem + buf * 192, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dK, kk * 2048), idS, kk > 0);
         umma_commit(&bar->s_full[buf]);
         umma_commit(&bar->q_empty[s]);
       }
@@ -628,11 +637,17 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       __syncwarp();
       for (int qi = lane; qi < qpc; qi += 32) {
         const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
-        uint8_t* dst = sSt + s * SM::kStage + qi * p.hpg * 128;
+        uint8_t* stg = sSt + s * SM::kStage;
+        if (p.g5) {
+          tma_load_5d_outer(&tmQt, &bar->q_full[s], stg + qi * p.hpg * (DK * 2), r2 / p.hpg);
+          tma_load_5d_outer(&tmdOt, &bar->q_full[s], stg + SM::kQ + qi * p.hpg * (DV * 2), r2 / p.hpg);
+        } else {
+          uint8_t* dst = stg + qi * p.hpg * 128;
 #pragma unroll
-        for (int cc = 0; cc < DK / 64; ++cc) tma_load_2d(&tmQt, &bar->q_full[s], dst + cc * 16384, cc * 64, r2);
+          for (int cc = 0; cc < DK / 64; ++cc) tma_load_2d(&tmQt, &bar->q_full[s], dst + cc * 16384, cc * 64, r2);
 #pragma unroll
-        for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
+          for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
+        }
       }
     }
     if (!ok && lane == 0) {
@@ -641,6 +656,8 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     }
   } else if (warp == 8) {
     // UMMA issuer: warp-uniform loop, one elected lane issues
+    const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;  // Q tile: row-group / column-block strides
+    const uint32_t sboO = p.g5 ? (DV / 64) * 1024 : 1024, cbO = p.g5 ? 1024 : 16384;  // dO tile
     constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);    // Q rows x K block (keys contiguous)
     constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);   // dO rows x V block read K-major (dv contiguous)
     constexpr uint32_t iddQh = idesc_bf16(128, DK / 2, 0, 0);   // dS (TMEM) x half of the K block's dk rows, read K-major
@@ -653,15 +670,15 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       const int s = cc & 1;
       if (!mbar_wait_warp(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
       tc_fence_after();
-      const uint64_t dQ = smem_desc_sw128(smem_u32(sSt + s * SM::kStage), 16, 1024);
-      const uint64_t ddO = smem_desc_sw128(smem_u32(sSt + s * SM::kStage + SM::kQ), 16, 1024);
+      const uint64_t dQ = smem_desc_sw128(smem_u32(sSt + s * SM::kStage), 16, sboQ);
+      const uint64_t ddO = smem_desc_sw128(smem_u32(sSt + s * SM::kStage + SM::kQ), 16, sboO);
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
-          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
+          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < DV / 16; ++kk)
-          umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * 16384 + (kk & 3) * 32),
+          umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * cbO + (kk & 3) * 32),
                   desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP, kk > 0);
         umma_commit(&bar->sdp_full[s]);
         umma_commit(&bar->q_empty[s]);
@@ -921,7 +938,7 @@ __global__ void slc_combine_dq_bulk_kernel(const __nv_bfloat16* __restrict__ dq_
 template <int DK, int DV>
 struct SlcDkvSmem {
   static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2, kdO = 128 * DV * 2;
-  static constexpr int kStage = kQ + kdO + 2048;  // + lse2[128], D[128], t[128]
+  static constexpr int kStage = kQ + kdO;
   static constexpr int kHalf = 64 * 128;          // 64 rows x 64 keys of bf16 P (or dS), 128-byte swizzle
   static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, oP = oSt + 2 * kStage, odS = oP + kHalf, oBar = odS + kHalf;
   static constexpr int kDynamic = oBar + 256 + 1024;
@@ -982,7 +999,7 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     mbar_init(&bar->kv_full, 1);
     mbar_init(&bar->kv_empty, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar->q_full[i], 2);  // TMA bytes + the statistics written by the producer warp
+      mbar_init(&bar->q_full[i], 1);
       mbar_init(&bar->q_empty[i], 1);
       mbar_init(&bar->sdp_full[i], 1);
       mbar_init(&bar->sdp_free[i], 128);
@@ -1013,27 +1030,16 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   if (warp >= 10) {
   } else if (!has_work) {
   } else if (warp == 9) {
-    // producer warp: K/V block and gathered Q / dO rows by TMA (lane qi issues query qi); all lanes fetch the rows' statistics
+    // producer warp: K/V block and gathered Q / dO rows by TMA (lane qi issues query qi)
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     const int oob_row = p.B * p.H * p.Tq;
     bool ok = true;
     int c = 0, kvidx = -1, last_blk = -1;
     for (; !w.done(); w.next(), ++c) {
       const int cnt = w.count();
-      // entries and statistics of this chunk are fetched before the stage is free
+      // this chunk's entries are fetched while the stage is still busy
       int row = oob_row;
       if (lane < cnt) row = (int)(((int64_t)bg * p.Tq + (ent[w.e + lane] & 0xFFFFFF)) * p.hpg);
-      float st_l[4], st_d[4];
-      int st_t[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int rr = lane + 32 * i, qi = rr / p.hpg, hh = rr % p.hpg;
-        const bool valid = qi < cnt;
-        st_t[i] = valid ? (ent[w.e + qi] & 0xFFFFFF) : -1;  // -1: row not in use
-        const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + max(st_t[i], 0);
-        st_l[i] = valid ? p.lse2[srow] : CUDART_INF_F;
-        st_d[i] = valid ? p.D[srow] : 0.f;
-      }
       if (w.blk != last_blk) {
         last_blk = w.blk;
         ++kvidx;
@@ -1054,22 +1060,17 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       __syncwarp();
       for (int qi = lane; qi < qpc; qi += 32) {
         const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
-        uint8_t* dst = st + qi * p.hpg * 128;
+        if (p.g5) {
+          tma_load_5d_outer(&tmQt, &bar->q_full[s], st + qi * p.hpg * (DK * 2), r2 / p.hpg);
+          tma_load_5d_outer(&tmdOt, &bar->q_full[s], st + SM::kQ + qi * p.hpg * (DV * 2), r2 / p.hpg);
+        } else {
+          uint8_t* dst = st + qi * p.hpg * 128;
 #pragma unroll
-        for (int cc = 0; cc < DK / 64; ++cc) tma_load_2d(&tmQt, &bar->q_full[s], dst + cc * 16384, cc * 64, r2);
+          for (int cc = 0; cc < DK / 64; ++cc) tma_load_2d(&tmQt, &bar->q_full[s], dst + cc * 16384, cc * 64, r2);
 #pragma unroll
-        for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
+          for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
+        }
       }
-      float* stat = reinterpret_cast<float*>(st + SM::kQ + SM::kdO);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int rr = lane + 32 * i;
-        stat[rr] = st_l[i];
-        stat[128 + rr] = st_d[i];
-        reinterpret_cast<int*>(stat)[256 + rr] = st_t[i];
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->q_full[s]);
     }
     if (!ok && lane == 0) {
       if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
@@ -1086,6 +1087,8 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
     const uint64_t dPb = smem_desc_sw128(smem_u32(sP), 16, 1024);    // one 64-key MN block: LBO unused
     const uint64_t dSb = smem_desc_sw128(smem_u32(sdS), 16, 1024);
+    const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;  // Q tile: row-group / column-block strides
+    const uint32_t sboO = p.g5 ? (DV / 64) * 1024 : 1024, cbO = p.g5 ? 1024 : 16384;  // dO tile
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     bool ok = true;
     int c = 0, kvidx = 0, last_blk = w.blk, seg = 0, u = 0;
@@ -1096,14 +1099,14 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       if (!mbar_wait_warp(&bar->sdp_free[s], ((cc >> 1) & 1) ^ 1, abort)) return false;  // S/dP of chunk cc-2 are in registers
       tc_fence_after();
       const uint32_t st = smem_u32(sSt + s * SM::kStage);
-      const uint64_t dQ = smem_desc_sw128(st, 16, 1024), ddO = smem_desc_sw128(st + SM::kQ, 16, 1024);
+      const uint64_t dQ = smem_desc_sw128(st, 16, sboQ), ddO = smem_desc_sw128(st + SM::kQ, 16, sboO);
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
-          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
+          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < DV / 16; ++kk)
-          umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * 16384 + (kk & 3) * 32),
+          umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * cbO + (kk & 3) * 32),
                   desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP, kk > 0);
         umma_commit(&bar->sdp_full[s]);
       }
@@ -1113,12 +1116,14 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     ok = mbar_wait_warp(&bar->kv_full, 0, abort) && issue_sdp(0);
     while (ok && !w.done()) {
       const int cur = c;
+      if (lane == 0) NSA_TR(1, cur, 0);
       w.next();
       const bool more = !w.done();
       const bool same_blk = more && w.blk == last_blk;
       if (same_blk) {
         ok = issue_sdp(cur + 1);  // look ahead while this chunk's P / dS are being computed
         if (!ok) break;
+        if (lane == 0) NSA_TR(1, cur, 1);
       } else if (more) {
         // the single K/V slot is refilled once everything issued so far has finished with it
         if (elect_one()) umma_commit(&bar->kv_empty);
@@ -1129,36 +1134,40 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         if (!ok) break;
       }
       const uint32_t st = smem_u32(sSt + (cur & 1) * SM::kStage);
-      // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart, column blocks 16 KB apart
-      const uint64_t dQt = smem_desc_sw128(st, 16384, 1024), dOt = smem_desc_sw128(st + SM::kQ, 16384, 1024);
+      // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart inside an 8-row group
+      const uint64_t dQt = smem_desc_sw128(st, cbQ, sboQ), dOt = smem_desc_sw128(st + SM::kQ, cbO, sboO);
       for (int h = 0; h < 2 && ok; ++h, ++u) {
         ok = mbar_wait_warp(&bar->p_full, u & 1, abort);
         if (!ok) break;
+        if (lane == 0) NSA_TR(1, cur, 2 + 4 * h);
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tmem + cdV, desc_advance(dOt, h * 8192 + kk * 2048), desc_advance(dPb, kk * 2048), iddV,
+            umma_ss(tmem + cdV, desc_advance(dOt, (h * 8 + kk * 2) * sboO), desc_advance(dPb, kk * 2048), iddV,
                     !(fresh && h == 0 && kk == 0));
           umma_commit(&bar->p_free[u & 3]);
         }
         __syncwarp();
+        if (lane == 0) NSA_TR(1, cur, 3 + 4 * h);
         ok = mbar_wait_warp(&bar->ds_full, u & 1, abort);
         if (!ok) break;
+        if (lane == 0) NSA_TR(1, cur, 4 + 4 * h);
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            umma_ss(tmem + cdK1, desc_advance(dQt, h * 8192 + kk * 2048), desc_advance(dSb, kk * 2048), iddK1,
+            umma_ss(tmem + cdK1, desc_advance(dQt, (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK1,
                     !(fresh && h == 0 && kk == 0));
             if (MK2)
-              umma_ss(tmem + cdK2, desc_advance(dQt, 2 * 16384 + h * 8192 + kk * 2048), desc_advance(dSb, kk * 2048), iddK2,
+              umma_ss(tmem + cdK2, desc_advance(dQt, 2 * cbQ + (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK2,
                       !(fresh && h == 0 && kk == 0));
           }
           umma_commit(&bar->ds_free[u & 3]);
           if (h == 1) umma_commit(&bar->q_empty[cur & 1]);
         }
         __syncwarp();
+        if (lane == 0) NSA_TR(1, cur, 5 + 4 * h);
       }
       if (!ok) break;
       fresh = false;
@@ -1201,6 +1210,24 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       ++seg;
       return true;
     };
+    // statistics of this thread's row in a given chunk: t (-1: row not in use), lse2 (+inf then, so P = 0), D
+    const int qi = r / p.hpg, hh = r % p.hpg;
+    int t_next = -1;
+    float lse_next = CUDART_INF_F, D_next = 0.f;
+    auto fetch = [&](const ChunkWalker& wk) {
+      t_next = -1; lse_next = CUDART_INF_F; D_next = 0.f;
+      if (!wk.done() && qi < wk.count()) {
+        t_next = ent[wk.e + qi] & 0xFFFFFF;
+        const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + t_next;
+        lse_next = p.lse2[srow];
+        D_next = p.D[srow];
+      }
+    };
+    {
+      ChunkWalker w0 = w;
+      if (grp == 1 && !w0.done()) w0.next();
+      fetch(w0);
+    }
     for (; !w.done() && ok; w.next(), ++c) {
       if (w.blk != last_blk) {
         if (last_blk >= 0) ok = flush(last_blk);
@@ -1209,14 +1236,19 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
       if ((c & 1) != grp) continue;
       const int buf = grp, it = c >> 1;
-      ok = mbar_wait(&bar->q_full[buf], it & 1, abort);
-      if (!ok) break;
-      const float* stat = reinterpret_cast<const float*>(sSt + buf * SM::kStage + SM::kQ + SM::kdO);
-      const float lse2 = stat[r], Dr = stat[128 + r];
-      const int t = reinterpret_cast<const int*>(stat)[256 + r];  // -1: row not in use (lse2 = +inf, so P = 0)
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 0);
+      const int t = t_next;
+      const float lse2 = lse_next, Dr = D_next;
       const int chi = t - w.blk * 64;
+      {  // this group's next chunk: fetch its statistics one chunk ahead
+        ChunkWalker w2 = w;
+        w2.next();
+        if (!w2.done()) w2.next();
+        fetch(w2);
+      }
       ok = mbar_wait(&bar->sdp_full[buf], it & 1, abort);
       if (!ok) break;
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 1);
       tc_fence_after();
       uint32_t pP[32], pS[32];
 #pragma unroll
@@ -1242,24 +1274,29 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
       // hand-over: the staging tiles are used by (chunk, half) in order; use u waits for the MMAs of use u - 1
       const int u = 2 * c + half;
+      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 2 + 6 * half);
       if (u > 0) {
         ok = mbar_wait(&bar->p_free[(u - 1) & 3], ((u - 1) >> 2) & 1, abort);
         if (!ok) break;
       }
+      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 3 + 6 * half);
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         *reinterpret_cast<uint4*>(sP + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pP[4 * j], pP[4 * j + 1], pP[4 * j + 2], pP[4 * j + 3]);
       fence_proxy_async();
       mbar_arrive(&bar->p_full);
+      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 4 + 6 * half);
       if (u > 0) {
         ok = mbar_wait(&bar->ds_free[(u - 1) & 3], ((u - 1) >> 2) & 1, abort);
         if (!ok) break;
       }
+      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 5 + 6 * half);
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         *reinterpret_cast<uint4*>(sdS + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pS[4 * j], pS[4 * j + 1], pS[4 * j + 2], pS[4 * j + 3]);
       fence_proxy_async();
       mbar_arrive(&bar->ds_full);
+      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 6 + 6 * half);
     }
     if (ok && last_blk >= 0) flush(last_blk);
   }
@@ -1382,7 +1419,12 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
   if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
   if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, 64)) return rc;
   CUtensorMap tqt;
-  if (int rc = make_tmap_bf16_2d(&tqt, qt, (uint64_t)B * H * Tq, dk, H / G)) return rc;
+  p.g5 = (H / G) % 8 == 0 ? 1 : 0;  // whole 8-row swizzle atoms per query: one rank-5 tile load per query
+  if (p.g5) {
+    if (int rc = make_tmap_token_rows(&tqt, qt, (uint64_t)B * G * Tq, H / G, dk)) return rc;
+  } else if (int rc = make_tmap_bf16_2d(&tqt, qt, (uint64_t)B * H * Tq, dk, H / G)) {
+    return rc;
+  }
   CUtensorMap top;  // partial outputs as rows of dv values; one box = the heads of a group for one (query, slot)
   if (int rc = make_tmap_bf16_2d(&top, p.o_part, (uint64_t)rows, dv, (uint32_t)(H / G < 32 ? H / G : 32))) return rc;
   if (dk == 192 && dv == 128) return launch_slc_fwd_t<192, 128>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
@@ -1489,8 +1531,14 @@ int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indice
   if (int rc = token_major_copy_w(dk, q, w + o_qt, B, H, G, Tq, "slc_q_token_major", st)) return rc;
   if (int rc = token_major_copy_w(dv, dout, w + o_dot, B, H, G, Tq, "slc_do_token_major", st)) return rc;
   CUtensorMap tqt, tdot;
-  if (int rc = make_tmap_bf16_2d(&tqt, w + o_qt, (uint64_t)B * H * Tq, dk, H / G)) return rc;
-  if (int rc = make_tmap_bf16_2d(&tdot, w + o_dot, (uint64_t)B * H * Tq, dv, H / G)) return rc;
+  p.g5 = (H / G) % 8 == 0 ? 1 : 0;  // whole 8-row swizzle atoms per query: one rank-5 tile load per query and tensor
+  if (p.g5) {
+    if (int rc = make_tmap_token_rows(&tqt, w + o_qt, (uint64_t)B * G * Tq, H / G, dk)) return rc;
+    if (int rc = make_tmap_token_rows(&tdot, w + o_dot, (uint64_t)B * G * Tq, H / G, dv)) return rc;
+  } else {
+    if (int rc = make_tmap_bf16_2d(&tqt, w + o_qt, (uint64_t)B * H * Tq, dk, H / G)) return rc;
+    if (int rc = make_tmap_bf16_2d(&tdot, w + o_dot, (uint64_t)B * H * Tq, dv, H / G)) return rc;
+  }
   if (dk == 192 && dv == 128) return launch_slc_bwd_t<192, 128>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, st);
   if (dk == 128 && dv == 128) return launch_slc_bwd_t<128, 128>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, st);
   if (dk == 64 && dv == 64) return launch_slc_bwd_t<64, 64>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, st);
