@@ -1053,6 +1053,18 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         }
       }
       const int s = c & 1;
+      // the stage is usually still busy: start the rows on their way to L2 so that the tile loads find them there
+      if (lane < cnt && lane < qpc) {
+        if (p.g5) {
+          tma_prefetch_5d_outer(&tmQt, row / p.hpg);
+          tma_prefetch_5d_outer(&tmdOt, row / p.hpg);
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < DK / 64; ++cc) tma_prefetch_2d(&tmQt, cc * 64, row);
+#pragma unroll
+          for (int cc = 0; cc < DV / 64; ++cc) tma_prefetch_2d(&tmdOt, cc * 64, row);
+        }
+      }
       ok = mbar_wait_warp(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
       if (!ok) break;
       uint8_t* st = sSt + s * SM::kStage;
@@ -1124,7 +1136,8 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         ok = issue_sdp(cur + 1);  // look ahead while this chunk's P / dS are being computed
         if (!ok) break;
         if (lane == 0) NSA_TR(1, cur, 1);
-      } else if (more) {
+      }
+      if (!same_blk && more) {
         // the single K/V slot is refilled once everything issued so far has finished with it
         if (elect_one()) umma_commit(&bar->kv_empty);
         __syncwarp();
