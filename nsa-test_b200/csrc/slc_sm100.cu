@@ -1065,8 +1065,10 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           for (int cc = 0; cc < DV / 64; ++cc) tma_prefetch_2d(&tmdOt, cc * 64, row);
         }
       }
+      if (lane == 0) NSA_TR(0, c, 0);
       ok = mbar_wait_warp(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
       if (!ok) break;
+      if (lane == 0) NSA_TR(0, c, 1);
       uint8_t* st = sSt + s * SM::kStage;
       if (lane == 0) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
       __syncwarp();
@@ -1083,6 +1085,7 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
         }
       }
+      if (lane == 0) NSA_TR(0, c, 2);
     }
     if (!ok && lane == 0) {
       if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
@@ -1101,102 +1104,120 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const uint64_t dSb = smem_desc_sw128(smem_u32(sdS), 16, 1024);
     const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;  // Q tile: row-group / column-block strides
     const uint32_t sboO = p.g5 ? (DV / 64) * 1024 : 1024, cbO = p.g5 ? 1024 : 16384;  // dO tile
-    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-    bool ok = true;
-    int c = 0, kvidx = 0, last_blk = w.blk, seg = 0, u = 0;
-    bool fresh = true;  // the next accumulation starts a new segment
-    auto issue_sdp = [&](int cc) -> bool {
-      const int s = cc & 1;
-      if (!mbar_wait_warp(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
-      if (!mbar_wait_warp(&bar->sdp_free[s], ((cc >> 1) & 1) ^ 1, abort)) return false;  // S/dP of chunk cc-2 are in registers
-      tc_fence_after();
-      const uint32_t st = smem_u32(sSt + s * SM::kStage);
-      const uint64_t dQ = smem_desc_sw128(st, 16, sboQ), ddO = smem_desc_sw128(st + SM::kQ, 16, sboO);
-      if (elect_one()) {
+    // Two streams of work share the tensor pipe: "produce" issues S / dP of the next chunk as soon as its rows have
+    // landed and its TMEM buffer is free, "consume" issues the accumulation MMAs of the oldest chunk as soon as the
+    // compute warps have handed over P or dS.  The warp polls both (non-blocking tests), so a load in flight never
+    // holds back accumulation work that is ready, and the other way round.
+    ChunkWalker wA(off, p.nblk, e0, e0 + kEntriesPerCta, qpc), wH = wA;
+    bool ok = true, fresh = true;  // fresh: the next accumulation starts a new segment
+    int ca = 0, ch = 0, hstep = 0;  // chunk to produce, chunk to consume and its step: P(h0), dS(h0), P(h1), dS(h1)
+    int kvidx = 0, blkA = wA.blk, seg = 0, u = 0;
+    bool kv_wait = true;           // the K/V tile of the block of chunk `ca` has not been seen to land yet
+    long long idle_since = 0;
+    while (ok && !wH.done()) {
+      bool did = false;
+      // ---- consume
+      if (ch < ca) {
+        bool ready = mbar_test((hstep & 1) ? &bar->ds_full : &bar->p_full, u & 1);
+        // a new segment overwrites the accumulators: the previous segment's sums must have been read out
+        if (ready && fresh && hstep == 0 && seg > 0) ready = mbar_test(&bar->acc_read, (seg - 1) & 1);
+        if (__all_sync(0xffffffffu, ready)) {
+          tc_fence_after();
+          const int h = hstep >> 1;
+          const uint32_t st = smem_u32(sSt + (ch & 1) * SM::kStage);
+          // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart inside an 8-row group
+          const uint64_t dQt = smem_desc_sw128(st, cbQ, sboQ), dOt = smem_desc_sw128(st + SM::kQ, cbO, sboO);
+          if ((hstep & 1) == 0) {
+            if (lane == 0) NSA_TR(1, ch, 2 + 4 * h);
+            if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < DK / 16; ++kk)
-          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
+              for (int kk = 0; kk < 4; ++kk)
+                umma_ss(tmem + cdV, desc_advance(dOt, (h * 8 + kk * 2) * sboO), desc_advance(dPb, kk * 2048), iddV,
+                        !(fresh && h == 0 && kk == 0));
+              umma_commit(&bar->p_free[u & 3]);
+            }
+          } else {
+            if (lane == 0) NSA_TR(1, ch, 4 + 4 * h);
+            if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < DV / 16; ++kk)
-          umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * cbO + (kk & 3) * 32),
-                  desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP, kk > 0);
-        umma_commit(&bar->sdp_full[s]);
-      }
-      __syncwarp();
-      return true;
-    };
-    ok = mbar_wait_warp(&bar->kv_full, 0, abort) && issue_sdp(0);
-    while (ok && !w.done()) {
-      const int cur = c;
-      if (lane == 0) NSA_TR(1, cur, 0);
-      w.next();
-      const bool more = !w.done();
-      const bool same_blk = more && w.blk == last_blk;
-      if (same_blk) {
-        ok = issue_sdp(cur + 1);  // look ahead while this chunk's P / dS are being computed
-        if (!ok) break;
-        if (lane == 0) NSA_TR(1, cur, 1);
-      }
-      if (!same_blk && more) {
-        // the single K/V slot is refilled once everything issued so far has finished with it
-        if (elect_one()) umma_commit(&bar->kv_empty);
-        __syncwarp();
-      }
-      if (fresh && seg > 0) {  // the previous segment's sums must have been read out of the accumulators
-        ok = mbar_wait_warp(&bar->acc_read, (seg - 1) & 1, abort);
-        if (!ok) break;
-      }
-      const uint32_t st = smem_u32(sSt + (cur & 1) * SM::kStage);
-      // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart inside an 8-row group
-      const uint64_t dQt = smem_desc_sw128(st, cbQ, sboQ), dOt = smem_desc_sw128(st + SM::kQ, cbO, sboO);
-      for (int h = 0; h < 2 && ok; ++h, ++u) {
-        ok = mbar_wait_warp(&bar->p_full, u & 1, abort);
-        if (!ok) break;
-        if (lane == 0) NSA_TR(1, cur, 2 + 4 * h);
-        tc_fence_after();
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tmem + cdV, desc_advance(dOt, (h * 8 + kk * 2) * sboO), desc_advance(dPb, kk * 2048), iddV,
-                    !(fresh && h == 0 && kk == 0));
-          umma_commit(&bar->p_free[u & 3]);
-        }
-        __syncwarp();
-        if (lane == 0) NSA_TR(1, cur, 3 + 4 * h);
-        ok = mbar_wait_warp(&bar->ds_full, u & 1, abort);
-        if (!ok) break;
-        if (lane == 0) NSA_TR(1, cur, 4 + 4 * h);
-        tc_fence_after();
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            umma_ss(tmem + cdK1, desc_advance(dQt, (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK1,
-                    !(fresh && h == 0 && kk == 0));
-            if (MK2)
-              umma_ss(tmem + cdK2, desc_advance(dQt, 2 * cbQ + (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK2,
-                      !(fresh && h == 0 && kk == 0));
+              for (int kk = 0; kk < 4; ++kk) {
+                umma_ss(tmem + cdK1, desc_advance(dQt, (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK1,
+                        !(fresh && h == 0 && kk == 0));
+                if (MK2)
+                  umma_ss(tmem + cdK2, desc_advance(dQt, 2 * cbQ + (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK2,
+                          !(fresh && h == 0 && kk == 0));
+              }
+              umma_commit(&bar->ds_free[u & 3]);
+              if (hstep == 3) umma_commit(&bar->q_empty[ch & 1]);  // the chunk's Q / dO stage is free again
+            }
           }
-          umma_commit(&bar->ds_free[u & 3]);
-          if (h == 1) umma_commit(&bar->q_empty[cur & 1]);
+          __syncwarp();
+          if (hstep == 1) fresh = false;
+          if (hstep & 1) ++u;
+          if (++hstep == 4) {
+            hstep = 0;
+            const int blk_done = wH.blk;
+            wH.next();
+            if (wH.done() || wH.blk != blk_done) {
+              // last chunk of the block (or of the CTA): hand the accumulators over
+              if (elect_one()) umma_commit(&bar->acc_full);
+              __syncwarp();
+              ++seg;
+              fresh = true;
+            }
+            ++ch;
+          }
+          did = true;
         }
-        __syncwarp();
-        if (lane == 0) NSA_TR(1, cur, 5 + 4 * h);
       }
-      if (!ok) break;
-      fresh = false;
-      if (!same_blk) {
-        // last chunk of the block (or of the CTA): hand the accumulators over
-        if (elect_one()) umma_commit(&bar->acc_full);
-        __syncwarp();
-        ++seg;
-        fresh = true;
-        if (more) {
-          last_blk = w.blk;
+      // ---- produce
+      if (!wA.done()) {
+        if (wA.blk != blkA) {
+          // first chunk of another block: the single K/V slot is refilled once everything issued so far has finished with it
+          if (elect_one()) umma_commit(&bar->kv_empty);
+          __syncwarp();
           ++kvidx;
-          ok = mbar_wait_warp(&bar->kv_full, kvidx & 1, abort) && issue_sdp(cur + 1);
+          kv_wait = true;
+          blkA = wA.blk;
+        }
+        const int s = ca & 1;
+        bool ready = mbar_test(&bar->q_full[s], (ca >> 1) & 1) && mbar_test(&bar->sdp_free[s], ((ca >> 1) & 1) ^ 1);
+        if (ready && kv_wait) ready = mbar_test(&bar->kv_full, kvidx & 1);
+        if (__all_sync(0xffffffffu, ready)) {
+          kv_wait = false;
+          if (lane == 0) NSA_TR(1, ca, 12);
+          tc_fence_after();
+          const uint32_t st = smem_u32(sSt + s * SM::kStage);
+          const uint64_t dQ = smem_desc_sw128(st, 16, sboQ), ddO = smem_desc_sw128(st + SM::kQ, 16, sboO);
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < DK / 16; ++kk)
+              umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < DV / 16; ++kk)
+              umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * cbO + (kk & 3) * 32),
+                      desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP, kk > 0);
+            umma_commit(&bar->sdp_full[s]);
+          }
+          __syncwarp();
+          if (lane == 0) NSA_TR(1, ca, 13);
+          wA.next();
+          ++ca;
+          did = true;
         }
       }
-      ++c;
+      // ---- nothing ready: bounded idling
+      if (did) {
+        idle_since = 0;
+      } else {
+        const long long now = clock64();
+        if (idle_since == 0) idle_since = now;
+        if (*abort || now - idle_since > (1ll << 28)) {
+          *abort = 1;
+          ok = false;
+        }
+        __nanosleep(32);
+      }
     }
   } else {
     // compute: one gathered row per thread; groups alternate chunks; both groups take part in every flush
