@@ -402,20 +402,22 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
   return NSA_OK;
 }
 
-// Token-major rows [tokens][heads][width] (bf16) -> rank-5 map whose box is all `heads` rows of one token, delivered as
-// [heads/8][width/64][8 rows][64 columns] with 128-byte swizzle: every 8-row x 128-byte swizzle atom of the token in one
-// copy, atoms of a row group next to each other.  heads must be a multiple of 8, width a multiple of 64.
-int make_tmap_token_rows(CUtensorMap* map, const void* base, uint64_t tokens, uint32_t heads, uint32_t width) {
+// Head-major rows [heads_total][T][width] (bf16, contiguous) -> rank-5 map whose box is one token's rows of `heads`
+// consecutive heads (a multiple of 8, starting at a multiple of 8), delivered as [heads/8][width/64][8 rows][64 columns]
+// with 128-byte swizzle: every 8-row x 128-byte swizzle atom of the (token, head group) in one copy, the atoms of a row
+// group next to each other.  Coordinates: (0, 0, 0, first_head / 8, token).
+int make_tmap_head_rows(CUtensorMap* map, const void* base, uint64_t heads_total, uint64_t T, uint32_t heads, uint32_t width) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(NSA_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t dims[5] = {64, 8, width / 64, heads / 8, tokens};
-  cuuint64_t strides[4] = {(cuuint64_t)width * 2, 128, (cuuint64_t)8 * width * 2, (cuuint64_t)heads * width * 2};
+  const cuuint64_t head_bytes = (cuuint64_t)T * width * 2;
+  cuuint64_t dims[5] = {64, 8, width / 64, heads_total / 8, T};
+  cuuint64_t strides[4] = {head_bytes, 128, 8 * head_bytes, (cuuint64_t)width * 2};
   cuuint32_t box[5] = {64, 8, width / 64, heads / 8, 1};
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(NSA_ERR_LAUNCH, "cuTensorMapEncodeTiled (token rows) failed with %d", (int)r);
+  if (r != CUDA_SUCCESS) return fail(NSA_ERR_LAUNCH, "cuTensorMapEncodeTiled (head rows) failed with %d", (int)r);
   return NSA_OK;
 }
 

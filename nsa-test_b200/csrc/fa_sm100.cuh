@@ -37,8 +37,9 @@ int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, con
 // bf16 row-major [rows, cols] matrix -> tensor map with box [box_rows, 64 columns], 128-byte swizzle
 int make_tmap_bf16_2d(::CUtensorMap_st* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
-// token-major bf16 rows [tokens][heads][width] -> rank-5 map, box = one token's rows as [heads/8][width/64][8][64], 128-byte swizzle
-int make_tmap_token_rows(::CUtensorMap_st* map, const void* base, uint64_t tokens, uint32_t heads, uint32_t width);
+// head-major bf16 rows [heads_total][T][width] -> rank-5 map, box = one token's rows of `heads` consecutive heads as
+// [heads/8][width/64][8][64], 128-byte swizzle; coordinates (0, 0, 0, first_head / 8, token)
+int make_tmap_head_rows(::CUtensorMap_st* map, const void* base, uint64_t heads_total, uint64_t T, uint32_t heads, uint32_t width);
 
 // Fused selection scoring (Eq. 8-11) on tensor cores; see score_sm100.cu.  k_cmp fp32 [B,G,dk,nbp] contiguous,
 // q bf16 [B,H,T,dk] contiguous, compressed block i ends at i*d + l - 1 for i < nb and is never visible beyond.

@@ -171,6 +171,7 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // ------------------------------------------------------------ producer warp: K/V blocks and gathered Q rows, all by TMA
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     const int oob_row = p.B * p.H * p.Tq;
+    const int oct0 = (b * p.H + g * p.hpg) >> 3;  // first head of the group, in units of 8 heads (rank-5 loads)
     bool ok = true;
     int c = 0, kvidx = -1, last_blk = -1;
     for (; !w.done(); w.next(), ++c) {
@@ -190,8 +191,11 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       }
       // this chunk's entries are fetched while the stage is still busy
       const int cnt = w.count();
-      int row = oob_row;
-      if (lane < cnt) row = (int)(((int64_t)bg * p.Tq + (ent[w.e + lane] & 0xFFFFFF)) * p.hpg);
+      int tok = p.Tq, row = oob_row;  // beyond the tensor: the tile is filled with zeros
+      if (lane < cnt) {
+        tok = ent[w.e + lane] & 0xFFFFFF;
+        row = (int)(((int64_t)bg * p.Tq + tok) * p.hpg);
+      }
       if (lane == 0) NSA_TR(0, c, 0);
       ok = mbar_wait_warp(&bar->q_empty[s], ((c / NQ) & 1) ^ 1, abort);
       if (!ok) break;
@@ -203,7 +207,7 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       for (int qi = lane; qi < qpc; qi += 32) {
         const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
         if (p.g5) {
-          tma_load_5d_outer(&tmQt, &bar->q_full[s], sQ + s * SM::kQ + qi * p.hpg * (DK * 2), r2 / p.hpg);
+          tma_load_5d_outer(&tmQt, &bar->q_full[s], sQ + s * SM::kQ + qi * p.hpg * (DK * 2), oct0, tok);
         } else {
 #pragma unroll
           for (int cc = 0; cc < DK / 64; ++cc)
@@ -612,13 +616,17 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     // producer warp: K/V block and gathered Q / dO rows by TMA; lane qi fetches and issues query qi of the chunk
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     const int oob_row = p.B * p.H * p.Tq;
+    const int oct0 = (b * p.H + g * p.hpg) >> 3;  // first head of the group, in units of 8 heads (rank-5 loads)
     bool ok = true;
     int c = 0, kvidx = -1, last_blk = -1;
     for (; !w.done(); w.next(), ++c) {
       const int s = c & 1;
       const int cnt = w.count();
-      int row = oob_row;
-      if (lane < cnt) row = (int)(((int64_t)bg * p.Tq + (ent[w.e + lane] & 0xFFFFFF)) * p.hpg);
+      int tok = p.Tq, row = oob_row;  // beyond the tensor: the tile is filled with zeros
+      if (lane < cnt) {
+        tok = ent[w.e + lane] & 0xFFFFFF;
+        row = (int)(((int64_t)bg * p.Tq + tok) * p.hpg);
+      }
       if (w.blk != last_blk) {
         last_blk = w.blk;
         ++kvidx;
@@ -639,8 +647,8 @@ slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
         uint8_t* stg = sSt + s * SM::kStage;
         if (p.g5) {
-          tma_load_5d_outer(&tmQt, &bar->q_full[s], stg + qi * p.hpg * (DK * 2), r2 / p.hpg);
-          tma_load_5d_outer(&tmdOt, &bar->q_full[s], stg + SM::kQ + qi * p.hpg * (DV * 2), r2 / p.hpg);
+          tma_load_5d_outer(&tmQt, &bar->q_full[s], stg + qi * p.hpg * (DK * 2), oct0, tok);
+          tma_load_5d_outer(&tmdOt, &bar->q_full[s], stg + SM::kQ + qi * p.hpg * (DV * 2), oct0, tok);
         } else {
           uint8_t* dst = stg + qi * p.hpg * 128;
 #pragma unroll
@@ -1033,13 +1041,17 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     // producer warp: K/V block and gathered Q / dO rows by TMA (lane qi issues query qi)
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     const int oob_row = p.B * p.H * p.Tq;
+    const int oct0 = (b * p.H + g * p.hpg) >> 3;  // first head of the group, in units of 8 heads (rank-5 loads)
     bool ok = true;
     int c = 0, kvidx = -1, last_blk = -1;
     for (; !w.done(); w.next(), ++c) {
       const int cnt = w.count();
       // this chunk's entries are fetched while the stage is still busy
-      int row = oob_row;
-      if (lane < cnt) row = (int)(((int64_t)bg * p.Tq + (ent[w.e + lane] & 0xFFFFFF)) * p.hpg);
+      int tok = p.Tq, row = oob_row;  // beyond the tensor: the tile is filled with zeros
+      if (lane < cnt) {
+        tok = ent[w.e + lane] & 0xFFFFFF;
+        row = (int)(((int64_t)bg * p.Tq + tok) * p.hpg);
+      }
       if (w.blk != last_blk) {
         last_blk = w.blk;
         ++kvidx;
@@ -1056,8 +1068,8 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       // the stage is usually still busy: start the rows on their way to L2 so that the tile loads find them there
       if (lane < cnt && lane < qpc) {
         if (p.g5) {
-          tma_prefetch_5d_outer(&tmQt, row / p.hpg);
-          tma_prefetch_5d_outer(&tmdOt, row / p.hpg);
+          tma_prefetch_5d_outer(&tmQt, oct0, tok);
+          tma_prefetch_5d_outer(&tmdOt, oct0, tok);
         } else {
 #pragma unroll
           for (int cc = 0; cc < DK / 64; ++cc) tma_prefetch_2d(&tmQt, cc * 64, row);
@@ -1075,8 +1087,8 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       for (int qi = lane; qi < qpc; qi += 32) {
         const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
         if (p.g5) {
-          tma_load_5d_outer(&tmQt, &bar->q_full[s], st + qi * p.hpg * (DK * 2), r2 / p.hpg);
-          tma_load_5d_outer(&tmdOt, &bar->q_full[s], st + SM::kQ + qi * p.hpg * (DV * 2), r2 / p.hpg);
+          tma_load_5d_outer(&tmQt, &bar->q_full[s], st + qi * p.hpg * (DK * 2), oct0, tok);
+          tma_load_5d_outer(&tmdOt, &bar->q_full[s], st + SM::kQ + qi * p.hpg * (DV * 2), oct0, tok);
         } else {
           uint8_t* dst = st + qi * p.hpg * 128;
 #pragma unroll
@@ -1444,7 +1456,6 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
   p.o_part = (__nv_bfloat16*)(w + csr_bytes);
   p.st_part = (float2*)(w + csr_bytes + al256(rows * dv * 2));
   void* qt = w + csr_bytes + al256(rows * dv * 2) + al256(rows * sizeof(float2));
-  if (int rc = token_major_copy_w(dk, q, qt, B, H, G, Tq, "slc_q_token_major", st)) return rc;
   p.q = (const __nv_bfloat16*)q;
   p.B = B; p.H = H; p.G = G; p.Tq = Tq; p.Tk = Tk; p.nslots = nslots; p.nblk = (Tk + 63) / 64; p.hpg = H / G;
   p.scale = scale; p.scale_log2 = scale * kLog2ef;
@@ -1453,11 +1464,14 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
   if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
   if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, 64)) return rc;
   CUtensorMap tqt;
-  p.g5 = (H / G) % 8 == 0 ? 1 : 0;  // whole 8-row swizzle atoms per query: one rank-5 tile load per query
+  // heads of a group filling whole 8-row swizzle atoms: one rank-5 tile load per query straight from q; otherwise the
+  // rows of a query are first made contiguous (token-major copy) and fetched with one 2-D tile per 64 columns
+  p.g5 = (H / G) % 8 == 0 ? 1 : 0;
   if (p.g5) {
-    if (int rc = make_tmap_token_rows(&tqt, qt, (uint64_t)B * G * Tq, H / G, dk)) return rc;
-  } else if (int rc = make_tmap_bf16_2d(&tqt, qt, (uint64_t)B * H * Tq, dk, H / G)) {
-    return rc;
+    if (int rc = make_tmap_head_rows(&tqt, q, (uint64_t)B * H, Tq, H / G, dk)) return rc;
+  } else {
+    if (int rc = token_major_copy_w(dk, q, qt, B, H, G, Tq, "slc_q_token_major", st)) return rc;
+    if (int rc = make_tmap_bf16_2d(&tqt, qt, (uint64_t)B * H * Tq, dk, H / G)) return rc;
   }
   CUtensorMap top;  // partial outputs as rows of dv values; one box = the heads of a group for one (query, slot)
   if (int rc = make_tmap_bf16_2d(&top, p.o_part, (uint64_t)rows, dv, (uint32_t)(H / G < 32 ? H / G : 32))) return rc;
@@ -1562,14 +1576,14 @@ int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indice
   CUtensorMap tk, tv;
   if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
   if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, 64)) return rc;
-  if (int rc = token_major_copy_w(dk, q, w + o_qt, B, H, G, Tq, "slc_q_token_major", st)) return rc;
-  if (int rc = token_major_copy_w(dv, dout, w + o_dot, B, H, G, Tq, "slc_do_token_major", st)) return rc;
   CUtensorMap tqt, tdot;
   p.g5 = (H / G) % 8 == 0 ? 1 : 0;  // whole 8-row swizzle atoms per query: one rank-5 tile load per query and tensor
   if (p.g5) {
-    if (int rc = make_tmap_token_rows(&tqt, w + o_qt, (uint64_t)B * G * Tq, H / G, dk)) return rc;
-    if (int rc = make_tmap_token_rows(&tdot, w + o_dot, (uint64_t)B * G * Tq, H / G, dv)) return rc;
+    if (int rc = make_tmap_head_rows(&tqt, q, (uint64_t)B * H, Tq, H / G, dk)) return rc;
+    if (int rc = make_tmap_head_rows(&tdot, dout, (uint64_t)B * H, Tq, H / G, dv)) return rc;
   } else {
+    if (int rc = token_major_copy_w(dk, q, w + o_qt, B, H, G, Tq, "slc_q_token_major", st)) return rc;
+    if (int rc = token_major_copy_w(dv, dout, w + o_dot, B, H, G, Tq, "slc_do_token_major", st)) return rc;
     if (int rc = make_tmap_bf16_2d(&tqt, w + o_qt, (uint64_t)B * H * Tq, dk, H / G)) return rc;
     if (int rc = make_tmap_bf16_2d(&tdot, w + o_dot, (uint64_t)B * H * Tq, dv, H / G)) return rc;
   }

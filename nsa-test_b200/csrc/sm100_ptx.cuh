@@ -111,16 +111,17 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
-// rank-5 tile load whose box starts at coordinate (0, 0, 0, 0, c4)
-__device__ __forceinline__ void tma_load_5d_outer(const CUtensorMap* map, uint64_t* bar, void* dst, int c4) {
+// rank-5 tile load whose box starts at coordinate (0, 0, 0, c3, c4)
+__device__ __forceinline__ void tma_load_5d_outer(const CUtensorMap* map, uint64_t* bar, void* dst, int c3, int c4) {
   asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(0), "r"(c4)
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(0), "r"(c3), "r"(c4)
       : "memory");
 }
 // bring the tiles a later load will fetch into L2 (no shared-memory destination, no completion tracking)
-__device__ __forceinline__ void tma_prefetch_5d_outer(const CUtensorMap* map, int c4) {
-  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %1, %1, %1, %2}];" ::"l"(map), "r"(0), "r"(c4) : "memory");
+__device__ __forceinline__ void tma_prefetch_5d_outer(const CUtensorMap* map, int c3, int c4) {
+  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %1, %1, %2, %3}];" ::"l"(map), "r"(0), "r"(c3), "r"(c4)
+               : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
