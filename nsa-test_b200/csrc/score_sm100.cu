@@ -332,7 +332,9 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
 // One warp per query row: top-k of the row's n_sel block scores (score descending, ties to the lower id), then the
 // forced blocks first, repeats dropped, cut to n, padded with -1.  Scores of blocks past the last key tile of the
-// row's query tile were never written and count as 0.
+// row's query tile were never written and count as 0.  Lane i owns the ids i, i + 32, ...: PER of them in registers
+// (PER * 32 >= n_sel), or the row in shared memory when PER == 0 (any n_sel).
+template <int PER>
 __global__ void __launch_bounds__(128)
 topn_rows_kernel(const float* __restrict__ sel, int32_t* __restrict__ out, int64_t rows, int T, int n_sel, int per_tile, int l,
                  int d, int nb, int lprime, int n, int n_fixed) {
@@ -344,16 +346,28 @@ topn_rows_kernel(const float* __restrict__ sel, int32_t* __restrict__ out, int64
   const int tl = (t / 128) * 128 + 127;
   const int kmax = tl >= l - 1 ? min(nb - 1, (tl - l + 1) / d) : -1;
   const int lim = min(n_sel, max(1, kmax / 128 + 1) * per_tile);
-  float* v = sm_rows + warp * n_sel;
   const float* src = sel + row * n_sel;
+  float* v = sm_rows + warp * n_sel;  // PER == 0 only
+  float vr[PER > 0 ? PER : 1];        // PER > 0 only
   float bv = -CUDART_INF_F;
   int bi = 0x7fffffff;
-  for (int j = lane; j < n_sel; j += 32) {
-    const float x = j < lim ? src[j] : 0.f;
-    v[j] = x;
-    if (x > bv) { bv = x; bi = j; }  // ascending j: an equal score never displaces an earlier id
+  if (PER > 0) {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int j = lane + 32 * i;
+      vr[i] = j < lim ? src[j] : (j < n_sel ? 0.f : -CUDART_INF_F);
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if (vr[i] > bv) { bv = vr[i]; bi = lane + 32 * i; }  // ascending id: an equal score never displaces an earlier id
+  } else {
+    for (int j = lane; j < n_sel; j += 32) {
+      const float x = j < lim ? src[j] : 0.f;
+      v[j] = x;
+      if (x > bv) { bv = x; bi = j; }
+    }
+    __syncwarp();
   }
-  __syncwarp();
   const int k_actual = min(n, n_sel);
   int mytop = -1;  // lane r keeps the r-th pick
   for (int r = 0; r < k_actual; ++r) {
@@ -366,37 +380,64 @@ topn_rows_kernel(const float* __restrict__ sel, int32_t* __restrict__ out, int64
       if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
     }
     if (lane == r) mytop = wi;
-    if ((wi & 31) == lane) {  // the owner retires the pick and looks for its next best
-      v[wi] = -CUDART_INF_F;
-      bv = -CUDART_INF_F;
-      bi = 0x7fffffff;
-      for (int j = lane; j < n_sel; j += 32) {
-        const float x = v[j];
-        if (x > bv) { bv = x; bi = j; }
+    // the owner retires the pick and looks for its next best
+    if (PER > 0) {
+      const bool mine = (wi & 31) == lane;
+      const int slot = wi >> 5;
+      if (mine) { bv = -CUDART_INF_F; bi = 0x7fffffff; }
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        if (mine && i == slot) vr[i] = -CUDART_INF_F;
+        if (mine && vr[i] > bv) { bv = vr[i]; bi = lane + 32 * i; }
       }
+    } else {
+      if ((wi & 31) == lane) {
+        v[wi] = -CUDART_INF_F;
+        bv = -CUDART_INF_F;
+        bi = 0x7fffffff;
+        for (int j = lane; j < n_sel; j += 32) {
+          const float x = v[j];
+          if (x > bv) { bv = x; bi = j; }
+        }
+      }
+      __syncwarp();
     }
-    __syncwarp();
   }
-  int res[kScoreMaxN];
-  int nres = 0;
-  auto push = [&](int id) {
-    if (nres >= n) return;
-    for (int i = 0; i < nres; ++i)
-      if (res[i] == id) return;
-    res[nres++] = id;
-  };
-  if (n_fixed > 0) {
-    push(0);
-    push(t < lprime ? 0 : (t - lprime) / lprime);
-    push(t / lprime);
-  }
-  for (int i = 0; i < k_actual; ++i) {
-    const int id = __shfl_sync(0xffffffffu, mytop, i);
-    push(id);
-  }
-  if (lane == 0) {
-    int32_t* dst = out + row * n;
-    for (int i = 0; i < n; ++i) dst[i] = i < nres ? res[i] : -1;
+  int32_t* dst = out + row * n;
+  const int nf = n_fixed > 0 ? 3 : 0;
+  if (nf + k_actual <= 32) {
+    // lane i holds candidate i: the forced blocks, then the picks in order; a candidate equal to an earlier one is dropped
+    int cand = -1;
+    const int pick = __shfl_sync(0xffffffffu, mytop, (lane - nf) & 31);
+    if (lane < nf) cand = lane == 0 ? 0 : (lane == 1 ? (t < lprime ? 0 : (t - lprime) / lprime) : t / lprime);
+    else if (lane < nf + k_actual) cand = pick;
+    const unsigned same = __match_any_sync(0xffffffffu, cand);
+    const bool keep = cand >= 0 && (same & ((1u << lane) - 1u)) == 0;
+    const unsigned kept = __ballot_sync(0xffffffffu, keep);
+    const int pos = __popc(kept & ((1u << lane) - 1u));
+    if (keep && pos < n) dst[pos] = cand;
+    const int cnt = min(n, __popc(kept));
+    for (int i = cnt + lane; i < n; i += 32) dst[i] = -1;
+  } else {
+    int res[kScoreMaxN];
+    int nres = 0;
+    auto push = [&](int id) {
+      if (nres >= n) return;
+      for (int i = 0; i < nres; ++i)
+        if (res[i] == id) return;
+      res[nres++] = id;
+    };
+    if (nf) {
+      push(0);
+      push(t < lprime ? 0 : (t - lprime) / lprime);
+      push(t / lprime);
+    }
+    for (int i = 0; i < k_actual; ++i) {
+      const int id = __shfl_sync(0xffffffffu, mytop, i);
+      push(id);
+    }
+    if (lane == 0)
+      for (int i = 0; i < n; ++i) dst[i] = i < nres ? res[i] : -1;
   }
 }
 
@@ -472,11 +513,23 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
   else rc = launch_score_t<64>(tq, thi, tlo, p, st);
   if (rc) return rc;
   const int64_t rows = (int64_t)B * G * T;
-  const size_t sm = 4 * (size_t)n_sel * sizeof(float);
-  if (cudaFuncSetAttribute(topn_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
-    return fail(NSA_ERR_LAUNCH, "score_topn: cannot reserve shared memory for the row selection");
   KernelTimer kt("score_topn_rows", st);
-  topn_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, sm, st>>>(sel, out, rows, T, n_sel, 128 / s_, l, d, nb, lprime, n, n_fixed);
+  const unsigned grid = (unsigned)((rows + 3) / 4);
+#define NSA_ROWS_CASE(PER_)                                                                                                   \
+  topn_rows_kernel<PER_><<<grid, 128, 0, st>>>(sel, out, rows, T, n_sel, 128 / s_, l, d, nb, lprime, n, n_fixed)
+  if (n_sel <= 8 * 32) {
+    NSA_ROWS_CASE(8);
+  } else if (n_sel <= 16 * 32) {
+    NSA_ROWS_CASE(16);
+  } else if (n_sel <= 32 * 32) {
+    NSA_ROWS_CASE(32);
+  } else {
+    const size_t sm = 4 * (size_t)n_sel * sizeof(float);
+    if (cudaFuncSetAttribute(topn_rows_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
+      return fail(NSA_ERR_LAUNCH, "score_topn: cannot reserve shared memory for the row selection");
+    topn_rows_kernel<0><<<grid, 128, sm, st>>>(sel, out, rows, T, n_sel, 128 / s_, l, d, nb, lprime, n, n_fixed);
+  }
+#undef NSA_ROWS_CASE
   return check_launch("score_topn_rows");
 }
 
