@@ -15,6 +15,7 @@
 // CTAs own fixed-size ranges of the inverse index (not whole blocks), so a block selected by every
 // query (block 0) is spread over many CTAs.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "attn_args.cuh"
 #include "common.cuh"
@@ -1355,6 +1356,480 @@ slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// backward, fused: dQ partials AND dK/dV of each block from one pass over the gathered rows.
+// Per chunk: S = Q K^T, dP = dO V^T (one TMEM buffer), rows -> P, dS; dS goes back to TMEM (bf16, over
+// the dP columns) for dQ_part = dS K, and P / dS go through shared memory (64-row halves) for the
+// transposed accumulations dV^T += dO^T P, dK^T += Q^T dS.  TMEM: S 64 | dP 64 | dQ dk | dV^T 64 | dK^T 64 (+64)
+// = 512 columns at dk = 192.  The rows are gathered once and S / dP computed once, instead of once per kernel.
+// The issuer polls four kinds of work: S of the next chunk, dQ of the current one, dP of the next one (program
+// order after dQ, which reads dS from the same columns), and the accumulation steps.
+// ------------------------------------------------------------------------------------------------
+template <int DK, int DV>
+struct SlcBwdSmem {
+  static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2, kdO = 128 * DV * 2;
+  static constexpr int kStage = kQ + kdO;
+  static constexpr int kHalf = 64 * 128;   // 64 rows x 64 keys of bf16 P (or dS), 128-byte swizzle
+  static constexpr int kOut = 8 * 1024;    // per compute warp: 32 rows x 32 bytes of dQ being transposed for the stores
+  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, oP = oSt + 2 * kStage, odS = oP + kHalf, oOut = odS + kHalf,
+                       oBar = oOut + kOut;
+  static constexpr int kDynamic = oBar + 256 + 1024;
+};
+struct SlcBwdBarriers {
+  // sdp_full / dq_full: one barrier per compute group (chunk parity).  A group only sees every other chunk, and a parity
+  // wait on a barrier shared by both groups could not tell its chunk's completion from the one two chunks earlier.
+  uint64_t kv_full, kv_empty, q_full[2], q_empty[2], sdp_full[2], sdp_free, dst_full, dq_full[2], dq_read, p_full, p_free[4], ds_full,
+      ds_free[4], acc_full, acc_read;
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(384, 1)
+slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                     const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmdOt, const SlcParams p) {
+  using SM = SlcBwdSmem<DK, DV>;
+  constexpr int MK1 = DK >= 128 ? 128 : 64, MK2 = DK - MK1;  // dK^T as one or two accumulators
+  static_assert(MK2 == 0 || MK2 == 64, "dk is 64, 128 or 192");
+  static_assert(DV == 64 || DV == 128, "dv is 64 or 128");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sSt = smem + SM::oSt, *sP = smem + SM::oP, *sdS = smem + SM::odS;
+  SlcBwdBarriers* bar = reinterpret_cast<SlcBwdBarriers*>(smem + SM::oBar);
+  volatile int* abort = &bar->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bg = blockIdx.y, b = bg / p.G, g = bg % p.G;
+  const int* off = p.csr_off + (int64_t)bg * (p.nblk + 1);
+  const int* ent = p.csr_t + (int64_t)bg * p.Tq * p.nslots;
+  const int e0 = blockIdx.x * kEntriesPerCta;
+  const int qpc = 128 / p.hpg;
+  // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
+  const bool has_work = e0 < off[p.nblk] && !(p.timeouts && *(volatile const int*)p.timeouts != 0);
+  const int nseg = gridDim.x + p.nblk;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->kv_full, 1);
+    mbar_init(&bar->kv_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->q_full[i], 1);
+      mbar_init(&bar->q_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->sdp_full[i], 1);
+      mbar_init(&bar->dq_full[i], 1);
+    }
+    mbar_init(&bar->sdp_free, 128);
+    mbar_init(&bar->dst_full, 128);
+    mbar_init(&bar->dq_read, 128);
+    mbar_init(&bar->p_full, 64);
+    mbar_init(&bar->ds_full, 64);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&bar->p_free[i], 1);
+      mbar_init(&bar->ds_free[i], 1);
+    }
+    mbar_init(&bar->acc_full, 1);
+    mbar_init(&bar->acc_read, 256);
+    bar->abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 8) tmem_alloc(&bar->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  constexpr uint32_t cS = 0, cdP = 64, cdQ = 128, cdV = 128 + DK, cdK1 = cdV + 64, cdK2 = cdK1 + 64;
+  static_assert(cdK2 + (MK2 ? 64 : 0) <= 512, "TMEM columns");
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+
+  if (warp >= 10) {
+  } else if (!has_work) {
+  } else if (warp == 9) {
+    // producer warp: K/V block and gathered Q / dO rows by TMA (lane qi issues query qi)
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    const int oob_row = p.B * p.H * p.Tq;
+    const int oct0 = (b * p.H + g * p.hpg) >> 3;  // first head of the group, in units of 8 heads (rank-5 loads)
+    bool ok = true;
+    int c = 0, kvidx = -1, last_blk = -1;
+    for (; !w.done(); w.next(), ++c) {
+      const int cnt = w.count();
+      int tok = p.Tq, row = oob_row;  // beyond the tensor: the tile is filled with zeros
+      if (lane < cnt) {
+        tok = ent[w.e + lane] & 0xFFFFFF;
+        row = (int)(((int64_t)bg * p.Tq + tok) * p.hpg);
+      }
+      if (w.blk != last_blk) {
+        last_blk = w.blk;
+        ++kvidx;
+        ok = mbar_wait_warp(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
+          tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
+          for (int cc = 0; cc < DV / 64; ++cc)
+            tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
+        }
+      }
+      const int s = c & 1;
+      // the stage is usually still busy: start the rows on their way to L2 so that the tile loads find them there
+      if (lane < cnt && lane < qpc) {
+        if (p.g5) {
+          tma_prefetch_5d_outer(&tmQt, oct0, tok);
+          tma_prefetch_5d_outer(&tmdOt, oct0, tok);
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < DK / 64; ++cc) tma_prefetch_2d(&tmQt, cc * 64, row);
+#pragma unroll
+          for (int cc = 0; cc < DV / 64; ++cc) tma_prefetch_2d(&tmdOt, cc * 64, row);
+        }
+      }
+      ok = mbar_wait_warp(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
+      if (!ok) break;
+      uint8_t* st = sSt + s * SM::kStage;
+      if (lane == 0) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
+      __syncwarp();
+      for (int qi = lane; qi < qpc; qi += 32) {
+        const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
+        if (p.g5) {
+          tma_load_5d_outer(&tmQt, &bar->q_full[s], st + qi * p.hpg * (DK * 2), oct0, tok);
+          tma_load_5d_outer(&tmdOt, &bar->q_full[s], st + SM::kQ + qi * p.hpg * (DV * 2), oct0, tok);
+        } else {
+          uint8_t* dst = st + qi * p.hpg * 128;
+#pragma unroll
+          for (int cc = 0; cc < DK / 64; ++cc) tma_load_2d(&tmQt, &bar->q_full[s], dst + cc * 16384, cc * 64, r2);
+#pragma unroll
+          for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
+      for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
+    }
+  } else if (warp == 8) {
+    // UMMA issuer: warp-uniform polling loop, one elected lane issues
+    constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);     // Q rows (K-major) x K block (keys contiguous)
+    constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);    // dO rows (K-major) x V block read K-major (dv contiguous)
+    constexpr uint32_t iddQh = idesc_bf16(128, DK / 2, 0, 0);  // dS (TMEM) x half of the K block's dk rows, read K-major
+    constexpr uint32_t iddV = idesc_bf16(DV, 64, 1, 1);     // dO^T (dv contiguous) x P (keys contiguous), K = gathered rows
+    constexpr uint32_t iddK1 = idesc_bf16(MK1, 64, 1, 1);   // Q^T (dk contiguous) x dS (keys contiguous)
+    constexpr uint32_t iddK2 = idesc_bf16(64, 64, 1, 1);
+    const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024);
+    const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
+    const uint64_t dPb = smem_desc_sw128(smem_u32(sP), 16, 1024);    // one 64-key MN block: LBO unused
+    const uint64_t dSb = smem_desc_sw128(smem_u32(sdS), 16, 1024);
+    const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;  // Q tile: row-group / column-block strides
+    const uint32_t sboO = p.g5 ? (DV / 64) * 1024 : 1024, cbO = p.g5 ? 1024 : 16384;  // dO tile
+    ChunkWalker wA(off, p.nblk, e0, e0 + kEntriesPerCta, qpc), wH = wA;
+    bool ok = true, fresh = true;      // fresh: the next accumulation starts a new segment
+    int cs = 0, cp = 0, cq = 0;        // next chunk whose S / dP / dQ MMAs are issued (cp <= cs, cq <= cp)
+    int ch = 0, hstep = 0;             // chunk whose P / dS are consumed and its step: P(h0), dS(h0), P(h1), dS(h1)
+    int kvidx = 0, blkA = wA.blk, seg = 0, u = 0;
+    bool kv_wait = true;               // the K/V tile of the block of chunk `cs` has not been seen to land yet
+    bool kv_switch = false;            // chunk `cs` starts another block: its K/V tile has yet to be asked for
+    long long idle_since = 0;
+    while (ok && !wH.done()) {
+      bool did = false;
+      // ---- accumulate: dV^T / dK^T of chunk ch
+      if (ch < cp) {
+        bool ready = mbar_test((hstep & 1) ? &bar->ds_full : &bar->p_full, u & 1);
+        // a new segment overwrites the accumulators: the previous segment's sums must have been read out
+        if (ready && fresh && hstep == 0 && seg > 0) ready = mbar_test(&bar->acc_read, (seg - 1) & 1);
+        if (__all_sync(0xffffffffu, ready)) {
+          tc_fence_after();
+          const int h = hstep >> 1;
+          const uint32_t st = smem_u32(sSt + (ch & 1) * SM::kStage);
+          // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart inside an 8-row group
+          const uint64_t dQt = smem_desc_sw128(st, cbQ, sboQ), dOt = smem_desc_sw128(st + SM::kQ, cbO, sboO);
+          if ((hstep & 1) == 0) {
+            if (elect_one()) {
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                umma_ss(tmem + cdV, desc_advance(dOt, (h * 8 + kk * 2) * sboO), desc_advance(dPb, kk * 2048), iddV,
+                        !(fresh && h == 0 && kk == 0));
+              umma_commit(&bar->p_free[u & 3]);
+            }
+          } else {
+            if (elect_one()) {
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) {
+                umma_ss(tmem + cdK1, desc_advance(dQt, (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK1,
+                        !(fresh && h == 0 && kk == 0));
+                if (MK2)
+                  umma_ss(tmem + cdK2, desc_advance(dQt, 2 * cbQ + (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK2,
+                          !(fresh && h == 0 && kk == 0));
+              }
+              umma_commit(&bar->ds_free[u & 3]);
+              if (hstep == 3) umma_commit(&bar->q_empty[ch & 1]);  // the chunk's Q / dO stage is free again
+            }
+          }
+          __syncwarp();
+          if (hstep == 1) fresh = false;
+          if (hstep & 1) ++u;
+          if (++hstep == 4) {
+            hstep = 0;
+            const int blk_done = wH.blk;
+            wH.next();
+            if (wH.done() || wH.blk != blk_done) {
+              // last chunk of the block (or of the CTA): hand the accumulators over
+              if (elect_one()) umma_commit(&bar->acc_full);
+              __syncwarp();
+              ++seg;
+              fresh = true;
+            }
+            ++ch;
+          }
+          did = true;
+        }
+      }
+      // ---- dQ partial of chunk cq: dS is in TMEM, the accumulator has been drained by the previous chunk's epilogue
+      if (cq < cp) {
+        bool ready = mbar_test(&bar->dst_full, cq & 1);
+        if (ready && cq > 0) ready = mbar_test(&bar->dq_read, (cq - 1) & 1);
+        if (__all_sync(0xffffffffu, ready)) {
+          tc_fence_after();
+          if (elect_one()) {
+#pragma unroll
+            for (int hh2 = 0; hh2 < 2; ++hh2)
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                umma_ts(tmem + cdQ + hh2 * (DK / 2), tmem + cdP + kk * 8, desc_advance(dKmn, hh2 * (DK / 2) * 128 + kk * 32), iddQh,
+                        kk > 0);
+            umma_commit(&bar->dq_full[cq & 1]);
+          }
+          __syncwarp();
+          ++cq;
+          did = true;
+        }
+      }
+      // ---- dP of chunk cp: after S of the same chunk, and in program order after dQ of the chunk before (same columns)
+      if (cp < cs && cq == cp) {
+        const int s = cp & 1;
+        const uint32_t st = smem_u32(sSt + s * SM::kStage);
+        const uint64_t ddO = smem_desc_sw128(st + SM::kQ, 16, sboO);
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < DV / 16; ++kk)
+            umma_ss(tmem + cdP, desc_advance(ddO, (kk >> 2) * cbO + (kk & 3) * 32), desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32),
+                    iddP, kk > 0);
+          umma_commit(&bar->sdp_full[cp & 1]);
+        }
+        __syncwarp();
+        ++cp;
+        did = true;
+      }
+      // ---- S of chunk cs: its rows have landed and the compute warps have taken S / dP of the chunk before
+      if (!wA.done() && cs == cp) {
+        if (wA.blk != blkA && !kv_switch) kv_switch = true;
+        bool ready = true;
+        if (kv_switch) {
+          // another block: the single K/V slot is refilled once dQ of every chunk of the old block has been issued
+          if (cq == cs) {
+            if (elect_one()) umma_commit(&bar->kv_empty);
+            __syncwarp();
+            ++kvidx;
+            kv_wait = true;
+            kv_switch = false;
+            blkA = wA.blk;
+          } else {
+            ready = false;
+          }
+        }
+        const int s = cs & 1;
+        if (ready) ready = mbar_test(&bar->q_full[s], (cs >> 1) & 1) && (cs == 0 || mbar_test(&bar->sdp_free, (cs - 1) & 1));
+        if (ready && kv_wait) ready = mbar_test(&bar->kv_full, kvidx & 1);
+        if (__all_sync(0xffffffffu, ready)) {
+          kv_wait = false;
+          tc_fence_after();
+          const uint32_t st = smem_u32(sSt + s * SM::kStage);
+          const uint64_t dQ = smem_desc_sw128(st, 16, sboQ);
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < DK / 16; ++kk)
+              umma_ss(tmem + cS, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
+          }
+          __syncwarp();
+          wA.next();
+          ++cs;
+          did = true;
+        }
+      }
+      // ---- nothing ready: bounded idling
+      if (did) {
+        idle_since = 0;
+      } else {
+        const long long now = clock64();
+        if (idle_since == 0) idle_since = now;
+        if (*abort || now - idle_since > (1ll << 28)) {
+          *abort = 1;
+          ok = false;
+        }
+        __nanosleep(32);
+      }
+    }
+  } else {
+    // compute: one gathered row per thread; groups alternate chunks; both groups take part in every flush
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+    const int grp = warp >> 2, warp4 = warp & 3;
+    const int r = warp4 * 32 + lane;
+    const int half = warp4 >> 1, rr = r & 63;  // which 64-row half of the chunk this row is handed over in
+    const uint32_t lane_base = (uint32_t)(warp4 * 32) << 16;
+    uint8_t* ostage = smem + SM::oOut + warp * 1024;
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    bool ok = true;
+    int c = 0, last_blk = -1, seg = 0;
+    auto flush = [&](int blk) -> bool {
+      if (!mbar_wait(&bar->acc_full, seg & 1, abort)) return false;
+      tc_fence_after();
+      const int64_t key_base = ((int64_t)bg * nseg + blockIdx.x + blk) * 64;
+      if (grp == 0) {
+        slc_flush_rows<MK1>(tmem + cdK1, p.dk_part, key_base, DK, 0, warp4, lane);
+        if (MK2) slc_flush_rows<64>(tmem + cdK2, p.dk_part, key_base, DK, MK1, warp4, lane);
+      } else {
+        slc_flush_rows<DV>(tmem + cdV, p.dv_part, key_base, DV, 0, warp4, lane);
+      }
+      tc_fence_before();
+      mbar_arrive(&bar->acc_read);
+      ++seg;
+      return true;
+    };
+    // this thread's row in a given chunk: entry (-1: row not in use), lse2 (+inf then, so P = 0), D
+    const int qi = r / p.hpg, hh = r % p.hpg;
+    int ent_next = -1;
+    float lse_next = CUDART_INF_F, D_next = 0.f;
+    auto fetch = [&](const ChunkWalker& wk) {
+      ent_next = -1; lse_next = CUDART_INF_F; D_next = 0.f;
+      if (!wk.done() && qi < wk.count()) {
+        ent_next = ent[wk.e + qi];
+        const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + (ent_next & 0xFFFFFF);
+        lse_next = p.lse2[srow];
+        D_next = p.D[srow];
+      }
+    };
+    {
+      ChunkWalker w0 = w;
+      if (grp == 1 && !w0.done()) w0.next();
+      fetch(w0);
+    }
+    for (; !w.done() && ok; w.next(), ++c) {
+      if (w.blk != last_blk) {
+        if (last_blk >= 0) ok = flush(last_blk);
+        if (!ok) break;
+        last_blk = w.blk;
+      }
+      if ((c & 1) != grp) continue;
+      const int entry = ent_next;
+      const float lse2 = lse_next, Dr = D_next;
+      const int t = entry < 0 ? -1 : (entry & 0xFFFFFF), slot = entry < 0 ? 0 : (entry >> 24);
+      const int chi = t - w.blk * 64;
+      {  // this group's next chunk: fetch its statistics one chunk ahead
+        ChunkWalker w2 = w;
+        w2.next();
+        if (!w2.done()) w2.next();
+        fetch(w2);
+      }
+      ok = mbar_wait(&bar->sdp_full[grp], (c >> 1) & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t pP[32], pS[32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sv[32], dp[32];
+        tmem_ld32(tmem + lane_base + cS + cc * 32, sv);
+        tmem_ld32(tmem + lane_base + cdP + cc * 32, dp);
+        tc_wait_ld();
+        if (cc == 1) {  // both tiles are in registers: S of the next chunk may be issued
+          tc_fence_before();
+          mbar_arrive(&bar->sdp_free);
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int c0 = cc * 32 + 2 * e;
+          const float p0 = c0 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse2)) : 0.f;
+          const float p1 = c0 + 1 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse2)) : 0.f;
+          __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1);
+          __nv_bfloat162 y = __floats2bfloat162_rn(p0 * (__uint_as_float(dp[2 * e]) - Dr), p1 * (__uint_as_float(dp[2 * e + 1]) - Dr));
+          pP[cc * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
+          pS[cc * 16 + e] = *reinterpret_cast<uint32_t*>(&y);
+        }
+      }
+      // dS for the dQ MMA: bf16 over the first half of the dP columns (dP of the next chunk is issued after that MMA)
+      tmem_st32(tmem + lane_base + cdP, pS);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->dst_full);
+      // hand-over of P / dS for the transposed accumulations: the staging tiles are used by (chunk, half) in order
+      const int u = 2 * c + half;
+      if (u > 0) {
+        ok = mbar_wait(&bar->p_free[(u - 1) & 3], ((u - 1) >> 2) & 1, abort);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(sP + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pP[4 * j], pP[4 * j + 1], pP[4 * j + 2], pP[4 * j + 3]);
+      fence_proxy_async();
+      mbar_arrive(&bar->p_full);
+      if (u > 0) {
+        ok = mbar_wait(&bar->ds_free[(u - 1) & 3], ((u - 1) >> 2) & 1, abort);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(sdS + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pS[4 * j], pS[4 * j + 1], pS[4 * j + 2], pS[4 * j + 3]);
+      fence_proxy_async();
+      mbar_arrive(&bar->ds_full);
+      // dQ partial of this chunk: TMEM -> registers -> per-warp staging (32 rows x 32 bytes, pieces swapped for odd
+      // groups of four rows) -> 32-byte runs of 16 rows per store instruction
+      const int prow = entry >= 0 ? (int)((((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh) : -1;
+      ok = mbar_wait(&bar->dq_full[grp], (c >> 1) & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < DK / 32; ++cc) {
+        uint32_t ov[32];
+        tmem_ld32(tmem + lane_base + cdQ + cc * 32, ov);
+        tc_wait_ld();
+        if (cc == DK / 32 - 1) {  // the accumulator sits in registers: the next chunk's dQ may be issued
+          tc_fence_before();
+          mbar_arrive(&bar->dq_read);
+        }
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          __syncwarp();  // the previous 16 columns have been read back
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const uint32_t* src = &ov[sub * 16 + j * 8];
+            uint4 wv;
+            __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
+            __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
+            __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
+            __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            wv.x = *reinterpret_cast<uint32_t*>(&a0); wv.y = *reinterpret_cast<uint32_t*>(&a1);
+            wv.z = *reinterpret_cast<uint32_t*>(&a2); wv.w = *reinterpret_cast<uint32_t*>(&a3);
+            *reinterpret_cast<uint4*>(ostage + lane * 32 + ((j ^ ((lane >> 2) & 1)) << 4)) = wv;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int r2 = i * 16 + (lane >> 1), piece = lane & 1;  // row of this warp whose piece this lane forwards
+            const int grow = __shfl_sync(0xffffffffu, prow, r2);
+            const uint4 wv = *reinterpret_cast<const uint4*>(ostage + r2 * 32 + ((piece ^ ((r2 >> 2) & 1)) << 4));
+            if (grow >= 0) *reinterpret_cast<uint4*>(p.dq_part + (int64_t)grow * DK + cc * 32 + sub * 16 + piece * 8) = wv;
+          }
+        }
+      }
+    }
+    if (ok && last_blk >= 0) flush(last_blk);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 // dK/dV of block `blk` += sum of its segment partials in segment order
 __global__ void slc_reduce_dkv_kernel(const float* __restrict__ dk_part, const float* __restrict__ dv_part,
                                       const int* __restrict__ csr_off, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
@@ -1516,7 +1991,14 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
       cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, SlcDkvSmem<DK, DV>::kDynamic) != cudaSuccess)
     return fail(NSA_ERR_LAUNCH, "slc_bwd: cannot reserve shared memory");
   const int nparts = (int)(((int64_t)p.Tq * p.nslots + kEntriesPerCta - 1) / kEntriesPerCta);
-  {
+  static const bool split = getenv("NSA_SLC_BWD_SPLIT") != nullptr;
+  if (!split) {
+    auto kf = slc_bwd_fused_kernel<DK, DV>;
+    if (cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, SlcBwdSmem<DK, DV>::kDynamic) != cudaSuccess)
+      return fail(NSA_ERR_LAUNCH, "slc_bwd: cannot reserve shared memory");
+    KernelTimer kt("slc_bwd_fused", st);
+    kf<<<dim3(nparts, p.B * p.G), 384, SlcBwdSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
+  } else {
     KernelTimer kt("slc_bwd_dq", st);
     kq<<<dim3(nparts, p.B * p.G), 320, SlcDqSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
   }
@@ -1537,7 +2019,7 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
     }
   }
   if (int rc = check_launch("slc_combine_dq")) return rc;
-  {
+  if (split) {
     KernelTimer kt("slc_bwd_dkv", st);
     kkv<<<dim3(nparts, p.B * p.G), 384, SlcDkvSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
   }
