@@ -165,8 +165,7 @@ def kernel_flops(T):
         f[f"fa_bwd_dq_{br}"] = unit[br] * 2 * (2 * dk + dv)             # S, dP, dQ
         f[f"fa_bwd_dkv_{br}"] = unit[br] * 2 * (2 * dk + 2 * dv)        # S^T, dP^T, dV, dK
     f["slc_fwd"] = unit["slc"] * 2 * (dk + dv)
-    f["slc_bwd_dq"] = unit["slc"] * 2 * (2 * dk + dv)
-    f["slc_bwd_dkv"] = unit["slc"] * 2 * (2 * dk + 2 * dv)
+    f["slc_bwd_fused"] = unit["slc"] * 2 * (3 * dk + 2 * dv)           # S, dP, dQ, dV, dK
     return f
 
 

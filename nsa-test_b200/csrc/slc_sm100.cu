@@ -10,12 +10,11 @@
 // partial result; partials of a query are merged afterwards in slot order, which keeps everything
 // deterministic:
 //   forward   partial O (normalised, bf16) + (max, sum) per (query, slot, head) -> slc_combine_fwd
-//   backward  dQ partials per (query, slot, head) -> slc_combine_dq; dK/dV accumulate inside the CTA
-//             that owns the block (transposed tiles, M = 64 keys) and are flushed once per CTA.
+//   backward  one fused kernel: dQ partials per (query, slot, head) -> slc_combine_dq; dK/dV accumulate
+//             (transposed, in TMEM) inside the CTA that owns the block and are flushed once per CTA and block.
 // CTAs own fixed-size ranges of the inverse index (not whole blocks), so a block selected by every
 // query (block 0) is spread over many CTAs.
 #include <cuda.h>
-#include <stdlib.h>
 
 #include "attn_args.cuh"
 #include "common.cuh"
@@ -554,293 +553,8 @@ __global__ void slc_combine_fwd_bulk_kernel(const __nv_bfloat16* __restrict__ o_
 }
 
 // ------------------------------------------------------------------------------------------------
-// backward, part 1: dQ partials.  Per chunk: S = Q K^T, dP = dO V^T, dS = P*(dP - D) -> TMEM (bf16),
-// dQ_part = dS K.  One K/V slot (a block change drains the pipe), two S/dP buffers, one dQ buffer.
+// backward: combine of the per-(query, slot) dQ partials written by the fused kernel below
 // ------------------------------------------------------------------------------------------------
-template <int DK, int DV>
-struct SlcDqSmem {
-  static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2, kdO = 128 * DV * 2;
-  static constexpr int kOut = 8 * 2048;  // per compute warp: 32 rows x 32 bf16 columns being transposed for coalesced stores
-  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, kStage = kQ + kdO, oOut = oSt + 2 * kStage, oBar = oOut + kOut;
-  static constexpr int kDynamic = oBar + 256 + 1024;
-};
-struct SlcDqBarriers {
-  uint64_t kv_full, kv_empty, q_full[2], q_empty[2], sdp_full[2], ds_full[2], dq_full[2], dq_read_lo[2], dq_read_hi[2];
-  uint32_t tmem_base;
-  int abort;
-};
-
-template <int DK, int DV>
-__global__ void __launch_bounds__(320, 1)
-slc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                  const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmdOt, const SlcParams p) {
-  using SM = SlcDqSmem<DK, DV>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sSt = smem + SM::oSt;
-  SlcDqBarriers* bar = reinterpret_cast<SlcDqBarriers*>(smem + SM::oBar);
-  volatile int* abort = &bar->abort;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bg = blockIdx.y, b = bg / p.G, g = bg % p.G;
-  const int* off = p.csr_off + (int64_t)bg * (p.nblk + 1);
-  const int* ent = p.csr_t + (int64_t)bg * p.Tq * p.nslots;
-  const int e0 = blockIdx.x * kEntriesPerCta;
-  const int qpc = 128 / p.hpg;
-  // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
-  const bool has_work = e0 < off[p.nblk] && !(p.timeouts && *(volatile const int*)p.timeouts != 0);
-
-  if (threadIdx.x == 0) {
-    mbar_init(&bar->kv_full, 1);
-    mbar_init(&bar->kv_empty, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar->q_full[i], 1);
-      mbar_init(&bar->q_empty[i], 1);
-      mbar_init(&bar->sdp_full[i], 1);
-      mbar_init(&bar->ds_full[i], 128);
-      mbar_init(&bar->dq_full[i], 1);   // per compute group: a group only ever sees its own chunks' phases
-      mbar_init(&bar->dq_read_lo[i], 128);  // the dQ accumulator is handed back in two column halves
-      mbar_init(&bar->dq_read_hi[i], 128);
-    }
-    bar->abort = 0;
-    fence_barrier_init();
-    fence_proxy_async();
-  }
-  if (warp == 8) tmem_alloc(&bar->tmem_base, 512);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = bar->tmem_base;
-  constexpr uint32_t cdQ = 256;
-
-  if (!has_work) {
-  } else if (warp == 9) {
-    // producer warp: K/V block and gathered Q / dO rows by TMA; lane qi fetches and issues query qi of the chunk
-    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-    const int oob_row = p.B * p.H * p.Tq;
-    const int oct0 = (b * p.H + g * p.hpg) >> 3;  // first head of the group, in units of 8 heads (rank-5 loads)
-    bool ok = true;
-    int c = 0, kvidx = -1, last_blk = -1;
-    for (; !w.done(); w.next(), ++c) {
-      const int s = c & 1;
-      const int cnt = w.count();
-      int tok = p.Tq, row = oob_row;  // beyond the tensor: the tile is filled with zeros
-      if (lane < cnt) {
-        tok = ent[w.e + lane] & 0xFFFFFF;
-        row = (int)(((int64_t)bg * p.Tq + tok) * p.hpg);
-      }
-      if (w.blk != last_blk) {
-        last_blk = w.blk;
-        ++kvidx;
-        ok = mbar_wait_warp(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
-        if (!ok) break;
-        if (lane == 0) {
-          mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
-          tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
-          for (int cc = 0; cc < DV / 64; ++cc)
-            tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
-        }
-      }
-      ok = mbar_wait_warp(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
-      if (!ok) break;
-      if (lane == 0) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
-      __syncwarp();
-      for (int qi = lane; qi < qpc; qi += 32) {
-        const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
-        uint8_t* stg = sSt + s * SM::kStage;
-        if (p.g5) {
-          tma_load_5d_outer(&tmQt, &bar->q_full[s], stg + qi * p.hpg * (DK * 2), oct0, tok);
-          tma_load_5d_outer(&tmdOt, &bar->q_full[s], stg + SM::kQ + qi * p.hpg * (DV * 2), oct0, tok);
-        } else {
-          uint8_t* dst = stg + qi * p.hpg * 128;
-#pragma unroll
-          for (int cc = 0; cc < DK / 64; ++cc) tma_load_2d(&tmQt, &bar->q_full[s], dst + cc * 16384, cc * 64, r2);
-#pragma unroll
-          for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
-        }
-      }
-    }
-    if (!ok && lane == 0) {
-      if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
-      for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
-    }
-  } else if (warp == 8) {
-    // UMMA issuer: warp-uniform loop, one elected lane issues
-    const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;  // Q tile: row-group / column-block strides
-    const uint32_t sboO = p.g5 ? (DV / 64) * 1024 : 1024, cbO = p.g5 ? 1024 : 16384;  // dO tile
-    constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);    // Q rows x K block (keys contiguous)
-    constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);   // dO rows x V block read K-major (dv contiguous)
-    constexpr uint32_t iddQh = idesc_bf16(128, DK / 2, 0, 0);   // dS (TMEM) x half of the K block's dk rows, read K-major
-    const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024), dKk = dKmn;
-    const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
-    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-    bool ok = true;
-    int c = 0, kvidx = 0, last_blk = w.blk;
-    auto issue_sdp = [&](int cc) -> bool {
-      const int s = cc & 1;
-      if (!mbar_wait_warp(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
-      tc_fence_after();
-      const uint64_t dQ = smem_desc_sw128(smem_u32(sSt + s * SM::kStage), 16, sboQ);
-      const uint64_t ddO = smem_desc_sw128(smem_u32(sSt + s * SM::kStage + SM::kQ), 16, sboO);
-      if (elect_one()) {
-#pragma unroll
-        for (int kk = 0; kk < DK / 16; ++kk)
-          umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < DV / 16; ++kk)
-          umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * cbO + (kk & 3) * 32),
-                  desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP, kk > 0);
-        umma_commit(&bar->sdp_full[s]);
-        umma_commit(&bar->q_empty[s]);
-      }
-      __syncwarp();
-      return true;
-    };
-    ok = mbar_wait_warp(&bar->kv_full, 0, abort) && issue_sdp(0);
-    while (ok && !w.done()) {
-      const int cur = c;
-      w.next();
-      const bool more = !w.done();
-      const bool same_blk = more && w.blk == last_blk;
-      if (same_blk) ok = issue_sdp(cur + 1);  // look ahead while this chunk's dS is being computed
-      if (!ok) break;
-      ok = mbar_wait_warp(&bar->ds_full[cur & 1], (cur >> 1) & 1, abort);
-      // the single dQ accumulator is drained by the epilogue of the previous chunk (other group) one column half at
-      // a time; each half is refilled as soon as it has been read
-      if (ok && cur > 0) ok = mbar_wait_warp(&bar->dq_read_lo[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
-      if (!ok) break;
-      tc_fence_after();
-      if (elect_one()) {
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem + cdQ, tmem + (cur & 1) * 128 + kk * 8, desc_advance(dKk, kk * 32), iddQh, kk > 0);
-      }
-      __syncwarp();
-      if (cur > 0) ok = mbar_wait_warp(&bar->dq_read_hi[(cur - 1) & 1], ((cur - 1) >> 1) & 1, abort);
-      if (!ok) break;
-      tc_fence_after();
-      if (elect_one()) {
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem + cdQ + DK / 2, tmem + (cur & 1) * 128 + kk * 8, desc_advance(dKk, (DK / 2) * 128 + kk * 32), iddQh, kk > 0);
-        umma_commit(&bar->dq_full[cur & 1]);
-        // when the single K/V slot is reloaded, everything issued so far must have finished with it
-        if (more && !same_blk) umma_commit(&bar->kv_empty);
-      }
-      __syncwarp();
-      if (more && !same_blk) {
-        last_blk = w.blk;
-        ++kvidx;
-        ok = mbar_wait_warp(&bar->kv_full, kvidx & 1, abort) && issue_sdp(cur + 1);
-      }
-      ++c;
-    }
-  } else {
-    const int grp = warp >> 2;
-    const int r = (warp & 3) * 32 + lane;
-    const int qi = r / p.hpg, hh = r % p.hpg;
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    // dQ partials go through a per-warp staging area (32 rows x 64 bytes, 16-byte pieces rotated by the row) so that
-    // a store instruction writes whole 64-byte runs of 8 rows instead of one 16-byte piece of 32 rows
-    uint8_t* stage = smem + SM::oOut + warp * 2048;
-    const int srow_l = lane >> 2, spiece = lane & 3;  // read-back role: row within a group of 8, 16-byte piece
-    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-    bool ok = true;
-    if (grp == 1 && !w.done()) w.next();
-    // this group's next chunk: entry and backward statistics are fetched one chunk ahead
-    int entry_next = 0;
-    float lse_next = CUDART_INF_F, D_next = 0.f;
-    auto fetch = [&]() {
-      entry_next = 0; lse_next = CUDART_INF_F; D_next = 0.f;
-      if (!w.done() && qi < w.count()) {
-        entry_next = ent[w.e + qi];
-        const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + (entry_next & 0xFFFFFF);
-        lse_next = p.lse2[srow];
-        D_next = p.D[srow];
-      }
-    };
-    fetch();
-    for (int c = grp; !w.done() && ok; c += 2) {
-      const int buf = grp, it = c >> 1;
-      const bool valid = qi < w.count();
-      const int entry = entry_next;
-      const float lse2 = lse_next, Dr = D_next;
-      const int t = entry & 0xFFFFFF, slot = entry >> 24;
-      const int chi = t - w.blk * 64;
-      w.next();
-      if (!w.done()) w.next();
-      fetch();
-      ok = mbar_wait(&bar->sdp_full[buf], it & 1, abort);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t pk[32];
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t sv[32], dp[32];
-        tmem_ld32(tmem + lane_base + buf * 128 + cc * 32, sv);
-        tmem_ld32(tmem + lane_base + buf * 128 + 64 + cc * 32, dp);
-        tc_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int c0 = cc * 32 + 2 * e;
-          const float p0 = c0 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse2)) : 0.f;
-          const float p1 = c0 + 1 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse2)) : 0.f;
-          __nv_bfloat162 x = __floats2bfloat162_rn(p0 * (__uint_as_float(dp[2 * e]) - Dr), p1 * (__uint_as_float(dp[2 * e + 1]) - Dr));
-          pk[cc * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
-        }
-      }
-      tmem_st32(tmem + lane_base + buf * 128, pk);
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(&bar->ds_full[buf]);
-      const int prow = valid ? (int)((((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh) : -1;
-      ok = mbar_wait(&bar->dq_full[buf], it & 1, abort);
-      if (!ok) break;
-      tc_fence_after();
-#pragma unroll
-      for (int cc = 0; cc < DK / 32; ++cc) {
-        uint32_t ov[32];
-        tmem_ld32(tmem + lane_base + cdQ + cc * 32, ov);
-        tc_wait_ld();
-        if (cc == DK / 64 - 1) {
-          tc_fence_before();
-          mbar_arrive(&bar->dq_read_lo[buf]);
-        }
-        if (cc == DK / 32 - 1) {
-          tc_fence_before();
-          mbar_arrive(&bar->dq_read_hi[buf]);
-        }
-        __syncwarp();  // the previous 32 columns have been read back
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 wv;
-          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[8 * j]), __uint_as_float(ov[8 * j + 1]));
-          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[8 * j + 2]), __uint_as_float(ov[8 * j + 3]));
-          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[8 * j + 4]), __uint_as_float(ov[8 * j + 5]));
-          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[8 * j + 6]), __uint_as_float(ov[8 * j + 7]));
-          wv.x = *reinterpret_cast<uint32_t*>(&a0); wv.y = *reinterpret_cast<uint32_t*>(&a1);
-          wv.z = *reinterpret_cast<uint32_t*>(&a2); wv.w = *reinterpret_cast<uint32_t*>(&a3);
-          *reinterpret_cast<uint4*>(stage + lane * 64 + (((j + (lane >> 1)) & 3) << 4)) = wv;
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int rr = i * 8 + srow_l;  // row of this warp whose piece this lane forwards
-          const int grow = __shfl_sync(0xffffffffu, prow, rr);
-          const uint4 wv = *reinterpret_cast<const uint4*>(stage + rr * 64 + (((spiece + (rr >> 1)) & 3) << 4));
-          if (grow >= 0) *reinterpret_cast<uint4*>(p.dq_part + (int64_t)grow * DK + cc * 32 + spiece * 8) = wv;
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
-  if (warp == 8) {
-    tc_fence_after();
-    tmem_dealloc(tmem, 512);
-  }
-}
-
 // dQ[b,h,t,:] = scale * sum of the contributing slots' partials, slot order: one warp per row; the loads of 8 slots
 // are in flight together and do not wait for the index row
 template <int DK>
@@ -935,31 +649,6 @@ __global__ void slc_combine_dq_bulk_kernel(const __nv_bfloat16* __restrict__ dq_
   if (threadIdx.x == 0 && abort_flag && timeouts) atomicAdd(timeouts, 1);
 }
 
-// ------------------------------------------------------------------------------------------------
-// backward, part 2: dK/dV of each block.  Per chunk (128 gathered rows): S = Q K^T and dP = dO V^T with the
-// rows on the M axis (one row per compute thread, statistics in registers), P and dS (bf16) are handed to
-// the tensor core through shared memory, 64 rows at a time, and the accumulators are kept transposed:
-//   dV^T [dv x 64 keys] += dO^T P,   dK^T [dk x 64 keys] += Q^T dS     (dk = 192 as an M = 128 and an M = 64 part).
-// They live in TMEM for as long as the CTA stays on a block and are then written as one fp32 partial
-// ([64 keys][dk|dv], coalesced: a warp's lanes are consecutive dk / dv indices); slc_reduce_dkv adds the
-// partials of a block in a fixed order.
-// ------------------------------------------------------------------------------------------------
-template <int DK, int DV>
-struct SlcDkvSmem {
-  static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2, kdO = 128 * DV * 2;
-  static constexpr int kStage = kQ + kdO;
-  static constexpr int kHalf = 64 * 128;          // 64 rows x 64 keys of bf16 P (or dS), 128-byte swizzle
-  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, oP = oSt + 2 * kStage, odS = oP + kHalf, oBar = odS + kHalf;
-  static constexpr int kDynamic = oBar + 256 + 1024;
-};
-struct SlcDkvBarriers {
-  // p_free / ds_free are rings of four: a writer may arrive several hand-overs early, and a parity wait tells apart only
-  // the last two completions of one barrier
-  uint64_t kv_full, kv_empty, q_full[2], q_empty[2], sdp_full[2], sdp_free[2], p_full, p_free[4], ds_full, ds_free[4], acc_full, acc_read;
-  uint32_t tmem_base;
-  int abort;
-};
-
 // accumulator rows [M x 64 keys] in TMEM -> part[(key_base + key) * W + off + row]; M = 128: row = TMEM lane,
 // M = 64: 16 rows per warp in its first 16 lanes
 template <int M>
@@ -978,381 +667,6 @@ __device__ __forceinline__ void slc_flush_rows(uint32_t taddr, float* __restrict
 #pragma unroll
       for (int e = 0; e < 32; ++e) dst[(int64_t)e * W] = __uint_as_float(ov[e]);
     }
-  }
-}
-
-template <int DK, int DV>
-__global__ void __launch_bounds__(384, 1)
-slc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                   const __grid_constant__ CUtensorMap tmQt, const __grid_constant__ CUtensorMap tmdOt, const SlcParams p) {
-  using SM = SlcDkvSmem<DK, DV>;
-  constexpr int MK1 = DK >= 128 ? 128 : 64, MK2 = DK - MK1;  // dK^T as one or two accumulators
-  static_assert(MK2 == 0 || MK2 == 64, "dk is 64, 128 or 192");
-  static_assert(DV == 64 || DV == 128, "dv is 64 or 128");
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t *sK = smem + SM::oK, *sV = smem + SM::oV, *sSt = smem + SM::oSt, *sP = smem + SM::oP, *sdS = smem + SM::odS;
-  SlcDkvBarriers* bar = reinterpret_cast<SlcDkvBarriers*>(smem + SM::oBar);
-  volatile int* abort = &bar->abort;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bg = blockIdx.y, b = bg / p.G, g = bg % p.G;
-  const int* off = p.csr_off + (int64_t)bg * (p.nblk + 1);
-  const int* ent = p.csr_t + (int64_t)bg * p.Tq * p.nslots;
-  const int e0 = blockIdx.x * kEntriesPerCta;
-  const int qpc = 128 / p.hpg;
-  // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
-  const bool has_work = e0 < off[p.nblk] && !(p.timeouts && *(volatile const int*)p.timeouts != 0);
-  const int nseg = gridDim.x + p.nblk;
-
-  if (threadIdx.x == 0) {
-    mbar_init(&bar->kv_full, 1);
-    mbar_init(&bar->kv_empty, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar->q_full[i], 1);
-      mbar_init(&bar->q_empty[i], 1);
-      mbar_init(&bar->sdp_full[i], 1);
-      mbar_init(&bar->sdp_free[i], 128);
-    }
-    mbar_init(&bar->p_full, 64);
-    mbar_init(&bar->ds_full, 64);
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(&bar->p_free[i], 1);
-      mbar_init(&bar->ds_free[i], 1);
-    }
-    mbar_init(&bar->acc_full, 1);
-    mbar_init(&bar->acc_read, 256);
-    bar->abort = 0;
-    fence_barrier_init();
-    fence_proxy_async();
-  }
-  if (warp == 8) tmem_alloc(&bar->tmem_base, 512);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = bar->tmem_base;
-  // S / dP of chunk c in columns (c & 1) * 128 + {0, 64}; then the transposed accumulators
-  constexpr uint32_t cdV = 256, cdK1 = 320, cdK2 = 384;
-  // 12 warps: 8 compute, UMMA issuer, producer, 2 idle ones completing the third warpgroup, whose registers go to the
-  // compute warpgroups
-  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
-
-  if (warp >= 10) {
-  } else if (!has_work) {
-  } else if (warp == 9) {
-    // producer warp: K/V block and gathered Q / dO rows by TMA (lane qi issues query qi)
-    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-    const int oob_row = p.B * p.H * p.Tq;
-    const int oct0 = (b * p.H + g * p.hpg) >> 3;  // first head of the group, in units of 8 heads (rank-5 loads)
-    bool ok = true;
-    int c = 0, kvidx = -1, last_blk = -1;
-    for (; !w.done(); w.next(), ++c) {
-      const int cnt = w.count();
-      // this chunk's entries are fetched while the stage is still busy
-      int tok = p.Tq, row = oob_row;  // beyond the tensor: the tile is filled with zeros
-      if (lane < cnt) {
-        tok = ent[w.e + lane] & 0xFFFFFF;
-        row = (int)(((int64_t)bg * p.Tq + tok) * p.hpg);
-      }
-      if (w.blk != last_blk) {
-        last_blk = w.blk;
-        ++kvidx;
-        ok = mbar_wait_warp(&bar->kv_empty, (kvidx & 1) ^ 1, abort);
-        if (!ok) break;
-        if (lane == 0) {
-          mbar_arrive_expect_tx(&bar->kv_full, SM::kK + SM::kV);
-          tma_load_2d(&tmK, &bar->kv_full, sK, w.blk * 64, (b * p.G + g) * DK);
-          for (int cc = 0; cc < DV / 64; ++cc)
-            tma_load_2d(&tmV, &bar->kv_full, sV + cc * 8192, cc * 64, (b * p.G + g) * p.Tk + w.blk * 64);
-        }
-      }
-      const int s = c & 1;
-      // the stage is usually still busy: start the rows on their way to L2 so that the tile loads find them there
-      if (lane < cnt && lane < qpc) {
-        if (p.g5) {
-          tma_prefetch_5d_outer(&tmQt, oct0, tok);
-          tma_prefetch_5d_outer(&tmdOt, oct0, tok);
-        } else {
-#pragma unroll
-          for (int cc = 0; cc < DK / 64; ++cc) tma_prefetch_2d(&tmQt, cc * 64, row);
-#pragma unroll
-          for (int cc = 0; cc < DV / 64; ++cc) tma_prefetch_2d(&tmdOt, cc * 64, row);
-        }
-      }
-      if (lane == 0) NSA_TR(0, c, 0);
-      ok = mbar_wait_warp(&bar->q_empty[s], ((c >> 1) & 1) ^ 1, abort);
-      if (!ok) break;
-      if (lane == 0) NSA_TR(0, c, 1);
-      uint8_t* st = sSt + s * SM::kStage;
-      if (lane == 0) mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ + SM::kdO);
-      __syncwarp();
-      for (int qi = lane; qi < qpc; qi += 32) {
-        const int r2 = qi < 32 ? row : (qi < cnt ? (int)(((int64_t)bg * p.Tq + (ent[w.e + qi] & 0xFFFFFF)) * p.hpg) : oob_row);
-        if (p.g5) {
-          tma_load_5d_outer(&tmQt, &bar->q_full[s], st + qi * p.hpg * (DK * 2), oct0, tok);
-          tma_load_5d_outer(&tmdOt, &bar->q_full[s], st + SM::kQ + qi * p.hpg * (DV * 2), oct0, tok);
-        } else {
-          uint8_t* dst = st + qi * p.hpg * 128;
-#pragma unroll
-          for (int cc = 0; cc < DK / 64; ++cc) tma_load_2d(&tmQt, &bar->q_full[s], dst + cc * 16384, cc * 64, r2);
-#pragma unroll
-          for (int cc = 0; cc < DV / 64; ++cc) tma_load_2d(&tmdOt, &bar->q_full[s], dst + SM::kQ + cc * 16384, cc * 64, r2);
-        }
-      }
-      if (lane == 0) NSA_TR(0, c, 2);
-    }
-    if (!ok && lane == 0) {
-      if (kvidx >= 0) mbar_wait(&bar->kv_full, kvidx & 1, abort);
-      for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
-    }
-  } else if (warp == 8) {
-    // UMMA issuer: warp-uniform loop, one elected lane issues
-    constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);     // Q rows (K-major) x K block (keys contiguous)
-    constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);    // dO rows (K-major) x V block read K-major (dv contiguous)
-    constexpr uint32_t iddV = idesc_bf16(DV, 64, 1, 1);     // dO^T (dv contiguous) x P (keys contiguous), K = gathered rows
-    constexpr uint32_t iddK1 = idesc_bf16(MK1, 64, 1, 1);   // Q^T (dk contiguous) x dS (keys contiguous)
-    constexpr uint32_t iddK2 = idesc_bf16(64, 64, 1, 1);
-    const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024);
-    const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
-    const uint64_t dPb = smem_desc_sw128(smem_u32(sP), 16, 1024);    // one 64-key MN block: LBO unused
-    const uint64_t dSb = smem_desc_sw128(smem_u32(sdS), 16, 1024);
-    const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;  // Q tile: row-group / column-block strides
-    const uint32_t sboO = p.g5 ? (DV / 64) * 1024 : 1024, cbO = p.g5 ? 1024 : 16384;  // dO tile
-    // Two streams of work share the tensor pipe: "produce" issues S / dP of the next chunk as soon as its rows have
-    // landed and its TMEM buffer is free, "consume" issues the accumulation MMAs of the oldest chunk as soon as the
-    // compute warps have handed over P or dS.  The warp polls both (non-blocking tests), so a load in flight never
-    // holds back accumulation work that is ready, and the other way round.
-    ChunkWalker wA(off, p.nblk, e0, e0 + kEntriesPerCta, qpc), wH = wA;
-    bool ok = true, fresh = true;  // fresh: the next accumulation starts a new segment
-    int ca = 0, ch = 0, hstep = 0;  // chunk to produce, chunk to consume and its step: P(h0), dS(h0), P(h1), dS(h1)
-    int kvidx = 0, blkA = wA.blk, seg = 0, u = 0;
-    bool kv_wait = true;           // the K/V tile of the block of chunk `ca` has not been seen to land yet
-    long long idle_since = 0;
-    while (ok && !wH.done()) {
-      bool did = false;
-      // ---- consume
-      if (ch < ca) {
-        bool ready = mbar_test((hstep & 1) ? &bar->ds_full : &bar->p_full, u & 1);
-        // a new segment overwrites the accumulators: the previous segment's sums must have been read out
-        if (ready && fresh && hstep == 0 && seg > 0) ready = mbar_test(&bar->acc_read, (seg - 1) & 1);
-        if (__all_sync(0xffffffffu, ready)) {
-          tc_fence_after();
-          const int h = hstep >> 1;
-          const uint32_t st = smem_u32(sSt + (ch & 1) * SM::kStage);
-          // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart inside an 8-row group
-          const uint64_t dQt = smem_desc_sw128(st, cbQ, sboQ), dOt = smem_desc_sw128(st + SM::kQ, cbO, sboO);
-          if ((hstep & 1) == 0) {
-            if (lane == 0) NSA_TR(1, ch, 2 + 4 * h);
-            if (elect_one()) {
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk)
-                umma_ss(tmem + cdV, desc_advance(dOt, (h * 8 + kk * 2) * sboO), desc_advance(dPb, kk * 2048), iddV,
-                        !(fresh && h == 0 && kk == 0));
-              umma_commit(&bar->p_free[u & 3]);
-            }
-          } else {
-            if (lane == 0) NSA_TR(1, ch, 4 + 4 * h);
-            if (elect_one()) {
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {
-                umma_ss(tmem + cdK1, desc_advance(dQt, (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK1,
-                        !(fresh && h == 0 && kk == 0));
-                if (MK2)
-                  umma_ss(tmem + cdK2, desc_advance(dQt, 2 * cbQ + (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK2,
-                          !(fresh && h == 0 && kk == 0));
-              }
-              umma_commit(&bar->ds_free[u & 3]);
-              if (hstep == 3) umma_commit(&bar->q_empty[ch & 1]);  // the chunk's Q / dO stage is free again
-            }
-          }
-          __syncwarp();
-          if (hstep == 1) fresh = false;
-          if (hstep & 1) ++u;
-          if (++hstep == 4) {
-            hstep = 0;
-            const int blk_done = wH.blk;
-            wH.next();
-            if (wH.done() || wH.blk != blk_done) {
-              // last chunk of the block (or of the CTA): hand the accumulators over
-              if (elect_one()) umma_commit(&bar->acc_full);
-              __syncwarp();
-              ++seg;
-              fresh = true;
-            }
-            ++ch;
-          }
-          did = true;
-        }
-      }
-      // ---- produce
-      if (!wA.done()) {
-        if (wA.blk != blkA) {
-          // first chunk of another block: the single K/V slot is refilled once everything issued so far has finished with it
-          if (elect_one()) umma_commit(&bar->kv_empty);
-          __syncwarp();
-          ++kvidx;
-          kv_wait = true;
-          blkA = wA.blk;
-        }
-        const int s = ca & 1;
-        bool ready = mbar_test(&bar->q_full[s], (ca >> 1) & 1) && mbar_test(&bar->sdp_free[s], ((ca >> 1) & 1) ^ 1);
-        if (ready && kv_wait) ready = mbar_test(&bar->kv_full, kvidx & 1);
-        if (__all_sync(0xffffffffu, ready)) {
-          kv_wait = false;
-          if (lane == 0) NSA_TR(1, ca, 12);
-          tc_fence_after();
-          const uint32_t st = smem_u32(sSt + s * SM::kStage);
-          const uint64_t dQ = smem_desc_sw128(st, 16, sboQ), ddO = smem_desc_sw128(st + SM::kQ, 16, sboO);
-          if (elect_one()) {
-#pragma unroll
-            for (int kk = 0; kk < DK / 16; ++kk)
-              umma_ss(tmem + s * 128, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
-#pragma unroll
-            for (int kk = 0; kk < DV / 16; ++kk)
-              umma_ss(tmem + s * 128 + 64, desc_advance(ddO, (kk >> 2) * cbO + (kk & 3) * 32),
-                      desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP, kk > 0);
-            umma_commit(&bar->sdp_full[s]);
-          }
-          __syncwarp();
-          if (lane == 0) NSA_TR(1, ca, 13);
-          wA.next();
-          ++ca;
-          did = true;
-        }
-      }
-      // ---- nothing ready: bounded idling
-      if (did) {
-        idle_since = 0;
-      } else {
-        const long long now = clock64();
-        if (idle_since == 0) idle_since = now;
-        if (*abort || now - idle_since > (1ll << 28)) {
-          *abort = 1;
-          ok = false;
-        }
-        __nanosleep(32);
-      }
-    }
-  } else {
-    // compute: one gathered row per thread; groups alternate chunks; both groups take part in every flush
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
-    const int grp = warp >> 2, warp4 = warp & 3;
-    const int r = warp4 * 32 + lane;
-    const int half = warp4 >> 1, rr = r & 63;  // which 64-row half of the chunk this row is handed over in
-    const uint32_t lane_base = (uint32_t)(warp4 * 32) << 16;
-    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
-    bool ok = true;
-    int c = 0, last_blk = -1, seg = 0;
-    auto flush = [&](int blk) -> bool {
-      if (!mbar_wait(&bar->acc_full, seg & 1, abort)) return false;
-      tc_fence_after();
-      const int64_t key_base = ((int64_t)bg * nseg + blockIdx.x + blk) * 64;
-      if (grp == 0) {
-        slc_flush_rows<MK1>(tmem + cdK1, p.dk_part, key_base, DK, 0, warp4, lane);
-        if (MK2) slc_flush_rows<64>(tmem + cdK2, p.dk_part, key_base, DK, MK1, warp4, lane);
-      } else {
-        slc_flush_rows<DV>(tmem + cdV, p.dv_part, key_base, DV, 0, warp4, lane);
-      }
-      tc_fence_before();
-      mbar_arrive(&bar->acc_read);
-      ++seg;
-      return true;
-    };
-    // statistics of this thread's row in a given chunk: t (-1: row not in use), lse2 (+inf then, so P = 0), D
-    const int qi = r / p.hpg, hh = r % p.hpg;
-    int t_next = -1;
-    float lse_next = CUDART_INF_F, D_next = 0.f;
-    auto fetch = [&](const ChunkWalker& wk) {
-      t_next = -1; lse_next = CUDART_INF_F; D_next = 0.f;
-      if (!wk.done() && qi < wk.count()) {
-        t_next = ent[wk.e + qi] & 0xFFFFFF;
-        const int64_t srow = ((int64_t)b * p.H + g * p.hpg + hh) * p.Tq + t_next;
-        lse_next = p.lse2[srow];
-        D_next = p.D[srow];
-      }
-    };
-    {
-      ChunkWalker w0 = w;
-      if (grp == 1 && !w0.done()) w0.next();
-      fetch(w0);
-    }
-    for (; !w.done() && ok; w.next(), ++c) {
-      if (w.blk != last_blk) {
-        if (last_blk >= 0) ok = flush(last_blk);
-        if (!ok) break;
-        last_blk = w.blk;
-      }
-      if ((c & 1) != grp) continue;
-      const int buf = grp, it = c >> 1;
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 0);
-      const int t = t_next;
-      const float lse2 = lse_next, Dr = D_next;
-      const int chi = t - w.blk * 64;
-      {  // this group's next chunk: fetch its statistics one chunk ahead
-        ChunkWalker w2 = w;
-        w2.next();
-        if (!w2.done()) w2.next();
-        fetch(w2);
-      }
-      ok = mbar_wait(&bar->sdp_full[buf], it & 1, abort);
-      if (!ok) break;
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 1);
-      tc_fence_after();
-      uint32_t pP[32], pS[32];
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t sv[32], dp[32];
-        tmem_ld32(tmem + lane_base + buf * 128 + cc * 32, sv);
-        tmem_ld32(tmem + lane_base + buf * 128 + 64 + cc * 32, dp);
-        tc_wait_ld();
-        if (cc == 1) {  // both tiles are in registers: the tensor core may overwrite them
-          tc_fence_before();
-          mbar_arrive(&bar->sdp_free[buf]);
-        }
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int c0 = cc * 32 + 2 * e;
-          const float p0 = c0 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse2)) : 0.f;
-          const float p1 = c0 + 1 <= chi ? ex2(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse2)) : 0.f;
-          __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1);
-          __nv_bfloat162 y = __floats2bfloat162_rn(p0 * (__uint_as_float(dp[2 * e]) - Dr), p1 * (__uint_as_float(dp[2 * e + 1]) - Dr));
-          pP[cc * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
-          pS[cc * 16 + e] = *reinterpret_cast<uint32_t*>(&y);
-        }
-      }
-      // hand-over: the staging tiles are used by (chunk, half) in order; use u waits for the MMAs of use u - 1
-      const int u = 2 * c + half;
-      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 2 + 6 * half);
-      if (u > 0) {
-        ok = mbar_wait(&bar->p_free[(u - 1) & 3], ((u - 1) >> 2) & 1, abort);
-        if (!ok) break;
-      }
-      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 3 + 6 * half);
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(sP + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pP[4 * j], pP[4 * j + 1], pP[4 * j + 2], pP[4 * j + 3]);
-      fence_proxy_async();
-      mbar_arrive(&bar->p_full);
-      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 4 + 6 * half);
-      if (u > 0) {
-        ok = mbar_wait(&bar->ds_free[(u - 1) & 3], ((u - 1) >> 2) & 1, abort);
-        if (!ok) break;
-      }
-      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 5 + 6 * half);
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(sdS + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pS[4 * j], pS[4 * j + 1], pS[4 * j + 2], pS[4 * j + 3]);
-      fence_proxy_async();
-      mbar_arrive(&bar->ds_full);
-      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 6 + 6 * half);
-    }
-    if (ok && last_blk >= 0) flush(last_blk);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
-  if (warp == 8) {
-    tc_fence_after();
-    tmem_dealloc(tmem, 512);
   }
 }
 
@@ -1537,6 +851,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (ready && fresh && hstep == 0 && seg > 0) ready = mbar_test(&bar->acc_read, (seg - 1) & 1);
         if (__all_sync(0xffffffffu, ready)) {
           tc_fence_after();
+          if (lane == 0) NSA_TR(1, ch, 4 + hstep);
           const int h = hstep >> 1;
           const uint32_t st = smem_u32(sSt + (ch & 1) * SM::kStage);
           // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart inside an 8-row group
@@ -1588,6 +903,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (ready && cq > 0) ready = mbar_test(&bar->dq_read, (cq - 1) & 1);
         if (__all_sync(0xffffffffu, ready)) {
           tc_fence_after();
+          if (lane == 0) NSA_TR(1, cq, 2);
           if (elect_one()) {
 #pragma unroll
             for (int hh2 = 0; hh2 < 2; ++hh2)
@@ -1605,6 +921,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       // ---- dP of chunk cp: after S of the same chunk, and in program order after dQ of the chunk before (same columns)
       if (cp < cs && cq == cp) {
         const int s = cp & 1;
+        if (lane == 0) NSA_TR(1, cp, 1);
         const uint32_t st = smem_u32(sSt + s * SM::kStage);
         const uint64_t ddO = smem_desc_sw128(st + SM::kQ, 16, sboO);
         if (elect_one()) {
@@ -1641,6 +958,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (__all_sync(0xffffffffu, ready)) {
           kv_wait = false;
           tc_fence_after();
+          if (lane == 0) NSA_TR(1, cs, 0);
           const uint32_t st = smem_u32(sSt + s * SM::kStage);
           const uint64_t dQ = smem_desc_sw128(st, 16, sboQ);
           if (elect_one()) {
@@ -1664,7 +982,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
           *abort = 1;
           ok = false;
         }
-        __nanosleep(32);
+
       }
     }
   } else {
@@ -1728,8 +1046,10 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (!w2.done()) w2.next();
         fetch(w2);
       }
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 0);
       ok = mbar_wait(&bar->sdp_full[grp], (c >> 1) & 1, abort);
       if (!ok) break;
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 1);
       tc_fence_after();
       uint32_t pP[32], pS[32];
 #pragma unroll
@@ -1758,6 +1078,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bar->dst_full);
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 2);
       // hand-over of P / dS for the transposed accumulations: the staging tiles are used by (chunk, half) in order
       const int u = 2 * c + half;
       if (u > 0) {
@@ -1778,11 +1099,13 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         *reinterpret_cast<uint4*>(sdS + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pS[4 * j], pS[4 * j + 1], pS[4 * j + 2], pS[4 * j + 3]);
       fence_proxy_async();
       mbar_arrive(&bar->ds_full);
+      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 3 + half);
       // dQ partial of this chunk: TMEM -> registers -> per-warp staging (32 rows x 32 bytes, pieces swapped for odd
       // groups of four rows) -> 32-byte runs of 16 rows per store instruction
       const int prow = entry >= 0 ? (int)((((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh) : -1;
       ok = mbar_wait(&bar->dq_full[grp], (c >> 1) & 1, abort);
       if (!ok) break;
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 5);
       tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < DK / 32; ++cc) {
@@ -1818,6 +1141,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
           }
         }
       }
+      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 6);
     }
     if (ok && last_blk >= 0) flush(last_blk);
   }
@@ -1985,24 +1309,15 @@ template <int DK, int DV>
 static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tqt, const CUtensorMap& tdot,
                             const SlcParams& p, const int* indices,
                             const int64_t* sidx, __nv_bfloat16* dq, cudaStream_t st) {
-  auto kq = slc_bwd_dq_kernel<DK, DV>;
-  auto kkv = slc_bwd_dkv_kernel<DK, DV>;
-  if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, SlcDqSmem<DK, DV>::kDynamic) != cudaSuccess ||
-      cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, SlcDkvSmem<DK, DV>::kDynamic) != cudaSuccess)
-    return fail(NSA_ERR_LAUNCH, "slc_bwd: cannot reserve shared memory");
   const int nparts = (int)(((int64_t)p.Tq * p.nslots + kEntriesPerCta - 1) / kEntriesPerCta);
-  static const bool split = getenv("NSA_SLC_BWD_SPLIT") != nullptr;
-  if (!split) {
+  {
     auto kf = slc_bwd_fused_kernel<DK, DV>;
     if (cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, SlcBwdSmem<DK, DV>::kDynamic) != cudaSuccess)
       return fail(NSA_ERR_LAUNCH, "slc_bwd: cannot reserve shared memory");
     KernelTimer kt("slc_bwd_fused", st);
     kf<<<dim3(nparts, p.B * p.G), 384, SlcBwdSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
-  } else {
-    KernelTimer kt("slc_bwd_dq", st);
-    kq<<<dim3(nparts, p.B * p.G), 320, SlcDqSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
   }
-  if (int rc = check_launch("slc_bwd_dq_sm100")) return rc;
+  if (int rc = check_launch("slc_bwd_fused_sm100")) return rc;
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
   {
     KernelTimer kt("slc_combine_dq", st);
@@ -2019,11 +1334,6 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
     }
   }
   if (int rc = check_launch("slc_combine_dq")) return rc;
-  if (split) {
-    KernelTimer kt("slc_bwd_dkv", st);
-    kkv<<<dim3(nparts, p.B * p.G), 384, SlcDkvSmem<DK, DV>::kDynamic, st>>>(tk, tv, tqt, tdot, p);
-  }
-  if (int rc = check_launch("slc_bwd_dkv_sm100")) return rc;
   KernelTimer kt("slc_reduce_dkv", st);
   slc_reduce_dkv_kernel<<<dim3(p.nblk, p.B * p.G), 256, 0, st>>>(p.dk_part, p.dv_part, p.csr_off, p.dk_out, p.dv_out, p.G, p.Tk,
                                                                  p.nblk, nparts, DK, DV, p.scale);
