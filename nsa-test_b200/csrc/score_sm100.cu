@@ -349,49 +349,82 @@ topn_rows_kernel(const float* __restrict__ sel, int32_t* __restrict__ out, int64
   const float* src = sel + row * n_sel;
   float* v = sm_rows + warp * n_sel;  // PER == 0 only
   float vr[PER > 0 ? PER : 1];        // PER > 0 only
-  float bv = -CUDART_INF_F;
-  int bi = 0x7fffffff;
+  const int k_actual = min(n, n_sel);
+  int mytop = -1;  // lane r keeps the r-th pick
   if (PER > 0) {
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
       const int j = lane + 32 * i;
       vr[i] = j < lim ? src[j] : (j < n_sel ? 0.f : -CUDART_INF_F);
     }
+    // Every lane keeps a sorted list of its next four candidates; the order is (score descending, id ascending).
+    // A list is refilled from the lane's registers with the candidates that come after the last one it gave away.
+    float b0, b1, b2, b3, last_v = CUDART_INF_F;
+    int i0, i1, i2, i3, last_i = -1, cnt = 0;
+    auto refill = [&]() {
+      b0 = b1 = b2 = b3 = -CUDART_INF_F;
+      i0 = i1 = i2 = i3 = 0x7fffffff;
+      cnt = 0;
 #pragma unroll
-    for (int i = 0; i < PER; ++i)
-      if (vr[i] > bv) { bv = vr[i]; bi = lane + 32 * i; }  // ascending id: an equal score never displaces an earlier id
+      for (int i = 0; i < PER; ++i) {
+        const float x = vr[i];
+        const int id = lane + 32 * i;
+        const bool after = x < last_v || (x == last_v && id > last_i);
+        if (after && x > -CUDART_INF_F && x > b3) {  // ascending id: an equal score never displaces an earlier id
+          ++cnt;
+          if (x > b2) {
+            b3 = b2; i3 = i2;
+            if (x > b1) {
+              b2 = b1; i2 = i1;
+              if (x > b0) { b1 = b0; i1 = i0; b0 = x; i0 = id; }
+              else { b1 = x; i1 = id; }
+            } else { b2 = x; i2 = id; }
+          } else { b3 = x; i3 = id; }
+        }
+      }
+      cnt = min(cnt, 4);
+    };
+    refill();
+    for (int r = 0; r < k_actual; ++r) {
+      float wv = b0;
+      int wi = i0;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+        if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
+      }
+      if (lane == r) mytop = wi;
+      const bool mine = (wi & 31) == lane && wi == i0;
+      if (mine) {
+        last_v = b0; last_i = i0;
+        b0 = b1; i0 = i1; b1 = b2; i1 = i2; b2 = b3; i2 = i3; b3 = -CUDART_INF_F; i3 = 0x7fffffff;
+        --cnt;
+      }
+      if (__any_sync(0xffffffffu, mine && cnt == 0)) {
+        if (mine && cnt == 0) refill();
+      }
+    }
   } else {
+    float bv = -CUDART_INF_F;
+    int bi = 0x7fffffff;
     for (int j = lane; j < n_sel; j += 32) {
       const float x = j < lim ? src[j] : 0.f;
       v[j] = x;
       if (x > bv) { bv = x; bi = j; }
     }
     __syncwarp();
-  }
-  const int k_actual = min(n, n_sel);
-  int mytop = -1;  // lane r keeps the r-th pick
-  for (int r = 0; r < k_actual; ++r) {
-    float wv = bv;
-    int wi = bi;
+    for (int r = 0; r < k_actual; ++r) {
+      float wv = bv;
+      int wi = bi;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
-      if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
-    }
-    if (lane == r) mytop = wi;
-    // the owner retires the pick and looks for its next best
-    if (PER > 0) {
-      const bool mine = (wi & 31) == lane;
-      const int slot = wi >> 5;
-      if (mine) { bv = -CUDART_INF_F; bi = 0x7fffffff; }
-#pragma unroll
-      for (int i = 0; i < PER; ++i) {
-        if (mine && i == slot) vr[i] = -CUDART_INF_F;
-        if (mine && vr[i] > bv) { bv = vr[i]; bi = lane + 32 * i; }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+        if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
       }
-    } else {
-      if ((wi & 31) == lane) {
+      if (lane == r) mytop = wi;
+      if ((wi & 31) == lane) {  // the owner retires the pick and looks for its next best
         v[wi] = -CUDART_INF_F;
         bv = -CUDART_INF_F;
         bi = 0x7fffffff;
