@@ -137,6 +137,24 @@ def layer_step(inp, params, cfg, world):
     return out[0, 0, -1, :8].float().sum() + grads[0][0, 0, -1, :8].float().sum()
 
 
+def layer_step_query_sharded(inp, params, cfg, world):
+    """Long-context mode: `inp` holds this rank's slice of the positions; K/V are all-gathered inside the layer and
+    their gradients come back reduce-scattered (nsa.sharding.query_sharded_layer)."""
+    from nsa.sharding import allreduce_grads, query_sharded_layer
+    lin = torch.nn.functional.linear
+    q = inp["q"].detach().requires_grad_(True)
+    k = inp["k"].detach().requires_grad_(True)
+    v = inp["v"].detach().requires_grad_(True)
+    logits = lin(torch.relu(lin(inp["x"], params["gw1"], params["gb1"])), params["gw2"], params["gb2"])
+    phi = (params["pos_embed"], params["w1"], params["b1"], params["w2"], params["b2"])
+    out = query_sharded_layer(q, k, v, logits, phi, cfg)
+    plist = list(params.values())
+    grads = torch.autograd.grad(out, [q, k, v] + plist, inp["do"])
+    if world > 1:
+        allreduce_grads(grads[3:])
+    return out[0, 0, -1, :8].float().sum() + grads[0][0, 0, -1, :8].float().sum()
+
+
 def attention_flops(T):
     """Algorithmic attention FLOPs per sequence (masked-out keys do not count): forward 2(dk+dv)N,
     backward 2(3dk+2dv)N per (head, query) with N valid keys; selection counted at n full blocks minus
@@ -224,6 +242,9 @@ def main():
     ap.add_argument("--T", type=int, default=65536)
     ap.add_argument("--cpu-sample", type=int, default=2048, help="sequence length of the CPU-oracle sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--shard", default="sequence", choices=["sequence", "query"],
+                    help="sequence: one T-token sequence per GPU (weak scaling, the default); query: ONE T-token sequence "
+                         "split by position over the GPUs, K/V all-gathered (long-context mode, strong scaling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -242,7 +263,18 @@ def main():
     c = CFG
     cfg = nsa.NSAConfig(d_model=c["d_model"], head_dim_qk=c["dk"], head_dim_v=c["dv"], l=c["l"], d=c["d"], l_prime=c["l_prime"],
                         n=c["n"], w=c["w"], n_heads=c["H"], n_kv_groups=c["G"])
-    inp, params = make_device_inputs(T, dev, seed=rank)
+    query_mode = args.shard == "query" and world > 1
+    if query_mode:
+        from nsa.sharding import query_shard
+        inp, params = make_device_inputs(T, dev, seed=0)        # the same sequence on every rank; each keeps its slice
+        t0, t1 = query_shard(T, world, rank)
+        inp = dict(q=inp["q"][:, :, t0:t1].contiguous(), k=inp["k"][..., t0:t1].contiguous(), v=inp["v"][:, :, t0:t1].contiguous(),
+                   do=inp["do"][:, :, t0:t1].contiguous(), x=inp["x"][:, t0:t1].contiguous())
+        torch.cuda.empty_cache()
+    else:
+        inp, params = make_device_inputs(T, dev, seed=rank)
+    step_fn = layer_step_query_sharded if query_mode else layer_step
+    seqs = 1 if query_mode else world                            # sequences processed per step by the whole job
 
     def barrier():
         if world > 1:
@@ -251,7 +283,7 @@ def main():
 
     # ---- device-resident throughput -------------------------------------------------------------
     for _ in range(max(args.warmup, 3)):
-        layer_step(inp, params, cfg, world)
+        step_fn(inp, params, cfg, world)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -259,7 +291,7 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        layer_step(inp, params, cfg, world)
+        step_fn(inp, params, cfg, world)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
@@ -268,7 +300,7 @@ def main():
     if world > 1:
         torch.distributed.all_reduce(t_ms, op=torch.distributed.ReduceOp.MAX)
     ms_per_step = t_ms.item() / args.steps
-    value = world * T / (ms_per_step * 1e-3)
+    value = seqs * T / (ms_per_step * 1e-3)
 
     # ---- end to end: inputs come from pinned host memory every step, result read back -----------
     host = {k_: torch.empty(v_.shape, dtype=v_.dtype, pin_memory=True).copy_(v_) for k_, v_ in inp.items()}
@@ -297,7 +329,7 @@ def main():
             if i + 1 < n:
                 upload(i + 1)
             cur.wait_event(copied[i % 2])
-            res = layer_step(slots[i % 2], params, cfg, world)
+            res = step_fn(slots[i % 2], params, cfg, world)
             res_host.copy_(res.reshape(1), non_blocking=True)
             consumed[i % 2].record(cur)
         cur.synchronize()
@@ -312,10 +344,10 @@ def main():
     t_e2e = torch.tensor([e0.elapsed_time(e1)], device=dev)
     if world > 1:
         torch.distributed.all_reduce(t_e2e, op=torch.distributed.ReduceOp.MAX)
-    e2e_value = world * T / (t_e2e.item() / e2e_steps * 1e-3)
+    e2e_value = seqs * T / (t_e2e.item() / e2e_steps * 1e-3)
 
     # ---- per-kernel times (CUDA events around every launch, outside the timed region) -----------
-    prof = _lib.profile_kernels(lambda: layer_step(inp, params, cfg, world))
+    prof = _lib.profile_kernels(lambda: step_fn(inp, params, cfg, world))
     launches = sum(n_ for n_, _ in prof.values())
     kflops = kernel_flops(T)
     peaks = measured_peaks()
@@ -324,7 +356,7 @@ def main():
         cand = {k_: v_ for k_, v_ in prof.items() if k_ in kflops}
         top = max(cand, key=lambda k_: cand[k_][1]) if cand else None
         roofline = None
-        if top:
+        if top and not query_mode:   # per-launch FLOP figures assume a whole sequence per launch
             n_l, tot = cand[top]
             achieved = kflops[top] / (tot / n_l * 1e-3) / 1e12
             roofline = dict(bound="tensor", kernel=top, achieved=round(achieved, 1), peak=peaks["tflops_sustained"], unit="TFLOP/s",
@@ -341,14 +373,17 @@ def main():
             cpu = dict(value=round(tps, 2), unit="tokens/s", cores=threads, kind="port",
                        sample=f"one full-layer fwd+bwd of the CPU oracle (fp32) at T={args.cpu_sample}, same heads/dims, {sec:.1f} s")
         line = dict(metric=METRIC, value=round(value, 1), unit="tokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
-                    ms_per_step=round(ms_per_step, 3), higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                    ms_per_step=round(ms_per_step, 3), higher_is_better=True, scaling="strong" if query_mode else "weak",
+                    vs_baseline=None, dtype="bf16",
                     data="synthetic", impl="ours",
-                    config=dict(workload=f"NSA layer fwd+bwd, one sequence per GPU, T={T}", l2="inputs (>= 1.6 GB per tensor) exceed the 126 MB L2",
-                                parallelism=f"dp{world}", **c),
+                    config=dict(workload=(f"NSA layer fwd+bwd, ONE sequence of T={T} split by position over the GPUs, K/V all-gathered"
+                                          if query_mode else f"NSA layer fwd+bwd, one sequence per GPU, T={T}"),
+                                l2="inputs (>= 1.6 GB per tensor) exceed the 126 MB L2",
+                                parallelism=f"sp{world}" if query_mode else f"dp{world}", **c),
                     e2e=dict(value=round(e2e_value, 1), unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=4),
                     gpu_launches=launches * args.steps, roofline=roofline, cpu_baseline=cpu, clocks=clocks,
                     attention_tflops_per_s=round(att_total / (ms_per_step * 1e-3) / 1e12, 1),
-                    attention_frac_of_peak=round(att_total / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"], 4),
+                    attention_frac_of_peak=round(att_total / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"] / (world if query_mode else 1), 4),
                     kernel_ms=breakdown, kernel_ms_total=round(kern_ms, 3), device_timeouts=timeouts)
         print(json.dumps(line))
     if world > 1:

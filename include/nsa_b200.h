@@ -49,6 +49,11 @@ enum {
  * qualifies (bf16, canonical contiguous layouts, supported head dims, T multiple of 128) and the
  * stride-generic kernels elsewhere; 1 forces the stride-generic kernels.  Process-wide. */
 NSA_API int nsa_set_kernel_family(int family);
+/* Query-sharded long-context runs (the reference has no counterpart; its wrappers assume query row t sits at
+ * position t): position of query row 0 in the sequence for the calls THIS HOST THREAD makes next.  The keys keep
+ * starting at position 0.  Honoured by the bf16 tensor-core paths of nsa_cmp_attn_fwd/bwd, nsa_score_topn and
+ * nsa_slc_fwd/bwd; any other path refuses a non-zero offset with NSA_ERR_ARG.  Set it back to 0 afterwards. */
+NSA_API int nsa_set_query_offset(int position);
 /* Number of thread blocks of the tensor-core kernels that ever gave up on a bounded barrier wait
  * (0 in a healthy run; their output is then invalid).  Synchronises the device.  reset != 0 clears
  * the counter.  Negative = error. */

@@ -79,6 +79,11 @@ static bool tensor_core_bwd_ok_slc(const int64_t* s, int dtype, int H, int G, in
                                    const void* dkey, const void* dval);
 static int g_kernel_family = 0;
 int kernel_family() { return g_kernel_family; }  // 0: tensor-core kernels where they apply, 1: stride-generic kernels only
+// Position of query row 0 in the sequence for the calls this host thread makes next (query-sharded long-context runs:
+// the queries are a slice of the positions, keys cover the sequence from position 0).  Honoured by the tensor-core paths
+// of the compressed attention, the scoring and the selected-block attention; every other path refuses a non-zero offset.
+static thread_local int g_query_pos0 = 0;
+int query_pos0() { return g_query_pos0; }
 
 // canonical contiguous layouts: q [B,H,T,dk], k [B,G,dk,Tk] (strides given as z,g,n,k), v [B,G,Tk,dv], o [B,H,T,dv]
 static bool canonical_fwd(const int64_t* s, int H, int G, int Tq, int Tk, int dk, int dv) {
@@ -164,6 +169,15 @@ extern "C" NSA_API int nsa_set_kernel_family(int family) {
   return NSA_OK;
 }
 
+extern "C" NSA_API int nsa_set_query_offset(int position) {
+  NSA_REQUIRE(position >= 0, "query offset must be >= 0");
+  g_query_pos0 = position;
+  return NSA_OK;
+}
+
+#define NSA_NO_QUERY_OFFSET(what) \
+  NSA_REQUIRE(g_query_pos0 == 0, what ": a query offset (nsa_set_query_offset) needs the bf16 tensor-core path of this call")
+
 extern "C" NSA_API size_t nsa_attn_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int is_compression) {
   if (B <= 0 || H <= 0 || G <= 0 || Tq <= 0 || Tk <= 0 || H % G != 0) return 256;
   return fa_bwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, is_compression ? kCmp : kWin);
@@ -223,8 +237,10 @@ extern "C" NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const 
   if (g_kernel_family == 0 && blocks_d > 0 && dtype == NSA_BF16 && L && M && fa_fwd_sm100_supported(H, G, T, NB, dk, dv) &&
       canonical_fwd(strides, H, G, T, NB, dk, dv) && aligned16(q) && aligned16(k_cmp) && aligned16(v_cmp) &&
       aligned16(out) && (int64_t)B * (H / 2) <= 65535)
-    return fa_fwd_sm100(q, k_cmp, v_cmp, out, L, M, B, H, G, T, NB, dk, dv, kCmp, 0, blocks_l, blocks_d, blocks_n, scale,
-                        (cudaStream_t)stream);
+    // block i is visible to the query at position q0 + t iff i*d + l - 1 <= q0 + t: the same rule with l - q0 for row t
+    return fa_fwd_sm100(q, k_cmp, v_cmp, out, L, M, B, H, G, T, NB, dk, dv, kCmp, 0, blocks_l - g_query_pos0, blocks_d, blocks_n,
+                        scale, (cudaStream_t)stream);
+  NSA_NO_QUERY_OFFSET("cmp_attn_fwd");
   AttnArgs a = {};
   a.q = q; a.k = k_cmp; a.v = v_cmp; a.o = out; a.L = L; a.M = M; a.block_ends = block_ends;
   fill_fwd_strides(a, strides);
@@ -243,8 +259,9 @@ extern "C" NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const 
   NSA_REQUIRE(blocks_d >= 0 && (blocks_d == 0 || (blocks_l > 0 && blocks_n >= 0 && blocks_n <= NB)),
               "cmp_attn_bwd: bad block layout hint (l=%d, d=%d, n=%d)", blocks_l, blocks_d, blocks_n);
   if (blocks_d > 0 && tensor_core_bwd_ok(strides, dtype, B, H, G, T, NB, dk, dv, q, k_cmp, v_cmp, out, dout, dq, dk_cmp, dv_cmp))
-    return fa_bwd_sm100(q, k_cmp, v_cmp, out, dout, L, M, dq, dk_cmp, dv_cmp, B, H, G, T, NB, dk, dv, kCmp, 0, blocks_l,
-                        blocks_d, blocks_n, scale, workspace, workspace_bytes, (cudaStream_t)stream);
+    return fa_bwd_sm100(q, k_cmp, v_cmp, out, dout, L, M, dq, dk_cmp, dv_cmp, B, H, G, T, NB, dk, dv, kCmp, 0,
+                        blocks_l - g_query_pos0, blocks_d, blocks_n, scale, workspace, workspace_bytes, (cudaStream_t)stream);
+  NSA_NO_QUERY_OFFSET("cmp_attn_bwd");
   AttnArgs a = {};
   a.q = q; a.k = k_cmp; a.v = v_cmp; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.block_ends = block_ends;
   a.dq = dq; a.dk_out = dk_cmp; a.dv_out = dv_cmp;
@@ -263,7 +280,8 @@ extern "C" NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, 
   if (g_kernel_family == 0 && dtype == NSA_BF16 && L && M && B > 0 && slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime) &&
       canonical_fwd(strides, H, G, Tq, Tkv, dk, dv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out))
     return slc_fwd_sm100(q, k, v, indices, strides + 22, out, L, M, B, H, G, Tq, Tkv, dk, dv, n_slots, l_prime, scale,
-                         workspace, workspace_bytes, (cudaStream_t)stream);
+                         g_query_pos0, workspace, workspace_bytes, (cudaStream_t)stream);
+  NSA_NO_QUERY_OFFSET("slc_fwd");
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o = out; a.L = L; a.M = M; a.indices = indices;
   fill_fwd_strides(a, strides);
@@ -299,7 +317,8 @@ extern "C" NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, 
   if (slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime) &&
       tensor_core_bwd_ok_slc(strides, dtype, H, G, Tq, Tkv, dk, dv, q, k, v, out, dout, dq, dkey, dval))
     return slc_bwd_sm100(q, k, v, indices, strides + 34, out, dout, L, M, dq, dkey, dval, B, H, G, Tq, Tkv, dk, dv, n_slots,
-                         l_prime, scale, workspace, workspace_bytes, (cudaStream_t)stream);
+                         l_prime, scale, g_query_pos0, workspace, workspace_bytes, (cudaStream_t)stream);
+  NSA_NO_QUERY_OFFSET("slc_bwd");
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.indices = indices;
   a.dq = dq; a.dk_out = dkey; a.dv_out = dval;
@@ -308,7 +327,7 @@ extern "C" NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, 
   a.B = B; a.H = H; a.G = G; a.Tq = Tq; a.Tk = Tkv; a.dk = dk; a.dv = dv; a.scale = scale; a.causal = 1;
   a.nslots = n_slots; a.lprime = l_prime; a.nblk = (Tkv + l_prime - 1) / l_prime;
   cudaStream_t st = (cudaStream_t)stream;
-  if (int rc = build_slc_csr(indices, a.sidx, B, G, Tq, Tkv, n_slots, l_prime, 1, workspace, workspace_bytes,
+  if (int rc = build_slc_csr(indices, a.sidx, B, G, Tq, Tkv, n_slots, l_prime, 1, 0, workspace, workspace_bytes,
                              &a.csr_off, &a.csr_t, st))
     return rc;
   return launch_attn_generic(a, kSlc, dtype, true, st);

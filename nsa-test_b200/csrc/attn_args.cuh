@@ -45,7 +45,7 @@ int launch_attn_generic(const AttnArgs& a, int mode, int dtype, bool backward, c
 // Inverse index "key block -> queries that selected it" for the selection backward.
 size_t slc_csr_workspace_bytes(int B, int G, int Tq, int Tkv, int nslots, int lprime);
 int build_slc_csr(const int* indices, const int64_t* sidx, int B, int G, int Tq, int Tkv, int nslots,
-                  int lprime, int causal, void* workspace, size_t workspace_bytes, const int** csr_off,
+                  int lprime, int causal, int q0, void* workspace, size_t workspace_bytes, const int** csr_off,
                   const int** csr_t, cudaStream_t st);
 
 }  // namespace nsa

@@ -359,7 +359,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     qs_hi = min(p.Tq - 1, n0 + 126 + p.window) / 64;
   } else {
     const int64_t tfirst = (int64_t)n0 * p.cmp_d + p.cmp_l - 1;
-    qs_lo = (n0 < p.cmp_nb && tfirst < p.Tq) ? (int)(tfirst / 64) : 1;
+    qs_lo = (n0 < p.cmp_nb && tfirst < p.Tq) ? (int)(max(tfirst, (int64_t)0) / 64) : 1;  // tfirst < 0: visible from the first row on
     qs_hi = (n0 < p.cmp_nb && tfirst < p.Tq) ? (p.Tq - 1) / 64 : 0;
   }
   const bool poisoned = p.timeouts && *(volatile const int*)p.timeouts != 0;  // a block gave up on a wait earlier: skip

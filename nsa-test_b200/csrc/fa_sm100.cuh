@@ -46,7 +46,7 @@ int make_tmap_head_rows(::CUtensorMap_st* map, const void* base, uint64_t heads_
 bool score_sm100_supported(int H, int G, int T, int dk, int nbp, int l, int d, int lprime, int n);
 size_t score_sm100_workspace_bytes(int B, int G, int T, int dk, int nbp, int d, int lprime);
 int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
-                     int lprime, int nb, int n, int n_fixed, float scale, void* workspace, size_t workspace_bytes,
+                     int lprime, int nb, int n, int n_fixed, float scale, int q0, void* workspace, size_t workspace_bytes,
                      cudaStream_t st);
 
 // Device address (on the current device) of the counter of CTAs that gave up on a barrier wait.

@@ -35,6 +35,7 @@ struct ScoreParams {
   float* sel;    // [B,G,T,n_sel] selection-block scores (blocks beyond a query tile's last key tile are not written)
   int B, H, G, T, nbp;
   int l, d, lprime, nb, n_sel;
+  int q0;        // position of query row 0 in the sequence (query-sharded runs; 0 otherwise)
   float scale_log2;
   int* timeouts;
 };
@@ -72,7 +73,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = (gridDim.x - 1 - blockIdx.x) * 128;
   const int bg = blockIdx.y, b = bg / p.G, g = bg % p.G;
-  const int tl = m0 + 127;
+  const int tl = p.q0 + m0 + 127;
   const int kmax = tl >= p.l - 1 ? min(p.nb - 1, (tl - p.l + 1) / p.d) : -1;
   const int ntiles = max(1, kmax / 128 + 1);
   const int steps_per_pass = ntiles * hpg;
@@ -190,7 +191,8 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane, t = m0 + r;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const int vis = t >= p.l - 1 ? min(p.nb - 1, (t - p.l + 1) / p.d) : -1;  // last visible compressed block
+    const int tp = p.q0 + t;  // position in the sequence
+    const int vis = tp >= p.l - 1 ? min(p.nb - 1, (tp - p.l + 1) / p.d) : -1;  // last visible compressed block
     const int s_ = p.lprime / p.d;   // keys per selection block (a power of two on this path); l / d == 2
     const int smask = s_ - 1, sshift = 31 - __clz(s_);
     const int per_tile = 128 >> sshift;
@@ -337,13 +339,13 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 template <int PER>
 __global__ void __launch_bounds__(128)
 topn_rows_kernel(const float* __restrict__ sel, int32_t* __restrict__ out, int64_t rows, int T, int n_sel, int per_tile, int l,
-                 int d, int nb, int lprime, int n, int n_fixed) {
+                 int d, int nb, int lprime, int n, int n_fixed, int q0) {
   extern __shared__ float sm_rows[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 4 + warp;
   if (row >= rows) return;  // warps are independent: no block-wide barrier below
-  const int t = (int)(row % T);
-  const int tl = (t / 128) * 128 + 127;
+  const int tloc = (int)(row % T), t = q0 + tloc;  // row of the launch, position in the sequence
+  const int tl = q0 + (tloc / 128) * 128 + 127;
   const int kmax = tl >= l - 1 ? min(nb - 1, (tl - l + 1) / d) : -1;
   const int lim = min(n_sel, max(1, kmax / 128 + 1) * per_tile);
   const float* src = sel + row * n_sel;
@@ -514,7 +516,7 @@ static int launch_score_t(const CUtensorMap& tq, const CUtensorMap& thi, const C
 }
 
 int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
-                     int lprime, int nb, int n, int n_fixed, float scale, void* workspace, size_t workspace_bytes,
+                     int lprime, int nb, int n, int n_fixed, float scale, int q0, void* workspace, size_t workspace_bytes,
                      cudaStream_t st) {
   if (!score_sm100_supported(H, G, T, dk, nbp, l, d, lprime, n)) return fail(NSA_ERR_UNSUPPORTED, "score_topn_sm100: unsupported shape");
   const size_t need = score_sm100_workspace_bytes(B, G, T, dk, nbp, d, lprime);
@@ -537,6 +539,7 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
   const int s_ = lprime / d, n_sel = nbp / s_;
   ScoreParams p;
   p.sel = sel;
+  p.q0 = q0;
   p.B = B; p.H = H; p.G = G; p.T = T; p.nbp = nbp; p.l = l; p.d = d; p.lprime = lprime; p.nb = nb; p.n_sel = n_sel;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.timeouts = fa_timeout_counter();
@@ -549,7 +552,7 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
   KernelTimer kt("score_topn_rows", st);
   const unsigned grid = (unsigned)((rows + 3) / 4);
 #define NSA_ROWS_CASE(PER_)                                                                                                   \
-  topn_rows_kernel<PER_><<<grid, 128, 0, st>>>(sel, out, rows, T, n_sel, 128 / s_, l, d, nb, lprime, n, n_fixed)
+  topn_rows_kernel<PER_><<<grid, 128, 0, st>>>(sel, out, rows, T, n_sel, 128 / s_, l, d, nb, lprime, n, n_fixed, q0)
   if (n_sel <= 8 * 32) {
     NSA_ROWS_CASE(8);
   } else if (n_sel <= 16 * 32) {
@@ -560,7 +563,7 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
     const size_t sm = 4 * (size_t)n_sel * sizeof(float);
     if (cudaFuncSetAttribute(topn_rows_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
       return fail(NSA_ERR_LAUNCH, "score_topn: cannot reserve shared memory for the row selection");
-    topn_rows_kernel<0><<<grid, 128, sm, st>>>(sel, out, rows, T, n_sel, 128 / s_, l, d, nb, lprime, n, n_fixed);
+    topn_rows_kernel<0><<<grid, 128, sm, st>>>(sel, out, rows, T, n_sel, 128 / s_, l, d, nb, lprime, n, n_fixed, q0);
   }
 #undef NSA_ROWS_CASE
   return check_launch("score_topn_rows");

@@ -167,7 +167,7 @@ topn_from_scores_kernel(const float* __restrict__ scores, int32_t* __restrict__ 
 
 using namespace nsa;
 
-namespace nsa { int kernel_family(); }
+namespace nsa { int kernel_family(); int query_pos0(); }
 
 static bool score_tc_ok(const void* q, const int64_t* qs, int B, int H, int G, int T, int dk, int nbp, int l, int d, int l_prime,
                         int n, int n_real_blocks, int dtype) {
@@ -192,8 +192,9 @@ extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const fl
                               size_t workspace_bytes, void* stream) {
   NSA_REQUIRE(q && qs && k_cmp && block_ends && indices_out, "score_topn: null pointer");
   if (B > 0 && T > 0 && score_tc_ok(q, qs, B, H, G, T, dk, nbp, l, d, l_prime, n, n_real_blocks, dtype))
-    return score_topn_sm100(q, k_cmp, indices_out, B, H, G, T, dk, nbp, l, d, l_prime, n_real_blocks, n, n_fixed, scale, workspace,
-                            workspace_bytes, (cudaStream_t)stream);
+    return score_topn_sm100(q, k_cmp, indices_out, B, H, G, T, dk, nbp, l, d, l_prime, n_real_blocks, n, n_fixed, scale,
+                            nsa::query_pos0(), workspace, workspace_bytes, (cudaStream_t)stream);
+  NSA_REQUIRE(nsa::query_pos0() == 0, "score_topn: a query offset (nsa_set_query_offset) needs the bf16 tensor-core path of this call");
   NSA_REQUIRE(G > 0 && H % G == 0 && d > 0 && l % d == 0 && l_prime % d == 0 && l > 0 && l_prime > 0,
               "score_topn: bad block parameters");
   NSA_REQUIRE(n > 0 && n <= kMaxN, "score_topn: n=%d outside 1..%d", n, kMaxN);

@@ -17,7 +17,7 @@ constexpr int kChunk = 128;  // queries per histogram chunk (one warp orders the
 struct CsrArgs {
   const int* indices;
   int64_t sidx[4];
-  int B, G, Tq, Tkv, nslots, lprime, nblk, nchunks, causal;
+  int B, G, Tq, Tkv, nslots, lprime, nblk, nchunks, causal, q0;
   int *hist, *off, *csr_t;
 };
 
@@ -30,7 +30,7 @@ __global__ void csr_count(const CsrArgs a) {
   for (int e = threadIdx.x; e < (t1 - t0) * a.nslots; e += blockDim.x) {
     const int t = t0 + e / a.nslots, s = e % a.nslots;
     const int* row = a.indices + b * a.sidx[0] + g * a.sidx[1] + (int64_t)t * a.sidx[2];
-    const int id = slot_block(row, a.sidx[3], s, t, a.Tkv, a.lprime, a.causal);
+    const int id = slot_block(row, a.sidx[3], s, a.q0 + t, a.Tkv, a.lprime, a.causal);
     if (id >= 0) atomicAdd(&sh[id], 1);
   }
   __syncthreads();
@@ -94,7 +94,7 @@ __global__ void csr_fill(const CsrArgs a, int slots_pad) {
     int id = -1;
     if (t < t1 && s < a.nslots) {
       const int* row = a.indices + b * a.sidx[0] + g * a.sidx[1] + (int64_t)t * a.sidx[2];
-      id = slot_block(row, a.sidx[3], s, t, a.Tkv, a.lprime, a.causal);
+      id = slot_block(row, a.sidx[3], s, a.q0 + t, a.Tkv, a.lprime, a.causal);
     }
     const unsigned peers = __match_any_sync(0xffffffffu, id >= 0 ? id : -1 - lane);
     const int rank = __popc(peers & ((1u << lane) - 1u));
@@ -126,7 +126,7 @@ size_t slc_csr_workspace_bytes(int B, int G, int Tq, int Tkv, int nslots, int lp
 }
 
 int build_slc_csr(const int* indices, const int64_t* sidx, int B, int G, int Tq, int Tkv, int nslots,
-                  int lprime, int causal, void* workspace, size_t workspace_bytes, const int** csr_off,
+                  int lprime, int causal, int q0, void* workspace, size_t workspace_bytes, const int** csr_off,
                   const int** csr_t, cudaStream_t st) {
   CsrArgs a;
   size_t o_hist, o_off, o_t, total;
@@ -138,7 +138,7 @@ int build_slc_csr(const int* indices, const int64_t* sidx, int B, int G, int Tq,
   if ((size_t)a.nblk * sizeof(int) > 160 * 1024) return fail(NSA_ERR_UNSUPPORTED, "too many key blocks (%d)", a.nblk);
   a.indices = indices;
   for (int i = 0; i < 4; ++i) a.sidx[i] = sidx[i];
-  a.B = B; a.G = G; a.Tq = Tq; a.Tkv = Tkv; a.nslots = nslots; a.lprime = lprime; a.causal = causal;
+  a.B = B; a.G = G; a.Tq = Tq; a.Tkv = Tkv; a.nslots = nslots; a.lprime = lprime; a.causal = causal; a.q0 = q0;
   char* w = (char*)workspace;
   a.hist = (int*)(w + o_hist);
   a.off = (int*)(w + o_off);

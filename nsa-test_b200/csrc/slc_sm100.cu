@@ -45,6 +45,7 @@ struct SlcParams {
   float *dk_part, *dv_part;    // [BG, nparts+nblk, 64, dk|dv] per-(CTA, block) partial sums (backward)
   __nv_bfloat16 *dk_out, *dv_out;  // [B,G,Tk,dk|dv] gradients the reduced partials are added into
   int B, H, G, Tq, Tk, nslots, nblk, hpg;
+  int q0;  // position of query row 0 in the sequence (query-sharded runs; 0 otherwise)
   int g5;  // gathered rows arrive as one rank-5 tile per query ([heads/8][width/64][8 rows][64 columns]) instead of one tile per 64 columns
   float scale, scale_log2;
   int* timeouts;
@@ -325,7 +326,7 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       tmem_ld32(tmem + lane_base + buf * 192, sv[0]);
       tmem_ld32(tmem + lane_base + buf * 192 + 32, sv[1]);
       tc_wait_ld();
-      const int chi = valid ? t - key0 : 63;  // causal: keys key0 + c <= t
+      const int chi = valid ? p.q0 + t - key0 : 63;  // causal: keys key0 + c <= position of the query
       float mx = -CUDART_INF_F;
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc)
@@ -420,7 +421,7 @@ template <int DV>
 __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part, const float2* __restrict__ st_part,
                                        const int* __restrict__ indices, int64_t s0, int64_t s1, int64_t s2, int64_t s3,
                                        __nv_bfloat16* __restrict__ out, float* __restrict__ L, float* __restrict__ M, int B,
-                                       int H, int G, int Tq, int Tk, int nslots, int lprime) {
+                                       int H, int G, int Tq, int Tk, int nslots, int lprime, int q0) {
   static_assert(DV % 64 == 0, "lanes own 2 or 4 consecutive output columns");
   constexpr int VPL = DV / 32;  // values per lane
   // consecutive warps take the heads of one (group, query): together they stream that query's contiguous block of partials
@@ -451,7 +452,7 @@ __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part,
       }
     }
     if (s16 == 0) {
-      validmask = valid_slot_mask(irow, s3, nslots, t, Tk, lprime, lane);
+      validmask = valid_slot_mask(irow, s3, nslots, q0 + t, Tk, lprime, lane);
       const bool mine = (validmask >> lane) & 1;
       if (!mine) st = make_float2(-CUDART_INF_F, 0.f);
       mx = warp_max(st.x);
@@ -489,7 +490,7 @@ template <int DV>
 __global__ void slc_combine_fwd_bulk_kernel(const __nv_bfloat16* __restrict__ o_part, const float2* __restrict__ st_part,
                                             const int* __restrict__ indices, int64_t s0, int64_t s1, int64_t s2, int64_t s3,
                                             __nv_bfloat16* __restrict__ out, float* __restrict__ L, float* __restrict__ M, int B,
-                                            int H, int G, int Tq, int Tk, int nslots, int lprime, int* timeouts) {
+                                            int H, int G, int Tq, int Tk, int nslots, int lprime, int q0, int* timeouts) {
   constexpr int VPL = DV / 32;
   extern __shared__ __align__(128) uint8_t sm_part[];
   __shared__ uint64_t bar;
@@ -513,7 +514,7 @@ __global__ void slc_combine_fwd_bulk_kernel(const __nv_bfloat16* __restrict__ o_
   const int64_t base = (q * nslots) * hpg + hh;
   float2 st = make_float2(-CUDART_INF_F, 0.f);
   if (lane < nslots) st = st_part[base + (int64_t)lane * hpg];
-  const unsigned validmask = valid_slot_mask(irow, s3, nslots, t, Tk, lprime, lane);
+  const unsigned validmask = valid_slot_mask(irow, s3, nslots, q0 + t, Tk, lprime, lane);
   const bool mine = (validmask >> lane) & 1;
   if (!mine) st = make_float2(-CUDART_INF_F, 0.f);
   const float mx = warp_max(st.x);
@@ -560,7 +561,7 @@ __global__ void slc_combine_fwd_bulk_kernel(const __nv_bfloat16* __restrict__ o_
 template <int DK>
 __global__ void slc_combine_dq_kernel(const __nv_bfloat16* __restrict__ dq_part, const int* __restrict__ indices, int64_t s0,
                                       int64_t s1, int64_t s2, int64_t s3, __nv_bfloat16* __restrict__ dq, int B, int H, int G,
-                                      int Tq, int Tk, int nslots, int lprime, float scale) {
+                                      int Tq, int Tk, int nslots, int lprime, float scale, int q0) {
   // consecutive warps take the heads of one (group, query): together they stream that query's contiguous block of partials
   const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -583,7 +584,7 @@ __global__ void slc_combine_dq_kernel(const __nv_bfloat16* __restrict__ dq_part,
 #pragma unroll
       for (int c = 0; c < DK / 64; ++c) raw[u][c] = s8 + u < nslots ? *reinterpret_cast<const uint32_t*>(src + c * 64 + lane * 2) : 0u;
     }
-    if (s8 == 0) validmask = valid_slot_mask(irow, s3, nslots, t, Tk, lprime, lane);
+    if (s8 == 0) validmask = valid_slot_mask(irow, s3, nslots, q0 + t, Tk, lprime, lane);
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       if (s8 + u >= nslots || !((validmask >> (s8 + u)) & 1)) continue;  // never written: discard
@@ -605,7 +606,7 @@ __global__ void slc_combine_dq_kernel(const __nv_bfloat16* __restrict__ dq_part,
 template <int DK>
 __global__ void slc_combine_dq_bulk_kernel(const __nv_bfloat16* __restrict__ dq_part, const int* __restrict__ indices, int64_t s0,
                                            int64_t s1, int64_t s2, int64_t s3, __nv_bfloat16* __restrict__ dq, int B, int H, int G,
-                                           int Tq, int Tk, int nslots, int lprime, float scale, int* timeouts) {
+                                           int Tq, int Tk, int nslots, int lprime, float scale, int q0, int* timeouts) {
   extern __shared__ __align__(128) uint8_t sm_part[];
   __shared__ uint64_t bar;
   __shared__ int abort_flag;
@@ -625,7 +626,7 @@ __global__ void slc_combine_dq_bulk_kernel(const __nv_bfloat16* __restrict__ dq_
   }
   const int64_t row = ((int64_t)b * H + h) * Tq + t;
   const int* irow = indices + b * s0 + g * s1 + (int64_t)t * s2;
-  const unsigned validmask = valid_slot_mask(irow, s3, nslots, t, Tk, lprime, lane);
+  const unsigned validmask = valid_slot_mask(irow, s3, nslots, q0 + t, Tk, lprime, lane);
   float acc[DK / 32];
 #pragma unroll
   for (int c = 0; c < DK / 32; ++c) acc[c] = 0.f;
@@ -1039,7 +1040,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       const int entry = ent_next;
       const float lse2 = lse_next, Dr = D_next;
       const int t = entry < 0 ? -1 : (entry & 0xFFFFFF), slot = entry < 0 ? 0 : (entry >> 24);
-      const int chi = t - w.blk * 64;
+      const int chi = t < 0 ? -1 : p.q0 + t - w.blk * 64;
       {  // this group's next chunk: fetch its statistics one chunk ahead
         ChunkWalker w2 = w;
         w2.next();
@@ -1232,16 +1233,16 @@ static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
     if (cudaFuncSetAttribute(kc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qbytes) != cudaSuccess)
       return fail(NSA_ERR_LAUNCH, "slc_combine_fwd: cannot reserve shared memory");
     kc<<<(unsigned)((int64_t)p.B * p.G * p.Tq), p.hpg * 32, qbytes, st>>>(p.o_part, p.st_part, indices, sidx[0], sidx[1], sidx[2], sidx[3],
-                                                                      out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.timeouts);
+                                                                      out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.q0, p.timeouts);
   } else {
     slc_combine_fwd_kernel<DV><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.o_part, p.st_part, indices, sidx[0], sidx[1], sidx[2],
-                                                                           sidx[3], out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64);
+                                                                           sidx[3], out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.q0);
   }
   return check_launch("slc_combine_fwd");
 }
 
 int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, void* out, float* L,
-                  float* M, int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale,
+                  float* M, int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, int q0,
                   void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!slc_sm100_supported(H, G, Tq, Tk, dk, dv, nslots, lprime)) return fail(NSA_ERR_UNSUPPORTED, "slc_fwd_sm100: unsupported shape");
   const size_t need = slc_fwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, nslots, lprime);
@@ -1250,7 +1251,8 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
   SlcParams p = {};
   char* w = (char*)workspace;
   const size_t csr_bytes = al256(slc_csr_workspace_bytes(B, G, Tq, Tk, nslots, lprime));
-  if (int rc = build_slc_csr(indices, sidx, B, G, Tq, Tk, nslots, lprime, 1, w, csr_bytes, &p.csr_off, &p.csr_t, st)) return rc;
+  if (int rc = build_slc_csr(indices, sidx, B, G, Tq, Tk, nslots, lprime, 1, q0, w, csr_bytes, &p.csr_off, &p.csr_t, st)) return rc;
+  p.q0 = q0;
   const size_t rows = (size_t)B * H * Tq * nslots;
   p.o_part = (__nv_bfloat16*)(w + csr_bytes);
   p.st_part = (float2*)(w + csr_bytes + al256(rows * dv * 2));
@@ -1327,10 +1329,10 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
       if (cudaFuncSetAttribute(kc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qbytes) != cudaSuccess)
         return fail(NSA_ERR_LAUNCH, "slc_combine_dq: cannot reserve shared memory");
       kc<<<(unsigned)((int64_t)p.B * p.G * p.Tq), p.hpg * 32, qbytes, st>>>(p.dq_part, indices, sidx[0], sidx[1], sidx[2], sidx[3], dq, p.B,
-                                                                        p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale, p.timeouts);
+                                                                        p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale, p.q0, p.timeouts);
     } else {
       slc_combine_dq_kernel<DK><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.dq_part, indices, sidx[0], sidx[1], sidx[2], sidx[3], dq,
-                                                                            p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale);
+                                                                            p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale, p.q0);
     }
   }
   if (int rc = check_launch("slc_combine_dq")) return rc;
@@ -1342,7 +1344,7 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
 
 int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, const void* out,
                   const void* dout, const float* L, const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G,
-                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, void* workspace,
+                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, int q0, void* workspace,
                   size_t workspace_bytes, cudaStream_t st) {
   if (!slc_sm100_supported(H, G, Tq, Tk, dk, dv, nslots, lprime)) return fail(NSA_ERR_UNSUPPORTED, "slc_bwd_sm100: unsupported shape");
   size_t o_stat, o_dq, o_dk, o_dv, o_qt, o_dot, need;
@@ -1351,7 +1353,8 @@ int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indice
     return fail(NSA_ERR_WORKSPACE, "selection backward needs %zu workspace bytes, got %zu", need, workspace_bytes);
   SlcParams p = {};
   char* w = (char*)workspace;
-  if (int rc = build_slc_csr(indices, sidx, B, G, Tq, Tk, nslots, lprime, 1, w, o_stat, &p.csr_off, &p.csr_t, st)) return rc;
+  if (int rc = build_slc_csr(indices, sidx, B, G, Tq, Tk, nslots, lprime, 1, q0, w, o_stat, &p.csr_off, &p.csr_t, st)) return rc;
+  p.q0 = q0;
   const size_t rows = (size_t)B * H * Tq;
   float* D = (float*)(w + o_stat);
   float* lse2 = (float*)(w + o_stat + al256(rows * sizeof(float)));

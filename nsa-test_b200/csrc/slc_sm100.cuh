@@ -10,14 +10,14 @@ bool slc_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv, int nslot
 
 size_t slc_fwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime);
 int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, void* out, float* L,
-                  float* M, int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale,
+                  float* M, int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, int q0,
                   void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 
 size_t slc_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime);
 int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, const void* out,
                   const void* dout, const float* L, const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G,
-                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, void* workspace,
+                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, int q0, void* workspace,
                   size_t workspace_bytes, cudaStream_t st);
 
 }  // namespace nsa

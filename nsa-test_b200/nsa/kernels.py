@@ -121,25 +121,25 @@ class CompressionAttention(torch.autograd.Function):
     """``apply(q, k_compressed [B,G,dk,NB], v_compressed [B,G,NB,dv], block_ends [NB], scale, config)``."""
 
     @staticmethod
-    def forward(ctx, q, k_compressed, v_compressed, block_ends, scale, config=None, blocks=None):
-        o, L, M = ops.cmp_attn_fwd(q, k_compressed, v_compressed, block_ends, scale, blocks)
+    def forward(ctx, q, k_compressed, v_compressed, block_ends, scale, config=None, blocks=None, q_pos0=0):
+        o, L, M = ops.cmp_attn_fwd(q, k_compressed, v_compressed, block_ends, scale, blocks, q_pos0)
         ctx.save_for_backward(q, k_compressed, v_compressed, block_ends, o, L, M)
-        ctx.scale, ctx.blocks = scale, blocks
+        ctx.scale, ctx.blocks, ctx.q_pos0 = scale, blocks, q_pos0
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, kc, vc, block_ends, o, L, M = ctx.saved_tensors
-        dq, dkc, dvc = ops.cmp_attn_bwd(q, kc, vc, block_ends, o, do, L, M, ctx.scale, ctx.blocks)
-        return dq, dkc.transpose(-1, -2), dvc, None, None, None, None
+        dq, dkc, dvc = ops.cmp_attn_bwd(q, kc, vc, block_ends, o, do, L, M, ctx.scale, ctx.blocks, ctx.q_pos0)
+        return dq, dkc.transpose(-1, -2), dvc, None, None, None, None, None
 
 
-def _selection_fallback(indices: torch.Tensor, l_prime: int) -> torch.Tensor:
+def _selection_fallback(indices: torch.Tensor, l_prime: int, q_pos0: int = 0) -> torch.Tensor:
     """Rows whose slots are all -1 attend the block holding the query (nsa/kernels.py:199-205)."""
     if indices.numel() == 0:
         return indices
     T = indices.shape[2]
-    t_blocks = (torch.arange(T, device=indices.device, dtype=indices.dtype) // l_prime).view(1, 1, T, 1)
+    t_blocks = ((torch.arange(T, device=indices.device, dtype=indices.dtype) + q_pos0) // l_prime).view(1, 1, T, 1)
     none_valid = (indices < 0).all(dim=-1, keepdim=True)
     return torch.where(none_valid, t_blocks, indices)
 
@@ -148,18 +148,18 @@ class SelectionAttention(torch.autograd.Function):
     """``apply(q, k [B,G,dk,T], v [B,G,T,dv], indices [B,G,T,n], scale, config) -> o``."""
 
     @staticmethod
-    def forward(ctx, q, k, v, indices, scale, config):
-        idx = _selection_fallback(indices, config.l_prime).to(torch.int32).contiguous()
-        o, L, M = ops.slc_fwd(q, k, v, idx, config.l_prime, scale)
+    def forward(ctx, q, k, v, indices, scale, config, q_pos0=0):
+        idx = _selection_fallback(indices, config.l_prime, q_pos0).to(torch.int32).contiguous()
+        o, L, M = ops.slc_fwd(q, k, v, idx, config.l_prime, scale, q_pos0)
         ctx.save_for_backward(q, k, v, idx, o, L, M)
-        ctx.scale, ctx.l_prime = scale, config.l_prime
+        ctx.scale, ctx.l_prime, ctx.q_pos0 = scale, config.l_prime, q_pos0
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, idx, o, L, M = ctx.saved_tensors
-        dq, dkey, dval = ops.slc_bwd(q, k, v, idx, o, do, L, M, ctx.l_prime, ctx.scale)
-        return dq, dkey.transpose(-1, -2), dval, None, None, None
+        dq, dkey, dval = ops.slc_bwd(q, k, v, idx, o, do, L, M, ctx.l_prime, ctx.scale, ctx.q_pos0)
+        return dq, dkey.transpose(-1, -2), dval, None, None, None, None
 
 
 # --------------------------------------------------------------------------------------------------
@@ -252,30 +252,51 @@ class _GateMix(torch.autograd.Function):
         return dlogits.to(ctx.ldtype), d0, d1, d2, None
 
 
+def _sliding_with_offset(q, kw, vw, scale, cfg, q_pos0: int):
+    """Sliding-window branch for queries at positions q_pos0 + [0, Tq) against keys from position 0: the window only
+    reaches w - 1 positions back, so the kernel runs on the key slice that starts a (tile-aligned) margin before the
+    first query, with as many zero query rows in front; their outputs are dropped and, their upstream gradient being
+    zero, they add nothing to dK/dV."""
+    Tq = q.shape[2]
+    if q_pos0 == 0 and kw.shape[-1] == Tq:
+        return SlidingWindowAttention.apply(q, kw, vw, scale, cfg.w, cfg)
+    pad = min(q_pos0, ((cfg.w - 1 + 127) // 128) * 128)
+    lo, hi = q_pos0 - pad, q_pos0 + Tq
+    ks = kw[..., lo:hi].contiguous()
+    vs = vw[:, :, lo:hi].contiguous()
+    qp = torch.cat([q.new_zeros(q.shape[0], q.shape[1], pad, q.shape[3]), q], dim=2) if pad else q
+    return SlidingWindowAttention.apply(qp, ks, vs, scale, cfg.w, cfg)[:, :, pad:]
+
+
 def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv_compress=None, kv_sliding=None,
-              scale: Optional[float] = None, return_info: bool = False):
+              scale: Optional[float] = None, return_info: bool = False, q_pos0: int = 0):
     """The NSA hot path between the q/k/v projections and o_proj (nsa/kernels.py:2298-2463).
 
     q [B,H,T,dk]; k_* [B,G,dk,T]; v_* [B,G,T,dv]; gate_logits [B,T,3H]; phi_params =
     (pos_embed [l,l], w1 [2dk,dk+l], b1, w2 [dk,2dk], b2).  One (k,v) feeds all branches unless
     ``kv_compress`` / ``kv_sliding`` are given.  Returns the mixed output [B,H,T,dv] (and a dict with
     indices, gates, k_cmp, v_cmp, block_ends when ``return_info``).
+
+    Query-sharded long-context runs: q and gate_logits hold the Tq query rows at positions
+    ``q_pos0 + [0, Tq)`` while k/v cover the sequence from position 0 (at least up to the last query); the
+    gradients of k/v then hold this query slice's contribution only (summed over the ranks by the caller).
     """
     cfg = config
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     kc_src, vc_src = kv_compress if kv_compress is not None else (k_slc, v_slc)
     kw, vw = kv_sliding if kv_sliding is not None else (k_slc, v_slc)
-    T = q.shape[2]
+    T = kc_src.shape[-1]   # sequence length covered by the keys (== query rows unless q_pos0 shards the queries)
     pos_embed, w1, b1, w2, b2 = phi_params
     k_cmp, v_cmp = _PhiCompress.apply(kc_src.transpose(-1, -2), vc_src, pos_embed, w1, b1, w2, b2, cfg.l, cfg.d)
     nb = (T - cfg.l) // cfg.d + 1
     block_ends = torch.full((k_cmp.shape[-1],), PAD_BLOCK_END, device=q.device, dtype=torch.int32)
     block_ends[:nb] = torch.arange(nb, device=q.device, dtype=torch.int32) * cfg.d + (cfg.l - 1)
     n_fixed = cfg.n_fixed if cfg.include_fixed_in_selection else 0
-    indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale, nb)
-    o_cmp = CompressionAttention.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, scale, cfg, (cfg.l, cfg.d, nb))
-    o_slc = SelectionAttention.apply(q, k_slc, v_slc, indices, scale, cfg)
-    o_win = SlidingWindowAttention.apply(q, kw, vw, scale, cfg.w, cfg)
+    indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale, nb,
+                             q_pos0)
+    o_cmp = CompressionAttention.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, scale, cfg, (cfg.l, cfg.d, nb), q_pos0)
+    o_slc = SelectionAttention.apply(q, k_slc, v_slc, indices, scale, cfg, q_pos0)
+    o_win = _sliding_with_offset(q, kw, vw, scale, cfg, q_pos0)
     out, gates = _GateMix.apply(gate_logits, o_cmp, o_slc, o_win, cfg.gate_mode)
     if return_info:
         return out, dict(indices=indices, gates=gates, k_cmp=k_cmp, v_cmp=v_cmp, block_ends=block_ends,

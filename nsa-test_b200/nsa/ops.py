@@ -68,7 +68,25 @@ def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float):
     return dq, dkey, dval
 
 
-def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None):
+class query_offset:
+    """``with query_offset(p):`` the library calls made inside treat query row t as position p + t of the sequence
+    (query-sharded long-context runs; keys start at position 0).  Thread-local in the library; restored to 0 on exit."""
+
+    def __init__(self, position: int):
+        self.position = int(position)
+
+    def __enter__(self):
+        if self.position:
+            check(lib.nsa_set_query_offset(self.position), "nsa_set_query_offset")
+        return self
+
+    def __exit__(self, *exc):
+        if self.position:
+            lib.nsa_set_query_offset(0)
+        return False
+
+
+def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None, q_pos0: int = 0):
     """``blocks=(l, d, n_blocks)`` asserts block_ends[i] == i*d + l - 1 for i < n_blocks and no later block
     ever visible; it lets the tensor-core kernel bound its key loop."""
     bl, bd, bn = blocks if blocks is not None else (0, 0, 0)
@@ -77,14 +95,14 @@ def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None):
     G, NB, dv = k_cmp.shape[1], k_cmp.shape[-1], v_cmp.shape[-1]
     be = block_ends.to(torch.int32).contiguous()
     o, L, M = _stats(q, dv)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), query_offset(q_pos0):
         check(lib.nsa_cmp_attn_fwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(L), ptr(M),
                                    i64(_fwd_strides(q, k_cmp, v_cmp, o, L, M)), B, H, G, T, NB, dk, dv, float(scale),
                                    dtype_code(q), int(bl), int(bd), int(bn), stream_ptr(dev)), "nsa_cmp_attn_fwd")
     return o, L, M
 
 
-def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=None):
+def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=None, q_pos0: int = 0):
     bl, bd, bn = blocks if blocks is not None else (0, 0, 0)
     dev = require_cuda(q, k_cmp, v_cmp, block_ends, o, do, L, M)
     B, H, T, dk = q.shape
@@ -99,14 +117,14 @@ def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=
     s = _fwd_strides(q, k_cmp, v_cmp, o, L, M) + list(dq.stride()) + list(dkc.stride()) + list(dvc.stride())
     nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, T, NB, dk, dv, 1)
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), query_offset(q_pos0):
         check(lib.nsa_cmp_attn_bwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq),
                                    ptr(dkc), ptr(dvc), i64(s), B, H, G, T, NB, dk, dv, float(scale), dtype_code(q),
                                    int(bl), int(bd), int(bn), ptr(ws), nbytes, stream_ptr(dev)), "nsa_cmp_attn_bwd")
     return dq, dkc, dvc
 
 
-def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float):
+def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float, q_pos0: int = 0):
     dev = require_cuda(q, k, v, indices_i32)
     B, H, Tq, dk = q.shape
     G, Tkv, dv = k.shape[1], k.shape[-1], v.shape[-1]
@@ -116,14 +134,14 @@ def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float):
     n = indices_i32.shape[-1]
     nbytes = lib.nsa_slc_fwd_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n, int(l_prime), dtype_code(q))
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), query_offset(q_pos0):
         check(lib.nsa_slc_fwd(ptr(q), ptr(k), ptr(v), ptr(indices_i32), ptr(o), ptr(L), ptr(M), i64(s), B, H, G, Tq, Tkv,
                               n, int(l_prime), dk, dv, float(scale), dtype_code(q), ptr(ws), nbytes, stream_ptr(dev)),
               "nsa_slc_fwd")
     return o, L, M
 
 
-def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float):
+def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float, q_pos0: int = 0):
     dev = require_cuda(q, k, v, indices_i32, o, do, L, M)
     B, H, Tq, dk = q.shape
     G, Tkv, dv = k.shape[1], k.shape[-1], v.shape[-1]
@@ -138,7 +156,7 @@ def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float):
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     s = (_fwd_strides(q, k, v, o, L, M) + list(dq.stride()) + list(dkey.stride()) + list(dval.stride())
          + list(indices_i32.stride()))
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), query_offset(q_pos0):
         check(lib.nsa_slc_bwd(ptr(q), ptr(k), ptr(v), ptr(indices_i32), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq),
                               ptr(dkey), ptr(dval), i64(s), B, H, G, Tq, Tkv, n, int(l_prime), dk, dv, float(scale),
                               dtype_code(q), ptr(ws), nbytes, stream_ptr(dev)), "nsa_slc_bwd")
@@ -179,7 +197,7 @@ def phi_pool_bwd(a, c, dhbar, dv_cmp, l: int, d: int, n_blocks: int):
 
 
 def score_topn(q, k_cmp_f32, block_ends, l: int, d: int, l_prime: int, n: int, n_fixed: int, scale: float,
-               n_real_blocks: int = -1):
+               n_real_blocks: int = -1, q_pos0: int = 0):
     """q [B,H,T,dk], k_cmp fp32 [B,G,dk,nbp] -> int32 indices [B,G,T,n].  ``n_real_blocks >= 0`` asserts the
     canonical block ends (block i ends at i*d + l - 1 for i < n_real_blocks, later blocks never visible)."""
     dev = require_cuda(q, k_cmp_f32, block_ends)
@@ -190,7 +208,7 @@ def score_topn(q, k_cmp_f32, block_ends, l: int, d: int, l_prime: int, n: int, n
     out = torch.empty(B, G, T, n, device=dev, dtype=torch.int32)
     nbytes = lib.nsa_score_topn_workspace_bytes(B, H, G, T, dk, nbp, int(l), int(d), int(l_prime), int(n), dtype_code(q))
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), query_offset(q_pos0):
         check(lib.nsa_score_topn(ptr(q), i64(q.stride()), ptr(kc), ptr(be), ptr(out), B, H, G, T, dk, nbp, int(l), int(d),
                                  int(l_prime), int(n), int(n_fixed), float(scale), dtype_code(q), int(n_real_blocks), ptr(ws),
                                  nbytes, stream_ptr(dev)), "nsa_score_topn")

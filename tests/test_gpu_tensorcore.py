@@ -263,7 +263,9 @@ def test_selection_backward_tensorcore_vs_generic_at_scale():
         _grad_close(a, b_.float().cpu(), "selection " + nme)
 
 
-@pytest.mark.parametrize("dk,H,G,T", [(64, 8, 2, 2048), (192, 16, 1, 4096)])
+# the two long cases reach the 16- and 32-candidates-per-lane variants of the row top-n kernel (n_sel = 512, 1024)
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("dk,H,G,T", [(64, 8, 2, 2048), (192, 16, 1, 4096), (64, 4, 2, 32768), (64, 2, 1, 65536)])
 def test_score_topn_tensorcore_bit_exact_outside_ambiguity(dk, H, G, T):
     """Fused Eq. 8-11 on tensor cores (bf16 hi + lo split of the fp32 keys) against the fp32 CPU oracle:
     identical block ids on every row whose ranking does not hinge on rounding, and identical to the

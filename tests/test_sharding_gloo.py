@@ -57,3 +57,47 @@ def test_two_rank_weight_gradient_allreduce():
     ret = mgr.dict()
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     assert ret["err"] < 1e-5
+
+
+def _gather_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nsa.sharding import all_gather_seq, query_shard
+        T, step = 512, 256
+        g = torch.Generator().manual_seed(9)
+        full = torch.randn(2, 3, T, generator=g)
+        wgt = torch.randn(2, 3, T, generator=g) * (rank + 1)       # each rank's loss weighs the gathered tensor differently
+        t0, t1 = query_shard(T, world, rank)
+        x = full[..., t0:t1].clone().requires_grad_(True)
+        y = all_gather_seq(x, -1)
+        (y * wgt).sum().backward()
+        ok_fwd = torch.equal(y.detach(), full)
+        g2 = torch.Generator().manual_seed(9)
+        torch.randn(2, 3, T, generator=g2)
+        base = torch.randn(2, 3, T, generator=g2)
+        want = base * sum(r + 1 for r in range(world))              # gradient summed over the ranks' losses
+        ret[rank] = (ok_fwd, (x.grad - want[..., t0:t1]).abs().max().item(), (t1 - t0) == step)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_query_shard_bounds():
+    from nsa.sharding import query_shard
+    assert [query_shard(1024, 4, r) for r in range(4)] == [(0, 256), (256, 512), (512, 768), (768, 1024)]
+    with pytest.raises(ValueError):
+        query_shard(1000, 4, 0)
+    with pytest.raises(ValueError):
+        query_shard(512, 8, 0)      # 64-row slices are not whole query tiles
+
+
+def test_two_rank_sequence_all_gather_and_gradient_reduce_scatter():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_gather_worker, args=(2, port, ret), nprocs=2, join=True)
+    for r in range(2):
+        ok_fwd, err, ok_len = ret[r]
+        assert ok_fwd and ok_len and err < 1e-5
