@@ -35,6 +35,14 @@ CFG = dict(H=64, G=4, dk=192, dv=128, w=512, l=32, d=16, l_prime=64, n=16, d_mod
 METRIC = "NSA layer fwd+bwd tokens/s at T=64K"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from an ncu capture at T=8192 (profiles/ncu_dram_bytes_T8192.md),
+# per (group, query, slot) unit of the selection kernels.  That case is too small to be captured at full size under the
+# capture-size rule, so the figure is scaled by the units of the workload; at T=8192 62 % of the gathers hit L2, at
+# T=65536 fewer do, so the scaled figure is a lower bound of the full-size traffic.
+NCU_DRAM_BYTES_PER_UNIT = {"slc_bwd_fused": (3438014976 + 3070898432) / (8192 * 4 * 16),
+                           "slc_fwd": (1592842240 + 2031976192) / (8192 * 4 * 16)}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -240,7 +248,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--T", type=int, default=65536)
-    ap.add_argument("--cpu-sample", type=int, default=2048, help="sequence length of the CPU-oracle sample")
+    ap.add_argument("--cpu-sample", type=int, default=4096, help="sequence length of the CPU-oracle sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--shard", default="sequence", choices=["sequence", "query"],
                     help="sequence: one T-token sequence per GPU (weak scaling, the default); query: ONE T-token sequence "
@@ -359,8 +367,12 @@ def main():
         if top and not query_mode:   # per-launch FLOP figures assume a whole sequence per launch
             n_l, tot = cand[top]
             achieved = kflops[top] / (tot / n_l * 1e-3) / 1e12
+            units = c["G"] * T * c["n"]                                   # (group, query, slot) triples of one launch
+            traffic = int(NCU_DRAM_BYTES_PER_UNIT[top] * units) if top in NCU_DRAM_BYTES_PER_UNIT else None
             roofline = dict(bound="tensor", kernel=top, achieved=round(achieved, 1), peak=peaks["tflops_sustained"], unit="TFLOP/s",
-                            frac=round(achieved / peaks["tflops_sustained"], 4), traffic=None, peak_source=peaks["source"] + " (sustained bf16)",
+                            frac=round(achieved / peaks["tflops_sustained"], 4), traffic=traffic,
+                            traffic_source="ncu dram bytes at T=8192 scaled by (group, query, slot) units; lower bound" if traffic else None,
+                            peak_source=peaks["source"] + " (sustained bf16)",
                             ms_per_launch=round(tot / n_l, 4))
         att = attention_flops(T)
         att_total = sum(att[b_][p_] for b_ in att for p_ in att[b_])
