@@ -755,7 +755,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   const uint32_t tmem = bar->tmem_base;
   constexpr uint32_t cS = 0, cdP = 64, cdQ = 128, cdV = 128 + DK, cdK1 = cdV + 64, cdK2 = cdK1 + 64;
   static_assert(cdK2 + (MK2 ? 64 : 0) <= 512, "TMEM columns");
-  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 136;");
 
   if (warp >= 10) {
   } else if (!has_work) {
@@ -988,7 +988,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     }
   } else {
     // compute: one gathered row per thread; groups alternate chunks; both groups take part in every flush
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
     const int grp = warp >> 2, warp4 = warp & 3;
     const int r = warp4 * 32 + lane;
     const int half = warp4 >> 1, rr = r & 63;  // which 64-row half of the chunk this row is handed over in
