@@ -149,13 +149,14 @@ def layer_step_query_sharded(inp, params, cfg, world):
     """Long-context mode: `inp` holds this rank's slice of the positions; K/V are all-gathered inside the layer and
     their gradients come back reduce-scattered (nsa.sharding.query_sharded_layer)."""
     from nsa.sharding import allreduce_grads, query_sharded_layer
+    bounds = inp.get("bounds")
     lin = torch.nn.functional.linear
     q = inp["q"].detach().requires_grad_(True)
     k = inp["k"].detach().requires_grad_(True)
     v = inp["v"].detach().requires_grad_(True)
     logits = lin(torch.relu(lin(inp["x"], params["gw1"], params["gb1"])), params["gw2"], params["gb2"])
     phi = (params["pos_embed"], params["w1"], params["b1"], params["w2"], params["b2"])
-    out = query_sharded_layer(q, k, v, logits, phi, cfg)
+    out = query_sharded_layer(q, k, v, logits, phi, cfg, bounds=bounds)
     plist = list(params.values())
     grads = torch.autograd.grad(out, [q, k, v] + plist, inp["do"])
     if world > 1:
@@ -273,11 +274,13 @@ def main():
                         n=c["n"], w=c["w"], n_heads=c["H"], n_kv_groups=c["G"])
     query_mode = args.shard == "query" and world > 1
     if query_mode:
-        from nsa.sharding import query_shard
+        from nsa.sharding import balanced_query_bounds
         inp, params = make_device_inputs(T, dev, seed=0)        # the same sequence on every rank; each keeps its slice
-        t0, t1 = query_shard(T, world, rank)
+        # slices sized for equal attention work: w + n*l' keys per query everywhere, plus t/d compressed keys
+        bounds = balanced_query_bounds(T, world, c["w"] + c["n"] * c["l_prime"], c["d"])
+        t0, t1 = bounds[rank], bounds[rank + 1]
         inp = dict(q=inp["q"][:, :, t0:t1].contiguous(), k=inp["k"][..., t0:t1].contiguous(), v=inp["v"][:, :, t0:t1].contiguous(),
-                   do=inp["do"][:, :, t0:t1].contiguous(), x=inp["x"][:, t0:t1].contiguous())
+                   do=inp["do"][:, :, t0:t1].contiguous(), x=inp["x"][:, t0:t1].contiguous(), bounds=bounds)
         torch.cuda.empty_cache()
     else:
         inp, params = make_device_inputs(T, dev, seed=rank)
@@ -311,14 +314,14 @@ def main():
     value = seqs * T / (ms_per_step * 1e-3)
 
     # ---- end to end: inputs come from pinned host memory every step, result read back -----------
-    host = {k_: torch.empty(v_.shape, dtype=v_.dtype, pin_memory=True).copy_(v_) for k_, v_ in inp.items()}
+    host = {k_: torch.empty(v_.shape, dtype=v_.dtype, pin_memory=True).copy_(v_) for k_, v_ in inp.items() if torch.is_tensor(v_)}
     h2d = sum(t_.numel() * t_.element_size() for t_ in host.values())
     res_host = torch.empty(1, dtype=torch.float32, pin_memory=True)
 
     # Inputs are double-buffered on the device: the copy of step i+1 runs on its own stream while step i computes, as a
     # data loader would feed the layer.  Every step's inputs are copied, and its result read back, inside the timed region.
     copy_stream = torch.cuda.Stream(device=dev)
-    slots = [{k_: torch.empty_like(v_) for k_, v_ in inp.items()} for _ in range(2)]
+    slots = [{k_: (torch.empty_like(v_) if torch.is_tensor(v_) else v_) for k_, v_ in inp.items()} for _ in range(2)]
     copied = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
 

@@ -49,48 +49,90 @@ def query_shard(T: int, world: int, rank: int, multiple: int = 128) -> Tuple[int
     return rank * step, (rank + 1) * step
 
 
+def balanced_query_bounds(T: int, world: int, per_query_fixed: float, d: int, multiple: int = 128) -> List[int]:
+    """Slice boundaries [0 = b_0 < b_1 < ... < b_world = T] (multiples of the 128-row query tile) that give every rank about
+    the same attention work when the cost of the query at position t is ``per_query_fixed + t / d`` keys: a constant for
+    the sliding window and the selected blocks, plus the compressed keys it can see, which grow with t.  Equal slices
+    would leave the last rank with most of the causal work."""
+    if T % multiple or T // multiple < world:
+        raise ValueError(f"T={T} does not split into {world} slices that are multiples of {multiple}")
+    c0 = float(per_query_fixed)
+    total = c0 * T + T * T / (2.0 * d)
+    bounds = [0]
+    for r in range(1, world):
+        target = total * r / world
+        s_ = d * (-c0 + (c0 * c0 + 2.0 * target / d) ** 0.5)
+        b = int(round(s_ / multiple)) * multiple
+        b = max(b, bounds[-1] + multiple)
+        b = min(b, T - (world - r) * multiple)
+        bounds.append(b)
+    bounds.append(T)
+    return bounds
+
+
 class _AllGatherSeq(torch.autograd.Function):
-    """All-gather of equal slices along `dim`.  Backward: the gradient of the gathered tensor is summed over the ranks
-    in fp32 and every rank keeps its own slice (a reduce-scatter; all-reduce + slice where the backend has none)."""
+    """All-gather of slices along `dim` (``sizes``: every rank's slice length; equal slices when None).  Backward: the
+    gradient of the gathered tensor is summed over the ranks in fp32 and every rank keeps its own slice (a reduce-scatter;
+    all-reduce + slice where the backend has none).  Uneven slices travel padded to the longest one."""
 
     @staticmethod
-    def forward(ctx, x, dim, group):
+    def forward(ctx, x, dim, group, sizes=None):
         world = dist.get_world_size(group)
-        ctx.dim, ctx.group, ctx.world, ctx.rank = dim % x.dim(), group, world, dist.get_rank(group)
-        parts = [torch.empty_like(x) for _ in range(world)]
-        dist.all_gather(parts, x.contiguous(), group=group)
-        return torch.cat(parts, dim=ctx.dim)
+        dim = dim % x.dim()
+        sizes = [x.shape[dim]] * world if sizes is None else [int(v_) for v_ in sizes]
+        ctx.dim, ctx.group, ctx.world, ctx.rank, ctx.sizes = dim, group, world, dist.get_rank(group), sizes
+        big = max(sizes)
+        xp = x.contiguous()
+        if xp.shape[dim] < big:
+            pad_shape = list(xp.shape)
+            pad_shape[dim] = big - xp.shape[dim]
+            xp = torch.cat([xp, xp.new_zeros(pad_shape)], dim=dim)
+        parts = [torch.empty_like(xp) for _ in range(world)]
+        dist.all_gather(parts, xp, group=group)
+        return torch.cat([p_.narrow(dim, 0, n_) for p_, n_ in zip(parts, sizes)], dim=dim)
 
     @staticmethod
     def backward(ctx, g):
-        chunks = [c.float().contiguous() for c in g.chunk(ctx.world, dim=ctx.dim)]
+        big = max(ctx.sizes)
+        chunks = []
+        for c in g.split(ctx.sizes, dim=ctx.dim):
+            c = c.float()
+            if c.shape[ctx.dim] < big:
+                pad_shape = list(c.shape)
+                pad_shape[ctx.dim] = big - c.shape[ctx.dim]
+                c = torch.cat([c, c.new_zeros(pad_shape)], dim=ctx.dim)
+            chunks.append(c.contiguous())
         if dist.get_backend(ctx.group) == "nccl":
             out = torch.empty_like(chunks[ctx.rank])
             dist.reduce_scatter(out, chunks, op=dist.ReduceOp.SUM, group=ctx.group)
         else:
-            full = torch.cat(chunks, dim=ctx.dim)
+            full = torch.stack(chunks)
             dist.all_reduce(full, op=dist.ReduceOp.SUM, group=ctx.group)
-            out = full.chunk(ctx.world, dim=ctx.dim)[ctx.rank]
-        return out.to(g.dtype), None, None
+            out = full[ctx.rank]
+        return out.narrow(ctx.dim, 0, ctx.sizes[ctx.rank]).to(g.dtype), None, None, None
 
 
-def all_gather_seq(x: torch.Tensor, dim: int, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+def all_gather_seq(x: torch.Tensor, dim: int, group: Optional[dist.ProcessGroup] = None, sizes=None) -> torch.Tensor:
     """Differentiable all-gather along `dim` (identity without a process group or with one rank)."""
     if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return x
-    return _AllGatherSeq.apply(x, dim, group)
+    return _AllGatherSeq.apply(x, dim, group, sizes)
 
 
-def query_sharded_layer(q_local, k_local, v_local, gate_logits_local, phi_params, config, group=None, **kw):
+def query_sharded_layer(q_local, k_local, v_local, gate_logits_local, phi_params, config, group=None, bounds=None, **kw):
     """The NSA layer with the sequence split by position over the ranks of `group`: every rank holds the q
-    [B,H,T/N,dk], k [B,G,dk,T/N], v [B,G,T/N,dv] and gate-logit slices of its positions.  K and V are all-gathered
-    (their gradients come back reduce-scattered), each rank then runs its query slice against the gathered keys; the
-    compressed keys/values are recomputed from the gathered K/V on every rank (a few percent of the layer's work)
-    instead of being exchanged.  Weight gradients (phi, gate MLP) still need `allreduce_grads`."""
+    [B,H,Tr,dk], k [B,G,dk,Tr], v [B,G,Tr,dv] and gate-logit slices of its positions ``bounds[rank]:bounds[rank+1]``
+    (equal slices when ``bounds`` is None; see `balanced_query_bounds`).  K and V are all-gathered (their gradients
+    come back reduce-scattered), each rank then runs its query slice against the gathered keys; the compressed
+    keys/values are recomputed from the gathered K/V on every rank (a few percent of the layer's work) instead of being
+    exchanged.  Weight gradients (phi, gate MLP) still need `allreduce_grads`."""
     from .kernels import nsa_layer
     world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
     rank = dist.get_rank(group) if world > 1 else 0
-    Tl = q_local.shape[2]
-    k_full = all_gather_seq(k_local, -1, group)
-    v_full = all_gather_seq(v_local, 2, group)
-    return nsa_layer(q_local, k_full, v_full, gate_logits_local, phi_params, config, q_pos0=rank * Tl, **kw)
+    if bounds is None:
+        sizes, q_pos0 = None, rank * q_local.shape[2]
+    else:
+        sizes, q_pos0 = [bounds[i + 1] - bounds[i] for i in range(world)], bounds[rank]
+    k_full = all_gather_seq(k_local, -1, group, sizes)
+    v_full = all_gather_seq(v_local, 2, group, sizes)
+    return nsa_layer(q_local, k_full, v_full, gate_logits_local, phi_params, config, q_pos0=q_pos0, **kw)

@@ -71,15 +71,34 @@ def _gather_worker(rank, world, port, ret):
         t0, t1 = query_shard(T, world, rank)
         x = full[..., t0:t1].clone().requires_grad_(True)
         y = all_gather_seq(x, -1)
+        # uneven slices (work-balanced long-context split) travel padded
+        bounds = [0, 384, 512]
+        xu = full[..., bounds[rank]:bounds[rank + 1]].clone().requires_grad_(True)
+        yu = all_gather_seq(xu, -1, None, [384, 128])
+        (yu * wgt).sum().backward()
         (y * wgt).sum().backward()
         ok_fwd = torch.equal(y.detach(), full)
         g2 = torch.Generator().manual_seed(9)
         torch.randn(2, 3, T, generator=g2)
         base = torch.randn(2, 3, T, generator=g2)
         want = base * sum(r + 1 for r in range(world))              # gradient summed over the ranks' losses
-        ret[rank] = (ok_fwd, (x.grad - want[..., t0:t1]).abs().max().item(), (t1 - t0) == step)
+        ok_fwd = ok_fwd and torch.equal(yu.detach(), full)
+        err_u = (xu.grad - want[..., bounds[rank]:bounds[rank + 1]]).abs().max().item()
+        ret[rank] = (ok_fwd, max((x.grad - want[..., t0:t1]).abs().max().item(), err_u), (t1 - t0) == step)
     finally:
         dist.destroy_process_group()
+
+
+def test_balanced_query_bounds():
+    from nsa.sharding import balanced_query_bounds
+    b = balanced_query_bounds(65536, 8, 512 + 16 * 64, 16)
+    assert b[0] == 0 and b[-1] == 65536 and all(x % 128 == 0 for x in b) and all(y > x for x, y in zip(b, b[1:]))
+    cost = lambda lo, hi: sum(1536 + t / 16 for t in range(lo, hi, 64)) * 64
+    works = [cost(lo, hi) for lo, hi in zip(b, b[1:])]
+    assert max(works) / min(works) < 1.05          # equal work within the tile rounding
+    assert (b[1] - b[0]) > 2 * (b[-1] - b[-2])     # early slices are much longer than late ones
+    with pytest.raises(ValueError):
+        balanced_query_bounds(256, 4, 100.0, 16)
 
 
 def test_query_shard_bounds():
