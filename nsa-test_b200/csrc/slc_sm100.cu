@@ -1155,7 +1155,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   }
 }
 
-// dK/dV of block `blk` += sum of its segment partials in segment order
+// dK/dV of block `blk` += sum of its segment partials in segment order; a thread owns four consecutive columns of a row
 __global__ void slc_reduce_dkv_kernel(const float* __restrict__ dk_part, const float* __restrict__ dv_part,
                                       const int* __restrict__ csr_off, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
                                       int G, int Tk, int nblk, int nparts, int DK, int DV, float scale) {
@@ -1165,17 +1165,29 @@ __global__ void slc_reduce_dkv_kernel(const float* __restrict__ dk_part, const f
   if (hi <= lo) return;
   const int p_lo = lo / kEntriesPerCta, p_hi = (hi - 1) / kEntriesPerCta;
   const int nseg = nparts + nblk;
-  const int W = DK + DV;
-  for (int i = threadIdx.x; i < 64 * W; i += blockDim.x) {
-    const int r = i / W, c = i % W;
-    float acc = 0.f;
+  const int W4 = (DK + DV) / 4, DK4 = DK / 4;
+  for (int i = threadIdx.x; i < 64 * W4; i += blockDim.x) {
+    const int r = i / W4, c4 = i - r * W4;
+    const bool is_k = c4 < DK4;
+    const int col = is_k ? c4 * 4 : (c4 - DK4) * 4, width = is_k ? DK : DV;
+    const float* part = is_k ? dk_part : dv_part;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int pp = p_lo; pp <= p_hi; ++pp) {
       const int64_t sidx = ((int64_t)bg * nseg + pp + blk) * 64 + r;
-      acc += c < DK ? dk_part[sidx * DK + c] : dv_part[sidx * DV + (c - DK)];
+      const float4 v = *reinterpret_cast<const float4*>(part + sidx * width + col);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
+    const float mul = is_k ? scale : 1.f;
     const int64_t krow = (int64_t)bg * Tk + blk * 64 + r;
-    __nv_bfloat16* dst = c < DK ? dk + krow * DK + c : dv + krow * DV + (c - DK);
-    *dst = __float2bfloat16_rn(__bfloat162float(*dst) + (c < DK ? acc * scale : acc));
+    __nv_bfloat16* dst = (is_k ? dk : dv) + krow * width + col;
+    uint2 raw = *reinterpret_cast<const uint2*>(dst);
+    float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    __nv_bfloat162 o0 = __floats2bfloat162_rn(a0.x + acc.x * mul, a0.y + acc.y * mul);
+    __nv_bfloat162 o1 = __floats2bfloat162_rn(a1.x + acc.z * mul, a1.y + acc.w * mul);
+    raw.x = *reinterpret_cast<uint32_t*>(&o0);
+    raw.y = *reinterpret_cast<uint32_t*>(&o1);
+    *reinterpret_cast<uint2*>(dst) = raw;
   }
 }
 
