@@ -1,0 +1,109 @@
+"""Incremental forward (chunked prefill and single-token decode against a key/value + compressed cache): the rows it
+returns must equal the same rows of the full-sequence forward, and the cache's compressed blocks must equal the
+full-sequence compression."""
+import pytest
+import torch
+
+from tests.util import max_abs
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _inputs(H, G, T, dk, dv, seed):
+    from oracle import nsa_oracle as O
+    inp = O.make_inputs(1, H, G, T, dk, dv, 64, 32, seed=seed, block_offset_std=0.5, dtype=torch.bfloat16)
+    q, k, v = (inp[n].bfloat16().to(DEV) for n in ("q", "k", "v"))
+    g = torch.Generator().manual_seed(seed + 1)
+    logits = torch.randn(1, T, 3 * H, generator=g).to(DEV)
+    phi = tuple(p.to(DEV).float() for p in (inp["phi"].pos_embed, inp["phi"].w1, inp["phi"].b1, inp["phi"].w2,
+                                            inp["phi"].b2))
+    return q, k, v, logits, phi
+
+
+def _cfg(H, G, dk, dv):
+    import nsa
+    return nsa.NSAConfig(d_model=64, head_dim_qk=dk, head_dim_v=dv, l=32, d=16, l_prime=64, n=16, w=512, n_heads=H,
+                         n_kv_groups=G)
+
+
+@pytest.mark.parametrize("dk,dv,H,G,T,chunks", [
+    (64, 64, 8, 2, 2048, [1024, 512, 128, 383, 1]),       # ragged chunks: positions off the 128-row tiles
+    (192, 128, 16, 1, 4096, [3000, 1000, 95, 1]),
+])
+def test_chunks_reproduce_the_full_sequence_rows(dk, dv, H, G, T, chunks):
+    from nsa.kernels import nsa_layer
+    from nsa.incremental import NSACache, nsa_layer_incremental
+    from nsa._lib import lib
+    assert sum(chunks) == T
+    cfg = _cfg(H, G, dk, dv)
+    q, k, v, logits, phi = _inputs(H, G, T, dk, dv, seed=33)
+    with torch.no_grad():
+        out_full, info = nsa_layer(q, k, v, logits, phi, cfg, return_info=True)
+    cache = NSACache(cfg, 1, T, DEV, shared_kv=True)
+    p = 0
+    for Tn in chunks:
+        sl = slice(p, p + Tn)
+        assert cache.append(phi, k[..., sl], v[:, :, sl]) == p
+        # The compressed blocks decide the top-n; take them bit-for-bit from the full run (the cache's own are
+        # checked below) so that this test compares the attention paths and not fp32 GEMM summation orders.
+        nb = cache.n_blocks
+        cache.k_cmp[..., :nb] = info["k_cmp"][..., :nb]
+        cache.k_cmp_lp[..., :nb] = info["k_cmp"][..., :nb].to(cache.dtype)
+        cache.v_cmp[:, :, :nb] = info["v_cmp"][:, :, :nb]
+        out, part = nsa_layer_incremental(q[:, :, sl], logits[:, sl], cache, return_info=True)
+        torch.cuda.synchronize()
+        assert out.shape == (1, H, Tn, dv)
+        assert torch.equal(part["indices"], info["indices"][:, :, sl]), f"selected blocks differ in chunk at {p}"
+        for name in ("o_cmp", "o_slc", "o_win"):
+            assert max_abs(part[name].float(), info[name][:, :, sl].float()) < 2e-2, f"{name} differs in chunk at {p}"
+        assert max_abs(out.float(), out_full[:, :, sl].float()) < 2e-2            # bf16 I/O tolerance
+        p += Tn
+    assert cache.length == T and cache.n_blocks == (T - cfg.l) // cfg.d + 1
+    assert lib.nsa_device_timeouts(0) == 0
+
+
+def test_cache_compresses_the_blocks_each_chunk_completes():
+    from nsa.kernels import nsa_layer
+    from nsa.incremental import NSACache
+    H, G, dk, dv, T = 8, 2, 64, 64, 1024
+    cfg = _cfg(H, G, dk, dv)
+    q, k, v, logits, phi = _inputs(H, G, T, dk, dv, seed=34)
+    with torch.no_grad():
+        _, info = nsa_layer(q, k, v, logits, phi, cfg, return_info=True)
+    cache = NSACache(cfg, 1, T, DEV, shared_kv=True)
+    p = 0
+    for Tn in [20, 11, 1, 200, 7, 16, 1, 768]:            # the first two chunks complete no block
+        cache.append(phi, k[..., p:p + Tn], v[:, :, p:p + Tn])
+        p += Tn
+        assert cache.n_blocks == ((p - cfg.l) // cfg.d + 1 if p >= cfg.l else 0)
+    nb = cache.n_blocks
+    assert nb == (T - cfg.l) // cfg.d + 1
+    ref = info["k_cmp"][..., :nb]
+    assert max_abs(cache.k_cmp[..., :nb], ref) < 1e-3 * max(1.0, ref.abs().max().item())   # fp32 GEMMs, other shapes
+    assert max_abs(cache.v_cmp[:, :, :nb].float(), info["v_cmp"][:, :, :nb].float()) < 1e-2
+    assert torch.equal(cache.block_ends[:nb], info["block_ends"][:nb])
+    assert (cache.block_ends[nb:] == 999999).all()
+
+
+def test_module_decodes_token_by_token():
+    import nsa
+    from nsa.incremental import NSACache, module_forward_incremental
+    torch.manual_seed(5)
+    cfg = nsa.NSAConfig(d_model=256, head_dim_qk=64, head_dim_v=64, l=32, d=16, l_prime=64, n=16, w=512, n_heads=8,
+                        n_kv_groups=2)
+    m = nsa.NSAAttention(cfg).to(DEV).bfloat16().eval()
+    T, prefill = 1024, 1000
+    x = torch.randn(1, T, 256, device=DEV).bfloat16()
+    with torch.no_grad():
+        y_full, _ = m(x)
+        cache = NSACache(cfg, 1, T, DEV, shared_kv=False)
+        ys = [module_forward_incremental(m, x[:, :prefill], cache)]
+        for t in range(prefill, T):
+            ys.append(module_forward_incremental(m, x[:, t:t + 1], cache))
+    y = torch.cat(ys, dim=1)
+    err = (y.float() - y_full.float()).abs().amax(dim=-1).flatten()
+    # The cache compresses with differently shaped fp32 GEMMs, so a near-tie in the top-n can pick another block
+    # for a few rows; everything else has to agree within the bf16 tolerance.
+    assert (err < 2e-2).float().mean().item() > 0.98, f"only {(err < 2e-2).float().mean().item():.3f} of rows agree"
+    assert err.median().item() < 5e-3
