@@ -127,7 +127,7 @@ def make_device_inputs(T, dev, seed, B=1):
     return dict(q=q, k=k, v=v, do=do, x=x), params
 
 
-def layer_step(inp, params, cfg, world):
+def layer_step(inp, params, cfg, world, before_backward=None):
     """One forward + backward of the layer; returns a scalar tensor summarising the result."""
     from nsa.kernels import nsa_layer
     lin = torch.nn.functional.linear
@@ -138,6 +138,8 @@ def layer_step(inp, params, cfg, world):
     phi = (params["pos_embed"], params["w1"], params["b1"], params["w2"], params["b2"])
     out = nsa_layer(q, k, v, logits, phi, cfg)
     plist = list(params.values())
+    if before_backward is not None:
+        before_backward()           # the upstream gradient is first needed here
     grads = torch.autograd.grad(out, [q, k, v] + plist, inp["do"])
     if world > 1:
         from nsa.sharding import allreduce_grads
@@ -145,7 +147,7 @@ def layer_step(inp, params, cfg, world):
     return out[0, 0, -1, :8].float().sum() + grads[0][0, 0, -1, :8].float().sum()
 
 
-def layer_step_query_sharded(inp, params, cfg, world):
+def layer_step_query_sharded(inp, params, cfg, world, before_backward=None):
     """Long-context mode: `inp` holds this rank's slice of the positions; K/V are all-gathered inside the layer and
     their gradients come back reduce-scattered (nsa.sharding.query_sharded_layer)."""
     from nsa.sharding import allreduce_grads, query_sharded_layer
@@ -158,6 +160,8 @@ def layer_step_query_sharded(inp, params, cfg, world):
     phi = (params["pos_embed"], params["w1"], params["b1"], params["w2"], params["b2"])
     out = query_sharded_layer(q, k, v, logits, phi, cfg, bounds=bounds)
     plist = list(params.values())
+    if before_backward is not None:
+        before_backward()           # the upstream gradient is first needed here
     grads = torch.autograd.grad(out, [q, k, v] + plist, inp["do"])
     if world > 1:
         allreduce_grads(grads[3:])
@@ -322,16 +326,20 @@ def main():
     # data loader would feed the layer.  Every step's inputs are copied, and its result read back, inside the timed region.
     copy_stream = torch.cuda.Stream(device=dev)
     slots = [{k_: (torch.empty_like(v_) if torch.is_tensor(v_) else v_) for k_, v_ in inp.items()} for _ in range(2)]
-    copied = [torch.cuda.Event() for _ in range(2)]
+    copied_fwd = [torch.cuda.Event() for _ in range(2)]     # q, k, v, x of the slot have landed
+    copied_all = [torch.cuda.Event() for _ in range(2)]     # ... and the upstream gradient dO, first used by the backward
     consumed = [torch.cuda.Event() for _ in range(2)]
+    fwd_names = [k_ for k_ in host if k_ != "do"]
 
     def upload(i):
         with torch.cuda.stream(copy_stream):
             if i >= 2:
                 copy_stream.wait_event(consumed[i % 2])
-            for k_, v_ in host.items():
-                slots[i % 2][k_].copy_(v_, non_blocking=True)
-            copied[i % 2].record(copy_stream)
+            for k_ in fwd_names:
+                slots[i % 2][k_].copy_(host[k_], non_blocking=True)
+            copied_fwd[i % 2].record(copy_stream)
+            slots[i % 2]["do"].copy_(host["do"], non_blocking=True)
+            copied_all[i % 2].record(copy_stream)
 
     def e2e_run(n):
         cur = torch.cuda.current_stream()
@@ -339,15 +347,17 @@ def main():
         for i in range(n):
             if i + 1 < n:
                 upload(i + 1)
-            cur.wait_event(copied[i % 2])
-            res = step_fn(slots[i % 2], params, cfg, world)
+            cur.wait_event(copied_fwd[i % 2])
+            res = step_fn(slots[i % 2], params, cfg, world, before_backward=lambda: cur.wait_event(copied_all[i % 2]))
             res_host.copy_(res.reshape(1), non_blocking=True)
             consumed[i % 2].record(cur)
         cur.synchronize()
 
     e2e_run(1)
     barrier()
-    e2e_steps = max(1, args.steps)
+    # The first step's copy has nothing to hide behind (pipeline fill) and is inside the timed region; the run is long
+    # enough that the figure is the sustained rate of the double-buffered loop rather than of its first step.
+    e2e_steps = max(20, args.steps)
     e0.record()
     e2e_run(e2e_steps)
     e1.record()
@@ -395,7 +405,7 @@ def main():
                                           if query_mode else f"NSA layer fwd+bwd, one sequence per GPU, T={T}"),
                                 l2="inputs (>= 1.6 GB per tensor) exceed the 126 MB L2",
                                 parallelism=f"sp{world}" if query_mode else f"dp{world}", **c),
-                    e2e=dict(value=round(e2e_value, 1), unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=4),
+                    e2e=dict(value=round(e2e_value, 1), unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=4, steps=e2e_steps),
                     gpu_launches=launches * args.steps, roofline=roofline, cpu_baseline=cpu, clocks=clocks,
                     attention_tflops_per_s=round(att_total / (ms_per_step * 1e-3) / 1e12, 1),
                     attention_frac_of_peak=round(att_total / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"] / (world if query_mode else 1), 4),

@@ -19,7 +19,7 @@ from typing import Optional
 import torch
 
 from . import ops
-from .kernels import NSAConfig, PAD_BLOCK_END, _PhiCompress, _next_pow2, _selection_fallback
+from .kernels import NSAConfig, PAD_BLOCK_END, _PhiCompress, _next_pow2, _project_heads, _selection_fallback
 
 __all__ = ["NSACache", "nsa_layer_incremental", "module_forward_incremental"]
 
@@ -161,10 +161,10 @@ def module_forward_incremental(module, hidden_new: torch.Tensor, cache: NSACache
     c = module.config
     B, Tn, _ = hidden_new.shape
     H, G, dk, dv = c.n_heads, c.n_kv_groups, c.head_dim_qk, c.head_dim_v
-    q = module.q_proj(hidden_new).view(B, Tn, H, dk).transpose(1, 2).contiguous()
+    q = _project_heads(hidden_new, module.q_proj, H, dk)
 
     def kv(kp, vp):
-        return (kp(hidden_new).view(B, Tn, G, dk).permute(0, 2, 3, 1), vp(hidden_new).view(B, Tn, G, dv).transpose(1, 2))
+        return _project_heads(hidden_new, kp, G, dk, transposed=True), _project_heads(hidden_new, vp, G, dv)
 
     k_sel, v_sel = kv(module.k_select, module.v_select)
     cache.append(module._phi_params(), k_sel, v_sel, kv_compress=kv(module.k_compress, module.v_compress),

@@ -308,6 +308,20 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
 # module (nsa/kernels.py:2043-2507)
 # --------------------------------------------------------------------------------------------------
 
+def _project_heads(x: torch.Tensor, linear: torch.nn.Linear, heads: int, dim: int, transposed: bool = False):
+    """``linear(x)`` of x [B,T,d_model] written by the GEMM itself in the kernels' layout: [B,heads,T,dim], or
+    [B,heads,dim,T] when ``transposed`` (keys).  The reference projects to [B,T,heads*dim] and then copies into these
+    layouts (``transpose().contiguous()``, nsa/kernels.py:2361-2364).  Keys come out of one GEMM W x^T per batch
+    element; queries and values out of a GEMM batched over the heads, with x shared by a zero batch stride."""
+    w, b = linear.weight, linear.bias
+    if transposed:
+        y = torch.matmul(w, x.transpose(1, 2)).view(x.shape[0], heads, dim, x.shape[1])          # [B,heads,dim,T]
+        return y if b is None else y + b.view(heads, dim, 1)
+    wt = w.view(heads, dim, -1).transpose(1, 2)                                                  # [heads,d_model,dim]
+    y = torch.stack([torch.matmul(xb, wt) for xb in x]) if x.shape[0] > 1 else torch.matmul(x[0], wt).unsqueeze(0)
+    return y if b is None else y + b.view(heads, 1, dim)
+
+
 class NSAAttention(torch.nn.Module):
     """Drop-in for the reference's ``NSAAttention``: same parameter names (so its state_dicts load),
     same ``forward(hidden_states, attention_mask=None, output_attentions=False) -> (out, info)``."""
@@ -354,12 +368,11 @@ class NSAAttention(torch.nn.Module):
         c = self.config
         B, T, _ = hidden_states.shape
         H, G, dk, dv = c.n_heads, c.n_kv_groups, c.head_dim_qk, c.head_dim_v
-        q = self.q_proj(hidden_states).view(B, T, H, dk).transpose(1, 2).contiguous()           # [B,H,T,dk]
+        q = _project_heads(hidden_states, self.q_proj, H, dk)                                    # [B,H,T,dk]
 
         def kv(kp, vp):
-            k = kp(hidden_states).view(B, T, G, dk).permute(0, 2, 3, 1).contiguous()             # [B,G,dk,T]
-            v = vp(hidden_states).view(B, T, G, dv).transpose(1, 2).contiguous()                 # [B,G,T,dv]
-            return k, v
+            return (_project_heads(hidden_states, kp, G, dk, transposed=True),                   # [B,G,dk,T]
+                    _project_heads(hidden_states, vp, G, dv))                                    # [B,G,T,dv]
 
         k_sel, v_sel = kv(self.k_select, self.v_select)
         gate_logits = self.gate_mlp(hidden_states)                                               # [B,T,3H]
