@@ -225,8 +225,19 @@ class _PhiCompress(torch.autograd.Function):
         dhbar = torch.matmul(dkc, w2.float())                                       # [B,G,nb,U]
         da, dc, dvals = ops.phi_pool_bwd(a, c, dhbar, dv_cmp, l, d, nb)
         w1k, w1p = w1[:, :dk].float(), w1[:, dk:].float()
-        dkeys = torch.matmul(da, w1k)                                               # [B,G,T,dk]
-        dw1k = da.reshape(-1, U).t() @ keys.float().reshape(-1, dk)
+        if keys.dtype in (torch.bfloat16, torch.float16):
+            # The key gradient leaves in the I/O precision anyway, so these two products run on the tensor cores
+            # from da rounded to it (fp32 accumulation, fp32 weight gradient).  The forward product stays fp32:
+            # it decides the top-n.  keys usually is the transposed view of K [B,G,dk,T], used as it lies.
+            da_lp = da.to(keys.dtype)
+            dkeys = torch.matmul(da_lp, w1k.to(keys.dtype))                         # [B,G,T,dk]
+            kt = keys.transpose(-1, -2)
+            kt = kt if kt.is_contiguous() else kt.contiguous()
+            dw1k = torch.bmm(kt.reshape(B * G, dk, T), da_lp.reshape(B * G, T, U),
+                             out_dtype=torch.float32).sum(0).t()                    # [U,dk]
+        else:
+            dkeys = torch.matmul(da, w1k)                                           # [B,G,T,dk]
+            dw1k = da.reshape(-1, U).t() @ keys.float().reshape(-1, dk)
         dw1p = dc.t() @ pos_embed.float()
         dpos = dc @ w1p
         dw1 = torch.cat([dw1k, dw1p], dim=1)
