@@ -255,6 +255,7 @@ def main():
     ap.add_argument("--T", type=int, default=65536)
     ap.add_argument("--cpu-sample", type=int, default=4096, help="sequence length of the CPU-oracle sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end leg (default: max(20, --steps))")
     ap.add_argument("--shard", default="sequence", choices=["sequence", "query"],
                     help="sequence: one T-token sequence per GPU (weak scaling, the default); query: ONE T-token sequence "
                          "split by position over the GPUs, K/V all-gathered (long-context mode, strong scaling)")
@@ -357,7 +358,7 @@ def main():
     barrier()
     # The first step's copy has nothing to hide behind (pipeline fill) and is inside the timed region; the run is long
     # enough that the figure is the sustained rate of the double-buffered loop rather than of its first step.
-    e2e_steps = max(20, args.steps)
+    e2e_steps = args.e2e_steps if args.e2e_steps > 0 else max(20, args.steps)
     e0.record()
     e2e_run(e2e_steps)
     e1.record()
