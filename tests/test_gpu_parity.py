@@ -456,3 +456,34 @@ def test_cpu_tensors_are_rejected(nsa_mod):
     from nsa import ops
     with pytest.raises(RuntimeError):
         ops.sliding_fwd(torch.zeros(1, 2, 4, 8), torch.zeros(1, 1, 8, 4), torch.zeros(1, 1, 4, 8), 2, 1.0)
+
+
+@pytest.mark.parametrize("T,dk,dv,H,G,n,w,include_fixed,gate_mode", [
+    (777, 96, 80, 6, 3, 5, 100, True, "sigmoid"),       # ragged T (padded-block n_sel), head dims off the tile sizes
+    (333, 64, 64, 4, 2, 3, 50, False, "softmax"),       # no forced blocks, softmax gates
+    (40, 32, 48, 2, 1, 16, 512, True, "sigmoid"),       # barely one compression block, window and n beyond T
+])
+def test_layer_fp32_odd_shapes(nsa_mod, T, dk, dv, H, G, n, w, include_fixed, gate_mode):
+    """The generic kernels on shapes off every tile size, against the oracle layer (fp32)."""
+    c = dict(B=2, H=H, G=G, T=T, dk=dk, dv=dv, d_model=48, l=32, d=16, l_prime=64, n=n, w=w, seed=41)
+    inp = O.make_inputs(c["B"], H, G, T, dk, dv, c["d_model"], c["l"], seed=c["seed"], block_offset_std=0.5)
+    from nsa.kernels import nsa_layer
+    cfg = _cfg(nsa_mod, c, gate_mode=gate_mode, include_fixed_in_selection=include_fixed)
+    q, k, v = (_dev(inp[x], torch.float32, True) for x in ("q", "k", "v"))
+    phi, gp = inp["phi"], inp["gate"]
+    params = [_dev(p, grad=True) for p in (phi.pos_embed, phi.w1, phi.b1, phi.w2, phi.b2, gp.w1, gp.b1, gp.w2, gp.b2)]
+    lin = torch.nn.functional.linear
+    logits = lin(torch.relu(lin(_dev(inp["x"]), params[5], params[6])), params[7], params[8])
+    out, info = nsa_layer(q, k, v, logits, tuple(params[:5]), cfg, return_info=True)
+    grads = torch.autograd.grad(out, [q, k, v], _dev(inp["do"]))
+    qo, ko, vo = (inp[x].clone().requires_grad_(True) for x in ("q", "k", "v"))
+    r = O.nsa_layer(qo, ko, vo, inp["x"], phi, gp, l=c["l"], d=c["d"], l_prime=c["l_prime"], n=n, w=w,
+                    include_fixed=include_fixed, gate_mode=gate_mode)
+    gref = torch.autograd.grad(r["out"], [qo, ko, vo], inp["do"])
+    agg = r["sel_scores"].view(c["B"], G, H // G, T, -1).sum(2)
+    mism = (info["indices"].cpu().long() != r["indices"]).any(-1)
+    assert not (mism & ~ambiguous_rows(agg, n)).any(), "selected block ids differ from the oracle"
+    if not mism.any():
+        assert rel_err(out, r["out"]) < 1e-3
+        for nme, a, b in zip(("dq", "dk", "dv"), grads, gref):
+            assert rel_err(a, b) < 1e-3, nme
