@@ -31,6 +31,8 @@ __all__ = [
 ]
 
 PAD_BLOCK_END = 999999  # block end of the padding blocks (nsa/kernels.py:2190)
+_TILE_ROWS = 128         # query/key rows per tile of the tensor-core kernels
+_PAD_FROM = 2048         # ragged bf16 sequences at least this long are padded to a whole tile
 
 
 def _next_pow2(n: int) -> int:
@@ -294,6 +296,32 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
     """
     cfg = config
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    T_in = q.shape[2]
+    if (q.dtype == torch.bfloat16 and q_pos0 == 0 and T_in % _TILE_ROWS and T_in >= _PAD_FROM
+            and k_slc.shape[-1] == T_in):
+        # The tensor-core kernels work on 128-row tiles; a long ragged sequence is padded with zero tokens to the next
+        # tile instead of falling to the generic kernels.  The pad sits after every real token, so causality hides it:
+        # real queries never see a pad key, a compressed block that reaches into the pad ends after the last real
+        # query, and with T >= 2048 there are more selection blocks than slots, so the indices of the real rows do
+        # not depend on the padded block count.  The pad rows are computed and dropped; autograd slices the gradients.
+        pad = _TILE_ROWS - T_in % _TILE_ROWS
+        F = torch.nn.functional
+        pk = lambda kv: None if kv is None else (F.pad(kv[0], (0, pad)), F.pad(kv[1], (0, 0, 0, pad)))
+        res = nsa_layer(F.pad(q, (0, 0, 0, pad)), *pk((k_slc, v_slc)), F.pad(gate_logits, (0, 0, 0, pad)), phi_params,
+                        config, kv_compress=pk(kv_compress), kv_sliding=pk(kv_sliding), scale=scale,
+                        return_info=return_info)
+        if not return_info:
+            return res[:, :, :T_in]
+        out, info = res
+        rows = ("indices", "gates", "o_cmp", "o_slc", "o_win")
+        info = {k_: (v_[:, :, :T_in] if k_ in rows else v_) for k_, v_ in info.items()}
+        # compressed blocks as the unpadded sequence has them: its block count, its power-of-two padding
+        nb = (T_in - cfg.l) // cfg.d + 1
+        nbp = _next_pow2(nb)
+        info["k_cmp"], info["v_cmp"] = info["k_cmp"][..., :nbp], info["v_cmp"][:, :, :nbp]
+        info["block_ends"] = info["block_ends"][:nbp].clone()
+        info["block_ends"][nb:] = PAD_BLOCK_END
+        return out[:, :, :T_in], info
     kc_src, vc_src = kv_compress if kv_compress is not None else (k_slc, v_slc)
     kw, vw = kv_sliding if kv_sliding is not None else (k_slc, v_slc)
     T = kc_src.shape[-1]   # sequence length covered by the keys (== query rows unless q_pos0 shards the queries)

@@ -296,3 +296,46 @@ def test_score_topn_tensorcore_bit_exact_outside_ambiguity(dk, H, G, T):
     assert (tc != ref).any(-1).float().mean() < 0.01 and (gen != ref).any(-1).float().mean() < 0.01
     # early rows: forced blocks first, never-visible blocks listed in id order, -1 padding only when blocks run out
     assert tc[0, 0, 0].tolist()[:3] == [0, 1, 2] and (tc >= -1).all() and (tc < (T + lp - 1) // lp).all()
+
+
+def test_ragged_bf16_sequence_runs_on_padded_tiles():
+    """A long bf16 sequence whose length is no multiple of the 128-row tile is padded inside nsa_layer and runs on the
+    tensor-core kernels; rows, indices and gradients are those of the unpadded sequence (oracle, bf16 tolerance)."""
+    import nsa
+    from nsa.kernels import nsa_layer
+    from nsa._lib import lib
+    from tests.util import ambiguous_rows, oracle_layer_with_grads
+    c = dict(B=1, H=4, G=2, T=2048 + 77, dk=64, dv=64, d_model=32, l=32, d=16, l_prime=64, n=16, w=512)
+    inp = O.make_inputs(c["B"], c["H"], c["G"], c["T"], c["dk"], c["dv"], c["d_model"], c["l"], seed=17,
+                        block_offset_std=0.5, dtype=torch.bfloat16)
+    cfg = nsa.NSAConfig(d_model=c["d_model"], head_dim_qk=c["dk"], head_dim_v=c["dv"], l=c["l"], d=c["d"],
+                        l_prime=c["l_prime"], n=c["n"], w=c["w"], n_heads=c["H"], n_kv_groups=c["G"])
+    q, k, v = (inp[x].bfloat16().to(DEV).requires_grad_(True) for x in ("q", "k", "v"))
+    phi, gp = inp["phi"], inp["gate"]
+    params = [p.to(DEV).requires_grad_(True) for p in (phi.pos_embed, phi.w1, phi.b1, phi.w2, phi.b2)]
+    lin = torch.nn.functional.linear
+    xg = inp["x"].to(DEV)
+    logits = lin(torch.relu(lin(xg, gp.w1.to(DEV), gp.b1.to(DEV))), gp.w2.to(DEV), gp.b2.to(DEV))
+    lib.nsa_profile_enable(1)
+    out, info = nsa_layer(q, k, v, logits, tuple(params), cfg, return_info=True)
+    grads = torch.autograd.grad(out, [q, k, v], inp["do"].bfloat16().to(DEV))
+    import ctypes
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.nsa_profile_report(buf, 1 << 16)
+    lib.nsa_profile_enable(0)
+    launched = buf.value.decode()
+    assert "slc_bwd_fused" in launched and "score_topn_tc" in launched, launched    # the tensor-core path ran
+    _no_timeouts()
+    T = c["T"]
+    assert out.shape == (1, c["H"], T, c["dv"]) and info["indices"].shape[2] == T and grads[1].shape == k.shape
+    nb = (T - c["l"]) // c["d"] + 1
+    assert info["k_cmp"].shape[-1] == O.next_pow2(nb) and int(info["block_ends"][nb - 1]) == (nb - 1) * c["d"] + c["l"] - 1
+    assert (info["block_ends"][nb:] == 999999).all()
+    r, gref = oracle_layer_with_grads(inp, c)
+    agg = r["sel_scores"].view(1, c["G"], c["H"] // c["G"], T, -1).sum(2)
+    mism = (info["indices"].cpu().long() != r["indices"]).any(-1)
+    assert not (mism & ~ambiguous_rows(agg, c["n"])).any()
+    if not mism.any():
+        assert max_abs(out.float(), r["out"]) < 2e-2
+        for a, b in zip(grads, gref[:3]):
+            assert max_abs(a.float(), b) < 2e-2 * max(1.0, b.abs().max().item())
