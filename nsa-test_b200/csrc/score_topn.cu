@@ -82,66 +82,81 @@ __device__ void topn_and_merge(float* agg, int n_sel, int t, int l_prime, int n,
   }
 }
 
-template <typename T>
+// HB heads share one sweep over the compressed keys (each key element is loaded once per HB heads); the softmax
+// and the Eq. 9 sums then run head by head in head order, so the result does not depend on HB.
+template <typename T, int HB>
 __global__ void __launch_bounds__(kThreads)
 score_topn_kernel(const T* __restrict__ q, int64_t sqz, int64_t sqh, int64_t sqm, int64_t sqk,
                   const float* __restrict__ kc, const int* __restrict__ block_ends, int32_t* __restrict__ out, int H,
                   int G, int T_, int dk, int nbp, int a_, int s_, int n_sel, int l_prime, int n, int n_fixed,
-                  float scale) {
+                  float scale, int q0) {
   extern __shared__ float sm[];
-  const int t = blockIdx.x, bg = blockIdx.y, b = bg / G, g = bg % G, hpg = H / G;
+  const int tq = blockIdx.x, bg = blockIdx.y, b = bg / G, g = bg % G, hpg = H / G;
+  const int t = q0 + tq;                // position of query row tq
+  const int pstride = nbp + a_ + s_;
   float* qs = sm;                       // [hpg][dk]
-  float* p = qs + hpg * dk;             // [nbp + a_ + s_]
-  float* agg = p + nbp + a_ + s_;       // [n_sel]
+  float* p = qs + hpg * dk;             // [HB][nbp + a_ + s_]
+  float* agg = p + HB * pstride;        // [n_sel]
   float* redv = agg + n_sel;            // [8]
   int* redi = (int*)(redv + 8);         // [8]
   int* top = redi + 8;                  // [kMaxN]
   for (int i = threadIdx.x; i < hpg * dk; i += kThreads) {
     const int hh = i / dk, d = i % dk;
-    qs[i] = Elem<T>::ld(q + b * sqz + (int64_t)(g * hpg + hh) * sqh + (int64_t)t * sqm + d * sqk);
+    qs[i] = Elem<T>::ld(q + b * sqz + (int64_t)(g * hpg + hh) * sqh + (int64_t)tq * sqm + d * sqk);
   }
   for (int j = threadIdx.x; j < n_sel; j += kThreads) agg[j] = 0.f;
-  for (int i = nbp + threadIdx.x; i < nbp + a_ + s_; i += kThreads) p[i] = 0.f;
+  for (int u = 0; u < HB; ++u)
+    for (int i = nbp + threadIdx.x; i < pstride; i += kThreads) p[u * pstride + i] = 0.f;
   __syncthreads();
   const float* kb = kc + (int64_t)bg * dk * nbp;
-  for (int hh = 0; hh < hpg; ++hh) {
-    const float* qh = qs + hh * dk;
-    float mx = -CUDART_INF_F;
+  for (int h0 = 0; h0 < hpg; h0 += HB) {
     for (int i = threadIdx.x; i < nbp; i += kThreads) {
-      float s = -CUDART_INF_F;
-      if (block_ends[i] <= t) {
-        float acc = 0.f;
-        for (int d = 0; d < dk; ++d) acc = fmaf(qh[d], kb[(int64_t)d * nbp + i], acc);
-        s = acc * scale;
+      float acc[HB];
+#pragma unroll
+      for (int u = 0; u < HB; ++u) acc[u] = 0.f;
+      const bool vis = block_ends[i] <= t;
+      if (vis) {
+#pragma unroll 8
+        for (int d = 0; d < dk; ++d) {
+          const float kv = __ldg(kb + (int64_t)d * nbp + i);
+#pragma unroll
+          for (int u = 0; u < HB; ++u) acc[u] = fmaf(qs[(h0 + u) * dk + d], kv, acc[u]);
+        }
       }
-      p[i] = s;
-      mx = fmaxf(mx, s);
-    }
-    mx = block_max(mx, redv);
-    if (mx == -CUDART_INF_F) {  // nothing visible: block 0 alone
-      for (int i = threadIdx.x; i < nbp; i += kThreads) p[i] = i == 0 ? 1.f : 0.f;
-    } else {
-      float sum = 0.f;
-      for (int i = threadIdx.x; i < nbp; i += kThreads) {
-        const float e = expf(p[i] - mx);  // exp(-inf) = 0 for hidden blocks
-        p[i] = e;
-        sum += e;
-      }
-      sum = block_sum(sum, redv);
-      const float inv = 1.f / sum;
-      for (int i = threadIdx.x; i < nbp; i += kThreads) p[i] *= inv;
+#pragma unroll
+      for (int u = 0; u < HB; ++u) p[u * pstride + i] = vis ? acc[u] * scale : -CUDART_INF_F;
     }
     __syncthreads();
-    for (int j = threadIdx.x; j < n_sel; j += kThreads) {
-      float sel = 0.f;
-      for (int m = 0; m < s_; ++m)
-        for (int nn = 0; nn < a_; ++nn) sel += p[s_ * j + m + nn];  // zero padding stands for skipped terms
-      agg[j] += sel;
+    for (int u = 0; u < HB; ++u) {
+      float* ph = p + u * pstride;
+      float mx = -CUDART_INF_F;
+      for (int i = threadIdx.x; i < nbp; i += kThreads) mx = fmaxf(mx, ph[i]);
+      mx = block_max(mx, redv);
+      if (mx == -CUDART_INF_F) {  // nothing visible: block 0 alone
+        for (int i = threadIdx.x; i < nbp; i += kThreads) ph[i] = i == 0 ? 1.f : 0.f;
+      } else {
+        float sum = 0.f;
+        for (int i = threadIdx.x; i < nbp; i += kThreads) {
+          const float e = expf(ph[i] - mx);  // exp(-inf) = 0 for hidden blocks
+          ph[i] = e;
+          sum += e;
+        }
+        sum = block_sum(sum, redv);
+        const float inv = 1.f / sum;
+        for (int i = threadIdx.x; i < nbp; i += kThreads) ph[i] *= inv;
+      }
+      __syncthreads();
+      for (int j = threadIdx.x; j < n_sel; j += kThreads) {
+        float sel = 0.f;
+        for (int m = 0; m < s_; ++m)
+          for (int nn = 0; nn < a_; ++nn) sel += ph[s_ * j + m + nn];  // zero padding stands for skipped terms
+        agg[j] += sel;
+      }
+      __syncthreads();
     }
-    __syncthreads();
   }
   topn_and_merge(agg, n_sel, t, l_prime, n, n_fixed, top, redv, redi,
-                 out + ((int64_t)bg * T_ + t) * n);
+                 out + ((int64_t)bg * T_ + tq) * n);
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -194,31 +209,34 @@ extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const fl
   if (B > 0 && T > 0 && score_tc_ok(q, qs, B, H, G, T, dk, nbp, l, d, l_prime, n, n_real_blocks, dtype))
     return score_topn_sm100(q, k_cmp, indices_out, B, H, G, T, dk, nbp, l, d, l_prime, n_real_blocks, n, n_fixed, scale,
                             nsa::query_pos0(), workspace, workspace_bytes, (cudaStream_t)stream);
-  NSA_REQUIRE(nsa::query_pos0() == 0, "score_topn: a query offset (nsa_set_query_offset) needs the bf16 tensor-core path of this call");
   NSA_REQUIRE(G > 0 && H % G == 0 && d > 0 && l % d == 0 && l_prime % d == 0 && l > 0 && l_prime > 0,
               "score_topn: bad block parameters");
   NSA_REQUIRE(n > 0 && n <= kMaxN, "score_topn: n=%d outside 1..%d", n, kMaxN);
   NSA_REQUIRE(nbp > 0, "score_topn: no compressed blocks");
   if (B * G == 0 || T == 0) return NSA_OK;
   const int a_ = l / d, s_ = l_prime / d, n_sel = (nbp + s_ - 1) / s_, hpg = H / G;
-  const size_t sm = ((size_t)hpg * dk + nbp + a_ + s_ + n_sel + 16 + kMaxN) * sizeof(float);
+  auto smem_for = [&](int hb) { return ((size_t)hpg * dk + (size_t)hb * (nbp + a_ + s_) + n_sel + 16 + kMaxN) * sizeof(float); };
+  const int hb = (hpg % 4 == 0 && smem_for(4) <= 160 * 1024) ? 4 : (hpg % 2 == 0 && smem_for(2) <= 160 * 1024) ? 2 : 1;
+  const size_t sm = smem_for(hb);
   if (sm > 200 * 1024) return fail(NSA_ERR_UNSUPPORTED, "score_topn: %zu bytes of shared memory needed", sm);
+  if (dtype != NSA_F32 && dtype != NSA_BF16) return fail(NSA_ERR_ARG, "score_topn: unsupported dtype %d", dtype);
   cudaStream_t st = (cudaStream_t)stream;
   KernelTimer kt("score_topn", st);
   dim3 grid(T, B * G);
+  const int q0 = nsa::query_pos0();
+#define NSA_SCORE_LAUNCH(TYPE, HB_)                                                                                    \
+  do {                                                                                                                 \
+    cudaFuncSetAttribute(score_topn_kernel<TYPE, HB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);          \
+    score_topn_kernel<TYPE, HB_><<<grid, kThreads, sm, st>>>((const TYPE*)q, qs[0], qs[1], qs[2], qs[3], k_cmp,        \
+                                                             block_ends, indices_out, H, G, T, dk, nbp, a_, s_, n_sel, \
+                                                             l_prime, n, n_fixed, scale, q0);                          \
+  } while (0)
   if (dtype == NSA_F32) {
-    cudaFuncSetAttribute(score_topn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    score_topn_kernel<float><<<grid, kThreads, sm, st>>>((const float*)q, qs[0], qs[1], qs[2], qs[3], k_cmp, block_ends,
-                                                          indices_out, H, G, T, dk, nbp, a_, s_, n_sel, l_prime, n,
-                                                          n_fixed, scale);
-  } else if (dtype == NSA_BF16) {
-    cudaFuncSetAttribute(score_topn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    score_topn_kernel<__nv_bfloat16><<<grid, kThreads, sm, st>>>((const __nv_bfloat16*)q, qs[0], qs[1], qs[2], qs[3],
-                                                                  k_cmp, block_ends, indices_out, H, G, T, dk, nbp, a_,
-                                                                  s_, n_sel, l_prime, n, n_fixed, scale);
+    if (hb == 4) NSA_SCORE_LAUNCH(float, 4); else if (hb == 2) NSA_SCORE_LAUNCH(float, 2); else NSA_SCORE_LAUNCH(float, 1);
   } else {
-    return fail(NSA_ERR_ARG, "score_topn: unsupported dtype %d", dtype);
+    if (hb == 4) NSA_SCORE_LAUNCH(__nv_bfloat16, 4); else if (hb == 2) NSA_SCORE_LAUNCH(__nv_bfloat16, 2); else NSA_SCORE_LAUNCH(__nv_bfloat16, 1);
   }
+#undef NSA_SCORE_LAUNCH
   return check_launch("score_topn");
 }
 

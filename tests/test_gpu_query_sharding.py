@@ -56,3 +56,25 @@ def test_query_slices_match_the_unsharded_layer(dk, dv, H, G, T, world):
     for name, a, b in zip(("dk", "dv", "dpos", "dw1", "db1", "dw2", "db2"), sums, g_full[1:]):
         scale = max(1.0, b.abs().max().item())
         assert max_abs(a, b) < 3e-2 * scale, f"{name}: sharded sum differs by {max_abs(a, b)} (scale {scale})"
+
+
+def test_generic_scoring_kernel_honours_the_query_offset():
+    """fp32 tensors take the row-per-CTA scoring kernel: a query slice with its position offset selects the same blocks
+    as the same rows of the whole sequence."""
+    from nsa import ops
+    from oracle import nsa_oracle as O
+    B, H, G, T, dk, l, d, lp, n = 2, 6, 3, 600, 48, 32, 16, 64, 5
+    gen = torch.Generator().manual_seed(3)
+    q = torch.randn(B, H, T, dk, generator=gen).to(DEV)
+    nb = (T - l) // d + 1
+    nbp = O.next_pow2(nb)
+    kc = torch.zeros(B, G, dk, nbp)
+    kc[..., :nb] = torch.randn(B, G, dk, nb, generator=gen)
+    kc = kc.to(DEV)
+    be = torch.full((nbp,), 999999, dtype=torch.int32)
+    be[:nb] = torch.arange(nb, dtype=torch.int32) * d + l - 1
+    be = be.to(DEV)
+    full = ops.score_topn(q, kc, be, l, d, lp, n, 3, dk ** -0.5)
+    for lo, hi in ((0, 100), (100, 357), (357, 600)):
+        part = ops.score_topn(q[:, :, lo:hi].contiguous(), kc, be, l, d, lp, n, 3, dk ** -0.5, -1, lo)
+        assert torch.equal(part, full[:, :, lo:hi]), f"rows {lo}:{hi}"
