@@ -13,6 +13,7 @@
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i = bf16 pairs in S_i[0,64).
 // Issue order PV0(j) QK0(j+1) PV1(j) QK1(j+1) keeps the tensor pipe busy while the other tile's
 // softmax runs.  All waits are bounded; a timeout raises a device flag readable from the host.
+#include <algorithm>
 #include <cuda.h>
 
 #include "attn_args.cuh"
@@ -47,7 +48,7 @@ struct FaSmem {
 };
 
 struct FaBarriers {
-  uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full[2], pv_done[2];
+  uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full[2], pv_done[2], o_free[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -80,28 +81,40 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hpg = p.H / p.G;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) query tiles first
-  const int m0 = qt * kBM;
-  const int pairs = p.H / 2;
-  const int b = blockIdx.y / pairs, h0 = (blockIdx.y % pairs) * 2, g = h0 / hpg;
-
-  // key-tile range visited by this query tile
-  int jlo, jhi;
-  if (MODE == kWin) {
-    jlo = max(0, m0 - p.window + 1) / kBN;
-    jhi = min(m0 + kBM - 1, p.Tk - 1) / kBN;
-  } else {
-    const int tl = m0 + kBM - 1;
-    const int kmax = tl >= p.cmp_l - 1 ? min(p.cmp_nb - 1, (tl - p.cmp_l + 1) / p.cmp_d) : -1;
-    jlo = 0;
-    jhi = kmax >= 0 ? kmax / kBN : -1;
-  }
+  // Work items: (query tile, batch, head pair), late (heavy) query tiles first; the CTAs of the persistent grid take
+  // them round robin, and every role below walks the same item list on its own, so that the loads and the first
+  // S MMAs of an item run while the softmax warps are still in the epilogue of the one before.
+  const int pairs = p.H / 2, per_qt = p.B * pairs, nqt = p.Tq / kBM;
+  const int nitems = nqt * per_qt;
   // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
-  const int ntiles = *(volatile const int*)&g_fa_fwd_timeouts != 0 ? 0 : jhi - jlo + 1;
+  const bool poisoned = *(volatile const int*)&g_fa_fwd_timeouts != 0;
+  struct Item { int m0, b, h0, g, jlo, ntiles; };
+  auto item_at = [&](int it) {
+    Item w;
+    const int qt = nqt - 1 - it / per_qt, y = it % per_qt;
+    w.m0 = qt * kBM;
+    w.b = y / pairs;
+    w.h0 = (y % pairs) * 2;
+    w.g = w.h0 / hpg;
+    int jhi;
+    if (MODE == kWin) {
+      w.jlo = max(0, w.m0 - p.window + 1) / kBN;
+      jhi = min(w.m0 + kBM - 1, p.Tk - 1) / kBN;
+    } else {
+      const int tl = w.m0 + kBM - 1;
+      const int kmax = tl >= p.cmp_l - 1 ? min(p.cmp_nb - 1, (tl - p.cmp_l + 1) / p.cmp_d) : -1;
+      w.jlo = 0;
+      jhi = kmax >= 0 ? kmax / kBN : -1;
+    }
+    w.ntiles = poisoned ? 0 : jhi - w.jlo + 1;
+    return w;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->q_full, 1);
+    mbar_init(&bar->q_empty, 1);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->o_free[i], 128);
       mbar_init(&bar->k_full[i], 1);
       mbar_init(&bar->k_empty[i], 1);
       mbar_init(&bar->s_full[i], 1);
@@ -125,85 +138,103 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   if (warp >= 10) {
     // idle half of the third warpgroup
   } else if (warp == 8) {
-    // ------------------------------------------------------------ TMA producer (warp-uniform loop, one elected lane issues)
-    if (ntiles > 0) {
+    // ------------------------------------------------------------ TMA producer (warp-uniform loops, one elected lane issues)
+    if (elect_one()) {
+      prefetch_tensormap(&tmQ);
+      prefetch_tensormap(&tmK);
+      prefetch_tensormap(&tmV);
+    }
+    __syncwarp();
+    bool ok = true;
+    int ic = 0, kc = 0;        // items with tiles / key tiles loaded so far by this CTA (barrier phases run on)
+    bool q_pending = false;
+    for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
+      const Item w = item_at(it);
+      if (w.ntiles <= 0) continue;
+      ok = mbar_wait_warp(&bar->q_empty, (ic & 1) ^ 1, abort);   // the S MMAs of the item before have read Q
+      if (!ok) break;
       if (elect_one()) {
-        prefetch_tensormap(&tmQ);
-        prefetch_tensormap(&tmK);
-        prefetch_tensormap(&tmV);
         mbar_arrive_expect_tx(&bar->q_full, 2 * SM::kQBytes);
         for (int i = 0; i < 2; ++i)
           for (int c = 0; c < DK / 64; ++c)
             tma_load_2d(&tmQ, &bar->q_full, sQ + i * SM::kQBytes + c * (kBM * 128), c * 64,
-                        (b * p.H + h0 + i) * p.Tq + m0);
+                        (w.b * p.H + w.h0 + i) * p.Tq + w.m0);
       }
       __syncwarp();
-      bool ok = true;
-      int issued = 0;
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int n0 = (jlo + j) * kBN, ks = j & 1;
-        ok = mbar_wait_warp(&bar->k_empty[ks], ((j >> 1) & 1) ^ 1, abort);
+      q_pending = true;
+      for (int j = 0; j < w.ntiles && ok; ++j, ++kc) {
+        const int n0 = (w.jlo + j) * kBN, ks = kc & 1;
+        ok = mbar_wait_warp(&bar->k_empty[ks], ((kc >> 1) & 1) ^ 1, abort);
         if (!ok) break;
         if (elect_one()) {
           mbar_arrive_expect_tx(&bar->k_full[ks], SM::kKBytes);
           for (int hf = 0; hf < 2; ++hf)
-            tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kKBytes + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
+            tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kKBytes + hf * (DK * 128), n0 + hf * 64, (w.b * p.G + w.g) * DK);
         }
         __syncwarp();
-        ok = mbar_wait_warp(&bar->v_empty, (j & 1) ^ 1, abort);
+        ok = mbar_wait_warp(&bar->v_empty, (kc & 1) ^ 1, abort);
         if (!ok) {
-          if (lane == 0) mbar_wait(&bar->k_full[ks], (j >> 1) & 1, abort);
+          if (lane == 0) mbar_wait(&bar->k_full[ks], (kc >> 1) & 1, abort);
           break;
         }
         if (elect_one()) {
           mbar_arrive_expect_tx(&bar->v_full, SM::kVBytes);
           for (int c = 0; c < DV / 64; ++c)
-            tma_load_2d(&tmV, &bar->v_full, sV + c * (kBN * 128), c * 64, (b * p.G + g) * p.Tk + n0);
+            tma_load_2d(&tmV, &bar->v_full, sV + c * (kBN * 128), c * 64, (w.b * p.G + w.g) * p.Tk + n0);
         }
         __syncwarp();
-        issued = j + 1;
       }
-      if (!ok && lane == 0) {
-        // let copies already in flight land before the CTA gives its shared memory back
-        mbar_wait(&bar->q_full, 0, abort);
-        for (int j = max(0, issued - 2); j < issued; ++j) mbar_wait(&bar->k_full[j & 1], (j >> 1) & 1, abort);
-        if (issued > 0) mbar_wait(&bar->v_full, (issued - 1) & 1, abort);
-      }
+      if (ok) { ++ic; q_pending = false; }
+    }
+    if (!ok && lane == 0) {
+      // let copies already in flight land before the CTA gives its shared memory back
+      if (q_pending) mbar_wait(&bar->q_full, ic & 1, abort);
+      for (int c = max(0, kc - 2); c < kc; ++c) mbar_wait(&bar->k_full[c & 1], (c >> 1) & 1, abort);
+      if (kc > 0) mbar_wait(&bar->v_full, (kc - 1) & 1, abort);
     }
   } else if (warp == 9) {
-    // ------------------------------------------------------------ UMMA issuer (warp-uniform loop, one elected lane issues)
-    if (ntiles > 0) {
-      constexpr uint32_t idQK = idesc_bf16(kBM, kBN, 0, 1);
-      constexpr uint32_t idPV = idesc_bf16(kBM, DV, 0, 1);
-      const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t dK0 = smem_desc_sw128(smem_u32(sK), DK * 128, 1024);
-      const uint64_t dV = smem_desc_sw128(smem_u32(sV), kBN * 128, 1024);
-      // issue S_i = Q_i K^T for key slot ks; called by the elected lane only
-      auto issue_qk = [&](int i, int ks) {
-        const uint64_t dQ = desc_advance(dQ0, i * SM::kQBytes), dK = desc_advance(dK0, ks * SM::kKBytes);
+    // ------------------------------------------------------------ UMMA issuer (warp-uniform loops, one elected lane issues)
+    constexpr uint32_t idQK = idesc_bf16(kBM, kBN, 0, 1);
+    constexpr uint32_t idPV = idesc_bf16(kBM, DV, 0, 1);
+    const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+    const uint64_t dK0 = smem_desc_sw128(smem_u32(sK), DK * 128, 1024);
+    const uint64_t dV = smem_desc_sw128(smem_u32(sV), kBN * 128, 1024);
+    // issue S_i = Q_i K^T for key slot ks; called by the elected lane only
+    auto issue_qk = [&](int i, int ks) {
+      const uint64_t dQ = desc_advance(dQ0, i * SM::kQBytes), dK = desc_advance(dK0, ks * SM::kKBytes);
 #pragma unroll
-        for (int kk = 0; kk < DK / 16; ++kk)
-          umma_ss(tmem + i * 128, desc_advance(dQ, (kk >> 2) * (kBM * 128) + (kk & 3) * 32), desc_advance(dK, kk * 2048), idQK,
-                  kk > 0);
-        umma_commit(&bar->s_full[i]);
-      };
-      bool ok = mbar_wait_warp(&bar->q_full, 0, abort) && mbar_wait_warp(&bar->k_full[0], 0, abort);
-      if (ok) {
-        tc_fence_after();
-        if (elect_one()) {
-          issue_qk(0, 0);
-          issue_qk(1, 0);
-          umma_commit(&bar->k_empty[0]);
-        }
-        __syncwarp();
+      for (int kk = 0; kk < DK / 16; ++kk)
+        umma_ss(tmem + i * 128, desc_advance(dQ, (kk >> 2) * (kBM * 128) + (kk & 3) * 32), desc_advance(dK, kk * 2048), idQK,
+                kk > 0);
+      umma_commit(&bar->s_full[i]);
+    };
+    bool ok = true;
+    int ic = 0, kc = 0;        // items with tiles / key tiles consumed so far by this CTA
+    for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
+      const Item w = item_at(it);
+      if (w.ntiles <= 0) continue;
+      ok = mbar_wait_warp(&bar->q_full, ic & 1, abort) && mbar_wait_warp(&bar->k_full[kc & 1], (kc >> 1) & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        issue_qk(0, kc & 1);
+        issue_qk(1, kc & 1);
+        umma_commit(&bar->k_empty[kc & 1]);
       }
-      for (int j = 0; j < ntiles && ok; ++j) {
-        ok = mbar_wait_warp(&bar->v_full, j & 1, abort);
+      __syncwarp();
+      for (int j = 0; j < w.ntiles && ok; ++j, ++kc) {
+        const bool more = j + 1 < w.ntiles;
+        if (!more) {
+          // every S MMA of this item has been issued: Q may be replaced once they have run
+          if (elect_one()) umma_commit(&bar->q_empty);
+          __syncwarp();
+        }
+        ok = mbar_wait_warp(&bar->v_full, kc & 1, abort);
         for (int i = 0; i < 2 && ok; ++i) {
-          ok = mbar_wait_warp(&bar->p_full[i], j & 1, abort);
+          ok = mbar_wait_warp(&bar->p_full[i], kc & 1, abort);
+          if (ok && j == 0) ok = mbar_wait_warp(&bar->o_free[i], (ic & 1) ^ 1, abort);  // O_i of the item before was read out
           if (!ok) break;
-          const bool more = j + 1 < ntiles;
-          const int ks = (j + 1) & 1;
+          const int ks = (kc + 1) & 1;
           tc_fence_after();
           if (elect_one()) {
 #pragma unroll
@@ -215,7 +246,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           __syncwarp();
           if (more) {
             if (i == 0) {
-              ok = mbar_wait_warp(&bar->k_full[ks], ((j + 1) >> 1) & 1, abort);
+              ok = mbar_wait_warp(&bar->k_full[ks], ((kc + 1) >> 1) & 1, abort);
               if (!ok) break;
               tc_fence_after();
             }
@@ -227,22 +258,27 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
         }
       }
+      ++ic;
     }
   } else {
     // ------------------------------------------------------------ softmax + epilogue, one row per thread
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int i = warp >> 2;                   // which MMA tile / head
     const int r = (warp & 3) * 32 + lane;      // row inside the tile == TMEM lane
-    const int t = m0 + r;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_base + i * 128;
     const uint32_t tO = tmem + lane_base + 256 + i * 128;
-    float m_true = -CUDART_INF_F, m_ref = -CUDART_INF_F, l = 0.f;
     bool ok = true;
+    int tc = 0;                                // key tiles of earlier items (barrier phases run on)
     uint32_t sv[4][32];
+    for (int it = blockIdx.x; it < nitems; it += gridDim.x) {
+    const Item w = item_at(it);
+    const int m0 = w.m0, b = w.b, h0 = w.h0, jlo = w.jlo, ntiles = ok ? w.ntiles : 0;
+    const int t = m0 + r;
+    float m_true = -CUDART_INF_F, m_ref = -CUDART_INF_F, l = 0.f;
     for (int j = 0; j < ntiles && ok; ++j) {
       const int n0 = (jlo + j) * kBN;
-      ok = mbar_wait(&bar->s_full[i], j & 1, abort);
+      ok = mbar_wait(&bar->s_full[i], (tc + j) & 1, abort);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -283,7 +319,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const bool grow = m_true > m_ref + kRescaleThreshold;  // also true on the first finite maximum
       const bool need_o = grow && m_ref != -CUDART_INF_F;
       if (__any_sync(0xffffffffu, need_o)) {
-        ok = mbar_wait(&bar->pv_done[i], (j - 1) & 1, abort);  // O_i must hold PV(j-1) before it is scaled
+        ok = mbar_wait(&bar->pv_done[i], (tc + j - 1) & 1, abort);  // O_i must hold PV(j-1) before it is scaled
         if (!ok) break;
         tc_fence_after();
         const float f = need_o ? ex2(m_ref - m_true) : 1.f;
@@ -325,7 +361,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int h = h0 + i;
     const int64_t row = ((int64_t)b * p.H + h) * p.Tq + t;
     __nv_bfloat16* orow = p.o + row * DV;
-    if (ok && ntiles > 0) ok = mbar_wait(&bar->pv_done[i], (ntiles - 1) & 1, abort);
+    if (ok && ntiles > 0) ok = mbar_wait(&bar->pv_done[i], (tc + ntiles - 1) & 1, abort);
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -355,7 +391,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       if (p.L) p.L[row] = l > 0.f ? logf(l) + (m_ref - m_true) * kLn2 : -CUDART_INF_F;
       if (p.M) p.M[row] = m_true * kLn2;  // back from log2 units to the natural-log scale of the logits
+      if (ntiles > 0) {
+        tc_fence_before();
+        mbar_arrive(&bar->o_free[i]);  // O_i is in registers: the first PV of the next item may overwrite it
+      }
     }
+    tc += ntiles;
+    }  // items
   }
 
   // ------------------------------------------------------------ teardown (every thread gets here)
@@ -421,6 +463,19 @@ int make_tmap_head_rows(CUtensorMap* map, const void* base, uint64_t heads_total
   return NSA_OK;
 }
 
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 template <int DK, int DV, int MODE>
 static int launch_fa_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaFwdParams& p,
                            cudaStream_t st) {
@@ -428,7 +483,8 @@ static int launch_fa_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const C
   auto kern = fa_fwd_kernel<DK, DV, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kDynamic);
   if (e != cudaSuccess) return fail(NSA_ERR_LAUNCH, "fa_fwd: cannot reserve %d bytes of shared memory: %s", SM::kDynamic, cudaGetErrorString(e));
-  dim3 grid(p.Tq / kBM, p.B * (p.H / 2));
+  const int nitems = (p.Tq / kBM) * p.B * (p.H / 2);
+  dim3 grid((unsigned)std::min(nitems, sm_count()));   // persistent: one CTA per SM walks the item list
   KernelTimer kt(MODE == kWin ? "fa_fwd_win" : "fa_fwd_cmp", st);
   kern<<<grid, kFaThreads, SM::kDynamic, st>>>(tq, tk, tv, p);
   return check_launch("fa_fwd_sm100");
@@ -443,7 +499,7 @@ int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L,
                  int Tk, int dk, int dv, int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale,
                  cudaStream_t st) {
   if (!fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: unsupported shape");
-  if ((int64_t)B * (H / 2) > 65535) return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: too many (batch, head) pairs");
+  if ((int64_t)B * (H / 2) * (Tq / kBM) > 0x7fffffff) return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: too many work items");
   CUtensorMap tq, tk, tv;
   if (int rc = make_tmap_bf16_2d(&tq, q, (uint64_t)B * H * Tq, dk, kBM)) return rc;
   if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
