@@ -11,6 +11,7 @@
 //          head of the group; P^T and dS^T stay in TMEM as A operands of dV += P^T dO, dK += dS^T Q.
 //          TMEM: dK 192 + dV 128 + S^T 64 + dP^T 64 columns.  Heads may be split over several CTAs
 //          (compressed branch, few key tiles): partial sums go to scratch and are added in head order.
+#include <algorithm>
 #include <cuda.h>
 
 #include <mutex>
@@ -23,6 +24,19 @@
 namespace nsa {
 
 using namespace ptx;
+
+static int bwd_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -77,7 +91,7 @@ struct DqSmem {
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct DqBarriers {
-  uint64_t qdo_full, k_full[2], k_empty[2], v_full, v_empty, sdp_full, sdp_free, ds_full, ds_free, dq_done;
+  uint64_t qdo_full, qdo_empty, k_full[2], k_empty[2], v_full, v_empty, sdp_full, sdp_free, ds_full, ds_free, dq_done, dq_free;
   uint32_t tmem_base;
   int abort;
 };
@@ -96,21 +110,33 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   DqBarriers* bar = reinterpret_cast<DqBarriers*>(smem + SM::oBar);
   volatile int* abort = &bar->abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = (gridDim.x - 1 - blockIdx.x) * 128;
-  const int b = blockIdx.y / p.H, h = blockIdx.y % p.H, g = h / (p.H / p.G);
-  int jlo, jhi;
-  if (MODE == kWin) {
-    jlo = max(0, m0 - p.window + 1) / 128;
-    jhi = min(m0 + 127, p.Tk - 1) / 128;
-  } else {
-    const int tl = m0 + 127;
-    const int kmax = tl >= p.cmp_l - 1 ? min(p.cmp_nb - 1, (tl - p.cmp_l + 1) / p.cmp_d) : -1;
-    jlo = 0;
-    jhi = kmax >= 0 ? kmax / 128 : -1;
-  }
+  // Work items: (query tile, batch, head), late (heavy) query tiles first, taken round robin by the CTAs of a persistent
+  // grid; every role walks the same list on its own, so the loads and the first S/dP MMAs of an item overlap the dQ
+  // epilogue of the one before.
+  const int per_qt = p.B * p.H, nqt = p.Tq / 128, nitems = nqt * per_qt;
   // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
   const bool poisoned = p.timeouts && *(volatile const int*)p.timeouts != 0;
-  const int ntiles = poisoned ? 0 : jhi - jlo + 1;
+  struct Item { int m0, b, h, g, jlo, ntiles; };
+  auto item_at = [&](int it) {
+    Item w;
+    const int qt = nqt - 1 - it / per_qt, y = it % per_qt;
+    w.m0 = qt * 128;
+    w.b = y / p.H;
+    w.h = y % p.H;
+    w.g = w.h / (p.H / p.G);
+    int jhi;
+    if (MODE == kWin) {
+      w.jlo = max(0, w.m0 - p.window + 1) / 128;
+      jhi = min(w.m0 + 127, p.Tk - 1) / 128;
+    } else {
+      const int tl = w.m0 + 127;
+      const int kmax = tl >= p.cmp_l - 1 ? min(p.cmp_nb - 1, (tl - p.cmp_l + 1) / p.cmp_d) : -1;
+      w.jlo = 0;
+      jhi = kmax >= 0 ? kmax / 128 : -1;
+    }
+    w.ntiles = poisoned ? 0 : jhi - w.jlo + 1;
+    return w;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->qdo_full, 1);
@@ -122,6 +148,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(&bar->ds_full, 256);
     mbar_init(&bar->ds_free, 1);
     mbar_init(&bar->dq_done, 1);
+    mbar_init(&bar->qdo_empty, 1);
+    mbar_init(&bar->dq_free, 256);
     bar->abort = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -134,82 +162,100 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr uint32_t cS = 0, cdP = 128, cdQ = 256, cdS = 256 + DK;
 
   if (warp == 8) {
-    // TMA producer: warp-uniform loop, one elected lane issues
-    if (ntiles > 0) {
+    // TMA producer: warp-uniform loops, one elected lane issues
+    bool ok = true;
+    int ic = 0, kc = 0;      // items with tiles / key tiles loaded so far by this CTA (barrier phases run on)
+    bool q_pending = false;
+    for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
+      const Item w = item_at(it);
+      if (w.ntiles <= 0) continue;
+      ok = mbar_wait_warp(&bar->qdo_empty, (ic & 1) ^ 1, abort);   // the S/dP MMAs of the item before have read Q and dO
+      if (!ok) break;
       if (elect_one()) {
         mbar_arrive_expect_tx(&bar->qdo_full, SM::kQ + SM::kdO);
-        const int qrow = (b * p.H + h) * p.Tq + m0;
+        const int qrow = (w.b * p.H + w.h) * p.Tq + w.m0;
         for (int c = 0; c < DK / 64; ++c) tma_load_2d(&tmQ, &bar->qdo_full, sQ + c * 16384, c * 64, qrow);
         for (int c = 0; c < DV / 64; ++c) tma_load_2d(&tmdO, &bar->qdo_full, sdO + c * 16384, c * 64, qrow);
       }
       __syncwarp();
-      bool ok = true;
-      int issued = 0;
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int n0 = (jlo + j) * 128, ks = j & 1;
-        ok = mbar_wait_warp(&bar->k_empty[ks], ((j >> 1) & 1) ^ 1, abort);
+      q_pending = true;
+      for (int j = 0; j < w.ntiles && ok; ++j, ++kc) {
+        const int n0 = (w.jlo + j) * 128, ks = kc & 1;
+        ok = mbar_wait_warp(&bar->k_empty[ks], ((kc >> 1) & 1) ^ 1, abort);
         if (!ok) break;
         if (elect_one()) {
           mbar_arrive_expect_tx(&bar->k_full[ks], SM::kK);
           for (int hf = 0; hf < 2; ++hf)
-            tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kK + hf * (DK * 128), n0 + hf * 64, (b * p.G + g) * DK);
+            tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kK + hf * (DK * 128), n0 + hf * 64, (w.b * p.G + w.g) * DK);
         }
         __syncwarp();
-        ok = mbar_wait_warp(&bar->v_empty, (j & 1) ^ 1, abort);
+        ok = mbar_wait_warp(&bar->v_empty, (kc & 1) ^ 1, abort);
         if (!ok) {
-          if (lane == 0) mbar_wait(&bar->k_full[ks], (j >> 1) & 1, abort);
+          if (lane == 0) mbar_wait(&bar->k_full[ks], (kc >> 1) & 1, abort);
           break;
         }
         if (elect_one()) {
           mbar_arrive_expect_tx(&bar->v_full, SM::kV);
           for (int c = 0; c < DV / 64; ++c)
-            tma_load_2d(&tmV, &bar->v_full, sV + c * 16384, c * 64, (b * p.G + g) * p.Tk + n0);
+            tma_load_2d(&tmV, &bar->v_full, sV + c * 16384, c * 64, (w.b * p.G + w.g) * p.Tk + n0);
         }
         __syncwarp();
-        issued = j + 1;
       }
-      if (!ok && lane == 0) {
-        mbar_wait(&bar->qdo_full, 0, abort);
-        for (int j = max(0, issued - 2); j < issued; ++j) mbar_wait(&bar->k_full[j & 1], (j >> 1) & 1, abort);
-        if (issued > 0) mbar_wait(&bar->v_full, (issued - 1) & 1, abort);
-      }
+      if (ok) { ++ic; q_pending = false; }
+    }
+    if (!ok && lane == 0) {
+      // let copies already in flight land before the CTA gives its shared memory back
+      if (q_pending) mbar_wait(&bar->qdo_full, ic & 1, abort);
+      for (int c = max(0, kc - 2); c < kc; ++c) mbar_wait(&bar->k_full[c & 1], (c >> 1) & 1, abort);
+      if (kc > 0) mbar_wait(&bar->v_full, (kc - 1) & 1, abort);
     }
   } else if (warp == 9) {
-    // UMMA issuer: warp-uniform loop, one elected lane issues
-    if (ntiles > 0) {
-      constexpr uint32_t idS = idesc_bf16(128, 128, 0, 1);    // Q (K-major) x K tile (MN-major: keys contiguous)
-      constexpr uint32_t iddP = idesc_bf16(128, 128, 0, 0);   // dO (K-major) x V tile (K-major: dv contiguous)
-      constexpr uint32_t iddQ = idesc_bf16(128, DK, 0, 0);    // dS (TMEM) x K tile read K-major (keys = K dim)
-      const uint64_t dQd = smem_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t ddO = smem_desc_sw128(smem_u32(sdO), 16, 1024);
-      const uint64_t dVd = smem_desc_sw128(smem_u32(sV), 16, 1024);
-      auto issue_sdp = [&](int j) -> bool {
-        const int ks = j & 1;
-        const uint64_t dK_mn = smem_desc_sw128(smem_u32(sK + ks * SM::kK), DK * 128, 1024);
-        if (!(mbar_wait_warp(&bar->k_full[ks], (j >> 1) & 1, abort) && mbar_wait_warp(&bar->v_full, j & 1, abort))) return false;
-        if (j > 0 && !mbar_wait_warp(&bar->sdp_free, (j - 1) & 1, abort)) return false;  // S/dP of tile j-1 are in registers
-        tc_fence_after();
-        if (elect_one()) {
+    // UMMA issuer: warp-uniform loops, one elected lane issues
+    constexpr uint32_t idS = idesc_bf16(128, 128, 0, 1);    // Q (K-major) x K tile (MN-major: keys contiguous)
+    constexpr uint32_t iddP = idesc_bf16(128, 128, 0, 0);   // dO (K-major) x V tile (K-major: dv contiguous)
+    constexpr uint32_t iddQ = idesc_bf16(128, DK, 0, 0);    // dS (TMEM) x K tile read K-major (keys = K dim)
+    const uint64_t dQd = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+    const uint64_t ddO = smem_desc_sw128(smem_u32(sdO), 16, 1024);
+    const uint64_t dVd = smem_desc_sw128(smem_u32(sV), 16, 1024);
+    // S and dP of the key tile with running index c (over all items of this CTA)
+    auto issue_sdp = [&](int c) -> bool {
+      const int ks = c & 1;
+      const uint64_t dK_mn = smem_desc_sw128(smem_u32(sK + ks * SM::kK), DK * 128, 1024);
+      if (!(mbar_wait_warp(&bar->k_full[ks], (c >> 1) & 1, abort) && mbar_wait_warp(&bar->v_full, c & 1, abort))) return false;
+      if (c > 0 && !mbar_wait_warp(&bar->sdp_free, (c - 1) & 1, abort)) return false;  // S/dP of the tile before are in registers
+      tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < DK / 16; ++kk)
-            umma_ss(tmem + cS, desc_advance(dQd, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dK_mn, kk * 2048), idS, kk > 0);
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + cS, desc_advance(dQd, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dK_mn, kk * 2048), idS, kk > 0);
 #pragma unroll
-          for (int kk = 0; kk < DV / 16; ++kk)
-            umma_ss(tmem + cdP, desc_advance(ddO, (kk >> 2) * 16384 + (kk & 3) * 32),
-                    desc_advance(dVd, (kk >> 2) * 16384 + (kk & 3) * 32), iddP, kk > 0);
-          umma_commit(&bar->sdp_full);
-          umma_commit(&bar->v_empty);
-        }
-        __syncwarp();
-        return true;
-      };
-      bool ok = mbar_wait_warp(&bar->qdo_full, 0, abort) && issue_sdp(0);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int ks = j & 1;
+        for (int kk = 0; kk < DV / 16; ++kk)
+          umma_ss(tmem + cdP, desc_advance(ddO, (kk >> 2) * 16384 + (kk & 3) * 32),
+                  desc_advance(dVd, (kk >> 2) * 16384 + (kk & 3) * 32), iddP, kk > 0);
+        umma_commit(&bar->sdp_full);
+        umma_commit(&bar->v_empty);
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = true;
+    int ic = 0, kc = 0;      // items with tiles / key tiles consumed so far by this CTA
+    for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
+      const Item w = item_at(it);
+      if (w.ntiles <= 0) continue;
+      ok = mbar_wait_warp(&bar->qdo_full, ic & 1, abort) && issue_sdp(kc);
+      for (int j = 0; j < w.ntiles && ok; ++j) {
+        const int ks = (kc + j) & 1;
         const uint64_t dK_k = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);
-        if (j + 1 < ntiles) ok = issue_sdp(j + 1);
+        if (j + 1 < w.ntiles) ok = issue_sdp(kc + j + 1);
         if (!ok) break;
-        ok = mbar_wait_warp(&bar->ds_full, j & 1, abort);
+        if (j == w.ntiles - 1) {
+          // every S/dP MMA of this item has been issued: Q and dO may be replaced once they have run
+          if (elect_one()) umma_commit(&bar->qdo_empty);
+          __syncwarp();
+        }
+        ok = mbar_wait_warp(&bar->ds_full, (kc + j) & 1, abort);
+        if (ok && j == 0) ok = mbar_wait_warp(&bar->dq_free, (ic & 1) ^ 1, abort);  // dQ of the item before was read out
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
@@ -226,17 +272,23 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (elect_one()) umma_commit(&bar->dq_done);
         __syncwarp();
       }
+      kc += w.ntiles;
+      ++ic;
     }
   } else {
     const int gsel = warp >> 2;                 // which half of the key columns this thread handles
-    const int r = (warp & 3) * 32 + lane, t = m0 + r;
+    const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const int64_t row = ((int64_t)b * p.H + h) * p.Tq + t;
-    const float lse2 = p.lse2[row], Dr = p.D[row];
     bool ok = true;
+    int ic = 0, tc = 0;      // items with tiles / key tiles of earlier items (barrier phases run on)
+    for (int it = blockIdx.x; it < nitems; it += gridDim.x) {
+    const Item w = item_at(it);
+    const int jlo = w.jlo, ntiles = ok ? w.ntiles : 0, t = w.m0 + r;
+    const int64_t row = ((int64_t)w.b * p.H + w.h) * p.Tq + t;
+    const float lse2 = p.lse2[row], Dr = p.D[row];
     for (int j = 0; j < ntiles && ok; ++j) {
       const int n0 = (jlo + j) * 128 + gsel * 64;   // first key of this thread's columns
-      ok = mbar_wait(&bar->sdp_full, j & 1, abort);
+      ok = mbar_wait(&bar->sdp_full, (tc + j) & 1, abort);
       if (!ok) break;
       tc_fence_after();
       uint32_t sv[2][32], dp[2][32], pk[32];
@@ -271,8 +323,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           __nv_bfloat162 x = __floats2bfloat162_rn(p0 * (__uint_as_float(dp[c][2 * e]) - Dr), p1 * (__uint_as_float(dp[c][2 * e + 1]) - Dr));
           pk[c * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
         }
-      if (j > 0) {  // dS of the previous tile must have been consumed by its dQ MMAs
-        ok = mbar_wait(&bar->ds_free, (j - 1) & 1, abort);
+      if (tc + j > 0) {  // dS of the tile before (of this item or the one before) must have been consumed by its dQ MMAs
+        ok = mbar_wait(&bar->ds_free, (tc + j - 1) & 1, abort);
         if (!ok) break;
         tc_fence_after();
       }
@@ -281,7 +333,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       mbar_arrive(&bar->ds_full);
     }
-    if (ok && ntiles > 0) ok = mbar_wait(&bar->dq_done, 0, abort);
+    if (ok && ntiles > 0) ok = mbar_wait(&bar->dq_done, ic & 1, abort);
     if (ok) {
       tc_fence_after();
       __nv_bfloat16* dst = p.dq + row * DK + gsel * (DK / 2);
@@ -307,7 +359,13 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           *reinterpret_cast<uint4*>(dst + c * 32 + e) = w;
         }
       }
+      if (ntiles > 0) {
+        tc_fence_before();
+        mbar_arrive(&bar->dq_free);  // dQ is in registers: the first dQ MMA of the next item may overwrite it
+      }
     }
+    if (ntiles > 0) { tc += ntiles; ++ic; }
+    }  // items
   }
   tc_fence_before();
   __syncthreads();
@@ -638,7 +696,7 @@ static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, con
     return fail(NSA_ERR_LAUNCH, "fa_bwd: cannot reserve shared memory");
   {
     KernelTimer kt(MODE == kWin ? "fa_bwd_dq_win" : "fa_bwd_dq_cmp", st);
-    kq<<<dim3(p.Tq / 128, p.B * p.H), 320, DqSmem<DK, DV>::kDynamic, st>>>(tq128, tdo128, tk, tv, p);
+    kq<<<dim3((unsigned)std::min((p.Tq / 128) * p.B * p.H, bwd_sm_count())), 320, DqSmem<DK, DV>::kDynamic, st>>>(tq128, tdo128, tk, tv, p);
   }
   if (int rc = check_launch("fa_bwd_dq_sm100")) return rc;
   KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);
