@@ -54,6 +54,12 @@ NSA_API int nsa_set_kernel_family(int family);
  * starting at position 0.  Honoured by the bf16 tensor-core paths of nsa_cmp_attn_fwd/bwd, nsa_score_topn and
  * nsa_slc_fwd/bwd; any other path refuses a non-zero offset with NSA_ERR_ARG.  Set it back to 0 afterwards. */
 NSA_API int nsa_set_query_offset(int position);
+
+/* Backward of the whole layer: dQ is the sum of the three branches' dQ (the reference leaves that sum to autograd,
+ * nsa/kernels.py:2446-2463 feeds one q to all three).  After nsa_set_dq_addends(a, b) the next nsa_slc_bwd of this host
+ * thread writes dq = dq_selection + a + b (a, b: dQ of the other branches, same dtype and contiguous [B,H,T,dk] layout
+ * as dq; either may be NULL), summed in fp32 and rounded once.  The addends serve that one call. */
+NSA_API int nsa_set_dq_addends(const void* a, const void* b);
 /* Number of thread blocks of the tensor-core kernels that ever gave up on a bounded barrier wait
  * (0 in a healthy run; their output is then invalid).  Synchronises the device.  reset != 0 clears
  * the counter.  Negative = error. */

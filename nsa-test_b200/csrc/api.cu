@@ -84,6 +84,19 @@ int kernel_family() { return g_kernel_family; }  // 0: tensor-core kernels where
 // of the compressed attention, the scoring and the selected-block attention; every other path refuses a non-zero offset.
 static thread_local int g_query_pos0 = 0;
 int query_pos0() { return g_query_pos0; }
+// dQ of the other two branches, added by the next nsa_slc_bwd of this thread (which clears them)
+static thread_local const void* g_dq_add[2] = {nullptr, nullptr};
+void dq_addends(const void** a, const void** b) { *a = g_dq_add[0]; *b = g_dq_add[1]; }
+
+template <typename T>
+__global__ void add_dq_addends_kernel(T* __restrict__ dq, const T* __restrict__ a, const T* __restrict__ b, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float x = Elem<T>::ld(dq + i);
+  if (a) x += Elem<T>::ld(a + i);
+  if (b) x += Elem<T>::ld(b + i);
+  Elem<T>::st(dq + i, x);
+}
 
 // canonical contiguous layouts: q [B,H,T,dk], k [B,G,dk,Tk] (strides given as z,g,n,k), v [B,G,Tk,dv], o [B,H,T,dv]
 static bool canonical_fwd(const int64_t* s, int H, int G, int Tq, int Tk, int dk, int dv) {
@@ -172,6 +185,12 @@ extern "C" NSA_API int nsa_set_kernel_family(int family) {
 extern "C" NSA_API int nsa_set_query_offset(int position) {
   NSA_REQUIRE(position >= 0, "query offset must be >= 0");
   g_query_pos0 = position;
+  return NSA_OK;
+}
+
+extern "C" NSA_API int nsa_set_dq_addends(const void* a, const void* b) {
+  g_dq_add[0] = a;
+  g_dq_add[1] = b;
   return NSA_OK;
 }
 
@@ -310,6 +329,7 @@ extern "C" NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, 
                            const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots, int l_prime,
                            int dk, int dv, float scale, int dtype, void* workspace, size_t workspace_bytes,
                            void* stream) {
+  struct ClearAddends { ~ClearAddends() { g_dq_add[0] = g_dq_add[1] = nullptr; } } clear_addends;  // they serve one call only
   if (int rc = check_common("slc_bwd", B, H, G, Tq, Tkv, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && indices && out && dout && L && M && dq && dkey && dval && strides, "slc_bwd: null pointer");
   NSA_REQUIRE(l_prime > 0 && n_slots > 0, "slc_bwd: bad block size / slot count");
@@ -319,6 +339,10 @@ extern "C" NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, 
     return slc_bwd_sm100(q, k, v, indices, strides + 34, out, dout, L, M, dq, dkey, dval, B, H, G, Tq, Tkv, dk, dv, n_slots,
                          l_prime, scale, g_query_pos0, workspace, workspace_bytes, (cudaStream_t)stream);
   NSA_NO_QUERY_OFFSET("slc_bwd");
+  const void *add0 = g_dq_add[0], *add1 = g_dq_add[1];
+  if (add0 || add1)
+    NSA_REQUIRE(strides[25] == 1 && strides[24] == dk && strides[23] == (int64_t)Tq * dk && strides[22] == (int64_t)H * Tq * dk,
+                "slc_bwd: dQ addends need a contiguous [B,H,T,dk] dq");
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.indices = indices;
   a.dq = dq; a.dk_out = dkey; a.dv_out = dval;
@@ -330,5 +354,16 @@ extern "C" NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, 
   if (int rc = build_slc_csr(indices, a.sidx, B, G, Tq, Tkv, n_slots, l_prime, 1, 0, workspace, workspace_bytes,
                              &a.csr_off, &a.csr_t, st))
     return rc;
-  return launch_attn_generic(a, kSlc, dtype, true, st);
+  if (int rc = launch_attn_generic(a, kSlc, dtype, true, st)) return rc;
+  if (add0 || add1) {
+    const int64_t n = (int64_t)B * H * Tq * dk;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == NSA_F32)
+      add_dq_addends_kernel<float><<<blocks, 256, 0, st>>>((float*)dq, (const float*)add0, (const float*)add1, n);
+    else
+      add_dq_addends_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((__nv_bfloat16*)dq, (const __nv_bfloat16*)add0,
+                                                                  (const __nv_bfloat16*)add1, n);
+    return check_launch("slc_bwd dq addends");
+  }
+  return NSA_OK;
 }

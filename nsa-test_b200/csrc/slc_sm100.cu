@@ -558,10 +558,27 @@ __global__ void slc_combine_fwd_bulk_kernel(const __nv_bfloat16* __restrict__ o_
 // ------------------------------------------------------------------------------------------------
 // dQ[b,h,t,:] = scale * sum of the contributing slots' partials, slot order: one warp per row; the loads of 8 slots
 // are in flight together and do not wait for the index row
+// dQ of the selection branch plus, when given, the dQ of the two other branches (same layout): one rounding of the sum
+__device__ __forceinline__ __nv_bfloat162 slc_dq_total(float x, float y, const __nv_bfloat16* add0, const __nv_bfloat16* add1,
+                                                       int64_t at) {
+  if (add0) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(add0 + at));
+    x += a.x;
+    y += a.y;
+  }
+  if (add1) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(add1 + at));
+    x += a.x;
+    y += a.y;
+  }
+  return __floats2bfloat162_rn(x, y);
+}
+
 template <int DK>
 __global__ void slc_combine_dq_kernel(const __nv_bfloat16* __restrict__ dq_part, const int* __restrict__ indices, int64_t s0,
                                       int64_t s1, int64_t s2, int64_t s3, __nv_bfloat16* __restrict__ dq, int B, int H, int G,
-                                      int Tq, int Tk, int nslots, int lprime, float scale, int q0) {
+                                      int Tq, int Tk, int nslots, int lprime, float scale, int q0,
+                                      const __nv_bfloat16* __restrict__ add0, const __nv_bfloat16* __restrict__ add1) {
   // consecutive warps take the heads of one (group, query): together they stream that query's contiguous block of partials
   const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -597,8 +614,10 @@ __global__ void slc_combine_dq_kernel(const __nv_bfloat16* __restrict__ dq_part,
     }
   }
 #pragma unroll
-  for (int c = 0; c < DK / 64; ++c)
-    *reinterpret_cast<__nv_bfloat162*>(dq + row * DK + c * 64 + lane * 2) = __floats2bfloat162_rn(acc[2 * c] * scale, acc[2 * c + 1] * scale);
+  for (int c = 0; c < DK / 64; ++c) {
+    const int64_t at = row * DK + c * 64 + lane * 2;
+    *reinterpret_cast<__nv_bfloat162*>(dq + at) = slc_dq_total(acc[2 * c] * scale, acc[2 * c + 1] * scale, add0, add1, at);
+  }
 }
 
 // Same sum with the query's contiguous block of partials ([slots][heads][dk]) brought in by one bulk copy:
@@ -606,7 +625,8 @@ __global__ void slc_combine_dq_kernel(const __nv_bfloat16* __restrict__ dq_part,
 template <int DK>
 __global__ void slc_combine_dq_bulk_kernel(const __nv_bfloat16* __restrict__ dq_part, const int* __restrict__ indices, int64_t s0,
                                            int64_t s1, int64_t s2, int64_t s3, __nv_bfloat16* __restrict__ dq, int B, int H, int G,
-                                           int Tq, int Tk, int nslots, int lprime, float scale, int q0, int* timeouts) {
+                                           int Tq, int Tk, int nslots, int lprime, float scale, int q0, int* timeouts,
+                                           const __nv_bfloat16* __restrict__ add0, const __nv_bfloat16* __restrict__ add1) {
   extern __shared__ __align__(128) uint8_t sm_part[];
   __shared__ uint64_t bar;
   __shared__ int abort_flag;
@@ -643,8 +663,10 @@ __global__ void slc_combine_dq_bulk_kernel(const __nv_bfloat16* __restrict__ dq_
       }
     }
 #pragma unroll
-    for (int c = 0; c < DK / 64; ++c)
-      *reinterpret_cast<__nv_bfloat162*>(dq + row * DK + c * 64 + lane * 2) = __floats2bfloat162_rn(acc[2 * c] * scale, acc[2 * c + 1] * scale);
+    for (int c = 0; c < DK / 64; ++c) {
+      const int64_t at = row * DK + c * 64 + lane * 2;
+      *reinterpret_cast<__nv_bfloat162*>(dq + at) = slc_dq_total(acc[2 * c] * scale, acc[2 * c + 1] * scale, add0, add1, at);
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0 && abort_flag && timeouts) atomicAdd(timeouts, 1);
@@ -1333,6 +1355,8 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   }
   if (int rc = check_launch("slc_bwd_fused_sm100")) return rc;
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
+  const void *add0 = nullptr, *add1 = nullptr;
+  dq_addends(&add0, &add1);   // dQ of the other branches, set for this call through nsa_set_dq_addends
   {
     KernelTimer kt("slc_combine_dq", st);
     const size_t qbytes = (size_t)p.nslots * p.hpg * DK * 2;  // one query's partials
@@ -1341,10 +1365,12 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
       if (cudaFuncSetAttribute(kc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qbytes) != cudaSuccess)
         return fail(NSA_ERR_LAUNCH, "slc_combine_dq: cannot reserve shared memory");
       kc<<<(unsigned)((int64_t)p.B * p.G * p.Tq), p.hpg * 32, qbytes, st>>>(p.dq_part, indices, sidx[0], sidx[1], sidx[2], sidx[3], dq, p.B,
-                                                                        p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale, p.q0, p.timeouts);
+                                                                        p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale, p.q0, p.timeouts,
+                                                                        (const __nv_bfloat16*)add0, (const __nv_bfloat16*)add1);
     } else {
       slc_combine_dq_kernel<DK><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.dq_part, indices, sidx[0], sidx[1], sidx[2], sidx[3], dq,
-                                                                            p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale, p.q0);
+                                                                            p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.scale, p.q0,
+                                                                            (const __nv_bfloat16*)add0, (const __nv_bfloat16*)add1);
     }
   }
   if (int rc = check_launch("slc_combine_dq")) return rc;

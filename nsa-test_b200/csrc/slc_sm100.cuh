@@ -5,6 +5,9 @@
 
 namespace nsa {
 
+// dQ of the other branches that the next selection backward of this thread adds to its own (set through the C ABI)
+void dq_addends(const void** a, const void** b);
+
 // bf16, canonical contiguous layouts, 64-key selection blocks, heads-per-group dividing 128
 bool slc_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime);
 

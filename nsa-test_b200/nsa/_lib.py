@@ -33,6 +33,7 @@ PROTOTYPES = {
     "nsa_last_error": (c_char_p, []),
     "nsa_version": (c_char_p, []),
     "nsa_set_kernel_family": (c_int, [c_int]),
+    "nsa_set_dq_addends": (c_int, [c_void_p, c_void_p]),
     "nsa_set_query_offset": (c_int, [c_int]),
     "nsa_profile_enable": (c_int, [c_int]),
     "nsa_profile_report": (c_int, [ctypes.c_char_p, c_size_t]),

@@ -141,7 +141,9 @@ def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float, q_pos0: int = 0):
     return o, L, M
 
 
-def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float, q_pos0: int = 0):
+def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float, q_pos0: int = 0, dq_addends=()):
+    """``dq_addends``: up to two tensors shaped and typed like q (the dQ of the other branches) that the kernel adds
+    to the selection branch's dQ before the one rounding of the sum."""
     dev = require_cuda(q, k, v, indices_i32, o, do, L, M)
     B, H, Tq, dk = q.shape
     G, Tkv, dv = k.shape[1], k.shape[-1], v.shape[-1]
@@ -149,14 +151,19 @@ def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float, q_pos
     if do.stride() != o.stride():
         do = do.contiguous()
         o = o.contiguous()
-    dq = torch.empty_like(q)
+    dq = torch.empty_like(q, memory_format=torch.contiguous_format)
     dkey = torch.zeros(B, G, Tkv, dk, device=dev, dtype=q.dtype)
     dval = torch.zeros(B, G, Tkv, dv, device=dev, dtype=q.dtype)
     nbytes = lib.nsa_slc_bwd_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n, int(l_prime), dtype_code(q))
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     s = (_fwd_strides(q, k, v, o, L, M) + list(dq.stride()) + list(dkey.stride()) + list(dval.stride())
          + list(indices_i32.stride()))
+    adds = [a.contiguous() for a in dq_addends]
+    if any(a.shape != q.shape or a.dtype != q.dtype or a.device != q.device for a in adds) or len(adds) > 2:
+        raise ValueError("slc_bwd: dq_addends must be at most two tensors shaped and typed like q")
     with torch.cuda.device(dev), query_offset(q_pos0):
+        if adds:
+            check(lib.nsa_set_dq_addends(ptr(adds[0]), ptr(adds[1]) if len(adds) > 1 else None), "nsa_set_dq_addends")
         check(lib.nsa_slc_bwd(ptr(q), ptr(k), ptr(v), ptr(indices_i32), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq),
                               ptr(dkey), ptr(dval), i64(s), B, H, G, Tq, Tkv, n, int(l_prime), dk, dv, float(scale),
                               dtype_code(q), ptr(ws), nbytes, stream_ptr(dev)), "nsa_slc_bwd")

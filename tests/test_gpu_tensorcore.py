@@ -339,3 +339,28 @@ def test_ragged_bf16_sequence_runs_on_padded_tiles():
         assert max_abs(out.float(), r["out"]) < 2e-2
         for a, b in zip(grads, gref[:3]):
             assert max_abs(a.float(), b) < 2e-2 * max(1.0, b.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype,T", [(torch.bfloat16, 1024), (torch.float32, 300)])
+def test_selection_backward_adds_the_other_branches_dq(dtype, T):
+    """nsa_set_dq_addends: dq = dq_selection + a + b, summed in fp32 and rounded once (tensor-core and generic paths)."""
+    from nsa import ops
+    B, H, G, dk, dv, n = 1, 16, 1, 64, 64, 8
+    gen = torch.Generator().manual_seed(12)
+    q, k, v, do = (t.to(DEV, dtype) for t in _inputs(B, H, G, T, dk, dv, seed=12))
+    idx = _random_indices(B, G, T, n, 64, gen, with_holes=False).to(DEV)
+    a, b_ = (torch.randn(B, H, T, dk, generator=gen).to(DEV, dtype) for _ in range(2))
+    scale = dk ** -0.5
+    o, L, M = ops.slc_fwd(q, k, v, idx, 64, scale)
+    plain = ops.slc_bwd(q, k, v, idx, o, do, L, M, 64, scale)
+    both = ops.slc_bwd(q, k, v, idx, o, do, L, M, 64, scale, dq_addends=(a, b_))
+    one = ops.slc_bwd(q, k, v, idx, o, do, L, M, 64, scale, dq_addends=(a,))
+    again = ops.slc_bwd(q, k, v, idx, o, do, L, M, 64, scale)          # the addends served one call only
+    torch.cuda.synchronize()
+    _no_timeouts()
+    assert torch.equal(again[0], plain[0]) and torch.equal(both[1], plain[1]) and torch.equal(both[2], plain[2])
+    tol = 4e-2 if dtype == torch.bfloat16 else 1e-5
+    want = plain[0].float() + a.float() + b_.float()
+    assert max_abs(both[0].float(), want) < tol * max(1.0, want.abs().max().item())
+    want1 = plain[0].float() + a.float()
+    assert max_abs(one[0].float(), want1) < tol * max(1.0, want1.abs().max().item())
