@@ -337,31 +337,34 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok) {
       tc_fence_after();
       __nv_bfloat16* dst = p.dq + row * DK + gsel * (DK / 2);
+      // dQ goes to registers in one go and is handed back at once: the first dQ MMA of the next item may overwrite it
+      // while this warp converts and stores.
+      uint32_t ov[DK / 64][32];
+      if (ntiles > 0) {
+#pragma unroll
+        for (int c = 0; c < DK / 64; ++c) tmem_ld32(tmem + lane_base + cdQ + gsel * (DK / 2) + c * 32, ov[c]);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&bar->dq_free);
+      } else {
+#pragma unroll
+        for (int c = 0; c < DK / 64; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[c][e] = 0;
+      }
 #pragma unroll
       for (int c = 0; c < DK / 64; ++c) {
-        uint32_t ov[32];
-        if (ntiles > 0) {
-          tmem_ld32(tmem + lane_base + cdQ + gsel * (DK / 2) + c * 32, ov);
-          tc_wait_ld();
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) ov[e] = 0;
-        }
 #pragma unroll
         for (int e = 0; e < 32; e += 8) {
-          uint4 w;
-          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[e]) * p.scale, __uint_as_float(ov[e + 1]) * p.scale);
-          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2]) * p.scale, __uint_as_float(ov[e + 3]) * p.scale);
-          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 4]) * p.scale, __uint_as_float(ov[e + 5]) * p.scale);
-          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[e + 6]) * p.scale, __uint_as_float(ov[e + 7]) * p.scale);
-          w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
-          w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
-          *reinterpret_cast<uint4*>(dst + c * 32 + e) = w;
+          uint4 pkt;
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[c][e]) * p.scale, __uint_as_float(ov[c][e + 1]) * p.scale);
+          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[c][e + 2]) * p.scale, __uint_as_float(ov[c][e + 3]) * p.scale);
+          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[c][e + 4]) * p.scale, __uint_as_float(ov[c][e + 5]) * p.scale);
+          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[c][e + 6]) * p.scale, __uint_as_float(ov[c][e + 7]) * p.scale);
+          pkt.x = *reinterpret_cast<uint32_t*>(&a0); pkt.y = *reinterpret_cast<uint32_t*>(&a1);
+          pkt.z = *reinterpret_cast<uint32_t*>(&a2); pkt.w = *reinterpret_cast<uint32_t*>(&a3);
+          *reinterpret_cast<uint4*>(dst + c * 32 + e) = pkt;
         }
-      }
-      if (ntiles > 0) {
-        tc_fence_before();
-        mbar_arrive(&bar->dq_free);  // dQ is in registers: the first dQ MMA of the next item may overwrite it
       }
     }
     if (ntiles > 0) { tc += ntiles; ++ic; }

@@ -365,36 +365,39 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
+      // O_i goes to registers in one go (the score registers are free by now) and is handed back at once: the first
+      // PV of the next item may overwrite it while this warp converts and stores.
+      uint32_t ov[DV / 32][32];
+      if (ntiles > 0) {
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c) tmem_ld32(tO + c * 32, ov[c]);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&bar->o_free[i]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[c][e] = 0;
+      }
 #pragma unroll
       for (int c = 0; c < DV / 32; ++c) {
-        uint32_t ov[32];
-        if (ntiles > 0) {
-          tmem_ld32(tO + c * 32, ov);
-          tc_wait_ld();
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) ov[e] = 0;
-        }
 #pragma unroll
         for (int e = 0; e < 32; e += 8) {
-          uint4 w;
-          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[e]) * inv, __uint_as_float(ov[e + 1]) * inv);
-          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2]) * inv, __uint_as_float(ov[e + 3]) * inv);
-          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 4]) * inv, __uint_as_float(ov[e + 5]) * inv);
-          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[e + 6]) * inv, __uint_as_float(ov[e + 7]) * inv);
-          w.x = *reinterpret_cast<uint32_t*>(&a0);
-          w.y = *reinterpret_cast<uint32_t*>(&a1);
-          w.z = *reinterpret_cast<uint32_t*>(&a2);
-          w.w = *reinterpret_cast<uint32_t*>(&a3);
-          *reinterpret_cast<uint4*>(orow + c * 32 + e) = w;
+          uint4 pkt;
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[c][e]) * inv, __uint_as_float(ov[c][e + 1]) * inv);
+          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[c][e + 2]) * inv, __uint_as_float(ov[c][e + 3]) * inv);
+          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[c][e + 4]) * inv, __uint_as_float(ov[c][e + 5]) * inv);
+          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[c][e + 6]) * inv, __uint_as_float(ov[c][e + 7]) * inv);
+          pkt.x = *reinterpret_cast<uint32_t*>(&a0);
+          pkt.y = *reinterpret_cast<uint32_t*>(&a1);
+          pkt.z = *reinterpret_cast<uint32_t*>(&a2);
+          pkt.w = *reinterpret_cast<uint32_t*>(&a3);
+          *reinterpret_cast<uint4*>(orow + c * 32 + e) = pkt;
         }
       }
       if (p.L) p.L[row] = l > 0.f ? logf(l) + (m_ref - m_true) * kLn2 : -CUDART_INF_F;
       if (p.M) p.M[row] = m_true * kLn2;  // back from log2 units to the natural-log scale of the logits
-      if (ntiles > 0) {
-        tc_fence_before();
-        mbar_arrive(&bar->o_free[i]);  // O_i is in registers: the first PV of the next item may overwrite it
-      }
     }
     tc += ntiles;
     }  // items
