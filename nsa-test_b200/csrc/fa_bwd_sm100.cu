@@ -380,7 +380,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------
-// dK/dV kernel: 128 keys per CTA, loops over (head, 64-query sub-tile); transposed tiles in TMEM
+// dK/dV kernel: 128 keys per CTA, loops over (head, 64-query sub-tile); transposed tiles in TMEM.
+// 320 threads: warps 0-3 / 4-7 turn the two 32-query halves of S^T, dP^T into P^T, dS^T; warp 8 TMA; warp 9 UMMA.
 // ------------------------------------------------------------------------------------------------
 template <int DK, int DV>
 struct DkvSmem {
@@ -397,7 +398,7 @@ struct DkvBarriers {
 };
 
 template <int DK, int DV, int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FaBwdParams p) {
   using SM = DkvSmem<DK, DV>;
@@ -431,24 +432,25 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(&bar->kv_full, 1);
     for (int i = 0; i < 3; ++i) { mbar_init(&bar->full[i], 2); mbar_init(&bar->empty[i], 1); }
     mbar_init(&bar->stp_full, 1);
-    mbar_init(&bar->st_free, 128);
-    mbar_init(&bar->pds_full, 128);
+    mbar_init(&bar->st_free, 256);
+    mbar_init(&bar->pds_full, 256);
     mbar_init(&bar->pds_free, 1);
     mbar_init(&bar->acc_done, 1);
     bar->abort = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 5) tmem_alloc(&bar->tmem_base, 512);
+  if (warp == 9) tmem_alloc(&bar->tmem_base, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
   // fp32 S^T / dP^T tiles and their bf16 successors P^T / dS^T have separate columns, so the next tile's
-  // S^T / dP^T can be produced while this tile's P^T / dS^T are still being consumed
-  constexpr uint32_t cdK = 0, cdV = DK, cST = DK + DV, cdPT = DK + DV + 64, cP = DK + DV + 128, cdS = DK + DV + 160;
+  // S^T / dP^T can be produced while this tile's P^T / dS^T are still being consumed.  The bf16 columns are laid out per
+  // compute group (queries [0,32) and [32,64) of the sub-tile): P^T of the group (16 columns), then its dS^T (16).
+  constexpr uint32_t cdK = 0, cdV = DK, cST = DK + DV, cdPT = DK + DV + 64, cPS = DK + DV + 128;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // producer: the whole warp takes part (lanes fill the per-query statistics), one elected lane drives TMA
     if (n_it > 0) {
       if (elect_one()) {
@@ -489,7 +491,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int it = max(0, issued - 3); it < issued; ++it) mbar_wait(&bar->full[it % 3], (it / 3) & 1, abort);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // UMMA issuer: warp-uniform loop, one elected lane issues
     if (n_it > 0) {
       constexpr uint32_t idST = idesc_bf16(128, 64, 1, 0);    // K tile as A (MN-major: keys contiguous) x Q sub-tile (K-major)
@@ -531,10 +533,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ts(tmem + cdV, tmem + cP + kk * 8, desc_advance(dOmn, kk * 2048), iddV, (it > 0) || (kk > 0));
+            umma_ts(tmem + cdV, tmem + cPS + (kk >> 1) * 32 + (kk & 1) * 8, desc_advance(dOmn, kk * 2048), iddV, (it > 0) || (kk > 0));
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ts(tmem + cdK, tmem + cdS + kk * 8, desc_advance(dQmn, kk * 2048), iddK, (it > 0) || (kk > 0));
+            umma_ts(tmem + cdK, tmem + cPS + (kk >> 1) * 32 + 16 + (kk & 1) * 8, desc_advance(dQmn, kk * 2048), iddK, (it > 0) || (kk > 0));
           umma_commit(&bar->empty[s]);
           umma_commit(&bar->pds_free);
         }
@@ -548,8 +550,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
     }
   } else {
-    const int r = warp * 32 + lane, key = n0 + r;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // warps 0-3 / 4-7: queries [0,32) / [32,64) of every sub-tile, the same 128 key rows
+    const int gsel = warp >> 2;
+    const int r = (warp & 3) * 32 + lane, key = n0 + r;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     int s = -1, ph = 0, qs = qs_lo - 1;
     for (int it = 0; it < n_it && ok; ++it) {
@@ -570,40 +574,35 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         chi = 0x40000000;
       }
       const bool allvis = clo <= 0 && chi >= 63;  // this key sees all 64 queries of the sub-tile
-      uint32_t sT[2][32], dpT[2][32];
-      tmem_ld32(tmem + lane_base + cST, sT[0]);
-      tmem_ld32(tmem + lane_base + cST + 32, sT[1]);
-      tmem_ld32(tmem + lane_base + cdPT, dpT[0]);
-      tmem_ld32(tmem + lane_base + cdPT + 32, dpT[1]);
+      uint32_t sT[32], dpT[32];
+      tmem_ld32(tmem + lane_base + cST + gsel * 32, sT);
+      tmem_ld32(tmem + lane_base + cdPT + gsel * 32, dpT);
       tc_wait_ld();
       tc_fence_before();
       mbar_arrive(&bar->st_free);   // the fp32 tiles may be overwritten by the next iteration's MMAs
-      uint32_t pk[32], dk_[32];
+      uint32_t pk[32];  // [0,16): P^T of this group's 32 queries, [16,32): dS^T
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int c0 = c * 32 + 2 * e;
-          const float l0 = stat[c0], l1 = stat[c0 + 1], D0 = stat[64 + c0], D1 = stat[64 + c0 + 1];
-          float p0 = ex2(fmaf(__uint_as_float(sT[c][2 * e]), p.scale_log2, -l0));
-          float p1 = ex2(fmaf(__uint_as_float(sT[c][2 * e + 1]), p.scale_log2, -l1));
-          if (!allvis) {
-            p0 = (c0 >= clo && c0 <= chi) ? p0 : 0.f;
-            p1 = (c0 + 1 >= clo && c0 + 1 <= chi) ? p1 : 0.f;
-          }
-          const float s0 = p0 * (__uint_as_float(dpT[c][2 * e]) - D0), s1 = p1 * (__uint_as_float(dpT[c][2 * e + 1]) - D1);
-          __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1), y = __floats2bfloat162_rn(s0, s1);
-          pk[c * 16 + e] = *reinterpret_cast<uint32_t*>(&x);
-          dk_[c * 16 + e] = *reinterpret_cast<uint32_t*>(&y);
+      for (int e = 0; e < 16; ++e) {
+        const int c0 = gsel * 32 + 2 * e;
+        const float l0 = stat[c0], l1 = stat[c0 + 1], D0 = stat[64 + c0], D1 = stat[64 + c0 + 1];
+        float p0 = ex2(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0));
+        float p1 = ex2(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1));
+        if (!allvis) {
+          p0 = (c0 >= clo && c0 <= chi) ? p0 : 0.f;
+          p1 = (c0 + 1 >= clo && c0 + 1 <= chi) ? p1 : 0.f;
         }
+        const float s0 = p0 * (__uint_as_float(dpT[2 * e]) - D0), s1 = p1 * (__uint_as_float(dpT[2 * e + 1]) - D1);
+        __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1), y = __floats2bfloat162_rn(s0, s1);
+        pk[e] = *reinterpret_cast<uint32_t*>(&x);
+        pk[16 + e] = *reinterpret_cast<uint32_t*>(&y);
+      }
       // P^T / dS^T of the previous iteration must have been consumed before they are overwritten
       if (it > 0) {
         ok = mbar_wait(&bar->pds_free, (it - 1) & 1, abort);
         if (!ok) break;
         tc_fence_after();
       }
-      tmem_st32(tmem + lane_base + cP, pk);
-      tmem_st32(tmem + lane_base + cdS, dk_);
+      tmem_st32(tmem + lane_base + cPS + gsel * 32, pk);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bar->pds_full);
@@ -613,7 +612,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_after();
       const int64_t krow = ((int64_t)b * p.G + g) * p.Tk + key;
       auto flush = [&](uint32_t col0, int width, float mul, __nv_bfloat16* out_bf, float* out_part) {
-        for (int c = 0; c < width / 32; ++c) {
+        for (int c = gsel * (width / 64); c < (gsel + 1) * (width / 64); ++c) {   // each compute group flushes half of the columns
           uint32_t ov[32];
           if (n_it > 0) {
             tmem_ld32(tmem + lane_base + col0 + c * 32, ov);
@@ -647,7 +646,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -703,7 +702,7 @@ static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, con
   }
   if (int rc = check_launch("fa_bwd_dq_sm100")) return rc;
   KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);
-  kkv<<<dim3(p.Tk / 128, p.hsplit, p.B * p.G), 192, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, p);
+  kkv<<<dim3(p.Tk / 128, p.hsplit, p.B * p.G), 320, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, p);
   return check_launch("fa_bwd_dkv_sm100");
 }
 
