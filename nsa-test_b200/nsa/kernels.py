@@ -237,7 +237,21 @@ class _PhiCompress(torch.autograd.Function):
         nbp = _next_pow2(nb)
         w1k, w1p = w1[:, :dk].float(), w1[:, dk:].float()
         c = torch.addmm(b1.float(), pos_embed.float(), w1p.t())                     # [l,U]
-        a = torch.matmul(keys.float(), w1k.t())                                     # [B,G,T,U]
+        kt = keys.transpose(-1, -2)                                                 # [B,G,dk,T], usually K as it lies
+        if keys.dtype == torch.bfloat16 and keys.is_cuda and kt.is_contiguous():
+            # fp32-exact product on the tensor cores: the keys are bf16 already, and a weight is the sum of three bf16
+            # terms (8 + 8 + 8 mantissa bits), so [k k k] x [hi; mid; lo] holds exactly the products of the fp32 GEMM,
+            # accumulated in fp32.  This product decides the top-n, so nothing is rounded away.
+            hi = w1k.to(torch.bfloat16)
+            r1 = w1k - hi.float()
+            mid = r1.to(torch.bfloat16)
+            lo = (r1 - mid.float()).to(torch.bfloat16)
+            w3 = torch.cat([hi, mid, lo], dim=1)                                    # [U, 3dk]
+            k3 = torch.cat([kt, kt, kt], dim=2).reshape(B * G, 3 * dk, T)
+            a = torch.bmm(k3.transpose(1, 2), w3.t().unsqueeze(0).expand(B * G, -1, -1),
+                          out_dtype=torch.float32).view(B, G, T, -1)
+        else:
+            a = torch.matmul(keys.float(), w1k.t())                                 # [B,G,T,U]
         hbar, v_cmp = ops.phi_pool_fwd(a, c, values, l, d, nb, nbp)
         kc = torch.matmul(hbar, w2.float().t()) + b2.float()                        # [B,G,nb,dk]
         k_cmp = torch.zeros(B, G, dk, nbp, device=keys.device, dtype=torch.float32)
