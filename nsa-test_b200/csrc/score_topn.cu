@@ -7,6 +7,7 @@
 // count), select_top_k_blocks_per_query_with_gqa (nsa/kernels.py:1986-2040: heads summed in order,
 // stable descending sort so ties go to the lower block id, fixed blocks first, repeats dropped,
 // -1 padding).  Nothing of size [B,H,T,n_cmp] ever reaches HBM: one CTA owns one (b,g,t).
+#include <algorithm>
 #include "common.cuh"
 #include "fa_sm100.cuh"
 
@@ -82,6 +83,40 @@ __device__ void topn_and_merge(float* agg, int n_sel, int t, int l_prime, int n,
   }
 }
 
+// A handful of query rows (decode): the q.k products of every head against every visible compressed block, one thread
+// per block and all heads of the group in registers, so that the keys are read once per row and the work spreads over
+// (blocks / 128) x (group, row) CTAs instead of one CTA per row.  Same fmaf chain over the head dimension as the row
+// kernel's own loop.
+template <typename T, int HPG>
+__global__ void __launch_bounds__(128)
+score_logits_kernel(const T* __restrict__ q, int64_t sqz, int64_t sqh, int64_t sqm, int64_t sqk, const float* __restrict__ kc,
+                    const int* __restrict__ block_ends, float* __restrict__ logits, int H, int G, int T_, int dk, int nbp,
+                    int q0) {
+  extern __shared__ float qsm[];        // [HPG][dk]
+  const int tq = blockIdx.z, bg = blockIdx.y, b = bg / G, g = bg % G;
+  const int t = q0 + tq;
+  for (int i = threadIdx.x; i < HPG * dk; i += 128) {
+    const int hh = i / dk, d = i % dk;
+    qsm[i] = Elem<T>::ld(q + b * sqz + (int64_t)(g * HPG + hh) * sqh + (int64_t)tq * sqm + d * sqk);
+  }
+  __syncthreads();
+  const int i = blockIdx.x * 128 + threadIdx.x;
+  if (i >= nbp || block_ends[i] > t) return;   // hidden blocks are never read back
+  const float* kb = kc + (int64_t)bg * dk * nbp + i;
+  float acc[HPG];
+#pragma unroll
+  for (int u = 0; u < HPG; ++u) acc[u] = 0.f;
+#pragma unroll 8
+  for (int d = 0; d < dk; ++d) {
+    const float kv = __ldg(kb + (int64_t)d * nbp);
+#pragma unroll
+    for (int u = 0; u < HPG; ++u) acc[u] = fmaf(qsm[u * dk + d], kv, acc[u]);
+  }
+  float* dst = logits + (((int64_t)bg * T_ + tq) * HPG) * nbp + i;
+#pragma unroll
+  for (int u = 0; u < HPG; ++u) dst[(int64_t)u * nbp] = acc[u];
+}
+
 // HB heads share one sweep over the compressed keys (each key element is loaded once per HB heads); the softmax
 // and the Eq. 9 sums then run head by head in head order, so the result does not depend on HB.
 template <typename T, int HB>
@@ -89,7 +124,7 @@ __global__ void __launch_bounds__(kThreads)
 score_topn_kernel(const T* __restrict__ q, int64_t sqz, int64_t sqh, int64_t sqm, int64_t sqk,
                   const float* __restrict__ kc, const int* __restrict__ block_ends, int32_t* __restrict__ out, int H,
                   int G, int T_, int dk, int nbp, int a_, int s_, int n_sel, int l_prime, int n, int n_fixed,
-                  float scale, int q0) {
+                  float scale, int q0, const float* __restrict__ logits) {
   extern __shared__ float sm[];
   const int tq = blockIdx.x, bg = blockIdx.y, b = bg / G, g = bg % G, hpg = H / G;
   const int t = q0 + tq;                // position of query row tq
@@ -110,12 +145,17 @@ score_topn_kernel(const T* __restrict__ q, int64_t sqz, int64_t sqh, int64_t sqm
   __syncthreads();
   const float* kb = kc + (int64_t)bg * dk * nbp;
   for (int h0 = 0; h0 < hpg; h0 += HB) {
+    // logits given: q.k products [hpg][nbp] of this (group, row) from score_logits_kernel (same sums, same order)
+    const float* lrow = logits ? logits + (((int64_t)bg * T_ + tq) * hpg + h0) * nbp : nullptr;
     for (int i = threadIdx.x; i < nbp; i += kThreads) {
       float acc[HB];
 #pragma unroll
       for (int u = 0; u < HB; ++u) acc[u] = 0.f;
       const bool vis = block_ends[i] <= t;
-      if (vis) {
+      if (vis && lrow) {
+#pragma unroll
+        for (int u = 0; u < HB; ++u) acc[u] = lrow[(int64_t)u * nbp + i];
+      } else if (vis) {
 #pragma unroll 8
         for (int d = 0; d < dk; ++d) {
           const float kv = __ldg(kb + (int64_t)d * nbp + i);
@@ -194,10 +234,19 @@ static bool score_tc_ok(const void* q, const int64_t* qs, int B, int H, int G, i
   return (reinterpret_cast<uintptr_t>(q) & 15) == 0;
 }
 
+// few query rows (decode): q.k products staged in the workspace by score_logits_kernel
+static constexpr int kFewRows = 64;
+static size_t few_rows_logit_bytes(int B, int H, int G, int T, int nbp) {
+  if (B <= 0 || G <= 0 || T <= 0 || H % G != 0 || (int64_t)B * G * T > kFewRows) return 0;
+  const int hpg = H / G;
+  if (hpg != 1 && hpg != 2 && hpg != 4 && hpg != 8 && hpg != 16) return 0;
+  return (size_t)B * G * T * hpg * nbp * sizeof(float);
+}
+
 extern "C" NSA_API size_t nsa_score_topn_workspace_bytes(int B, int H, int G, int T, int dk, int nbp, int l, int d, int l_prime,
                                                          int n, int dtype) {
   if (B <= 0 || G <= 0 || dtype != NSA_BF16 || nsa::kernel_family() != 0 || !score_sm100_supported(H, G, T, dk, nbp, l, d, l_prime, n))
-    return 256;
+    return std::max<size_t>(256, few_rows_logit_bytes(B, H, G, T, nbp));
   return score_sm100_workspace_bytes(B, G, T, dk, nbp, d, l_prime);
 }
 
@@ -221,15 +270,39 @@ extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const fl
   if (sm > 200 * 1024) return fail(NSA_ERR_UNSUPPORTED, "score_topn: %zu bytes of shared memory needed", sm);
   if (dtype != NSA_F32 && dtype != NSA_BF16) return fail(NSA_ERR_ARG, "score_topn: unsupported dtype %d", dtype);
   cudaStream_t st = (cudaStream_t)stream;
+  const int q0 = nsa::query_pos0();
+  const float* logits = nullptr;
+  const size_t lbytes = few_rows_logit_bytes(B, H, G, T, nbp);
+  if (lbytes > 0 && workspace && workspace_bytes >= lbytes && (size_t)hpg * dk * sizeof(float) <= 48 * 1024) {
+    KernelTimer ktl("score_logits", st);
+    const dim3 lgrid((nbp + 127) / 128, B * G, T);
+    const size_t lsm = (size_t)hpg * dk * sizeof(float);
+    float* lw = (float*)workspace;
+#define NSA_LOGITS(TYPE, HPG_)                                                                                       \
+  score_logits_kernel<TYPE, HPG_><<<lgrid, 128, lsm, st>>>((const TYPE*)q, qs[0], qs[1], qs[2], qs[3], k_cmp, block_ends, \
+                                                           lw, H, G, T, dk, nbp, q0)
+#define NSA_LOGITS_T(TYPE)                                                                        \
+  switch (hpg) {                                                                                  \
+    case 1: NSA_LOGITS(TYPE, 1); break;                                                           \
+    case 2: NSA_LOGITS(TYPE, 2); break;                                                           \
+    case 4: NSA_LOGITS(TYPE, 4); break;                                                           \
+    case 8: NSA_LOGITS(TYPE, 8); break;                                                           \
+    default: NSA_LOGITS(TYPE, 16); break;                                                         \
+  }
+    if (dtype == NSA_F32) { NSA_LOGITS_T(float) } else { NSA_LOGITS_T(__nv_bfloat16) }
+#undef NSA_LOGITS_T
+#undef NSA_LOGITS
+    if (int rc = check_launch("score_logits")) return rc;
+    logits = lw;
+  }
   KernelTimer kt("score_topn", st);
   dim3 grid(T, B * G);
-  const int q0 = nsa::query_pos0();
 #define NSA_SCORE_LAUNCH(TYPE, HB_)                                                                                    \
   do {                                                                                                                 \
     cudaFuncSetAttribute(score_topn_kernel<TYPE, HB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);          \
     score_topn_kernel<TYPE, HB_><<<grid, kThreads, sm, st>>>((const TYPE*)q, qs[0], qs[1], qs[2], qs[3], k_cmp,        \
                                                              block_ends, indices_out, H, G, T, dk, nbp, a_, s_, n_sel, \
-                                                             l_prime, n, n_fixed, scale, q0);                          \
+                                                             l_prime, n, n_fixed, scale, q0, logits);                  \
   } while (0)
   if (dtype == NSA_F32) {
     if (hb == 4) NSA_SCORE_LAUNCH(float, 4); else if (hb == 2) NSA_SCORE_LAUNCH(float, 2); else NSA_SCORE_LAUNCH(float, 1);

@@ -24,6 +24,7 @@ from .kernels import NSAConfig, PAD_BLOCK_END, _PhiCompress, _next_pow2, _projec
 __all__ = ["NSACache", "nsa_layer_incremental", "module_forward_incremental"]
 
 _TILE = 128
+_FEW_ROWS = 64       # (sequence, group, row) count up to which scoring takes the unpadded rows
 
 
 def _round_up(x: int, m: int) -> int:
@@ -129,7 +130,15 @@ def nsa_layer_incremental(q_new: torch.Tensor, gate_logits_new: torch.Tensor, ca
     n_fixed = c.n_fixed if c.include_fixed_in_selection else 0
     nb = cache.n_blocks
 
-    indices = ops.score_topn(q, cache.k_cmp, cache.block_ends, c.l, c.d, c.l_prime, c.n, n_fixed, scale, nb, pos)
+    G = c.n_kv_groups
+    if Tn < rows and B * G * Tn <= _FEW_ROWS:
+        # A handful of rows (decode): the tile kernel would run one CTA per (sequence, group) over all compressed
+        # blocks; unpadded rows take the generic scoring path, whose q.k products spread over the whole GPU.
+        real = ops.score_topn(q_new.contiguous(), cache.k_cmp, cache.block_ends, c.l, c.d, c.l_prime, c.n, n_fixed, scale,
+                              nb, pos)
+        indices = torch.cat([real, real.new_full((B, G, rows - Tn, c.n), -1)], dim=2)
+    else:
+        indices = ops.score_topn(q, cache.k_cmp, cache.block_ends, c.l, c.d, c.l_prime, c.n, n_fixed, scale, nb, pos)
     o_cmp, _, _ = ops.cmp_attn_fwd(q, cache.k_cmp_lp, cache.v_cmp, cache.block_ends, scale, (c.l, c.d, nb), pos)
     idx = _selection_fallback(indices, c.l_prime, pos).to(torch.int32).contiguous()
     o_slc, _, _ = ops.slc_fwd(q, cache.k_slc, cache.v_slc, idx, c.l_prime, scale, pos)
