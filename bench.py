@@ -246,6 +246,43 @@ def run_reference(args):
 # GPU arm
 # --------------------------------------------------------------------------------------------------
 
+def run_decode(args):
+    """Single-token forward steps of one layer against a KV + compressed-KV cache of --T tokens (batch 1)."""
+    import nsa
+    from nsa.incremental import NSACache, nsa_layer_incremental
+    from nsa._lib import lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    c, T, N = CFG, args.T, args.decode
+    cfg = nsa.NSAConfig(d_model=c["d_model"], head_dim_qk=c["dk"], head_dim_v=c["dv"], l=c["l"], d=c["d"], l_prime=c["l_prime"],
+                        n=c["n"], w=c["w"], n_heads=c["H"], n_kv_groups=c["G"])
+    g = torch.Generator(device=dev).manual_seed(0)
+    rn = lambda *sh, std=1.0: torch.randn(*sh, generator=g, device=dev) * std
+    H, G, dk, dv, l = c["H"], c["G"], c["dk"], c["dv"], c["l"]
+    phi = (rn(l, l, std=0.02), rn(2 * dk, dk + l, std=0.02), torch.zeros(2 * dk, device=dev), rn(dk, 2 * dk, std=0.02),
+           torch.zeros(dk, device=dev))
+    warm = max(args.warmup, 3)
+    cache = NSACache(cfg, 1, T, dev, shared_kv=True)
+    pre = T - N - warm
+    cache.append(phi, rn(1, G, dk, pre).bfloat16(), rn(1, G, pre, dv).bfloat16())
+    toks = [(rn(1, G, dk, 1).bfloat16(), rn(1, G, 1, dv).bfloat16(), rn(1, H, 1, dk).bfloat16(), rn(1, 1, 3 * H))
+            for _ in range(N + warm)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i, (kn, vn, qn, lg) in enumerate(toks):
+        if i == warm:
+            torch.cuda.synchronize()
+            e0.record()
+        cache.append(phi, kn, vn)
+        out = nsa_layer_incremental(qn, lg, cache)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / N
+    print(json.dumps(dict(metric="NSA layer decode step (cache append + one-token forward), ms per token", value=round(ms, 4),
+                          unit="ms", n_gpus=1, steps=N, warmup=warm, higher_is_better=False, dtype="bf16", data="synthetic",
+                          config=dict(workload=f"one layer, batch 1, cache of {T} tokens", **c),
+                          checksum=float(out.float().sum()), device_timeouts=lib.nsa_device_timeouts(0))))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -259,9 +296,14 @@ def main():
     ap.add_argument("--shard", default="sequence", choices=["sequence", "query"],
                     help="sequence: one T-token sequence per GPU (weak scaling, the default); query: ONE T-token sequence "
                          "split by position over the GPUs, K/V all-gathered (long-context mode, strong scaling)")
+    ap.add_argument("--decode", type=int, default=0, metavar="N",
+                    help="instead of the training step: time N single-token forward steps of one layer against a cache of "
+                         "--T tokens (nsa.incremental) and print their own JSON line")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.decode > 0:
+        return run_decode(args)
 
     import nsa
     from nsa import _lib
