@@ -220,6 +220,19 @@ NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, const void* 
                      const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits,
                      int B, int H, int T, int dv, int gate_mode, int dtype, void* stream);
 
+/* Same, and also writes delta [3][B*H*T] (fp32): the row sums dO_b . O_b of the three branches (dO_b = g_b dO), which
+ * the branch backward kernels need.  Handing them over with nsa_set_row_delta() saves each backward its own pass over
+ * O and dO. */
+NSA_API int nsa_gate_mix_bwd_delta(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
+                                   const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits,
+                                   float* delta, int B, int H, int T, int dv, int gate_mode, int dtype, void* stream);
+
+/* The next nsa_sliding_bwd / nsa_cmp_attn_bwd / nsa_slc_bwd of this host thread takes its row sums dO . O [B,H,T] (fp32,
+ * contiguous) from `delta` instead of computing them (tensor-core path; the generic kernels compute their own).  The
+ * pointer serves that one call.  The reference computes these sums inside its backward kernels
+ * (nsa/kernels.py:1004-1010). */
+NSA_API int nsa_set_row_delta(const float* delta);
+
 #ifdef __cplusplus
 }
 #endif

@@ -84,6 +84,11 @@ int kernel_family() { return g_kernel_family; }  // 0: tensor-core kernels where
 // of the compressed attention, the scoring and the selected-block attention; every other path refuses a non-zero offset.
 static thread_local int g_query_pos0 = 0;
 int query_pos0() { return g_query_pos0; }
+// row sums dO.O of the next backward call of this thread (which clears the pointer)
+static thread_local const float* g_row_delta = nullptr;
+const float* row_delta() { return g_row_delta; }
+void clear_row_delta() { g_row_delta = nullptr; }
+struct ClearRowDelta { ~ClearRowDelta() { g_row_delta = nullptr; } };
 // dQ of the other two branches, added by the next nsa_slc_bwd of this thread (which clears them)
 static thread_local const void* g_dq_add[2] = {nullptr, nullptr};
 void dq_addends(const void** a, const void** b) { *a = g_dq_add[0]; *b = g_dq_add[1]; }
@@ -188,6 +193,11 @@ extern "C" NSA_API int nsa_set_query_offset(int position) {
   return NSA_OK;
 }
 
+extern "C" NSA_API int nsa_set_row_delta(const float* delta) {
+  g_row_delta = delta;
+  return NSA_OK;
+}
+
 extern "C" NSA_API int nsa_set_dq_addends(const void* a, const void* b) {
   g_dq_add[0] = a;
   g_dq_add[1] = b;
@@ -232,6 +242,7 @@ extern "C" NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void*
                                const float* L, const float* M, void* dq, void* dkey, void* dval,
                                const int64_t* strides, int B, int H, int G, int T, int dk, int dv, int window,
                                float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  ClearRowDelta clear_row_delta_guard;  // the caller's row sums serve this call only
   if (int rc = check_common("sliding_bwd", B, H, G, T, T, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && out && dout && L && M && dq && dkey && dval && strides, "sliding_bwd: null pointer");
   NSA_REQUIRE(window > 0, "sliding_bwd: window must be positive");
@@ -272,6 +283,7 @@ extern "C" NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const 
                                 void* dk_cmp, void* dv_cmp, const int64_t* strides, int B, int H, int G, int T, int NB,
                                 int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d, int blocks_n,
                                 void* workspace, size_t workspace_bytes, void* stream) {
+  ClearRowDelta clear_row_delta_guard;  // the caller's row sums serve this call only
   if (int rc = check_common("cmp_attn_bwd", B, H, G, T, NB, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k_cmp && v_cmp && block_ends && out && dout && L && M && dq && dk_cmp && dv_cmp && strides,
               "cmp_attn_bwd: null pointer");
@@ -329,6 +341,7 @@ extern "C" NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, 
                            const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots, int l_prime,
                            int dk, int dv, float scale, int dtype, void* workspace, size_t workspace_bytes,
                            void* stream) {
+  ClearRowDelta clear_row_delta_guard;  // the caller's row sums serve this call only
   struct ClearAddends { ~ClearAddends() { g_dq_add[0] = g_dq_add[1] = nullptr; } } clear_addends;  // they serve one call only
   if (int rc = check_common("slc_bwd", B, H, G, Tq, Tkv, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && indices && out && dout && L && M && dq && dkey && dval && strides, "slc_bwd: null pointer");

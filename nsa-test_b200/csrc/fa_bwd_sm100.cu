@@ -74,11 +74,24 @@ __global__ void fa_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __
   }
 }
 
+// the row sums dO.O come from the caller (nsa_set_row_delta): only the log-sum-exp has to be prepared
+__global__ void fa_bwd_prep_given_delta_kernel(const float* __restrict__ delta, const float* __restrict__ L, const float* __restrict__ M,
+                                               float* __restrict__ D, float* __restrict__ lse2, int64_t rows) {
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  D[row] = delta[row];
+  const float lse = M[row] + L[row];
+  lse2[row] = isfinite(lse) ? lse * kLog2e : CUDART_INF_F;
+}
+
 void launch_bwd_prep(const void* o, const void* dout, const float* L, const float* M, float* D, float* lse2, int64_t rows, int dv,
                      cudaStream_t st) {
   KernelTimer kt("bwd_prep", st);
-  fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, L, M, D, lse2,
-                                                               rows, dv);
+  if (const float* delta = row_delta())
+    fa_bwd_prep_given_delta_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(delta, L, M, D, lse2, rows);
+  else
+    fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, L, M, D, lse2,
+                                                                 rows, dv);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -732,8 +745,7 @@ int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, con
   p.window = window; p.cmp_l = cmp_l; p.cmp_d = cmp_d; p.cmp_nb = cmp_nb;
   p.scale = scale; p.scale_log2 = scale * kLog2e;
   p.timeouts = fa_timeout_counter();
-  fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, L, M, D,
-                                                               lse2, (int64_t)rows, dv);
+  launch_bwd_prep(o, dout, L, M, D, lse2, (int64_t)rows, dv, st);
   if (int rc = check_launch("fa_bwd_prep")) return rc;
   CUtensorMap tq128, tdo128, tq64, tdo64, tk, tv;
   if (int rc = make_tmap_bf16_2d(&tq128, q, (uint64_t)B * H * Tq, dk, 128)) return rc;
@@ -798,6 +810,7 @@ static int sliding_bwd_scratch_address(float** out) {
 extern "C" NSA_API int nsa_sliding_bwd_noalloc(const void* q, const void* k, const void* v, const void* out, const void* dout,
                                                const float* L, const float* M, void* dq, void* dkey, void* dval, int B, int H,
                                                int G, int T, int dk, int dv, int window, float scale, void* stream) {
+  nsa::clear_row_delta();  // this entry point always prepares its own row sums
   using namespace nsa;
   NSA_REQUIRE(q && k && v && out && dout && L && M && dq && dkey && dval, "sliding_bwd_noalloc: null pointer");
   NSA_REQUIRE(B > 0 && H > 0 && G > 0 && H % G == 0 && T > 0 && window > 0, "sliding_bwd_noalloc: bad sizes");

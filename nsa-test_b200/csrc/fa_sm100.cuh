@@ -8,6 +8,11 @@ struct CUtensorMap_st;
 
 namespace nsa {
 
+// Row sums dO.O [B,H,Tq] (fp32) handed in by the caller for the next backward call of this host thread, or null
+// (nsa_set_row_delta); the tensor-core backward then skips its own pass over O and dO.
+const float* row_delta();
+void clear_row_delta();
+
 struct FaFwdParams {
   __nv_bfloat16* o;  // [B,H,Tq,dv] contiguous
   float *L, *M;      // [B,H,Tq] contiguous, may be null

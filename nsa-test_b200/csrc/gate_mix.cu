@@ -41,7 +41,7 @@ template <typename T>
 __global__ void gate_mix_bwd_kernel(const float* __restrict__ gates, const T* __restrict__ oc, const T* __restrict__ os,
                                     const T* __restrict__ ow, const T* __restrict__ dout, T* __restrict__ doc,
                                     T* __restrict__ dos, T* __restrict__ dow, float* __restrict__ dlogits, int B, int H,
-                                    int T_, int dv, int mode) {
+                                    int T_, int dv, int mode, float* __restrict__ delta) {
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= (int64_t)B * H * T_) return;
@@ -60,6 +60,10 @@ __global__ void gate_mix_bwd_kernel(const float* __restrict__ gates, const T* __
   }
   d0 = warp_sum(d0); d1 = warp_sum(d1); d2 = warp_sum(d2);
   if (lane == 0) {
+    if (delta) {  // row sums dO_b . O_b of the three branches, dO_b = g_b dO
+      const int64_t rows = (int64_t)B * H * T_;
+      delta[row] = g0 * d0; delta[rows + row] = g1 * d1; delta[2 * rows + row] = g2 * d2;
+    }
     float* dl = dlogits + ((int64_t)b * T_ + t) * 3 * H + 3 * h;
     if (mode == NSA_GATE_SOFTMAX) {
       const float dot = g0 * d0 + g1 * d1 + g2 * d2;
@@ -130,7 +134,7 @@ __global__ void gate_mix_bwd_bf16x4_kernel(const float* __restrict__ gates, cons
                                            const __nv_bfloat16* __restrict__ os, const __nv_bfloat16* __restrict__ ow,
                                            const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ doc,
                                            __nv_bfloat16* __restrict__ dos, __nv_bfloat16* __restrict__ dow, float* __restrict__ dlogits,
-                                           int B, int H, int T_, int dv, int mode) {
+                                           int B, int H, int T_, int dv, int mode, float* __restrict__ delta) {
   const int lane = threadIdx.x & 31, hl = lane & 15;
   int64_t row = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
   const bool live = row < (int64_t)B * H * T_;  // both halves stay for the shuffles
@@ -162,6 +166,10 @@ __global__ void gate_mix_bwd_bf16x4_kernel(const float* __restrict__ gates, cons
     d2 += __shfl_xor_sync(0xffffffffu, d2, o);
   }
   if (hl == 0 && live) {
+    if (delta) {  // row sums dO_b . O_b of the three branches, dO_b = g_b dO
+      const int64_t rows = (int64_t)B * H * T_;
+      delta[row] = g0 * d0; delta[rows + row] = g1 * d1; delta[2 * rows + row] = g2 * d2;
+    }
     float* dl = dlogits + ((int64_t)b * T_ + t) * 3 * H + 3 * h;
     if (mode == NSA_GATE_SOFTMAX) {
       const float dot = g0 * d0 + g1 * d1 + g2 * d2;
@@ -200,9 +208,9 @@ extern "C" NSA_API int nsa_gate_mix_fwd(const float* logits, const void* o_cmp, 
   return check_launch("gate_mix_fwd");
 }
 
-extern "C" NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
-                                const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits, int B, int H,
-                                int T, int dv, int gate_mode, int dtype, void* stream) {
+extern "C" NSA_API int nsa_gate_mix_bwd_delta(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
+                                      const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits,
+                                      float* delta, int B, int H, int T, int dv, int gate_mode, int dtype, void* stream) {
   NSA_REQUIRE(gates && o_cmp && o_slc && o_win && dout && do_cmp && do_slc && do_win && dlogits, "gate_mix_bwd: null pointer");
   const int64_t rows = (int64_t)B * H * T;
   if (rows == 0) return NSA_OK;
@@ -212,17 +220,24 @@ extern "C" NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, c
   if (dtype == NSA_F32)
     gate_mix_bwd_kernel<float><<<grid, 256, 0, st>>>(gates, (const float*)o_cmp, (const float*)o_slc, (const float*)o_win,
                                                       (const float*)dout, (float*)do_cmp, (float*)do_slc, (float*)do_win,
-                                                      dlogits, B, H, T, dv, gate_mode);
+                                                      dlogits, B, H, T, dv, gate_mode, delta);
   else if (dtype == NSA_BF16 && dv % 128 == 0)
     gate_mix_bwd_bf16x4_kernel<<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(gates, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc,
                                                      (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)dout, (__nv_bfloat16*)do_cmp,
-                                                     (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, dlogits, B, H, T, dv, gate_mode);
+                                                     (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, dlogits, B, H, T, dv, gate_mode, delta);
   else if (dtype == NSA_BF16)
     gate_mix_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
         gates, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win,
         (const __nv_bfloat16*)dout, (__nv_bfloat16*)do_cmp, (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, dlogits, B, H,
-        T, dv, gate_mode);
+        T, dv, gate_mode, delta);
   else
     return fail(NSA_ERR_ARG, "gate_mix_bwd: unsupported dtype %d", dtype);
   return check_launch("gate_mix_bwd");
+}
+
+extern "C" NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
+                                const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits, int B, int H,
+                                int T, int dv, int gate_mode, int dtype, void* stream) {
+  return nsa_gate_mix_bwd_delta(gates, o_cmp, o_slc, o_win, dout, do_cmp, do_slc, do_win, dlogits, nullptr, B, H, T, dv,
+                                gate_mode, dtype, stream);
 }

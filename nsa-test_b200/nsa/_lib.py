@@ -34,6 +34,7 @@ PROTOTYPES = {
     "nsa_version": (c_char_p, []),
     "nsa_set_kernel_family": (c_int, [c_int]),
     "nsa_set_dq_addends": (c_int, [c_void_p, c_void_p]),
+    "nsa_set_row_delta": (c_int, [c_void_p]),
     "nsa_set_query_offset": (c_int, [c_int]),
     "nsa_profile_enable": (c_int, [c_int]),
     "nsa_profile_report": (c_int, [ctypes.c_char_p, c_size_t]),
@@ -57,6 +58,7 @@ PROTOTYPES = {
     "nsa_eq9_scores": (c_int, [_P, _P, c_int64] + [c_int] * 4 + [_P]),
     "nsa_gate_mix_fwd": (c_int, [_P] * 6 + [c_int] * 6 + [_P]),
     "nsa_gate_mix_bwd": (c_int, [_P] * 9 + [c_int] * 6 + [_P]),
+    "nsa_gate_mix_bwd_delta": (c_int, [_P] * 10 + [c_int] * 6 + [_P]),
 }
 
 for _name, (_res, _args) in PROTOTYPES.items():

@@ -164,35 +164,45 @@ class SelectionAttention(torch.autograd.Function):
         return dq, dkey.transpose(-1, -2), dval, None, None, None, None
 
 
-class _ThreeBranches(torch.autograd.Function):
-    """The three attention branches of one layer under a single autograd node, so that the backward can hand the dQ of
-    the compression and sliding-window branches to the selection backward, which adds them to its own before the one
-    rounding of the sum (autograd would add the three [B,H,T,dk] tensors with two more passes over memory).
+class _BranchesAndMix(torch.autograd.Function):
+    """The three attention branches and the gate mix of one layer under a single autograd node
+    (nsa/kernels.py:2401-2463), so that the backward can pass on what the reference leaves to separate kernels and to
+    autograd: the gate/mix backward also produces the row sums dO_b.O_b that each branch backward needs, and the
+    selection backward adds the dQ of the other two branches to its own before the one rounding of the sum.
 
-    ``apply(q, k_cmp, v_cmp, block_ends, k_slc, v_slc, indices, k_win, v_win, scale, config, blocks)``
-    -> (o_cmp, o_slc, o_win); same kernels and layouts as the three wrappers above, query offset 0 only."""
+    ``apply(q, k_cmp, v_cmp, block_ends, k_slc, v_slc, indices, k_win, v_win, gate_logits, scale, config, blocks)``
+    -> (out, gates, o_cmp, o_slc, o_win); only ``out`` is differentiable.  Same kernels and layouts as the separate
+    wrappers above, query offset 0 only."""
 
     @staticmethod
-    def forward(ctx, q, k_cmp, v_cmp, block_ends, k_slc, v_slc, indices, k_win, v_win, scale, config, blocks):
+    def forward(ctx, q, k_cmp, v_cmp, block_ends, k_slc, v_slc, indices, k_win, v_win, gate_logits, scale, config, blocks):
         o_cmp, Lc, Mc = ops.cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale, blocks)
         idx = _selection_fallback(indices, config.l_prime).to(torch.int32).contiguous()
         o_slc, Ls, Ms = ops.slc_fwd(q, k_slc, v_slc, idx, config.l_prime, scale)
         o_win, Lw, Mw = ops.sliding_fwd(q, k_win, v_win, config.w, scale)
+        out, gates = ops.gate_mix_fwd(gate_logits, o_cmp, o_slc, o_win, config.gate_mode)
         ctx.save_for_backward(q, k_cmp, v_cmp, block_ends, k_slc, v_slc, idx, k_win, v_win, o_cmp, Lc, Mc, o_slc, Ls, Ms,
-                              o_win, Lw, Mw)
+                              o_win, Lw, Mw, gates)
         ctx.scale, ctx.l_prime, ctx.w, ctx.blocks = scale, config.l_prime, config.w, blocks
-        return o_cmp, o_slc, o_win
+        ctx.gate_mode, ctx.ldtype = config.gate_mode, gate_logits.dtype
+        ctx.mark_non_differentiable(gates, o_cmp, o_slc, o_win)
+        return out, gates, o_cmp, o_slc, o_win
 
     @staticmethod
-    def backward(ctx, d_cmp, d_slc, d_win):
-        (q, k_cmp, v_cmp, block_ends, k_slc, v_slc, idx, k_win, v_win, o_cmp, Lc, Mc, o_slc, Ls, Ms, o_win, Lw,
-         Mw) = ctx.saved_tensors
-        dq_c, dkc, dvc = ops.cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o_cmp, d_cmp, Lc, Mc, ctx.scale, ctx.blocks)
-        dq_w, dkw, dvw = ops.sliding_bwd(q, k_win, v_win, o_win, d_win, Lw, Mw, ctx.w, ctx.scale)
-        dq, dks, dvs = ops.slc_bwd(q, k_slc, v_slc, idx, o_slc, d_slc, Ls, Ms, ctx.l_prime, ctx.scale,
-                                   dq_addends=(dq_c, dq_w))
-        return (dq, dkc.transpose(-1, -2), dvc, None, dks.transpose(-1, -2), dvs, None, dkw.transpose(-1, -2), dvw, None,
-                None, None)
+    def backward(ctx, dout, *_unused):
+        (q, k_cmp, v_cmp, block_ends, k_slc, v_slc, idx, k_win, v_win, o_cmp, Lc, Mc, o_slc, Ls, Ms, o_win, Lw, Mw,
+         gates) = ctx.saved_tensors
+        d_cmp, d_slc, d_win, dlogits, delta = ops.gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, ctx.gate_mode,
+                                                               want_delta=True)
+        with ops.row_delta(delta[0]):
+            dq_c, dkc, dvc = ops.cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o_cmp, d_cmp, Lc, Mc, ctx.scale, ctx.blocks)
+        with ops.row_delta(delta[2]):
+            dq_w, dkw, dvw = ops.sliding_bwd(q, k_win, v_win, o_win, d_win, Lw, Mw, ctx.w, ctx.scale)
+        with ops.row_delta(delta[1]):
+            dq, dks, dvs = ops.slc_bwd(q, k_slc, v_slc, idx, o_slc, d_slc, Ls, Ms, ctx.l_prime, ctx.scale,
+                                       dq_addends=(dq_c, dq_w))
+        return (dq, dkc.transpose(-1, -2), dvc, None, dks.transpose(-1, -2), dvs, None, dkw.transpose(-1, -2), dvw,
+                dlogits.to(ctx.ldtype), None, None, None)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -379,13 +389,13 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
     indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale, nb,
                              q_pos0)
     if q_pos0 == 0 and kw.shape[-1] == q.shape[2]:
-        o_cmp, o_slc, o_win = _ThreeBranches.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, k_slc, v_slc, indices, kw, vw,
-                                                   scale, cfg, (cfg.l, cfg.d, nb))
+        out, gates, o_cmp, o_slc, o_win = _BranchesAndMix.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, k_slc, v_slc, indices,
+                                                                kw, vw, gate_logits, scale, cfg, (cfg.l, cfg.d, nb))
     else:
         o_cmp = CompressionAttention.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, scale, cfg, (cfg.l, cfg.d, nb), q_pos0)
         o_slc = SelectionAttention.apply(q, k_slc, v_slc, indices, scale, cfg, q_pos0)
         o_win = _sliding_with_offset(q, kw, vw, scale, cfg, q_pos0)
-    out, gates = _GateMix.apply(gate_logits, o_cmp, o_slc, o_win, cfg.gate_mode)
+        out, gates = _GateMix.apply(gate_logits, o_cmp, o_slc, o_win, cfg.gate_mode)
     if return_info:
         return out, dict(indices=indices, gates=gates, k_cmp=k_cmp, v_cmp=v_cmp, block_ends=block_ends,
                          o_cmp=o_cmp, o_slc=o_slc, o_win=o_win)

@@ -68,6 +68,22 @@ def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float):
     return dq, dkey, dval
 
 
+class row_delta:
+    """``with row_delta(d):`` hands the row sums dO.O [B,H,T] (fp32) to the backward call inside the block."""
+
+    def __init__(self, delta):
+        self.delta = None if delta is None else delta.contiguous()   # kept alive until the block ends
+
+    def __enter__(self):
+        if self.delta is not None:
+            check(lib.nsa_set_row_delta(ptr(self.delta)), "nsa_set_row_delta")
+
+    def __exit__(self, *exc):
+        if self.delta is not None:
+            lib.nsa_set_row_delta(None)
+        return False
+
+
 class query_offset:
     """``with query_offset(p):`` the library calls made inside treat query row t as position p + t of the sequence
     (query-sharded long-context runs; keys start at position 0).  Thread-local in the library; restored to 0 on exit."""
@@ -277,7 +293,7 @@ def gate_mix_fwd(logits, o_cmp, o_slc, o_win, gate_mode: str):
     return out, gates
 
 
-def gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, gate_mode: str):
+def gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, gate_mode: str, want_delta: bool = False):
     """-> (do_cmp, do_slc, do_win, dlogits [B,T,3H] fp32)."""
     dev = require_cuda(gates, o_cmp, o_slc, o_win, dout)
     B, H, T, dv = o_cmp.shape
@@ -286,7 +302,9 @@ def gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, gate_mode: str):
     d0, d1, d2 = torch.empty_like(o_cmp), torch.empty_like(o_cmp), torch.empty_like(o_cmp)
     dlogits = torch.empty(B, T, 3 * H, device=dev, dtype=torch.float32)
     mode = _lib.GATE_SOFTMAX if gate_mode == "softmax" else _lib.GATE_SIGMOID
+    delta = torch.empty(3, B, H, T, device=dev, dtype=torch.float32) if want_delta else None
     with torch.cuda.device(dev):
-        check(lib.nsa_gate_mix_bwd(ptr(gates), ptr(o_cmp), ptr(o_slc), ptr(o_win), ptr(dout), ptr(d0), ptr(d1), ptr(d2),
-                                   ptr(dlogits), B, H, T, dv, mode, dtype_code(o_cmp), stream_ptr(dev)), "nsa_gate_mix_bwd")
-    return d0, d1, d2, dlogits
+        check(lib.nsa_gate_mix_bwd_delta(ptr(gates), ptr(o_cmp), ptr(o_slc), ptr(o_win), ptr(dout), ptr(d0), ptr(d1), ptr(d2),
+                                         ptr(dlogits), ptr(delta), B, H, T, dv, mode, dtype_code(o_cmp), stream_ptr(dev)),
+              "nsa_gate_mix_bwd")
+    return (d0, d1, d2, dlogits, delta) if want_delta else (d0, d1, d2, dlogits)

@@ -53,8 +53,12 @@ def test_query_slices_match_the_unsharded_layer(dk, dv, H, G, T, world):
     assert torch.equal(torch.cat(idxs, dim=2), idx_full), "selected blocks differ between sharded and unsharded runs"
     assert max_abs(torch.cat(outs, dim=2).float(), out_full.float()) < 2e-2          # bf16 I/O tolerance
     assert max_abs(torch.cat(dqs, dim=2), g_full[0]) < 2e-2
-    for name, a, b in zip(("dk", "dv", "dpos", "dw1", "db1", "dw2", "db2"), sums, g_full[1:]):
-        scale = max(1.0, b.abs().max().item())
+    names = ("dk", "dv", "dpos", "dw1", "db1", "dw2", "db2")
+    ref = dict(zip(names, g_full[1:]))
+    for name, a, b in zip(names, sums, g_full[1:]):
+        # db2 is zero mathematically (a constant added to every compressed key leaves the softmax unchanged): both sides
+        # hold rounding noise, compared on the scale of the weight gradient next to it
+        scale = max(1.0, (ref["dw2"] if name == "db2" else b).abs().max().item())
         assert max_abs(a, b) < 3e-2 * scale, f"{name}: sharded sum differs by {max_abs(a, b)} (scale {scale})"
 
 

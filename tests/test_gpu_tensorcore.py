@@ -364,3 +364,34 @@ def test_selection_backward_adds_the_other_branches_dq(dtype, T):
     assert max_abs(both[0].float(), want) < tol * max(1.0, want.abs().max().item())
     want1 = plain[0].float() + a.float()
     assert max_abs(one[0].float(), want1) < tol * max(1.0, want1.abs().max().item())
+
+
+def test_backward_takes_the_row_sums_from_the_caller():
+    """nsa_set_row_delta: with the row sums dO.O handed in, the three tensor-core backward paths return what they return
+    when they compute the sums themselves (same sums up to fp32 summation order), and a wrong delta changes the result,
+    which shows that it is used; the hint serves one call."""
+    from nsa import ops
+    B, H, G, T, dk, dv, n = 1, 16, 1, 1024, 64, 64, 8
+    gen = torch.Generator().manual_seed(14)
+    q, k, v, do = (t.to(DEV) for t in _inputs(B, H, G, T, dk, dv, seed=14))
+    scale = dk ** -0.5
+    idx = _random_indices(B, G, T, n, 64, gen, with_holes=False).to(DEV)
+
+    def check(fwd, bwd):
+        o, L, M = fwd()
+        delta = (o.float() * do.float()).sum(-1)
+        plain = bwd(o, L, M)
+        with ops.row_delta(delta):
+            given = bwd(o, L, M)
+        after = bwd(o, L, M)
+        with ops.row_delta(delta + 1.0):
+            wrong = bwd(o, L, M)
+        torch.cuda.synchronize()
+        _no_timeouts()
+        for a, b_, c in zip(plain, given, after):
+            assert torch.equal(a, c)
+            assert max_abs(a.float(), b_.float()) < 2e-2 * max(1.0, a.float().abs().max().item())
+        assert max_abs(plain[0].float(), wrong[0].float()) > 0.05
+
+    check(lambda: ops.sliding_fwd(q, k, v, 512, scale), lambda o, L, M: ops.sliding_bwd(q, k, v, o, do, L, M, 512, scale))
+    check(lambda: ops.slc_fwd(q, k, v, idx, 64, scale), lambda o, L, M: ops.slc_bwd(q, k, v, idx, o, do, L, M, 64, scale))
