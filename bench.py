@@ -35,8 +35,8 @@ CFG = dict(H=64, G=4, dk=192, dv=128, w=512, l=32, d=16, l_prime=64, n=16, d_mod
 METRIC = "NSA layer fwd+bwd tokens/s at T=64K"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from an ncu capture at T=8192 (profiles/ncu_dram_bytes_T8192.md),
-# per (group, query, slot) unit of the selection kernels.  That case is too small to be captured at full size under the
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from an ncu capture at T=8192, per (group, query, slot) unit of
+# the selection kernels.  That case is too small to be captured at full size under the
 # capture-size rule, so the figure is scaled by the units of the workload; at T=8192 62 % of the gathers hit L2, at
 # T=65536 fewer do, so the scaled figure is a lower bound of the full-size traffic.
 NCU_DRAM_BYTES_PER_UNIT = {"slc_bwd_fused": (3438014976 + 3070898432) / (8192 * 4 * 16),
@@ -231,8 +231,7 @@ def run_reference(args):
     for _ in range(min(args.warmup, 1)):
         cpu_oracle_tokens_per_s(T_sample, 1, threads)
     tps, sec = cpu_oracle_tokens_per_s(T_sample, max(1, args.steps), threads)
-    value = tps * args.gpus  # N independent sequences would take N times as long on the same host
-    value = tps
+    value = tps                 # one host: N sequences take N times as long, so the rate does not grow with --gpus
     sample = f"full layer fwd+bwd, fp32 on bf16-rounded inputs, one sequence of T={T_sample} (same heads/dims as the workload)"
     line = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
                 ms_per_step=sec * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",

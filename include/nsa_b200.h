@@ -45,25 +45,37 @@ enum {
   NSA_ERR_UNSUPPORTED = -4 /* shape outside what the requested kernel family covers */
 };
 
-/* Kernel-family switch for testing: 0 (default) uses the tensor-core (tcgen05) kernels wherever a call
- * qualifies (bf16, canonical contiguous layouts, supported head dims, T multiple of 128) and the
- * stride-generic kernels elsewhere; 1 forces the stride-generic kernels.  Process-wide. */
-NSA_API int nsa_set_kernel_family(int family);
-/* Query-sharded long-context runs (the reference has no counterpart; its wrappers assume query row t sits at
- * position t): position of query row 0 in the sequence for the calls THIS HOST THREAD makes next.  The keys keep
- * starting at position 0.  Honoured by the bf16 tensor-core paths of nsa_cmp_attn_fwd/bwd, nsa_score_topn and
- * nsa_slc_fwd/bwd; any other path refuses a non-zero offset with NSA_ERR_ARG.  Set it back to 0 afterwards. */
-NSA_API int nsa_set_query_offset(int position);
+/* `flags` argument of the attention and scoring entry points (testing / cross-checks): by default a call runs the
+ * tensor-core (tcgen05) kernels when it qualifies (bf16, canonical contiguous layouts, supported head dims, T a
+ * multiple of 128) and the stride-generic kernels otherwise; NSA_FLAG_GENERIC forces the stride-generic kernels. */
+enum { NSA_FLAG_GENERIC = 1 };
 
-/* Backward of the whole layer: dQ is the sum of the three branches' dQ (the reference leaves that sum to autograd,
- * nsa/kernels.py:2446-2463 feeds one q to all three).  After nsa_set_dq_addends(a, b) the next nsa_slc_bwd of this host
- * thread writes dq = dq_selection + a + b (a, b: dQ of the other branches, same dtype and contiguous [B,H,T,dk] layout
- * as dq; either may be NULL), summed in fp32 and rounded once.  The addends serve that one call. */
-NSA_API int nsa_set_dq_addends(const void* a, const void* b);
-/* Number of thread blocks of the tensor-core kernels that ever gave up on a bounded barrier wait
- * (0 in a healthy run; their output is then invalid).  Synchronises the device.  reset != 0 clears
- * the counter.  Negative = error. */
+/* `q_pos0` argument (query-sharded long-context runs and incremental decoding; the reference has no counterpart, its
+ * wrappers assume query row t sits at position t): position of query row 0 in the sequence.  The keys keep starting
+ * at position 0.  Honoured by the bf16 tensor-core paths of nsa_cmp_attn_fwd/bwd, nsa_slc_fwd/bwd and by
+ * nsa_score_topn; any other path refuses a non-zero offset with NSA_ERR_ARG.
+ *
+ * `row_delta` argument of the backward entry points: the row sums dO . O [B,H,T] (fp32, contiguous) when the caller
+ * has them already (nsa_gate_mix_bwd_delta writes them), else NULL and the call computes them (the reference computes
+ * them inside its backward kernels, nsa/kernels.py:1004-1010).  Used by the tensor-core paths.
+ *
+ * `dq_add0/dq_add1` of nsa_slc_bwd: dQ of the other two branches (same dtype and contiguous [B,H,T,dk] layout as dq,
+ * either may be NULL); the call then writes dq = dq_selection + dq_add0 + dq_add1, summed in fp32 and rounded once (the
+ * reference leaves that sum to autograd, nsa/kernels.py:2446-2463 feeds one q to all three branches).
+ *
+ * The library keeps no per-call state between entry points: everything a call depends on is in its argument list. */
+
+/* Every wait inside the tensor-core kernels is bounded (about 0.15 s).  A thread block whose wait runs out tears
+ * down cleanly, counts itself on the device and raises a flag in mapped host memory; blocks and launches that start
+ * afterwards skip their work, and EVERY attention / scoring entry point then returns NSA_ERR_LAUNCH (tested on entry,
+ * without synchronising) until the caller acknowledges with nsa_device_timeouts(1).  nsa_device_timeouts returns the
+ * number of blocks that gave up on the current device (0 in a healthy run), synchronises the device, and with
+ * reset != 0 clears counter and flag.  Negative = error. */
 NSA_API int nsa_device_timeouts(int reset);
+/* Self-test of that mechanism (no counterpart in the reference): one warp waits `limit_clocks` (1..2^24) on a barrier
+ * that nothing arrives at, gives up and reports like a product kernel.  Synchronises the stream.  Afterwards
+ * nsa_device_timeouts(0) reads 1 and the entry points refuse work until nsa_device_timeouts(1). */
+NSA_API int nsa_selftest_wait_timeout(long long limit_clocks, void* stream);
 
 /* Per-kernel timing for benchmarks: while enabled, every kernel launch of this library is bracketed
  * by a CUDA event pair on its stream.  nsa_profile_report() synchronises the device and writes one
@@ -87,7 +99,7 @@ NSA_API const char* nsa_version(void);
  * Replaces _nsa_sliding_window_fwd_kernel / _bwd_kernel (nsa/kernels.py:1151-1300, 1303-1530). */
 NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void* v, void* out, float* L, float* M,
                     const int64_t* strides22, int B, int H, int G, int T, int dk, int dv, int window,
-                    float scale, int dtype, void* stream);
+                    float scale, int dtype, int flags, void* stream);
 /* The backward entry points of the sliding and compression branches take scratch memory of
  * nsa_attn_bwd_workspace_bytes() bytes (used by the tensor-core kernels: per-row statistics and, for
  * the compression branch, per-head-chunk partial dK/dV sums that are then added in a fixed order). */
@@ -96,7 +108,8 @@ NSA_API size_t nsa_attn_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tk,
 NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                     const float* L, const float* M, void* dq, void* dkey, void* dval,
                     const int64_t* strides34, int B, int H, int G, int T, int dk, int dv, int window,
-                    float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+                    float scale, int dtype, const float* row_delta, int flags, void* workspace,
+                    size_t workspace_bytes, void* stream);
 
 /* Sliding-window backward for callers that cannot allocate device memory.  (No counterpart in the reference
  * project: its wrappers allocate freely through torch.)
@@ -131,12 +144,13 @@ NSA_API int nsa_sliding_bwd_noalloc(const void* q, const void* k, const void* v,
 NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                      void* out, float* L, float* M, const int64_t* strides22, int B, int H, int G,
                      int T, int NB, int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d,
-                     int blocks_n, void* stream);
+                     int blocks_n, int q_pos0, int flags, void* stream);
 NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                      const void* out, const void* dout, const float* L, const float* M, void* dq,
                      void* dk_cmp, void* dv_cmp, const int64_t* strides34, int B, int H, int G, int T,
                      int NB, int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d,
-                     int blocks_n, void* workspace, size_t workspace_bytes, void* stream);
+                     int blocks_n, int q_pos0, const float* row_delta, int flags, void* workspace,
+                     size_t workspace_bytes, void* stream);
 
 /* Selected-block attention: query t of group g sees the union of blocks indices[b,g,t,:] (ids < 0
  * and blocks starting at or beyond Tkv ignored, a repeated id counts once) intersected with
@@ -146,21 +160,22 @@ NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp
  * and heads that selected it) and needs scratch for the inverse index and per-(query, slot) partial
  * results: nsa_slc_fwd_workspace_bytes() bytes (256 when the stride-generic kernels will run). */
 NSA_API size_t nsa_slc_fwd_workspace_bytes(int B, int H, int G, int Tq, int Tkv, int dk, int dv,
-                                           int n_slots, int l_prime, int dtype);
+                                           int n_slots, int l_prime, int dtype, int flags);
 NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, const int32_t* indices, void* out,
                 float* L, float* M, const int64_t* strides26, int B, int H, int G, int Tq, int Tkv,
-                int n_slots, int l_prime, int dk, int dv, float scale, int dtype, void* workspace,
-                size_t workspace_bytes, void* stream);
+                int n_slots, int l_prime, int dk, int dv, float scale, int dtype, int q_pos0, int flags,
+                void* workspace, size_t workspace_bytes, void* stream);
 /* Backward; dK/dV are reduced per key block over the queries that selected it in a fixed order (an
  * inverse index "block -> queries" is built in the workspace; the tensor-core path also keeps per-
  * (query, slot) dQ partials and per-block dK/dV partials there), so results are run-to-run identical. */
 NSA_API size_t nsa_slc_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tkv, int dk, int dv,
-                                           int n_slots, int l_prime, int dtype);
+                                           int n_slots, int l_prime, int dtype, int flags);
 NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, const int32_t* indices, const void* out,
                 const void* dout, const float* L, const float* M, void* dq, void* dkey, void* dval,
                 const int64_t* strides38, int B, int H, int G, int Tq, int Tkv, int n_slots,
-                int l_prime, int dk, int dv, float scale, int dtype, void* workspace,
-                size_t workspace_bytes, void* stream);
+                int l_prime, int dk, int dv, float scale, int dtype, int q_pos0, const float* row_delta,
+                const void* dq_add0, const void* dq_add1, int flags, void* workspace, size_t workspace_bytes,
+                void* stream);
 
 /* Pooling half of the block-compression MLP phi (NSAAttention.compress_tokens, nsa/kernels.py:
  * 2119-2208).  With A[t,:] = W1[:, :dk] k_t (a plain GEMM done by the caller) and the table
@@ -189,11 +204,12 @@ NSA_API int nsa_phi_pool_bwd(const float* a, const float* c, const float* dhbar,
  * visible, which admits the tensor-core kernel (fp32 keys split into bf16 hi + lo parts held in the
  * workspace of nsa_score_topn_workspace_bytes() bytes); -1 makes no assumption. */
 NSA_API size_t nsa_score_topn_workspace_bytes(int B, int H, int G, int T, int dk, int nbp, int l, int d,
-                                              int l_prime, int n, int dtype);
+                                              int l_prime, int n, int dtype, int flags);
 NSA_API int nsa_score_topn(const void* q, const int64_t* q_strides4, const float* k_cmp,
                    const int32_t* block_ends, int32_t* indices_out, int B, int H, int G, int T, int dk,
                    int nbp, int l, int d, int l_prime, int n, int n_fixed, float scale, int dtype,
-                   int n_real_blocks, void* workspace, size_t workspace_bytes, void* stream);
+                   int n_real_blocks, int q_pos0, int flags, void* workspace, size_t workspace_bytes,
+                   void* stream);
 /* Eq. 10/11 alone on a given score tensor [B,H,T,n_sel] fp32 contiguous
  * (select_top_k_blocks_per_query_with_gqa, nsa/kernels.py:1965-2040). */
 NSA_API int nsa_topn_from_scores(const float* scores, int32_t* indices_out, int B, int H, int G, int T,
@@ -221,17 +237,10 @@ NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, const void* 
                      int B, int H, int T, int dv, int gate_mode, int dtype, void* stream);
 
 /* Same, and also writes delta [3][B*H*T] (fp32): the row sums dO_b . O_b of the three branches (dO_b = g_b dO), which
- * the branch backward kernels need.  Handing them over with nsa_set_row_delta() saves each backward its own pass over
- * O and dO. */
+ * the branch backward kernels need.  Handing them over as `row_delta` saves each backward its own pass over O and dO. */
 NSA_API int nsa_gate_mix_bwd_delta(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
                                    const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits,
                                    float* delta, int B, int H, int T, int dv, int gate_mode, int dtype, void* stream);
-
-/* The next nsa_sliding_bwd / nsa_cmp_attn_bwd / nsa_slc_bwd of this host thread takes its row sums dO . O [B,H,T] (fp32,
- * contiguous) from `delta` instead of computing them (tensor-core path; the generic kernels compute their own).  The
- * pointer serves that one call.  The reference computes these sums inside its backward kernels
- * (nsa/kernels.py:1004-1010). */
-NSA_API int nsa_set_row_delta(const float* delta);
 
 #ifdef __cplusplus
 }

@@ -74,25 +74,6 @@ static int check_common(const char* who, int B, int H, int G, int Tq, int Tk, in
   return NSA_OK;
 }
 
-static bool tensor_core_bwd_ok_slc(const int64_t* s, int dtype, int H, int G, int Tq, int Tk, int dk, int dv, const void* q,
-                                   const void* k, const void* v, const void* o, const void* dout, const void* dq,
-                                   const void* dkey, const void* dval);
-static int g_kernel_family = 0;
-int kernel_family() { return g_kernel_family; }  // 0: tensor-core kernels where they apply, 1: stride-generic kernels only
-// Position of query row 0 in the sequence for the calls this host thread makes next (query-sharded long-context runs:
-// the queries are a slice of the positions, keys cover the sequence from position 0).  Honoured by the tensor-core paths
-// of the compressed attention, the scoring and the selected-block attention; every other path refuses a non-zero offset.
-static thread_local int g_query_pos0 = 0;
-int query_pos0() { return g_query_pos0; }
-// row sums dO.O of the next backward call of this thread (which clears the pointer)
-static thread_local const float* g_row_delta = nullptr;
-const float* row_delta() { return g_row_delta; }
-void clear_row_delta() { g_row_delta = nullptr; }
-struct ClearRowDelta { ~ClearRowDelta() { g_row_delta = nullptr; } };
-// dQ of the other two branches, added by the next nsa_slc_bwd of this thread (which clears them)
-static thread_local const void* g_dq_add[2] = {nullptr, nullptr};
-void dq_addends(const void** a, const void** b) { *a = g_dq_add[0]; *b = g_dq_add[1]; }
-
 template <typename T>
 __global__ void add_dq_addends_kernel(T* __restrict__ dq, const T* __restrict__ a, const T* __restrict__ b, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -122,7 +103,7 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 static bool tensor_core_bwd_ok(const int64_t* s, int dtype, int B, int H, int G, int Tq, int Tk, int dk, int dv,
                                const void* q, const void* k, const void* v, const void* o, const void* dout, const void* dq,
                                const void* dkey, const void* dval) {
-  if (g_kernel_family != 0 || dtype != NSA_BF16 || !fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return false;
+  if (dtype != NSA_BF16 || !fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return false;
   if (!canonical_fwd(s, H, G, Tq, Tk, dk, dv) || (int64_t)B * H > 65535) return false;
   const int64_t gq[4] = {(int64_t)H * Tq * dk, (int64_t)Tq * dk, dk, 1};
   const int64_t gk[4] = {(int64_t)G * Tk * dk, (int64_t)Tk * dk, dk, 1};
@@ -136,7 +117,7 @@ static bool tensor_core_bwd_ok(const int64_t* s, int dtype, int B, int H, int G,
 static bool tensor_core_bwd_ok_slc(const int64_t* s, int dtype, int H, int G, int Tq, int Tk, int dk, int dv, const void* q,
                                    const void* k, const void* v, const void* o, const void* dout, const void* dq,
                                    const void* dkey, const void* dval) {
-  if (g_kernel_family != 0 || dtype != NSA_BF16 || !canonical_fwd(s, H, G, Tq, Tk, dk, dv)) return false;
+  if (dtype != NSA_BF16 || !canonical_fwd(s, H, G, Tq, Tk, dk, dv)) return false;
   const int64_t gq[4] = {(int64_t)H * Tq * dk, (int64_t)Tq * dk, dk, 1};
   const int64_t gk[4] = {(int64_t)G * Tk * dk, (int64_t)Tk * dk, dk, 1};
   const int64_t gv[4] = {(int64_t)G * Tk * dv, (int64_t)Tk * dv, dv, 1};
@@ -181,31 +162,26 @@ extern "C" NSA_API int nsa_profile_report(char* buf, size_t buf_bytes) {
   return NSA_OK;
 }
 
-extern "C" NSA_API int nsa_set_kernel_family(int family) {
-  NSA_REQUIRE(family == 0 || family == 1, "kernel family must be 0 (auto) or 1 (generic)");
-  g_kernel_family = family;
-  return NSA_OK;
-}
-
-extern "C" NSA_API int nsa_set_query_offset(int position) {
-  NSA_REQUIRE(position >= 0, "query offset must be >= 0");
-  g_query_pos0 = position;
-  return NSA_OK;
-}
-
-extern "C" NSA_API int nsa_set_row_delta(const float* delta) {
-  g_row_delta = delta;
-  return NSA_OK;
-}
-
-extern "C" NSA_API int nsa_set_dq_addends(const void* a, const void* b) {
-  g_dq_add[0] = a;
-  g_dq_add[1] = b;
-  return NSA_OK;
-}
+// An earlier tensor-core launch gave up on a bounded wait: everything launched since then skipped its work, so no entry
+// point may report success until the caller has acknowledged it (nsa_device_timeouts(1)).
+#define NSA_REFUSE_AFTER_TIMEOUT(what)                                                                                      \
+  do {                                                                                                                      \
+    if (timeout_flagged())                                                                                                  \
+      return fail(NSA_ERR_LAUNCH, what ": a tensor-core kernel gave up on a barrier wait earlier (device time-out); results " \
+                  "since then are invalid.  nsa_device_timeouts(1) reports and clears the condition");                      \
+  } while (0)
 
 #define NSA_NO_QUERY_OFFSET(what) \
-  NSA_REQUIRE(g_query_pos0 == 0, what ": a query offset (nsa_set_query_offset) needs the bf16 tensor-core path of this call")
+  NSA_REQUIRE(q_pos0 == 0, what ": a query offset needs the bf16 tensor-core path of this call")
+
+static bool want_tc(int flags) { return (flags & NSA_FLAG_GENERIC) == 0; }
+
+extern "C" NSA_API int nsa_selftest_wait_timeout(long long limit_clocks, void* stream) {
+  NSA_REQUIRE(limit_clocks > 0 && limit_clocks <= (1ll << 24), "selftest: limit must be within 1..2^24 clocks");
+  if (int rc = wait_timeout_selftest(limit_clocks, nullptr, (cudaStream_t)stream)) return rc;
+  if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return fail(NSA_ERR_LAUNCH, "selftest: device error");
+  return NSA_OK;
+}
 
 extern "C" NSA_API size_t nsa_attn_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int is_compression) {
   if (B <= 0 || H <= 0 || G <= 0 || Tq <= 0 || Tk <= 0 || H % G != 0) return 256;
@@ -223,11 +199,12 @@ extern "C" NSA_API const char* nsa_version(void) { return "nsa_b200 0.1.0 sm_100
 
 extern "C" NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void* v, void* out, float* L, float* M,
                                const int64_t* strides, int B, int H, int G, int T, int dk, int dv, int window,
-                               float scale, int dtype, void* stream) {
+                               float scale, int dtype, int flags, void* stream) {
   if (int rc = check_common("sliding_fwd", B, H, G, T, T, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && out && strides, "sliding_fwd: null pointer");
   NSA_REQUIRE(window > 0, "sliding_fwd: window must be positive");
-  if (g_kernel_family == 0 && dtype == NSA_BF16 && L && M && fa_fwd_sm100_supported(H, G, T, T, dk, dv) &&
+  NSA_REFUSE_AFTER_TIMEOUT("sliding_fwd");
+  if (want_tc(flags) && dtype == NSA_BF16 && L && M && fa_fwd_sm100_supported(H, G, T, T, dk, dv) &&
       canonical_fwd(strides, H, G, T, T, dk, dv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
       (int64_t)B * (H / 2) <= 65535)
     return fa_fwd_sm100(q, k, v, out, L, M, B, H, G, T, T, dk, dv, kWin, window, 0, 0, 0, scale, (cudaStream_t)stream);
@@ -241,14 +218,15 @@ extern "C" NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void*
 extern "C" NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                                const float* L, const float* M, void* dq, void* dkey, void* dval,
                                const int64_t* strides, int B, int H, int G, int T, int dk, int dv, int window,
-                               float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
-  ClearRowDelta clear_row_delta_guard;  // the caller's row sums serve this call only
+                               float scale, int dtype, const float* row_delta, int flags, void* workspace,
+                               size_t workspace_bytes, void* stream) {
   if (int rc = check_common("sliding_bwd", B, H, G, T, T, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && out && dout && L && M && dq && dkey && dval && strides, "sliding_bwd: null pointer");
   NSA_REQUIRE(window > 0, "sliding_bwd: window must be positive");
-  if (tensor_core_bwd_ok(strides, dtype, B, H, G, T, T, dk, dv, q, k, v, out, dout, dq, dkey, dval))
+  NSA_REFUSE_AFTER_TIMEOUT("sliding_bwd");
+  if (want_tc(flags) && tensor_core_bwd_ok(strides, dtype, B, H, G, T, T, dk, dv, q, k, v, out, dout, dq, dkey, dval))
     return fa_bwd_sm100(q, k, v, out, dout, L, M, dq, dkey, dval, B, H, G, T, T, dk, dv, kWin, window, 0, 0, 0, scale,
-                        workspace, workspace_bytes, (cudaStream_t)stream);
+                        row_delta, workspace, workspace_bytes, (cudaStream_t)stream);
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.dq = dq; a.dk_out = dkey; a.dv_out = dval;
   fill_bwd_strides(a, strides);
@@ -259,16 +237,18 @@ extern "C" NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void*
 extern "C" NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                                 void* out, float* L, float* M, const int64_t* strides, int B, int H, int G, int T,
                                 int NB, int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d,
-                                int blocks_n, void* stream) {
+                                int blocks_n, int q_pos0, int flags, void* stream) {
   if (int rc = check_common("cmp_attn_fwd", B, H, G, T, NB, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k_cmp && v_cmp && block_ends && out && strides, "cmp_attn_fwd: null pointer");
   NSA_REQUIRE(blocks_d >= 0 && (blocks_d == 0 || (blocks_l > 0 && blocks_n >= 0 && blocks_n <= NB)),
               "cmp_attn_fwd: bad block layout hint (l=%d, d=%d, n=%d)", blocks_l, blocks_d, blocks_n);
-  if (g_kernel_family == 0 && blocks_d > 0 && dtype == NSA_BF16 && L && M && fa_fwd_sm100_supported(H, G, T, NB, dk, dv) &&
+  NSA_REQUIRE(q_pos0 >= 0, "cmp_attn_fwd: negative query offset");
+  NSA_REFUSE_AFTER_TIMEOUT("cmp_attn_fwd");
+  if (want_tc(flags) && blocks_d > 0 && dtype == NSA_BF16 && L && M && fa_fwd_sm100_supported(H, G, T, NB, dk, dv) &&
       canonical_fwd(strides, H, G, T, NB, dk, dv) && aligned16(q) && aligned16(k_cmp) && aligned16(v_cmp) &&
       aligned16(out) && (int64_t)B * (H / 2) <= 65535)
     // block i is visible to the query at position q0 + t iff i*d + l - 1 <= q0 + t: the same rule with l - q0 for row t
-    return fa_fwd_sm100(q, k_cmp, v_cmp, out, L, M, B, H, G, T, NB, dk, dv, kCmp, 0, blocks_l - g_query_pos0, blocks_d, blocks_n,
+    return fa_fwd_sm100(q, k_cmp, v_cmp, out, L, M, B, H, G, T, NB, dk, dv, kCmp, 0, blocks_l - q_pos0, blocks_d, blocks_n,
                         scale, (cudaStream_t)stream);
   NSA_NO_QUERY_OFFSET("cmp_attn_fwd");
   AttnArgs a = {};
@@ -282,16 +262,20 @@ extern "C" NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const 
                                 const void* out, const void* dout, const float* L, const float* M, void* dq,
                                 void* dk_cmp, void* dv_cmp, const int64_t* strides, int B, int H, int G, int T, int NB,
                                 int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d, int blocks_n,
-                                void* workspace, size_t workspace_bytes, void* stream) {
-  ClearRowDelta clear_row_delta_guard;  // the caller's row sums serve this call only
+                                int q_pos0, const float* row_delta, int flags, void* workspace, size_t workspace_bytes,
+                                void* stream) {
   if (int rc = check_common("cmp_attn_bwd", B, H, G, T, NB, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k_cmp && v_cmp && block_ends && out && dout && L && M && dq && dk_cmp && dv_cmp && strides,
               "cmp_attn_bwd: null pointer");
   NSA_REQUIRE(blocks_d >= 0 && (blocks_d == 0 || (blocks_l > 0 && blocks_n >= 0 && blocks_n <= NB)),
               "cmp_attn_bwd: bad block layout hint (l=%d, d=%d, n=%d)", blocks_l, blocks_d, blocks_n);
-  if (blocks_d > 0 && tensor_core_bwd_ok(strides, dtype, B, H, G, T, NB, dk, dv, q, k_cmp, v_cmp, out, dout, dq, dk_cmp, dv_cmp))
+  NSA_REQUIRE(q_pos0 >= 0, "cmp_attn_bwd: negative query offset");
+  NSA_REFUSE_AFTER_TIMEOUT("cmp_attn_bwd");
+  if (want_tc(flags) && blocks_d > 0 &&
+      tensor_core_bwd_ok(strides, dtype, B, H, G, T, NB, dk, dv, q, k_cmp, v_cmp, out, dout, dq, dk_cmp, dv_cmp))
     return fa_bwd_sm100(q, k_cmp, v_cmp, out, dout, L, M, dq, dk_cmp, dv_cmp, B, H, G, T, NB, dk, dv, kCmp, 0,
-                        blocks_l - g_query_pos0, blocks_d, blocks_n, scale, workspace, workspace_bytes, (cudaStream_t)stream);
+                        blocks_l - q_pos0, blocks_d, blocks_n, scale, row_delta, workspace, workspace_bytes,
+                        (cudaStream_t)stream);
   NSA_NO_QUERY_OFFSET("cmp_attn_bwd");
   AttnArgs a = {};
   a.q = q; a.k = k_cmp; a.v = v_cmp; a.o_in = out; a.dout = dout; a.Lc = L; a.Mc = M; a.block_ends = block_ends;
@@ -303,15 +287,17 @@ extern "C" NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const 
 
 extern "C" NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, const int32_t* indices, void* out, float* L,
                            float* M, const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots,
-                           int l_prime, int dk, int dv, float scale, int dtype, void* workspace, size_t workspace_bytes,
-                           void* stream) {
+                           int l_prime, int dk, int dv, float scale, int dtype, int q_pos0, int flags, void* workspace,
+                           size_t workspace_bytes, void* stream) {
   if (int rc = check_common("slc_fwd", B, H, G, Tq, Tkv, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && indices && out && strides, "slc_fwd: null pointer");
   NSA_REQUIRE(l_prime > 0 && n_slots >= 0, "slc_fwd: bad block size / slot count");
-  if (g_kernel_family == 0 && dtype == NSA_BF16 && L && M && B > 0 && slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime) &&
+  NSA_REQUIRE(q_pos0 >= 0, "slc_fwd: negative query offset");
+  NSA_REFUSE_AFTER_TIMEOUT("slc_fwd");
+  if (want_tc(flags) && dtype == NSA_BF16 && L && M && B > 0 && slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime) &&
       canonical_fwd(strides, H, G, Tq, Tkv, dk, dv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out))
     return slc_fwd_sm100(q, k, v, indices, strides + 22, out, L, M, B, H, G, Tq, Tkv, dk, dv, n_slots, l_prime, scale,
-                         g_query_pos0, workspace, workspace_bytes, (cudaStream_t)stream);
+                         q_pos0, workspace, workspace_bytes, (cudaStream_t)stream);
   NSA_NO_QUERY_OFFSET("slc_fwd");
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o = out; a.L = L; a.M = M; a.indices = indices;
@@ -323,15 +309,15 @@ extern "C" NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, 
 }
 
 extern "C" NSA_API size_t nsa_slc_fwd_workspace_bytes(int B, int H, int G, int Tq, int Tkv, int dk, int dv, int n_slots,
-                                                      int l_prime, int dtype) {
-  if (g_kernel_family != 0 || dtype != NSA_BF16 || B <= 0 || !slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime)) return 256;
+                                                      int l_prime, int dtype, int flags) {
+  if (!want_tc(flags) || dtype != NSA_BF16 || B <= 0 || !slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime)) return 256;
   return slc_fwd_sm100_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n_slots, l_prime);
 }
 
 extern "C" NSA_API size_t nsa_slc_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tkv, int dk, int dv, int n_slots,
-                                                      int l_prime, int dtype) {
+                                                      int l_prime, int dtype, int flags) {
   if (B <= 0 || G <= 0 || Tq <= 0 || Tkv <= 0 || n_slots <= 0 || l_prime <= 0) return 256;
-  if (g_kernel_family == 0 && dtype == NSA_BF16 && slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime))
+  if (want_tc(flags) && dtype == NSA_BF16 && slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime))
     return slc_bwd_sm100_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n_slots, l_prime);
   return slc_csr_workspace_bytes(B, G, Tq, Tkv, n_slots, l_prime);
 }
@@ -339,20 +325,22 @@ extern "C" NSA_API size_t nsa_slc_bwd_workspace_bytes(int B, int H, int G, int T
 extern "C" NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, const int32_t* indices, const void* out,
                            const void* dout, const float* L, const float* M, void* dq, void* dkey, void* dval,
                            const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots, int l_prime,
-                           int dk, int dv, float scale, int dtype, void* workspace, size_t workspace_bytes,
+                           int dk, int dv, float scale, int dtype, int q_pos0, const float* row_delta,
+                           const void* dq_add0, const void* dq_add1, int flags, void* workspace, size_t workspace_bytes,
                            void* stream) {
-  ClearRowDelta clear_row_delta_guard;  // the caller's row sums serve this call only
-  struct ClearAddends { ~ClearAddends() { g_dq_add[0] = g_dq_add[1] = nullptr; } } clear_addends;  // they serve one call only
   if (int rc = check_common("slc_bwd", B, H, G, Tq, Tkv, dk, dv, dtype)) return rc;
   NSA_REQUIRE(q && k && v && indices && out && dout && L && M && dq && dkey && dval && strides, "slc_bwd: null pointer");
   NSA_REQUIRE(l_prime > 0 && n_slots > 0, "slc_bwd: bad block size / slot count");
+  NSA_REQUIRE(q_pos0 >= 0, "slc_bwd: negative query offset");
+  NSA_REFUSE_AFTER_TIMEOUT("slc_bwd");
   if (B == 0 || Tq == 0 || Tkv == 0) return NSA_OK;
-  if (slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime) &&
+  if (want_tc(flags) && slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime) &&
       tensor_core_bwd_ok_slc(strides, dtype, H, G, Tq, Tkv, dk, dv, q, k, v, out, dout, dq, dkey, dval))
     return slc_bwd_sm100(q, k, v, indices, strides + 34, out, dout, L, M, dq, dkey, dval, B, H, G, Tq, Tkv, dk, dv, n_slots,
-                         l_prime, scale, g_query_pos0, workspace, workspace_bytes, (cudaStream_t)stream);
+                         l_prime, scale, q_pos0, row_delta, dq_add0, dq_add1, workspace, workspace_bytes,
+                         (cudaStream_t)stream);
   NSA_NO_QUERY_OFFSET("slc_bwd");
-  const void *add0 = g_dq_add[0], *add1 = g_dq_add[1];
+  const void *add0 = dq_add0, *add1 = dq_add1;
   if (add0 || add1)
     NSA_REQUIRE(strides[25] == 1 && strides[24] == dk && strides[23] == (int64_t)Tq * dk && strides[22] == (int64_t)H * Tq * dk,
                 "slc_bwd: dQ addends need a contiguous [B,H,T,dk] dq");

@@ -74,7 +74,7 @@ __global__ void fa_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __
   }
 }
 
-// the row sums dO.O come from the caller (nsa_set_row_delta): only the log-sum-exp has to be prepared
+// the row sums dO.O come from the caller: only the log-sum-exp has to be prepared
 __global__ void fa_bwd_prep_given_delta_kernel(const float* __restrict__ delta, const float* __restrict__ L, const float* __restrict__ M,
                                                float* __restrict__ D, float* __restrict__ lse2, int64_t rows) {
   const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -84,10 +84,10 @@ __global__ void fa_bwd_prep_given_delta_kernel(const float* __restrict__ delta, 
   lse2[row] = isfinite(lse) ? lse * kLog2e : CUDART_INF_F;
 }
 
-void launch_bwd_prep(const void* o, const void* dout, const float* L, const float* M, float* D, float* lse2, int64_t rows, int dv,
-                     cudaStream_t st) {
+void launch_bwd_prep(const void* o, const void* dout, const float* L, const float* M, const float* delta, float* D, float* lse2,
+                     int64_t rows, int dv, cudaStream_t st) {
   KernelTimer kt("bwd_prep", st);
-  if (const float* delta = row_delta())
+  if (delta)
     fa_bwd_prep_given_delta_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(delta, L, M, D, lse2, rows);
   else
     fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, L, M, D, lse2,
@@ -385,7 +385,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (threadIdx.x == 0 && bar->abort) ptx::report_timeout(p.timeouts);
   if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -658,7 +658,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (threadIdx.x == 0 && bar->abort) ptx::report_timeout(p.timeouts);
   if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -721,8 +721,8 @@ static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, con
 
 int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* L,
                  const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G, int Tq, int Tk, int dk, int dv,
-                 int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale, void* workspace,
-                 size_t workspace_bytes, cudaStream_t st) {
+                 int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale, const float* row_delta,
+                 void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return fail(NSA_ERR_UNSUPPORTED, "fa_bwd_sm100: unsupported shape");
   if ((int64_t)B * H > 65535) return fail(NSA_ERR_UNSUPPORTED, "fa_bwd_sm100: B*H too large");
   const size_t need = fa_bwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, mode);
@@ -745,7 +745,7 @@ int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, con
   p.window = window; p.cmp_l = cmp_l; p.cmp_d = cmp_d; p.cmp_nb = cmp_nb;
   p.scale = scale; p.scale_log2 = scale * kLog2e;
   p.timeouts = fa_timeout_counter();
-  launch_bwd_prep(o, dout, L, M, D, lse2, (int64_t)rows, dv, st);
+  launch_bwd_prep(o, dout, L, M, row_delta, D, lse2, (int64_t)rows, dv, st);
   if (int rc = check_launch("fa_bwd_prep")) return rc;
   CUtensorMap tq128, tdo128, tq64, tdo64, tk, tv;
   if (int rc = make_tmap_bf16_2d(&tq128, q, (uint64_t)B * H * Tq, dk, 128)) return rc;
@@ -810,7 +810,6 @@ static int sliding_bwd_scratch_address(float** out) {
 extern "C" NSA_API int nsa_sliding_bwd_noalloc(const void* q, const void* k, const void* v, const void* out, const void* dout,
                                                const float* L, const float* M, void* dq, void* dkey, void* dval, int B, int H,
                                                int G, int T, int dk, int dv, int window, float scale, void* stream) {
-  nsa::clear_row_delta();  // this entry point always prepares its own row sums
   using namespace nsa;
   NSA_REQUIRE(q && k && v && out && dout && L && M && dq && dkey && dval, "sliding_bwd_noalloc: null pointer");
   NSA_REQUIRE(B > 0 && H > 0 && G > 0 && H % G == 0 && T > 0 && window > 0, "sliding_bwd_noalloc: bad sizes");
@@ -828,6 +827,6 @@ extern "C" NSA_API int nsa_sliding_bwd_noalloc(const void* q, const void* k, con
   float* scratch = nullptr;
   if (int rc = sliding_bwd_scratch_address(&scratch)) return rc;
   // Nothing in the scratch has to start at zero: the preparation kernel overwrites every row this call reads.
-  return fa_bwd_sm100(q, k, v, out, dout, L, M, dq, dkey, dval, B, H, G, T, T, dk, dv, kWin, window, 0, 0, 0, scale, scratch,
+  return fa_bwd_sm100(q, k, v, out, dout, L, M, dq, dkey, dval, B, H, G, T, T, dk, dv, kWin, window, 0, 0, 0, scale, nullptr, scratch,
                       sizeof(float) * 2 * kNoAllocMaxRows, (cudaStream_t)stream);
 }

@@ -17,6 +17,8 @@
 #include <cuda.h>
 
 #include "attn_args.cuh"
+#include <mutex>
+
 #include "common.cuh"
 #include "fa_sm100.cuh"
 #include "sm100_ptx.cuh"
@@ -25,7 +27,7 @@ namespace nsa {
 
 using namespace ptx;
 
-static __device__ int g_fa_fwd_timeouts;  // CTAs that gave up on a barrier (0 in every healthy run)
+static __device__ TimeoutRecord g_timeout_record;  // CTAs that gave up on a barrier wait (count 0 in every healthy run)
 
 constexpr int kBM = 128;  // queries per MMA tile
 constexpr int kBN = 128;  // keys per tile
@@ -87,7 +89,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int pairs = p.H / 2, per_qt = p.B * pairs, nqt = p.Tq / kBM;
   const int nitems = nqt * per_qt;
   // once any block has given up on a wait the device results are void: later blocks skip their work and end at once
-  const bool poisoned = *(volatile const int*)&g_fa_fwd_timeouts != 0;
+  const bool poisoned = *(volatile const int*)&g_timeout_record.count != 0;
   struct Item { int m0, b, h0, g, jlo, ntiles; };
   auto item_at = [&](int it) {
     Item w;
@@ -406,7 +408,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   // ------------------------------------------------------------ teardown (every thread gets here)
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && bar->abort) atomicAdd(&g_fa_fwd_timeouts, 1);
+  if (threadIdx.x == 0 && bar->abort) report_timeout(&g_timeout_record.count);
   if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -502,6 +504,7 @@ int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L,
                  int Tk, int dk, int dv, int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale,
                  cudaStream_t st) {
   if (!fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: unsupported shape");
+  if (!fa_timeout_counter()) return fail(NSA_ERR_LAUNCH, "fa_fwd_sm100: cannot set up the time-out record of this device");
   if ((int64_t)B * (H / 2) * (Tq / kBM) > 0x7fffffff) return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: too many work items");
   CUtensorMap tq, tk, tv;
   if (int rc = make_tmap_bf16_2d(&tq, q, (uint64_t)B * H * Tq, dk, kBM)) return rc;
@@ -522,20 +525,77 @@ int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L,
   return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: unsupported head dims");
 }
 
+// Host side of the time-out record.  One page of this library's own host memory is pinned and mapped into the device
+// address space once per process (no allocation); a CTA that gives up on a wait sets its first word, so every entry
+// point can notice a time-out without synchronising.  Each device's record learns the flag's device address on the first
+// tensor-core launch on that device.
+alignas(4096) static int g_host_timeout_flag[1024];
+
+bool timeout_flagged() { return *(volatile int*)&g_host_timeout_flag[0] != 0; }
+
 int* fa_timeout_counter() {
-  int* ptr = nullptr;
-  if (cudaGetSymbolAddress((void**)&ptr, g_fa_fwd_timeouts) != cudaSuccess) return nullptr;
-  return ptr;
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int* cached[kMaxDevices] = {};
+  static int host_state = 0;  // 0: not tried, 1: registered, -1: registration refused (count-only reporting)
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (cached[dev]) return cached[dev];
+  TimeoutRecord* rec = nullptr;
+  if (cudaGetSymbolAddress((void**)&rec, g_timeout_record) != cudaSuccess || !rec) return nullptr;
+  if (host_state == 0) {
+    const cudaError_t e = cudaHostRegister(g_host_timeout_flag, sizeof(g_host_timeout_flag), cudaHostRegisterPortable | cudaHostRegisterMapped);
+    host_state = e == cudaSuccess ? 1 : -1;
+    if (e != cudaSuccess) cudaGetLastError();
+  }
+  int* flag_dev = nullptr;
+  if (host_state == 1 && cudaHostGetDevicePointer((void**)&flag_dev, g_host_timeout_flag, 0) != cudaSuccess) {
+    flag_dev = nullptr;
+    cudaGetLastError();
+  }
+  if (cudaMemcpy(&rec->host_flag, &flag_dev, sizeof(flag_dev), cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
+  cached[dev] = &rec->count;
+  return cached[dev];
 }
 
 int fa_fwd_sm100_timeouts(int* count, bool reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(count, g_fa_fwd_timeouts, sizeof(int));
+  cudaError_t e = cudaMemcpyFromSymbol(count, g_timeout_record, sizeof(int));
   if (e != cudaSuccess) return fail(NSA_ERR_LAUNCH, "cannot read the timeout counter: %s", cudaGetErrorString(e));
   if (reset) {
     const int z = 0;
-    cudaMemcpyToSymbol(g_fa_fwd_timeouts, &z, sizeof(int));
+    cudaMemcpyToSymbol(g_timeout_record, &z, sizeof(int));
+    *(volatile int*)&g_host_timeout_flag[0] = 0;
   }
   return NSA_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one warp waits on a barrier that nothing ever arrives at, with a short limit, and
+// leaves through the same report path as the product kernels.  No fault, no trap, no unbounded spin.
+// ------------------------------------------------------------------------------------------------
+__global__ void wait_timeout_selftest_kernel(int* timeouts, long long limit_clocks, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const bool ok = mbar_wait_warp(&bar, 0, &abort_flag, limit_clocks);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!ok && abort_flag) report_timeout(timeouts);
+    if (gave_up) *gave_up = ok ? 0 : 1;
+  }
+}
+
+int wait_timeout_selftest(long long limit_clocks, int* gave_up_dev, cudaStream_t st) {
+  int* t = fa_timeout_counter();
+  if (!t) return fail(NSA_ERR_LAUNCH, "selftest: no time-out record on this device");
+  wait_timeout_selftest_kernel<<<1, 32, 0, st>>>(t, limit_clocks, gave_up_dev);
+  return check_launch("wait_timeout_selftest");
 }
 
 }  // namespace nsa

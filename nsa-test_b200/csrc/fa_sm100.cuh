@@ -8,11 +8,6 @@ struct CUtensorMap_st;
 
 namespace nsa {
 
-// Row sums dO.O [B,H,Tq] (fp32) handed in by the caller for the next backward call of this host thread, or null
-// (nsa_set_row_delta); the tensor-core backward then skips its own pass over O and dO.
-const float* row_delta();
-void clear_row_delta();
-
 struct FaFwdParams {
   __nv_bfloat16* o;  // [B,H,Tq,dv] contiguous
   float *L, *M;      // [B,H,Tq] contiguous, may be null
@@ -33,11 +28,12 @@ int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L,
 // Backward of the same two branches.  Adds into dk [B,G,Tk,dk] and dv [B,G,Tk,dv] (time-major, bf16),
 // overwrites dq [B,H,Tq,dk].  Three launches: delta/lse preparation, a query-stationary dQ kernel and
 // a key-stationary dK/dV kernel whose per-head-chunk partial sums are combined in a fixed order.
+// row_delta: the row sums dO.O [B,H,Tq] (fp32) when the caller has them already, else null (computed here).
 size_t fa_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int mode);
 int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* L,
                  const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G, int Tq, int Tk, int dk, int dv,
-                 int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale, void* workspace,
-                 size_t workspace_bytes, cudaStream_t st);
+                 int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale, const float* row_delta,
+                 void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 // bf16 row-major [rows, cols] matrix -> tensor map with box [box_rows, 64 columns], 128-byte swizzle
 int make_tmap_bf16_2d(::CUtensorMap_st* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
@@ -54,8 +50,15 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
                      int lprime, int nb, int n, int n_fixed, float scale, int q0, void* workspace, size_t workspace_bytes,
                      cudaStream_t st);
 
-// Device address (on the current device) of the counter of CTAs that gave up on a barrier wait.
+// Device address (on the current device) of the counter of CTAs that gave up on a barrier wait; the first call on a
+// device sets up that device's time-out record (null on failure).
 int* fa_timeout_counter();
+// True once any CTA on any device has given up on a wait since the last reset (read from mapped host memory: no
+// synchronisation).
+bool timeout_flagged();
+// One warp waits `limit_clocks` on a barrier nothing arrives at and reports the time-out like a product kernel would;
+// *gave_up_dev (device int, may be null) is set to 1 when the wait ran out.
+int wait_timeout_selftest(long long limit_clocks, int* gave_up_dev, cudaStream_t st);
 
 // Number of CTAs that ever gave up on a barrier wait (0 in a healthy run); optionally reset.
 int fa_fwd_sm100_timeouts(int* count, bool reset);

@@ -19,7 +19,6 @@
 #include "common.cuh"
 #include "fa_sm100.cuh"
 #include "sm100_ptx.cuh"
-#include "trace.cuh"
 
 namespace nsa {
 
@@ -27,9 +26,6 @@ using namespace ptx;
 
 constexpr int kScoreMaxN = 32;
 
-NSA_TRACE_STORAGE
-// trace slot of a step: the first 64 steps of each pass
-#define NSA_TRC(step, spp) (((step) % (spp)) < 64 ? ((step) / (spp)) * 64 + ((step) % (spp)) : 128)
 
 struct ScoreParams {
   float* sel;    // [B,G,T,n_sel] selection-block scores (blocks beyond a query tile's last key tile are not written)
@@ -126,10 +122,8 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         kissued = kidx + 1;
       }
       const int s = step & 1;
-      if (lane == 0) NSA_TR(0, NSA_TRC(step, steps_per_pass), 0);
       ok = mbar_wait_warp(&bar->q_empty[s], ((step >> 1) & 1) ^ 1, abort);
       if (!ok) break;
-      if (lane == 0) NSA_TR(0, NSA_TRC(step, steps_per_pass), 1);
       if (elect_one()) {
         mbar_arrive_expect_tx(&bar->q_full[s], kQ);
         for (int c = 0; c < DK / 64; ++c)
@@ -155,14 +149,10 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     int hh = 0, ktiles = 0;
     for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
       const int s = step & 1;
-      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 0);
       if (hh == 0) ok = mbar_wait_warp(&bar->k_full, ktiles & 1, abort);
-      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 1);
       ok = ok && mbar_wait_warp(&bar->q_full[s], (step >> 1) & 1, abort);
-      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 2);
       ok = ok && mbar_wait_warp(&bar->s_free[s], ((step >> 1) & 1) ^ 1, abort);
       if (!ok) break;
-      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 3);
       tc_fence_after();
       const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * kQ), 16, 1024);
       if (elect_one()) {
@@ -177,7 +167,6 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (hh == hpg - 1) umma_commit(&bar->k_empty);
       }
       __syncwarp();
-      if (lane == 0) NSA_TR(1, NSA_TRC(step, steps_per_pass), 4);
       if (++hh == hpg) {
         hh = 0;
         ++ktiles;
@@ -213,10 +202,8 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int i = 0; i < 128; ++i) agg[i] = 0.f;
       }
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 0);
       ok = mbar_wait(&bar->s_full[s], (step >> 1) & 1, abort);
       if (!ok) break;
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 1);
       tc_fence_after();
       const bool full = chi >= 127;  // every key of this tile is visible to this row: no per-element mask
       if (pass == 0) {
@@ -237,7 +224,6 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         tc_fence_before();
         mbar_arrive(&bar->s_free[s]);
-        if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 2);
         if (raw_mx != -CUDART_INF_F) {
           const float mx = fmaxf(m_old, raw_mx * p.scale_log2);
           float sum0 = 0.f, sum1 = 0.f;
@@ -268,7 +254,6 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         tc_fence_before();
         mbar_arrive(&bar->s_free[s]);
-        if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 2);
         if (vis < 0 && kt == 0) agg[0] += 1.f;  // a row that sees no block puts all its mass on block 0
         if (wg == 1 && hh == hpg - 1) {
           // park this group's sums for group 0 (the previous tile's must have been picked up)
@@ -318,14 +303,13 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
         }
       }
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + wg, NSA_TRC(step, steps_per_pass), 3);
     }
     // the last block's final term lies beyond every visible key: + 0
     if (ok && wg == 0) srow[ntiles * per_tile - 1] = cur;
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (threadIdx.x == 0 && bar->abort) ptx::report_timeout(p.timeouts);
   if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -571,4 +555,3 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
 
 }  // namespace nsa
 
-NSA_TRACE_READER(nsa_trace_read_score)

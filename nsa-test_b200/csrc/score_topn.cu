@@ -222,11 +222,9 @@ topn_from_scores_kernel(const float* __restrict__ scores, int32_t* __restrict__ 
 
 using namespace nsa;
 
-namespace nsa { int kernel_family(); int query_pos0(); }
-
 static bool score_tc_ok(const void* q, const int64_t* qs, int B, int H, int G, int T, int dk, int nbp, int l, int d, int l_prime,
-                        int n, int n_real_blocks, int dtype) {
-  if (nsa::kernel_family() != 0 || dtype != NSA_BF16 || n_real_blocks < 0 || n_real_blocks > nbp) return false;
+                        int n, int n_real_blocks, int dtype, int flags) {
+  if ((flags & NSA_FLAG_GENERIC) || dtype != NSA_BF16 || n_real_blocks < 0 || n_real_blocks > nbp) return false;
   if (!score_sm100_supported(H, G, T, dk, nbp, l, d, l_prime, n) || (int64_t)B * G > 65535) return false;
   const int64_t cq[4] = {(int64_t)H * T * dk, (int64_t)T * dk, dk, 1};
   for (int i = 0; i < 4; ++i)
@@ -244,20 +242,24 @@ static size_t few_rows_logit_bytes(int B, int H, int G, int T, int nbp) {
 }
 
 extern "C" NSA_API size_t nsa_score_topn_workspace_bytes(int B, int H, int G, int T, int dk, int nbp, int l, int d, int l_prime,
-                                                         int n, int dtype) {
-  if (B <= 0 || G <= 0 || dtype != NSA_BF16 || nsa::kernel_family() != 0 || !score_sm100_supported(H, G, T, dk, nbp, l, d, l_prime, n))
+                                                         int n, int dtype, int flags) {
+  if (B <= 0 || G <= 0 || dtype != NSA_BF16 || (flags & NSA_FLAG_GENERIC) || !score_sm100_supported(H, G, T, dk, nbp, l, d, l_prime, n))
     return std::max<size_t>(256, few_rows_logit_bytes(B, H, G, T, nbp));
   return score_sm100_workspace_bytes(B, G, T, dk, nbp, d, l_prime);
 }
 
 extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const float* k_cmp, const int32_t* block_ends,
                               int32_t* indices_out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
-                              int l_prime, int n, int n_fixed, float scale, int dtype, int n_real_blocks, void* workspace,
-                              size_t workspace_bytes, void* stream) {
+                              int l_prime, int n, int n_fixed, float scale, int dtype, int n_real_blocks, int q_pos0, int flags,
+                              void* workspace, size_t workspace_bytes, void* stream) {
   NSA_REQUIRE(q && qs && k_cmp && block_ends && indices_out, "score_topn: null pointer");
-  if (B > 0 && T > 0 && score_tc_ok(q, qs, B, H, G, T, dk, nbp, l, d, l_prime, n, n_real_blocks, dtype))
+  NSA_REQUIRE(q_pos0 >= 0, "score_topn: negative query offset");
+  if (timeout_flagged())
+    return fail(NSA_ERR_LAUNCH, "score_topn: a tensor-core kernel gave up on a barrier wait earlier (device time-out); results "
+                "since then are invalid.  nsa_device_timeouts(1) reports and clears the condition");
+  if (B > 0 && T > 0 && score_tc_ok(q, qs, B, H, G, T, dk, nbp, l, d, l_prime, n, n_real_blocks, dtype, flags))
     return score_topn_sm100(q, k_cmp, indices_out, B, H, G, T, dk, nbp, l, d, l_prime, n_real_blocks, n, n_fixed, scale,
-                            nsa::query_pos0(), workspace, workspace_bytes, (cudaStream_t)stream);
+                            q_pos0, workspace, workspace_bytes, (cudaStream_t)stream);
   NSA_REQUIRE(G > 0 && H % G == 0 && d > 0 && l % d == 0 && l_prime % d == 0 && l > 0 && l_prime > 0,
               "score_topn: bad block parameters");
   NSA_REQUIRE(n > 0 && n <= kMaxN, "score_topn: n=%d outside 1..%d", n, kMaxN);
@@ -270,7 +272,7 @@ extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const fl
   if (sm > 200 * 1024) return fail(NSA_ERR_UNSUPPORTED, "score_topn: %zu bytes of shared memory needed", sm);
   if (dtype != NSA_F32 && dtype != NSA_BF16) return fail(NSA_ERR_ARG, "score_topn: unsupported dtype %d", dtype);
   cudaStream_t st = (cudaStream_t)stream;
-  const int q0 = nsa::query_pos0();
+  const int q0 = q_pos0;
   const float* logits = nullptr;
   const size_t lbytes = few_rows_logit_bytes(B, H, G, T, nbp);
   if (lbytes > 0 && workspace && workspace_bytes >= lbytes && (size_t)hpg * dk * sizeof(float) <= 48 * 1024) {

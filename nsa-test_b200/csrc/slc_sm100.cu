@@ -21,7 +21,6 @@
 #include "fa_sm100.cuh"
 #include "slc_sm100.cuh"
 #include "sm100_ptx.cuh"
-#include "trace.cuh"
 
 namespace nsa {
 
@@ -31,7 +30,6 @@ constexpr int kEntriesPerCta = 1024;  // inverse-index entries handled by one CT
 constexpr float kLn2f = 0.6931471805599453f;
 constexpr float kLog2ef = 1.4426950408889634f;
 
-NSA_TRACE_STORAGE
 
 struct SlcParams {
   const __nv_bfloat16* q;      // [B,H,Tq,dk]
@@ -197,11 +195,9 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         tok = ent[w.e + lane] & 0xFFFFFF;
         row = (int)(((int64_t)bg * p.Tq + tok) * p.hpg);
       }
-      if (lane == 0) NSA_TR(0, c, 0);
       ok = mbar_wait_warp(&bar->q_empty[s], ((c / NQ) & 1) ^ 1, abort);
       if (!ok) break;
       if (lane == 0) {
-        NSA_TR(0, c, 1);
         mbar_arrive_expect_tx(&bar->q_full[s], SM::kQ);
       }
       __syncwarp();
@@ -215,7 +211,6 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             tma_load_2d(&tmQt, &bar->q_full[s], sQ + s * SM::kQ + cc * 16384 + qi * p.hpg * 128, cc * 64, r2);
         }
       }
-      if (lane == 0) NSA_TR(0, c, 2);
     }
     if (!ok && lane == 0) {  // let copies in flight land before the CTA gives its shared memory back
       if (kvidx >= 0) mbar_wait(&bar->kv_full[kvidx & 1], (kvidx >> 1) & 1, abort);
@@ -232,11 +227,8 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     int c = 0, kvidx = 0, ks_cur = 0, cur_blk = w.blk;
     auto issue_s = [&](int cc, int ks) -> bool {
       const int s = cc % NQ, buf = cc & 1;
-      if (lane == 0) NSA_TR(1, cc, 0);
       if (!mbar_wait_warp(&bar->q_full[s], (cc / NQ) & 1, abort)) return false;
-      if (lane == 0) NSA_TR(1, cc, 1);
       if (!mbar_wait_warp(&bar->o_read[buf], ((cc >> 1) & 1) ^ 1, abort)) return false;
-      if (lane == 0) NSA_TR(1, cc, 2);
       tc_fence_after();
       const uint64_t dQ = smem_desc_sw128(smem_u32(sQ + s * SM::kQ), 16, sboQ);
       const uint64_t dK = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);  // one 64-key MN block: LBO unused
@@ -248,7 +240,6 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         umma_commit(&bar->q_empty[s]);
       }
       __syncwarp();
-      if (lane == 0) NSA_TR(1, cc, 3);
       return true;
     };
     // prologue: S(0)
@@ -273,10 +264,8 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         if (!ok) break;
       }
       const int buf = c & 1;
-      if (lane == 0) NSA_TR(1, c, 4);
       ok = mbar_wait_warp(&bar->p_full[buf], (c >> 1) & 1, abort);
       if (!ok) break;
-      if (lane == 0) NSA_TR(1, c, 5);
       tc_fence_after();
       const uint64_t dV = smem_desc_sw128(smem_u32(sV + ks_cur * SM::kV), 8192, 1024);
       if (elect_one()) {
@@ -287,7 +276,6 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         if (last_of_block) umma_commit(&bar->kv_empty[ks_cur]);
       }
       __syncwarp();
-      if (lane == 0) NSA_TR(1, c, 6);
       ks_cur = ks_next;
       ++c;
     }
@@ -317,10 +305,8 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       w.next();
       if (!w.done()) w.next();
       if (!w.done() && qi < w.count()) entry_next = ent[w.e + qi];
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 0);
       ok = mbar_wait(&bar->s_full[buf], it & 1, abort);
       if (!ok) break;
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 1);
       tc_fence_after();
       uint32_t sv[2][32];
       tmem_ld32(tmem + lane_base + buf * 192, sv[0]);
@@ -350,7 +336,6 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bar->p_full[buf]);
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 2);
       const float inv = 1.f / l;
       const int64_t prow = (((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh;
       if (valid) p.st_part[prow] = make_float2(mx, l);
@@ -358,7 +343,6 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const int box_row = __shfl_sync(0xffffffffu, valid ? (int)prow : -1, box_lane);
       ok = mbar_wait(&bar->o_full[buf], it & 1, abort);
       if (!ok) break;
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 3);
       tc_fence_after();
 #pragma unroll
       for (int half = 0; half < DV / 64; ++half) {
@@ -389,13 +373,12 @@ slc_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         if (lane < nbox && box_row >= 0) tma_store_2d(&tmOp, stage + lane * boxrows * 128, half * 64, box_row);
         bulk_commit();
       }
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 4);
     }
     bulk_wait_read<0>();
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (threadIdx.x == 0 && bar->abort) ptx::report_timeout(p.timeouts);
   if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -550,7 +533,7 @@ __global__ void slc_combine_fwd_bulk_kernel(const __nv_bfloat16* __restrict__ o_
     }
   }
   __syncthreads();  // the copy has landed (or was given up on) before shared memory is handed back
-  if (threadIdx.x == 0 && abort_flag && timeouts) atomicAdd(timeouts, 1);
+  if (threadIdx.x == 0 && abort_flag) ptx::report_timeout(timeouts);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -669,7 +652,7 @@ __global__ void slc_combine_dq_bulk_kernel(const __nv_bfloat16* __restrict__ dq_
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0 && abort_flag && timeouts) atomicAdd(timeouts, 1);
+  if (threadIdx.x == 0 && abort_flag) ptx::report_timeout(timeouts);
 }
 
 // accumulator rows [M x 64 keys] in TMEM -> part[(key_base + key) * W + off + row]; M = 128: row = TMEM lane,
@@ -874,7 +857,6 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (ready && fresh && hstep == 0 && seg > 0) ready = mbar_test(&bar->acc_read, (seg - 1) & 1);
         if (__all_sync(0xffffffffu, ready)) {
           tc_fence_after();
-          if (lane == 0) NSA_TR(1, ch, 4 + hstep);
           const int h = hstep >> 1;
           const uint32_t st = smem_u32(sSt + (ch & 1) * SM::kStage);
           // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart inside an 8-row group
@@ -926,7 +908,6 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (ready && cq > 0) ready = mbar_test(&bar->dq_read, (cq - 1) & 1);
         if (__all_sync(0xffffffffu, ready)) {
           tc_fence_after();
-          if (lane == 0) NSA_TR(1, cq, 2);
           if (elect_one()) {
 #pragma unroll
             for (int hh2 = 0; hh2 < 2; ++hh2)
@@ -944,7 +925,6 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       // ---- dP of chunk cp: after S of the same chunk, and in program order after dQ of the chunk before (same columns)
       if (cp < cs && cq == cp) {
         const int s = cp & 1;
-        if (lane == 0) NSA_TR(1, cp, 1);
         const uint32_t st = smem_u32(sSt + s * SM::kStage);
         const uint64_t ddO = smem_desc_sw128(st + SM::kQ, 16, sboO);
         if (elect_one()) {
@@ -981,7 +961,6 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (__all_sync(0xffffffffu, ready)) {
           kv_wait = false;
           tc_fence_after();
-          if (lane == 0) NSA_TR(1, cs, 0);
           const uint32_t st = smem_u32(sSt + s * SM::kStage);
           const uint64_t dQ = smem_desc_sw128(st, 16, sboQ);
           if (elect_one()) {
@@ -1069,10 +1048,8 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (!w2.done()) w2.next();
         fetch(w2);
       }
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 0);
       ok = mbar_wait(&bar->sdp_full[grp], (c >> 1) & 1, abort);
       if (!ok) break;
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 1);
       tc_fence_after();
       uint32_t pP[32], pS[32];
 #pragma unroll
@@ -1101,7 +1078,6 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bar->dst_full);
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 2);
       // hand-over of P / dS for the transposed accumulations: the staging tiles are used by (chunk, half) in order
       const int u = 2 * c + half;
       if (u > 0) {
@@ -1122,13 +1098,11 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         *reinterpret_cast<uint4*>(sdS + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pS[4 * j], pS[4 * j + 1], pS[4 * j + 2], pS[4 * j + 3]);
       fence_proxy_async();
       mbar_arrive(&bar->ds_full);
-      if ((threadIdx.x & 63) == 0) NSA_TR(2 + grp, c, 3 + half);
       // dQ partial of this chunk: TMEM -> registers -> per-warp staging (32 rows x 32 bytes, pieces swapped for odd
       // groups of four rows) -> 32-byte runs of 16 rows per store instruction
       const int prow = entry >= 0 ? (int)((((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh) : -1;
       ok = mbar_wait(&bar->dq_full[grp], (c >> 1) & 1, abort);
       if (!ok) break;
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 5);
       tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < DK / 32; ++cc) {
@@ -1164,13 +1138,12 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
           }
         }
       }
-      if ((threadIdx.x & 127) == 0) NSA_TR(2 + grp, c, 6);
     }
     if (ok && last_blk >= 0) flush(last_blk);
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && bar->abort && p.timeouts) atomicAdd(p.timeouts, 1);
+  if (threadIdx.x == 0 && bar->abort) ptx::report_timeout(p.timeouts);
   if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -1317,8 +1290,8 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
 }
 
 // prep kernel shared with the dense backward (defined in fa_bwd_sm100.cu)
-void launch_bwd_prep(const void* o, const void* dout, const float* L, const float* M, float* D, float* lse2, int64_t rows, int dv,
-                     cudaStream_t st);
+void launch_bwd_prep(const void* o, const void* dout, const float* L, const float* M, const float* delta, float* D, float* lse2,
+                     int64_t rows, int dv, cudaStream_t st);
 
 static void slc_bwd_layout(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, size_t* o_stat,
                            size_t* o_dq, size_t* o_dk, size_t* o_dv, size_t* o_qt, size_t* o_dot, size_t* total) {
@@ -1344,7 +1317,7 @@ size_t slc_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk
 template <int DK, int DV>
 static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tqt, const CUtensorMap& tdot,
                             const SlcParams& p, const int* indices,
-                            const int64_t* sidx, __nv_bfloat16* dq, cudaStream_t st) {
+                            const int64_t* sidx, __nv_bfloat16* dq, const void* add0, const void* add1, cudaStream_t st) {
   const int nparts = (int)(((int64_t)p.Tq * p.nslots + kEntriesPerCta - 1) / kEntriesPerCta);
   {
     auto kf = slc_bwd_fused_kernel<DK, DV>;
@@ -1355,8 +1328,6 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   }
   if (int rc = check_launch("slc_bwd_fused_sm100")) return rc;
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
-  const void *add0 = nullptr, *add1 = nullptr;
-  dq_addends(&add0, &add1);   // dQ of the other branches, set for this call through nsa_set_dq_addends
   {
     KernelTimer kt("slc_combine_dq", st);
     const size_t qbytes = (size_t)p.nslots * p.hpg * DK * 2;  // one query's partials
@@ -1382,8 +1353,8 @@ static int launch_slc_bwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
 
 int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, const void* out,
                   const void* dout, const float* L, const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G,
-                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, int q0, void* workspace,
-                  size_t workspace_bytes, cudaStream_t st) {
+                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, int q0, const float* row_delta,
+                  const void* dq_add0, const void* dq_add1, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!slc_sm100_supported(H, G, Tq, Tk, dk, dv, nslots, lprime)) return fail(NSA_ERR_UNSUPPORTED, "slc_bwd_sm100: unsupported shape");
   size_t o_stat, o_dq, o_dk, o_dv, o_qt, o_dot, need;
   slc_bwd_layout(B, H, G, Tq, Tk, dk, dv, nslots, lprime, &o_stat, &o_dq, &o_dk, &o_dv, &o_qt, &o_dot, &need);
@@ -1396,7 +1367,7 @@ int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indice
   const size_t rows = (size_t)B * H * Tq;
   float* D = (float*)(w + o_stat);
   float* lse2 = (float*)(w + o_stat + al256(rows * sizeof(float)));
-  launch_bwd_prep(out, dout, L, M, D, lse2, (int64_t)rows, dv, st);
+  launch_bwd_prep(out, dout, L, M, row_delta, D, lse2, (int64_t)rows, dv, st);
   if (int rc = check_launch("fa_bwd_prep")) return rc;
   p.q = (const __nv_bfloat16*)q; p.dout = (const __nv_bfloat16*)dout;
   p.D = D; p.lse2 = lse2;
@@ -1420,12 +1391,11 @@ int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indice
     if (int rc = make_tmap_bf16_2d(&tqt, w + o_qt, (uint64_t)B * H * Tq, dk, H / G)) return rc;
     if (int rc = make_tmap_bf16_2d(&tdot, w + o_dot, (uint64_t)B * H * Tq, dv, H / G)) return rc;
   }
-  if (dk == 192 && dv == 128) return launch_slc_bwd_t<192, 128>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, st);
-  if (dk == 128 && dv == 128) return launch_slc_bwd_t<128, 128>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, st);
-  if (dk == 64 && dv == 64) return launch_slc_bwd_t<64, 64>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, st);
+  if (dk == 192 && dv == 128) return launch_slc_bwd_t<192, 128>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, dq_add0, dq_add1, st);
+  if (dk == 128 && dv == 128) return launch_slc_bwd_t<128, 128>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, dq_add0, dq_add1, st);
+  if (dk == 64 && dv == 64) return launch_slc_bwd_t<64, 64>(tk, tv, tqt, tdot, p, indices, sidx, (__nv_bfloat16*)dq, dq_add0, dq_add1, st);
   return fail(NSA_ERR_UNSUPPORTED, "slc_bwd_sm100: unsupported head dims");
 }
 
 }  // namespace nsa
 
-NSA_TRACE_READER(nsa_trace_read)

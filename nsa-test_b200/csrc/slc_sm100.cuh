@@ -5,9 +5,6 @@
 
 namespace nsa {
 
-// dQ of the other branches that the next selection backward of this thread adds to its own (set through the C ABI)
-void dq_addends(const void** a, const void** b);
-
 // bf16, canonical contiguous layouts, 64-key selection blocks, heads-per-group dividing 128
 bool slc_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime);
 
@@ -17,10 +14,12 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
                   void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 
+// row_delta: row sums dO.O [B,H,Tq] fp32 or null (computed here); dq_add0/1: dQ of the other branches (bf16, laid out like
+// dq) added to the selection dQ in fp32 before the one rounding, or null.
 size_t slc_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime);
 int slc_bwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, const void* out,
                   const void* dout, const float* L, const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G,
-                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, int q0, void* workspace,
-                  size_t workspace_bytes, cudaStream_t st);
+                  int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, int q0, const float* row_delta,
+                  const void* dq_add0, const void* dq_add1, void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 }  // namespace nsa

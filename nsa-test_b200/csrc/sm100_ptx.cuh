@@ -49,11 +49,13 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Gives up after ~2^28 clock ticks (over a tenth of a second; a healthy wait lasts microseconds)
-// or as soon as another role of the
-// CTA has raised *abort; on giving up it raises *abort itself and returns false.  Callers then skip
-// their remaining work and fall through to the common teardown, so the kernel always terminates.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+// Bounded wait.  Gives up after `limit` clock ticks (default 2^28: over a tenth of a second; a healthy wait lasts
+// microseconds) or as soon as another role of the CTA has raised *abort; on giving up it raises *abort itself and
+// returns false.  Callers then skip their remaining work and fall through to the common teardown, so the kernel
+// always terminates.
+constexpr long long kWaitLimitClocks = 1ll << 28;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                          long long limit = kWaitLimitClocks) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
@@ -61,7 +63,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
-    if (clock64() - t0 > (1ll << 28)) {
+    if (clock64() - t0 > limit) {
       *abort = 1;
       return false;
     }
@@ -71,8 +73,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // Whole-warp form: every lane waits (one warp-wide instruction per poll), the verdict is made uniform.
 // Roles that issue tcgen05 instructions run their loops warp-uniformly and elect one lane per
 // instruction, so that descriptors and addresses stay in the uniform datapath.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort));
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                               long long limit = kWaitLimitClocks) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort, limit));
 }
 // true in exactly one lane of a converged warp (the same lane every time)
 __device__ __forceinline__ bool elect_one() {
@@ -83,6 +86,25 @@ __device__ __forceinline__ bool elect_one() {
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(pred));
   return pred != 0;
+}
+
+// Time-out record of the library, one per device: the count of CTAs that ever gave up on a bounded wait, and the
+// address (filled in by the host at set-up) of a flag in mapped host memory that the host can test without
+// synchronising.  Kernels get a pointer to `count`.
+struct TimeoutRecord {
+  int count;
+  int reserved;
+  int* host_flag;
+};
+// called by one thread of a CTA whose roles gave up on a wait
+__device__ __forceinline__ void report_timeout(int* count) {
+  if (!count) return;
+  atomicAdd(count, 1);
+  int* hf = reinterpret_cast<TimeoutRecord*>(count)->host_flag;
+  if (hf) {
+    *(volatile int*)hf = 1;
+    __threadfence_system();
+  }
 }
 
 // ---------------------------------------------------------------- TMA (tiled bulk tensor loads, this CTA only)

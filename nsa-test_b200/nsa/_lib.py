@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libnsa_b200.so")
 
 F32, BF16 = 0, 1
 GATE_SIGMOID, GATE_SOFTMAX = 0, 1
+FLAG_GENERIC = 1
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -32,27 +33,24 @@ _I64P = POINTER(c_int64)
 PROTOTYPES = {
     "nsa_last_error": (c_char_p, []),
     "nsa_version": (c_char_p, []),
-    "nsa_set_kernel_family": (c_int, [c_int]),
-    "nsa_set_dq_addends": (c_int, [c_void_p, c_void_p]),
-    "nsa_set_row_delta": (c_int, [c_void_p]),
-    "nsa_set_query_offset": (c_int, [c_int]),
+    "nsa_selftest_wait_timeout": (c_int, [ctypes.c_longlong, _P]),
     "nsa_profile_enable": (c_int, [c_int]),
     "nsa_profile_report": (c_int, [ctypes.c_char_p, c_size_t]),
     "nsa_device_timeouts": (c_int, [c_int]),
-    "nsa_sliding_fwd": (c_int, [_P] * 6 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P]),
+    "nsa_sliding_fwd": (c_int, [_P] * 6 + [_I64P] + [c_int] * 7 + [c_float, c_int, c_int, _P]),
     "nsa_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 8),
-    "nsa_sliding_bwd": (c_int, [_P] * 10 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P, c_size_t, _P]),
+    "nsa_sliding_bwd": (c_int, [_P] * 10 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P, c_int, _P, c_size_t, _P]),
     "nsa_sliding_bwd_noalloc": (c_int, [_P] * 10 + [c_int] * 7 + [c_float, _P]),
-    "nsa_cmp_attn_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 7 + [c_float, c_int, c_int, c_int, c_int, _P]),
-    "nsa_cmp_attn_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 7 + [c_float, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
-    "nsa_slc_fwd_workspace_bytes": (c_size_t, [c_int] * 10),
-    "nsa_slc_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 9 + [c_float, c_int, _P, c_size_t, _P]),
-    "nsa_slc_bwd_workspace_bytes": (c_size_t, [c_int] * 10),
-    "nsa_slc_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 9 + [c_float, c_int, _P, c_size_t, _P]),
+    "nsa_cmp_attn_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 7 + [c_float] + [c_int] * 6 + [_P]),
+    "nsa_cmp_attn_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 7 + [c_float] + [c_int] * 5 + [_P, c_int, _P, c_size_t, _P]),
+    "nsa_slc_fwd_workspace_bytes": (c_size_t, [c_int] * 11),
+    "nsa_slc_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 9 + [c_float, c_int, c_int, c_int, _P, c_size_t, _P]),
+    "nsa_slc_bwd_workspace_bytes": (c_size_t, [c_int] * 11),
+    "nsa_slc_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 9 + [c_float, c_int, c_int, _P, _P, _P, c_int, _P, c_size_t, _P]),
     "nsa_phi_pool_fwd": (c_int, [_P, _P, _P, _I64P, _P, _P] + [c_int] * 10 + [_P]),
     "nsa_phi_pool_bwd": (c_int, [_P] * 7 + [c_int] * 9 + [_P]),
-    "nsa_score_topn_workspace_bytes": (c_size_t, [c_int] * 11),
-    "nsa_score_topn": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 11 + [c_float, c_int, c_int, _P, c_size_t, _P]),
+    "nsa_score_topn_workspace_bytes": (c_size_t, [c_int] * 12),
+    "nsa_score_topn": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 11 + [c_float, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "nsa_topn_from_scores": (c_int, [_P, _P] + [c_int] * 8 + [_P]),
     "nsa_cmp_probs": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 6 + [c_float, c_int, _P]),
     "nsa_eq9_scores": (c_int, [_P, _P, c_int64] + [c_int] * 4 + [_P]),

@@ -194,13 +194,11 @@ class _BranchesAndMix(torch.autograd.Function):
          gates) = ctx.saved_tensors
         d_cmp, d_slc, d_win, dlogits, delta = ops.gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, ctx.gate_mode,
                                                                want_delta=True)
-        with ops.row_delta(delta[0]):
-            dq_c, dkc, dvc = ops.cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o_cmp, d_cmp, Lc, Mc, ctx.scale, ctx.blocks)
-        with ops.row_delta(delta[2]):
-            dq_w, dkw, dvw = ops.sliding_bwd(q, k_win, v_win, o_win, d_win, Lw, Mw, ctx.w, ctx.scale)
-        with ops.row_delta(delta[1]):
-            dq, dks, dvs = ops.slc_bwd(q, k_slc, v_slc, idx, o_slc, d_slc, Ls, Ms, ctx.l_prime, ctx.scale,
-                                       dq_addends=(dq_c, dq_w))
+        dq_c, dkc, dvc = ops.cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o_cmp, d_cmp, Lc, Mc, ctx.scale, ctx.blocks,
+                                          row_delta=delta[0])
+        dq_w, dkw, dvw = ops.sliding_bwd(q, k_win, v_win, o_win, d_win, Lw, Mw, ctx.w, ctx.scale, row_delta=delta[2])
+        dq, dks, dvs = ops.slc_bwd(q, k_slc, v_slc, idx, o_slc, d_slc, Ls, Ms, ctx.l_prime, ctx.scale,
+                                   dq_addends=(dq_c, dq_w), row_delta=delta[1])
         return (dq, dkc.transpose(-1, -2), dvc, None, dks.transpose(-1, -2), dvs, None, dkw.transpose(-1, -2), dvw,
                 dlogits.to(ctx.ldtype), None, None, None)
 
@@ -337,7 +335,7 @@ def _sliding_with_offset(q, kw, vw, scale, cfg, q_pos0: int):
 
 
 def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv_compress=None, kv_sliding=None,
-              scale: Optional[float] = None, return_info: bool = False, q_pos0: int = 0):
+              scale: Optional[float] = None, return_info: bool = False, q_pos0: int = 0, indices=None):
     """The NSA hot path between the q/k/v projections and o_proj (nsa/kernels.py:2298-2463).
 
     q [B,H,T,dk]; k_* [B,G,dk,T]; v_* [B,G,T,dv]; gate_logits [B,T,3H]; phi_params =
@@ -348,6 +346,9 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
     Query-sharded long-context runs: q and gate_logits hold the Tq query rows at positions
     ``q_pos0 + [0, Tq)`` while k/v cover the sequence from position 0 (at least up to the last query); the
     gradients of k/v then hold this query slice's contribution only (summed over the ranks by the caller).
+
+    ``indices`` [B,G,Tq,n] (int) replaces the layer's own Eq. 8-11 block choice, e.g. to evaluate two
+    implementations on identical selections; the selection is not differentiable either way.
     """
     cfg = config
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
@@ -364,7 +365,8 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
         pk = lambda kv: None if kv is None else (F.pad(kv[0], (0, pad)), F.pad(kv[1], (0, 0, 0, pad)))
         res = nsa_layer(F.pad(q, (0, 0, 0, pad)), *pk((k_slc, v_slc)), F.pad(gate_logits, (0, 0, 0, pad)), phi_params,
                         config, kv_compress=pk(kv_compress), kv_sliding=pk(kv_sliding), scale=scale,
-                        return_info=return_info)
+                        return_info=return_info,
+                        indices=None if indices is None else F.pad(indices, (0, 0, 0, pad), value=-1))
         if not return_info:
             return res[:, :, :T_in]
         out, info = res
@@ -386,8 +388,11 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
     block_ends = torch.full((k_cmp.shape[-1],), PAD_BLOCK_END, device=q.device, dtype=torch.int32)
     block_ends[:nb] = torch.arange(nb, device=q.device, dtype=torch.int32) * cfg.d + (cfg.l - 1)
     n_fixed = cfg.n_fixed if cfg.include_fixed_in_selection else 0
-    indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale, nb,
-                             q_pos0)
+    if indices is None:
+        indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale,
+                                 nb, q_pos0)
+    else:
+        indices = indices.to(device=q.device, dtype=torch.int32).contiguous()
     if q_pos0 == 0 and kw.shape[-1] == q.shape[2]:
         out, gates, o_cmp, o_slc, o_win = _BranchesAndMix.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, k_slc, v_slc, indices,
                                                                 kw, vw, gate_logits, scale, cfg, (cfg.l, cfg.d, nb))
@@ -511,9 +516,11 @@ class _Launcher:
     """``launcher[grid](*positional, **constexpr)`` with the reference kernel's parameter order.
 
     ``grid`` is accepted and ignored (the CUDA kernels size their own grids), as are BLOCK_M/BLOCK_N.
-    The strides passed by the caller are honoured as given; if they address memory beyond a tensor's
-    storage (the contract tests pass wrong strides on purpose), the tensor is first copied into a
-    zero-padded buffer so that nothing is read out of bounds.
+    The strides passed by the caller are honoured as given.  Before any launch the extent every tensor's strides
+    address is checked against its storage: a tensor the kernels read (Q, K, V, dOut, and Out/L/M in the backward) is
+    served from a zero-padded copy when the strides reach past it (the contract tests pass wrong K strides on purpose
+    and expect a different answer, not a fault); a tensor the kernels write (Out, L, M, dQ, dK, dV) or the index tensor
+    raises ValueError instead, as do negative strides and a Block_ends shorter than N_BLOCKS.
     """
 
     def __init__(self, name: str, positional: List[str], kind: str, backward: bool):
@@ -533,15 +540,36 @@ class _Launcher:
         return launch
 
     @staticmethod
-    def _safe(t: torch.Tensor, strides, dims):
-        need = 1 + sum((int(n) - 1) * int(s) for n, s in zip(dims, strides) if n > 0)
-        have = t.untyped_storage().nbytes() // t.element_size() - t.storage_offset()
+    def _extent(name: str, strides, dims) -> int:
+        """Elements from the first to one past the last one addressed through ``strides`` over ``dims``."""
+        if any(int(s_) < 0 for s_ in strides):
+            raise ValueError(f"{name}: negative strides are not supported")
+        if any(int(n_) <= 0 for n_ in dims):
+            return 0
+        return 1 + sum((int(n_) - 1) * int(s_) for n_, s_ in zip(dims, strides))
+
+    @staticmethod
+    def _have(t: torch.Tensor) -> int:
+        return t.untyped_storage().nbytes() // t.element_size() - t.storage_offset()
+
+    @classmethod
+    def _safe(cls, name: str, t: torch.Tensor, strides, dims):
+        """A tensor the kernels only READ: served from a zero-padded copy when the strides reach past its storage."""
+        need, have = cls._extent(name, strides, dims), cls._have(t)
         if need <= have:
             return t
         buf = torch.zeros(need, device=t.device, dtype=t.dtype)
-        flat = torch.as_strided(t, (have,), (1,))
-        buf[:have] = flat
+        buf[:have] = torch.as_strided(t, (have,), (1,))
         return buf
+
+    @classmethod
+    def _fits(cls, name: str, t: torch.Tensor, strides, dims):
+        """A tensor the kernels WRITE: refused (before any launch) when the strides reach past its storage."""
+        need, have = cls._extent(name, strides, dims), cls._have(t)
+        if need > have:
+            raise ValueError(f"{name}: strides {tuple(int(s_) for s_ in strides)} over shape {tuple(int(n_) for n_ in dims)} "
+                             f"address {need} elements but the tensor's storage holds {have}")
+        return t
 
     def _run(self, a):
         from ._lib import check, dtype_code, i64, lib, ptr, require_cuda, stream_ptr
@@ -563,60 +591,77 @@ class _Launcher:
         scale = float(a["sm_scale"])
         dev = require_cuda(Q, K, V, Out)
         sq, sk, sv, so = ([a[n] for n in names] for names in (_Q, _K, _V, _O))
-        Q = self._safe(Q, sq, (B, H, Tq, dk))
-        K = self._safe(K, sk, (B, G, Tk, dk))
-        V = self._safe(V, sv, (B, G, Tk, dv))
+        sl, sm = [a[n] for n in _LM[:3]], [a[n] for n in _LM[3:]]
         L, M = a["L"], a["M"]
-        strides = sq + sk + sv + so + [a[n] for n in _LM]
-        tail = []
+        Q = self._safe("Q", Q, sq, (B, H, Tq, dk))
+        K = self._safe("K", K, sk, (B, G, Tk, dk))
+        V = self._safe("V", V, sv, (B, G, Tk, dv))
+        if self.backward:      # read by the backward kernels
+            Out = self._safe("Out", Out, so, (B, H, Tq, dv))
+            L = self._safe("L", L, sl, (B, H, Tq))
+            M = self._safe("M", M, sm, (B, H, Tq))
+        else:                  # written by the forward kernels
+            self._fits("Out", Out, so, (B, H, Tq, dv))
+            self._fits("L", L, sl, (B, H, Tq))
+            self._fits("M", M, sm, (B, H, Tq))
+        strides = sq + sk + sv + so + sl + sm
         idx = None
         if self.backward:
-            strides += [a[n] for n in _DG]
+            sdq, sdk, sdv = ([a[n] for n in names] for names in (_DG[:4], _DG[4:8], _DG[8:]))
+            strides += sdq + sdk + sdv
+            dO = self._safe("dOut", a["dOut"], so, (B, H, Tq, dv))     # dOut shares Out's strides
+            dQ = self._fits("dQ", a["dQ"], sdq, (B, H, Tq, dk))
+            dK = self._fits("dK", a["dK"], sdk, (B, G, Tk, dk))
+            dV = self._fits("dV", a["dV"], sdv, (B, G, Tk, dv))
         if kind == "slc":
             idx = a["Block_indices"]
             if idx.dtype != torch.int32:
                 raise TypeError("Block_indices must be int32")
-            strides += [a[n] for n in _BI]
+            sb = [a[n] for n in _BI]
+            self._fits("Block_indices", idx, sb, (B, G, Tq, int(a["N_BLOCKS"])))
+            strides += sb
             if not bool(a.get("IS_CAUSAL", True)):
                 raise NotImplementedError("selection kernels are causal")
+        be = None
+        if kind == "cmp":
+            be = a["Block_ends"].to(torch.int32).contiguous()
+            if be.numel() < Tk:
+                raise ValueError(f"Block_ends holds {be.numel()} entries, N_BLOCKS is {Tk}")
         code = dtype_code(Q)
         st = stream_ptr(dev)
         with torch.cuda.device(dev):
             if not self.backward:
                 if kind == "win":
                     rc = lib.nsa_sliding_fwd(ptr(Q), ptr(K), ptr(V), ptr(Out), ptr(L), ptr(M), i64(strides), B, H, G, Tq,
-                                             dk, dv, int(a["WINDOW_SIZE"]), scale, code, st)
+                                             dk, dv, int(a["WINDOW_SIZE"]), scale, code, 0, st)
                 elif kind == "cmp":
-                    be = a["Block_ends"].to(torch.int32).contiguous()
                     rc = lib.nsa_cmp_attn_fwd(ptr(Q), ptr(K), ptr(V), ptr(be), ptr(Out), ptr(L), ptr(M), i64(strides), B, H,
-                                              G, Tq, Tk, dk, dv, scale, code, 0, 0, 0, st)
+                                              G, Tq, Tk, dk, dv, scale, code, 0, 0, 0, 0, 0, st)
                 else:
                     n, lp = int(a["N_BLOCKS"]), int(a["BLOCK_SIZE_SELECTION"])
-                    nbytes = lib.nsa_slc_fwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, n, lp, code)
+                    nbytes = lib.nsa_slc_fwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, n, lp, code, 0)
                     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
                     rc = lib.nsa_slc_fwd(ptr(Q), ptr(K), ptr(V), ptr(idx), ptr(Out), ptr(L), ptr(M), i64(strides), B, H, G,
-                                         Tq, Tk, n, lp, dk, dv, scale, code, ptr(ws), nbytes, st)
+                                         Tq, Tk, n, lp, dk, dv, scale, code, 0, 0, ptr(ws), nbytes, st)
             else:
-                dO, dQ, dK, dV = a["dOut"], a["dQ"], a["dK"], a["dV"]
                 if kind == "win":
                     nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, 0)
                     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
                     rc = lib.nsa_sliding_bwd(ptr(Q), ptr(K), ptr(V), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ), ptr(dK),
                                              ptr(dV), i64(strides), B, H, G, Tq, dk, dv, int(a["WINDOW_SIZE"]), scale, code,
-                                             ptr(ws), nbytes, st)
+                                             None, 0, ptr(ws), nbytes, st)
                 elif kind == "cmp":
-                    be = a["Block_ends"].to(torch.int32).contiguous()
                     rc = lib.nsa_cmp_attn_bwd(ptr(Q), ptr(K), ptr(V), ptr(be), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ),
                                               ptr(dK), ptr(dV), i64(strides), B, H, G, Tq, Tk, dk, dv, scale, code, 0, 0, 0,
-                                              None, 0, st)
+                                              0, None, 0, None, 0, st)
                 else:
                     n = int(a["N_BLOCKS"])
                     lp = int(a["BLOCK_SIZE_SELECTION"])
-                    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, n, lp, code)
+                    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, n, lp, code, 0)
                     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
                     rc = lib.nsa_slc_bwd(ptr(Q), ptr(K), ptr(V), ptr(idx), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ),
                                          ptr(dK), ptr(dV), i64(strides), B, H, G, Tq, Tk, n, lp, dk, dv, scale, code,
-                                         ptr(ws), nbytes, st)
+                                         0, None, None, None, 0, ptr(ws), nbytes, st)
         check(rc, self.__name__)
 
 

@@ -36,20 +36,23 @@ def _stats(q, o_dv):
 # the three branches
 # ------------------------------------------------------------------------------------------------
 
-def sliding_fwd(q, k, v, window: int, scale: float):
+def sliding_fwd(q, k, v, window: int, scale: float, generic: bool = False):
+    """``generic=True`` forces the stride-generic kernels (cross-checks); same for the functions below."""
     dev = require_cuda(q, k, v)
     B, H, T, dk = q.shape
     G, dv = k.shape[1], v.shape[-1]
     o, L, M = _stats(q, dv)
     with torch.cuda.device(dev):
         check(lib.nsa_sliding_fwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(L), ptr(M), i64(_fwd_strides(q, k, v, o, L, M)),
-                                  B, H, G, T, dk, dv, int(window), float(scale), dtype_code(q), stream_ptr(dev)),
-              "nsa_sliding_fwd")
+                                  B, H, G, T, dk, dv, int(window), float(scale), dtype_code(q), _flags(generic),
+                                  stream_ptr(dev)), "nsa_sliding_fwd")
     return o, L, M
 
 
-def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float):
+def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float, row_delta=None, generic: bool = False):
+    """``row_delta``: the row sums dO.O [B,H,T] (fp32) when the caller has them, else they are computed here."""
     dev = require_cuda(q, k, v, o, do, L, M)
+    delta, dptr = _delta_ptr(row_delta, q)
     B, H, T, dk = q.shape
     G, dv = k.shape[1], v.shape[-1]
     if do.stride() != o.stride():
@@ -63,46 +66,26 @@ def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float):
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
         check(lib.nsa_sliding_bwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq), ptr(dkey), ptr(dval),
-                                  i64(s), B, H, G, T, dk, dv, int(window), float(scale), dtype_code(q), ptr(ws), nbytes,
-                                  stream_ptr(dev)), "nsa_sliding_bwd")
+                                  i64(s), B, H, G, T, dk, dv, int(window), float(scale), dtype_code(q), dptr, _flags(generic),
+                                  ptr(ws), nbytes, stream_ptr(dev)), "nsa_sliding_bwd")
     return dq, dkey, dval
 
 
-class row_delta:
-    """``with row_delta(d):`` hands the row sums dO.O [B,H,T] (fp32) to the backward call inside the block."""
-
-    def __init__(self, delta):
-        self.delta = None if delta is None else delta.contiguous()   # kept alive until the block ends
-
-    def __enter__(self):
-        if self.delta is not None:
-            check(lib.nsa_set_row_delta(ptr(self.delta)), "nsa_set_row_delta")
-
-    def __exit__(self, *exc):
-        if self.delta is not None:
-            lib.nsa_set_row_delta(None)
-        return False
+def _flags(generic: bool) -> int:
+    return _lib.FLAG_GENERIC if generic else 0
 
 
-class query_offset:
-    """``with query_offset(p):`` the library calls made inside treat query row t as position p + t of the sequence
-    (query-sharded long-context runs; keys start at position 0).  Thread-local in the library; restored to 0 on exit."""
-
-    def __init__(self, position: int):
-        self.position = int(position)
-
-    def __enter__(self):
-        if self.position:
-            check(lib.nsa_set_query_offset(self.position), "nsa_set_query_offset")
-        return self
-
-    def __exit__(self, *exc):
-        if self.position:
-            lib.nsa_set_query_offset(0)
-        return False
+def _delta_ptr(row_delta, q):
+    """Row sums dO.O [B,H,T] fp32 handed to a backward call, or None."""
+    if row_delta is None:
+        return None, None
+    d = row_delta.contiguous()
+    if d.dtype != torch.float32 or d.shape != q.shape[:3] or d.device != q.device:
+        raise ValueError("row_delta must be a float32 [B,H,T] tensor on the device of q")
+    return d, ptr(d)
 
 
-def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None, q_pos0: int = 0):
+def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None, q_pos0: int = 0, generic: bool = False):
     """``blocks=(l, d, n_blocks)`` asserts block_ends[i] == i*d + l - 1 for i < n_blocks and no later block
     ever visible; it lets the tensor-core kernel bound its key loop."""
     bl, bd, bn = blocks if blocks is not None else (0, 0, 0)
@@ -111,16 +94,19 @@ def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None, q_pos0:
     G, NB, dv = k_cmp.shape[1], k_cmp.shape[-1], v_cmp.shape[-1]
     be = block_ends.to(torch.int32).contiguous()
     o, L, M = _stats(q, dv)
-    with torch.cuda.device(dev), query_offset(q_pos0):
+    with torch.cuda.device(dev):
         check(lib.nsa_cmp_attn_fwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(L), ptr(M),
                                    i64(_fwd_strides(q, k_cmp, v_cmp, o, L, M)), B, H, G, T, NB, dk, dv, float(scale),
-                                   dtype_code(q), int(bl), int(bd), int(bn), stream_ptr(dev)), "nsa_cmp_attn_fwd")
+                                   dtype_code(q), int(bl), int(bd), int(bn), int(q_pos0), _flags(generic), stream_ptr(dev)),
+              "nsa_cmp_attn_fwd")
     return o, L, M
 
 
-def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=None, q_pos0: int = 0):
+def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=None, q_pos0: int = 0, row_delta=None,
+                 generic: bool = False):
     bl, bd, bn = blocks if blocks is not None else (0, 0, 0)
     dev = require_cuda(q, k_cmp, v_cmp, block_ends, o, do, L, M)
+    delta, dptr = _delta_ptr(row_delta, q)
     B, H, T, dk = q.shape
     G, NB, dv = k_cmp.shape[1], k_cmp.shape[-1], v_cmp.shape[-1]
     be = block_ends.to(torch.int32).contiguous()
@@ -133,14 +119,15 @@ def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=
     s = _fwd_strides(q, k_cmp, v_cmp, o, L, M) + list(dq.stride()) + list(dkc.stride()) + list(dvc.stride())
     nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, T, NB, dk, dv, 1)
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-    with torch.cuda.device(dev), query_offset(q_pos0):
+    with torch.cuda.device(dev):
         check(lib.nsa_cmp_attn_bwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq),
                                    ptr(dkc), ptr(dvc), i64(s), B, H, G, T, NB, dk, dv, float(scale), dtype_code(q),
-                                   int(bl), int(bd), int(bn), ptr(ws), nbytes, stream_ptr(dev)), "nsa_cmp_attn_bwd")
+                                   int(bl), int(bd), int(bn), int(q_pos0), dptr, _flags(generic), ptr(ws), nbytes,
+                                   stream_ptr(dev)), "nsa_cmp_attn_bwd")
     return dq, dkc, dvc
 
 
-def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float, q_pos0: int = 0):
+def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float, q_pos0: int = 0, generic: bool = False):
     dev = require_cuda(q, k, v, indices_i32)
     B, H, Tq, dk = q.shape
     G, Tkv, dv = k.shape[1], k.shape[-1], v.shape[-1]
@@ -148,19 +135,21 @@ def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float, q_pos0: int = 0):
     o, L, M = _stats(q, dv)
     s = _fwd_strides(q, k, v, o, L, M) + list(indices_i32.stride())
     n = indices_i32.shape[-1]
-    nbytes = lib.nsa_slc_fwd_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n, int(l_prime), dtype_code(q))
+    nbytes = lib.nsa_slc_fwd_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n, int(l_prime), dtype_code(q), _flags(generic))
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-    with torch.cuda.device(dev), query_offset(q_pos0):
+    with torch.cuda.device(dev):
         check(lib.nsa_slc_fwd(ptr(q), ptr(k), ptr(v), ptr(indices_i32), ptr(o), ptr(L), ptr(M), i64(s), B, H, G, Tq, Tkv,
-                              n, int(l_prime), dk, dv, float(scale), dtype_code(q), ptr(ws), nbytes, stream_ptr(dev)),
-              "nsa_slc_fwd")
+                              n, int(l_prime), dk, dv, float(scale), dtype_code(q), int(q_pos0), _flags(generic), ptr(ws),
+                              nbytes, stream_ptr(dev)), "nsa_slc_fwd")
     return o, L, M
 
 
-def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float, q_pos0: int = 0, dq_addends=()):
+def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float, q_pos0: int = 0, dq_addends=(), row_delta=None,
+            generic: bool = False):
     """``dq_addends``: up to two tensors shaped and typed like q (the dQ of the other branches) that the kernel adds
     to the selection branch's dQ before the one rounding of the sum."""
     dev = require_cuda(q, k, v, indices_i32, o, do, L, M)
+    delta, dptr = _delta_ptr(row_delta, q)
     B, H, Tq, dk = q.shape
     G, Tkv, dv = k.shape[1], k.shape[-1], v.shape[-1]
     n = indices_i32.shape[-1]
@@ -170,19 +159,20 @@ def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float, q_pos
     dq = torch.empty_like(q, memory_format=torch.contiguous_format)
     dkey = torch.zeros(B, G, Tkv, dk, device=dev, dtype=q.dtype)
     dval = torch.zeros(B, G, Tkv, dv, device=dev, dtype=q.dtype)
-    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n, int(l_prime), dtype_code(q))
+    nbytes = lib.nsa_slc_bwd_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n, int(l_prime), dtype_code(q), _flags(generic))
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     s = (_fwd_strides(q, k, v, o, L, M) + list(dq.stride()) + list(dkey.stride()) + list(dval.stride())
          + list(indices_i32.stride()))
     adds = [a.contiguous() for a in dq_addends]
     if any(a.shape != q.shape or a.dtype != q.dtype or a.device != q.device for a in adds) or len(adds) > 2:
         raise ValueError("slc_bwd: dq_addends must be at most two tensors shaped and typed like q")
-    with torch.cuda.device(dev), query_offset(q_pos0):
-        if adds:
-            check(lib.nsa_set_dq_addends(ptr(adds[0]), ptr(adds[1]) if len(adds) > 1 else None), "nsa_set_dq_addends")
+    add0 = ptr(adds[0]) if len(adds) > 0 else None
+    add1 = ptr(adds[1]) if len(adds) > 1 else None
+    with torch.cuda.device(dev):
         check(lib.nsa_slc_bwd(ptr(q), ptr(k), ptr(v), ptr(indices_i32), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq),
                               ptr(dkey), ptr(dval), i64(s), B, H, G, Tq, Tkv, n, int(l_prime), dk, dv, float(scale),
-                              dtype_code(q), ptr(ws), nbytes, stream_ptr(dev)), "nsa_slc_bwd")
+                              dtype_code(q), int(q_pos0), dptr, add0, add1, _flags(generic), ptr(ws), nbytes,
+                              stream_ptr(dev)), "nsa_slc_bwd")
     return dq, dkey, dval
 
 
@@ -220,7 +210,7 @@ def phi_pool_bwd(a, c, dhbar, dv_cmp, l: int, d: int, n_blocks: int):
 
 
 def score_topn(q, k_cmp_f32, block_ends, l: int, d: int, l_prime: int, n: int, n_fixed: int, scale: float,
-               n_real_blocks: int = -1, q_pos0: int = 0):
+               n_real_blocks: int = -1, q_pos0: int = 0, generic: bool = False):
     """q [B,H,T,dk], k_cmp fp32 [B,G,dk,nbp] -> int32 indices [B,G,T,n].  ``n_real_blocks >= 0`` asserts the
     canonical block ends (block i ends at i*d + l - 1 for i < n_real_blocks, later blocks never visible)."""
     dev = require_cuda(q, k_cmp_f32, block_ends)
@@ -229,12 +219,13 @@ def score_topn(q, k_cmp_f32, block_ends, l: int, d: int, l_prime: int, n: int, n
     kc = k_cmp_f32.float().contiguous()
     be = block_ends.to(torch.int32).contiguous()
     out = torch.empty(B, G, T, n, device=dev, dtype=torch.int32)
-    nbytes = lib.nsa_score_topn_workspace_bytes(B, H, G, T, dk, nbp, int(l), int(d), int(l_prime), int(n), dtype_code(q))
+    nbytes = lib.nsa_score_topn_workspace_bytes(B, H, G, T, dk, nbp, int(l), int(d), int(l_prime), int(n), dtype_code(q),
+                                                _flags(generic))
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-    with torch.cuda.device(dev), query_offset(q_pos0):
+    with torch.cuda.device(dev):
         check(lib.nsa_score_topn(ptr(q), i64(q.stride()), ptr(kc), ptr(be), ptr(out), B, H, G, T, dk, nbp, int(l), int(d),
-                                 int(l_prime), int(n), int(n_fixed), float(scale), dtype_code(q), int(n_real_blocks), ptr(ws),
-                                 nbytes, stream_ptr(dev)), "nsa_score_topn")
+                                 int(l_prime), int(n), int(n_fixed), float(scale), dtype_code(q), int(n_real_blocks),
+                                 int(q_pos0), _flags(generic), ptr(ws), nbytes, stream_ptr(dev)), "nsa_score_topn")
     return out
 
 

@@ -25,8 +25,10 @@ from dataclasses import dataclass
 from typing import Callable, Dict, Optional, Tuple
 
 import torch
+import torch.utils.checkpoint
 
 PAD_BLOCK_END = 999999  # sentinel block end of padded compressed blocks (nsa/kernels.py:2190)
+LOW_MEMORY = False      # True: the dense score chunks are recomputed in backward (same numbers, a fraction of the memory)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -56,11 +58,9 @@ def masked_attention(
     B, H, T, dk = q.shape
     ke = _expand_groups(k, H)
     ve = _expand_groups(v, H)
-    outs, Ms, Ls = [], [], []
-    for t0 in range(0, T, chunk):
-        t1 = min(T, t0 + chunk)
-        s = torch.matmul(q[:, :, t0:t1] * scale, ke)                       # [B,H,c,Tk]
-        vis = visible(t0, t1)
+
+    def one_chunk(qc, ke_, ve_, vis):
+        s = torch.matmul(qc * scale, ke_)                                   # [B,H,c,Tk]
         s = s.masked_fill(~vis, float("-inf"))
         m = s.amax(dim=-1, keepdim=True)
         has = torch.isfinite(m)
@@ -68,10 +68,21 @@ def masked_attention(
         e = torch.exp(s - m_safe)                                           # masked -> exp(-inf) = 0
         l = e.sum(dim=-1, keepdim=True)
         p = e / torch.where(has, l, torch.ones_like(l))
-        outs.append(torch.matmul(p, ve))
-        Ms.append(m.squeeze(-1))
-        Ls.append(torch.where(has, torch.log(torch.where(has, l, torch.ones_like(l))),
-                              torch.full_like(l, float("-inf"))).squeeze(-1))
+        L_ = torch.where(has, torch.log(torch.where(has, l, torch.ones_like(l))), torch.full_like(l, float("-inf")))
+        return torch.matmul(p, ve_), m.squeeze(-1), L_.squeeze(-1)
+
+    outs, Ms, Ls = [], [], []
+    for t0 in range(0, T, chunk):
+        t1 = min(T, t0 + chunk)
+        vis = visible(t0, t1)
+        if LOW_MEMORY and torch.is_grad_enabled():
+            # same operations, recomputed in the backward pass instead of kept: long sequences with many heads
+            o_, m_, l_ = torch.utils.checkpoint.checkpoint(one_chunk, q[:, :, t0:t1], ke, ve, vis, use_reentrant=False)
+        else:
+            o_, m_, l_ = one_chunk(q[:, :, t0:t1], ke, ve, vis)
+        outs.append(o_)
+        Ms.append(m_)
+        Ls.append(l_)
     return torch.cat(outs, 2), torch.cat(Ms, 2), torch.cat(Ls, 2)
 
 
@@ -188,13 +199,15 @@ def compress_tokens(keys: torch.Tensor, values: torch.Tensor, phi: PhiParams, l:
     return k_cmp, v_cmp, block_ends, nb
 
 
-def compression_probabilities(q, k_cmp, block_ends, scale: float) -> torch.Tensor:
+def compression_probabilities(q, k_cmp, block_ends, scale: float, positions=None) -> torch.Tensor:
     """Eq. 8 (nsa/kernels.py:2316-2343): softmax over visible compressed blocks; a row that sees no
-    block falls back to block 0 alone (one-hot).  Returns [B,H,T,nbp]."""
+    block falls back to block 0 alone (one-hot).  Returns [B,H,T,nbp].  ``positions`` [T] gives the
+    sequence position of every query row when the rows are a sample of a longer sequence (row t sits
+    at position t by default, as in the reference)."""
     B, H, T, _ = q.shape
     ke = _expand_groups(k_cmp, H)
     s = torch.matmul(q, ke) * scale
-    t = torch.arange(T)
+    t = torch.arange(T) if positions is None else positions.to(torch.int64)
     vis = block_ends.to(torch.int64)[None, :] <= t[:, None]                  # [T,nbp]
     first = torch.zeros_like(vis)
     first[:, 0] = True
@@ -220,18 +233,18 @@ def selection_scores_from_compression(p_cmp: torch.Tensor, l: int, d: int, l_pri
 
 
 def select_top_n(sel_scores: torch.Tensor, G: int, n: int, l_prime: int,
-                 include_fixed: bool = True, n_fixed: int = 3) -> torch.Tensor:
+                 include_fixed: bool = True, n_fixed: int = 3, positions=None) -> torch.Tensor:
     """Eq. 10/11 (nsa/kernels.py:1986-2040): sum the heads of each group, stable descending sort
     (ties to the lower block id), keep min(n, n_blocks); with fixed blocks, prepend
     [0, max(0,(t-l')//l'), t//l'], drop repeats keeping first occurrences, cut to n, pad with -1.
-    Returns int64 [B,G,T,n]."""
+    Returns int64 [B,G,T,n].  ``positions`` as in compression_probabilities."""
     B, H, T, nb = sel_scores.shape
     agg = sel_scores.view(B, G, H // G, T, nb).sum(dim=2)
     order = torch.sort(agg, dim=-1, descending=True, stable=True).indices[..., : min(n, nb)]
     if not (include_fixed and n_fixed > 0):
         pad = torch.full((B, G, T, n - order.shape[-1]), -1, dtype=torch.int64)
         return torch.cat([order, pad], dim=-1)[..., :n]
-    t = torch.arange(T)
+    t = torch.arange(T) if positions is None else positions.to(torch.int64)
     fixed = torch.stack([torch.zeros_like(t), torch.clamp((t - l_prime) // l_prime, min=0), t // l_prime], -1)
     cand = torch.cat([fixed.view(1, 1, T, 3).expand(B, G, T, 3), order], dim=-1)   # [B,G,T,C]
     C = cand.shape[-1]
@@ -243,6 +256,67 @@ def select_top_n(sel_scores: torch.Tensor, G: int, n: int, l_prime: int,
     slot = torch.where(keep & (rank < n), rank, torch.full_like(rank, n))
     out.scatter_(-1, slot, cand)
     return out[..., :n]
+
+
+# ----------------------------------------------------------------------------------------------
+# the three branches for a SAMPLE of query rows of a long sequence (row-by-row, as the reference loops)
+# ----------------------------------------------------------------------------------------------
+
+def _row_attention(qr: torch.Tensor, keys: torch.Tensor, vals: torch.Tensor, scale: float) -> torch.Tensor:
+    """One query position, the heads of one KV group: qr [hpg,dk], keys [dk,N], vals [N,dv] -> [hpg,dv];
+    N = 0 gives zeros (nsa/reference.py:133-141)."""
+    if keys.shape[-1] == 0:
+        return qr.new_zeros(qr.shape[0], vals.shape[-1])
+    p = torch.softmax((qr @ keys) * scale, dim=-1)
+    return p @ vals
+
+
+def branch_rows(q_rows, positions, k, v, k_cmp, v_cmp, block_ends, indices_rows, *, w: int, l_prime: int,
+                scale: Optional[float] = None):
+    """O_cmp, O_slc, O_win for sampled query rows of a sequence too long for the dense functions above.
+
+    q_rows [B,H,S,dk] are the queries at ``positions`` [S]; k [B,G,dk,T], v [B,G,T,dv] the whole
+    sequence; indices_rows [B,G,S,n] the selected blocks of those rows (all -1 falls back to the
+    query's own block, nsa/kernels.py:199-205).  Follows the reference's per-(batch, head, token) loops:
+    window keys [max(0,t-w+1), t] (nsa/reference.py:50-77), compressed blocks with block_ends <= t
+    (nsa/reference.py:116-141), union of the selected blocks clipped causally, ids < 0 or starting
+    beyond the keys ignored (nsa/reference.py:232-251).  Returns three [B,H,S,dv] tensors."""
+    B, H, S, dk = q_rows.shape
+    G, T = k.shape[1], k.shape[-1]
+    hpg = H // G
+    scale = 1.0 / math.sqrt(dk) if scale is None else scale
+    dv = v.shape[-1]
+    o_cmp, o_slc, o_win = (q_rows.new_zeros(B, H, S, dv) for _ in range(3))
+    be = block_ends.to(torch.int64)
+    for b in range(B):
+        for g in range(G):
+            hs = slice(g * hpg, (g + 1) * hpg)
+            for i, t in enumerate(int(x) for x in positions):
+                qr = q_rows[b, hs, i]
+                lo = max(0, t - w + 1)
+                o_win[b, hs, i] = _row_attention(qr, k[b, g, :, lo:t + 1], v[b, g, lo:t + 1], scale)
+                vis = (be <= t).nonzero().flatten()
+                o_cmp[b, hs, i] = _row_attention(qr, k_cmp[b, g][:, vis], v_cmp[b, g][vis], scale)
+                ids = [int(x) for x in indices_rows[b, g, i]]
+                if all(x < 0 for x in ids):
+                    ids = [t // l_prime]
+                keys = sorted({x for x in ids if x >= 0 and x * l_prime < T and x * l_prime <= t})   # future blocks hold no key <= t
+                pos = torch.cat([torch.arange(x * l_prime, min((x + 1) * l_prime, T, t + 1)) for x in keys]) if keys \
+                    else torch.zeros(0, dtype=torch.int64)
+                o_slc[b, hs, i] = _row_attention(qr, k[b, g][:, pos], v[b, g][pos], scale)
+    return o_cmp, o_slc, o_win
+
+
+def score_rows(q_rows, positions, k_cmp, block_ends, *, l: int, d: int, l_prime: int, n: int, scale: float,
+               include_fixed: bool = True, n_fixed: int = 3):
+    """Eq. 8 -> 9 -> 10/11 for sampled query rows: returns (indices [B,G,S,n] int64, aggregated scores
+    [B,G,S,n_sel]); the same three functions the layer composes, told the rows' positions."""
+    B, H, S, _ = q_rows.shape
+    G = k_cmp.shape[1]
+    p = compression_probabilities(q_rows, k_cmp, block_ends, scale, positions)
+    sel = selection_scores_from_compression(p, l, d, l_prime)
+    idx = select_top_n(sel, G, n, l_prime, include_fixed, n_fixed if include_fixed else 0, positions)
+    return idx, sel.view(B, G, H // G, S, -1).sum(dim=2)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -274,14 +348,15 @@ def mix_branches(gates, o_cmp, o_slc, o_win):
 
 def nsa_layer(q, k, v, x, phi: PhiParams, gp: GateParams, *, l=32, d=16, l_prime=64, n=16, w=512,
               include_fixed=True, n_fixed=3, gate_mode="sigmoid", scale=None,
-              kv_compress=None, kv_sliding=None) -> Dict[str, torch.Tensor]:
+              kv_compress=None, kv_sliding=None, indices=None) -> Dict[str, torch.Tensor]:
     """The layer between the q/k/v projections and o_proj.
 
     Composition of nsa/kernels.py:2298-2463 with the training-path fallback for all-(-1) index rows
     (nsa/kernels.py:199-205).  q [B,H,T,dk], k [B,G,dk,T], v [B,G,T,dv], x [B,T,d_model].  By
     default one k,v feeds the three branches; ``kv_compress`` / ``kv_sliding`` give the compression
     and sliding branches their own (k,v) as the reference module's separate projections do, (k,v)
-    then being the selection branch's.
+    then being the selection branch's.  ``indices`` [B,G,T,n] replaces the layer's own top-n choice
+    (used to compare implementations on identical selections; the scoring still runs and is returned).
     """
     B, H, T, dk = q.shape
     G = k.shape[1]
@@ -291,14 +366,15 @@ def nsa_layer(q, k, v, x, phi: PhiParams, gp: GateParams, *, l=32, d=16, l_prime
     k_cmp, v_cmp, block_ends, nb = compress_tokens(kc_src.transpose(-1, -2), vc_src, phi, l, d)
     p_cmp = compression_probabilities(q, k_cmp, block_ends, scale)
     sel = selection_scores_from_compression(p_cmp, l, d, l_prime)
-    idx = select_top_n(sel.detach(), G, n, l_prime, include_fixed, n_fixed if include_fixed else 0)
+    idx_own = select_top_n(sel.detach(), G, n, l_prime, include_fixed, n_fixed if include_fixed else 0)
+    idx = idx_own if indices is None else indices.to(torch.int64)
     o_cmp = compression_attention(q, k_cmp, v_cmp, block_ends, scale)
     o_slc = selection_attention(q, k, v, selection_fallback_indices(idx, l_prime), l_prime, scale)
     o_win = sliding_window_attention(q, kw, vw, w, scale)
     gates = gates_from_hidden(x, gp, H, gate_mode)
     out = mix_branches(gates, o_cmp, o_slc, o_win)
     return dict(out=out, o_cmp=o_cmp, o_slc=o_slc, o_win=o_win, indices=idx, gates=gates,
-                k_cmp=k_cmp, v_cmp=v_cmp, block_ends=block_ends, p_cmp=p_cmp, sel_scores=sel)
+                k_cmp=k_cmp, v_cmp=v_cmp, block_ends=block_ends, p_cmp=p_cmp, sel_scores=sel, indices_own=idx_own)
 
 
 # ----------------------------------------------------------------------------------------------

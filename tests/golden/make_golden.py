@@ -134,7 +134,7 @@ def run_case(name, c, K, R):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project (Noumena-Network/NSA-Test)")
     args = ap.parse_args()
     K, R = load_reference(args.reference)
     meta = {"torch": torch.__version__, "cases": CASES, "shapes": {}}

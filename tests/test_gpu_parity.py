@@ -13,7 +13,8 @@ import pytest
 import torch
 
 from oracle import nsa_oracle as O
-from tests.util import ambiguous_rows, max_abs, oracle_layer_with_grads, rel_err
+from tests.util import (INDEX_LOG, ambiguous_rows, check_layer_against_oracle, close, heads_mask, index_agreement, max_abs,
+                        oracle_layer_with_grads, rel_err)
 
 pytestmark = pytest.mark.gpu
 
@@ -313,6 +314,7 @@ def test_score_topn_indices_bit_exact(nsa_mod, name):
     agg = sel.view(c["B"], c["G"], c["H"] // c["G"], c["T"], -1).sum(2)
     amb = ambiguous_rows(agg, c["n"]) | (torch.from_numpy(g["indices_fp64"]) != gold).any(-1)
     mism = (idx != gold).any(-1)
+    INDEX_LOG.append((f"score_topn fp32 {name}", mism.numel(), int(amb.sum()), int(mism.sum()), int((mism & ~amb).sum())))
     assert not (mism & ~amb).any(), f"{int((mism & ~amb).sum())} unambiguous rows differ"
     assert amb.float().mean() < 0.05
     # Eq. 9 / Eq. 10-11 on materialised tensors through the mirrored host functions
@@ -371,53 +373,36 @@ def test_gate_mix(nsa_mod, mode, dtype, dv):
 # the whole layer (BASELINE config 1) and the module
 # ---------------------------------------------------------------------------------------------
 
-def _run_layer(nsa_mod, c, inp, dtype, gate_mode="sigmoid"):
-    from nsa.kernels import nsa_layer
-    cfg = _cfg(nsa_mod, c, gate_mode=gate_mode)
-    q, k, v = (_dev(inp[n], dtype, True) for n in ("q", "k", "v"))
-    phi, gp = inp["phi"], inp["gate"]
-    params = [_dev(p, grad=True) for p in (phi.pos_embed, phi.w1, phi.b1, phi.w2, phi.b2, gp.w1, gp.b1, gp.w2, gp.b2)]
-    x = _dev(inp["x"])
-    lin = torch.nn.functional.linear
-    logits = lin(torch.relu(lin(x, params[5], params[6])), params[7], params[8])
-    out, info = nsa_layer(q, k, v, logits, tuple(params[:5]), cfg, return_info=True)
-    grads = torch.autograd.grad(out, [q, k, v] + params, _dev(inp["do"], dtype))
-    return out, info, grads
-
-
 @pytest.mark.parametrize("name,gate_mode", [("cfg1", "sigmoid"), ("small", "softmax")])
 def test_layer_fp32_forward_backward(nsa_mod, name, gate_mode):
     c, g, inp = _case(name)
-    out, info, grads = _run_layer(nsa_mod, c, inp, torch.float32, gate_mode)
-    r, gref = oracle_layer_with_grads(inp, dict(c, gate_mode=gate_mode))
-    assert torch.equal(info["indices"].cpu().long(), r["indices"]), "selected block ids differ from the oracle"
-    for key in ("o_cmp", "o_slc", "o_win"):
-        assert rel_err(info[key], r[key]) < 1e-3
-    assert rel_err(out, r["out"]) < 1e-3
-    names = ["dq", "dk", "dv", "dpos", "dw1", "db1", "dw2", "db2", "dgw1", "dgb1", "dgw2", "dgb2"]
-    ref = dict(zip(names, gref))
-    for nme, a, b in zip(names, grads, gref):
-        if nme == "db2":
-            # a constant added to every compressed key leaves the softmax unchanged: the true gradient is
-            # zero and both sides hold rounding noise; compare on the scale of the weight gradient
-            assert max_abs(a, b) < 1e-3 * ref["dw2"].abs().max().item(), nme
-        else:
-            assert rel_err(a, b) < 1e-3, nme
+    info, mism, r = check_layer_against_oracle(f"layer fp32 {name}", nsa_mod, c, inp, torch.float32, gate_mode=gate_mode)
+    assert not mism.any(), "fp32 I/O: selected block ids must equal the oracle's on these fixtures"
 
 
 def test_layer_bf16_forward_backward(nsa_mod):
     c, g, inp = _case("cfg1")
     inp = O.make_inputs(c["B"], c["H"], c["G"], c["T"], c["dk"], c["dv"], c["d_model"], c["l"], seed=c["seed"],
                         l_prime=c["l_prime"], dtype=torch.bfloat16)
-    out, info, grads = _run_layer(nsa_mod, c, inp, torch.bfloat16)
-    r, gref = oracle_layer_with_grads(inp, c)
-    agg = r["sel_scores"].view(c["B"], c["G"], c["H"] // c["G"], c["T"], -1).sum(2)
-    mism = (info["indices"].cpu().long() != r["indices"]).any(-1)
-    assert not (mism & ~ambiguous_rows(agg, c["n"])).any()
-    if not mism.any():
-        assert max_abs(out.float(), r["out"]) < 2e-2
-        for a, b in zip(grads[:3], gref[:3]):
-            assert max_abs(a.float(), b) < 2e-2 * max(1.0, b.abs().max().item())
+    check_layer_against_oracle("layer bf16 cfg1", nsa_mod, c, inp, torch.bfloat16)
+
+
+@pytest.mark.timeout(1200)
+@pytest.mark.parametrize("T", [2048, 4096])
+def test_layer_bf16_at_the_benchmarked_head_configuration(nsa_mod, T):
+    """H=64 query heads in G=4 groups, dk=192, dv=128, keys with per-block offsets (BASELINE configs 3-5), bf16, through the
+    single autograd node the benchmark uses (dQ of the three branches summed in the selection backward, row sums handed
+    over by the gate/mix backward): outputs and all twelve gradients against the oracle."""
+    from nsa._lib import lib
+    c = dict(B=1, H=64, G=4, T=T, dk=192, dv=128, d_model=512, l=32, d=16, l_prime=64, n=16, w=512)
+    inp = O.make_inputs(c["B"], c["H"], c["G"], T, c["dk"], c["dv"], c["d_model"], c["l"], seed=23, block_offset_std=0.5,
+                        l_prime=c["l_prime"], dtype=torch.bfloat16)
+    O.LOW_MEMORY = True
+    try:
+        check_layer_against_oracle(f"layer bf16 H=64 G=4 dk=192 dv=128 T={T}", nsa_mod, c, inp, torch.bfloat16)
+    finally:
+        O.LOW_MEMORY = False
+    assert lib.nsa_device_timeouts(0) == 0
 
 
 def test_module_forward_matches_reference_module(nsa_mod):
@@ -443,8 +428,16 @@ def test_module_forward_matches_reference_module(nsa_mod):
         assert rel_err(info["compression_scores"][:, :, rows], torch.from_numpy(g["mod_p_cmp"])) < 1e-3
         assert rel_err(info["selection_scores"][:, :, rows], torch.from_numpy(g["mod_sel"])) < 1e-3
         assert rel_err(info["gates"][:, rows], torch.from_numpy(g["mod_gates"])) < 1e-3
-        if torch.equal(info["selected_indices"].cpu(), torch.from_numpy(g["mod_indices"]).long()):
-            assert rel_err(y[:, rows], torch.from_numpy(g["mod_y"])) < 1e-3
+        # the module's output row t mixes all heads of position t: compare the positions whose block ids agree in
+        # every group (always, whether or not other rows differ), and require agreement outside near-ties
+        gold_idx = torch.from_numpy(g["mod_indices"]).long()
+        same = (info["selected_indices"].cpu() == gold_idx).all(-1).all(1)            # [B,T]
+        INDEX_LOG.append((f"module small training={training}", same.numel(), -1, int((~same).sum()), -1))
+        assert same.float().mean() > 0.98
+        got, want = y[:, rows].detach().cpu(), torch.from_numpy(g["mod_y"])
+        keep = same[:, rows]
+        assert keep.any()
+        assert ((got - want).abs()[keep].max() / want.abs().max()).item() < 1e-3
     y.sum().backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
     k_cmp, v_cmp, be, nb = model.compress_tokens(torch.randn(1, c["G"], 24 * 4, c["dk"], device=DEV),
@@ -467,23 +460,5 @@ def test_layer_fp32_odd_shapes(nsa_mod, T, dk, dv, H, G, n, w, include_fixed, ga
     """The generic kernels on shapes off every tile size, against the oracle layer (fp32)."""
     c = dict(B=2, H=H, G=G, T=T, dk=dk, dv=dv, d_model=48, l=32, d=16, l_prime=64, n=n, w=w, seed=41)
     inp = O.make_inputs(c["B"], H, G, T, dk, dv, c["d_model"], c["l"], seed=c["seed"], block_offset_std=0.5)
-    from nsa.kernels import nsa_layer
-    cfg = _cfg(nsa_mod, c, gate_mode=gate_mode, include_fixed_in_selection=include_fixed)
-    q, k, v = (_dev(inp[x], torch.float32, True) for x in ("q", "k", "v"))
-    phi, gp = inp["phi"], inp["gate"]
-    params = [_dev(p, grad=True) for p in (phi.pos_embed, phi.w1, phi.b1, phi.w2, phi.b2, gp.w1, gp.b1, gp.w2, gp.b2)]
-    lin = torch.nn.functional.linear
-    logits = lin(torch.relu(lin(_dev(inp["x"]), params[5], params[6])), params[7], params[8])
-    out, info = nsa_layer(q, k, v, logits, tuple(params[:5]), cfg, return_info=True)
-    grads = torch.autograd.grad(out, [q, k, v], _dev(inp["do"]))
-    qo, ko, vo = (inp[x].clone().requires_grad_(True) for x in ("q", "k", "v"))
-    r = O.nsa_layer(qo, ko, vo, inp["x"], phi, gp, l=c["l"], d=c["d"], l_prime=c["l_prime"], n=n, w=w,
-                    include_fixed=include_fixed, gate_mode=gate_mode)
-    gref = torch.autograd.grad(r["out"], [qo, ko, vo], inp["do"])
-    agg = r["sel_scores"].view(c["B"], G, H // G, T, -1).sum(2)
-    mism = (info["indices"].cpu().long() != r["indices"]).any(-1)
-    assert not (mism & ~ambiguous_rows(agg, n)).any(), "selected block ids differ from the oracle"
-    if not mism.any():
-        assert rel_err(out, r["out"]) < 1e-3
-        for nme, a, b in zip(("dq", "dk", "dv"), grads, gref):
-            assert rel_err(a, b) < 1e-3, nme
+    check_layer_against_oracle(f"layer fp32 odd T={T} dk={dk} dv={dv}", nsa_mod, c, inp, torch.float32, gate_mode=gate_mode,
+                               include_fixed=include_fixed)

@@ -23,13 +23,15 @@ def test_library_exports_every_declared_symbol():
 def test_argument_errors_without_a_gpu():
     """Bad arguments are rejected before any CUDA call, with a message."""
     import nsa._lib as L
-    rc = L.lib.nsa_sliding_fwd(None, None, None, None, None, None, None, 1, 3, 2, 8, 8, 8, 4, 1.0, 0, None)
+    rc = L.lib.nsa_sliding_fwd(None, None, None, None, None, None, None, 1, 3, 2, 8, 8, 8, 4, 1.0, 0, 0, None)
     assert rc == -1 and b"H/G" in L.lib.nsa_last_error()
-    rc = L.lib.nsa_sliding_fwd(None, None, None, None, None, None, None, 1, 4, 2, 8, 8, 8, 4, 1.0, 0, None)
+    rc = L.lib.nsa_sliding_fwd(None, None, None, None, None, None, None, 1, 4, 2, 8, 8, 8, 4, 1.0, 0, 0, None)
     assert rc == -1 and b"null" in L.lib.nsa_last_error()
     rc = L.lib.nsa_topn_from_scores(None, None, 1, 4, 2, 8, 8, 2, 100, 0, None)
     assert rc == -1
-    assert L.lib.nsa_slc_bwd_workspace_bytes(1, 64, 4, 65536, 65536, 192, 128, 16, 64, 1) > 4 * 65536 * 16 * 4
+    assert L.lib.nsa_slc_bwd_workspace_bytes(1, 64, 4, 65536, 65536, 192, 128, 16, 64, 1, 0) > 4 * 65536 * 16 * 4
+    # the stride-generic family only needs the inverse index
+    assert L.lib.nsa_slc_bwd_workspace_bytes(1, 64, 4, 65536, 65536, 192, 128, 16, 64, 1, L.FLAG_GENERIC) < (1 << 28)
 
 
 def test_config_defaults_and_validation():
@@ -86,3 +88,30 @@ def test_reference_helpers():
     assert create_block_ends(20, 8, 4, device="cpu").tolist() == [7, 11, 15, 19]
     ok, _ = compare_outputs(torch.ones(3), torch.ones(3))
     assert ok
+
+
+def test_library_keeps_no_call_pairing_state():
+    """Query offset, row sums and dQ addends travel in the argument lists: no setter is exported."""
+    import nsa._lib as L
+    for gone in ("nsa_set_query_offset", "nsa_set_row_delta", "nsa_set_dq_addends", "nsa_set_kernel_family"):
+        assert not hasattr(L.lib, gone), gone
+
+
+def test_launcher_checks_every_tensor_before_launching():
+    """The launcher shims refuse, before any launch, strides that would make a kernel write past a tensor, negative
+    strides, and serve over-reaching read-only tensors from a padded copy."""
+    from nsa.kernels import _Launcher
+    t = torch.zeros(2, 3, 8, 4)
+    assert _Launcher._extent("t", t.stride(), t.shape) == t.numel()
+    assert _Launcher._fits("t", t, t.stride(), t.shape) is t
+    with pytest.raises(ValueError, match="storage holds"):
+        _Launcher._fits("dK", t, (192, 64, 8, 1), (2, 3, 8, 8))         # strides of a tensor twice as wide
+    with pytest.raises(ValueError, match="negative"):
+        _Launcher._fits("Out", t, (96, 32, -4, 1), t.shape)
+    wide = _Launcher._safe("K", t, (192, 64, 8, 1), (2, 3, 8, 8))       # read-only: padded copy, original values first
+    assert wide.numel() >= _Launcher._extent("K", (192, 64, 8, 1), (2, 3, 8, 8)) and wide is not t
+    assert _Launcher._fits("K^T", t, (96, 32, 1, 4), (2, 3, 4, 8)) is t   # a transposed view stays inside the storage
+    assert _Launcher._safe("K", t, t.stride(), t.shape) is t
+    view = t[:, :, 2:]                                                   # storage offset counts against the room left
+    with pytest.raises(ValueError):
+        _Launcher._fits("dQ", view, t.stride(), t.shape)

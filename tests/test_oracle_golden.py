@@ -124,3 +124,31 @@ def test_eq9_stencil():
     w = torch.tensor([1., 2., 2., 2., 1.])
     for j in range(8):
         assert torch.allclose(sel[..., j], (pp[..., 4 * j:4 * j + 5] * w).sum(-1), rtol=1e-6, atol=1e-7)
+
+
+def test_row_functions_agree_with_the_dense_oracle():
+    """The sampled-row forms (used where a sequence is too long for the dense functions) against the dense, golden-pinned
+    ones on the rows they share."""
+    c = dict(B=2, H=8, G=2, T=700, dk=32, dv=48, l=32, d=16, lp=64, n=6, w=100)
+    inp = O.make_inputs(c["B"], c["H"], c["G"], c["T"], c["dk"], c["dv"], 32, c["l"], seed=5, block_offset_std=0.5)
+    scale = c["dk"] ** -0.5
+    r = O.nsa_layer(inp["q"], inp["k"], inp["v"], inp["x"], inp["phi"], inp["gate"], l=c["l"], d=c["d"], l_prime=c["lp"],
+                    n=c["n"], w=c["w"])
+    pos = torch.tensor([0, 5, 30, 31, 32, 63, 64, 99, 100, 101, 383, 384, 385, 500, 699])
+    qr = inp["q"][:, :, pos]
+    idx, agg = O.score_rows(qr, pos, r["k_cmp"], r["block_ends"], l=c["l"], d=c["d"], l_prime=c["lp"], n=c["n"], scale=scale)
+    assert torch.equal(idx, r["indices"][:, :, pos])
+    full_agg = r["sel_scores"].view(c["B"], c["G"], c["H"] // c["G"], c["T"], -1).sum(2)[:, :, pos]
+    assert torch.allclose(agg, full_agg, rtol=1e-5, atol=1e-7)
+    o_cmp, o_slc, o_win = O.branch_rows(qr, pos, inp["k"], inp["v"], r["k_cmp"], r["v_cmp"], r["block_ends"], idx, w=c["w"],
+                                        l_prime=c["lp"], scale=scale)
+    for got, name in ((o_cmp, "o_cmp"), (o_slc, "o_slc"), (o_win, "o_win")):
+        want = r[name][:, :, pos]
+        assert (got - want).abs().max().item() <= 2e-5 * max(1.0, want.abs().max().item()), name
+    # forced ids replace the layer's own choice and nothing else
+    forced = r["indices"].clone()
+    forced[:, :, 200:, 3:] = -1
+    r2 = O.nsa_layer(inp["q"], inp["k"], inp["v"], inp["x"], inp["phi"], inp["gate"], l=c["l"], d=c["d"], l_prime=c["lp"],
+                     n=c["n"], w=c["w"], indices=forced)
+    assert torch.equal(r2["indices_own"], r["indices"]) and torch.equal(r2["o_cmp"], r["o_cmp"])
+    assert torch.equal(r2["o_slc"][:, :, :200], r["o_slc"][:, :, :200]) and not torch.equal(r2["o_slc"], r["o_slc"])
