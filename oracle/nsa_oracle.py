@@ -378,6 +378,33 @@ def nsa_layer(q, k, v, x, phi: PhiParams, gp: GateParams, *, l=32, d=16, l_prime
 
 
 # ----------------------------------------------------------------------------------------------
+# what "bit-exact block ids" can mean between independent implementations
+# ----------------------------------------------------------------------------------------------
+
+def ambiguous_rows(sel_scores_grouped: torch.Tensor, n: int, tau: float = 1e-5) -> torch.Tensor:
+    """Rows [B,G,T] whose top-(n+1) aggregated scores hold an adjacent pair closer than tau (relative): there the
+    ranking depends on fp32 rounding order (the reference's own fp32 and fp64 runs disagree on such rows), so no
+    independent implementation can be expected to agree bit for bit.  Exact ties are decided by block id
+    (nsa/kernels.py:1986-1990, stable sort) and are not ambiguous."""
+    k = min(n + 1, sel_scores_grouped.shape[-1])
+    top = torch.sort(sel_scores_grouped.double(), dim=-1, descending=True).values[..., :k]
+    gap = (top[..., :-1] - top[..., 1:]) / top[..., :-1].abs().clamp_min(1e-30)
+    both_zero = (top[..., :-1] == 0) & (top[..., 1:] == 0)
+    return ((gap < tau) & ~both_zero).any(dim=-1)
+
+
+def sample_positions(T: int, count: int, l: int = 32, w: int = 512, l_prime: int = 64, n: int = 16, seed: int = 0) -> torch.Tensor:
+    """`count` query positions of [0,T): the boundary rows of every branch (first rows, around the first compressed
+    block, the window edge, the point where the selection blocks run out, the last row) plus seeded random ones;
+    sorted, unique."""
+    must = [0, l - 2, l - 1, l, w - 1, w, n * l_prime - 1, n * l_prime, n * l_prime + 1, T - 1]
+    must = [t for t in must if 0 <= t < T]
+    g = torch.Generator().manual_seed(seed)
+    rnd = torch.randint(0, T, (max(0, count - len(must)),), generator=g).tolist()
+    return torch.tensor(sorted(set(must + rnd)), dtype=torch.int64)
+
+
+# ----------------------------------------------------------------------------------------------
 # seeded inputs shared by tests, fixtures and the benchmark
 # ----------------------------------------------------------------------------------------------
 

@@ -284,10 +284,12 @@ def test_score_topn_tensorcore_bit_exact_outside_ambiguity(dk, H, G, T):
     INDEX_LOG.append((f"score_topn generic     dk={dk} H={H} G={G} T={T}", amb.numel(), int(amb.sum()), int((gen != ref).any(-1).sum()), int(bad_gen.sum())))
     assert not bad_gen.any(), f"generic kernel: {int(bad_gen.sum())} unambiguous rows differ"
     assert not bad_tc.any(), f"tensor-core kernel: {int(bad_tc.sum())} unambiguous rows differ, first {bad_tc.nonzero()[:3].tolist()}"
-    # the ambiguity set is a property of the data (near-uniform scores); what must stay small is the number
-    # of rows that actually differ, inside the set included
-    assert amb.float().mean() < 0.5
-    assert (tc != ref).any(-1).float().mean() < 0.01 and (gen != ref).any(-1).float().mean() < 0.01
+    # the ambiguity set is a property of the data (phi weights N(0,0.02) make the softmax over thousands of compressed
+    # blocks nearly uniform: 14 % of the rows at T=2048, 19 % at 4096, 39 % at 32768 and 43 % at 65536 hold a pair of
+    # adjacent top scores within 1e-5 relative); what must stay small is the number of rows that actually differ,
+    # inside the set included (measured: at most 0.21 %)
+    assert amb.float().mean() < 0.46
+    assert (tc != ref).any(-1).float().mean() < 0.004 and (gen != ref).any(-1).float().mean() < 0.004
     # early rows: forced blocks first, never-visible blocks listed in id order, -1 padding only when blocks run out
     assert tc[0, 0, 0].tolist()[:3] == [0, 1, 2] and (tc >= -1).all() and (tc < (T + lp - 1) // lp).all()
 

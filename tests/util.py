@@ -44,15 +44,7 @@ def close(where, name, got, ref, *, bf16, grad=False, rows=None, bound=None):
     assert err < tol, f"{where}: {name} max-abs {err:.4g} exceeds {tol:.4g} (largest reference magnitude {ref_max:.4g})"
 
 
-def ambiguous_rows(sel_scores_grouped, n, tau=1e-5):
-    """Rows [B,G,T] whose top-(n+1) aggregated scores hold an adjacent pair closer than tau (relative):
-    there the ranking depends on fp32 rounding order and no independent implementation can be
-    expected to agree bit for bit."""
-    k = min(n + 1, sel_scores_grouped.shape[-1])
-    top = torch.sort(sel_scores_grouped.double(), dim=-1, descending=True).values[..., :k]
-    gap = (top[..., :-1] - top[..., 1:]) / top[..., :-1].abs().clamp_min(1e-30)
-    both_zero = (top[..., :-1] == 0) & (top[..., 1:] == 0)      # exact ties are decided by index: not ambiguous
-    return ((gap < tau) & ~both_zero).any(dim=-1)
+ambiguous_rows = O.ambiguous_rows
 
 
 def index_agreement(where, idx_gpu, idx_ref, agg_scores, n, extra_ambiguous=None):
@@ -140,9 +132,10 @@ def check_layer_against_oracle(where, nsa_mod, c, inp, dtype, *, gate_mode="sigm
             close(where, name + "[oracle ids]", a, b, bf16=bf16, grad=True)
         elif name == "db2":
             # a constant added to every compressed key leaves the softmax unchanged: the true gradient is zero and
-            # both sides hold rounding noise; compared on the scale of the weight gradient next to it
+            # both sides hold rounding noise (with bf16 I/O: the sum over all blocks of the bf16 roundings of dK_cmp,
+            # which no weight scales down); compared on the scale of the weight gradient next to it
             err = max_abs(a, b)
-            tol = (3e-2 if bf16 else 1e-3) * ref["dw2"].abs().max().item()
+            tol = (0.25 if bf16 else 1e-3) * ref["dw2"].abs().max().item() + 1e-12      # dw2 = 0 when no block is ever visible
             PARITY_LOG.append((where, "db2 (on the scale of dw2)", err, ref["dw2"].abs().max().item(), tol))
             assert err < tol, f"{where}: db2 {err} vs {tol}"
         else:
@@ -154,13 +147,4 @@ def check_layer_against_oracle(where, nsa_mod, c, inp, dtype, *, gate_mode="sigm
     return info, mism, r
 
 
-# sampled rows of a long sequence ------------------------------------------------------------------------
-
-def sample_positions(T, count, l=32, w=512, l_prime=64, n=16, seed=0):
-    """`count` query positions of [0,T): the boundary rows of every branch (first rows, around the first compressed
-    block, the window edge, the point where the selection blocks run out) plus seeded random ones; sorted, unique."""
-    must = [0, l - 2, l - 1, l, w - 1, w, n * l_prime - 1, n * l_prime, n * l_prime + 1, T - 1]
-    must = [t for t in must if 0 <= t < T]
-    g = torch.Generator().manual_seed(seed)
-    rnd = torch.randint(0, T, (max(0, count - len(must)),), generator=g).tolist()
-    return torch.tensor(sorted(set(must + rnd)), dtype=torch.int64)
+sample_positions = O.sample_positions
