@@ -168,6 +168,58 @@ def layer_step_query_sharded(inp, params, cfg, world, before_backward=None):
     return out[0, 0, -1, :8].float().sum() + grads[0][0, 0, -1, :8].float().sum()
 
 
+def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
+    """Long-context mode inside a multi-GPU run: ONE sequence of T tokens split by position over the ranks (K/V and
+    the compressed K/V all-gathered, their gradients reduce-scattered), 5 warm-up + 10 timed steps, device-timed, max
+    over ranks.  `headline_ms`: this run's time for one whole T=65536 sequence on one GPU (the weak-scaling step), the
+    one-GPU reference of the speed-up at that length."""
+    import torch.distributed as dist
+    from nsa import sharding
+    c = CFG
+    inp, params = make_device_inputs(T, dev, seed=0)            # the same sequence on every rank; each keeps its slice
+    bounds = sharding.balanced_query_bounds(T, world, c["w"] + c["n"] * c["l_prime"], c["d"])
+    t0, t1 = bounds[rank], bounds[rank + 1]
+    inp = dict(q=inp["q"][:, :, t0:t1].contiguous(), k=inp["k"][..., t0:t1].contiguous(), v=inp["v"][:, :, t0:t1].contiguous(),
+               do=inp["do"][:, :, t0:t1].contiguous(), x=inp["x"][:, t0:t1].contiguous(), bounds=bounds)
+    torch.cuda.empty_cache()
+    for _ in range(5):
+        layer_step_query_sharded(inp, params, cfg, world)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = 10
+    e0.record()
+    for _ in range(steps):
+        layer_step_query_sharded(inp, params, cfg, world)
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t_ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    # the exchange steps alone (same tensors, same collectives as inside the layer), device-timed, max over ranks
+    sizes = [bounds[i + 1] - bounds[i] for i in range(world)]
+    kk, vv = inp["k"].detach().requires_grad_(True), inp["v"].detach().requires_grad_(True)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    for rep in range(3):
+        kk.grad = vv.grad = None
+        ev[0].record()
+        kf, vf = sharding.all_gather_seq(kk, -1, None, sizes), sharding.all_gather_seq(vv, 2, None, sizes)
+        ev[1].record()
+        torch.autograd.backward([kf, vf], [torch.ones_like(kf), torch.ones_like(vf)])
+        ev[2].record()
+    torch.cuda.synchronize()
+    coll = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], device=dev)
+    dist.all_reduce(coll, op=dist.ReduceOp.MAX)
+    ms = t_ms.item()
+    kv_bytes = c["G"] * T * (c["dk"] + c["dv"]) * 2
+    return dict(T=T, n_gpus=world, steps=steps, warmup=5, ms_per_step=round(ms, 3), tokens_per_s=round(T / (ms * 1e-3), 1),
+                speedup_vs_n1=round(headline_ms / ms, 3) if T == args.T else None,
+                n1_reference="this run's one-GPU step for a whole sequence of the same length" if T == args.T else None,
+                allgather_ms=round(coll[0].item(), 3), reduce_scatter_ms=round(coll[1].item(), 3),
+                allgather_bytes=kv_bytes, reduce_scatter_bytes=2 * kv_bytes,
+                slices=[bounds[i + 1] - bounds[i] for i in range(world)])
+
+
 def attention_flops(T):
     """Algorithmic attention FLOPs per sequence (masked-out keys do not count): forward 2(dk+dv)N,
     backward 2(3dk+2dv)N per (head, query) with N valid keys; selection counted at n full blocks minus
@@ -195,6 +247,7 @@ def kernel_flops(T):
         f[f"fa_fwd_{br}"] = unit[br] * 2 * (dk + dv)
         f[f"fa_bwd_dq_{br}"] = unit[br] * 2 * (2 * dk + dv)             # S, dP, dQ
         f[f"fa_bwd_dkv_{br}"] = unit[br] * 2 * (2 * dk + 2 * dv)        # S^T, dP^T, dV, dK
+        f[f"fa_bwd_dqds_{br}"] = unit[br] * 2 * dk                      # dQ from the dS^T tiles the dK/dV kernel left
     f["slc_fwd"] = unit["slc"] * 2 * (dk + dv)
     f["slc_bwd_fused"] = unit["slc"] * 2 * (3 * dk + 2 * dv)           # S, dP, dQ, dV, dK
     return f
@@ -324,6 +377,8 @@ def main():
     ap.add_argument("--T", type=int, default=65536)
     ap.add_argument("--cpu-sample", type=int, default=4096, help="sequence length of the CPU-oracle sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-long-context", action="store_true",
+                    help="multi-GPU runs: skip the extra leg that times ONE sequence split by position over the GPUs")
     ap.add_argument("--no-parity", action="store_true", help="skip the sampled-row check of the workload against the oracle")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end leg (default: max(20, --steps))")
     ap.add_argument("--shard", default="sequence", choices=["sequence", "query"],
@@ -443,6 +498,17 @@ def main():
         torch.distributed.all_reduce(t_e2e, op=torch.distributed.ReduceOp.MAX)
     e2e_value = seqs * T / (t_e2e.item() / e2e_steps * 1e-3)
 
+    # ---- long-context mode (one sequence split by position), recorded with every multi-GPU run --
+    long_context = None
+    if world > 1 and not query_mode and not args.no_long_context:
+        del inp, host, slots            # the weak-scaling inputs make room; rebuilt below for the profiled step
+        torch.cuda.empty_cache()
+        long_context = [long_context_leg(args, cfg, dev, world, rank, T, ms_per_step)]
+        if world >= 8:
+            long_context.append(long_context_leg(args, cfg, dev, world, rank, 2 * T, ms_per_step))
+        torch.cuda.empty_cache()
+        inp, _ = make_device_inputs(T, dev, seed=rank)
+
     # ---- per-kernel times (CUDA events around every launch, outside the timed region) -----------
     prof = _lib.profile_kernels(lambda: step_fn(inp, params, cfg, world))
     launches = sum(n_ for n_, _ in prof.values())
@@ -495,7 +561,8 @@ def main():
                     gpu_launches=launches * args.steps, roofline=roofline, cpu_baseline=cpu, clocks=clocks,
                     attention_tflops_per_s=round(att_total / (ms_per_step * 1e-3) / 1e12, 1),
                     attention_frac_of_peak=round(att_total / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"] / (world if query_mode else 1), 4),
-                    kernel_ms=breakdown, kernel_ms_total=round(kern_ms, 3), device_timeouts=timeouts, parity=parity)
+                    kernel_ms=breakdown, kernel_ms_total=round(kern_ms, 3), device_timeouts=timeouts, parity=parity,
+                    long_context=long_context)
         print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -48,7 +48,7 @@ enum {
 /* `flags` argument of the attention and scoring entry points (testing / cross-checks): by default a call runs the
  * tensor-core (tcgen05) kernels when it qualifies (bf16, canonical contiguous layouts, supported head dims, T a
  * multiple of 128) and the stride-generic kernels otherwise; NSA_FLAG_GENERIC forces the stride-generic kernels. */
-enum { NSA_FLAG_GENERIC = 1 };
+enum { NSA_FLAG_GENERIC = 1, NSA_FLAG_RECOMPUTE = 2 };
 
 /* `q_pos0` argument (query-sharded long-context runs and incremental decoding; the reference has no counterpart, its
  * wrappers assume query row t sits at position t): position of query row 0 in the sequence.  The keys keep starting
@@ -101,10 +101,15 @@ NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void* v, void* o
                     const int64_t* strides22, int B, int H, int G, int T, int dk, int dv, int window,
                     float scale, int dtype, int flags, void* stream);
 /* The backward entry points of the sliding and compression branches take scratch memory of
- * nsa_attn_bwd_workspace_bytes() bytes (used by the tensor-core kernels: per-row statistics and, for
- * the compression branch, per-head-chunk partial dK/dV sums that are then added in a fixed order). */
+ * nsa_attn_bwd_workspace_bytes() bytes, used by the tensor-core kernels: per-row statistics, for the compression
+ * branch per-head-chunk partial dK/dV sums that are then added in a fixed order, and the dS^T tiles (bf16, one
+ * 16 KiB tile per visible (key tile, 64-query sub-tile, head)) that the key-stationary dK/dV kernel leaves for the
+ * dQ kernel, so that S and dP are computed once per backward step.  With flags = NSA_FLAG_RECOMPUTE the query
+ * returns the small scratch only; a backward call given that much recomputes S and dP in its dQ kernel instead
+ * (same results up to the rounding of dS, several times less scratch, more time).  `window` is the sliding
+ * window (ignored for the compression branch). */
 NSA_API size_t nsa_attn_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv,
-                                            int is_compression);
+                                            int is_compression, int window, int flags);
 NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                     const float* L, const float* M, void* dq, void* dkey, void* dval,
                     const int64_t* strides34, int B, int H, int G, int T, int dk, int dv, int window,
@@ -165,6 +170,19 @@ NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, const int32
                 float* L, float* M, const int64_t* strides26, int B, int H, int G, int Tq, int Tkv,
                 int n_slots, int l_prime, int dk, int dv, float scale, int dtype, int q_pos0, int flags,
                 void* workspace, size_t workspace_bytes, void* stream);
+/* The same forward with the gate + mix of the layer (nsa/kernels.py:2446-2463) as its epilogue: the selection branch
+ * runs last, and the kernel that merges a query's per-slot partials, holding the finished O_slc row, also writes
+ * out_mixed = g0*o_cmp + g1*O_slc + g2*o_win and the gates (gates_out [B,H,Tq,3] fp32; gate_logits [B,Tq,3H] fp32;
+ * o_cmp, o_win contiguous [B,H,Tq,dv] in dtype).  out_mixed is head-major [B,H,Tq,dv], or with
+ * out_token_major != 0 token-major [B,Tq,H,dv], which the output projection reads without a transposing copy
+ * (the reference copies: nsa/kernels.py:2466-2467).  `out` still receives O_slc (the backward needs it).  Calls
+ * that run on the stride-generic kernels do the mix as a separate pass inside this entry point. */
+NSA_API int nsa_slc_fwd_mix(const void* q, const void* k, const void* v, const int32_t* indices, void* out,
+                    float* L, float* M, const int64_t* strides26, int B, int H, int G, int Tq, int Tkv,
+                    int n_slots, int l_prime, int dk, int dv, float scale, int dtype, int q_pos0, int flags,
+                    const float* gate_logits, const void* o_cmp, const void* o_win, void* out_mixed,
+                    float* gates_out, int gate_mode, int out_token_major, void* workspace,
+                    size_t workspace_bytes, void* stream);
 /* Backward; dK/dV are reduced per key block over the queries that selected it in a fixed order (an
  * inverse index "block -> queries" is built in the workspace; the tensor-core path also keeps per-
  * (query, slot) dQ partials and per-block dK/dV partials there), so results are run-to-run identical. */
@@ -226,21 +244,25 @@ NSA_API int nsa_eq9_scores(const float* p_cmp, float* out, int64_t rows, int n_c
                            int l_prime, void* stream);
 
 /* Gate + mix (nsa/kernels.py:2446-2463): gates = sigmoid | softmax-over-3 of logits[b,t,3h+i],
- * out = g0*o_cmp + g1*o_slc + g2*o_win.  logits [B,T,3H] fp32, branch outputs and out [B,H,T,dv]
- * contiguous in dtype, gates_out [B,H,T,3] fp32 (saved for backward / diagnostics). */
+ * out = g0*o_cmp + g1*o_slc + g2*o_win.  logits [B,T,3H] fp32, branch outputs [B,H,T,dv] contiguous in dtype,
+ * gates_out [B,H,T,3] fp32 (saved for backward / diagnostics).  out is head-major [B,H,T,dv] or, with
+ * out_token_major != 0, token-major [B,T,H,dv] (what the output projection consumes without a copy). */
 NSA_API int nsa_gate_mix_fwd(const float* logits, const void* o_cmp, const void* o_slc, const void* o_win,
                      void* out, float* gates_out, int B, int H, int T, int dv, int gate_mode,
-                     int dtype, void* stream);
-/* Backward: d_branch_i = g_i * dout (three tensors in dtype), dlogits [B,T,3H] fp32. */
+                     int dtype, int out_token_major, void* stream);
+/* Backward: d_branch_i = g_i * dout (three tensors in dtype, head-major), dlogits [B,T,3H] fp32; dout is head-major
+ * or (dout_token_major != 0) token-major like the forward's out. */
 NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
                      const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits,
-                     int B, int H, int T, int dv, int gate_mode, int dtype, void* stream);
+                     int B, int H, int T, int dv, int gate_mode, int dtype, int dout_token_major,
+                     void* stream);
 
 /* Same, and also writes delta [3][B*H*T] (fp32): the row sums dO_b . O_b of the three branches (dO_b = g_b dO), which
  * the branch backward kernels need.  Handing them over as `row_delta` saves each backward its own pass over O and dO. */
 NSA_API int nsa_gate_mix_bwd_delta(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
                                    const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits,
-                                   float* delta, int B, int H, int T, int dv, int gate_mode, int dtype, void* stream);
+                                   float* delta, int B, int H, int T, int dv, int gate_mode, int dtype,
+                                   int dout_token_major, void* stream);
 
 #ifdef __cplusplus
 }

@@ -183,9 +183,12 @@ extern "C" NSA_API int nsa_selftest_wait_timeout(long long limit_clocks, void* s
   return NSA_OK;
 }
 
-extern "C" NSA_API size_t nsa_attn_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int is_compression) {
+extern "C" NSA_API size_t nsa_attn_bwd_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int is_compression,
+                                                       int window, int flags) {
   if (B <= 0 || H <= 0 || G <= 0 || Tq <= 0 || Tk <= 0 || H % G != 0) return 256;
-  return fa_bwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, is_compression ? kCmp : kWin);
+  if (!is_compression && window <= 0) return 256;
+  return fa_bwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, is_compression ? kCmp : kWin, is_compression ? 0 : window,
+                                      (flags & NSA_FLAG_RECOMPUTE) != 0);
 }
 
 extern "C" NSA_API int nsa_device_timeouts(int reset) {
@@ -285,27 +288,60 @@ extern "C" NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const 
   return launch_attn_generic(a, kCmp, dtype, true, (cudaStream_t)stream);
 }
 
-extern "C" NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, const int32_t* indices, void* out, float* L,
-                           float* M, const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots,
-                           int l_prime, int dk, int dv, float scale, int dtype, int q_pos0, int flags, void* workspace,
-                           size_t workspace_bytes, void* stream) {
-  if (int rc = check_common("slc_fwd", B, H, G, Tq, Tkv, dk, dv, dtype)) return rc;
-  NSA_REQUIRE(q && k && v && indices && out && strides, "slc_fwd: null pointer");
-  NSA_REQUIRE(l_prime > 0 && n_slots >= 0, "slc_fwd: bad block size / slot count");
-  NSA_REQUIRE(q_pos0 >= 0, "slc_fwd: negative query offset");
-  NSA_REFUSE_AFTER_TIMEOUT("slc_fwd");
+static int slc_fwd_impl(const char* who, const void* q, const void* k, const void* v, const int32_t* indices, void* out, float* L,
+                        float* M, const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots, int l_prime, int dk,
+                        int dv, float scale, int dtype, int q_pos0, int flags, const SlcMix& mix, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  if (int rc = check_common(who, B, H, G, Tq, Tkv, dk, dv, dtype)) return rc;
+  NSA_REQUIRE(q && k && v && indices && out && strides, "%s: null pointer", who);
+  NSA_REQUIRE(l_prime > 0 && n_slots >= 0, "%s: bad block size / slot count", who);
+  NSA_REQUIRE(q_pos0 >= 0, "%s: negative query offset", who);
+  if (timeout_flagged())
+    return fail(NSA_ERR_LAUNCH, "%s: a tensor-core kernel gave up on a barrier wait earlier (device time-out); results since "
+                "then are invalid.  nsa_device_timeouts(1) reports and clears the condition", who);
   if (want_tc(flags) && dtype == NSA_BF16 && L && M && B > 0 && slc_sm100_supported(H, G, Tq, Tkv, dk, dv, n_slots, l_prime) &&
-      canonical_fwd(strides, H, G, Tq, Tkv, dk, dv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out))
+      canonical_fwd(strides, H, G, Tq, Tkv, dk, dv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
+      (!mix.out || (aligned16(mix.out) && aligned16(mix.o_cmp) && aligned16(mix.o_win))))
     return slc_fwd_sm100(q, k, v, indices, strides + 22, out, L, M, B, H, G, Tq, Tkv, dk, dv, n_slots, l_prime, scale,
-                         q_pos0, workspace, workspace_bytes, (cudaStream_t)stream);
-  NSA_NO_QUERY_OFFSET("slc_fwd");
+                         q_pos0, mix, workspace, workspace_bytes, (cudaStream_t)stream);
+  NSA_REQUIRE(q_pos0 == 0, "%s: a query offset needs the bf16 tensor-core path of this call", who);
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o = out; a.L = L; a.M = M; a.indices = indices;
   fill_fwd_strides(a, strides);
   for (int i = 0; i < 4; ++i) a.sidx[i] = strides[22 + i];
   a.B = B; a.H = H; a.G = G; a.Tq = Tq; a.Tk = Tkv; a.dk = dk; a.dv = dv; a.scale = scale; a.causal = 1;
   a.nslots = n_slots; a.lprime = l_prime; a.nblk = (Tkv + l_prime - 1) / l_prime;
-  return launch_attn_generic(a, kSlc, dtype, false, (cudaStream_t)stream);
+  if (int rc = launch_attn_generic(a, kSlc, dtype, false, (cudaStream_t)stream)) return rc;
+  if (!mix.out) return NSA_OK;
+  // stride-generic kernels: the mix runs as its own pass over the three branch outputs (contiguous [B,H,Tq,dv])
+  NSA_REQUIRE(strides[15] == 1 && strides[14] == dv && strides[13] == (int64_t)Tq * dv && strides[12] == (int64_t)H * Tq * dv,
+              "%s: the gate/mix epilogue needs a contiguous [B,H,T,dv] selection output", who);
+  return nsa_gate_mix_fwd(mix.logits, mix.o_cmp, out, mix.o_win, mix.out, mix.gates, B, H, Tq, dv, mix.mode, dtype,
+                          mix.token_major, stream);
+}
+
+extern "C" NSA_API int nsa_slc_fwd(const void* q, const void* k, const void* v, const int32_t* indices, void* out, float* L,
+                           float* M, const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots,
+                           int l_prime, int dk, int dv, float scale, int dtype, int q_pos0, int flags, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  const SlcMix none = {};
+  return slc_fwd_impl("slc_fwd", q, k, v, indices, out, L, M, strides, B, H, G, Tq, Tkv, n_slots, l_prime, dk, dv, scale, dtype,
+                      q_pos0, flags, none, workspace, workspace_bytes, stream);
+}
+
+extern "C" NSA_API int nsa_slc_fwd_mix(const void* q, const void* k, const void* v, const int32_t* indices, void* out, float* L,
+                               float* M, const int64_t* strides, int B, int H, int G, int Tq, int Tkv, int n_slots,
+                               int l_prime, int dk, int dv, float scale, int dtype, int q_pos0, int flags,
+                               const float* gate_logits, const void* o_cmp, const void* o_win, void* out_mixed,
+                               float* gates_out, int gate_mode, int out_token_major, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  NSA_REQUIRE(gate_logits && o_cmp && o_win && out_mixed && gates_out, "slc_fwd_mix: null pointer");
+  NSA_REQUIRE(gate_mode == NSA_GATE_SIGMOID || gate_mode == NSA_GATE_SOFTMAX, "slc_fwd_mix: bad gate mode %d", gate_mode);
+  SlcMix mix = {};
+  mix.logits = gate_logits; mix.o_cmp = o_cmp; mix.o_win = o_win; mix.out = out_mixed; mix.gates = gates_out;
+  mix.mode = gate_mode; mix.token_major = out_token_major ? 1 : 0;
+  return slc_fwd_impl("slc_fwd_mix", q, k, v, indices, out, L, M, strides, B, H, G, Tq, Tkv, n_slots, l_prime, dk, dv, scale,
+                      dtype, q_pos0, flags, mix, workspace, workspace_bytes, stream);
 }
 
 extern "C" NSA_API size_t nsa_slc_fwd_workspace_bytes(int B, int H, int G, int Tq, int Tkv, int dk, int dv, int n_slots,

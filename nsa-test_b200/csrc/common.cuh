@@ -52,6 +52,25 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
+// gates of one (batch, head, token): sigmoid of the three logits, or their softmax (nsa/kernels.py:2446-2451)
+__device__ __forceinline__ void gates3(const float* lg, int mode, float g[3]) {
+  if (mode == NSA_GATE_SOFTMAX) {
+    const float m = fmaxf(lg[0], fmaxf(lg[1], lg[2]));
+    const float e0 = expf(lg[0] - m), e1 = expf(lg[1] - m), e2 = expf(lg[2] - m);
+    const float inv = 1.f / (e0 + e1 + e2);
+    g[0] = e0 * inv; g[1] = e1 * inv; g[2] = e2 * inv;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 3; ++i) g[i] = 1.f / (1.f + expf(-lg[i]));
+  }
+}
+
+// Row index of (b,h,t) in the mixed output (and in its gradient): head-major [B,H,T,dv] like the branch outputs, or
+// token-major [B,T,H,dv], the layout the output projection consumes without a transposing copy.
+__device__ __forceinline__ int64_t mixed_row(int64_t row, int b, int h, int t, int H, int T_, int token_major) {
+  return token_major ? ((int64_t)b * T_ + t) * H + h : row;
+}
+
 constexpr int kMaxHeadDim = 256;  // generic kernels keep head_dim/32 accumulators per lane
 
 }  // namespace nsa

@@ -49,7 +49,41 @@ struct FaBwdParams {
   int hsplit;
   float scale, scale_log2;
   int* timeouts;
+  // dS^T tiles handed from the dK/dV kernel to the dQ kernel (null: the dQ kernel recomputes S and dP itself):
+  // [B*H][Tk/128 key tiles][ds_per_j sub-tile slots][128 keys][64 queries] bf16, one 16 KiB tile per (key tile, 64-query sub-tile)
+  __nv_bfloat16* ds;
+  int ds_per_j;
 };
+
+// Which 64-query sub-tiles meet key tile j (keys [128 j, 128 j + 128)).  The range is widened to whole 128-query tiles
+// (first sub-tile even, last odd; Tq is a multiple of 128), so that the dQ kernel, which works on 128-query tiles, finds
+// either both halves of a tile written or neither.  Shared by the dK/dV kernel (writer of the dS^T tiles) and the dQ
+// kernel (reader): both must agree on the set of tiles.
+template <int MODE>
+__host__ __device__ __forceinline__ void subtile_range(int j, int Tq, int window, int cmp_l, int cmp_d, int cmp_nb, int* qs_lo,
+                                                       int* qs_hi) {
+  const int n0 = j * 128;
+  if (MODE == kWin) {
+    *qs_lo = n0 / 64;
+    const int last = n0 + 126 + window;
+    *qs_hi = ((last < Tq - 1 ? last : Tq - 1) / 64) | 1;
+  } else {
+    const int64_t tfirst = (int64_t)n0 * cmp_d + cmp_l - 1;
+    if (n0 < cmp_nb && tfirst < Tq) {
+      *qs_lo = (int)((tfirst > 0 ? tfirst : 0) / 64) & ~1;   // tfirst < 0: visible from the first row on
+      *qs_hi = (Tq - 1) / 64;
+    } else {
+      *qs_lo = 1;
+      *qs_hi = 0;
+    }
+  }
+}
+// slot of sub-tile qs in key tile j's row of the dS^T scratch: the window branch stores only the sub-tiles near the
+// diagonal (slot = distance from the first one), the compressed branch all of them
+template <int MODE>
+__host__ __device__ __forceinline__ int ds_slot(int j, int qs) { return MODE == kWin ? qs - 2 * j : qs; }
+static int ds_slots_per_key_tile(int mode, int Tq, int window) { return mode == kWin ? (((126 + window) / 64) | 1) + 1 : Tq / 64; }
+
 
 // ------------------------------------------------------------------------------------------------
 // prep: one warp per (b,h,t)
@@ -393,6 +427,210 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------
+// dQ from stored dS^T: dQ[128 queries x DK] = sum over key tiles of dS[queries x keys] K[keys x DK].
+// The dK/dV kernel has left dS^T (bf16) in scratch memory as [128 keys][64 queries] tiles; here they are the A operand
+// straight from shared memory (MN-major: queries contiguous), K tiles the B operand (keys contiguous), so S and dP are
+// computed once per step of the backward instead of once per kernel.  HBM-bound: 32 KiB of dS^T per 6.3 MFLOP.
+// 192 threads: warps 0-3 read the accumulator out (one query row per thread), warp 4 TMA, warp 5 UMMA.
+// Persistent grid over (query tile, batch, head) items, late (long) query tiles first; two accumulators in TMEM, so the
+// MMAs of an item run under the epilogue of the one before; dS^T tiles in a ring of four stages, K tiles in a ring of two.
+// ------------------------------------------------------------------------------------------------
+template <int DK>
+struct DqDsSmem {
+  static constexpr int kDs = 2 * 128 * 64 * 2, kK = 128 * DK * 2;
+  static constexpr int kDsStages = 4, kKStages = 2;
+  static constexpr int oDs = 0, oK = oDs + kDsStages * kDs, oBar = oK + kKStages * kK;
+  static constexpr int kDynamic = oBar + 256 + 1024;
+};
+struct DqDsBarriers {
+  uint64_t ds_full[4], ds_empty[4], k_full[2], k_empty[2], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int DK, int MODE>
+__global__ void __launch_bounds__(192, 1)
+fa_bwd_dq_ds_kernel(const __grid_constant__ CUtensorMap tmDs, const __grid_constant__ CUtensorMap tmK, const FaBwdParams p) {
+  using SM = DqDsSmem<DK>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t *sDs = smem + SM::oDs, *sK = smem + SM::oK;
+  DqDsBarriers* bar = reinterpret_cast<DqDsBarriers*>(smem + SM::oBar);
+  volatile int* abort = &bar->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_qt = p.B * p.H, nqt = p.Tq / 128, nitems = nqt * per_qt, nkt = p.Tk / 128;
+  const bool poisoned = p.timeouts && *(volatile const int*)p.timeouts != 0;
+  struct Item { int qt, b, h, g, jlo, ntiles; };
+  // key tiles whose widened sub-tile range holds query tile qt: a contiguous run of j ending at jhi
+  auto tile_visible = [&](int j, int qt) {
+    int lo, hi;
+    subtile_range<MODE>(j, p.Tq, p.window, p.cmp_l, p.cmp_d, p.cmp_nb, &lo, &hi);
+    return lo <= 2 * qt && 2 * qt + 1 <= hi;
+  };
+  auto item_at = [&](int it) {
+    Item w;
+    const int y = it % per_qt;
+    w.qt = nqt - 1 - it / per_qt;
+    w.b = y / p.H;
+    w.h = y % p.H;
+    w.g = w.h / (p.H / p.G);
+    int jhi;
+    if (MODE == kWin) {
+      jhi = min(w.qt, nkt - 1);
+      w.jlo = jhi;
+      while (w.jlo > 0 && tile_visible(w.jlo - 1, w.qt)) --w.jlo;
+      if (!tile_visible(jhi, w.qt)) jhi = w.jlo - 1;
+    } else {
+      // visibility is monotone: key tile j is met from its first visible query tile on
+      w.jlo = 0;
+      jhi = -1;
+      int lo = 0, hi = nkt - 1;
+      while (lo <= hi) {   // last j with tile_visible(j, qt)
+        const int mid = (lo + hi) >> 1;
+        if (tile_visible(mid, w.qt)) { jhi = mid; lo = mid + 1; } else hi = mid - 1;
+      }
+    }
+    w.ntiles = poisoned ? 0 : jhi - w.jlo + 1;
+    return w;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 4; ++i) { mbar_init(&bar->ds_full[i], 1); mbar_init(&bar->ds_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->k_full[i], 1); mbar_init(&bar->k_empty[i], 1);
+      mbar_init(&bar->acc_full[i], 1); mbar_init(&bar->acc_empty[i], 128);
+    }
+    bar->abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) tmem_alloc(&bar->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp == 4) {
+    // TMA producer
+    bool ok = true;
+    int kc = 0;   // key tiles loaded so far by this CTA (ring phases run on across items)
+    for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
+      const Item w = item_at(it);
+      for (int jj = 0; jj < w.ntiles && ok; ++jj, ++kc) {
+        const int j = w.jlo + jj, s = kc & 3, ks = kc & 1;
+        ok = mbar_wait_warp(&bar->ds_empty[s], ((kc >> 2) & 1) ^ 1, abort);
+        if (!ok) break;
+        if (elect_one()) {
+          const int64_t tile = (((int64_t)w.b * p.H + w.h) * nkt + j) * p.ds_per_j + ds_slot<MODE>(j, 2 * w.qt);
+          mbar_arrive_expect_tx(&bar->ds_full[s], SM::kDs);
+          tma_load_2d(&tmDs, &bar->ds_full[s], sDs + s * SM::kDs, 0, (int)(tile * 128));
+          tma_load_2d(&tmDs, &bar->ds_full[s], sDs + s * SM::kDs + 16384, 0, (int)(tile * 128 + 128));
+        }
+        __syncwarp();
+        ok = mbar_wait_warp(&bar->k_empty[ks], ((kc >> 1) & 1) ^ 1, abort);
+        if (!ok) {
+          if (lane == 0) mbar_wait(&bar->ds_full[s], (kc >> 2) & 1, abort);
+          break;
+        }
+        if (elect_one()) {
+          mbar_arrive_expect_tx(&bar->k_full[ks], SM::kK);
+          for (int hf = 0; hf < 2; ++hf)
+            tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kK + hf * (DK * 128), j * 128 + hf * 64, (w.b * p.G + w.g) * DK);
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok && lane == 0) {
+      // let copies already in flight land before the CTA gives its shared memory back
+      for (int c = max(0, kc - 4); c < kc; ++c) mbar_wait(&bar->ds_full[c & 3], (c >> 2) & 1, abort);
+      for (int c = max(0, kc - 2); c < kc; ++c) mbar_wait(&bar->k_full[c & 1], (c >> 1) & 1, abort);
+    }
+  } else if (warp == 5) {
+    // UMMA issuer
+    constexpr uint32_t idesc = idesc_bf16(128, DK, 1, 0);   // dS^T tiles as A (MN-major: queries contiguous) x K tile (K-major)
+    bool ok = true;
+    int ic = 0, kc = 0;
+    for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
+      const Item w = item_at(it);
+      if (w.ntiles <= 0) continue;
+      const int a = ic & 1;
+      ok = mbar_wait_warp(&bar->acc_empty[a], ((ic >> 1) & 1) ^ 1, abort);   // the epilogue has read this accumulator out
+      for (int jj = 0; jj < w.ntiles && ok; ++jj, ++kc) {
+        const int s = kc & 3, ks = kc & 1;
+        ok = mbar_wait_warp(&bar->ds_full[s], (kc >> 2) & 1, abort) && mbar_wait_warp(&bar->k_full[ks], (kc >> 1) & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
+          const uint64_t dA = smem_desc_sw128(smem_u32(sDs + s * SM::kDs), 16384, 1024);
+          const uint64_t dB = smem_desc_sw128(smem_u32(sK + ks * SM::kK), 16, 1024);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tmem + a * 256, desc_advance(dA, kk * 2048), desc_advance(dB, (kk >> 2) * (DK * 128) + (kk & 3) * 32), idesc,
+                    (jj > 0) || (kk > 0));
+          umma_commit(&bar->ds_empty[s]);
+          umma_commit(&bar->k_empty[ks]);
+          if (jj == w.ntiles - 1) umma_commit(&bar->acc_full[a]);
+        }
+        __syncwarp();
+      }
+      ++ic;
+    }
+  } else {
+    // epilogue: one query row per thread
+    const int r = warp * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    bool ok = true;
+    int ic = 0;
+    for (int it = blockIdx.x; it < nitems; it += gridDim.x) {
+      const Item w = item_at(it);
+      const int ntiles = ok ? w.ntiles : 0;
+      const int64_t row = ((int64_t)w.b * p.H + w.h) * p.Tq + w.qt * 128 + r;
+      __nv_bfloat16* dst = p.dq + row * DK;
+      const int a = ic & 1;
+      if (ntiles > 0) {
+        ok = mbar_wait(&bar->acc_full[a], (ic >> 1) & 1, abort);
+        if (ok) tc_fence_after();
+      }
+      if (!ok) continue;
+#pragma unroll
+      for (int c = 0; c < DK / 32; ++c) {
+        uint32_t ov[32];
+        if (ntiles > 0) {
+          tmem_ld32(tmem + lane_base + a * 256 + c * 32, ov);
+          tc_wait_ld();
+          if (c == DK / 32 - 1) {
+            tc_fence_before();
+            mbar_arrive(&bar->acc_empty[a]);   // the next item but one may overwrite this accumulator
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[e] = 0;
+        }
+#pragma unroll
+        for (int e = 0; e < 32; e += 8) {
+          uint4 pkt;
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(ov[e]) * p.scale, __uint_as_float(ov[e + 1]) * p.scale);
+          __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(ov[e + 2]) * p.scale, __uint_as_float(ov[e + 3]) * p.scale);
+          __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[e + 4]) * p.scale, __uint_as_float(ov[e + 5]) * p.scale);
+          __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(ov[e + 6]) * p.scale, __uint_as_float(ov[e + 7]) * p.scale);
+          pkt.x = *reinterpret_cast<uint32_t*>(&a0); pkt.y = *reinterpret_cast<uint32_t*>(&a1);
+          pkt.z = *reinterpret_cast<uint32_t*>(&a2); pkt.w = *reinterpret_cast<uint32_t*>(&a3);
+          *reinterpret_cast<uint4*>(dst + c * 32 + e) = pkt;
+        }
+      }
+      if (ntiles > 0) ++ic;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bar->abort) ptx::report_timeout(p.timeouts);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // dK/dV kernel: 128 keys per CTA, loops over (head, 64-query sub-tile); transposed tiles in TMEM.
 // 320 threads: warps 0-3 / 4-7 turn the two 32-query halves of S^T, dP^T into P^T, dS^T; warp 8 TMA; warp 9 UMMA.
 // ------------------------------------------------------------------------------------------------
@@ -429,14 +667,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   // 64-query sub-tiles that can see this key tile
   int qs_lo, qs_hi;
-  if (MODE == kWin) {
-    qs_lo = n0 / 64;
-    qs_hi = min(p.Tq - 1, n0 + 126 + p.window) / 64;
-  } else {
-    const int64_t tfirst = (int64_t)n0 * p.cmp_d + p.cmp_l - 1;
-    qs_lo = (n0 < p.cmp_nb && tfirst < p.Tq) ? (int)(max(tfirst, (int64_t)0) / 64) : 1;  // tfirst < 0: visible from the first row on
-    qs_hi = (n0 < p.cmp_nb && tfirst < p.Tq) ? (p.Tq - 1) / 64 : 0;
-  }
+  subtile_range<MODE>(blockIdx.x, p.Tq, p.window, p.cmp_l, p.cmp_d, p.cmp_nb, &qs_lo, &qs_hi);
   const bool poisoned = p.timeouts && *(volatile const int*)p.timeouts != 0;  // a block gave up on a wait earlier: skip
   const int nq = poisoned ? 0 : max(0, qs_hi - qs_lo + 1);
   const int n_it = nq * hper;
@@ -568,10 +799,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int r = (warp & 3) * 32 + lane, key = n0 + r;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
-    int s = -1, ph = 0, qs = qs_lo - 1;
+    int s = -1, ph = 0, qs = qs_lo - 1, h = hbeg;
     for (int it = 0; it < n_it && ok; ++it) {
       if (++s == 3) { s = 0; ph ^= 1; }
-      if (++qs > qs_hi) qs = qs_lo;
+      if (++qs > qs_hi) { qs = qs_lo; ++h; }
       const int tq0 = qs * 64;
       ok = mbar_wait(&bar->full[s], ph, abort) && mbar_wait(&bar->stp_full, it & 1, abort);
       if (!ok) break;
@@ -608,6 +839,14 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1), y = __floats2bfloat162_rn(s0, s1);
         pk[e] = *reinterpret_cast<uint32_t*>(&x);
         pk[16 + e] = *reinterpret_cast<uint32_t*>(&y);
+      }
+      if (p.ds) {
+        // hand dS^T to the dQ kernel: this thread's key row, the 32 queries of its group (64 contiguous bytes of the
+        // tile's 128-byte row)
+        const int64_t tile = (((int64_t)b * p.H + h) * gridDim.x + blockIdx.x) * p.ds_per_j + ds_slot<MODE>(blockIdx.x, qs);
+        uint4* dst = reinterpret_cast<uint4*>(p.ds + tile * 8192 + r * 64 + gsel * 32);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dst[e] = make_uint4(pk[16 + 4 * e], pk[17 + 4 * e], pk[18 + 4 * e], pk[19 + 4 * e]);
       }
       // P^T / dS^T of the previous iteration must have been consumed before they are overwritten
       if (it > 0) {
@@ -693,29 +932,58 @@ static int pick_hsplit(int B, int G, int H, int Tk, int mode) {
   return hs;
 }
 
-size_t fa_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int mode) {
+static size_t bwd_base_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int mode) {
   const int hs = pick_hsplit(B, G, H, Tk, mode);
   size_t n = 2 * al256((size_t)B * H * Tq * sizeof(float));
   if (hs > 1) n += al256((size_t)hs * B * G * Tk * dk * sizeof(float)) + al256((size_t)hs * B * G * Tk * dv * sizeof(float));
   return n;
 }
+// dS^T scratch handed from the dK/dV kernel to the dQ kernel; 0 when it would be unreasonably large (the dQ kernel then
+// recomputes S and dP) or its row count would not fit a tensor-map coordinate
+constexpr size_t kMaxDsBytes = (size_t)48 << 30;
+static size_t bwd_ds_bytes(int B, int H, int Tq, int Tk, int mode, int window) {
+  const size_t tiles = (size_t)B * H * (Tk / 128) * ds_slots_per_key_tile(mode, Tq, window);
+  const size_t bytes = tiles * 16384;
+  if (bytes > kMaxDsBytes || tiles * 128 >= ((size_t)1 << 31)) return 0;
+  return bytes;
+}
+
+size_t fa_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int mode, int window, bool recompute) {
+  const size_t base = bwd_base_bytes(B, H, G, Tq, Tk, dk, dv, mode);
+  return base + (recompute ? 0 : bwd_ds_bytes(B, H, Tq, Tk, mode, window));
+}
 
 template <int DK, int DV, int MODE>
 static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, const CUtensorMap& tq64,
-                        const CUtensorMap& tdo64, const CUtensorMap& tk, const CUtensorMap& tv, const FaBwdParams& p,
-                        cudaStream_t st) {
+                        const CUtensorMap& tdo64, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tds,
+                        const FaBwdParams& p, cudaStream_t st) {
   auto kq = fa_bwd_dq_kernel<DK, DV, MODE>;
+  auto kqd = fa_bwd_dq_ds_kernel<DK, MODE>;
   auto kkv = fa_bwd_dkv_kernel<DK, DV, MODE>;
   if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<DK, DV>::kDynamic) != cudaSuccess ||
+      cudaFuncSetAttribute(kqd, cudaFuncAttributeMaxDynamicSharedMemorySize, DqDsSmem<DK>::kDynamic) != cudaSuccess ||
       cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<DK, DV>::kDynamic) != cudaSuccess)
     return fail(NSA_ERR_LAUNCH, "fa_bwd: cannot reserve shared memory");
+  const dim3 qgrid((unsigned)std::min((p.Tq / 128) * p.B * p.H, bwd_sm_count()));
+  const dim3 kvgrid(p.Tk / 128, p.hsplit, p.B * p.G);
+  if (p.ds) {
+    // key-stationary kernel first: it leaves dS^T behind, from which the dQ kernel only has one product left to do
+    {
+      KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);
+      kkv<<<kvgrid, 320, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, p);
+    }
+    if (int rc = check_launch("fa_bwd_dkv_sm100")) return rc;
+    KernelTimer kt(MODE == kWin ? "fa_bwd_dqds_win" : "fa_bwd_dqds_cmp", st);
+    kqd<<<qgrid, 192, DqDsSmem<DK>::kDynamic, st>>>(tds, tk, p);
+    return check_launch("fa_bwd_dq_ds_sm100");
+  }
   {
     KernelTimer kt(MODE == kWin ? "fa_bwd_dq_win" : "fa_bwd_dq_cmp", st);
-    kq<<<dim3((unsigned)std::min((p.Tq / 128) * p.B * p.H, bwd_sm_count())), 320, DqSmem<DK, DV>::kDynamic, st>>>(tq128, tdo128, tk, tv, p);
+    kq<<<qgrid, 320, DqSmem<DK, DV>::kDynamic, st>>>(tq128, tdo128, tk, tv, p);
   }
   if (int rc = check_launch("fa_bwd_dq_sm100")) return rc;
   KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);
-  kkv<<<dim3(p.Tk / 128, p.hsplit, p.B * p.G), 320, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, p);
+  kkv<<<kvgrid, 320, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, p);
   return check_launch("fa_bwd_dkv_sm100");
 }
 
@@ -725,11 +993,16 @@ int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, con
                  void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return fail(NSA_ERR_UNSUPPORTED, "fa_bwd_sm100: unsupported shape");
   if ((int64_t)B * H > 65535) return fail(NSA_ERR_UNSUPPORTED, "fa_bwd_sm100: B*H too large");
-  const size_t need = fa_bwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, mode);
+  const size_t need = bwd_base_bytes(B, H, G, Tq, Tk, dk, dv, mode);
   if (!workspace || workspace_bytes < need)
     return fail(NSA_ERR_WORKSPACE, "attention backward needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  // with room for the dS^T tiles behind the basic scratch, S and dP are computed once (dK/dV kernel) instead of twice
+  const size_t ds_bytes = bwd_ds_bytes(B, H, Tq, Tk, mode, window);
+  const bool use_ds = ds_bytes > 0 && workspace_bytes >= need + ds_bytes;
   FaBwdParams p;
   char* w = (char*)workspace;
+  p.ds = use_ds ? (__nv_bfloat16*)(w + need) : nullptr;
+  p.ds_per_j = ds_slots_per_key_tile(mode, Tq, window);
   const size_t rows = (size_t)B * H * Tq;
   float* D = (float*)w;
   float* lse2 = (float*)(w + al256(rows * sizeof(float)));
@@ -747,7 +1020,12 @@ int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, con
   p.timeouts = fa_timeout_counter();
   launch_bwd_prep(o, dout, L, M, row_delta, D, lse2, (int64_t)rows, dv, st);
   if (int rc = check_launch("fa_bwd_prep")) return rc;
-  CUtensorMap tq128, tdo128, tq64, tdo64, tk, tv;
+  CUtensorMap tq128, tdo128, tq64, tdo64, tk, tv, tds;
+  if (use_ds) {
+    if (int rc = make_tmap_bf16_2d(&tds, p.ds, (uint64_t)(ds_bytes / 128), 64, 128)) return rc;
+  } else {
+    tds = CUtensorMap{};
+  }
   if (int rc = make_tmap_bf16_2d(&tq128, q, (uint64_t)B * H * Tq, dk, 128)) return rc;
   if (int rc = make_tmap_bf16_2d(&tdo128, dout, (uint64_t)B * H * Tq, dv, 128)) return rc;
   if (int rc = make_tmap_bf16_2d(&tq64, q, (uint64_t)B * H * Tq, dk, 64)) return rc;
@@ -757,8 +1035,8 @@ int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, con
   int rc = NSA_ERR_UNSUPPORTED;
 #define NSA_BWD_CASE(DK_, DV_)                                                                               \
   if (dk == DK_ && dv == DV_)                                                                                \
-    rc = mode == kWin ? launch_bwd_t<DK_, DV_, kWin>(tq128, tdo128, tq64, tdo64, tk, tv, p, st)              \
-                      : launch_bwd_t<DK_, DV_, kCmp>(tq128, tdo128, tq64, tdo64, tk, tv, p, st);
+    rc = mode == kWin ? launch_bwd_t<DK_, DV_, kWin>(tq128, tdo128, tq64, tdo64, tk, tv, tds, p, st)         \
+                      : launch_bwd_t<DK_, DV_, kCmp>(tq128, tdo128, tq64, tdo64, tk, tv, tds, p, st);
   NSA_BWD_CASE(192, 128)
   NSA_BWD_CASE(128, 128)
   NSA_BWD_CASE(64, 64)

@@ -29,7 +29,10 @@ int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L,
 // overwrites dq [B,H,Tq,dk].  Three launches: delta/lse preparation, a query-stationary dQ kernel and
 // a key-stationary dK/dV kernel whose per-head-chunk partial sums are combined in a fixed order.
 // row_delta: the row sums dO.O [B,H,Tq] (fp32) when the caller has them already, else null (computed here).
-size_t fa_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int mode);
+// With room behind the basic scratch for the dS^T tiles (window: the sliding window, needed to size them), the dK/dV
+// kernel hands dS^T to the dQ kernel and S, dP are computed once per step; `recompute` asks for the basic scratch only
+// (the dQ kernel then recomputes S and dP).  fa_bwd_sm100 picks the path from the size of the workspace it is given.
+size_t fa_bwd_sm100_workspace_bytes(int B, int H, int G, int Tq, int Tk, int dk, int dv, int mode, int window, bool recompute);
 int fa_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* L,
                  const float* M, void* dq, void* dk_out, void* dv_out, int B, int H, int G, int Tq, int Tk, int dk, int dv,
                  int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale, const float* row_delta,

@@ -5,23 +5,11 @@
 
 namespace nsa {
 
-__device__ __forceinline__ void gates3(const float* lg, int mode, float g[3]) {
-  if (mode == NSA_GATE_SOFTMAX) {
-    const float m = fmaxf(lg[0], fmaxf(lg[1], lg[2]));
-    const float e0 = expf(lg[0] - m), e1 = expf(lg[1] - m), e2 = expf(lg[2] - m);
-    const float inv = 1.f / (e0 + e1 + e2);
-    g[0] = e0 * inv; g[1] = e1 * inv; g[2] = e2 * inv;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 3; ++i) g[i] = 1.f / (1.f + expf(-lg[i]));
-  }
-}
-
 // one warp per (b,h,t) row
 template <typename T>
 __global__ void gate_mix_fwd_kernel(const float* __restrict__ logits, const T* __restrict__ oc, const T* __restrict__ os,
                                     const T* __restrict__ ow, T* __restrict__ out, float* __restrict__ gates, int B,
-                                    int H, int T_, int dv, int mode) {
+                                    int H, int T_, int dv, int mode, int out_tm) {
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= (int64_t)B * H * T_) return;
@@ -29,11 +17,11 @@ __global__ void gate_mix_fwd_kernel(const float* __restrict__ logits, const T* _
   float g[3];
   gates3(logits + ((int64_t)b * T_ + t) * 3 * H + 3 * h, mode, g);
   if (lane < 3) gates[row * 3 + lane] = g[lane];
-  const int64_t base = row * dv;
+  const int64_t base = row * dv, obase = mixed_row(row, b, h, t, H, T_, out_tm) * dv;
   for (int c = lane; c < dv; c += 32) {
     const float x = Elem<T>::ld(oc + base + c) * g[0];
     const float y = x + Elem<T>::ld(os + base + c) * g[1];
-    Elem<T>::st(out + base + c, y + Elem<T>::ld(ow + base + c) * g[2]);
+    Elem<T>::st(out + obase + c, y + Elem<T>::ld(ow + base + c) * g[2]);
   }
 }
 
@@ -41,16 +29,16 @@ template <typename T>
 __global__ void gate_mix_bwd_kernel(const float* __restrict__ gates, const T* __restrict__ oc, const T* __restrict__ os,
                                     const T* __restrict__ ow, const T* __restrict__ dout, T* __restrict__ doc,
                                     T* __restrict__ dos, T* __restrict__ dow, float* __restrict__ dlogits, int B, int H,
-                                    int T_, int dv, int mode, float* __restrict__ delta) {
+                                    int T_, int dv, int mode, float* __restrict__ delta, int dout_tm) {
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= (int64_t)B * H * T_) return;
   const int t = row % T_, h = (row / T_) % H, b = row / ((int64_t)T_ * H);
   const float g0 = gates[row * 3], g1 = gates[row * 3 + 1], g2 = gates[row * 3 + 2];
-  const int64_t base = row * dv;
+  const int64_t base = row * dv, dbase = mixed_row(row, b, h, t, H, T_, dout_tm) * dv;
   float d0 = 0.f, d1 = 0.f, d2 = 0.f;
   for (int c = lane; c < dv; c += 32) {
-    const float dy = Elem<T>::ld(dout + base + c);
+    const float dy = Elem<T>::ld(dout + dbase + c);
     d0 = fmaf(dy, Elem<T>::ld(oc + base + c), d0);
     d1 = fmaf(dy, Elem<T>::ld(os + base + c), d1);
     d2 = fmaf(dy, Elem<T>::ld(ow + base + c), d2);
@@ -103,12 +91,12 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 __global__ void gate_mix_fwd_bf16x4_kernel(const float* __restrict__ logits, const __nv_bfloat16* __restrict__ oc,
                                            const __nv_bfloat16* __restrict__ os, const __nv_bfloat16* __restrict__ ow,
                                            __nv_bfloat16* __restrict__ out, float* __restrict__ gates, int B, int H, int T_, int dv,
-                                           int mode) {
+                                           int mode, int out_tm) {
   const int lane = threadIdx.x & 31, hl = lane & 15;
   const int64_t row = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
   if (row >= (int64_t)B * H * T_) return;
   const int t = row % T_, h = (row / T_) % H, b = row / ((int64_t)T_ * H);
-  const int64_t base = row * dv;
+  const int64_t base = row * dv, obase = mixed_row(row, b, h, t, H, T_, out_tm) * dv;
   // the tile loads go out before the gate arithmetic
   uint4 ra = *reinterpret_cast<const uint4*>(oc + base + hl * 8);
   uint4 rs = *reinterpret_cast<const uint4*>(os + base + hl * 8);
@@ -126,7 +114,7 @@ __global__ void gate_mix_fwd_bf16x4_kernel(const float* __restrict__ logits, con
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) y[i] = (a[i] * g[0] + s_[i] * g[1]) + w[i] * g[2];
-    *reinterpret_cast<uint4*>(out + base + c) = pack8(y);
+    *reinterpret_cast<uint4*>(out + obase + c) = pack8(y);
   }
 }
 
@@ -134,18 +122,18 @@ __global__ void gate_mix_bwd_bf16x4_kernel(const float* __restrict__ gates, cons
                                            const __nv_bfloat16* __restrict__ os, const __nv_bfloat16* __restrict__ ow,
                                            const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ doc,
                                            __nv_bfloat16* __restrict__ dos, __nv_bfloat16* __restrict__ dow, float* __restrict__ dlogits,
-                                           int B, int H, int T_, int dv, int mode, float* __restrict__ delta) {
+                                           int B, int H, int T_, int dv, int mode, float* __restrict__ delta, int dout_tm) {
   const int lane = threadIdx.x & 31, hl = lane & 15;
   int64_t row = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
   const bool live = row < (int64_t)B * H * T_;  // both halves stay for the shuffles
   if (!live) row = 0;
   const int t = row % T_, h = (row / T_) % H, b = row / ((int64_t)T_ * H);
   const float g0 = gates[row * 3], g1 = gates[row * 3 + 1], g2 = gates[row * 3 + 2];
-  const int64_t base = row * dv;
+  const int64_t base = row * dv, dbase = mixed_row(row, b, h, t, H, T_, dout_tm) * dv;
   float d0 = 0.f, d1 = 0.f, d2 = 0.f;
   for (int c = hl * 8; c < dv; c += 128) {
     float dy[8], a[8], s_[8], w[8], r0[8], r1[8], r2[8];
-    const uint4 qd = *reinterpret_cast<const uint4*>(dout + base + c), qa = *reinterpret_cast<const uint4*>(oc + base + c);
+    const uint4 qd = *reinterpret_cast<const uint4*>(dout + dbase + c), qa = *reinterpret_cast<const uint4*>(oc + base + c);
     const uint4 qs = *reinterpret_cast<const uint4*>(os + base + c), qw = *reinterpret_cast<const uint4*>(ow + base + c);
     unpack8(qd, dy); unpack8(qa, a); unpack8(qs, s_); unpack8(qw, w);
 #pragma unroll
@@ -185,7 +173,9 @@ __global__ void gate_mix_bwd_bf16x4_kernel(const float* __restrict__ gates, cons
 using namespace nsa;
 
 extern "C" NSA_API int nsa_gate_mix_fwd(const float* logits, const void* o_cmp, const void* o_slc, const void* o_win, void* out,
-                                float* gates_out, int B, int H, int T, int dv, int gate_mode, int dtype, void* stream) {
+                                float* gates_out, int B, int H, int T, int dv, int gate_mode, int dtype, int out_token_major,
+                                void* stream) {
+  const int out_tm = out_token_major ? 1 : 0;
   NSA_REQUIRE(logits && o_cmp && o_slc && o_win && out && gates_out, "gate_mix_fwd: null pointer");
   NSA_REQUIRE(gate_mode == NSA_GATE_SIGMOID || gate_mode == NSA_GATE_SOFTMAX, "gate_mix_fwd: bad gate mode %d", gate_mode);
   const int64_t rows = (int64_t)B * H * T;
@@ -195,14 +185,14 @@ extern "C" NSA_API int nsa_gate_mix_fwd(const float* logits, const void* o_cmp, 
   KernelTimer kt("gate_mix_fwd", st);
   if (dtype == NSA_F32)
     gate_mix_fwd_kernel<float><<<grid, 256, 0, st>>>(logits, (const float*)o_cmp, (const float*)o_slc, (const float*)o_win,
-                                                      (float*)out, gates_out, B, H, T, dv, gate_mode);
+                                                      (float*)out, gates_out, B, H, T, dv, gate_mode, out_tm);
   else if (dtype == NSA_BF16 && dv % 128 == 0)
     gate_mix_fwd_bf16x4_kernel<<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(logits, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc,
-                                                     (const __nv_bfloat16*)o_win, (__nv_bfloat16*)out, gates_out, B, H, T, dv, gate_mode);
+                                                     (const __nv_bfloat16*)o_win, (__nv_bfloat16*)out, gates_out, B, H, T, dv, gate_mode, out_tm);
   else if (dtype == NSA_BF16)
     gate_mix_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(logits, (const __nv_bfloat16*)o_cmp,
                                                               (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win,
-                                                              (__nv_bfloat16*)out, gates_out, B, H, T, dv, gate_mode);
+                                                              (__nv_bfloat16*)out, gates_out, B, H, T, dv, gate_mode, out_tm);
   else
     return fail(NSA_ERR_ARG, "gate_mix_fwd: unsupported dtype %d", dtype);
   return check_launch("gate_mix_fwd");
@@ -210,7 +200,9 @@ extern "C" NSA_API int nsa_gate_mix_fwd(const float* logits, const void* o_cmp, 
 
 extern "C" NSA_API int nsa_gate_mix_bwd_delta(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
                                       const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits,
-                                      float* delta, int B, int H, int T, int dv, int gate_mode, int dtype, void* stream) {
+                                      float* delta, int B, int H, int T, int dv, int gate_mode, int dtype, int dout_token_major,
+                                      void* stream) {
+  const int dout_tm = dout_token_major ? 1 : 0;
   NSA_REQUIRE(gates && o_cmp && o_slc && o_win && dout && do_cmp && do_slc && do_win && dlogits, "gate_mix_bwd: null pointer");
   const int64_t rows = (int64_t)B * H * T;
   if (rows == 0) return NSA_OK;
@@ -220,16 +212,16 @@ extern "C" NSA_API int nsa_gate_mix_bwd_delta(const float* gates, const void* o_
   if (dtype == NSA_F32)
     gate_mix_bwd_kernel<float><<<grid, 256, 0, st>>>(gates, (const float*)o_cmp, (const float*)o_slc, (const float*)o_win,
                                                       (const float*)dout, (float*)do_cmp, (float*)do_slc, (float*)do_win,
-                                                      dlogits, B, H, T, dv, gate_mode, delta);
+                                                      dlogits, B, H, T, dv, gate_mode, delta, dout_tm);
   else if (dtype == NSA_BF16 && dv % 128 == 0)
     gate_mix_bwd_bf16x4_kernel<<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(gates, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc,
                                                      (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)dout, (__nv_bfloat16*)do_cmp,
-                                                     (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, dlogits, B, H, T, dv, gate_mode, delta);
+                                                     (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, dlogits, B, H, T, dv, gate_mode, delta, dout_tm);
   else if (dtype == NSA_BF16)
     gate_mix_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
         gates, (const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win,
         (const __nv_bfloat16*)dout, (__nv_bfloat16*)do_cmp, (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, dlogits, B, H,
-        T, dv, gate_mode, delta);
+        T, dv, gate_mode, delta, dout_tm);
   else
     return fail(NSA_ERR_ARG, "gate_mix_bwd: unsupported dtype %d", dtype);
   return check_launch("gate_mix_bwd");
@@ -237,7 +229,7 @@ extern "C" NSA_API int nsa_gate_mix_bwd_delta(const float* gates, const void* o_
 
 extern "C" NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,
                                 const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits, int B, int H,
-                                int T, int dv, int gate_mode, int dtype, void* stream) {
+                                int T, int dv, int gate_mode, int dtype, int dout_token_major, void* stream) {
   return nsa_gate_mix_bwd_delta(gates, o_cmp, o_slc, o_win, dout, do_cmp, do_slc, do_win, dlogits, nullptr, B, H, T, dv,
-                                gate_mode, dtype, stream);
+                                gate_mode, dtype, dout_token_major, stream);
 }

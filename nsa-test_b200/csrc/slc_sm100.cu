@@ -397,6 +397,31 @@ __device__ __forceinline__ unsigned valid_slot_mask(const int* irow, int64_t s3,
   return __ballot_sync(0xffffffffu, ok);
 }
 
+// Gate + mix epilogue of the merge kernels: the warp holds the finished (rounded) O_slc row of (b,h,t), lane owning VPL
+// consecutive columns; the mixed row is (o_cmp g0 + o_slc g1) + o_win g2, the operation order of the stand-alone pass.
+template <int VPL>
+__device__ __forceinline__ void slc_mix_row(const SlcMix& mix, const __nv_bfloat162 (&oslc)[VPL / 2], int64_t row, int b, int h, int t,
+                                            int H, int Tq, int dv, int lane) {
+  const __nv_bfloat16* oc = (const __nv_bfloat16*)mix.o_cmp + row * dv + lane * VPL;
+  const __nv_bfloat16* ow = (const __nv_bfloat16*)mix.o_win + row * dv + lane * VPL;
+  __nv_bfloat162 a[VPL / 2], w[VPL / 2];
+#pragma unroll
+  for (int c = 0; c < VPL / 2; ++c) {
+    a[c] = *reinterpret_cast<const __nv_bfloat162*>(oc + 2 * c);
+    w[c] = *reinterpret_cast<const __nv_bfloat162*>(ow + 2 * c);
+  }
+  float g[3];
+  gates3(mix.logits + ((int64_t)b * Tq + t) * 3 * H + 3 * h, mix.mode, g);
+  if (lane < 3) mix.gates[row * 3 + lane] = g[lane];
+  __nv_bfloat16* dst = (__nv_bfloat16*)mix.out + mixed_row(row, b, h, t, H, Tq, mix.token_major) * dv + lane * VPL;
+#pragma unroll
+  for (int c = 0; c < VPL / 2; ++c) {
+    const float2 fa = __bfloat1622float2(a[c]), fs = __bfloat1622float2(oslc[c]), fw = __bfloat1622float2(w[c]);
+    *reinterpret_cast<__nv_bfloat162*>(dst + 2 * c) =
+        __floats2bfloat162_rn((fa.x * g[0] + fs.x * g[1]) + fw.x * g[2], (fa.y * g[0] + fs.y * g[1]) + fw.y * g[2]);
+  }
+}
+
 // merge the partials of a query in slot order: one warp per (b,h,t).  Every load of the row (index row, statistics,
 // all slots' partial outputs) is issued before the first value is used; slots that turn out not to contribute were
 // never written and their loads are discarded.
@@ -404,7 +429,7 @@ template <int DV>
 __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part, const float2* __restrict__ st_part,
                                        const int* __restrict__ indices, int64_t s0, int64_t s1, int64_t s2, int64_t s3,
                                        __nv_bfloat16* __restrict__ out, float* __restrict__ L, float* __restrict__ M, int B,
-                                       int H, int G, int Tq, int Tk, int nslots, int lprime, int q0) {
+                                       int H, int G, int Tq, int Tk, int nslots, int lprime, int q0, const SlcMix mix) {
   static_assert(DV % 64 == 0, "lanes own 2 or 4 consecutive output columns");
   constexpr int VPL = DV / 32;  // values per lane
   // consecutive warps take the heads of one (group, query): together they stream that query's contiguous block of partials
@@ -457,13 +482,17 @@ __global__ void slc_combine_fwd_kernel(const __nv_bfloat16* __restrict__ o_part,
   }
   const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
   __nv_bfloat16* dst = out + row * DV + lane * VPL;
+  __nv_bfloat162 rounded[VPL / 2];
 #pragma unroll
-  for (int c = 0; c < VPL; c += 2)
-    *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+  for (int c = 0; c < VPL; c += 2) {
+    rounded[c / 2] = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+    *reinterpret_cast<__nv_bfloat162*>(dst + c) = rounded[c / 2];
+  }
   if (lane == 0) {
     L[row] = lsum > 0.f ? logf(lsum) : -CUDART_INF_F;
     M[row] = lsum > 0.f ? mx * kLn2f : -CUDART_INF_F;
   }
+  if (mix.out) slc_mix_row<VPL>(mix, rounded, row, b, h, t, H, Tq, DV, lane);
 }
 
 // Same merge with the whole contiguous block of a query's partials ([slots][heads][dv]) brought into shared memory by
@@ -473,7 +502,8 @@ template <int DV>
 __global__ void slc_combine_fwd_bulk_kernel(const __nv_bfloat16* __restrict__ o_part, const float2* __restrict__ st_part,
                                             const int* __restrict__ indices, int64_t s0, int64_t s1, int64_t s2, int64_t s3,
                                             __nv_bfloat16* __restrict__ out, float* __restrict__ L, float* __restrict__ M, int B,
-                                            int H, int G, int Tq, int Tk, int nslots, int lprime, int q0, int* timeouts) {
+                                            int H, int G, int Tq, int Tk, int nslots, int lprime, int q0, int* timeouts,
+                                            const SlcMix mix) {
   constexpr int VPL = DV / 32;
   extern __shared__ __align__(128) uint8_t sm_part[];
   __shared__ uint64_t bar;
@@ -524,13 +554,17 @@ __global__ void slc_combine_fwd_bulk_kernel(const __nv_bfloat16* __restrict__ o_
     }
     const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
     __nv_bfloat16* dst = out + row * DV + lane * VPL;
+    __nv_bfloat162 rounded[VPL / 2];
 #pragma unroll
-    for (int c = 0; c < VPL; c += 2)
-      *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+    for (int c = 0; c < VPL; c += 2) {
+      rounded[c / 2] = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+      *reinterpret_cast<__nv_bfloat162*>(dst + c) = rounded[c / 2];
+    }
     if (lane == 0) {
       L[row] = lsum > 0.f ? logf(lsum) : -CUDART_INF_F;
       M[row] = lsum > 0.f ? mx * kLn2f : -CUDART_INF_F;
     }
+    if (mix.out) slc_mix_row<VPL>(mix, rounded, row, b, h, t, H, Tq, DV, lane);
   }
   __syncthreads();  // the copy has landed (or was given up on) before shared memory is handed back
   if (threadIdx.x == 0 && abort_flag) ptx::report_timeout(timeouts);
@@ -1221,7 +1255,7 @@ static int token_major_copy_w(int W, const void* in, void* out, int B, int H, in
 template <int DK, int DV>
 static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tqt, const CUtensorMap& top,
                             const SlcParams& p, const int* indices,
-                            const int64_t* sidx, __nv_bfloat16* out, float* L, float* M, cudaStream_t st) {
+                            const int64_t* sidx, __nv_bfloat16* out, float* L, float* M, const SlcMix& mix, cudaStream_t st) {
   using SM = SlcFwdSmem<DK, DV>;
   auto kern = slc_fwd_kernel<DK, DV>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kDynamic) != cudaSuccess)
@@ -1234,23 +1268,23 @@ static int launch_slc_fwd_t(const CUtensorMap& tk, const CUtensorMap& tv, const 
   if (int rc = check_launch("slc_fwd_sm100")) return rc;
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
   const size_t qbytes = (size_t)p.nslots * p.hpg * DV * 2;  // one query's partials
-  KernelTimer kt("slc_combine_fwd", st);
+  KernelTimer kt(mix.out ? "slc_combine_fwd_mix" : "slc_combine_fwd", st);
   if (p.hpg <= 32 && qbytes <= 100 * 1024 && (int64_t)p.B * p.G * p.Tq < (1ll << 31)) {
     auto kc = slc_combine_fwd_bulk_kernel<DV>;
     if (cudaFuncSetAttribute(kc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qbytes) != cudaSuccess)
       return fail(NSA_ERR_LAUNCH, "slc_combine_fwd: cannot reserve shared memory");
     kc<<<(unsigned)((int64_t)p.B * p.G * p.Tq), p.hpg * 32, qbytes, st>>>(p.o_part, p.st_part, indices, sidx[0], sidx[1], sidx[2], sidx[3],
-                                                                      out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.q0, p.timeouts);
+                                                                      out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.q0, p.timeouts, mix);
   } else {
     slc_combine_fwd_kernel<DV><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.o_part, p.st_part, indices, sidx[0], sidx[1], sidx[2],
-                                                                           sidx[3], out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.q0);
+                                                                           sidx[3], out, L, M, p.B, p.H, p.G, p.Tq, p.Tk, p.nslots, 64, p.q0, mix);
   }
   return check_launch("slc_combine_fwd");
 }
 
 int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indices, const int64_t* sidx, void* out, float* L,
                   float* M, int B, int H, int G, int Tq, int Tk, int dk, int dv, int nslots, int lprime, float scale, int q0,
-                  void* workspace, size_t workspace_bytes, cudaStream_t st) {
+                  const SlcMix& mix, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!slc_sm100_supported(H, G, Tq, Tk, dk, dv, nslots, lprime)) return fail(NSA_ERR_UNSUPPORTED, "slc_fwd_sm100: unsupported shape");
   const size_t need = slc_fwd_sm100_workspace_bytes(B, H, G, Tq, Tk, dk, dv, nslots, lprime);
   if (!workspace || workspace_bytes < need)
@@ -1283,9 +1317,9 @@ int slc_fwd_sm100(const void* q, const void* k, const void* v, const int* indice
   }
   CUtensorMap top;  // partial outputs as rows of dv values; one box = the heads of a group for one (query, slot)
   if (int rc = make_tmap_bf16_2d(&top, p.o_part, (uint64_t)rows, dv, (uint32_t)(H / G < 32 ? H / G : 32))) return rc;
-  if (dk == 192 && dv == 128) return launch_slc_fwd_t<192, 128>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
-  if (dk == 128 && dv == 128) return launch_slc_fwd_t<128, 128>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
-  if (dk == 64 && dv == 64) return launch_slc_fwd_t<64, 64>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, st);
+  if (dk == 192 && dv == 128) return launch_slc_fwd_t<192, 128>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, mix, st);
+  if (dk == 128 && dv == 128) return launch_slc_fwd_t<128, 128>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, mix, st);
+  if (dk == 64 && dv == 64) return launch_slc_fwd_t<64, 64>(tk, tv, tqt, top, p, indices, sidx, (__nv_bfloat16*)out, L, M, mix, st);
   return fail(NSA_ERR_UNSUPPORTED, "slc_fwd_sm100: unsupported head dims");
 }
 

@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libnsa_b200.so")
 
 F32, BF16 = 0, 1
 GATE_SIGMOID, GATE_SOFTMAX = 0, 1
-FLAG_GENERIC = 1
+FLAG_GENERIC, FLAG_RECOMPUTE = 1, 2
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -38,7 +38,7 @@ PROTOTYPES = {
     "nsa_profile_report": (c_int, [ctypes.c_char_p, c_size_t]),
     "nsa_device_timeouts": (c_int, [c_int]),
     "nsa_sliding_fwd": (c_int, [_P] * 6 + [_I64P] + [c_int] * 7 + [c_float, c_int, c_int, _P]),
-    "nsa_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 8),
+    "nsa_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 10),
     "nsa_sliding_bwd": (c_int, [_P] * 10 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P, c_int, _P, c_size_t, _P]),
     "nsa_sliding_bwd_noalloc": (c_int, [_P] * 10 + [c_int] * 7 + [c_float, _P]),
     "nsa_cmp_attn_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 7 + [c_float] + [c_int] * 6 + [_P]),
@@ -54,9 +54,10 @@ PROTOTYPES = {
     "nsa_topn_from_scores": (c_int, [_P, _P] + [c_int] * 8 + [_P]),
     "nsa_cmp_probs": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 6 + [c_float, c_int, _P]),
     "nsa_eq9_scores": (c_int, [_P, _P, c_int64] + [c_int] * 4 + [_P]),
-    "nsa_gate_mix_fwd": (c_int, [_P] * 6 + [c_int] * 6 + [_P]),
-    "nsa_gate_mix_bwd": (c_int, [_P] * 9 + [c_int] * 6 + [_P]),
-    "nsa_gate_mix_bwd_delta": (c_int, [_P] * 10 + [c_int] * 6 + [_P]),
+    "nsa_gate_mix_fwd": (c_int, [_P] * 6 + [c_int] * 7 + [_P]),
+    "nsa_gate_mix_bwd": (c_int, [_P] * 9 + [c_int] * 7 + [_P]),
+    "nsa_gate_mix_bwd_delta": (c_int, [_P] * 10 + [c_int] * 7 + [_P]),
+    "nsa_slc_fwd_mix": (c_int, [_P] * 7 + [_I64P] + [c_int] * 9 + [c_float, c_int, c_int, c_int] + [_P] * 5 + [c_int, c_int, _P, c_size_t, _P]),
 }
 
 for _name, (_res, _args) in PROTOTYPES.items():

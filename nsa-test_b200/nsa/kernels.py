@@ -164,43 +164,82 @@ class SelectionAttention(torch.autograd.Function):
         return dq, dkey.transpose(-1, -2), dval, None, None, None, None
 
 
+def _window_slice(q_pos0: int, Tq: int, Tk: int, w: int):
+    """Key range [lo, hi) and the number of zero query rows in front that let the sliding-window kernels (which take
+    query row t as position t of their key tensor) serve queries at positions q_pos0 + [0, Tq): the window reaches
+    w - 1 positions back, so the slice starts a tile-aligned margin before the first query."""
+    if q_pos0 == 0 and Tk == Tq:
+        return 0, Tk, 0
+    pad = min(q_pos0, ((w - 1 + _TILE_ROWS - 1) // _TILE_ROWS) * _TILE_ROWS)
+    return q_pos0 - pad, q_pos0 + Tq, pad
+
+
 class _BranchesAndMix(torch.autograd.Function):
     """The three attention branches and the gate mix of one layer under a single autograd node
     (nsa/kernels.py:2401-2463), so that the backward can pass on what the reference leaves to separate kernels and to
     autograd: the gate/mix backward also produces the row sums dO_b.O_b that each branch backward needs, and the
     selection backward adds the dQ of the other two branches to its own before the one rounding of the sum.
 
-    ``apply(q, k_cmp, v_cmp, block_ends, k_slc, v_slc, indices, k_win, v_win, gate_logits, scale, config, blocks)``
-    -> (out, gates, o_cmp, o_slc, o_win); only ``out`` is differentiable.  Same kernels and layouts as the separate
-    wrappers above, query offset 0 only."""
+    ``apply(q, k_cmp, v_cmp, block_ends, k_slc, v_slc, indices, k_win, v_win, gate_logits, scale, config, blocks, q_pos0,
+    token_major)`` -> (out, gates, o_cmp, o_slc, o_win); only ``out`` is differentiable.  The selection branch runs
+    last and does the gate + mix in its epilogue (north-star item: no separate pass over the three branch outputs in the
+    forward); ``token_major`` lays the mixed output out as [B,T,H,dv] in memory for the output projection.  Same kernels and layouts as the separate
+    wrappers above.  With ``q_pos0`` > 0 the query rows sit at positions q_pos0 + [0, Tq) of keys that start at
+    position 0 (long-context mode); the sliding-window kernels then run on the key slice around the queries."""
 
     @staticmethod
-    def forward(ctx, q, k_cmp, v_cmp, block_ends, k_slc, v_slc, indices, k_win, v_win, gate_logits, scale, config, blocks):
-        o_cmp, Lc, Mc = ops.cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale, blocks)
-        idx = _selection_fallback(indices, config.l_prime).to(torch.int32).contiguous()
-        o_slc, Ls, Ms = ops.slc_fwd(q, k_slc, v_slc, idx, config.l_prime, scale)
-        o_win, Lw, Mw = ops.sliding_fwd(q, k_win, v_win, config.w, scale)
-        out, gates = ops.gate_mix_fwd(gate_logits, o_cmp, o_slc, o_win, config.gate_mode)
-        ctx.save_for_backward(q, k_cmp, v_cmp, block_ends, k_slc, v_slc, idx, k_win, v_win, o_cmp, Lc, Mc, o_slc, Ls, Ms,
-                              o_win, Lw, Mw, gates)
+    def forward(ctx, q, k_cmp, v_cmp, block_ends, k_slc, v_slc, indices, k_win, v_win, gate_logits, scale, config, blocks,
+                q_pos0=0, token_major=False):
+        Tq = q.shape[2]
+        o_cmp, Lc, Mc = ops.cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale, blocks, q_pos0)
+        idx = _selection_fallback(indices, config.l_prime, q_pos0).to(torch.int32).contiguous()
+        lo, hi, pad = _window_slice(q_pos0, Tq, k_win.shape[-1], config.w)
+        if pad or lo or hi != k_win.shape[-1]:
+            kw_s, vw_s = k_win[..., lo:hi].contiguous(), v_win[:, :, lo:hi].contiguous()
+            qw = torch.cat([q.new_zeros(q.shape[0], q.shape[1], pad, q.shape[3]), q], dim=2) if pad else q
+        else:
+            kw_s, vw_s, qw = k_win, v_win, q
+        o_wp, Lw, Mw = ops.sliding_fwd(qw, kw_s, vw_s, config.w, scale)
+        o_win = o_wp[:, :, pad:] if pad else o_wp
+        o_slc, Ls, Ms, out, gates = ops.slc_fwd_mix(q, k_slc, v_slc, idx, config.l_prime, scale, gate_logits, o_cmp, o_win,
+                                                    config.gate_mode, q_pos0, token_major)
+        ctx.save_for_backward(q, k_cmp, v_cmp, block_ends, k_slc, v_slc, idx, kw_s, vw_s, qw, o_cmp, Lc, Mc, o_slc, Ls, Ms,
+                              o_wp, Lw, Mw, gates)
         ctx.scale, ctx.l_prime, ctx.w, ctx.blocks = scale, config.l_prime, config.w, blocks
         ctx.gate_mode, ctx.ldtype = config.gate_mode, gate_logits.dtype
+        ctx.q_pos0, ctx.win = q_pos0, (lo, hi, pad, tuple(k_win.shape), tuple(v_win.shape))
         ctx.mark_non_differentiable(gates, o_cmp, o_slc, o_win)
         return out, gates, o_cmp, o_slc, o_win
 
     @staticmethod
     def backward(ctx, dout, *_unused):
-        (q, k_cmp, v_cmp, block_ends, k_slc, v_slc, idx, k_win, v_win, o_cmp, Lc, Mc, o_slc, Ls, Ms, o_win, Lw, Mw,
+        (q, k_cmp, v_cmp, block_ends, k_slc, v_slc, idx, kw_s, vw_s, qw, o_cmp, Lc, Mc, o_slc, Ls, Ms, o_wp, Lw, Mw,
          gates) = ctx.saved_tensors
+        lo, hi, pad, kshape, vshape = ctx.win
+        o_win = o_wp[:, :, pad:] if pad else o_wp
         d_cmp, d_slc, d_win, dlogits, delta = ops.gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, ctx.gate_mode,
                                                                want_delta=True)
         dq_c, dkc, dvc = ops.cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o_cmp, d_cmp, Lc, Mc, ctx.scale, ctx.blocks,
-                                          row_delta=delta[0])
-        dq_w, dkw, dvw = ops.sliding_bwd(q, k_win, v_win, o_win, d_win, Lw, Mw, ctx.w, ctx.scale, row_delta=delta[2])
-        dq, dks, dvs = ops.slc_bwd(q, k_slc, v_slc, idx, o_slc, d_slc, Ls, Ms, ctx.l_prime, ctx.scale,
+                                          ctx.q_pos0, row_delta=delta[0])
+        if pad:
+            # the zero query rows in front get a zero upstream gradient and zero row sums: they add nothing to dK/dV
+            F = torch.nn.functional
+            d_wp, delta_w = F.pad(d_win, (0, 0, pad, 0)), F.pad(delta[2], (pad, 0))
+        else:
+            d_wp, delta_w = d_win, delta[2]
+        dq_w, dkw, dvw = ops.sliding_bwd(qw, kw_s, vw_s, o_wp, d_wp, Lw, Mw, ctx.w, ctx.scale, row_delta=delta_w)
+        if pad:
+            dq_w = dq_w[:, :, pad:].contiguous()
+        dkw = dkw.transpose(-1, -2)
+        if (lo, hi) != (0, kshape[-1]):
+            full_k, full_v = dkw.new_zeros(kshape), dvw.new_zeros(vshape)
+            full_k[..., lo:hi] = dkw
+            full_v[:, :, lo:hi] = dvw
+            dkw, dvw = full_k, full_v
+        dq, dks, dvs = ops.slc_bwd(q, k_slc, v_slc, idx, o_slc, d_slc, Ls, Ms, ctx.l_prime, ctx.scale, ctx.q_pos0,
                                    dq_addends=(dq_c, dq_w), row_delta=delta[1])
-        return (dq, dkc.transpose(-1, -2), dvc, None, dks.transpose(-1, -2), dvs, None, dkw.transpose(-1, -2), dvw,
-                dlogits.to(ctx.ldtype), None, None, None)
+        return (dq, dkc.transpose(-1, -2), dvc, None, dks.transpose(-1, -2), dvs, None, dkw, dvw,
+                dlogits.to(ctx.ldtype), None, None, None, None, None)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -318,24 +357,26 @@ class _GateMix(torch.autograd.Function):
         return dlogits.to(ctx.ldtype), d0, d1, d2, None
 
 
-def _sliding_with_offset(q, kw, vw, scale, cfg, q_pos0: int):
-    """Sliding-window branch for queries at positions q_pos0 + [0, Tq) against keys from position 0: the window only
-    reaches w - 1 positions back, so the kernel runs on the key slice that starts a (tile-aligned) margin before the
-    first query, with as many zero query rows in front; their outputs are dropped and, their upstream gradient being
-    zero, they add nothing to dK/dV."""
-    Tq = q.shape[2]
-    if q_pos0 == 0 and kw.shape[-1] == Tq:
-        return SlidingWindowAttention.apply(q, kw, vw, scale, cfg.w, cfg)
-    pad = min(q_pos0, ((cfg.w - 1 + 127) // 128) * 128)
-    lo, hi = q_pos0 - pad, q_pos0 + Tq
-    ks = kw[..., lo:hi].contiguous()
-    vs = vw[:, :, lo:hi].contiguous()
-    qp = torch.cat([q.new_zeros(q.shape[0], q.shape[1], pad, q.shape[3]), q], dim=2) if pad else q
-    return SlidingWindowAttention.apply(qp, ks, vs, scale, cfg.w, cfg)[:, :, pad:]
+_BLOCK_ENDS_CACHE: Dict[tuple, torch.Tensor] = {}
+
+
+def _block_ends(nbp: int, nb: int, l: int, d: int, device) -> torch.Tensor:
+    """int32 [nbp]: block i ends at i*d + l - 1 for i < nb, 999999 for the padding blocks (nsa/kernels.py:2185-2192).
+    The same few tensors recur every step, so they are built once per (shape, device)."""
+    key = (nbp, nb, l, d, str(device))
+    be = _BLOCK_ENDS_CACHE.get(key)
+    if be is None:
+        be = torch.full((nbp,), PAD_BLOCK_END, device=device, dtype=torch.int32)
+        be[:nb] = torch.arange(nb, device=device, dtype=torch.int32) * d + (l - 1)
+        if len(_BLOCK_ENDS_CACHE) > 64:
+            _BLOCK_ENDS_CACHE.clear()
+        _BLOCK_ENDS_CACHE[key] = be
+    return be
 
 
 def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv_compress=None, kv_sliding=None,
-              scale: Optional[float] = None, return_info: bool = False, q_pos0: int = 0, indices=None):
+              scale: Optional[float] = None, return_info: bool = False, q_pos0: int = 0, indices=None, compressed=None,
+              token_major_out: bool = False):
     """The NSA hot path between the q/k/v projections and o_proj (nsa/kernels.py:2298-2463).
 
     q [B,H,T,dk]; k_* [B,G,dk,T]; v_* [B,G,T,dv]; gate_logits [B,T,3H]; phi_params =
@@ -346,6 +387,13 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
     Query-sharded long-context runs: q and gate_logits hold the Tq query rows at positions
     ``q_pos0 + [0, Tq)`` while k/v cover the sequence from position 0 (at least up to the last query); the
     gradients of k/v then hold this query slice's contribution only (summed over the ranks by the caller).
+
+    ``compressed`` = (k_cmp fp32 [B,G,dk,nb], v_cmp [B,G,nb,dv]) of the whole sequence, when the caller has run the
+    block compression already (the long-context mode splits it over the ranks); phi_params are then not used here.
+
+    ``token_major_out``: the returned [B,H,T,dv] tensor is a view of a contiguous [B,T,H,dv] buffer (written that way by
+    the mix epilogue), so that ``out.permute(0, 2, 1, 3).reshape(B, T, H*dv)`` feeds the output projection without the
+    transposing copy of nsa/kernels.py:2466-2467; the upstream gradient is read in the same layout.
 
     ``indices`` [B,G,Tq,n] (int) replaces the layer's own Eq. 8-11 block choice, e.g. to evaluate two
     implementations on identical selections; the selection is not differentiable either way.
@@ -365,7 +413,7 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
         pk = lambda kv: None if kv is None else (F.pad(kv[0], (0, pad)), F.pad(kv[1], (0, 0, 0, pad)))
         res = nsa_layer(F.pad(q, (0, 0, 0, pad)), *pk((k_slc, v_slc)), F.pad(gate_logits, (0, 0, 0, pad)), phi_params,
                         config, kv_compress=pk(kv_compress), kv_sliding=pk(kv_sliding), scale=scale,
-                        return_info=return_info,
+                        return_info=return_info, token_major_out=token_major_out,
                         indices=None if indices is None else F.pad(indices, (0, 0, 0, pad), value=-1))
         if not return_info:
             return res[:, :, :T_in]
@@ -382,25 +430,28 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
     kc_src, vc_src = kv_compress if kv_compress is not None else (k_slc, v_slc)
     kw, vw = kv_sliding if kv_sliding is not None else (k_slc, v_slc)
     T = kc_src.shape[-1]   # sequence length covered by the keys (== query rows unless q_pos0 shards the queries)
-    pos_embed, w1, b1, w2, b2 = phi_params
-    k_cmp, v_cmp = _PhiCompress.apply(kc_src.transpose(-1, -2), vc_src, pos_embed, w1, b1, w2, b2, cfg.l, cfg.d)
     nb = (T - cfg.l) // cfg.d + 1
-    block_ends = torch.full((k_cmp.shape[-1],), PAD_BLOCK_END, device=q.device, dtype=torch.int32)
-    block_ends[:nb] = torch.arange(nb, device=q.device, dtype=torch.int32) * cfg.d + (cfg.l - 1)
+    if compressed is None:
+        pos_embed, w1, b1, w2, b2 = phi_params
+        k_cmp, v_cmp = _PhiCompress.apply(kc_src.transpose(-1, -2), vc_src, pos_embed, w1, b1, w2, b2, cfg.l, cfg.d)
+    else:
+        k_cmp, v_cmp = compressed
+        if k_cmp.shape[-1] < nb or v_cmp.shape[2] < nb:
+            raise ValueError(f"compressed keys/values hold {k_cmp.shape[-1]}/{v_cmp.shape[2]} blocks, the sequence has {nb}")
+        nbp = _next_pow2(nb)
+        F = torch.nn.functional
+        k_cmp = F.pad(k_cmp[..., :nb].float(), (0, nbp - nb))
+        v_cmp = F.pad(v_cmp[:, :, :nb], (0, 0, 0, nbp - nb))
+    block_ends = _block_ends(k_cmp.shape[-1], nb, cfg.l, cfg.d, q.device)
     n_fixed = cfg.n_fixed if cfg.include_fixed_in_selection else 0
     if indices is None:
         indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale,
                                  nb, q_pos0)
     else:
         indices = indices.to(device=q.device, dtype=torch.int32).contiguous()
-    if q_pos0 == 0 and kw.shape[-1] == q.shape[2]:
-        out, gates, o_cmp, o_slc, o_win = _BranchesAndMix.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, k_slc, v_slc, indices,
-                                                                kw, vw, gate_logits, scale, cfg, (cfg.l, cfg.d, nb))
-    else:
-        o_cmp = CompressionAttention.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, scale, cfg, (cfg.l, cfg.d, nb), q_pos0)
-        o_slc = SelectionAttention.apply(q, k_slc, v_slc, indices, scale, cfg, q_pos0)
-        o_win = _sliding_with_offset(q, kw, vw, scale, cfg, q_pos0)
-        out, gates = _GateMix.apply(gate_logits, o_cmp, o_slc, o_win, cfg.gate_mode)
+    out, gates, o_cmp, o_slc, o_win = _BranchesAndMix.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, k_slc, v_slc, indices,
+                                                            kw, vw, gate_logits, scale, cfg, (cfg.l, cfg.d, nb), q_pos0,
+                                                            token_major_out)
     if return_info:
         return out, dict(indices=indices, gates=gates, k_cmp=k_cmp, v_cmp=v_cmp, block_ends=block_ends,
                          o_cmp=o_cmp, o_slc=o_slc, o_win=o_win)
@@ -481,8 +532,10 @@ class NSAAttention(torch.nn.Module):
         gate_logits = self.gate_mlp(hidden_states)                                               # [B,T,3H]
         out, info = nsa_layer(q, k_sel, v_sel, gate_logits, self._phi_params(), c,
                               kv_compress=kv(self.k_compress, self.v_compress),
-                              kv_sliding=kv(self.k_sliding, self.v_sliding), scale=self.scale, return_info=True)
-        y = self.o_proj(out.transpose(1, 2).reshape(B, T, H * dv))
+                              kv_sliding=kv(self.k_sliding, self.v_sliding), scale=self.scale, return_info=True,
+                              token_major_out=True)
+        # the mix epilogue wrote [B,T,H,dv] in memory: this reshape is a view, not the copy of nsa/kernels.py:2466-2467
+        y = self.o_proj(out.permute(0, 2, 1, 3).reshape(B, T, H * dv))
         y = self.dropout(y)
         attn_info = None
         if output_attentions:
@@ -645,7 +698,7 @@ class _Launcher:
                                          Tq, Tk, n, lp, dk, dv, scale, code, 0, 0, ptr(ws), nbytes, st)
             else:
                 if kind == "win":
-                    nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, 0)
+                    nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, 0, int(a["WINDOW_SIZE"]), 0)
                     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
                     rc = lib.nsa_sliding_bwd(ptr(Q), ptr(K), ptr(V), ptr(Out), ptr(dO), ptr(L), ptr(M), ptr(dQ), ptr(dK),
                                              ptr(dV), i64(strides), B, H, G, Tq, dk, dv, int(a["WINDOW_SIZE"]), scale, code,

@@ -49,8 +49,10 @@ def sliding_fwd(q, k, v, window: int, scale: float, generic: bool = False):
     return o, L, M
 
 
-def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float, row_delta=None, generic: bool = False):
-    """``row_delta``: the row sums dO.O [B,H,T] (fp32) when the caller has them, else they are computed here."""
+def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float, row_delta=None, generic: bool = False,
+                recompute: bool = False):
+    """``row_delta``: the row sums dO.O [B,H,T] (fp32) when the caller has them, else they are computed here.
+    ``recompute``: small scratch; the dQ kernel recomputes S and dP instead of taking dS from the dK/dV kernel."""
     dev = require_cuda(q, k, v, o, do, L, M)
     delta, dptr = _delta_ptr(row_delta, q)
     B, H, T, dk = q.shape
@@ -62,7 +64,7 @@ def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float, row_delta=None,
     dkey = torch.zeros(B, G, T, dk, device=dev, dtype=q.dtype)
     dval = torch.zeros(B, G, T, dv, device=dev, dtype=q.dtype)
     s = _fwd_strides(q, k, v, o, L, M) + list(dq.stride()) + list(dkey.stride()) + list(dval.stride())
-    nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, T, T, dk, dv, 0)
+    nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, T, T, dk, dv, 0, int(window), _flags(generic, recompute))
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
         check(lib.nsa_sliding_bwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq), ptr(dkey), ptr(dval),
@@ -71,8 +73,8 @@ def sliding_bwd(q, k, v, o, do, L, M, window: int, scale: float, row_delta=None,
     return dq, dkey, dval
 
 
-def _flags(generic: bool) -> int:
-    return _lib.FLAG_GENERIC if generic else 0
+def _flags(generic: bool, recompute: bool = False) -> int:
+    return (_lib.FLAG_GENERIC if generic else 0) | (_lib.FLAG_RECOMPUTE if recompute else 0)
 
 
 def _delta_ptr(row_delta, q):
@@ -103,7 +105,7 @@ def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None, q_pos0:
 
 
 def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=None, q_pos0: int = 0, row_delta=None,
-                 generic: bool = False):
+                 generic: bool = False, recompute: bool = False):
     bl, bd, bn = blocks if blocks is not None else (0, 0, 0)
     dev = require_cuda(q, k_cmp, v_cmp, block_ends, o, do, L, M)
     delta, dptr = _delta_ptr(row_delta, q)
@@ -117,7 +119,7 @@ def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=
     dkc = torch.zeros(B, G, NB, dk, device=dev, dtype=q.dtype)
     dvc = torch.zeros(B, G, NB, dv, device=dev, dtype=q.dtype)
     s = _fwd_strides(q, k_cmp, v_cmp, o, L, M) + list(dq.stride()) + list(dkc.stride()) + list(dvc.stride())
-    nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, T, NB, dk, dv, 1)
+    nbytes = lib.nsa_attn_bwd_workspace_bytes(B, H, G, T, NB, dk, dv, 1, 0, _flags(generic, recompute))
     ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
         check(lib.nsa_cmp_attn_bwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(do), ptr(L), ptr(M), ptr(dq),
@@ -142,6 +144,40 @@ def slc_fwd(q, k, v, indices_i32, l_prime: int, scale: float, q_pos0: int = 0, g
                               n, int(l_prime), dk, dv, float(scale), dtype_code(q), int(q_pos0), _flags(generic), ptr(ws),
                               nbytes, stream_ptr(dev)), "nsa_slc_fwd")
     return o, L, M
+
+
+def _mixed_empty(like: torch.Tensor, token_major: bool) -> torch.Tensor:
+    """Buffer for the mixed output of shape [B,H,T,dv]: contiguous, or (token_major) a [B,H,T,dv] view of a contiguous
+    [B,T,H,dv] buffer, which ``.permute(0, 2, 1, 3).reshape(B, T, H*dv)`` turns into o_proj's input without a copy."""
+    B, H, T, dv = like.shape
+    if not token_major:
+        return torch.empty(B, H, T, dv, device=like.device, dtype=like.dtype)
+    return torch.empty(B, T, H, dv, device=like.device, dtype=like.dtype).permute(0, 2, 1, 3)
+
+
+def slc_fwd_mix(q, k, v, indices_i32, l_prime: int, scale: float, gate_logits, o_cmp, o_win, gate_mode: str, q_pos0: int = 0,
+                token_major: bool = False, generic: bool = False):
+    """Selection forward with the layer's gate + mix as its epilogue -> (o_slc, L, M, out_mixed, gates [B,H,T,3])."""
+    dev = require_cuda(q, k, v, indices_i32, gate_logits, o_cmp, o_win)
+    B, H, Tq, dk = q.shape
+    G, Tkv, dv = k.shape[1], k.shape[-1], v.shape[-1]
+    assert indices_i32.dtype == torch.int32
+    o, L, M = _stats(q, dv)
+    s = _fwd_strides(q, k, v, o, L, M) + list(indices_i32.stride())
+    n = indices_i32.shape[-1]
+    lg = gate_logits.float().contiguous()
+    o_cmp, o_win = o_cmp.contiguous(), o_win.contiguous()
+    out = _mixed_empty(o, token_major)
+    gates = torch.empty(B, H, Tq, 3, device=dev, dtype=torch.float32)
+    mode = _lib.GATE_SOFTMAX if gate_mode == "softmax" else _lib.GATE_SIGMOID
+    nbytes = lib.nsa_slc_fwd_workspace_bytes(B, H, G, Tq, Tkv, dk, dv, n, int(l_prime), dtype_code(q), _flags(generic))
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        check(lib.nsa_slc_fwd_mix(ptr(q), ptr(k), ptr(v), ptr(indices_i32), ptr(o), ptr(L), ptr(M), i64(s), B, H, G, Tq, Tkv,
+                                  n, int(l_prime), dk, dv, float(scale), dtype_code(q), int(q_pos0), _flags(generic), ptr(lg),
+                                  ptr(o_cmp), ptr(o_win), ptr(out), ptr(gates), mode, 1 if token_major else 0, ptr(ws), nbytes,
+                                  stream_ptr(dev)), "nsa_slc_fwd_mix")
+    return o, L, M, out, gates
 
 
 def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float, q_pos0: int = 0, dq_addends=(), row_delta=None,
@@ -269,18 +305,19 @@ def eq9_scores(p_cmp, l: int, d: int, l_prime: int):
     return out
 
 
-def gate_mix_fwd(logits, o_cmp, o_slc, o_win, gate_mode: str):
-    """logits [B,T,3H]; branch outputs [B,H,T,dv] -> out [B,H,T,dv], gates [B,H,T,3] fp32."""
+def gate_mix_fwd(logits, o_cmp, o_slc, o_win, gate_mode: str, token_major: bool = False):
+    """logits [B,T,3H]; branch outputs [B,H,T,dv] -> out [B,H,T,dv] (token_major: backed by a [B,T,H,dv] buffer),
+    gates [B,H,T,3] fp32."""
     dev = require_cuda(logits, o_cmp, o_slc, o_win)
     B, H, T, dv = o_cmp.shape
     lg = logits.float().contiguous()
     o_cmp, o_slc, o_win = o_cmp.contiguous(), o_slc.contiguous(), o_win.contiguous()
-    out = torch.empty_like(o_cmp)
+    out = _mixed_empty(o_cmp, token_major)
     gates = torch.empty(B, H, T, 3, device=dev, dtype=torch.float32)
     mode = _lib.GATE_SOFTMAX if gate_mode == "softmax" else _lib.GATE_SIGMOID
     with torch.cuda.device(dev):
         check(lib.nsa_gate_mix_fwd(ptr(lg), ptr(o_cmp), ptr(o_slc), ptr(o_win), ptr(out), ptr(gates), B, H, T, dv, mode,
-                                   dtype_code(o_cmp), stream_ptr(dev)), "nsa_gate_mix_fwd")
+                                   dtype_code(o_cmp), 1 if token_major else 0, stream_ptr(dev)), "nsa_gate_mix_fwd")
     return out, gates
 
 
@@ -288,7 +325,10 @@ def gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, gate_mode: str, want_delta: b
     """-> (do_cmp, do_slc, do_win, dlogits [B,T,3H] fp32)."""
     dev = require_cuda(gates, o_cmp, o_slc, o_win, dout)
     B, H, T, dv = o_cmp.shape
-    dout = dout.contiguous()
+    # the upstream gradient is read as it lies when it is head-major or token-major ([B,T,H,dv] memory), copied otherwise
+    dout_tm = (not dout.is_contiguous()) and dout.permute(0, 2, 1, 3).is_contiguous()
+    if not dout_tm:
+        dout = dout.contiguous()
     o_cmp, o_slc, o_win = o_cmp.contiguous(), o_slc.contiguous(), o_win.contiguous()
     d0, d1, d2 = torch.empty_like(o_cmp), torch.empty_like(o_cmp), torch.empty_like(o_cmp)
     dlogits = torch.empty(B, T, 3 * H, device=dev, dtype=torch.float32)
@@ -296,6 +336,7 @@ def gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, gate_mode: str, want_delta: b
     delta = torch.empty(3, B, H, T, device=dev, dtype=torch.float32) if want_delta else None
     with torch.cuda.device(dev):
         check(lib.nsa_gate_mix_bwd_delta(ptr(gates), ptr(o_cmp), ptr(o_slc), ptr(o_win), ptr(dout), ptr(d0), ptr(d1), ptr(d2),
-                                         ptr(dlogits), ptr(delta), B, H, T, dv, mode, dtype_code(o_cmp), stream_ptr(dev)),
+                                         ptr(dlogits), ptr(delta), B, H, T, dv, mode, dtype_code(o_cmp), 1 if dout_tm else 0,
+                                         stream_ptr(dev)),
               "nsa_gate_mix_bwd")
     return (d0, d1, d2, dlogits, delta) if want_delta else (d0, d1, d2, dlogits)

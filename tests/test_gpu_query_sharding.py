@@ -23,8 +23,9 @@ def _setup(H, G, T, dk, dv, d_model, seed):
     return q, k, v, logits, do, phi
 
 
-@pytest.mark.parametrize("dk,dv,H,G,T,world", [(64, 64, 8, 2, 2048, 2), (192, 128, 16, 1, 4096, 4)])
-def test_query_slices_match_the_unsharded_layer(dk, dv, H, G, T, world):
+@pytest.mark.parametrize("dk,dv,H,G,T,world,balanced", [(64, 64, 8, 2, 2048, 2, False), (192, 128, 16, 1, 4096, 4, False),
+                                                        (192, 128, 16, 1, 4096, 3, True)])
+def test_query_slices_match_the_unsharded_layer(dk, dv, H, G, T, world, balanced):
     import nsa
     from nsa.kernels import nsa_layer
     from nsa._lib import lib
@@ -39,12 +40,18 @@ def test_query_slices_match_the_unsharded_layer(dk, dv, H, G, T, world):
         return out.detach(), info["indices"], [g_.detach().float() for g_ in grads]
 
     out_full, idx_full, g_full = run(q, logits, do, 0)
-    Tl = T // world
+    if balanced:
+        # the uneven, work-balanced slices of the long-context mode (early ranks get more positions)
+        from nsa.sharding import balanced_query_bounds
+        bounds = balanced_query_bounds(T, world, 512 + 16 * 64, 16)
+        assert len(set(b - a for a, b in zip(bounds, bounds[1:]))) > 1
+    else:
+        bounds = [r * (T // world) for r in range(world + 1)]
     outs, idxs, dqs = [], [], []
     sums = [torch.zeros_like(g_) for g_ in g_full[1:]]
     for r in range(world):
-        sl = slice(r * Tl, (r + 1) * Tl)
-        o_r, i_r, g_r = run(q[:, :, sl].contiguous(), logits[:, sl].contiguous(), do[:, :, sl].contiguous(), r * Tl)
+        sl = slice(bounds[r], bounds[r + 1])
+        o_r, i_r, g_r = run(q[:, :, sl].contiguous(), logits[:, sl].contiguous(), do[:, :, sl].contiguous(), bounds[r])
         outs.append(o_r); idxs.append(i_r); dqs.append(g_r[0])
         for acc, g_ in zip(sums, g_r[1:]):
             acc += g_

@@ -108,12 +108,16 @@ def test_sliding_backward_tensorcore_vs_oracle(dk, dv, H, G, T, w):
     o, L, M = ops.sliding_fwd(qd, kd, vd, w, scale)
     dq, dkey, dval = ops.sliding_bwd(qd, kd, vd, o, dod, L, M, w, scale)
     dq2, dkey2, dval2 = ops.sliding_bwd(qd, kd, vd, o, dod, L, M, w, scale)
+    # small-scratch variant: the dQ kernel recomputes S and dP instead of taking dS^T from the dK/dV kernel
+    dq3, dkey3, dval3 = ops.sliding_bwd(qd, kd, vd, o, dod, L, M, w, scale, recompute=True)
     torch.cuda.synchronize()
     _no_timeouts()
     assert torch.equal(dq, dq2) and torch.equal(dkey, dkey2) and torch.equal(dval, dval2)   # fixed summation order
+    assert torch.equal(dkey, dkey3) and torch.equal(dval, dval3)
     qo, ko, vo = (t.float().requires_grad_(True) for t in (q, k, v))
     g = torch.autograd.grad(O.sliding_window_attention(qo, ko, vo, w, scale), (qo, ko, vo), do.float())
     _grad_close(dq, g[0], "dq")
+    _grad_close(dq3, g[0], "dq (recomputed S, dP)")
     _grad_close(dkey.transpose(-1, -2), g[1], "dk")
     _grad_close(dval, g[2], "dv")
 
@@ -133,11 +137,14 @@ def test_compression_backward_tensorcore_vs_oracle(dk, dv, H, G, T):
     qd, kd, vd, dod, bed = (t.to(DEV) for t in (q, kc, vc, do, be))
     o, L, M = ops.cmp_attn_fwd(qd, kd, vd, bed, scale, blocks=(l, d, nb))
     dq, dkc, dvc = ops.cmp_attn_bwd(qd, kd, vd, bed, o, dod, L, M, scale, blocks=(l, d, nb))
+    dq3, dkc3, dvc3 = ops.cmp_attn_bwd(qd, kd, vd, bed, o, dod, L, M, scale, blocks=(l, d, nb), recompute=True)
     torch.cuda.synchronize()
     _no_timeouts()
+    assert torch.equal(dkc, dkc3) and torch.equal(dvc, dvc3)
     qo, ko, vo = (t.float().requires_grad_(True) for t in (q, kc, vc))
     g = torch.autograd.grad(O.compression_attention(qo, ko, vo, be, scale), (qo, ko, vo), do.float())
     _grad_close(dq, g[0], "dq")
+    _grad_close(dq3, g[0], "dq (recomputed S, dP)")
     _grad_close(dkc.transpose(-1, -2), g[1], "dk_cmp")
     _grad_close(dvc, g[2], "dv_cmp")
     assert (dkc[:, :, nb:] == 0).all() and (dvc[:, :, nb:] == 0).all()
@@ -396,3 +403,42 @@ def test_backward_takes_the_row_sums_from_the_caller():
 
     check(lambda: ops.sliding_fwd(q, k, v, 512, scale), lambda o, L, M, **kw: ops.sliding_bwd(q, k, v, o, do, L, M, 512, scale, **kw))
     check(lambda: ops.slc_fwd(q, k, v, idx, 64, scale), lambda o, L, M, **kw: ops.slc_bwd(q, k, v, idx, o, do, L, M, 64, scale, **kw))
+
+
+@pytest.mark.parametrize("dtype,dk,dv,H,G,T,n", [(torch.bfloat16, 192, 128, 16, 1, 1024, 16), (torch.bfloat16, 64, 64, 8, 2, 512, 6),
+                                                 (torch.bfloat16, 128, 128, 64, 1, 256, 4), (torch.float32, 48, 80, 6, 3, 333, 5)])
+@pytest.mark.parametrize("mode", ["sigmoid", "softmax"])
+def test_selection_forward_with_the_mix_epilogue(dtype, dk, dv, H, G, T, n, mode):
+    """nsa_slc_fwd_mix: the gate + mix done by the kernel that merges the selection partials (tensor-core path: the
+    bulk-copy merge, and the plain one when a group has more than 32 heads; stride-generic path: a separate pass inside
+    the entry point) gives bit for bit what the stand-alone pass gives on the same branch outputs, in the head-major and
+    in the token-major output layout; the gate/mix backward reads a token-major upstream gradient as it lies."""
+    from nsa import ops
+    gen = torch.Generator().manual_seed(15)
+    B = 2
+    rnd = lambda *s: torch.randn(*s, generator=gen).to(dtype).to(DEV)
+    q, k, v = rnd(B, H, T, dk), rnd(B, G, dk, T), rnd(B, G, T, dv)
+    oc, ow, do = rnd(B, H, T, dv), rnd(B, H, T, dv), rnd(B, H, T, dv)
+    lg = torch.randn(B, T, 3 * H, generator=gen).to(DEV)
+    lp = 64 if dtype == torch.bfloat16 else 16
+    idx = torch.randint(-1, (T + lp - 1) // lp, (B, G, T, n), generator=gen).to(DEV, torch.int32)
+    idx[:, :, 5] = -1
+    scale = dk ** -0.5
+    o_ref, L_ref, M_ref = ops.slc_fwd(q, k, v, idx, lp, scale)
+    out_ref, gates_ref = ops.gate_mix_fwd(lg, oc, o_ref, ow, mode)
+    for tm in (False, True):
+        o, L, M, out, gates = ops.slc_fwd_mix(q, k, v, idx, lp, scale, lg, oc, ow, mode, token_major=tm)
+        torch.cuda.synchronize()
+        assert out.shape == out_ref.shape and out.permute(0, 2, 1, 3).is_contiguous() == tm
+        assert torch.equal(o, o_ref) and torch.equal(L, L_ref) and torch.equal(M, M_ref)
+        assert torch.equal(gates, gates_ref)
+        assert torch.equal(out.contiguous(), out_ref)
+        out2, _ = ops.gate_mix_fwd(lg, oc, o_ref, ow, mode, token_major=tm)
+        assert torch.equal(out2.contiguous(), out_ref)
+    plain = ops.gate_mix_bwd(gates_ref, oc, o_ref, ow, do, mode, want_delta=True)
+    do_tm = do.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)       # same values, [B,T,H,dv] in memory
+    assert not do_tm.is_contiguous()
+    given = ops.gate_mix_bwd(gates_ref, oc, o_ref, ow, do_tm, mode, want_delta=True)
+    torch.cuda.synchronize()
+    _no_timeouts()
+    assert all(torch.equal(a, b_) for a, b_ in zip(plain, given))

@@ -120,3 +120,64 @@ def test_two_rank_sequence_all_gather_and_gradient_reduce_scatter():
     for r in range(2):
         ok_fwd, err, ok_len = ret[r]
         assert ok_fwd and ok_len and err < 1e-5
+
+
+def _compress_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nsa.sharding import all_gather_seq, owned_block_range, sharded_compress
+        B, G, T, dk, dv, l, d = 1, 2, 256, 16, 8, 32, 16
+        inp = O.make_inputs(B, 4, G, T, dk, dv, 32, l, seed=3)
+        phi = inp["phi"]
+        bounds = [0, 160, 256]                                  # uneven slices; 160 is a multiple of the stride
+        sizes = [bounds[i + 1] - bounds[i] for i in range(world)]
+        t0, t1 = bounds[rank], bounds[rank + 1]
+        k_loc = inp["k"][..., t0:t1].clone().requires_grad_(True)
+        v_loc = inp["v"][:, :, t0:t1].clone().requires_grad_(True)
+        k_full = all_gather_seq(k_loc, -1, None, sizes)
+        v_full = all_gather_seq(v_loc, 2, None, sizes)
+        fn = lambda keys, values: O.compress_tokens(keys, values, phi, l, d)[:2]
+        k_cmp, v_cmp = sharded_compress(k_full, v_full, fn, bounds, rank, l, d)
+        nb = (T - l) // d + 1
+        gen = torch.Generator().manual_seed(17)
+        wk, wv = torch.randn(B, G, dk, nb, generator=gen), torch.randn(B, G, nb, dv, generator=gen)
+        ((k_cmp * wk).sum() * (rank + 1) + (v_cmp * wv).sum() * (rank + 1)).backward()   # every rank's loss weighs differently
+        # single-process reference of the summed losses
+        kr, vr = inp["k"].clone().requires_grad_(True), inp["v"].clone().requires_grad_(True)
+        kc_ref, vc_ref, _, nb_ref = O.compress_tokens(kr.transpose(-1, -2), vr, phi, l, d)
+        tot = sum(r + 1 for r in range(world))
+        ((kc_ref[..., :nb] * wk).sum() * tot + (vc_ref[:, :, :nb] * wv).sum() * tot).backward()
+        ret[rank] = dict(
+            shape=tuple(k_cmp.shape) == (B, G, dk, nb) and tuple(v_cmp.shape) == (B, G, nb, dv) and nb == nb_ref,
+            fwd=max((k_cmp.detach() - kc_ref.detach()[..., :nb]).abs().max().item(), (v_cmp.detach() - vc_ref.detach()[:, :, :nb]).abs().max().item()),
+            gk=(k_loc.grad - kr.grad[..., t0:t1]).abs().max().item() / kr.grad.abs().max().item(),
+            gv=(v_loc.grad - vr.grad[:, :, t0:t1]).abs().max().item() / vr.grad.abs().max().item(),
+            owned=owned_block_range(bounds, rank, l, d, T))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_split_compression_matches_the_whole_sequence():
+    """Long-context mode: every rank compresses the blocks that start in its slice (reaching l - d tokens into the next
+    one), the compressed keys/values are all-gathered, and their gradients return through a reduce-scatter and the
+    owners' phi backward into the gradient of the gathered K/V."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_compress_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert ret[0]["owned"] == (0, 10) and ret[1]["owned"] == (10, 15)
+    for r in range(2):
+        assert ret[r]["shape"] and ret[r]["fwd"] < 1e-6 and ret[r]["gk"] < 1e-5 and ret[r]["gv"] < 1e-5, dict(ret[r])
+
+
+def test_owned_block_ranges_cover_every_block_once():
+    from nsa.sharding import balanced_query_bounds, owned_block_range
+    T, l, d = 65536, 32, 16
+    b = balanced_query_bounds(T, 8, 512 + 16 * 64, d)
+    r = [owned_block_range(b, i, l, d, T) for i in range(8)]
+    assert r[0][0] == 0 and r[-1][1] == (T - l) // d + 1 and all(x[1] == y[0] for x, y in zip(r, r[1:]))
+    with pytest.raises(ValueError):
+        owned_block_range([0, 100, 256], 0, l, d, 256)
