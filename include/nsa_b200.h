@@ -195,6 +195,33 @@ NSA_API int nsa_slc_bwd(const void* q, const void* k, const void* v, const int32
                 const void* dq_add0, const void* dq_add1, int flags, void* workspace, size_t workspace_bytes,
                 void* stream);
 
+/* Block-compression MLP phi, whole (NSAAttention.compress_tokens, nsa/kernels.py:2096-2102, 2119-2208):
+ *   k_cmp[i] = mean_{j<l} ( W2 relu(W1 [k_{i d + j} || pos_embed[j]] + b1) + b2 ),   v_cmp[i] = mean_{j<l} v_{i d + j}
+ * for the (T - l) / d + 1 blocks of the sequence.  k [B,G,dk,T] and v [B,G,T,dv] contiguous in dtype (the layouts of
+ * the attention entry points); pos_embed [l,l], w1 [U,dk+l], b1 [U], w2 [dk,U], b2 [dk] fp32 (b1, b2 may be NULL);
+ * k_cmp fp32 [B,G,dk,nbp] (fp32 because it decides the top-n; blocks >= n_blocks zero), k_cmp_lp an optional copy of
+ * it in dtype for nsa_cmp_attn_fwd (or NULL), v_cmp [B,G,nbp,dv] in dtype (rows >= n_blocks zero).  The first product
+ * K^T W1[:, :dk]^T holds exactly the products of an fp32 GEMM also for bf16 keys (three-term bf16 split of the weight,
+ * fp32 accumulation).  `saved` (nsa_cmp_phi_saved_bytes) receives what the backward needs; `workspace`
+ * (nsa_cmp_phi_workspace_bytes, backward = 0 / 1) is scratch.  The dense products run on cuBLAS, which is looked up
+ * when first needed (NSA_ERR_UNSUPPORTED if it cannot be loaded); a cuBLAS handle is created once per device. */
+NSA_API size_t nsa_cmp_phi_saved_bytes(int B, int G, int T, int l, int d, int U);
+NSA_API size_t nsa_cmp_phi_workspace_bytes(int B, int G, int T, int dk, int dv, int l, int d, int U, int nbp,
+                                           int dtype, int backward);
+NSA_API int nsa_cmp_phi_fwd(const void* k, const void* v, const float* pos_embed, const float* w1, const float* b1,
+                    const float* w2, const float* b2, float* k_cmp, void* k_cmp_lp, void* v_cmp, int B, int G,
+                    int T, int dk, int dv, int l, int d, int U, int nbp, int dtype, void* saved,
+                    size_t saved_bytes, void* workspace, size_t workspace_bytes, void* stream);
+/* Backward of phi.  dk_cmp [B,G,nbp,dk] and dv_cmp [B,G,nbp,dv] in dtype are the gradients of the compressed keys and
+ * values as nsa_cmp_attn_bwd writes them (block-major).  dk_out [B,G,T,dk] and dv_out [B,G,T,dv] in dtype are ADDED
+ * INTO, like the dK/dV of the attention entry points, so one pair of buffers can collect the gradient of a k/v that
+ * feeds several branches.  dpos [l,l], dw1 [U,dk+l], db1 [U], dw2 [dk,U], db2 [dk] fp32 are overwritten. */
+NSA_API int nsa_cmp_phi_bwd(const void* k, const float* pos_embed, const float* w1, const float* w2,
+                    const void* dk_cmp, const void* dv_cmp, const void* saved, size_t saved_bytes, void* dk_out,
+                    void* dv_out, float* dpos, float* dw1, float* db1, float* dw2, float* db2, int B, int G,
+                    int T, int dk, int dv, int l, int d, int U, int nbp, int dtype, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
 /* Pooling half of the block-compression MLP phi (NSAAttention.compress_tokens, nsa/kernels.py:
  * 2119-2208).  With A[t,:] = W1[:, :dk] k_t (a plain GEMM done by the caller) and the table
  * C[j,:] = W1[:, dk:] pos_embed[j] + b1, computes hbar[i,:] = mean_{j<l} relu(A[i*d+j,:] + C[j,:])
@@ -263,6 +290,56 @@ NSA_API int nsa_gate_mix_bwd_delta(const float* gates, const void* o_cmp, const 
                                    const void* dout, void* do_cmp, void* do_slc, void* do_win, float* dlogits,
                                    float* delta, int B, int H, int T, int dv, int gate_mode, int dtype,
                                    int dout_token_major, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * The whole layer between the q/k/v projections and the output projection: the wiring of NSAAttention.forward
+ * (nsa/kernels.py:2298-2463) and of its backward, which the reference leaves to autograd, as two calls.
+ *   forward   phi -> Eq. 8-11 scoring and top-n -> compressed, sliding-window and selected-block attention ->
+ *             gate + mix (epilogue of the selection branch)
+ *   backward  gate/mix -> the three branches (dQ summed in fp32 and rounded once) -> phi
+ * Tensors are contiguous in the layouts of the branch entry points: q [B,H,T,dk]; every k [B,G,dk,T]; every v
+ * [B,G,T,dv]; gate_logits [B,T,3H] fp32; out [B,H,T,dv] or, with out_token_major, [B,T,H,dv]; phi parameters fp32 as
+ * for nsa_cmp_phi_fwd.  The three branches may share one k/v pair (pass the same pointers) or have their own
+ * (the module's separate projections): k_slc/v_slc feed the selection branch, k_cmp_src/v_cmp_src the compression,
+ * k_win/v_win the sliding window.  indices_in (int32 [B,G,T,n], or NULL) replaces the layer's own block choice.
+ * `ctx` (nsa_layer_ctx_bytes) receives what the backward needs and what diagnostics want to look at: with
+ * offsets != NULL the query also writes the byte offset of every piece (enum below; NSA_CTX_PIECES + 1 values, the
+ * last one the total).  `workspace` (nsa_layer_workspace_bytes) is scratch, free again when the call returns.
+ * Backward: dq [B,H,T,dk] is overwritten; dk_* [B,G,T,dk] (time-major, like every dK of this library) and dv_*
+ * [B,G,T,dv] are ADDED INTO (zero them first; branches that share a k/v pair share its gradient buffers);
+ * dlogits [B,T,3H], dpos, dw1, db1, dw2, db2 fp32 are overwritten; dout has out's layout.
+ * The query position offset of the long-context mode is not available through these two calls (the sliding-window
+ * branch needs a key slice per rank); that mode composes the branch entry points. */
+typedef struct nsa_layer_desc {
+  int B, H, G, T, dk, dv;
+  int U;                 /* hidden width of phi (rows of w1); the reference uses 2*dk */
+  int l, d, l_prime, n;  /* compression block and stride, selection block, blocks per query */
+  int n_fixed;           /* 3 = initial + two local blocks forced (include_fixed_in_selection), 0 = none */
+  int window;
+  int gate_mode;         /* NSA_GATE_SIGMOID / NSA_GATE_SOFTMAX */
+  int dtype;             /* NSA_F32 / NSA_BF16, of q, k, v, out */
+  int out_token_major;
+  float scale;
+} nsa_layer_desc;
+enum nsa_layer_ctx_piece {
+  NSA_CTX_O_CMP = 0, NSA_CTX_L_CMP, NSA_CTX_M_CMP, NSA_CTX_O_SLC, NSA_CTX_L_SLC, NSA_CTX_M_SLC, NSA_CTX_O_WIN, NSA_CTX_L_WIN,
+  NSA_CTX_M_WIN, NSA_CTX_GATES /* [B,H,T,3] fp32 */, NSA_CTX_INDICES /* int32 [B,G,T,n], all-empty rows already replaced */,
+  NSA_CTX_K_CMP /* fp32 [B,G,dk,nbp] */, NSA_CTX_K_CMP_LP, NSA_CTX_V_CMP /* [B,G,nbp,dv] */, NSA_CTX_BLOCK_ENDS /* int32 [nbp] */,
+  NSA_CTX_PHI_SAVED, NSA_CTX_PIECES
+};
+NSA_API size_t nsa_layer_ctx_bytes(const nsa_layer_desc* desc, size_t* offsets);
+NSA_API size_t nsa_layer_workspace_bytes(const nsa_layer_desc* desc, int backward);
+NSA_API int nsa_layer_fwd(const nsa_layer_desc* desc, const void* q, const void* k_slc, const void* v_slc,
+                  const void* k_cmp_src, const void* v_cmp_src, const void* k_win, const void* v_win,
+                  const float* gate_logits, const float* pos_embed, const float* w1, const float* b1,
+                  const float* w2, const float* b2, const int32_t* indices_in, void* out, void* ctx,
+                  size_t ctx_bytes, void* workspace, size_t workspace_bytes, void* stream);
+NSA_API int nsa_layer_bwd(const nsa_layer_desc* desc, const void* q, const void* k_slc, const void* v_slc,
+                  const void* k_cmp_src, const void* k_win, const void* v_win, const float* pos_embed,
+                  const float* w1, const float* w2, const void* ctx, size_t ctx_bytes, const void* dout, void* dq,
+                  void* dk_slc, void* dv_slc, void* dk_cmp_src, void* dv_cmp_src, void* dk_win, void* dv_win,
+                  float* dlogits, float* dpos, float* dw1, float* db1, float* dw2, float* db2, void* workspace,
+                  size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

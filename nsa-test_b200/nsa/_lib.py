@@ -29,6 +29,17 @@ lib = ctypes.CDLL(LIB_PATH)
 _P = c_void_p
 _I64P = POINTER(c_int64)
 
+class LayerDesc(ctypes.Structure):
+    """nsa_layer_desc of include/nsa_b200.h."""
+    _fields_ = [(n_, c_int) for n_ in ("B", "H", "G", "T", "dk", "dv", "U", "l", "d", "l_prime", "n", "n_fixed", "window",
+                                       "gate_mode", "dtype", "out_token_major")] + [("scale", c_float)]
+
+
+# pieces of the layer's context buffer, in the order of enum nsa_layer_ctx_piece
+CTX_PIECES = ("o_cmp", "L_cmp", "M_cmp", "o_slc", "L_slc", "M_slc", "o_win", "L_win", "M_win", "gates", "indices", "k_cmp",
+              "k_cmp_lp", "v_cmp", "block_ends", "phi_saved")
+_DESCP = POINTER(LayerDesc)
+
 # name -> (restype, argtypes); mirrors include/nsa_b200.h declaration by declaration
 PROTOTYPES = {
     "nsa_last_error": (c_char_p, []),
@@ -47,6 +58,14 @@ PROTOTYPES = {
     "nsa_slc_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 9 + [c_float, c_int, c_int, c_int, _P, c_size_t, _P]),
     "nsa_slc_bwd_workspace_bytes": (c_size_t, [c_int] * 11),
     "nsa_slc_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 9 + [c_float, c_int, c_int, _P, _P, _P, c_int, _P, c_size_t, _P]),
+    "nsa_cmp_phi_saved_bytes": (c_size_t, [c_int] * 6),
+    "nsa_cmp_phi_workspace_bytes": (c_size_t, [c_int] * 11),
+    "nsa_cmp_phi_fwd": (c_int, [_P] * 10 + [c_int] * 10 + [_P, c_size_t, _P, c_size_t, _P]),
+    "nsa_cmp_phi_bwd": (c_int, [_P] * 7 + [c_size_t] + [_P] * 7 + [c_int] * 10 + [_P, c_size_t, _P]),
+    "nsa_layer_ctx_bytes": (c_size_t, [_DESCP, POINTER(c_size_t)]),
+    "nsa_layer_workspace_bytes": (c_size_t, [_DESCP, c_int]),
+    "nsa_layer_fwd": (c_int, [_DESCP] + [_P] * 16 + [c_size_t, _P, c_size_t, _P]),
+    "nsa_layer_bwd": (c_int, [_DESCP] + [_P] * 10 + [c_size_t] + [_P] * 14 + [_P, c_size_t, _P]),
     "nsa_phi_pool_fwd": (c_int, [_P, _P, _P, _I64P, _P, _P] + [c_int] * 10 + [_P]),
     "nsa_phi_pool_bwd": (c_int, [_P] * 7 + [c_int] * 9 + [_P]),
     "nsa_score_topn_workspace_bytes": (c_size_t, [c_int] * 12),

@@ -31,6 +31,7 @@ __all__ = [
 ]
 
 PAD_BLOCK_END = 999999  # block end of the padding blocks (nsa/kernels.py:2190)
+_USE_C_LAYER = True      # False: nsa_layer composes the branch entry points itself (what the long-context mode always does)
 _TILE_ROWS = 128         # query/key rows per tile of the tensor-core kernels
 _PAD_FROM = 2048         # ragged bf16 sequences at least this long are padded to a whole tile
 
@@ -242,6 +243,48 @@ class _BranchesAndMix(torch.autograd.Function):
                 dlogits.to(ctx.ldtype), None, None, None, None, None)
 
 
+class _LayerC(torch.autograd.Function):
+    """The whole layer through the library's nsa_layer_fwd / nsa_layer_bwd (one C call each way).
+
+    ``apply(q, k_slc, v_slc, k_cmp, v_cmp, k_win, v_win, gate_logits, pos_embed, w1, b1, w2, b2, desc, shared_kv, indices)``
+    -> (out, ctx); only ``out`` is differentiable.  ``shared_kv``: the three k/v pairs are one pair (their gradients are
+    accumulated in one pair of buffers inside the library and returned for k_slc/v_slc only)."""
+
+    @staticmethod
+    def forward(ctx, q, k_slc, v_slc, k_cmp, v_cmp, k_win, v_win, gate_logits, pos_embed, w1, b1, w2, b2, desc, shared_kv, indices):
+        f32 = lambda p: None if p is None else p.detach().float().contiguous()
+        phi = tuple(f32(p) for p in (pos_embed, w1, b1, w2, b2))
+        lg = gate_logits.detach().float().contiguous()
+        out, saved = ops.layer_fwd(desc, q, (k_slc, v_slc), (k_cmp, v_cmp), (k_win, v_win), lg, phi, indices)
+        ctx.save_for_backward(q, k_slc, v_slc, k_cmp, k_win, v_win, phi[0], phi[1], phi[3], saved)
+        ctx.desc, ctx.shared_kv = desc, shared_kv
+        ctx.pdtypes = (gate_logits.dtype, pos_embed.dtype, w1.dtype, w2.dtype, b1 is not None, b2 is not None)
+        ctx.mark_non_differentiable(saved)
+        return out, saved
+
+    @staticmethod
+    def backward(ctx, dout, _dsaved):
+        q, k_slc, v_slc, k_cmp, k_win, v_win, pos, w1, w2, saved = ctx.saved_tensors
+        desc = ctx.desc
+        tm = bool(desc.out_token_major)
+        # the upstream gradient in the layout the forward wrote: read as it lies when it has it, copied otherwise
+        if tm:
+            if not dout.permute(0, 2, 1, 3).is_contiguous():
+                dout = dout.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+        else:
+            dout = dout.contiguous()
+        dq, g_slc, g_cmp, g_win, dlogits, (dpos, dw1, db1, dw2, db2) = ops.layer_bwd(
+            desc, q, (k_slc, v_slc), (k_cmp, None), (k_win, v_win), (pos, w1, None, w2, None), saved, dout, ctx.shared_kv)
+        ldt, pdt, w1dt, w2dt, has_b1, has_b2 = ctx.pdtypes
+        tk = lambda g: g.transpose(-1, -2)            # dK comes back time-major; the keys are [B,G,dk,T]
+        if ctx.shared_kv:
+            gk = (tk(g_slc[0]), g_slc[1], None, None, None, None)
+        else:
+            gk = (tk(g_slc[0]), g_slc[1], tk(g_cmp[0]), g_cmp[1], tk(g_win[0]), g_win[1])
+        return (dq, *gk, dlogits.to(ldt), dpos.to(pdt), dw1.to(w1dt), db1.to(w1dt) if has_b1 else None, dw2.to(w2dt),
+                db2.to(w2dt) if has_b2 else None, None, None, None)
+
+
 # --------------------------------------------------------------------------------------------------
 # scoring functions (nsa/kernels.py:1920-2040)
 # --------------------------------------------------------------------------------------------------
@@ -268,75 +311,35 @@ def select_top_k_blocks_per_query_with_gqa(selection_scores: torch.Tensor, confi
 # --------------------------------------------------------------------------------------------------
 
 class _PhiCompress(torch.autograd.Function):
-    """Block compression phi (nsa/kernels.py:2119-2208) with fp32 outputs.
+    """Block compression phi (nsa/kernels.py:2119-2208) with fp32 compressed keys, through the library's
+    nsa_cmp_phi_fwd / nsa_cmp_phi_bwd.
 
     k_cmp[i] = W2 mean_j relu(W1k k_{id+j} + W1p pos_j + b1) + b2, which equals the reference's
-    mean_j MLP([k_j || pos_j]) because the second linear layer commutes with the mean.  The two dense
-    products are plain GEMMs (cuBLAS through torch, fp32); the relu + positional table + pooling in
-    between is one fused streaming kernel.
-    """
+    mean_j MLP([k_j || pos_j]) because the second linear layer commutes with the mean.  ``keys`` [B,G,T,dk] (usually the
+    transposed view of K as it lies, [B,G,dk,T]), ``values`` [B,G,T,dv]."""
 
     @staticmethod
     def forward(ctx, keys, values, pos_embed, w1, b1, w2, b2, l, d):
-        B, G, T, dk = keys.shape
-        nb = (T - l) // d + 1
-        assert nb >= 1, f"sequence length {T} shorter than one compression block ({l})"
-        nbp = _next_pow2(nb)
-        w1k, w1p = w1[:, :dk].float(), w1[:, dk:].float()
-        c = torch.addmm(b1.float(), pos_embed.float(), w1p.t())                     # [l,U]
-        kt = keys.transpose(-1, -2)                                                 # [B,G,dk,T], usually K as it lies
-        if keys.dtype == torch.bfloat16 and keys.is_cuda and kt.is_contiguous():
-            # fp32-exact product on the tensor cores: the keys are bf16 already, and a weight is the sum of three bf16
-            # terms (8 + 8 + 8 mantissa bits), so [k k k] x [hi; mid; lo] holds exactly the products of the fp32 GEMM,
-            # accumulated in fp32.  This product decides the top-n, so nothing is rounded away.
-            hi = w1k.to(torch.bfloat16)
-            r1 = w1k - hi.float()
-            mid = r1.to(torch.bfloat16)
-            lo = (r1 - mid.float()).to(torch.bfloat16)
-            w3 = torch.cat([hi, mid, lo], dim=1)                                    # [U, 3dk]
-            k3 = torch.cat([kt, kt, kt], dim=2).reshape(B * G, 3 * dk, T)
-            a = torch.bmm(k3.transpose(1, 2), w3.t().unsqueeze(0).expand(B * G, -1, -1),
-                          out_dtype=torch.float32).view(B, G, T, -1)
-        else:
-            a = torch.matmul(keys.float(), w1k.t())                                 # [B,G,T,U]
-        hbar, v_cmp = ops.phi_pool_fwd(a, c, values, l, d, nb, nbp)
-        kc = torch.matmul(hbar, w2.float().t()) + b2.float()                        # [B,G,nb,dk]
-        k_cmp = torch.zeros(B, G, dk, nbp, device=keys.device, dtype=torch.float32)
-        k_cmp[..., :nb] = kc.transpose(-1, -2)
-        ctx.save_for_backward(keys, a, c, hbar, pos_embed, w1, w2)
-        ctx.cfg = (l, d, nb, nbp, values.dtype)
-        return k_cmp, v_cmp
+        kt = keys.transpose(-1, -2)                                                 # [B,G,dk,T]
+        kt = kt if kt.is_contiguous() else kt.contiguous()
+        vals = values.to(kt.dtype).contiguous()
+        f32 = lambda p: None if p is None else p.detach().float().contiguous()
+        pe, w1f, b1f, w2f, b2f = f32(pos_embed), f32(w1), f32(b1), f32(w2), f32(b2)
+        k_cmp, v_cmp, saved = ops.cmp_phi_fwd(kt, vals, pe, w1f, b1f, w2f, b2f, l, d)
+        ctx.save_for_backward(kt, pe, w1f, w2f, saved)
+        ctx.cfg = (l, d, vals.shape[-1], values.dtype, pos_embed.dtype, w1.dtype, w2.dtype, b1 is not None, b2 is not None)
+        return k_cmp, v_cmp.to(values.dtype)
 
     @staticmethod
     def backward(ctx, dk_cmp, dv_cmp):
-        keys, a, c, hbar, pos_embed, w1, w2 = ctx.saved_tensors
-        l, d, nb, nbp, vdtype = ctx.cfg
-        B, G, T, dk = keys.shape
-        U = w1.shape[0]
-        dkc = dk_cmp[..., :nb].transpose(-1, -2).float().contiguous()              # [B,G,nb,dk]
-        dw2 = dkc.reshape(-1, dk).t() @ hbar.reshape(-1, U)
-        db2 = dkc.reshape(-1, dk).sum(0)
-        dhbar = torch.matmul(dkc, w2.float())                                       # [B,G,nb,U]
-        da, dc, dvals = ops.phi_pool_bwd(a, c, dhbar, dv_cmp, l, d, nb)
-        w1k, w1p = w1[:, :dk].float(), w1[:, dk:].float()
-        if keys.dtype in (torch.bfloat16, torch.float16):
-            # The key gradient leaves in the I/O precision anyway, so these two products run on the tensor cores
-            # from da rounded to it (fp32 accumulation, fp32 weight gradient).  The forward product stays fp32:
-            # it decides the top-n.  keys usually is the transposed view of K [B,G,dk,T], used as it lies.
-            da_lp = da.to(keys.dtype)
-            dkeys = torch.matmul(da_lp, w1k.to(keys.dtype))                         # [B,G,T,dk]
-            kt = keys.transpose(-1, -2)
-            kt = kt if kt.is_contiguous() else kt.contiguous()
-            dw1k = torch.bmm(kt.reshape(B * G, dk, T), da_lp.reshape(B * G, T, U),
-                             out_dtype=torch.float32).sum(0).t()                    # [U,dk]
-        else:
-            dkeys = torch.matmul(da, w1k)                                           # [B,G,T,dk]
-            dw1k = da.reshape(-1, U).t() @ keys.float().reshape(-1, dk)
-        dw1p = dc.t() @ pos_embed.float()
-        dpos = dc @ w1p
-        dw1 = torch.cat([dw1k, dw1p], dim=1)
-        return (dkeys.to(keys.dtype), dvals.to(vdtype), dpos.to(pos_embed.dtype), dw1.to(w1.dtype),
-                dc.sum(0).to(w1.dtype), dw2.to(w2.dtype), db2.to(w2.dtype), None, None)
+        kt, pe, w1f, w2f, saved = ctx.saved_tensors
+        l, d, dv_dim, vdtype, pdtype, w1dtype, w2dtype, has_b1, has_b2 = ctx.cfg
+        # block-major gradients in the I/O type, as the compressed attention's backward writes them
+        dkc = dk_cmp.transpose(-1, -2).to(kt.dtype).contiguous()                    # [B,G,nbp,dk]
+        dvc = dv_cmp.to(kt.dtype).contiguous()                                      # [B,G,nbp,dv]
+        dkeys, dvals, dpos, dw1, db1, dw2, db2 = ops.cmp_phi_bwd(kt, pe, w1f, w2f, dkc, dvc, saved, dv_dim, l, d)
+        return (dkeys, dvals.to(vdtype), dpos.to(pdtype), dw1.to(w1dtype), db1.to(w1dtype) if has_b1 else None,
+                dw2.to(w2dtype), db2.to(w2dtype) if has_b2 else None, None, None)
 
 
 class _GateMix(torch.autograd.Function):
@@ -430,8 +433,28 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
     kc_src, vc_src = kv_compress if kv_compress is not None else (k_slc, v_slc)
     kw, vw = kv_sliding if kv_sliding is not None else (k_slc, v_slc)
     T = kc_src.shape[-1]   # sequence length covered by the keys (== query rows unless q_pos0 shards the queries)
-    nb = (T - cfg.l) // cfg.d + 1
-    if compressed is None:
+    if q_pos0 == 0 and compressed is None and T == T_in and k_slc.shape[-1] == T_in and kw.shape[-1] == T_in and _USE_C_LAYER:
+        # the common case: the whole layer is one call into the library each way (nsa_layer_fwd / nsa_layer_bwd)
+        shared = kv_compress is None and kv_sliding is None
+        cont = lambda t: t if t.is_contiguous() else t.contiguous()
+        desc = ops.layer_desc(q, k_slc, v_slc, phi_params[1].shape[0], cfg.l, cfg.d, cfg.l_prime, cfg.n,
+                              cfg.n_fixed if cfg.include_fixed_in_selection else 0, cfg.w, cfg.gate_mode, scale, token_major_out)
+        forced = None if indices is None else indices.to(device=q.device, dtype=torch.int32).contiguous()
+        out, saved = _LayerC.apply(cont(q), cont(k_slc), cont(v_slc), cont(kc_src), cont(vc_src), cont(kw), cont(vw), gate_logits,
+                                   *phi_params, desc, shared, forced)
+        if not return_info:
+            return out
+        v_ = ops.layer_ctx_views(desc, saved)
+        return out, dict(indices=indices.to(torch.int32) if indices is not None else v_["indices"], gates=v_["gates"],
+                         k_cmp=v_["k_cmp"], v_cmp=v_["v_cmp"], block_ends=v_["block_ends"], o_cmp=v_["o_cmp"], o_slc=v_["o_slc"],
+                         o_win=v_["o_win"])
+    nb = max(0, (T - cfg.l) // cfg.d + 1)
+    if nb == 0:
+        # shorter than one compression block: only the reference's padding block exists (nsa/kernels.py:2137-2142,
+        # 2181-2186); the compressed branch outputs zero and every row's Eq. 8 falls back to block 0
+        k_cmp = q.new_zeros(q.shape[0], k_slc.shape[1], q.shape[-1], 1, dtype=torch.float32)
+        v_cmp = q.new_zeros(q.shape[0], k_slc.shape[1], 1, v_slc.shape[-1])
+    elif compressed is None:
         pos_embed, w1, b1, w2, b2 = phi_params
         k_cmp, v_cmp = _PhiCompress.apply(kc_src.transpose(-1, -2), vc_src, pos_embed, w1, b1, w2, b2, cfg.l, cfg.d)
     else:
@@ -511,11 +534,13 @@ class NSAAttention(torch.nn.Module):
         blocks whose block end is 999999."""
         c = self.config
         T = keys.shape[2]
-        nb = (T - c.l) // c.d + 1
-        k_cmp, v_cmp = _PhiCompress.apply(keys, values, *self._phi_params(), c.l, c.d)
-        block_ends = torch.full((k_cmp.shape[-1],), PAD_BLOCK_END, device=keys.device, dtype=torch.int32)
-        block_ends[:nb] = torch.arange(nb, device=keys.device, dtype=torch.int32) * c.d + (c.l - 1)
-        return k_cmp.to(keys.dtype), v_cmp, block_ends, nb
+        nb = max(0, (T - c.l) // c.d + 1)
+        if nb == 0:
+            k_cmp = keys.new_zeros(keys.shape[0], keys.shape[1], keys.shape[3], 1)
+            v_cmp = values.new_zeros(values.shape[0], values.shape[1], 1, values.shape[3])
+        else:
+            k_cmp, v_cmp = _PhiCompress.apply(keys, values, *self._phi_params(), c.l, c.d)
+        return k_cmp.to(keys.dtype), v_cmp, _block_ends(k_cmp.shape[-1], nb, c.l, c.d, keys.device).clone(), nb
 
     def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
                 output_attentions: bool = False) -> Tuple[torch.Tensor, Optional[Dict]]:

@@ -216,6 +216,56 @@ def slc_bwd(q, k, v, indices_i32, o, do, L, M, l_prime: int, scale: float, q_pos
 # phi pooling, scoring, gates
 # ------------------------------------------------------------------------------------------------
 
+def _next_pow2(n: int) -> int:
+    p = 1
+    while p < n:
+        p *= 2
+    return p
+
+
+def cmp_phi_fwd(k, v, pos_embed, w1, b1, w2, b2, l: int, d: int):
+    """Block compression phi through the C ABI.  k [B,G,dk,T], v [B,G,T,dv] (contiguous, one dtype); fp32 parameters.
+    -> k_cmp fp32 [B,G,dk,nbp], v_cmp [B,G,nbp,dv], and the buffer the backward needs."""
+    dev = require_cuda(k, v, pos_embed, w1, w2)
+    B, G, dk, T = k.shape
+    dv, U = v.shape[-1], w1.shape[0]
+    if T < l:
+        raise ValueError(f"sequence length {T} shorter than one compression block ({l})")
+    nb = (T - l) // d + 1
+    nbp = _next_pow2(nb)
+    code = dtype_code(k)
+    k_cmp = torch.empty(B, G, dk, nbp, device=dev, dtype=torch.float32)
+    v_cmp = torch.empty(B, G, nbp, dv, device=dev, dtype=k.dtype)
+    saved = torch.empty(lib.nsa_cmp_phi_saved_bytes(B, G, T, int(l), int(d), U), device=dev, dtype=torch.uint8)
+    nbytes = lib.nsa_cmp_phi_workspace_bytes(B, G, T, dk, dv, int(l), int(d), U, nbp, code, 0)
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        check(lib.nsa_cmp_phi_fwd(ptr(k), ptr(v), ptr(pos_embed), ptr(w1), ptr(b1), ptr(w2), ptr(b2), ptr(k_cmp), None, ptr(v_cmp),
+                                  B, G, T, dk, dv, int(l), int(d), U, nbp, code, ptr(saved), saved.numel(), ptr(ws), nbytes,
+                                  stream_ptr(dev)), "nsa_cmp_phi_fwd")
+    return k_cmp, v_cmp, saved
+
+
+def cmp_phi_bwd(k, pos_embed, w1, w2, dk_cmp, dv_cmp, saved, dv_dim: int, l: int, d: int):
+    """dk_cmp [B,G,nbp,dk], dv_cmp [B,G,nbp,dv] in k's dtype -> (dk [B,G,T,dk], dv [B,G,T,dv] in k's dtype; dpos, dw1, db1,
+    dw2, db2 fp32)."""
+    dev = require_cuda(k, pos_embed, w1, w2, dk_cmp, dv_cmp, saved)
+    B, G, dk, T = k.shape
+    U, nbp = w1.shape[0], dk_cmp.shape[2]
+    code = dtype_code(k)
+    dkeys = torch.zeros(B, G, T, dk, device=dev, dtype=k.dtype)
+    dvals = torch.zeros(B, G, T, dv_dim, device=dev, dtype=k.dtype)
+    f32 = lambda *s_: torch.empty(*s_, device=dev, dtype=torch.float32)
+    dpos, dw1, db1, dw2, db2 = f32(l, l), f32(U, dk + l), f32(U), f32(dk, U), f32(dk)
+    nbytes = lib.nsa_cmp_phi_workspace_bytes(B, G, T, dk, dv_dim, int(l), int(d), U, nbp, code, 1)
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        check(lib.nsa_cmp_phi_bwd(ptr(k), ptr(pos_embed), ptr(w1), ptr(w2), ptr(dk_cmp), ptr(dv_cmp), ptr(saved), saved.numel(),
+                                  ptr(dkeys), ptr(dvals), ptr(dpos), ptr(dw1), ptr(db1), ptr(dw2), ptr(db2), B, G, T, dk, dv_dim,
+                                  int(l), int(d), U, nbp, code, ptr(ws), nbytes, stream_ptr(dev)), "nsa_cmp_phi_bwd")
+    return dkeys, dvals, dpos, dw1, db1, dw2, db2
+
+
 def phi_pool_fwd(a, c, v, l: int, d: int, n_blocks: int, nbp: int):
     """a [B,G,T,U] fp32, c [l,U] fp32, v [B,G,T,dv] -> hbar [B,G,n_blocks,U] fp32, v_cmp [B,G,nbp,dv] (zero padded)."""
     dev = require_cuda(a, c, v)
@@ -340,3 +390,93 @@ def gate_mix_bwd(gates, o_cmp, o_slc, o_win, dout, gate_mode: str, want_delta: b
                                          stream_ptr(dev)),
               "nsa_gate_mix_bwd")
     return (d0, d1, d2, dlogits, delta) if want_delta else (d0, d1, d2, dlogits)
+
+
+# ------------------------------------------------------------------------------------------------
+# the whole layer through nsa_layer_fwd / nsa_layer_bwd
+# ------------------------------------------------------------------------------------------------
+
+def layer_desc(q, k, v, U: int, l: int, d: int, l_prime: int, n: int, n_fixed: int, window: int, gate_mode: str, scale: float,
+               token_major: bool) -> "_lib.LayerDesc":
+    B, H, T, dk = q.shape
+    return _lib.LayerDesc(B=B, H=H, G=k.shape[1], T=T, dk=dk, dv=v.shape[-1], U=int(U), l=int(l), d=int(d), l_prime=int(l_prime),
+                          n=int(n), n_fixed=int(n_fixed), window=int(window),
+                          gate_mode=_lib.GATE_SOFTMAX if gate_mode == "softmax" else _lib.GATE_SIGMOID, dtype=dtype_code(q),
+                          out_token_major=1 if token_major else 0, scale=float(scale))
+
+
+def layer_ctx_views(desc, ctx: torch.Tensor):
+    """Named tensors inside the layer's context buffer (views, no copies)."""
+    import ctypes
+    offs = (ctypes.c_size_t * (len(_lib.CTX_PIECES) + 1))()
+    lib.nsa_layer_ctx_bytes(ctypes.byref(desc), offs)
+    B, H, G, T, dk, dv, n = desc.B, desc.H, desc.G, desc.T, desc.dk, desc.dv, desc.n
+    dt = torch.bfloat16 if desc.dtype == _lib.BF16 else torch.float32
+    nb = (T - desc.l) // desc.d + 1 if T >= desc.l else 0
+    nbp = _next_pow2(max(nb, 1))
+    shapes = dict(o_cmp=((B, H, T, dv), dt), L_cmp=((B, H, T), torch.float32), M_cmp=((B, H, T), torch.float32),
+                  o_slc=((B, H, T, dv), dt), L_slc=((B, H, T), torch.float32), M_slc=((B, H, T), torch.float32),
+                  o_win=((B, H, T, dv), dt), L_win=((B, H, T), torch.float32), M_win=((B, H, T), torch.float32),
+                  gates=((B, H, T, 3), torch.float32), indices=((B, G, T, n), torch.int32),
+                  k_cmp=((B, G, dk, nbp), torch.float32), k_cmp_lp=((B, G, dk, nbp), dt), v_cmp=((B, G, nbp, dv), dt),
+                  block_ends=((nbp,), torch.int32))
+    out = {}
+    for i, name in enumerate(_lib.CTX_PIECES):
+        if name not in shapes:
+            continue
+        shape, dtype = shapes[name]
+        numel = 1
+        for s_ in shape:
+            numel *= s_
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        out[name] = ctx[offs[i]:offs[i] + nbytes].view(dtype).view(shape)
+    return out
+
+
+def _mixed_out(desc, q):
+    if desc.out_token_major:
+        return torch.empty(desc.B, desc.T, desc.H, desc.dv, device=q.device, dtype=q.dtype).permute(0, 2, 1, 3)
+    return torch.empty(desc.B, desc.H, desc.T, desc.dv, device=q.device, dtype=q.dtype)
+
+
+def layer_fwd(desc, q, kv_slc, kv_cmp, kv_win, gate_logits, phi, indices=None):
+    """-> (out [B,H,T,dv] (token-major memory when the descriptor says so), ctx).  kv_* = (k [B,G,dk,T], v [B,G,T,dv])."""
+    import ctypes
+    dev = require_cuda(q, gate_logits)
+    ctx_bytes = lib.nsa_layer_ctx_bytes(ctypes.byref(desc), None)
+    if ctx_bytes == 0:
+        raise _lib.NSAKernelError(f"nsa_layer_ctx_bytes: {lib.nsa_last_error().decode()}")
+    ctx = torch.empty(ctx_bytes, device=dev, dtype=torch.uint8)
+    nbytes = lib.nsa_layer_workspace_bytes(ctypes.byref(desc), 0)
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    out = _mixed_out(desc, q)
+    pos, w1, b1, w2, b2 = phi
+    with torch.cuda.device(dev):
+        check(lib.nsa_layer_fwd(ctypes.byref(desc), ptr(q), ptr(kv_slc[0]), ptr(kv_slc[1]), ptr(kv_cmp[0]), ptr(kv_cmp[1]), ptr(kv_win[0]),
+                                ptr(kv_win[1]), ptr(gate_logits), ptr(pos), ptr(w1), ptr(b1), ptr(w2), ptr(b2), ptr(indices), ptr(out),
+                                ptr(ctx), ctx_bytes, ptr(ws), nbytes, stream_ptr(dev)), "nsa_layer_fwd")
+    return out, ctx
+
+
+def layer_bwd(desc, q, kv_slc, kv_cmp, kv_win, phi, ctx, dout, shared_kv: bool):
+    """-> dq, (dk, dv) per stream in the order selection, compression, window (time-major dK [B,G,T,dk]; with shared_kv
+    the three are one pair of buffers), dlogits fp32, (dpos, dw1, db1, dw2, db2) fp32."""
+    import ctypes
+    dev = require_cuda(q, ctx, dout)
+    B, H, G, T, dk, dv, U, l = desc.B, desc.H, desc.G, desc.T, desc.dk, desc.dv, desc.U, desc.l
+    dq = torch.empty_like(q)
+    mk = lambda: (torch.zeros(B, G, T, dk, device=dev, dtype=q.dtype), torch.zeros(B, G, T, dv, device=dev, dtype=q.dtype))
+    g_slc = mk()
+    g_cmp, g_win = (g_slc, g_slc) if shared_kv else (mk(), mk())
+    f32 = lambda *s_: torch.empty(*s_, device=dev, dtype=torch.float32)
+    dlogits = f32(B, T, 3 * H)
+    dpos, dw1, db1, dw2, db2 = f32(l, l), f32(U, dk + l), f32(U), f32(dk, U), f32(dk)
+    nbytes = lib.nsa_layer_workspace_bytes(ctypes.byref(desc), 1)
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    pos, w1, b1, w2, b2 = phi
+    with torch.cuda.device(dev):
+        check(lib.nsa_layer_bwd(ctypes.byref(desc), ptr(q), ptr(kv_slc[0]), ptr(kv_slc[1]), ptr(kv_cmp[0]), ptr(kv_win[0]), ptr(kv_win[1]),
+                                ptr(pos), ptr(w1), ptr(w2), ptr(ctx), ctx.numel(), ptr(dout), ptr(dq), ptr(g_slc[0]), ptr(g_slc[1]),
+                                ptr(g_cmp[0]), ptr(g_cmp[1]), ptr(g_win[0]), ptr(g_win[1]), ptr(dlogits), ptr(dpos), ptr(dw1), ptr(db1),
+                                ptr(dw2), ptr(db2), ptr(ws), nbytes, stream_ptr(dev)), "nsa_layer_bwd")
+    return dq, g_slc, g_cmp, g_win, dlogits, (dpos, dw1, db1, dw2, db2)

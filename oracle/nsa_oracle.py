@@ -181,8 +181,13 @@ def compress_tokens(keys: torch.Tensor, values: torch.Tensor, phi: PhiParams, l:
     """
     B, G, T, dk = keys.shape
     dv = values.shape[-1]
-    nb = (T - l) // d + 1
+    nb = max(0, (T - l) // d + 1)
     nbp = next_pow2(nb)
+    if nb == 0:
+        # a sequence shorter than one block: the reference's loop runs zero times and only the padding block is left
+        # (nsa/kernels.py:2137-2142, 2181-2186); every row then falls back to block 0 in Eq. 8
+        return (torch.zeros(B, G, dk, nbp, dtype=keys.dtype), torch.zeros(B, G, nbp, dv, dtype=values.dtype),
+                torch.full((nbp,), PAD_BLOCK_END, dtype=torch.int32), 0)
     kb = keys.unfold(2, l, d)[:, :, :nb].permute(0, 1, 2, 4, 3)             # [B,G,nb,l,dk]
     vb = values.unfold(2, l, d)[:, :, :nb].permute(0, 1, 2, 4, 3)           # [B,G,nb,l,dv]
     pos = phi.pos_embed.to(keys.dtype).view(1, 1, 1, l, l).expand(B, G, nb, l, l)

@@ -455,6 +455,7 @@ def test_cpu_tensors_are_rejected(nsa_mod):
     (777, 96, 80, 6, 3, 5, 100, True, "sigmoid"),       # ragged T (padded-block n_sel), head dims off the tile sizes
     (333, 64, 64, 4, 2, 3, 50, False, "softmax"),       # no forced blocks, softmax gates
     (40, 32, 48, 2, 1, 16, 512, True, "sigmoid"),       # barely one compression block, window and n beyond T
+    (20, 32, 32, 4, 2, 4, 8, True, "sigmoid"),          # shorter than one compression block: only the padding block exists
 ])
 def test_layer_fp32_odd_shapes(nsa_mod, T, dk, dv, H, G, n, w, include_fixed, gate_mode):
     """The generic kernels on shapes off every tile size, against the oracle layer (fp32)."""

@@ -442,3 +442,54 @@ def test_selection_forward_with_the_mix_epilogue(dtype, dk, dv, H, G, T, n, mode
     torch.cuda.synchronize()
     _no_timeouts()
     assert all(torch.equal(a, b_) for a, b_ in zip(plain, given))
+
+
+@pytest.mark.parametrize("shared_kv", [True, False])
+def test_layer_entry_points_match_the_composed_branch_calls(shared_kv):
+    """nsa_layer_fwd / nsa_layer_bwd (one C call each way) against the same layer composed from the branch entry points
+    (what the long-context mode runs): identical kernels, so outputs, dQ and the gate gradient agree bit for bit; dK/dV
+    are accumulated in one buffer per k/v pair inside the library (one bf16 rounding per branch) and agree within it."""
+    import nsa
+    import nsa.kernels as K
+    c = dict(B=1, H=8, G=2, T=1024, dk=64, dv=64, d_model=32, l=32, d=16, l_prime=64, n=8, w=200)
+    inp = O.make_inputs(c["B"], c["H"], c["G"], c["T"], c["dk"], c["dv"], c["d_model"], c["l"], seed=19, block_offset_std=0.5,
+                        dtype=torch.bfloat16)
+    cfg = nsa.NSAConfig(d_model=c["d_model"], head_dim_qk=c["dk"], head_dim_v=c["dv"], l=c["l"], d=c["d"], l_prime=c["l_prime"],
+                        n=c["n"], w=c["w"], n_heads=c["H"], n_kv_groups=c["G"])
+    gen = torch.Generator().manual_seed(4)
+    logits = torch.randn(1, c["T"], 3 * c["H"], generator=gen).to(DEV)
+    extra = None
+    if not shared_kv:
+        mk = lambda: (torch.randn(1, c["G"], c["dk"], c["T"], generator=gen).bfloat16().to(DEV),
+                      torch.randn(1, c["G"], c["T"], c["dv"], generator=gen).bfloat16().to(DEV))
+        extra = (mk(), mk())
+
+    def run(use_c):
+        K._USE_C_LAYER = use_c
+        try:
+            q, k, v = (inp[x].bfloat16().to(DEV).requires_grad_(True) for x in ("q", "k", "v"))
+            phi = [p.to(DEV).requires_grad_(True) for p in (inp["phi"].pos_embed, inp["phi"].w1, inp["phi"].b1, inp["phi"].w2, inp["phi"].b2)]
+            lg = logits.clone().requires_grad_(True)
+            kw = {}
+            leaves = [q, k, v, lg] + phi
+            if extra is not None:
+                kv = [tuple(t.clone().requires_grad_(True) for t in pair) for pair in extra]
+                kw = dict(kv_compress=kv[0], kv_sliding=kv[1])
+                leaves += [kv[0][0], kv[0][1], kv[1][0], kv[1][1]]
+            out, info = K.nsa_layer(q, k, v, lg, tuple(phi), cfg, return_info=True, **kw)
+            grads = torch.autograd.grad(out, leaves, inp["do"].bfloat16().to(DEV))
+            return out, info, grads
+        finally:
+            K._USE_C_LAYER = True
+
+    out_c, info_c, g_c = run(True)
+    out_p, info_p, g_p = run(False)
+    torch.cuda.synchronize()
+    _no_timeouts()
+    assert torch.equal(info_c["indices"], info_p["indices"])
+    for key in ("o_cmp", "o_slc", "o_win", "gates"):
+        assert torch.equal(info_c[key], info_p[key]), key
+    assert torch.equal(out_c, out_p)
+    assert torch.equal(g_c[0], g_p[0]) and torch.equal(g_c[3], g_p[3])          # dq, dlogits
+    for a, b_ in zip(g_c[1:3] + g_c[4:], g_p[1:3] + g_p[4:]):
+        _grad_close(a, b_.float().cpu(), "dk / dv / phi gradient")

@@ -78,8 +78,9 @@ def oracle_layer_with_grads(inp, cfg, dtype=torch.float32, include_fixed=True):
     gp2 = O.GateParams(*plist[5:])
     r = O.nsa_layer(q, k, v, inp["x"], phi2, gp2, l=cfg["l"], d=cfg["d"], l_prime=cfg["l_prime"], n=cfg["n"], w=cfg["w"],
                     gate_mode=cfg.get("gate_mode", "sigmoid"), include_fixed=include_fixed)
-    grads = torch.autograd.grad(r["out"], [q, k, v] + plist, inp["do"])
-    return r, grads
+    leaves = [q, k, v] + plist
+    grads = torch.autograd.grad(r["out"], leaves, inp["do"], allow_unused=True)   # phi is unused when T < l
+    return r, [torch.zeros_like(x) if g is None else g for g, x in zip(grads, leaves)]
 
 
 GRAD_NAMES = ["dq", "dk", "dv", "dpos", "dw1", "db1", "dw2", "db2", "dgw1", "dgb1", "dgw2", "dgb2"]
@@ -98,8 +99,9 @@ def gpu_layer_with_grads(nsa_mod, c, inp, dtype, dev="cuda", gate_mode="sigmoid"
     lin = torch.nn.functional.linear
     logits = lin(torch.relu(lin(inp["x"].to(dev), params[5], params[6])), params[7], params[8])
     out, info = nsa_layer(q, k, v, logits, tuple(params[:5]), cfg, return_info=True, indices=indices)
-    grads = torch.autograd.grad(out, [q, k, v] + params, inp["do"].to(dev, dtype))
-    return out, info, grads
+    leaves = [q, k, v] + params
+    grads = torch.autograd.grad(out, leaves, inp["do"].to(dev, dtype), allow_unused=True)
+    return out, info, [torch.zeros_like(x) if g is None else g for g, x in zip(grads, leaves)]
 
 
 def check_layer_against_oracle(where, nsa_mod, c, inp, dtype, *, gate_mode="sigmoid", include_fixed=True, dev="cuda"):
@@ -140,10 +142,10 @@ def check_layer_against_oracle(where, nsa_mod, c, inp, dtype, *, gate_mode="sigm
             assert err < tol, f"{where}: db2 {err} vs {tol}"
         else:
             # weight gradients are fp32 tensors on both sides; with bf16 activations they carry the activations' rounding
-            err, scale_ = max_abs(a, b), b.abs().max().item() + 1e-8
+            err, scale_ = max_abs(a, b), b.abs().max().item() + 1e-12
             tol = (3e-2 if bf16 else 1e-3) * scale_
             PARITY_LOG.append((where, name + "[oracle ids]", err, scale_, tol))
-            assert err < tol, f"{where}: {name} max-abs {err:.4g} exceeds {tol:.4g}"
+            assert err <= tol, f"{where}: {name} max-abs {err:.4g} exceeds {tol:.4g}"
     return info, mism, r
 
 
