@@ -129,12 +129,11 @@ def make_device_inputs(T, dev, seed, B=1):
 
 def layer_step(inp, params, cfg, world, before_backward=None):
     """One forward + backward of the layer; returns a scalar tensor summarising the result."""
-    from nsa.kernels import nsa_layer
-    lin = torch.nn.functional.linear
+    from nsa.kernels import _GateMLP, nsa_layer
     q = inp["q"].detach().requires_grad_(True)
     k = inp["k"].detach().requires_grad_(True)
     v = inp["v"].detach().requires_grad_(True)
-    logits = lin(torch.relu(lin(inp["x"], params["gw1"], params["gb1"])), params["gw2"], params["gb2"])
+    logits = _GateMLP.apply(inp["x"], params["gw1"], params["gb1"], params["gw2"], params["gb2"])    # gate MLP through the library
     phi = (params["pos_embed"], params["w1"], params["b1"], params["w2"], params["b2"])
     out = nsa_layer(q, k, v, logits, phi, cfg)
     plist = list(params.values())
@@ -150,13 +149,13 @@ def layer_step(inp, params, cfg, world, before_backward=None):
 def layer_step_query_sharded(inp, params, cfg, world, before_backward=None):
     """Long-context mode: `inp` holds this rank's slice of the positions; K/V are all-gathered inside the layer and
     their gradients come back reduce-scattered (nsa.sharding.query_sharded_layer)."""
+    from nsa.kernels import _GateMLP
     from nsa.sharding import allreduce_grads, query_sharded_layer
     bounds = inp.get("bounds")
-    lin = torch.nn.functional.linear
     q = inp["q"].detach().requires_grad_(True)
     k = inp["k"].detach().requires_grad_(True)
     v = inp["v"].detach().requires_grad_(True)
-    logits = lin(torch.relu(lin(inp["x"], params["gw1"], params["gb1"])), params["gw2"], params["gb2"])
+    logits = _GateMLP.apply(inp["x"], params["gw1"], params["gb1"], params["gw2"], params["gb2"])
     phi = (params["pos_embed"], params["w1"], params["b1"], params["w2"], params["b2"])
     out = query_sharded_layer(q, k, v, logits, phi, cfg, bounds=bounds)
     plist = list(params.values())

@@ -284,6 +284,18 @@ NSA_API int nsa_gate_mix_bwd(const float* gates, const void* o_cmp, const void* 
                      int B, int H, int T, int dv, int gate_mode, int dtype, int dout_token_major,
                      void* stream);
 
+/* Branch-gate MLP (nsa/kernels.py:2105-2109): logits = W2 relu(W1 x + b1) + b2 for N = B*T tokens.  x [N,Dm], w1 [D2,Dm],
+ * b1 [D2], w2 [O,D2], b2 [O] (O = 3H) in dtype (biases may be NULL); logits [N,O] fp32, the input of the gate/mix entry
+ * points; hidden [N,D2] in dtype receives the activation the backward needs.  GEMMs on cuBLAS (see nsa_cmp_phi_fwd).
+ * Backward: dlogits [N,O] fp32 -> dw1 [D2,Dm], db1 [D2], dw2 [O,D2], db2 [O] fp32 (overwritten) and, when dx != NULL, dx
+ * [N,Dm] in dtype; scratch of nsa_gate_mlp_workspace_bytes(..., backward = 1) bytes. */
+NSA_API size_t nsa_gate_mlp_workspace_bytes(int64_t N, int Dm, int D2, int O, int dtype, int backward);
+NSA_API int nsa_gate_mlp_fwd(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* hidden,
+                     float* logits, int64_t N, int Dm, int D2, int O, int dtype, void* stream);
+NSA_API int nsa_gate_mlp_bwd(const void* x, const void* w1, const void* w2, const void* hidden, const float* dlogits,
+                     void* dx, float* dw1, float* db1, float* dw2, float* db2, int64_t N, int Dm, int D2, int O,
+                     int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Same, and also writes delta [3][B*H*T] (fp32): the row sums dO_b . O_b of the three branches (dO_b = g_b dO), which
  * the branch backward kernels need.  Handing them over as `row_delta` saves each backward its own pass over O and dO. */
 NSA_API int nsa_gate_mix_bwd_delta(const float* gates, const void* o_cmp, const void* o_slc, const void* o_win,

@@ -130,12 +130,31 @@ __global__ void rows_to_f32_kernel(const T* __restrict__ in, float* __restrict__
   const int64_t bg = i / ((int64_t)W * nb_out);
   out[i] = r < nb ? Elem<T>::ld(in + (bg * nbp + r) * W + c) : 0.f;
 }
-// out[c] = sum over rows of in[row, c], rows added in order (one thread per column: deterministic, tiny)
-__global__ void colsum_kernel(const float* __restrict__ in, int64_t rows, int W, float* __restrict__ out) {
+// Column sums out[c] = sum over rows of in[row, c] in a fixed order: 1024-row chunks are summed by 8 row lanes per column
+// (stage 1, partial sums to scratch), the chunks then one after the other (stage 2).
+constexpr int kColsumChunk = 1024;
+template <typename T>
+__global__ void colsum_stage1_kernel(const T* __restrict__ in, int64_t rows, int W, float* __restrict__ part) {
+  __shared__ float sh[8][32];
+  const int c = blockIdx.x * 32 + (threadIdx.x & 31), rl = threadIdx.x >> 5;
+  const int64_t r0 = (int64_t)blockIdx.y * kColsumChunk, r1 = min(rows, r0 + kColsumChunk);
+  float acc = 0.f;
+  if (c < W)
+    for (int64_t r = r0 + rl; r < r1; r += 8) acc += Elem<T>::ld(in + r * W + c);
+  sh[rl][threadIdx.x & 31] = acc;
+  __syncthreads();
+  if (rl == 0 && c < W) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += sh[i][threadIdx.x & 31];
+    part[(int64_t)blockIdx.y * W + c] = t;
+  }
+}
+__global__ void colsum_stage2_kernel(const float* __restrict__ part, int chunks, int W, float* __restrict__ out) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= W) return;
   float acc = 0.f;
-  for (int64_t r = 0; r < rows; ++r) acc += in[r * W + c];
+  for (int i = 0; i < chunks; ++i) acc += part[(int64_t)i * W + c];
   out[c] = acc;
 }
 template <typename T>
@@ -181,6 +200,14 @@ __global__ void table_grads_kernel(const float* __restrict__ dc, const float* __
 
 unsigned blocks_for(int64_t n) { return (unsigned)((n + 255) / 256); }
 
+size_t colsum_scratch_bytes(int64_t rows, int W) { return al256((size_t)((rows + kColsumChunk - 1) / kColsumChunk) * W * sizeof(float)); }
+template <typename T>
+void colsum(const T* in, int64_t rows, int W, float* out, float* scratch, cudaStream_t st) {
+  const int chunks = (int)((rows + kColsumChunk - 1) / kColsumChunk);
+  colsum_stage1_kernel<T><<<dim3((W + 31) / 32, chunks), 256, 0, st>>>(in, rows, W, scratch);
+  colsum_stage2_kernel<<<blocks_for(W), 256, 0, st>>>(scratch, chunks, W, out);
+}
+
 struct SavedLayout { size_t o_a, o_c, o_hbar, total; };
 SavedLayout saved_layout(int B, int G, int T, int l, int d, int U) {
   const size_t BG = (size_t)B * G, nb = T >= l ? (size_t)(T - l) / d + 1 : 0;
@@ -191,7 +218,7 @@ SavedLayout saved_layout(int B, int G, int T, int l, int d, int U) {
   s.total = s.o_hbar + al256(BG * nb * U * sizeof(float));
   return s;
 }
-struct BwdLayout { size_t o_dkc, o_dhbar, o_dvc, o_da, o_dalp, o_dcpart, o_dc, o_dvt, o_w1k, total; };
+struct BwdLayout { size_t o_dkc, o_dhbar, o_dvc, o_da, o_dalp, o_dcpart, o_dc, o_dvt, o_w1k, o_cs, total; };
 BwdLayout bwd_layout(int B, int G, int T, int dk, int dv, int l, int d, int U, int nbp, int dtype) {
   const size_t BG = (size_t)B * G, nb = T >= l ? (size_t)(T - l) / d + 1 : 0, es = dtype == NSA_BF16 ? 2 : 4;
   BwdLayout w;
@@ -205,6 +232,7 @@ BwdLayout bwd_layout(int B, int G, int T, int dk, int dv, int l, int d, int U, i
   w.o_dc = o;     o += al256((size_t)l * U * sizeof(float));
   w.o_dvt = o;    o += al256(BG * T * dv * sizeof(float));
   w.o_w1k = o;    o += al256((size_t)U * dk * es);
+  w.o_cs = o;     o += colsum_scratch_bytes((int64_t)BG * nb, dk);
   w.total = o;
   return w;
 }
@@ -326,7 +354,7 @@ extern "C" NSA_API int nsa_cmp_phi_bwd(const void* k, const float* pos_embed, co
       rows_to_f32_kernel<float><<<blocks_for(nk), 256, 0, st>>>((const float*)dk_cmp, dkc, nbp, nb, nb, dk, nk);
       rows_to_f32_kernel<float><<<blocks_for(nv), 256, 0, st>>>((const float*)dv_cmp, dvc, nbp, nb, nbp, dv, nv);
     }
-    colsum_kernel<<<blocks_for(dk), 256, 0, st>>>(dkc, N, dk, db2);
+    colsum<float>(dkc, N, dk, db2, (float*)(w + wl.o_cs), st);
     // dW2 (dk x U, row-major) = dkc^T hbar; column-major: C(U x dk) = hbar (U x N) op_T(dkc (dk x N))
     if (int rc = gemm(h, CUBLAS_OP_N, CUBLAS_OP_T, U, dk, (int)N, hbar, CUDA_R_32F, U, 0, dkc, CUDA_R_32F, dk, 0, 0.f, dw2, CUDA_R_32F, U, 0,
                       1, "cmp_phi_bwd (dW2)"))
@@ -374,4 +402,106 @@ extern "C" NSA_API int nsa_cmp_phi_bwd(const void* k, const float* pos_embed, co
     else add_into_kernel<float><<<blocks_for(nvt), 256, 0, st>>>((float*)dv_out, dvt, nvt);
   }
   return check_launch("cmp_phi_bwd");
+}
+
+
+// ================================================================================================================
+// Branch-gate MLP (nsa/kernels.py:2105-2109): logits = W2 relu(W1 x + b1) + b2, forward and backward, on the same cuBLAS
+// handle.  x [N, Dm], w1 [D2, Dm], w2 [O, D2] and the biases in `dtype`; logits [N, O] fp32 (what the gate/mix kernels
+// take); the hidden activation [N, D2] in `dtype` is what the backward needs.
+// ================================================================================================================
+namespace nsa {
+namespace {
+template <typename T>
+__global__ void bias_relu_kernel(T* __restrict__ h, const T* __restrict__ b, int W, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float x = Elem<T>::ld(h + i) + (b ? Elem<T>::ld(b + i % W) : 0.f);
+  Elem<T>::st(h + i, x > 0.f ? x : 0.f);
+}
+template <typename T>
+__global__ void bias_add_f32_kernel(float* __restrict__ y, const T* __restrict__ b, int W, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] += Elem<T>::ld(b + i % W);
+}
+template <typename T>
+__global__ void relu_mask_kernel(T* __restrict__ dh, const T* __restrict__ h, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && !(Elem<T>::ld(h + i) > 0.f)) Elem<T>::st(dh + i, 0.f);
+}
+}  // namespace
+}  // namespace nsa
+
+extern "C" NSA_API size_t nsa_gate_mlp_workspace_bytes(int64_t N, int Dm, int D2, int O, int dtype, int backward) {
+  if (N <= 0 || Dm <= 0 || D2 <= 0 || O <= 0) return 256;
+  const size_t es = dtype == NSA_BF16 ? 2 : 4;
+  if (!backward) return 256;
+  return al256((size_t)N * O * es) + al256((size_t)N * D2 * es) + colsum_scratch_bytes(N, std::max(O, D2)) + 256;
+}
+
+extern "C" NSA_API int nsa_gate_mlp_fwd(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* hidden,
+                                        float* logits, int64_t N, int Dm, int D2, int O, int dtype, void* stream) {
+  NSA_REQUIRE(x && w1 && w2 && hidden && logits, "gate_mlp_fwd: null pointer");
+  NSA_REQUIRE(N >= 0 && N < (1ll << 31) && Dm > 0 && D2 > 0 && O > 0, "gate_mlp_fwd: bad sizes");
+  NSA_REQUIRE(dtype == NSA_F32 || dtype == NSA_BF16, "gate_mlp_fwd: unsupported dtype %d", dtype);
+  if (N == 0) return NSA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  cublasHandle_t h;
+  if (int rc = blas_handle(&h, st)) return rc;
+  const cudaDataType t = dtype == NSA_BF16 ? CUDA_R_16BF : CUDA_R_32F;
+  KernelTimer kt("gate_mlp_fwd", st);
+  // hidden (N x D2, row-major) = x W1^T; column-major: C(D2 x N) = op_T(W1 (Dm x D2)) x (Dm x N)
+  if (int rc = gemm(h, CUBLAS_OP_T, CUBLAS_OP_N, D2, (int)N, Dm, w1, t, Dm, 0, x, t, Dm, 0, 0.f, hidden, t, D2, 0, 1, "gate_mlp_fwd (x W1^T)")) return rc;
+  const int64_t nh = N * D2, nl = N * O;
+  if (dtype == NSA_BF16) bias_relu_kernel<__nv_bfloat16><<<blocks_for(nh), 256, 0, st>>>((__nv_bfloat16*)hidden, (const __nv_bfloat16*)b1, D2, nh);
+  else bias_relu_kernel<float><<<blocks_for(nh), 256, 0, st>>>((float*)hidden, (const float*)b1, D2, nh);
+  if (int rc = gemm(h, CUBLAS_OP_T, CUBLAS_OP_N, O, (int)N, D2, w2, t, D2, 0, hidden, t, D2, 0, 0.f, logits, CUDA_R_32F, O, 0, 1, "gate_mlp_fwd (h W2^T)")) return rc;
+  if (b2) {
+    if (dtype == NSA_BF16) bias_add_f32_kernel<__nv_bfloat16><<<blocks_for(nl), 256, 0, st>>>(logits, (const __nv_bfloat16*)b2, O, nl);
+    else bias_add_f32_kernel<float><<<blocks_for(nl), 256, 0, st>>>(logits, (const float*)b2, O, nl);
+  }
+  return check_launch("gate_mlp_fwd");
+}
+
+extern "C" NSA_API int nsa_gate_mlp_bwd(const void* x, const void* w1, const void* w2, const void* hidden, const float* dlogits, void* dx,
+                                        float* dw1, float* db1, float* dw2, float* db2, int64_t N, int Dm, int D2, int O, int dtype,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  NSA_REQUIRE(x && w1 && w2 && hidden && dlogits && dw1 && db1 && dw2 && db2, "gate_mlp_bwd: null pointer");
+  NSA_REQUIRE(N > 0 && N < (1ll << 31) && Dm > 0 && D2 > 0 && O > 0, "gate_mlp_bwd: bad sizes");
+  NSA_REQUIRE(dtype == NSA_F32 || dtype == NSA_BF16, "gate_mlp_bwd: unsupported dtype %d", dtype);
+  const size_t need = nsa_gate_mlp_workspace_bytes(N, Dm, D2, O, dtype, 1);
+  if (!workspace || workspace_bytes < need) return fail(NSA_ERR_WORKSPACE, "gate_mlp_bwd needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  cublasHandle_t h;
+  if (int rc = blas_handle(&h, st)) return rc;
+  const size_t es = dtype == NSA_BF16 ? 2 : 4;
+  const cudaDataType t = dtype == NSA_BF16 ? CUDA_R_16BF : CUDA_R_32F;
+  char* w = (char*)workspace;
+  void* dl = w;                                           // dlogits in the I/O type
+  void* dh = w + al256((size_t)N * O * es);               // gradient of the hidden activation
+  float* cs = (float*)(w + al256((size_t)N * O * es) + al256((size_t)N * D2 * es));
+  KernelTimer kt("gate_mlp_bwd", st);
+  const int64_t nl = N * O, nh = N * D2;
+  colsum<float>(dlogits, N, O, db2, cs, st);
+  const void* dl_op = dlogits;
+  if (dtype == NSA_BF16) {
+    cast_kernel<__nv_bfloat16><<<blocks_for(nl), 256, 0, st>>>(dlogits, (__nv_bfloat16*)dl, nl);
+    dl_op = dl;
+  }
+  // dW2 (O x D2, row-major) = dl^T hidden; column-major: C(D2 x O) = hidden (D2 x N) op_T(dl (O x N))
+  if (int rc = gemm(h, CUBLAS_OP_N, CUBLAS_OP_T, D2, O, (int)N, hidden, t, D2, 0, dl_op, t, O, 0, 0.f, dw2, CUDA_R_32F, D2, 0, 1, "gate_mlp_bwd (dW2)")) return rc;
+  // dh (N x D2) = dl W2; column-major: C(D2 x N) = W2 (D2 x O) dl (O x N)
+  if (int rc = gemm(h, CUBLAS_OP_N, CUBLAS_OP_N, D2, (int)N, O, w2, t, D2, 0, dl_op, t, O, 0, 0.f, dh, t, D2, 0, 1, "gate_mlp_bwd (dh)")) return rc;
+  if (dtype == NSA_BF16) {
+    relu_mask_kernel<__nv_bfloat16><<<blocks_for(nh), 256, 0, st>>>((__nv_bfloat16*)dh, (const __nv_bfloat16*)hidden, nh);
+    colsum<__nv_bfloat16>((const __nv_bfloat16*)dh, N, D2, db1, cs, st);
+  } else {
+    relu_mask_kernel<float><<<blocks_for(nh), 256, 0, st>>>((float*)dh, (const float*)hidden, nh);
+    colsum<float>((const float*)dh, N, D2, db1, cs, st);
+  }
+  // dW1 (D2 x Dm, row-major) = dh^T x; column-major: C(Dm x D2) = x (Dm x N) op_T(dh (D2 x N))
+  if (int rc = gemm(h, CUBLAS_OP_N, CUBLAS_OP_T, Dm, D2, (int)N, x, t, Dm, 0, dh, t, D2, 0, 0.f, dw1, CUDA_R_32F, Dm, 0, 1, "gate_mlp_bwd (dW1)")) return rc;
+  if (dx)  // dx (N x Dm) = dh W1; column-major: C(Dm x N) = W1 (Dm x D2) dh (D2 x N)
+    if (int rc = gemm(h, CUBLAS_OP_N, CUBLAS_OP_N, Dm, (int)N, D2, w1, t, Dm, 0, dh, t, D2, 0, 0.f, dx, t, Dm, 0, 1, "gate_mlp_bwd (dx)")) return rc;
+  return check_launch("gate_mlp_bwd");
 }

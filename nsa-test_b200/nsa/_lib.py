@@ -62,6 +62,9 @@ PROTOTYPES = {
     "nsa_cmp_phi_workspace_bytes": (c_size_t, [c_int] * 11),
     "nsa_cmp_phi_fwd": (c_int, [_P] * 10 + [c_int] * 10 + [_P, c_size_t, _P, c_size_t, _P]),
     "nsa_cmp_phi_bwd": (c_int, [_P] * 7 + [c_size_t] + [_P] * 7 + [c_int] * 10 + [_P, c_size_t, _P]),
+    "nsa_gate_mlp_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int, c_int]),
+    "nsa_gate_mlp_fwd": (c_int, [_P] * 7 + [c_int64, c_int, c_int, c_int, c_int, _P]),
+    "nsa_gate_mlp_bwd": (c_int, [_P] * 10 + [c_int64, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "nsa_layer_ctx_bytes": (c_size_t, [_DESCP, POINTER(c_size_t)]),
     "nsa_layer_workspace_bytes": (c_size_t, [_DESCP, c_int]),
     "nsa_layer_fwd": (c_int, [_DESCP] + [_P] * 16 + [c_size_t, _P, c_size_t, _P]),

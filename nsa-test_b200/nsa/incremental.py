@@ -19,7 +19,8 @@ from typing import Optional
 import torch
 
 from . import ops
-from .kernels import NSAConfig, PAD_BLOCK_END, _PhiCompress, _next_pow2, _project_heads, _selection_fallback
+from .kernels import (NSAConfig, PAD_BLOCK_END, _PhiCompress, _next_pow2, _project_heads, _selection_fallback,
+                      gate_logits_from_hidden)
 
 __all__ = ["NSACache", "nsa_layer_incremental", "module_forward_incremental"]
 
@@ -178,5 +179,5 @@ def module_forward_incremental(module, hidden_new: torch.Tensor, cache: NSACache
     k_sel, v_sel = kv(module.k_select, module.v_select)
     cache.append(module._phi_params(), k_sel, v_sel, kv_compress=kv(module.k_compress, module.v_compress),
                  kv_sliding=kv(module.k_sliding, module.v_sliding))
-    out = nsa_layer_incremental(q, module.gate_mlp(hidden_new), cache, module.scale)
+    out = nsa_layer_incremental(q, gate_logits_from_hidden(hidden_new, module.gate_mlp), cache, module.scale)
     return module.o_proj(out.transpose(1, 2).reshape(B, Tn, H * dv))

@@ -342,6 +342,32 @@ class _PhiCompress(torch.autograd.Function):
                 dw2.to(w2dtype), db2.to(w2dtype) if has_b2 else None, None, None)
 
 
+class _GateMLP(torch.autograd.Function):
+    """Branch-gate MLP (nsa/kernels.py:2105-2109) through the library's nsa_gate_mlp_fwd / nsa_gate_mlp_bwd:
+    ``apply(x [B,T,d_model], w1, b1, w2, b2) -> logits [B,T,3H]`` in fp32 (what the gate/mix kernels take)."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2):
+        cast = lambda p: None if p is None else p.detach().to(x.dtype).contiguous()
+        w1c, b1c, w2c, b2c = cast(w1), cast(b1), cast(w2), cast(b2)
+        logits, hidden = ops.gate_mlp_fwd(x.detach(), w1c, b1c, w2c, b2c)
+        ctx.save_for_backward(x, w1c, w2c, hidden)
+        ctx.meta = (w1.dtype, w2.dtype, None if b1 is None else b1.dtype, None if b2 is None else b2.dtype)
+        return logits
+
+    @staticmethod
+    def backward(ctx, dlogits):
+        x, w1c, w2c, hidden = ctx.saved_tensors
+        dx, dw1, db1, dw2, db2 = ops.gate_mlp_bwd(x, w1c, w2c, hidden, dlogits, ctx.needs_input_grad[0])
+        w1d, w2d, b1d, b2d = ctx.meta
+        return (dx, dw1.to(w1d), None if b1d is None else db1.to(b1d), dw2.to(w2d), None if b2d is None else db2.to(b2d))
+
+
+def gate_logits_from_hidden(x: torch.Tensor, gate_mlp: torch.nn.Sequential) -> torch.Tensor:
+    """The module's gate MLP (Linear, ReLU, Linear) applied through the library: fp32 logits [B,T,3H]."""
+    return _GateMLP.apply(x, gate_mlp[0].weight, gate_mlp[0].bias, gate_mlp[2].weight, gate_mlp[2].bias)
+
+
 class _GateMix(torch.autograd.Function):
     """out = g0*o_cmp + g1*o_slc + g2*o_win with gates from logits [B,T,3H] (nsa/kernels.py:2446-2463)."""
 
@@ -554,7 +580,7 @@ class NSAAttention(torch.nn.Module):
                     _project_heads(hidden_states, vp, G, dv))                                    # [B,G,T,dv]
 
         k_sel, v_sel = kv(self.k_select, self.v_select)
-        gate_logits = self.gate_mlp(hidden_states)                                               # [B,T,3H]
+        gate_logits = gate_logits_from_hidden(hidden_states, self.gate_mlp)                      # [B,T,3H] fp32
         out, info = nsa_layer(q, k_sel, v_sel, gate_logits, self._phi_params(), c,
                               kv_compress=kv(self.k_compress, self.v_compress),
                               kv_sliding=kv(self.k_sliding, self.v_sliding), scale=self.scale, return_info=True,

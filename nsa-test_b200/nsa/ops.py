@@ -355,6 +355,38 @@ def eq9_scores(p_cmp, l: int, d: int, l_prime: int):
     return out
 
 
+def gate_mlp_fwd(x, w1, b1, w2, b2):
+    """Branch-gate MLP through the C ABI: x [..., Dm] -> (logits [..., O] fp32, hidden [N, D2] for the backward)."""
+    dev = require_cuda(x, w1, w2)
+    Dm, D2, O = x.shape[-1], w1.shape[0], w2.shape[0]
+    x2 = x.reshape(-1, Dm).contiguous()
+    N = x2.shape[0]
+    hidden = torch.empty(N, D2, device=dev, dtype=x.dtype)
+    logits = torch.empty(*x.shape[:-1], O, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.nsa_gate_mlp_fwd(ptr(x2), ptr(w1), ptr(b1), ptr(w2), ptr(b2), ptr(hidden), ptr(logits), N, Dm, D2, O, dtype_code(x),
+                                   stream_ptr(dev)), "nsa_gate_mlp_fwd")
+    return logits, hidden
+
+
+def gate_mlp_bwd(x, w1, w2, hidden, dlogits, need_dx: bool):
+    """-> (dx [..., Dm] in x's dtype or None, dw1, db1, dw2, db2 fp32)."""
+    dev = require_cuda(x, w1, w2, hidden, dlogits)
+    Dm, D2, O = x.shape[-1], w1.shape[0], w2.shape[0]
+    x2 = x.reshape(-1, Dm).contiguous()
+    N = x2.shape[0]
+    dl = dlogits.reshape(N, O).float().contiguous()
+    dx = torch.empty(N, Dm, device=dev, dtype=x.dtype) if need_dx else None
+    f32 = lambda *s_: torch.empty(*s_, device=dev, dtype=torch.float32)
+    dw1, db1, dw2, db2 = f32(D2, Dm), f32(D2), f32(O, D2), f32(O)
+    nbytes = lib.nsa_gate_mlp_workspace_bytes(N, Dm, D2, O, dtype_code(x), 1)
+    ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        check(lib.nsa_gate_mlp_bwd(ptr(x2), ptr(w1), ptr(w2), ptr(hidden), ptr(dl), ptr(dx), ptr(dw1), ptr(db1), ptr(dw2), ptr(db2), N,
+                                   Dm, D2, O, dtype_code(x), ptr(ws), nbytes, stream_ptr(dev)), "nsa_gate_mlp_bwd")
+    return (dx.view(x.shape) if need_dx else None), dw1, db1, dw2, db2
+
+
 def gate_mix_fwd(logits, o_cmp, o_slc, o_win, gate_mode: str, token_major: bool = False):
     """logits [B,T,3H]; branch outputs [B,H,T,dv] -> out [B,H,T,dv] (token_major: backed by a [B,T,H,dv] buffer),
     gates [B,H,T,3] fp32."""
