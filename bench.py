@@ -305,14 +305,60 @@ def sampled_parity(inp, params, cfg, rows=192):
                 mismatched_outside_ambiguity=int((mism & ~amb).sum()), max_abs=errs, bound_bf16=2e-2)
 
 
+def cpu_reference_tokens_per_s(T_sample, steps, threads):
+    """The reference project's own module (NSAAttention in eval mode: its CPU path through nsa/reference.py, float64
+    loops over batch, head and token), forward + backward, from the copy oracle/install_reference.py made."""
+    import importlib.util
+    root = os.path.join(ROOT, "baseline", "_ref", "nsa")
+    if not os.path.exists(os.path.join(root, "kernels.py")):
+        raise FileNotFoundError("baseline/_ref/nsa is missing: run oracle/install_reference.py --reference <checkout>")
+    if "nsa_reference_project" not in sys.modules:
+        spec = importlib.util.spec_from_file_location("nsa_reference_project", os.path.join(root, "__init__.py"),
+                                                      submodule_search_locations=[root])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["nsa_reference_project"] = mod
+        spec.loader.exec_module(mod)
+    R = sys.modules["nsa_reference_project"]
+    c = CFG
+    torch.set_num_threads(threads)
+    torch.manual_seed(0)
+    cfg = R.NSAConfig(d_model=c["d_model"], head_dim_qk=c["dk"], head_dim_v=c["dv"], l=c["l"], d=c["d"], l_prime=c["l_prime"], n=c["n"],
+                      w=c["w"], n_heads=c["H"], n_kv_groups=c["G"])
+    model = R.NSAAttention(cfg).eval()
+    times = []
+    for _ in range(steps):
+        x = torch.randn(1, T_sample, c["d_model"], requires_grad=True)
+        t0 = time.perf_counter()
+        y, _info = model(x)
+        y.backward(torch.ones_like(y))
+        times.append(time.perf_counter() - t0)
+    return T_sample / (sum(times) / len(times)), sum(times) / len(times)
+
+
 def run_reference(args):
-    """`--impl reference`: the reference's CPU path.  The reference is a Python package that cannot be
-    installed on the benchmark box, so its algorithm runs as the committed CPU oracle (kind "port")."""
+    """`--impl reference`: the reference's algorithm on the host CPU.  Default: the committed CPU oracle, a vectorised
+    port that is some 40 times faster per token than the reference's own Python loops, on a T=4096 sample (kind "port": the
+    ratio against it understates the speed-up).  `--cpu-kind reference`: the reference project's own module from
+    baseline/_ref on a sample short enough for its loops (kind "reference")."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     T_sample = args.cpu_sample
+    if args.cpu_kind == "reference":
+        T_sample = min(T_sample, 128)
+        if args.warmup > 0:
+            cpu_reference_tokens_per_s(T_sample, 1, threads)
+        tps, sec = cpu_reference_tokens_per_s(T_sample, max(1, args.steps), threads)
+        sample = (f"the reference's NSAAttention (eval: its float64 CPU path) forward + backward, projections included, one sequence "
+                  f"of T={T_sample} (same heads/dims as the workload)")
+        line = dict(metric=METRIC, value=tps, unit="tokens/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=sec * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f64", data="synthetic",
+                    impl="reference", config=dict(workload=f"NSA layer fwd+bwd, B=1 per GPU, T={T_sample} sample of T={args.T}", **CFG),
+                    cpu_baseline=dict(value=tps, unit="tokens/s", cores=threads, kind="reference", sample=sample),
+                    e2e=dict(value=tps, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+        print(json.dumps(line))
+        return
     for _ in range(min(args.warmup, 1)):
         cpu_oracle_tokens_per_s(T_sample, 1, threads)
     tps, sec = cpu_oracle_tokens_per_s(T_sample, max(1, args.steps), threads)
@@ -375,6 +421,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--T", type=int, default=65536)
     ap.add_argument("--cpu-sample", type=int, default=4096, help="sequence length of the CPU-oracle sample")
+    ap.add_argument("--cpu-kind", default="port", choices=["port", "reference"],
+                    help="--impl reference: time the committed CPU oracle (port, default) or the reference project's own module")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-long-context", action="store_true",
                     help="multi-GPU runs: skip the extra leg that times ONE sequence split by position over the GPUs")

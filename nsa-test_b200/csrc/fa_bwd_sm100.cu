@@ -632,26 +632,29 @@ fa_bwd_dq_ds_kernel(const __grid_constant__ CUtensorMap tmDs, const __grid_const
 
 // ------------------------------------------------------------------------------------------------
 // dK/dV kernel: 128 keys per CTA, loops over (head, 64-query sub-tile); transposed tiles in TMEM.
-// 320 threads: warps 0-3 / 4-7 turn the two 32-query halves of S^T, dP^T into P^T, dS^T; warp 8 TMA; warp 9 UMMA.
+// 352 threads: warps 0-3 / 4-7 turn the two 32-query halves of S^T, dP^T into P^T, dS^T; warp 8 TMA; warp 9 UMMA; warp 10
+// stores the dS^T tiles the compute warps stage in shared memory.
 // ------------------------------------------------------------------------------------------------
 template <int DK, int DV>
 struct DkvSmem {
   static constexpr int kK = 128 * DK * 2, kV = 128 * DV * 2, kQs = 64 * DK * 2, kdOs = 64 * DV * 2;
   static constexpr int kStage = kQs + kdOs + 1024;  // + lse2[64], D[64] (512 B, padded to keep 1024 B alignment)
   static constexpr int kStages = 3;
-  static constexpr int oK = 0, oV = oK + kK, oStage = oV + kV, oBar = oStage + kStages * kStage;
+  static constexpr int kDsTile = 128 * 64 * 2;  // one dS^T tile on its way to global memory (128-byte-swizzled rows)
+  static constexpr int oK = 0, oV = oK + kK, oStage = oV + kV, oDs = oStage + kStages * kStage, oBar = oDs + kDsTile;
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct DkvBarriers {
-  uint64_t kv_full, full[3], empty[3], stp_full, st_free, pds_full, pds_free, acc_done;
+  uint64_t kv_full, full[3], empty[3], stp_full, st_free, pds_full, pds_free, acc_done, dst_ready, dst_free;
   uint32_t tmem_base;
   int abort;
 };
 
 template <int DK, int DV, int MODE>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
-                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FaBwdParams p) {
+                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                  const __grid_constant__ CUtensorMap tmDs, const FaBwdParams p) {
   using SM = DkvSmem<DK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -680,6 +683,8 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(&bar->pds_full, 256);
     mbar_init(&bar->pds_free, 1);
     mbar_init(&bar->acc_done, 1);
+    mbar_init(&bar->dst_ready, 256);
+    mbar_init(&bar->dst_free, 1);
     bar->abort = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -793,6 +798,22 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         __syncwarp();
       }
     }
+  } else if (warp == 10) {
+    // dS^T tile stores: one tile per iteration leaves through the staging area, off the compute warps' critical path
+    if (p.ds && lane == 0) {
+      const uint8_t* sDs = smem + SM::oDs;
+      int qs = qs_lo - 1, h = hbeg;
+      for (int it = 0; it < n_it; ++it) {
+        if (++qs > qs_hi) { qs = qs_lo; ++h; }
+        if (!mbar_wait(&bar->dst_ready, it & 1, abort)) break;
+        const int64_t tile = (((int64_t)b * p.H + h) * gridDim.x + blockIdx.x) * p.ds_per_j + ds_slot<MODE>(blockIdx.x, qs);
+        tma_store_2d(&tmDs, sDs, 0, (int)(tile * 128));
+        bulk_commit();
+        bulk_wait_read<0>();               // the staging area may be overwritten
+        mbar_arrive(&bar->dst_free);
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every tile has landed before the block ends
+    }
   } else {
     // warps 0-3 / 4-7: queries [0,32) / [32,64) of every sub-tile, the same 128 key rows
     const int gsel = warp >> 2;
@@ -841,12 +862,23 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         pk[16 + e] = *reinterpret_cast<uint32_t*>(&y);
       }
       if (p.ds) {
-        // hand dS^T to the dQ kernel: this thread's key row, the 32 queries of its group (64 contiguous bytes of the
-        // tile's 128-byte row)
-        const int64_t tile = (((int64_t)b * p.H + h) * gridDim.x + blockIdx.x) * p.ds_per_j + ds_slot<MODE>(blockIdx.x, qs);
-        uint4* dst = reinterpret_cast<uint4*>(p.ds + tile * 8192 + r * 64 + gsel * 32);
+        // Hand dS^T to the dQ kernel through a shared-memory tile and ONE tile store (whole 128-byte lines leave the
+        // SM; per-thread 16-byte stores at a 128-byte stride cost 32 partial-line writes per warp instruction).  This
+        // thread holds its key row x the 32 queries of its group: chunks gsel*4 .. gsel*4+3 of the row, placed where
+        // the 128-byte swizzle of the tile store expects them.
+        // Every wait is a bounded mbarrier wait (no bar.sync: a thread that gave up elsewhere must not strand the rest).
+        uint8_t* sDs = smem + SM::oDs;
+        if (it > 0) {  // the store of the tile before has read the staging area
+          ok = mbar_wait(&bar->dst_free, (it - 1) & 1, abort);
+          if (!ok) break;
+        }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) dst[e] = make_uint4(pk[16 + 4 * e], pk[17 + 4 * e], pk[18 + 4 * e], pk[19 + 4 * e]);
+        for (int e = 0; e < 4; ++e) {
+          const int chunk = (gsel * 4 + e) ^ (r & 7);
+          *reinterpret_cast<uint4*>(sDs + r * 128 + chunk * 16) = make_uint4(pk[16 + 4 * e], pk[17 + 4 * e], pk[18 + 4 * e], pk[19 + 4 * e]);
+        }
+        fence_proxy_async();
+        mbar_arrive(&bar->dst_ready);      // warp 10 sends the tile off
       }
       // P^T / dS^T of the previous iteration must have been consumed before they are overwritten
       if (it > 0) {
@@ -970,7 +1002,7 @@ static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, con
     // key-stationary kernel first: it leaves dS^T behind, from which the dQ kernel only has one product left to do
     {
       KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);
-      kkv<<<kvgrid, 320, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, p);
+      kkv<<<kvgrid, 352, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, tds, p);
     }
     if (int rc = check_launch("fa_bwd_dkv_sm100")) return rc;
     KernelTimer kt(MODE == kWin ? "fa_bwd_dqds_win" : "fa_bwd_dqds_cmp", st);
@@ -983,7 +1015,7 @@ static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, con
   }
   if (int rc = check_launch("fa_bwd_dq_sm100")) return rc;
   KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);
-  kkv<<<kvgrid, 320, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, p);
+  kkv<<<kvgrid, 352, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, tds, p);
   return check_launch("fa_bwd_dkv_sm100");
 }
 
