@@ -463,3 +463,27 @@ def test_layer_fp32_odd_shapes(nsa_mod, T, dk, dv, H, G, n, w, include_fixed, ga
     inp = O.make_inputs(c["B"], H, G, T, dk, dv, c["d_model"], c["l"], seed=c["seed"], block_offset_std=0.5)
     check_layer_against_oracle(f"layer fp32 odd T={T} dk={dk} dv={dv}", nsa_mod, c, inp, torch.float32, gate_mode=gate_mode,
                                include_fixed=include_fixed)
+
+
+def test_module_dropout_and_state_dict_round_trip(nsa_mod):
+    """dropout_p > 0 (the reference applies nn.Dropout to the projected output, nsa/kernels.py:2477): training-mode calls
+    differ from one another and from eval, eval is deterministic and equals the dropout-free module; the token-major
+    path into o_proj gives gradients for every parameter."""
+    c = dict(d_model=64, dk=64, dv=64, H=4, G=2, T=256)
+    mk = lambda p: nsa_mod.NSAAttention(nsa_mod.NSAConfig(d_model=c["d_model"], head_dim_qk=c["dk"], head_dim_v=c["dv"], n_heads=c["H"],
+                                                         n_kv_groups=c["G"], l=32, d=16, l_prime=64, n=4, w=64, dropout_p=p)).to(DEV)
+    torch.manual_seed(3)
+    plain, drop = mk(0.0), mk(0.5)
+    drop.load_state_dict(plain.state_dict(), strict=True)
+    x = torch.randn(2, c["T"], c["d_model"], device=DEV)
+    plain.eval(); drop.eval()
+    y0, _ = plain(x)
+    y1, _ = drop(x)
+    y2, _ = drop(x)
+    assert torch.equal(y1, y2) and torch.equal(y0, y1)
+    drop.train()
+    a, _ = drop(x)
+    b, _ = drop(x)
+    assert not torch.equal(a, b) and (a == 0).float().mean() > 0.3
+    a.sum().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in drop.parameters())
