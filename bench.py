@@ -167,6 +167,13 @@ def layer_step_query_sharded(inp, params, cfg, world, before_backward=None):
     return out[0, 0, -1, :8].float().sum() + grads[0][0, 0, -1, :8].float().sum()
 
 
+# Cost of a query that does not depend on its position (sliding window, selected blocks, gate/mix, its share of phi), in
+# units of one visible compressed key, for the work-balanced position split: from the measured kernel times of the
+# one-GPU step at T=65536 (40 ms of position-independent kernels, 33 ms of compression + scoring whose cost grows
+# linearly with the position: 0.61 us per query against 33 ms * 2t/T^2 -> 0.61 us / (33 ms * 2 / (T^2) * d) at d = 16).
+POSITION_INDEPENDENT_COST = 2480.0
+
+
 def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
     """Long-context mode inside a multi-GPU run: ONE sequence of T tokens split by position over the ranks (K/V and
     the compressed K/V all-gathered, their gradients reduce-scattered), 5 warm-up + 10 timed steps, device-timed, max
@@ -176,7 +183,7 @@ def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
     from nsa import sharding
     c = CFG
     inp, params = make_device_inputs(T, dev, seed=0)            # the same sequence on every rank; each keeps its slice
-    bounds = sharding.balanced_query_bounds(T, world, c["w"] + c["n"] * c["l_prime"], c["d"])
+    bounds = sharding.balanced_query_bounds(T, world, POSITION_INDEPENDENT_COST, c["d"])
     t0, t1 = bounds[rank], bounds[rank + 1]
     inp = dict(q=inp["q"][:, :, t0:t1].contiguous(), k=inp["k"][..., t0:t1].contiguous(), v=inp["v"][:, :, t0:t1].contiguous(),
                do=inp["do"][:, :, t0:t1].contiguous(), x=inp["x"][:, t0:t1].contiguous(), bounds=bounds)
@@ -193,8 +200,20 @@ def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
     e1.record()
     dist.barrier()
     torch.cuda.synchronize()
-    t_ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    mine = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    t_ms = mine.clone()
     dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    # every rank's own device time for its slice between two barriers: without the waits for the collectives of the
+    # other ranks (a step has four), i.e. how even the position split is
+    own = torch.zeros(world, device=dev)
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    e2.record()
+    layer_step_query_sharded(inp, params, cfg, world)
+    e3.record()
+    torch.cuda.synchronize()
+    own[rank] = e2.elapsed_time(e3)
+    dist.all_reduce(own)
     # the exchange steps alone (same tensors, same collectives as inside the layer), device-timed, max over ranks
     sizes = [bounds[i + 1] - bounds[i] for i in range(world)]
     kk, vv = inp["k"].detach().requires_grad_(True), inp["v"].detach().requires_grad_(True)
@@ -216,7 +235,7 @@ def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
                 n1_reference="this run's one-GPU step for a whole sequence of the same length" if T == args.T else None,
                 allgather_ms=round(coll[0].item(), 3), reduce_scatter_ms=round(coll[1].item(), 3),
                 allgather_bytes=kv_bytes, reduce_scatter_bytes=2 * kv_bytes,
-                slices=[bounds[i + 1] - bounds[i] for i in range(world)])
+                slices=[bounds[i + 1] - bounds[i] for i in range(world)], rank_step_ms=[round(x, 2) for x in own.tolist()])
 
 
 def attention_flops(T):
@@ -247,6 +266,7 @@ def kernel_flops(T):
         f[f"fa_bwd_dq_{br}"] = unit[br] * 2 * (2 * dk + dv)             # S, dP, dQ
         f[f"fa_bwd_dkv_{br}"] = unit[br] * 2 * (2 * dk + 2 * dv)        # S^T, dP^T, dV, dK
         f[f"fa_bwd_dqds_{br}"] = unit[br] * 2 * dk                      # dQ from the dS^T tiles the dK/dV kernel left
+    f["fa_fwd_cmp_exact"] = f["fa_fwd_cmp"]                            # keys as hi + lo halves: same role, 1.6x the MMAs
     f["slc_fwd"] = unit["slc"] * 2 * (dk + dv)
     f["slc_bwd_fused"] = unit["slc"] * 2 * (3 * dk + 2 * dv)           # S, dP, dQ, dV, dK
     return f
@@ -413,6 +433,39 @@ def run_decode(args):
                           checksum=float(out.float().sum()), device_timeouts=lib.nsa_device_timeouts(0))))
 
 
+def run_reference_shape(args):
+    """The one shape the reference project times itself (tests/test_large_scale.py:24-32: B=4, H=32, G=8, T=2048, dk=dv=128,
+    window 256, sliding-window forward + backward; tokens/s = B*T / (t_fwd + t_bwd)), through this library with CUDA
+    events: fp32 tensors (what that test passes; they run on the stride-generic kernels) and bf16 tensors (tensor-core
+    kernels)."""
+    from nsa import ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, H, G, T, d, w = 4, 32, 8, 2048, 128, 256
+    scale = d ** -0.5
+    res = {}
+    for name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        g = torch.Generator(device=dev).manual_seed(0)
+        q, k, v, do = (torch.randn(*s_, generator=g, device=dev).to(dt) for s_ in
+                       [(B, H, T, d), (B, G, d, T), (B, G, T, d), (B, H, T, d)])
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        fw, bw = [], []
+        for i in range(3 + 10):
+            ev[0].record()
+            o, L, M = ops.sliding_fwd(q, k, v, w, scale)
+            ev[1].record()
+            ops.sliding_bwd(q, k, v, o, do, L, M, w, scale)
+            ev[2].record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                fw.append(ev[0].elapsed_time(ev[1]))
+                bw.append(ev[1].elapsed_time(ev[2]))
+        f_ms, b_ms = sorted(fw)[len(fw) // 2], sorted(bw)[len(bw) // 2]
+        res[name] = dict(fwd_ms=round(f_ms, 3), bwd_ms=round(b_ms, 3), tokens_per_s=round(B * T / ((f_ms + b_ms) * 1e-3), 1))
+    print(json.dumps(dict(metric="sliding-window fwd+bwd at the reference's large-scale test shape", unit="tokens/s",
+                          config=dict(workload="B=4 H=32 G=8 T=2048 dk=dv=128 window=256, median of 10 after 3 warm-up"), **res)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -434,9 +487,14 @@ def main():
     ap.add_argument("--decode", type=int, default=0, metavar="N",
                     help="instead of the training step: time N single-token forward steps of one layer against a cache of "
                          "--T tokens (nsa.incremental) and print their own JSON line")
+    ap.add_argument("--ref-shape", action="store_true",
+                    help="instead of the training step: time the sliding-window branch at the shape the reference's own "
+                         "tests/test_large_scale.py times, fp32 and bf16")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.ref_shape:
+        return run_reference_shape(args)
     if args.decode > 0:
         return run_decode(args)
 
@@ -459,7 +517,7 @@ def main():
         from nsa.sharding import balanced_query_bounds
         inp, params = make_device_inputs(T, dev, seed=0)        # the same sequence on every rank; each keeps its slice
         # slices sized for equal attention work: w + n*l' keys per query everywhere, plus t/d compressed keys
-        bounds = balanced_query_bounds(T, world, c["w"] + c["n"] * c["l_prime"], c["d"])
+        bounds = balanced_query_bounds(T, world, POSITION_INDEPENDENT_COST, c["d"])
         t0, t1 = bounds[rank], bounds[rank + 1]
         inp = dict(q=inp["q"][:, :, t0:t1].contiguous(), k=inp["k"][..., t0:t1].contiguous(), v=inp["v"][:, :, t0:t1].contiguous(),
                    do=inp["do"][:, :, t0:t1].contiguous(), x=inp["x"][:, t0:t1].contiguous(), bounds=bounds)

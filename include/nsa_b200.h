@@ -146,10 +146,18 @@ NSA_API int nsa_sliding_bwd_noalloc(const void* q, const void* k, const void* v,
  * block_ends[i] == i*blocks_d + blocks_l - 1 for i < blocks_n and that later blocks are never
  * visible, which lets the tensor-core kernels skip tiles; blocks_d == 0 makes no assumption.
  * Replaces _nsa_compression_fwd_kernel / _bwd_kernel (nsa/kernels.py:1533-1687, 1690-1917). */
+/* Exact-key form (k_cmp_lo and lse2_out both non-NULL; bf16 tensor-core path only, nsa_cmp_attn_exact_supported tells
+ * for a shape, and the call needs the block layout hint, canonical layouts and L, M): k_cmp is the bf16 rounding of the
+ * fp32 compressed keys and k_cmp_lo [B,G,dk,NB] the bf16 rounding of the remainder (nsa_split_keys_hi_lo makes both);
+ * the logits are q (k_cmp + k_cmp_lo), i.e. those of the fp32 keys to 16 mantissa bits, and lse2_out [B,H,T] fp32
+ * receives their log-sum-exp in log2 units (+inf for rows that see no block).  That is the normaliser of Eq. 8, so
+ * nsa_score_topn given it as cmp_lse2 skips its own first sweep over the compressed keys. */
+NSA_API int nsa_cmp_attn_exact_supported(int B, int H, int G, int T, int NB, int dk, int dv, int dtype);
+NSA_API int nsa_split_keys_hi_lo(const float* x, void* hi, void* lo, int64_t n, void* stream);
 NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                      void* out, float* L, float* M, const int64_t* strides22, int B, int H, int G,
                      int T, int NB, int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d,
-                     int blocks_n, int q_pos0, int flags, void* stream);
+                     int blocks_n, int q_pos0, int flags, const void* k_cmp_lo, float* lse2_out, void* stream);
 NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                      const void* out, const void* dout, const float* L, const float* M, void* dq,
                      void* dk_cmp, void* dv_cmp, const int64_t* strides34, int B, int H, int G, int T,
@@ -247,14 +255,16 @@ NSA_API int nsa_phi_pool_bwd(const float* a, const float* c, const float* dhbar,
  * contiguous, block_ends [nbp], indices_out int32 [B,G,T,n] contiguous.
  * n_real_blocks >= 0 asserts block_ends[i] == i*d + l - 1 for i < n_real_blocks and no later block ever
  * visible, which admits the tensor-core kernel (fp32 keys split into bf16 hi + lo parts held in the
- * workspace of nsa_score_topn_workspace_bytes() bytes); -1 makes no assumption. */
+ * workspace of nsa_score_topn_workspace_bytes() bytes); -1 makes no assumption.  cmp_lse2 (or NULL): the
+ * log-sum-exp [B,H,T] of the same logits from nsa_cmp_attn_fwd's exact-key form (same q_pos0); the tensor-core kernel
+ * then makes one sweep over the compressed keys instead of two (other paths ignore it and compute their own). */
 NSA_API size_t nsa_score_topn_workspace_bytes(int B, int H, int G, int T, int dk, int nbp, int l, int d,
                                               int l_prime, int n, int dtype, int flags);
 NSA_API int nsa_score_topn(const void* q, const int64_t* q_strides4, const float* k_cmp,
                    const int32_t* block_ends, int32_t* indices_out, int B, int H, int G, int T, int dk,
                    int nbp, int l, int d, int l_prime, int n, int n_fixed, float scale, int dtype,
-                   int n_real_blocks, int q_pos0, int flags, void* workspace, size_t workspace_bytes,
-                   void* stream);
+                   int n_real_blocks, int q_pos0, int flags, const float* cmp_lse2, void* workspace,
+                   size_t workspace_bytes, void* stream);
 /* Eq. 10/11 alone on a given score tensor [B,H,T,n_sel] fp32 contiguous
  * (select_top_k_blocks_per_query_with_gqa, nsa/kernels.py:1965-2040). */
 NSA_API int nsa_topn_from_scores(const float* scores, int32_t* indices_out, int B, int H, int G, int T,
@@ -337,6 +347,7 @@ enum nsa_layer_ctx_piece {
   NSA_CTX_O_CMP = 0, NSA_CTX_L_CMP, NSA_CTX_M_CMP, NSA_CTX_O_SLC, NSA_CTX_L_SLC, NSA_CTX_M_SLC, NSA_CTX_O_WIN, NSA_CTX_L_WIN,
   NSA_CTX_M_WIN, NSA_CTX_GATES /* [B,H,T,3] fp32 */, NSA_CTX_INDICES /* int32 [B,G,T,n], all-empty rows already replaced */,
   NSA_CTX_K_CMP /* fp32 [B,G,dk,nbp] */, NSA_CTX_K_CMP_LP, NSA_CTX_V_CMP /* [B,G,nbp,dv] */, NSA_CTX_BLOCK_ENDS /* int32 [nbp] */,
+  NSA_CTX_K_CMP_LO /* bf16 remainder of the fp32 compressed keys */, NSA_CTX_LSE2_CMP /* fp32 [B,H,T], log2 units */,
   NSA_CTX_PHI_SAVED, NSA_CTX_PIECES
 };
 NSA_API size_t nsa_layer_ctx_bytes(const nsa_layer_desc* desc, size_t* offsets);

@@ -210,7 +210,7 @@ extern "C" NSA_API int nsa_sliding_fwd(const void* q, const void* k, const void*
   if (want_tc(flags) && dtype == NSA_BF16 && L && M && fa_fwd_sm100_supported(H, G, T, T, dk, dv) &&
       canonical_fwd(strides, H, G, T, T, dk, dv) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
       (int64_t)B * (H / 2) <= 65535)
-    return fa_fwd_sm100(q, k, v, out, L, M, B, H, G, T, T, dk, dv, kWin, window, 0, 0, 0, scale, (cudaStream_t)stream);
+    return fa_fwd_sm100(q, k, v, out, L, M, B, H, G, T, T, dk, dv, kWin, window, 0, 0, 0, scale, nullptr, nullptr, (cudaStream_t)stream);
   AttnArgs a = {};
   a.q = q; a.k = k; a.v = v; a.o = out; a.L = L; a.M = M;
   fill_fwd_strides(a, strides);
@@ -240,8 +240,9 @@ extern "C" NSA_API int nsa_sliding_bwd(const void* q, const void* k, const void*
 extern "C" NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,
                                 void* out, float* L, float* M, const int64_t* strides, int B, int H, int G, int T,
                                 int NB, int dk, int dv, float scale, int dtype, int blocks_l, int blocks_d,
-                                int blocks_n, int q_pos0, int flags, void* stream) {
+                                int blocks_n, int q_pos0, int flags, const void* k_cmp_lo, float* lse2_out, void* stream) {
   if (int rc = check_common("cmp_attn_fwd", B, H, G, T, NB, dk, dv, dtype)) return rc;
+  NSA_REQUIRE((k_cmp_lo == nullptr) == (lse2_out == nullptr), "cmp_attn_fwd: the low-order key part and the log-sum-exp output go together");
   NSA_REQUIRE(q && k_cmp && v_cmp && block_ends && out && strides, "cmp_attn_fwd: null pointer");
   NSA_REQUIRE(blocks_d >= 0 && (blocks_d == 0 || (blocks_l > 0 && blocks_n >= 0 && blocks_n <= NB)),
               "cmp_attn_fwd: bad block layout hint (l=%d, d=%d, n=%d)", blocks_l, blocks_d, blocks_n);
@@ -252,13 +253,19 @@ extern "C" NSA_API int nsa_cmp_attn_fwd(const void* q, const void* k_cmp, const 
       aligned16(out) && (int64_t)B * (H / 2) <= 65535)
     // block i is visible to the query at position q0 + t iff i*d + l - 1 <= q0 + t: the same rule with l - q0 for row t
     return fa_fwd_sm100(q, k_cmp, v_cmp, out, L, M, B, H, G, T, NB, dk, dv, kCmp, 0, blocks_l - q_pos0, blocks_d, blocks_n,
-                        scale, (cudaStream_t)stream);
+                        scale, k_cmp_lo, lse2_out, (cudaStream_t)stream);
+  if (k_cmp_lo)
+    return fail(NSA_ERR_UNSUPPORTED, "cmp_attn_fwd: the hi + lo key form needs the bf16 tensor-core path (see nsa_cmp_attn_exact_supported)");
   NSA_NO_QUERY_OFFSET("cmp_attn_fwd");
   AttnArgs a = {};
   a.q = q; a.k = k_cmp; a.v = v_cmp; a.o = out; a.L = L; a.M = M; a.block_ends = block_ends;
   fill_fwd_strides(a, strides);
   a.B = B; a.H = H; a.G = G; a.Tq = T; a.Tk = NB; a.dk = dk; a.dv = dv; a.scale = scale; a.causal = 1;
   return launch_attn_generic(a, kCmp, dtype, false, (cudaStream_t)stream);
+}
+
+extern "C" NSA_API int nsa_cmp_attn_exact_supported(int B, int H, int G, int T, int NB, int dk, int dv, int dtype) {
+  return dtype == NSA_BF16 && B > 0 && fa_fwd_sm100_supported(H, G, T, NB, dk, dv) && (int64_t)B * (H / 2) <= 65535 ? 1 : 0;
 }
 
 extern "C" NSA_API int nsa_cmp_attn_bwd(const void* q, const void* k_cmp, const void* v_cmp, const int32_t* block_ends,

@@ -68,10 +68,14 @@ __device__ __forceinline__ void row_bounds(const FaFwdParams& p, int t, int n0, 
   }
 }
 
-template <int DK, int DV, int MODE>
+// EXACT (compressed branch only): the keys come as a bf16 pair hi + lo whose sum is the fp32 key to 16 mantissa bits; S =
+// Q K_hi^T + Q K_lo^T, so the log-sum-exp this kernel emits (lse2, log2 units) is the one the selection scoring needs and
+// that kernel can skip its own first sweep.  The two K stages then hold the hi and the lo part of ONE tile (the next
+// tile's keys are fetched while the softmax warps work, once both heads' S MMAs have read the current ones).
+template <int DK, int DV, int MODE, bool EXACT>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-              const __grid_constant__ CUtensorMap tmV, const FaFwdParams p) {
+              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKlo, const FaFwdParams p) {
   using SM = FaSmem<DK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -111,6 +115,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     w.ntiles = poisoned ? 0 : jhi - w.jlo + 1;
     return w;
   };
+
+  // K stage and barrier phase of the tile with running index c: two alternating stages, or (EXACT) one double-width stage
+  auto kslot = [](int c) { return EXACT ? 0 : (c & 1); };
+  auto kphase = [](int c) { return EXACT ? (c & 1) : ((c >> 1) & 1); };
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->q_full, 1);
@@ -165,18 +173,21 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       __syncwarp();
       q_pending = true;
       for (int j = 0; j < w.ntiles && ok; ++j, ++kc) {
-        const int n0 = (w.jlo + j) * kBN, ks = kc & 1;
-        ok = mbar_wait_warp(&bar->k_empty[ks], ((kc >> 1) & 1) ^ 1, abort);
+        const int n0 = (w.jlo + j) * kBN, ks = kslot(kc);
+        ok = mbar_wait_warp(&bar->k_empty[ks], kphase(kc) ^ 1, abort);
         if (!ok) break;
         if (elect_one()) {
-          mbar_arrive_expect_tx(&bar->k_full[ks], SM::kKBytes);
+          mbar_arrive_expect_tx(&bar->k_full[ks], EXACT ? 2 * SM::kKBytes : SM::kKBytes);
           for (int hf = 0; hf < 2; ++hf)
             tma_load_2d(&tmK, &bar->k_full[ks], sK + ks * SM::kKBytes + hf * (DK * 128), n0 + hf * 64, (w.b * p.G + w.g) * DK);
+          if (EXACT)
+            for (int hf = 0; hf < 2; ++hf)
+              tma_load_2d(&tmKlo, &bar->k_full[ks], sK + SM::kKBytes + hf * (DK * 128), n0 + hf * 64, (w.b * p.G + w.g) * DK);
         }
         __syncwarp();
         ok = mbar_wait_warp(&bar->v_empty, (kc & 1) ^ 1, abort);
         if (!ok) {
-          if (lane == 0) mbar_wait(&bar->k_full[ks], (kc >> 1) & 1, abort);
+          if (lane == 0) mbar_wait(&bar->k_full[ks], kphase(kc), abort);
           break;
         }
         if (elect_one()) {
@@ -191,7 +202,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (!ok && lane == 0) {
       // let copies already in flight land before the CTA gives its shared memory back
       if (q_pending) mbar_wait(&bar->q_full, ic & 1, abort);
-      for (int c = max(0, kc - 2); c < kc; ++c) mbar_wait(&bar->k_full[c & 1], (c >> 1) & 1, abort);
+      for (int c = max(0, kc - (EXACT ? 1 : 2)); c < kc; ++c) mbar_wait(&bar->k_full[kslot(c)], kphase(c), abort);
       if (kc > 0) mbar_wait(&bar->v_full, (kc - 1) & 1, abort);
     }
   } else if (warp == 9) {
@@ -208,6 +219,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int kk = 0; kk < DK / 16; ++kk)
         umma_ss(tmem + i * 128, desc_advance(dQ, (kk >> 2) * (kBM * 128) + (kk & 3) * 32), desc_advance(dK, kk * 2048), idQK,
                 kk > 0);
+      if (EXACT) {
+        const uint64_t dKl = desc_advance(dK0, SM::kKBytes);
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + i * 128, desc_advance(dQ, (kk >> 2) * (kBM * 128) + (kk & 3) * 32), desc_advance(dKl, kk * 2048), idQK, 1);
+      }
       umma_commit(&bar->s_full[i]);
     };
     bool ok = true;
@@ -215,13 +232,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
       const Item w = item_at(it);
       if (w.ntiles <= 0) continue;
-      ok = mbar_wait_warp(&bar->q_full, ic & 1, abort) && mbar_wait_warp(&bar->k_full[kc & 1], (kc >> 1) & 1, abort);
+      ok = mbar_wait_warp(&bar->q_full, ic & 1, abort) && mbar_wait_warp(&bar->k_full[kslot(kc)], kphase(kc), abort);
       if (!ok) break;
       tc_fence_after();
       if (elect_one()) {
-        issue_qk(0, kc & 1);
-        issue_qk(1, kc & 1);
-        umma_commit(&bar->k_empty[kc & 1]);
+        issue_qk(0, kslot(kc));
+        issue_qk(1, kslot(kc));
+        umma_commit(&bar->k_empty[kslot(kc)]);
       }
       __syncwarp();
       for (int j = 0; j < w.ntiles && ok; ++j, ++kc) {
@@ -236,7 +253,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ok = mbar_wait_warp(&bar->p_full[i], kc & 1, abort);
           if (ok && j == 0) ok = mbar_wait_warp(&bar->o_free[i], (ic & 1) ^ 1, abort);  // O_i of the item before was read out
           if (!ok) break;
-          const int ks = (kc + 1) & 1;
+          const int ks = kslot(kc + 1);
           tc_fence_after();
           if (elect_one()) {
 #pragma unroll
@@ -248,7 +265,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           __syncwarp();
           if (more) {
             if (i == 0) {
-              ok = mbar_wait_warp(&bar->k_full[ks], ((kc + 1) >> 1) & 1, abort);
+              ok = mbar_wait_warp(&bar->k_full[ks], kphase(kc + 1), abort);
               if (!ok) break;
               tc_fence_after();
             }
@@ -400,6 +417,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       if (p.L) p.L[row] = l > 0.f ? logf(l) + (m_ref - m_true) * kLn2 : -CUDART_INF_F;
       if (p.M) p.M[row] = m_true * kLn2;  // back from log2 units to the natural-log scale of the logits
+      if (p.lse2) p.lse2[row] = l > 0.f ? m_ref + log2f(l) : CUDART_INF_F;   // log-sum-exp in log2 units (+inf: the row saw nothing)
     }
     tc += ntiles;
     }  // items
@@ -481,17 +499,17 @@ static int sm_count() {
   return cached[dev];
 }
 
-template <int DK, int DV, int MODE>
-static int launch_fa_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaFwdParams& p,
-                           cudaStream_t st) {
+template <int DK, int DV, int MODE, bool EXACT>
+static int launch_fa_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tklo,
+                           const FaFwdParams& p, cudaStream_t st) {
   using SM = FaSmem<DK, DV>;
-  auto kern = fa_fwd_kernel<DK, DV, MODE>;
+  auto kern = fa_fwd_kernel<DK, DV, MODE, EXACT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kDynamic);
   if (e != cudaSuccess) return fail(NSA_ERR_LAUNCH, "fa_fwd: cannot reserve %d bytes of shared memory: %s", SM::kDynamic, cudaGetErrorString(e));
   const int nitems = (p.Tq / kBM) * p.B * (p.H / 2);
   dim3 grid((unsigned)std::min(nitems, sm_count()));   // persistent: one CTA per SM walks the item list
-  KernelTimer kt(MODE == kWin ? "fa_fwd_win" : "fa_fwd_cmp", st);
-  kern<<<grid, kFaThreads, SM::kDynamic, st>>>(tq, tk, tv, p);
+  KernelTimer kt(MODE == kWin ? "fa_fwd_win" : (EXACT ? "fa_fwd_cmp_exact" : "fa_fwd_cmp"), st);
+  kern<<<grid, kFaThreads, SM::kDynamic, st>>>(tq, tk, tv, tklo, p);
   return check_launch("fa_fwd_sm100");
 }
 
@@ -502,22 +520,27 @@ bool fa_fwd_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv) {
 
 int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L, float* M, int B, int H, int G, int Tq,
                  int Tk, int dk, int dv, int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale,
-                 cudaStream_t st) {
+                 const void* k_lo, float* lse2, cudaStream_t st) {
   if (!fa_fwd_sm100_supported(H, G, Tq, Tk, dk, dv)) return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: unsupported shape");
   if (!fa_timeout_counter()) return fail(NSA_ERR_LAUNCH, "fa_fwd_sm100: cannot set up the time-out record of this device");
   if ((int64_t)B * (H / 2) * (Tq / kBM) > 0x7fffffff) return fail(NSA_ERR_UNSUPPORTED, "fa_fwd_sm100: too many work items");
-  CUtensorMap tq, tk, tv;
+  if (k_lo && mode != kCmp) return fail(NSA_ERR_ARG, "fa_fwd_sm100: a low-order key part belongs to the compressed branch");
+  CUtensorMap tq, tk, tv, tklo;
   if (int rc = make_tmap_bf16_2d(&tq, q, (uint64_t)B * H * Tq, dk, kBM)) return rc;
   if (int rc = make_tmap_bf16_2d(&tk, k, (uint64_t)B * G * dk, Tk, dk)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tklo, k_lo ? k_lo : k, (uint64_t)B * G * dk, Tk, dk)) return rc;
   if (int rc = make_tmap_bf16_2d(&tv, v, (uint64_t)B * G * Tk, dv, kBN)) return rc;
   FaFwdParams p;
   p.o = (__nv_bfloat16*)o; p.L = L; p.M = M;
   p.B = B; p.H = H; p.G = G; p.Tq = Tq; p.Tk = Tk;
   p.window = window; p.cmp_l = cmp_l; p.cmp_d = cmp_d; p.cmp_nb = cmp_nb;
   p.scale_log2 = scale * 1.4426950408889634f;
-#define NSA_FA_CASE(DK_, DV_)                                                                   \
-  if (dk == DK_ && dv == DV_)                                                                   \
-    return mode == kWin ? launch_fa_fwd_t<DK_, DV_, kWin>(tq, tk, tv, p, st) : launch_fa_fwd_t<DK_, DV_, kCmp>(tq, tk, tv, p, st);
+  p.lse2 = lse2;
+#define NSA_FA_CASE(DK_, DV_)                                                                                            \
+  if (dk == DK_ && dv == DV_)                                                                                            \
+    return mode == kWin ? launch_fa_fwd_t<DK_, DV_, kWin, false>(tq, tk, tv, tklo, p, st)                               \
+                        : (k_lo ? launch_fa_fwd_t<DK_, DV_, kCmp, true>(tq, tk, tv, tklo, p, st)                          \
+                                : launch_fa_fwd_t<DK_, DV_, kCmp, false>(tq, tk, tv, tklo, p, st));
   NSA_FA_CASE(192, 128)
   NSA_FA_CASE(128, 128)
   NSA_FA_CASE(64, 64)

@@ -11,6 +11,7 @@ namespace nsa {
 struct FaFwdParams {
   __nv_bfloat16* o;  // [B,H,Tq,dv] contiguous
   float *L, *M;      // [B,H,Tq] contiguous, may be null
+  float* lse2;       // [B,H,Tq] log-sum-exp of the scaled logits in log2 units (+inf for rows that see nothing), may be null
   int B, H, G, Tq, Tk;
   int window;                // sliding window: keys (t-window, t]
   int cmp_l, cmp_d, cmp_nb;  // compressed tokens: key i visible iff i < cmp_nb and i*cmp_d + cmp_l - 1 <= t
@@ -21,9 +22,11 @@ struct FaFwdParams {
 bool fa_fwd_sm100_supported(int H, int G, int Tq, int Tk, int dk, int dv);
 
 // q [B,H,Tq,dk], k [B,G,dk,Tk], v [B,G,Tk,dv], o [B,H,Tq,dv]: contiguous bf16.  mode = kWin or kCmp.
+// k_lo (compressed branch, or null): low-order bf16 part of the keys, S = Q (k + k_lo)^T; lse2 (or null): receives the
+// log-sum-exp in log2 units.
 int fa_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* L, float* M, int B, int H, int G, int Tq,
                  int Tk, int dk, int dv, int mode, int window, int cmp_l, int cmp_d, int cmp_nb, float scale,
-                 cudaStream_t st);
+                 const void* k_lo, float* lse2, cudaStream_t st);
 
 // Backward of the same two branches.  Adds into dk [B,G,Tk,dk] and dv [B,G,Tk,dv] (time-major, bf16),
 // overwrites dq [B,H,Tq,dk].  Three launches: delta/lse preparation, a query-stationary dQ kernel and
@@ -49,9 +52,12 @@ int make_tmap_head_rows(::CUtensorMap_st* map, const void* base, uint64_t heads_
 // q bf16 [B,H,T,dk] contiguous, compressed block i ends at i*d + l - 1 for i < nb and is never visible beyond.
 bool score_sm100_supported(int H, int G, int T, int dk, int nbp, int l, int d, int lprime, int n);
 size_t score_sm100_workspace_bytes(int B, int G, int T, int dk, int nbp, int d, int lprime);
+// lse2 (or null): the log-sum-exp [B,H,T] (log2 units, +inf for rows without a visible block) of the scaled logits over
+// the visible compressed blocks, when the caller has it from the compressed attention's forward with hi + lo keys; the
+// kernel then skips its own first sweep.
 int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
-                     int lprime, int nb, int n, int n_fixed, float scale, int q0, void* workspace, size_t workspace_bytes,
-                     cudaStream_t st);
+                     int lprime, int nb, int n, int n_fixed, float scale, int q0, const float* lse2, void* workspace,
+                     size_t workspace_bytes, cudaStream_t st);
 
 // Device address (on the current device) of the counter of CTAs that gave up on a barrier wait; the first call on a
 // device sets up that device's time-out record (null on failure).

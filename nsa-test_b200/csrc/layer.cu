@@ -52,6 +52,8 @@ void ctx_layout(const nsa_layer_desc& d, size_t off[NSA_CTX_PIECES + 1]) {
   put(NSA_CTX_K_CMP_LP, BG * d.dk * s.nbp * s.es);
   put(NSA_CTX_V_CMP, BG * s.nbp * d.dv * s.es);
   put(NSA_CTX_BLOCK_ENDS, (size_t)s.nbp * sizeof(int32_t));
+  put(NSA_CTX_K_CMP_LO, BG * d.dk * s.nbp * 2);
+  put(NSA_CTX_LSE2_CMP, s.stat_bytes);
   put(NSA_CTX_PHI_SAVED, s.nb > 0 ? nsa_cmp_phi_saved_bytes(d.B, d.G, d.T, d.l, d.d, d.U) : 256);
   off[NSA_CTX_PIECES] = o;
 }
@@ -189,13 +191,27 @@ extern "C" NSA_API int nsa_layer_fwd(const nsa_layer_desc* dp, const void* q, co
     cudaMemsetAsync(piece(NSA_CTX_K_CMP_LP), 0, BG * d.dk * s.nbp * s.es, st);
     cudaMemsetAsync(piece(NSA_CTX_V_CMP), 0, BG * s.nbp * d.dv * s.es, st);
   }
-  // 2. Eq. 8-11: which blocks every query attends
+  int64_t strides[26];
+  // 2. compressed attention.  On the tensor-core path it takes the keys as a bf16 pair hi + lo (the fp32 keys to 16
+  //    mantissa bits) and also emits the log-sum-exp of its logits, the normaliser the scoring needs: the scoring
+  //    kernel then makes one sweep over the compressed keys instead of two.
+  const bool exact = s.nb > 0 && nsa_cmp_attn_exact_supported(d.B, d.H, d.G, d.T, s.nbp, d.dk, d.dv, d.dtype) != 0;
+  float* lse2 = exact ? (float*)piece(NSA_CTX_LSE2_CMP) : nullptr;
+  void* k_lo = exact ? piece(NSA_CTX_K_CMP_LO) : nullptr;
+  if (exact)
+    if (int rc = nsa_split_keys_hi_lo(k_cmp, piece(NSA_CTX_K_CMP_LP), k_lo, (int64_t)BG * d.dk * s.nbp, stream)) return rc;
+  fill_strides(d, s.nbp, 0, false, false, strides);
+  if (int rc = nsa_cmp_attn_fwd(q, piece(NSA_CTX_K_CMP_LP), piece(NSA_CTX_V_CMP), be, piece(NSA_CTX_O_CMP), (float*)piece(NSA_CTX_L_CMP),
+                                (float*)piece(NSA_CTX_M_CMP), strides, d.B, d.H, d.G, d.T, s.nbp, d.dk, d.dv, d.scale, d.dtype, d.l, d.d,
+                                s.nb, 0, 0, k_lo, lse2, stream))
+    return rc;
+  // 3. Eq. 8-11: which blocks every query attends
   if (indices_in) {
     cudaMemcpyAsync(idx, indices_in, BG * d.T * d.n * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
   } else {
     const int64_t qs[4] = {(int64_t)d.H * d.T * d.dk, (int64_t)d.T * d.dk, d.dk, 1};
     if (int rc = nsa_score_topn(q, qs, k_cmp, be, idx, d.B, d.H, d.G, d.T, d.dk, s.nbp, d.l, d.d, d.l_prime, d.n, d.n_fixed, d.scale,
-                                d.dtype, s.nb, 0, 0, workspace, workspace_bytes, stream))
+                                d.dtype, s.nb, 0, 0, lse2, workspace, workspace_bytes, stream))
       return rc;
   }
   {
@@ -203,13 +219,7 @@ extern "C" NSA_API int nsa_layer_fwd(const nsa_layer_desc* dp, const void* q, co
     selection_fallback_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(idx, rows, d.T, d.n, d.l_prime);
   }
   if (int rc = check_launch("layer_fwd")) return rc;
-  int64_t strides[26];
-  // 3. compressed attention (bf16 copy of the compressed keys), 4. sliding window
-  fill_strides(d, s.nbp, 0, false, false, strides);
-  if (int rc = nsa_cmp_attn_fwd(q, piece(NSA_CTX_K_CMP_LP), piece(NSA_CTX_V_CMP), be, piece(NSA_CTX_O_CMP), (float*)piece(NSA_CTX_L_CMP),
-                                (float*)piece(NSA_CTX_M_CMP), strides, d.B, d.H, d.G, d.T, s.nbp, d.dk, d.dv, d.scale, d.dtype, d.l, d.d,
-                                s.nb, 0, 0, stream))
-    return rc;
+  // 4. sliding window
   fill_strides(d, d.T, 0, false, false, strides);
   if (int rc = nsa_sliding_fwd(q, k_win, v_win, piece(NSA_CTX_O_WIN), (float*)piece(NSA_CTX_L_WIN), (float*)piece(NSA_CTX_M_WIN), strides,
                                d.B, d.H, d.G, d.T, d.dk, d.dv, d.window, d.scale, d.dtype, 0, stream))

@@ -34,6 +34,7 @@ struct ScoreParams {
   int q0;        // position of query row 0 in the sequence (query-sharded runs; 0 otherwise)
   float scale_log2;
   int* timeouts;
+  const float* lse2_ext;  // [B,H,T] log-sum-exp (log2 units) from the compressed attention's exact forward, or null (own first sweep)
 };
 
 __global__ void split_hi_lo_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
@@ -73,6 +74,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int kmax = tl >= p.l - 1 ? min(p.nb - 1, (tl - p.l + 1) / p.d) : -1;
   const int ntiles = max(1, kmax / 128 + 1);
   const int steps_per_pass = ntiles * hpg;
+  const int nsteps = (p.lse2_ext ? 1 : 2) * steps_per_pass;   // with the log-sum-exp given, only the probability sweep runs
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->k_full, 1);
@@ -106,7 +108,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     bool ok = true;
     int kissued = 0, qissued = 0;
     int kt = 0, hh = 0;
-    for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
+    for (int step = 0; step < nsteps && ok; ++step) {
       if (hh == 0) {
         const int kidx = kissued;  // K tile loads so far
         ok = mbar_wait_warp(&bar->k_empty, (kidx & 1) ^ 1, abort);
@@ -147,7 +149,7 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint64_t dKlo = smem_desc_sw128(smem_u32(sKlo), DK * 128, 1024);
     bool ok = true;
     int hh = 0, ktiles = 0;
-    for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
+    for (int step = 0; step < nsteps && ok; ++step) {
       const int s = step & 1;
       if (hh == 0) ok = mbar_wait_warp(&bar->k_full, ktiles & 1, abort);
       ok = ok && mbar_wait_warp(&bar->q_full[s], (step >> 1) & 1, abort);
@@ -193,8 +195,8 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     float agg[128];     // pass A: scaled logits of the current tile; pass B: per-key probability sums over heads
     float cur = 0.f;    // running stencil sum of the selection block being assembled
-    for (int step = 0; step < 2 * steps_per_pass && ok; ++step) {
-      const int pass = step / steps_per_pass, within = step % steps_per_pass, kt = within / hpg, hh = within % hpg, s = step & 1;
+    for (int step = 0; step < nsteps && ok; ++step) {
+      const int pass = p.lse2_ext ? 1 : step / steps_per_pass, within = step % steps_per_pass, kt = within / hpg, hh = within % hpg, s = step & 1;
       if ((step & 1) != wg) continue;
       const int n0 = kt * 128;
       const int chi = vis - n0;
@@ -236,8 +238,13 @@ score_topn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           st_m[hh * 128 + r] = mx;
         }
       } else {
-        const float m_h = st_m[hh * 128 + r], l_h = st_l[hh * 128 + r];
-        const float lse2 = l_h > 0.f ? m_h + log2f(l_h) : CUDART_INF_F;
+        float lse2;
+        if (p.lse2_ext) {
+          lse2 = p.lse2_ext[((int64_t)b * p.H + g * hpg + hh) * p.T + t];
+        } else {
+          const float m_h = st_m[hh * 128 + r], l_h = st_l[hh * 128 + r];
+          lse2 = l_h > 0.f ? m_h + log2f(l_h) : CUDART_INF_F;
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t sv[32];
@@ -500,8 +507,8 @@ static int launch_score_t(const CUtensorMap& tq, const CUtensorMap& thi, const C
 }
 
 int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
-                     int lprime, int nb, int n, int n_fixed, float scale, int q0, void* workspace, size_t workspace_bytes,
-                     cudaStream_t st) {
+                     int lprime, int nb, int n, int n_fixed, float scale, int q0, const float* lse2, void* workspace,
+                     size_t workspace_bytes, cudaStream_t st) {
   if (!score_sm100_supported(H, G, T, dk, nbp, l, d, lprime, n)) return fail(NSA_ERR_UNSUPPORTED, "score_topn_sm100: unsupported shape");
   const size_t need = score_sm100_workspace_bytes(B, G, T, dk, nbp, d, lprime);
   if (!workspace || workspace_bytes < need)
@@ -527,6 +534,7 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
   p.B = B; p.H = H; p.G = G; p.T = T; p.nbp = nbp; p.l = l; p.d = d; p.lprime = lprime; p.nb = nb; p.n_sel = n_sel;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.timeouts = fa_timeout_counter();
+  p.lse2_ext = lse2;
   int rc;
   if (dk == 192) rc = launch_score_t<192>(tq, thi, tlo, p, st);
   else if (dk == 128) rc = launch_score_t<128>(tq, thi, tlo, p, st);
@@ -555,3 +563,13 @@ int score_topn_sm100(const void* q, const float* k_cmp, int32_t* out, int B, int
 
 }  // namespace nsa
 
+
+
+// fp32 -> bf16 pair (hi = the rounded value, lo = the rounded remainder): what the exact compressed-attention forward and
+// the scoring kernel take as keys
+extern "C" NSA_API int nsa_split_keys_hi_lo(const float* x, void* hi, void* lo, int64_t n, void* stream) {
+  NSA_REQUIRE(x && hi && lo && n >= 0, "split_keys_hi_lo: bad arguments");
+  if (n == 0) return NSA_OK;
+  nsa::split_hi_lo_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n);
+  return nsa::check_launch("split_keys_hi_lo");
+}

@@ -251,7 +251,7 @@ extern "C" NSA_API size_t nsa_score_topn_workspace_bytes(int B, int H, int G, in
 extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const float* k_cmp, const int32_t* block_ends,
                               int32_t* indices_out, int B, int H, int G, int T, int dk, int nbp, int l, int d,
                               int l_prime, int n, int n_fixed, float scale, int dtype, int n_real_blocks, int q_pos0, int flags,
-                              void* workspace, size_t workspace_bytes, void* stream) {
+                              const float* cmp_lse2, void* workspace, size_t workspace_bytes, void* stream) {
   NSA_REQUIRE(q && qs && k_cmp && block_ends && indices_out, "score_topn: null pointer");
   NSA_REQUIRE(q_pos0 >= 0, "score_topn: negative query offset");
   if (timeout_flagged())
@@ -259,7 +259,7 @@ extern "C" NSA_API int nsa_score_topn(const void* q, const int64_t* qs, const fl
                 "since then are invalid.  nsa_device_timeouts(1) reports and clears the condition");
   if (B > 0 && T > 0 && score_tc_ok(q, qs, B, H, G, T, dk, nbp, l, d, l_prime, n, n_real_blocks, dtype, flags))
     return score_topn_sm100(q, k_cmp, indices_out, B, H, G, T, dk, nbp, l, d, l_prime, n_real_blocks, n, n_fixed, scale,
-                            q_pos0, workspace, workspace_bytes, (cudaStream_t)stream);
+                            q_pos0, cmp_lse2, workspace, workspace_bytes, (cudaStream_t)stream);
   NSA_REQUIRE(G > 0 && H % G == 0 && d > 0 && l % d == 0 && l_prime % d == 0 && l > 0 && l_prime > 0,
               "score_topn: bad block parameters");
   NSA_REQUIRE(n > 0 && n <= kMaxN, "score_topn: n=%d outside 1..%d", n, kMaxN);

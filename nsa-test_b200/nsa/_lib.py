@@ -37,7 +37,7 @@ class LayerDesc(ctypes.Structure):
 
 # pieces of the layer's context buffer, in the order of enum nsa_layer_ctx_piece
 CTX_PIECES = ("o_cmp", "L_cmp", "M_cmp", "o_slc", "L_slc", "M_slc", "o_win", "L_win", "M_win", "gates", "indices", "k_cmp",
-              "k_cmp_lp", "v_cmp", "block_ends", "phi_saved")
+              "k_cmp_lp", "v_cmp", "block_ends", "k_cmp_lo", "lse2_cmp", "phi_saved")
 _DESCP = POINTER(LayerDesc)
 
 # name -> (restype, argtypes); mirrors include/nsa_b200.h declaration by declaration
@@ -52,7 +52,9 @@ PROTOTYPES = {
     "nsa_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 10),
     "nsa_sliding_bwd": (c_int, [_P] * 10 + [_I64P] + [c_int] * 7 + [c_float, c_int, _P, c_int, _P, c_size_t, _P]),
     "nsa_sliding_bwd_noalloc": (c_int, [_P] * 10 + [c_int] * 7 + [c_float, _P]),
-    "nsa_cmp_attn_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 7 + [c_float] + [c_int] * 6 + [_P]),
+    "nsa_cmp_attn_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 7 + [c_float] + [c_int] * 6 + [_P, _P, _P]),
+    "nsa_cmp_attn_exact_supported": (c_int, [c_int] * 8),
+    "nsa_split_keys_hi_lo": (c_int, [_P, _P, _P, c_int64, _P]),
     "nsa_cmp_attn_bwd": (c_int, [_P] * 11 + [_I64P] + [c_int] * 7 + [c_float] + [c_int] * 5 + [_P, c_int, _P, c_size_t, _P]),
     "nsa_slc_fwd_workspace_bytes": (c_size_t, [c_int] * 11),
     "nsa_slc_fwd": (c_int, [_P] * 7 + [_I64P] + [c_int] * 9 + [c_float, c_int, c_int, c_int, _P, c_size_t, _P]),
@@ -72,7 +74,7 @@ PROTOTYPES = {
     "nsa_phi_pool_fwd": (c_int, [_P, _P, _P, _I64P, _P, _P] + [c_int] * 10 + [_P]),
     "nsa_phi_pool_bwd": (c_int, [_P] * 7 + [c_int] * 9 + [_P]),
     "nsa_score_topn_workspace_bytes": (c_size_t, [c_int] * 12),
-    "nsa_score_topn": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 11 + [c_float, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
+    "nsa_score_topn": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 11 + [c_float, c_int, c_int, c_int, c_int, _P, _P, c_size_t, _P]),
     "nsa_topn_from_scores": (c_int, [_P, _P] + [c_int] * 8 + [_P]),
     "nsa_cmp_probs": (c_int, [_P, _I64P, _P, _P, _P] + [c_int] * 6 + [c_float, c_int, _P]),
     "nsa_eq9_scores": (c_int, [_P, _P, c_int64] + [c_int] * 4 + [_P]),

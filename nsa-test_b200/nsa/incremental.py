@@ -132,15 +132,24 @@ def nsa_layer_incremental(q_new: torch.Tensor, gate_logits_new: torch.Tensor, ca
     nb = cache.n_blocks
 
     G = c.n_kv_groups
+    blocks = (c.l, c.d, nb)
     if Tn < rows and B * G * Tn <= _FEW_ROWS:
         # A handful of rows (decode): the tile kernel would run one CTA per (sequence, group) over all compressed
         # blocks; unpadded rows take the generic scoring path, whose q.k products spread over the whole GPU.
         real = ops.score_topn(q_new.contiguous(), cache.k_cmp, cache.block_ends, c.l, c.d, c.l_prime, c.n, n_fixed, scale,
                               nb, pos)
         indices = torch.cat([real, real.new_full((B, G, rows - Tn, c.n), -1)], dim=2)
+        o_cmp, _, _ = ops.cmp_attn_fwd(q, cache.k_cmp_lp, cache.v_cmp, cache.block_ends, scale, blocks, pos)
+    elif ops.cmp_exact_supported(q, cache.k_cmp_lp, cache.v_cmp):
+        # as the full-sequence layer does it: the compressed attention runs on the fp32 keys (as bf16 hi + lo halves)
+        # and hands its log-sum-exp to the scoring kernel, so the two agree on every row, near-ties included
+        hi, lo = ops.split_keys(cache.k_cmp)
+        o_cmp, _, _, lse2 = ops.cmp_attn_fwd(q, hi, cache.v_cmp, cache.block_ends, scale, blocks, pos, k_lo=lo)
+        indices = ops.score_topn(q, cache.k_cmp, cache.block_ends, c.l, c.d, c.l_prime, c.n, n_fixed, scale, nb, pos,
+                                 cmp_lse2=lse2)
     else:
         indices = ops.score_topn(q, cache.k_cmp, cache.block_ends, c.l, c.d, c.l_prime, c.n, n_fixed, scale, nb, pos)
-    o_cmp, _, _ = ops.cmp_attn_fwd(q, cache.k_cmp_lp, cache.v_cmp, cache.block_ends, scale, (c.l, c.d, nb), pos)
+        o_cmp, _, _ = ops.cmp_attn_fwd(q, cache.k_cmp_lp, cache.v_cmp, cache.block_ends, scale, blocks, pos)
     idx = _selection_fallback(indices, c.l_prime, pos).to(torch.int32).contiguous()
     o_slc, _, _ = ops.slc_fwd(q, cache.k_slc, cache.v_slc, idx, c.l_prime, scale, pos)
 

@@ -190,9 +190,23 @@ class _BranchesAndMix(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k_cmp, v_cmp, block_ends, k_slc, v_slc, indices, k_win, v_win, gate_logits, scale, config, blocks,
-                q_pos0=0, token_major=False):
+                q_pos0=0, token_major=False, k_cmp_f32=None):
         Tq = q.shape[2]
-        o_cmp, Lc, Mc = ops.cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale, blocks, q_pos0)
+        # ``indices`` None: the blocks are chosen here (Eq. 8-11) from the fp32 compressed keys ``k_cmp_f32``.  Where the
+        # tensor-core kernels apply, the compressed attention runs on the keys as a bf16 pair hi + lo and hands its
+        # log-sum-exp to the scoring kernel, which then sweeps the compressed keys once instead of twice.
+        lse2 = None
+        if indices is None and k_cmp_f32 is not None and blocks is not None and ops.cmp_exact_supported(q, k_cmp, v_cmp):
+            hi, lo = ops.split_keys(k_cmp_f32)
+            o_cmp, Lc, Mc, lse2 = ops.cmp_attn_fwd(q, hi, v_cmp, block_ends, scale, blocks, q_pos0, k_lo=lo)
+            k_cmp = hi
+        else:
+            o_cmp, Lc, Mc = ops.cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale, blocks, q_pos0)
+        if indices is None:
+            n_fixed = config.n_fixed if config.include_fixed_in_selection else 0
+            indices = ops.score_topn(q, k_cmp_f32, block_ends, config.l, config.d, config.l_prime, config.n, n_fixed, scale,
+                                     blocks[2], q_pos0, cmp_lse2=lse2)
+        ctx.chosen = indices
         idx = _selection_fallback(indices, config.l_prime, q_pos0).to(torch.int32).contiguous()
         lo, hi, pad = _window_slice(q_pos0, Tq, k_win.shape[-1], config.w)
         if pad or lo or hi != k_win.shape[-1]:
@@ -209,8 +223,8 @@ class _BranchesAndMix(torch.autograd.Function):
         ctx.scale, ctx.l_prime, ctx.w, ctx.blocks = scale, config.l_prime, config.w, blocks
         ctx.gate_mode, ctx.ldtype = config.gate_mode, gate_logits.dtype
         ctx.q_pos0, ctx.win = q_pos0, (lo, hi, pad, tuple(k_win.shape), tuple(v_win.shape))
-        ctx.mark_non_differentiable(gates, o_cmp, o_slc, o_win)
-        return out, gates, o_cmp, o_slc, o_win
+        ctx.mark_non_differentiable(gates, o_cmp, o_slc, o_win, indices)
+        return out, gates, o_cmp, o_slc, o_win, indices
 
     @staticmethod
     def backward(ctx, dout, *_unused):
@@ -240,7 +254,7 @@ class _BranchesAndMix(torch.autograd.Function):
         dq, dks, dvs = ops.slc_bwd(q, k_slc, v_slc, idx, o_slc, d_slc, Ls, Ms, ctx.l_prime, ctx.scale, ctx.q_pos0,
                                    dq_addends=(dq_c, dq_w), row_delta=delta[1])
         return (dq, dkc.transpose(-1, -2), dvc, None, dks.transpose(-1, -2), dvs, None, dkw, dvw,
-                dlogits.to(ctx.ldtype), None, None, None, None, None)
+                dlogits.to(ctx.ldtype), None, None, None, None, None, None)
 
 
 class _LayerC(torch.autograd.Function):
@@ -492,15 +506,11 @@ def nsa_layer(q, k_slc, v_slc, gate_logits, phi_params, config: NSAConfig, *, kv
         k_cmp = F.pad(k_cmp[..., :nb].float(), (0, nbp - nb))
         v_cmp = F.pad(v_cmp[:, :, :nb], (0, 0, 0, nbp - nb))
     block_ends = _block_ends(k_cmp.shape[-1], nb, cfg.l, cfg.d, q.device)
-    n_fixed = cfg.n_fixed if cfg.include_fixed_in_selection else 0
-    if indices is None:
-        indices = ops.score_topn(q.detach(), k_cmp.detach(), block_ends, cfg.l, cfg.d, cfg.l_prime, cfg.n, n_fixed, scale,
-                                 nb, q_pos0)
-    else:
+    if indices is not None:
         indices = indices.to(device=q.device, dtype=torch.int32).contiguous()
-    out, gates, o_cmp, o_slc, o_win = _BranchesAndMix.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, k_slc, v_slc, indices,
-                                                            kw, vw, gate_logits, scale, cfg, (cfg.l, cfg.d, nb), q_pos0,
-                                                            token_major_out)
+    out, gates, o_cmp, o_slc, o_win, indices = _BranchesAndMix.apply(q, k_cmp.to(q.dtype), v_cmp, block_ends, k_slc, v_slc, indices,
+                                                                     kw, vw, gate_logits, scale, cfg, (cfg.l, cfg.d, nb), q_pos0,
+                                                                     token_major_out, k_cmp.detach())
     if return_info:
         return out, dict(indices=indices, gates=gates, k_cmp=k_cmp, v_cmp=v_cmp, block_ends=block_ends,
                          o_cmp=o_cmp, o_slc=o_slc, o_win=o_win)
@@ -740,7 +750,7 @@ class _Launcher:
                                              dk, dv, int(a["WINDOW_SIZE"]), scale, code, 0, st)
                 elif kind == "cmp":
                     rc = lib.nsa_cmp_attn_fwd(ptr(Q), ptr(K), ptr(V), ptr(be), ptr(Out), ptr(L), ptr(M), i64(strides), B, H,
-                                              G, Tq, Tk, dk, dv, scale, code, 0, 0, 0, 0, 0, st)
+                                              G, Tq, Tk, dk, dv, scale, code, 0, 0, 0, 0, 0, None, None, st)
                 else:
                     n, lp = int(a["N_BLOCKS"]), int(a["BLOCK_SIZE_SELECTION"])
                     nbytes = lib.nsa_slc_fwd_workspace_bytes(B, H, G, Tq, Tk, dk, dv, n, lp, code, 0)

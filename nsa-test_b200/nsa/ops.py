@@ -87,21 +87,42 @@ def _delta_ptr(row_delta, q):
     return d, ptr(d)
 
 
-def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None, q_pos0: int = 0, generic: bool = False):
+def cmp_exact_supported(q, k_cmp, v_cmp) -> bool:
+    """Does this shape admit the hi + lo key form of the compressed attention's forward (bf16 tensor-core path)?"""
+    B, H, T, dk = q.shape
+    return q.dtype == torch.bfloat16 and bool(lib.nsa_cmp_attn_exact_supported(B, H, k_cmp.shape[1], T, k_cmp.shape[-1], dk,
+                                                                              v_cmp.shape[-1], dtype_code(q)))
+
+
+def split_keys(k_cmp_f32):
+    """fp32 compressed keys -> (hi, lo) bf16 with hi + lo equal to the fp32 value to 16 mantissa bits."""
+    dev = require_cuda(k_cmp_f32)
+    x = k_cmp_f32.float().contiguous()
+    hi = torch.empty(x.shape, device=dev, dtype=torch.bfloat16)
+    lo = torch.empty(x.shape, device=dev, dtype=torch.bfloat16)
+    with torch.cuda.device(dev):
+        check(lib.nsa_split_keys_hi_lo(ptr(x), ptr(hi), ptr(lo), x.numel(), stream_ptr(dev)), "nsa_split_keys_hi_lo")
+    return hi, lo
+
+
+def cmp_attn_fwd(q, k_cmp, v_cmp, block_ends, scale: float, blocks=None, q_pos0: int = 0, generic: bool = False, k_lo=None):
     """``blocks=(l, d, n_blocks)`` asserts block_ends[i] == i*d + l - 1 for i < n_blocks and no later block
-    ever visible; it lets the tensor-core kernel bound its key loop."""
+    ever visible; it lets the tensor-core kernel bound its key loop.  ``k_lo`` (the low-order bf16 part of the keys,
+    k_cmp being the high-order one) selects the exact-key form; a fourth result, the log-sum-exp of the logits in log2
+    units (+inf on rows that see no block), is then returned for score_topn's ``cmp_lse2``."""
     bl, bd, bn = blocks if blocks is not None else (0, 0, 0)
     dev = require_cuda(q, k_cmp, v_cmp, block_ends)
     B, H, T, dk = q.shape
     G, NB, dv = k_cmp.shape[1], k_cmp.shape[-1], v_cmp.shape[-1]
     be = block_ends.to(torch.int32).contiguous()
     o, L, M = _stats(q, dv)
+    lse2 = torch.empty(B, H, T, device=dev, dtype=torch.float32) if k_lo is not None else None
     with torch.cuda.device(dev):
         check(lib.nsa_cmp_attn_fwd(ptr(q), ptr(k_cmp), ptr(v_cmp), ptr(be), ptr(o), ptr(L), ptr(M),
                                    i64(_fwd_strides(q, k_cmp, v_cmp, o, L, M)), B, H, G, T, NB, dk, dv, float(scale),
-                                   dtype_code(q), int(bl), int(bd), int(bn), int(q_pos0), _flags(generic), stream_ptr(dev)),
-              "nsa_cmp_attn_fwd")
-    return o, L, M
+                                   dtype_code(q), int(bl), int(bd), int(bn), int(q_pos0), _flags(generic), ptr(k_lo), ptr(lse2),
+                                   stream_ptr(dev)), "nsa_cmp_attn_fwd")
+    return (o, L, M) if k_lo is None else (o, L, M, lse2)
 
 
 def cmp_attn_bwd(q, k_cmp, v_cmp, block_ends, o, do, L, M, scale: float, blocks=None, q_pos0: int = 0, row_delta=None,
@@ -296,7 +317,7 @@ def phi_pool_bwd(a, c, dhbar, dv_cmp, l: int, d: int, n_blocks: int):
 
 
 def score_topn(q, k_cmp_f32, block_ends, l: int, d: int, l_prime: int, n: int, n_fixed: int, scale: float,
-               n_real_blocks: int = -1, q_pos0: int = 0, generic: bool = False):
+               n_real_blocks: int = -1, q_pos0: int = 0, generic: bool = False, cmp_lse2=None):
     """q [B,H,T,dk], k_cmp fp32 [B,G,dk,nbp] -> int32 indices [B,G,T,n].  ``n_real_blocks >= 0`` asserts the
     canonical block ends (block i ends at i*d + l - 1 for i < n_real_blocks, later blocks never visible)."""
     dev = require_cuda(q, k_cmp_f32, block_ends)
@@ -311,7 +332,7 @@ def score_topn(q, k_cmp_f32, block_ends, l: int, d: int, l_prime: int, n: int, n
     with torch.cuda.device(dev):
         check(lib.nsa_score_topn(ptr(q), i64(q.stride()), ptr(kc), ptr(be), ptr(out), B, H, G, T, dk, nbp, int(l), int(d),
                                  int(l_prime), int(n), int(n_fixed), float(scale), dtype_code(q), int(n_real_blocks),
-                                 int(q_pos0), _flags(generic), ptr(ws), nbytes, stream_ptr(dev)), "nsa_score_topn")
+                                 int(q_pos0), _flags(generic), ptr(cmp_lse2), ptr(ws), nbytes, stream_ptr(dev)), "nsa_score_topn")
     return out
 
 

@@ -493,3 +493,50 @@ def test_layer_entry_points_match_the_composed_branch_calls(shared_kv):
     assert torch.equal(g_c[0], g_p[0]) and torch.equal(g_c[3], g_p[3])          # dq, dlogits
     for a, b_ in zip(g_c[1:3] + g_c[4:], g_p[1:3] + g_p[4:]):
         _grad_close(a, b_.float().cpu(), "dk / dv / phi gradient")
+
+
+@pytest.mark.parametrize("dk,dv,H,G,T", [(64, 64, 4, 2, 2048), (192, 128, 4, 1, 4096 + 2048)])
+def test_compression_forward_on_split_keys_and_its_lse_in_scoring(dk, dv, H, G, T):
+    """fp32 compressed keys handed over as bf16 hi + lo halves: the output and statistics follow the oracle on the fp32
+    keys (closer than the bf16-key form can), the log-sum-exp equals the oracle's, and the scoring kernel that takes
+    that log-sum-exp selects exactly the blocks it selects when it computes the row statistics itself."""
+    from nsa import ops
+    l, d, lp, n = 32, 16, 64, 16
+    nb = (T - l) // d + 1
+    nbp = O.next_pow2(nb)
+    gen = torch.Generator().manual_seed(12)
+    q = torch.randn(1, H, T, dk, generator=gen).bfloat16()
+    kc = torch.zeros(1, G, dk, nbp)
+    kc[..., :nb] = torch.randn(1, G, dk, nb, generator=gen)
+    vc = torch.zeros(1, G, nbp, dv)
+    vc[:, :, :nb] = torch.randn(1, G, nb, dv, generator=gen)
+    vc = vc.bfloat16()
+    be = torch.full((nbp,), 999999, dtype=torch.int32)
+    be[:nb] = torch.arange(nb, dtype=torch.int32) * d + l - 1
+    scale = dk ** -0.5
+    qd, kd, vd, bed = q.to(DEV), kc.to(DEV), vc.to(DEV), be.to(DEV)
+    assert ops.cmp_exact_supported(qd, kd, vd)
+    hi, lo = ops.split_keys(kd)
+    assert (hi.float() + lo.float() - kd).abs().max() <= kd.abs().max() * 2.0 ** -16
+    o, L, M, lse2 = ops.cmp_attn_fwd(qd, hi, vd, bed, scale, blocks=(l, d, nb), k_lo=lo)
+    torch.cuda.synchronize()
+    _no_timeouts()
+    o_ref, M_ref, L_ref = O.compression_attention(q.float(), kc, vc.float(), be, scale, return_stats=True)
+    assert max_abs(o.float(), o_ref) < 2e-2
+    _check_stats(L, M, L_ref, M_ref)
+    fin = torch.isfinite(M_ref)
+    lse_ref = (M_ref + L_ref)[fin] * 1.4426950408889634        # L is the log of the row sum
+    assert torch.isinf(lse2.cpu()[~fin]).all() and (lse2.cpu()[~fin] > 0).all()
+    assert (lse2.cpu()[fin] - lse_ref).abs().max() < 2e-3
+    ids_own = ops.score_topn(qd, kd, bed, l, d, lp, n, 3, scale, n_real_blocks=nb)
+    ids_lse = ops.score_topn(qd, kd, bed, l, d, lp, n, 3, scale, n_real_blocks=nb, cmp_lse2=lse2)
+    torch.cuda.synchronize()
+    _no_timeouts()
+    differ = (ids_own != ids_lse).any(-1)
+    # the two log-sum-exps differ by rounding (1e-6 relative), which can swap two blocks whose scores tie to that level
+    assert differ.float().mean().item() < 2e-3, f"{int(differ.sum())} of {differ.numel()} rows select other blocks"
+    sel = O.selection_scores_from_compression(O.compression_probabilities(q.float(), kc, be, scale), l, d, lp)
+    ref = O.select_top_n(sel, G, n, lp)
+    clear = ~O.ambiguous_rows(sel.view(1, G, H // G, T, -1).sum(2), n)
+    assert clear.float().mean().item() > 0.9
+    assert torch.equal(ids_lse.cpu().long()[clear], ref[clear]), "rows without a near-tie select other blocks than the oracle"
