@@ -168,10 +168,10 @@ def layer_step_query_sharded(inp, params, cfg, world, before_backward=None):
 
 
 # Cost of a query that does not depend on its position (sliding window, selected blocks, gate/mix, its share of phi), in
-# units of one visible compressed key, for the work-balanced position split: from the measured kernel times of the
-# one-GPU step at T=65536 (40 ms of position-independent kernels, 33 ms of compression + scoring whose cost grows
-# linearly with the position: 0.61 us per query against 33 ms * 2t/T^2 -> 0.61 us / (33 ms * 2 / (T^2) * d) at d = 16).
-POSITION_INDEPENDENT_COST = 2480.0
+# units of one visible compressed key, for the work-balanced position split.  Fitted to the kernel time each of two ranks
+# spent on its slice of a T=65536 sequence (39808 rows: 41.7 ms, the other 25728: 38.2 ms): 0.78 us per query plus
+# 13.4 ps per (query, earlier position), i.e. 0.78 us / (13.4 ps * d) at d = 16.
+POSITION_INDEPENDENT_COST = 3650.0
 
 
 def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
@@ -203,16 +203,12 @@ def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
     mine = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
     t_ms = mine.clone()
     dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    # every rank's own device time for its slice between two barriers: without the waits for the collectives of the
-    # other ranks (a step has four), i.e. how even the position split is
+    # every rank's own kernel time for its slice (events around each launch of the library, collectives and waits
+    # for other ranks excluded): how even the position split is
+    from nsa import _lib
     own = torch.zeros(world, device=dev)
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    dist.barrier()
-    e2.record()
-    layer_step_query_sharded(inp, params, cfg, world)
-    e3.record()
-    torch.cuda.synchronize()
-    own[rank] = e2.elapsed_time(e3)
+    prof = _lib.profile_kernels(lambda: layer_step_query_sharded(inp, params, cfg, world))
+    own[rank] = sum(ms_ for _, ms_ in prof.values())
     dist.all_reduce(own)
     # the exchange steps alone (same tensors, same collectives as inside the layer), device-timed, max over ranks
     sizes = [bounds[i + 1] - bounds[i] for i in range(world)]
@@ -235,7 +231,7 @@ def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
                 n1_reference="this run's one-GPU step for a whole sequence of the same length" if T == args.T else None,
                 allgather_ms=round(coll[0].item(), 3), reduce_scatter_ms=round(coll[1].item(), 3),
                 allgather_bytes=kv_bytes, reduce_scatter_bytes=2 * kv_bytes,
-                slices=[bounds[i + 1] - bounds[i] for i in range(world)], rank_step_ms=[round(x, 2) for x in own.tolist()])
+                slices=[bounds[i + 1] - bounds[i] for i in range(world)], rank_kernel_ms=[round(x, 2) for x in own.tolist()])
 
 
 def attention_flops(T):
