@@ -724,9 +724,7 @@ struct SlcBwdSmem {
   static constexpr int kK = 64 * DK * 2, kV = 64 * DV * 2, kQ = 128 * DK * 2, kdO = 128 * DV * 2;
   static constexpr int kStage = kQ + kdO;
   static constexpr int kHalf = 64 * 128;   // 64 rows x 64 keys of bf16 P (or dS), 128-byte swizzle
-  static constexpr int kOut = 8 * 1024;    // per compute warp: 32 rows x 32 bytes of dQ being transposed for the stores
-  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, oP = oSt + 2 * kStage, odS = oP + kHalf, oOut = odS + kHalf,
-                       oBar = oOut + kOut;
+  static constexpr int oK = 0, oV = oK + kK, oSt = oV + kV, oP = oSt + 2 * kStage, odS = oP + kHalf, oBar = odS + kHalf;
   static constexpr int kDynamic = oBar + 256 + 1024;
 };
 struct SlcBwdBarriers {
@@ -796,7 +794,7 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   static_assert(cdK2 + (MK2 ? 64 : 0) <= 512, "TMEM columns");
   if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 136;");
 
-  if (warp >= 10) {
+  if (warp == 11) {
   } else if (!has_work) {
   } else if (warp == 9) {
     // producer warp: K/V block and gathered Q / dO rows by TMA (lane qi issues query qi)
@@ -861,164 +859,138 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       for (int cc = max(0, c - 2); cc < c; ++cc) mbar_wait(&bar->q_full[cc & 1], (cc >> 1) & 1, abort);
     }
   } else if (warp == 8) {
-    // UMMA issuer: warp-uniform polling loop, one elected lane issues
+    // UMMA issuer of the per-chunk chain (S, dQ, dP), warp-uniform, one elected lane issues.  Fixed order with blocking
+    // waits: S(c+1) as soon as the compute warps hold S / dP of chunk c in registers, dQ(c) once dS(c) sits in TMEM, then
+    // dP(c+1), which overwrites the dS columns and therefore follows dQ(c) in program order.  Where chunk c+1 starts
+    // another block, S(c+1) waits until dQ(c) has been issued: the single K/V slot is refilled in between.
     constexpr uint32_t idS = idesc_bf16(128, 64, 0, 1);     // Q rows (K-major) x K block (keys contiguous)
     constexpr uint32_t iddP = idesc_bf16(128, 64, 0, 0);    // dO rows (K-major) x V block read K-major (dv contiguous)
     constexpr uint32_t iddQh = idesc_bf16(128, DK / 2, 0, 0);  // dS (TMEM) x half of the K block's dk rows, read K-major
+    const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024);
+    const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
+    const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;  // Q tile: row-group / column-block strides
+    const uint32_t sboO = p.g5 ? (DV / 64) * 1024 : 1024, cbO = p.g5 ? 1024 : 16384;  // dO tile
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
+    bool ok = true;
+    int kvidx = 0;
+    auto issue_s = [&](int cc) -> bool {  // S of chunk cc: its rows have landed, S / dP of the chunk before are in registers
+      const int s = cc & 1;
+      if (!mbar_wait_warp(&bar->q_full[s], (cc >> 1) & 1, abort)) return false;
+      if (cc > 0 && !mbar_wait_warp(&bar->sdp_free, (cc - 1) & 1, abort)) return false;
+      tc_fence_after();
+      const uint64_t dQ = smem_desc_sw128(smem_u32(sSt + s * SM::kStage), 16, sboQ);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+          umma_ss(tmem + cS, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_dp = [&](int cc) {  // after S(cc) and, in program order, after dQ(cc - 1)
+      const uint64_t ddO = smem_desc_sw128(smem_u32(sSt + (cc & 1) * SM::kStage) + SM::kQ, 16, sboO);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < DV / 16; ++kk)
+          umma_ss(tmem + cdP, desc_advance(ddO, (kk >> 2) * cbO + (kk & 3) * 32), desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32), iddP,
+                  kk > 0);
+        umma_commit(&bar->sdp_full[cc & 1]);
+      }
+      __syncwarp();
+    };
+    ok = mbar_wait_warp(&bar->kv_full, 0, abort);
+    if (ok) ok = issue_s(0);
+    if (ok) issue_dp(0);
+    for (int c = 0; ok && !w.done(); ++c) {
+      const int blk_c = w.blk;
+      w.next();
+      const bool have_next = !w.done(), switch_kv = have_next && w.blk != blk_c;
+      if (have_next && !switch_kv) {
+        ok = issue_s(c + 1);
+        if (!ok) break;
+      }
+      // dQ partial of chunk c: dS is in TMEM, the accumulator has been drained by the previous chunk's epilogue
+      ok = mbar_wait_warp(&bar->dst_full, c & 1, abort);
+      if (ok && c > 0) ok = mbar_wait_warp(&bar->dq_read, (c - 1) & 1, abort);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int hh2 = 0; hh2 < 2; ++hh2)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ts(tmem + cdQ + hh2 * (DK / 2), tmem + cdP + kk * 8, desc_advance(dKmn, hh2 * (DK / 2) * 128 + kk * 32), iddQh, kk > 0);
+        umma_commit(&bar->dq_full[c & 1]);
+        if (switch_kv) umma_commit(&bar->kv_empty);  // every MMA that reads the old block's K / V has been issued
+      }
+      __syncwarp();
+      if (switch_kv) {
+        ++kvidx;
+        ok = mbar_wait_warp(&bar->kv_full, kvidx & 1, abort);
+        if (ok) ok = issue_s(c + 1);
+        if (!ok) break;
+      }
+      if (have_next) issue_dp(c + 1);
+    }
+  } else if (warp == 10) {
+    // UMMA issuer of the transposed accumulations dV^T += dO^T P, dK^T += Q^T dS: per 64-row half of a chunk, in the order
+    // the compute warps hand P and dS over.  Its MMAs touch only the accumulator columns, so they need no ordering
+    // against the other issuer's.
     constexpr uint32_t iddV = idesc_bf16(DV, 64, 1, 1);     // dO^T (dv contiguous) x P (keys contiguous), K = gathered rows
     constexpr uint32_t iddK1 = idesc_bf16(MK1, 64, 1, 1);   // Q^T (dk contiguous) x dS (keys contiguous)
     constexpr uint32_t iddK2 = idesc_bf16(64, 64, 1, 1);
-    const uint64_t dKmn = smem_desc_sw128(smem_u32(sK), 16, 1024);
-    const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
     const uint64_t dPb = smem_desc_sw128(smem_u32(sP), 16, 1024);    // one 64-key MN block: LBO unused
     const uint64_t dSb = smem_desc_sw128(smem_u32(sdS), 16, 1024);
-    const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;  // Q tile: row-group / column-block strides
-    const uint32_t sboO = p.g5 ? (DV / 64) * 1024 : 1024, cbO = p.g5 ? 1024 : 16384;  // dO tile
-    ChunkWalker wA(off, p.nblk, e0, e0 + kEntriesPerCta, qpc), wH = wA;
+    const uint32_t sboQ = p.g5 ? (DK / 64) * 1024 : 1024, cbQ = p.g5 ? 1024 : 16384;
+    const uint32_t sboO = p.g5 ? (DV / 64) * 1024 : 1024, cbO = p.g5 ? 1024 : 16384;
+    ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     bool ok = true, fresh = true;      // fresh: the next accumulation starts a new segment
-    int cs = 0, cp = 0, cq = 0;        // next chunk whose S / dP / dQ MMAs are issued (cp <= cs, cq <= cp)
-    int ch = 0, hstep = 0;             // chunk whose P / dS are consumed and its step: P(h0), dS(h0), P(h1), dS(h1)
-    int kvidx = 0, blkA = wA.blk, seg = 0, u = 0;
-    bool kv_wait = true;               // the K/V tile of the block of chunk `cs` has not been seen to land yet
-    bool kv_switch = false;            // chunk `cs` starts another block: its K/V tile has yet to be asked for
-    long long idle_since = 0;
-    while (ok && !wH.done()) {
-      bool did = false;
-      // ---- accumulate: dV^T / dK^T of chunk ch
-      if (ch < cp) {
-        bool ready = mbar_test((hstep & 1) ? &bar->ds_full : &bar->p_full, u & 1);
+    int seg = 0, u = 0;
+    for (int ch = 0; ok && !w.done(); ++ch) {
+      const uint32_t st = smem_u32(sSt + (ch & 1) * SM::kStage);
+      // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart inside an 8-row group
+      const uint64_t dQt = smem_desc_sw128(st, cbQ, sboQ), dOt = smem_desc_sw128(st + SM::kQ, cbO, sboO);
+      const int blk_c = w.blk;
+      w.next();
+      const bool last = w.done() || w.blk != blk_c;
+#pragma unroll
+      for (int h = 0; h < 2; ++h, ++u) {
+        ok = mbar_wait_warp(&bar->p_full, u & 1, abort);
         // a new segment overwrites the accumulators: the previous segment's sums must have been read out
-        if (ready && fresh && hstep == 0 && seg > 0) ready = mbar_test(&bar->acc_read, (seg - 1) & 1);
-        if (__all_sync(0xffffffffu, ready)) {
-          tc_fence_after();
-          const int h = hstep >> 1;
-          const uint32_t st = smem_u32(sSt + (ch & 1) * SM::kStage);
-          // transposed operands: 64-element runs along dk / dv, gathered rows 128 bytes apart inside an 8-row group
-          const uint64_t dQt = smem_desc_sw128(st, cbQ, sboQ), dOt = smem_desc_sw128(st + SM::kQ, cbO, sboO);
-          if ((hstep & 1) == 0) {
-            if (elect_one()) {
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk)
-                umma_ss(tmem + cdV, desc_advance(dOt, (h * 8 + kk * 2) * sboO), desc_advance(dPb, kk * 2048), iddV,
-                        !(fresh && h == 0 && kk == 0));
-              umma_commit(&bar->p_free[u & 3]);
-            }
-          } else {
-            if (elect_one()) {
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {
-                umma_ss(tmem + cdK1, desc_advance(dQt, (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK1,
-                        !(fresh && h == 0 && kk == 0));
-                if (MK2)
-                  umma_ss(tmem + cdK2, desc_advance(dQt, 2 * cbQ + (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK2,
-                          !(fresh && h == 0 && kk == 0));
-              }
-              umma_commit(&bar->ds_free[u & 3]);
-              if (hstep == 3) umma_commit(&bar->q_empty[ch & 1]);  // the chunk's Q / dO stage is free again
-            }
-          }
-          __syncwarp();
-          if (hstep == 1) fresh = false;
-          if (hstep & 1) ++u;
-          if (++hstep == 4) {
-            hstep = 0;
-            const int blk_done = wH.blk;
-            wH.next();
-            if (wH.done() || wH.blk != blk_done) {
-              // last chunk of the block (or of the CTA): hand the accumulators over
-              if (elect_one()) umma_commit(&bar->acc_full);
-              __syncwarp();
-              ++seg;
-              fresh = true;
-            }
-            ++ch;
-          }
-          did = true;
-        }
-      }
-      // ---- dQ partial of chunk cq: dS is in TMEM, the accumulator has been drained by the previous chunk's epilogue
-      if (cq < cp) {
-        bool ready = mbar_test(&bar->dst_full, cq & 1);
-        if (ready && cq > 0) ready = mbar_test(&bar->dq_read, (cq - 1) & 1);
-        if (__all_sync(0xffffffffu, ready)) {
-          tc_fence_after();
-          if (elect_one()) {
-#pragma unroll
-            for (int hh2 = 0; hh2 < 2; ++hh2)
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk)
-                umma_ts(tmem + cdQ + hh2 * (DK / 2), tmem + cdP + kk * 8, desc_advance(dKmn, hh2 * (DK / 2) * 128 + kk * 32), iddQh,
-                        kk > 0);
-            umma_commit(&bar->dq_full[cq & 1]);
-          }
-          __syncwarp();
-          ++cq;
-          did = true;
-        }
-      }
-      // ---- dP of chunk cp: after S of the same chunk, and in program order after dQ of the chunk before (same columns)
-      if (cp < cs && cq == cp) {
-        const int s = cp & 1;
-        const uint32_t st = smem_u32(sSt + s * SM::kStage);
-        const uint64_t ddO = smem_desc_sw128(st + SM::kQ, 16, sboO);
+        if (ok && fresh && h == 0 && seg > 0) ok = mbar_wait_warp(&bar->acc_read, (seg - 1) & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < DV / 16; ++kk)
-            umma_ss(tmem + cdP, desc_advance(ddO, (kk >> 2) * cbO + (kk & 3) * 32), desc_advance(dVk, (kk >> 2) * 8192 + (kk & 3) * 32),
-                    iddP, kk > 0);
-          umma_commit(&bar->sdp_full[cp & 1]);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tmem + cdV, desc_advance(dOt, (h * 8 + kk * 2) * sboO), desc_advance(dPb, kk * 2048), iddV, !(fresh && h == 0 && kk == 0));
+          umma_commit(&bar->p_free[u & 3]);
         }
         __syncwarp();
-        ++cp;
-        did = true;
-      }
-      // ---- S of chunk cs: its rows have landed and the compute warps have taken S / dP of the chunk before
-      if (!wA.done() && cs == cp) {
-        if (wA.blk != blkA && !kv_switch) kv_switch = true;
-        bool ready = true;
-        if (kv_switch) {
-          // another block: the single K/V slot is refilled once dQ of every chunk of the old block has been issued
-          if (cq == cs) {
-            if (elect_one()) umma_commit(&bar->kv_empty);
-            __syncwarp();
-            ++kvidx;
-            kv_wait = true;
-            kv_switch = false;
-            blkA = wA.blk;
-          } else {
-            ready = false;
-          }
-        }
-        const int s = cs & 1;
-        if (ready) ready = mbar_test(&bar->q_full[s], (cs >> 1) & 1) && (cs == 0 || mbar_test(&bar->sdp_free, (cs - 1) & 1));
-        if (ready && kv_wait) ready = mbar_test(&bar->kv_full, kvidx & 1);
-        if (__all_sync(0xffffffffu, ready)) {
-          kv_wait = false;
-          tc_fence_after();
-          const uint32_t st = smem_u32(sSt + s * SM::kStage);
-          const uint64_t dQ = smem_desc_sw128(st, 16, sboQ);
-          if (elect_one()) {
+        ok = mbar_wait_warp(&bar->ds_full, u & 1, abort);
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < DK / 16; ++kk)
-              umma_ss(tmem + cS, desc_advance(dQ, (kk >> 2) * cbQ + (kk & 3) * 32), desc_advance(dKmn, kk * 2048), idS, kk > 0);
+          for (int kk = 0; kk < 4; ++kk) {
+            umma_ss(tmem + cdK1, desc_advance(dQt, (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK1,
+                    !(fresh && h == 0 && kk == 0));
+            if (MK2)
+              umma_ss(tmem + cdK2, desc_advance(dQt, 2 * cbQ + (h * 8 + kk * 2) * sboQ), desc_advance(dSb, kk * 2048), iddK2,
+                      !(fresh && h == 0 && kk == 0));
           }
-          __syncwarp();
-          wA.next();
-          ++cs;
-          did = true;
+          umma_commit(&bar->ds_free[u & 3]);
+          if (h == 1) {
+            umma_commit(&bar->q_empty[ch & 1]);  // the chunk's Q / dO stage is free again
+            if (last) umma_commit(&bar->acc_full);  // last chunk of the block (or of the CTA): hand the accumulators over
+          }
         }
+        __syncwarp();
       }
-      // ---- nothing ready: bounded idling
-      if (did) {
-        idle_since = 0;
-      } else {
-        const long long now = clock64();
-        if (idle_since == 0) idle_since = now;
-        if (*abort || now - idle_since > (1ll << 28)) {
-          *abort = 1;
-          ok = false;
-        }
-
+      fresh = false;
+      if (last) {
+        ++seg;
+        fresh = true;
       }
     }
   } else {
@@ -1028,7 +1000,6 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int r = warp4 * 32 + lane;
     const int half = warp4 >> 1, rr = r & 63;  // which 64-row half of the chunk this row is handed over in
     const uint32_t lane_base = (uint32_t)(warp4 * 32) << 16;
-    uint8_t* ostage = smem + SM::oOut + warp * 1024;
     ChunkWalker w(off, p.nblk, e0, e0 + kEntriesPerCta, qpc);
     bool ok = true;
     int c = 0, last_blk = -1, seg = 0;
@@ -1132,9 +1103,8 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         *reinterpret_cast<uint4*>(sdS + rr * 128 + ((j ^ (rr & 7)) << 4)) = make_uint4(pS[4 * j], pS[4 * j + 1], pS[4 * j + 2], pS[4 * j + 3]);
       fence_proxy_async();
       mbar_arrive(&bar->ds_full);
-      // dQ partial of this chunk: TMEM -> registers -> per-warp staging (32 rows x 32 bytes, pieces swapped for odd
-      // groups of four rows) -> 32-byte runs of 16 rows per store instruction
-      const int prow = entry >= 0 ? (int)((((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh) : -1;
+      // dQ partial of this chunk: TMEM -> registers -> this row of the partial array, one 32-byte sector per store
+      __nv_bfloat16* drow = entry >= 0 ? p.dq_part + ((((int64_t)bg * p.Tq + t) * p.nslots + slot) * p.hpg + hh) * DK : nullptr;
       ok = mbar_wait(&bar->dq_full[grp], (c >> 1) & 1, abort);
       if (!ok) break;
       tc_fence_after();
@@ -1147,28 +1117,16 @@ slc_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
           tc_fence_before();
           mbar_arrive(&bar->dq_read);
         }
-#pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-          __syncwarp();  // the previous 16 columns have been read back
+        if (drow) {
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            const uint32_t* src = &ov[sub * 16 + j * 8];
-            uint4 wv;
-            __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
-            __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
-            __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
-            __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
-            wv.x = *reinterpret_cast<uint32_t*>(&a0); wv.y = *reinterpret_cast<uint32_t*>(&a1);
-            wv.z = *reinterpret_cast<uint32_t*>(&a2); wv.w = *reinterpret_cast<uint32_t*>(&a3);
-            *reinterpret_cast<uint4*>(ostage + lane * 32 + ((j ^ ((lane >> 2) & 1)) << 4)) = wv;
-          }
-          __syncwarp();
+            uint32_t wv[8];
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int r2 = i * 16 + (lane >> 1), piece = lane & 1;  // row of this warp whose piece this lane forwards
-            const int grow = __shfl_sync(0xffffffffu, prow, r2);
-            const uint4 wv = *reinterpret_cast<const uint4*>(ostage + r2 * 32 + ((piece ^ ((r2 >> 2) & 1)) << 4));
-            if (grow >= 0) *reinterpret_cast<uint4*>(p.dq_part + (int64_t)grow * DK + cc * 32 + sub * 16 + piece * 8) = wv;
+            for (int e = 0; e < 8; ++e) {
+              __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(ov[j * 16 + 2 * e]), __uint_as_float(ov[j * 16 + 2 * e + 1]));
+              wv[e] = *reinterpret_cast<uint32_t*>(&a2);
+            }
+            st_global_v8(drow + cc * 32 + j * 16, wv);
           }
         }
       }
