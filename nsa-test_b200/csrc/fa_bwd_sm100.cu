@@ -632,8 +632,8 @@ fa_bwd_dq_ds_kernel(const __grid_constant__ CUtensorMap tmDs, const __grid_const
 
 // ------------------------------------------------------------------------------------------------
 // dK/dV kernel: 128 keys per CTA, loops over (head, 64-query sub-tile); transposed tiles in TMEM.
-// 352 threads: warps 0-3 / 4-7 turn the two 32-query halves of S^T, dP^T into P^T, dS^T; warp 8 TMA; warp 9 UMMA; warp 10
-// stores the dS^T tiles the compute warps stage in shared memory.
+// 384 threads: warps 0-3 / 4-7 turn the two 32-query halves of S^T, dP^T into P^T, dS^T; warp 8 TMA; warp 9 issues the
+// S^T / dP^T products, warp 11 the accumulations; warp 10 stores the dS^T tiles the compute warps stage in shared memory.
 // ------------------------------------------------------------------------------------------------
 template <int DK, int DV>
 struct DkvSmem {
@@ -651,7 +651,7 @@ struct DkvBarriers {
 };
 
 template <int DK, int DV, int MODE>
-__global__ void __launch_bounds__(352, 1)
+__global__ void __launch_bounds__(384, 1)
 fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                   const __grid_constant__ CUtensorMap tmDs, const FaBwdParams p) {
@@ -745,8 +745,6 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (n_it > 0) {
       constexpr uint32_t idST = idesc_bf16(128, 64, 1, 0);    // K tile as A (MN-major: keys contiguous) x Q sub-tile (K-major)
       constexpr uint32_t iddPT = idesc_bf16(128, 64, 0, 0);   // V tile as A (K-major) x dO sub-tile (K-major)
-      constexpr uint32_t iddV = idesc_bf16(128, DV, 0, 1);    // P^T (TMEM) x dO sub-tile (MN-major: dv contiguous)
-      constexpr uint32_t iddK = idesc_bf16(128, DK, 0, 1);    // dS^T (TMEM) x Q sub-tile (MN-major: dk contiguous)
       const uint64_t dKa = smem_desc_sw128(smem_u32(sK), DK * 128, 1024);
       const uint64_t dVa = smem_desc_sw128(smem_u32(sV), 16, 1024);
       // S^T = K Q^T and dP^T = V dO^T of iteration `it`, whose stage is s (phase ph)
@@ -769,13 +767,25 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         __syncwarp();
         return true;
       };
-      bool ok = mbar_wait_warp(&bar->kv_full, 0, abort) && issue_st(0, 0, 0);
-      int s = 0, s1 = 1, ph1 = 0;  // stage of `it`, stage and phase of `it + 1`
+      // every iteration's S^T / dP^T as soon as its rows have landed and the fp32 tiles of the one before are in registers
+      bool ok = mbar_wait_warp(&bar->kv_full, 0, abort);
+      int s = 0, ph = 0;
+      for (int it = 0; it < n_it && ok; ++it) {
+        ok = issue_st(it, s, ph);
+        if (++s == 3) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 11) {
+    // second UMMA issuer: the accumulations dV += P^T dO, dK += dS^T Q.  They read other TMEM columns than the S^T / dP^T
+    // products, so the two issuers need no ordering between them and the bookkeeping of one runs under the MMAs of the other.
+    if (n_it > 0) {
+      constexpr uint32_t iddV = idesc_bf16(128, DV, 0, 1);    // P^T (TMEM) x dO sub-tile (MN-major: dv contiguous)
+      constexpr uint32_t iddK = idesc_bf16(128, DK, 0, 1);    // dS^T (TMEM) x Q sub-tile (MN-major: dk contiguous)
+      bool ok = true;
+      int s = 0;
       for (int it = 0; it < n_it && ok; ++it) {
         const uint32_t st = smem_u32(sSt + s * SM::kStage);
         const uint64_t dQmn = smem_desc_sw128(st, 8192, 1024), dOmn = smem_desc_sw128(st + SM::kQs, 8192, 1024);
-        if (it + 1 < n_it) ok = issue_st(it + 1, s1, ph1);   // runs on the tensor pipe while the compute warps work on `it`
-        if (!ok) break;
         ok = mbar_wait_warp(&bar->pds_full, it & 1, abort);
         if (!ok) break;
         tc_fence_after();
@@ -786,12 +796,11 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_ts(tmem + cdK, tmem + cPS + (kk >> 1) * 32 + 16 + (kk & 1) * 8, desc_advance(dQmn, kk * 2048), iddK, (it > 0) || (kk > 0));
-          umma_commit(&bar->empty[s]);
+          umma_commit(&bar->empty[s]);   // (the S^T / dP^T products that read this stage finished before P^T existed)
           umma_commit(&bar->pds_free);
         }
         __syncwarp();
-        s = s1;
-        if (++s1 == 3) { s1 = 0; ph1 ^= 1; }
+        if (++s == 3) s = 0;
       }
       if (ok) {
         if (elect_one()) umma_commit(&bar->acc_done);
@@ -1002,7 +1011,7 @@ static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, con
     // key-stationary kernel first: it leaves dS^T behind, from which the dQ kernel only has one product left to do
     {
       KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);
-      kkv<<<kvgrid, 352, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, tds, p);
+      kkv<<<kvgrid, 384, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, tds, p);
     }
     if (int rc = check_launch("fa_bwd_dkv_sm100")) return rc;
     KernelTimer kt(MODE == kWin ? "fa_bwd_dqds_win" : "fa_bwd_dqds_cmp", st);
@@ -1015,7 +1024,7 @@ static int launch_bwd_t(const CUtensorMap& tq128, const CUtensorMap& tdo128, con
   }
   if (int rc = check_launch("fa_bwd_dq_sm100")) return rc;
   KernelTimer kt(MODE == kWin ? "fa_bwd_dkv_win" : "fa_bwd_dkv_cmp", st);
-  kkv<<<kvgrid, 352, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, tds, p);
+  kkv<<<kvgrid, 384, DkvSmem<DK, DV>::kDynamic, st>>>(tq64, tdo64, tk, tv, tds, p);
   return check_launch("fa_bwd_dkv_sm100");
 }
 
