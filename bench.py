@@ -39,8 +39,19 @@ METRIC = "NSA layer fwd+bwd tokens/s at T=64K"
 # the selection kernels.  That case is too small to be captured at full size under the
 # capture-size rule, so the figure is scaled by the units of the workload; at T=8192 62 % of the gathers hit L2, at
 # T=65536 fewer do, so the scaled figure is a lower bound of the full-size traffic.
-NCU_DRAM_BYTES_PER_UNIT = {"slc_bwd_fused": (3438014976 + 3070898432) / (8192 * 4 * 16),
-                           "slc_fwd": (1592842240 + 2031976192) / (8192 * 4 * 16)}
+NCU_DRAM_BYTES_PER_UNIT = {"slc_bwd_fused": (3497088000 + 3072542000) / (8192 * 4 * 16),
+                           "slc_fwd": (1598514000 + 2035920000) / (8192 * 4 * 16)}
+
+
+def selection_bytes_per_unit(kernel):
+    """Algorithmic HBM bytes of one (group, query, slot) unit of the selection kernels: every unit gathers the query's
+    rows of all heads of the group (forward: Q; backward: Q and dO) and writes one partial (forward: normalised O rows and
+    two statistics per head; backward: dQ rows); the key/value blocks and the inverse index are 1 % of that."""
+    c = CFG
+    hpg = c["H"] // c["G"]
+    if kernel == "slc_fwd":
+        return hpg * (c["dk"] * 2 + c["dv"] * 2 + 8)
+    return hpg * ((c["dk"] + c["dv"]) * 2 + c["dk"] * 2)
 
 
 def measured_peaks():
@@ -625,18 +636,23 @@ def main():
             achieved = kflops[top] / (tot / n_l * 1e-3) / 1e12
             units = c["G"] * T * c["n"]                                   # (group, query, slot) triples of one launch
             traffic = int(NCU_DRAM_BYTES_PER_UNIT[top] * units) if top in NCU_DRAM_BYTES_PER_UNIT else None
-            # `bound` says what the kernel's committed ncu capture shows (profiles/): the dense kernels keep the tensor
-            # pipe busiest; the fused selection backward keeps DRAM busier (41 %) than the tensor pipe (16 %) and is held
-            # back by shared-memory traffic and latency, so its FLOP fraction is a distance to the ceiling, not a claim
-            # that the tensor pipe is the limiter.
-            counters = {"slc_bwd_fused": "dram 41 % > tensor pipe 16 % busy (ncu, T=8192): latency / shared-memory bound",
-                        "slc_fwd": "dram busiest (ncu, T=8192)"}
-            roofline = dict(bound="tensor", kernel=top, achieved=round(achieved, 1), peak=peaks["tflops_sustained"], unit="TFLOP/s",
-                            frac=round(achieved / peaks["tflops_sustained"], 4), traffic=traffic,
-                            counters=counters.get(top, "tensor pipe busiest (ncu, T=8192)"),
-                            traffic_source="ncu dram bytes at T=8192 scaled by (group, query, slot) units; lower bound" if traffic else None,
-                            peak_source=peaks["source"] + " (sustained bf16)",
-                            ms_per_launch=round(tot / n_l, 4))
+            # `bound` says what limits the kernel.  The dense kernels keep the tensor pipe busiest (ncu, profiles/) and are
+            # rated by FLOPs against the sustained cuBLAS rate.  The selection kernels move 16 KB (backward) / 10 KB (forward)
+            # through HBM per 13.6 / 5.2 MFLOP unit and are rated by their algorithmic bytes against the measured copy
+            # bandwidth: bringing rows into L2 earlier makes the backward slower, not faster (profiles/).
+            if top in NCU_DRAM_BYTES_PER_UNIT:
+                gbs = selection_bytes_per_unit(top) * units / (tot / n_l * 1e-3) / 1e9
+                roofline = dict(bound="hbm", kernel=top, achieved=round(gbs, 1), peak=peaks["hbm_gbs"], unit="GB/s",
+                                frac=round(gbs / peaks["hbm_gbs"], 4), traffic=traffic,
+                                counters="dram 51 % busy, tensor pipe 33 % (ncu, T=8192, where 56 % of the gathers hit L2)",
+                                traffic_source="ncu dram bytes at T=8192 scaled by (group, query, slot) units; lower bound",
+                                peak_source=peaks["source"] + " (copy bandwidth)", tflops=round(achieved, 1),
+                                ms_per_launch=round(tot / n_l, 4))
+            else:
+                roofline = dict(bound="tensor", kernel=top, achieved=round(achieved, 1), peak=peaks["tflops_sustained"],
+                                unit="TFLOP/s", frac=round(achieved / peaks["tflops_sustained"], 4), traffic=None,
+                                counters="tensor pipe busiest (ncu, T=8192)", traffic_source=None,
+                                peak_source=peaks["source"] + " (sustained bf16)", ms_per_launch=round(tot / n_l, 4))
         att = attention_flops(T)
         att_total = sum(att[b_][p_] for b_ in att for p_ in att[b_])
         kern_ms = sum(ms_ for _, ms_ in prof.values())
