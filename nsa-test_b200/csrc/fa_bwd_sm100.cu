@@ -856,19 +856,25 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_arrive(&bar->st_free);   // the fp32 tiles may be overwritten by the next iteration's MMAs
       uint32_t pk[32];  // [0,16): P^T of this group's 32 queries, [16,32): dS^T
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        const int c0 = gsel * 32 + 2 * e;
-        const float l0 = stat[c0], l1 = stat[c0 + 1], D0 = stat[64 + c0], D1 = stat[64 + c0 + 1];
-        float p0 = ex2(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0));
-        float p1 = ex2(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1));
-        if (!allvis) {
-          p0 = (c0 >= clo && c0 <= chi) ? p0 : 0.f;
-          p1 = (c0 + 1 >= clo && c0 + 1 <= chi) ? p1 : 0.f;
+      for (int e4 = 0; e4 < 8; ++e4) {
+        // the statistics of four queries per load (every lane reads the same words: a broadcast)
+        const float4 lv = reinterpret_cast<const float4*>(stat)[gsel * 8 + e4];
+        const float4 Dv = reinterpret_cast<const float4*>(stat + 64)[gsel * 8 + e4];
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int e = 2 * e4 + hf, c0 = gsel * 32 + 2 * e;
+          const float l0 = hf ? lv.z : lv.x, l1 = hf ? lv.w : lv.y, D0 = hf ? Dv.z : Dv.x, D1 = hf ? Dv.w : Dv.y;
+          float p0 = ex2(fmaf(__uint_as_float(sT[2 * e]), p.scale_log2, -l0));
+          float p1 = ex2(fmaf(__uint_as_float(sT[2 * e + 1]), p.scale_log2, -l1));
+          if (!allvis) {
+            p0 = (c0 >= clo && c0 <= chi) ? p0 : 0.f;
+            p1 = (c0 + 1 >= clo && c0 + 1 <= chi) ? p1 : 0.f;
+          }
+          const float s0 = p0 * (__uint_as_float(dpT[2 * e]) - D0), s1 = p1 * (__uint_as_float(dpT[2 * e + 1]) - D1);
+          __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1), y = __floats2bfloat162_rn(s0, s1);
+          pk[e] = *reinterpret_cast<uint32_t*>(&x);
+          pk[16 + e] = *reinterpret_cast<uint32_t*>(&y);
         }
-        const float s0 = p0 * (__uint_as_float(dpT[2 * e]) - D0), s1 = p1 * (__uint_as_float(dpT[2 * e + 1]) - D1);
-        __nv_bfloat162 x = __floats2bfloat162_rn(p0, p1), y = __floats2bfloat162_rn(s0, s1);
-        pk[e] = *reinterpret_cast<uint32_t*>(&x);
-        pk[16 + e] = *reinterpret_cast<uint32_t*>(&y);
       }
       if (p.ds) {
         // Hand dS^T to the dQ kernel through a shared-memory tile and ONE tile store (whole 128-byte lines leave the
