@@ -70,7 +70,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// Whole-warp form: every lane waits (one warp-wide instruction per poll), the verdict is made uniform.
+// Whole-warp form: every lane waits (one warp-wide instruction per poll), the outcome is made uniform.
 // Roles that issue tcgen05 instructions run their loops warp-uniformly and elect one lane per
 // instruction, so that descriptors and addresses stay in the uniform datapath.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort,
