@@ -194,6 +194,22 @@ def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
     from nsa import sharding
     c = CFG
     inp, params = make_device_inputs(T, dev, seed=0)            # the same sequence on every rank; each keeps its slice
+    one_gpu_ms = headline_ms if T == args.T else None
+    if one_gpu_ms is None:
+        # no one-GPU step of this length has been timed in this run: every rank times the whole sequence on its own GPU
+        # (world=1: no collective), 1 warm-up + 2 timed steps, max over ranks
+        layer_step(inp, params, cfg, 1)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(2):
+            layer_step(inp, params, cfg, 1)
+        b.record()
+        torch.cuda.synchronize()
+        t1 = torch.tensor([a.elapsed_time(b) / 2], device=dev)
+        dist.all_reduce(t1, op=dist.ReduceOp.MAX)
+        one_gpu_ms = t1.item()
+        torch.cuda.empty_cache()
     bounds = sharding.balanced_query_bounds(T, world, POSITION_INDEPENDENT_COST, c["d"])
     t0, t1 = bounds[rank], bounds[rank + 1]
     inp = dict(q=inp["q"][:, :, t0:t1].contiguous(), k=inp["k"][..., t0:t1].contiguous(), v=inp["v"][:, :, t0:t1].contiguous(),
@@ -238,8 +254,9 @@ def long_context_leg(args, cfg, dev, world, rank, T, headline_ms):
     ms = t_ms.item()
     kv_bytes = c["G"] * T * (c["dk"] + c["dv"]) * 2
     return dict(T=T, n_gpus=world, steps=steps, warmup=5, ms_per_step=round(ms, 3), tokens_per_s=round(T / (ms * 1e-3), 1),
-                speedup_vs_n1=round(headline_ms / ms, 3) if T == args.T else None,
-                n1_reference="this run's one-GPU step for a whole sequence of the same length" if T == args.T else None,
+                speedup_vs_n1=round(one_gpu_ms / ms, 3), n1_ms_per_step=round(one_gpu_ms, 3),
+                n1_reference="this run's one-GPU step for a whole sequence of the same length" + (
+                    "" if T == args.T else " (every rank alone on its GPU, 2 steps after 1 warm-up, max over ranks)"),
                 allgather_ms=round(coll[0].item(), 3), reduce_scatter_ms=round(coll[1].item(), 3),
                 allgather_bytes=kv_bytes, reduce_scatter_bytes=2 * kv_bytes,
                 slices=[bounds[i + 1] - bounds[i] for i in range(world)], rank_kernel_ms=[round(x, 2) for x in own.tolist()])
