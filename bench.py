@@ -503,6 +503,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-long-context", action="store_true",
                     help="multi-GPU runs: skip the extra leg that times ONE sequence split by position over the GPUs")
+    ap.add_argument("--long-context-2t", action="store_true",
+                    help="multi-GPU runs: also time the long-context leg at twice --T (always done on 8 GPUs)")
     ap.add_argument("--no-parity", action="store_true", help="skip the sampled-row check of the workload against the oracle")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end leg (default: max(50, --steps))")
     ap.add_argument("--shard", default="sequence", choices=["sequence", "query"],
@@ -634,7 +636,7 @@ def main():
         del inp, host, slots            # the weak-scaling inputs make room; rebuilt below for the profiled step
         torch.cuda.empty_cache()
         long_context = [long_context_leg(args, cfg, dev, world, rank, T, ms_per_step)]
-        if world >= 8:
+        if world >= 8 or args.long_context_2t:
             long_context.append(long_context_leg(args, cfg, dev, world, rank, 2 * T, ms_per_step))
         torch.cuda.empty_cache()
         inp, _ = make_device_inputs(T, dev, seed=rank)
