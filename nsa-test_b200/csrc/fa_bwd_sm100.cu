@@ -710,6 +710,23 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       __syncwarp();
       bool ok = true;
       int issued = 0, s = 0, ph = 0, h = hbeg, qs = qs_lo;
+      // A stage is held from its load to the end of the accumulations that read it, so with three stages a load's HBM
+      // latency (about 3 000 cycles under load) cannot hide behind the other two.  The rows of the iterations ahead are
+      // therefore started towards L2 early: the tile loads then find them there.
+      constexpr int kAhead = 4;
+      int h_pf = hbeg, qs_pf = qs_lo, it_pf = 0;
+      auto prefetch_next = [&]() {
+        if (it_pf < n_it) {
+          const int row = (int)((((int64_t)b * p.H + h_pf) * p.Tq) + qs_pf * 64);
+          for (int c = 0; c < DK / 64; ++c) tma_prefetch_2d(&tmQ, c * 64, row);
+          for (int c = 0; c < DV / 64; ++c) tma_prefetch_2d(&tmdO, c * 64, row);
+          ++it_pf;
+          if (++qs_pf > qs_hi) { qs_pf = qs_lo; ++h_pf; }
+        }
+      };
+      if (elect_one())
+        for (int k = 0; k < kAhead; ++k) prefetch_next();
+      __syncwarp();
       for (int it = 0; it < n_it; ++it) {
         const int tq0 = qs * 64;
         const int64_t qrow = ((int64_t)b * p.H + h) * p.Tq + tq0;
@@ -723,6 +740,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           mbar_arrive_expect_tx(&bar->full[s], SM::kQs + SM::kdOs);
           for (int c = 0; c < DK / 64; ++c) tma_load_2d(&tmQ, &bar->full[s], st + c * 8192, c * 64, (int)qrow);
           for (int c = 0; c < DV / 64; ++c) tma_load_2d(&tmdO, &bar->full[s], st + SM::kQs + c * 8192, c * 64, (int)qrow);
+          prefetch_next();
         }
         float* stat = reinterpret_cast<float*>(st + SM::kQs + SM::kdOs);
         stat[lane] = s_l0;
