@@ -540,3 +540,36 @@ def test_compression_forward_on_split_keys_and_its_lse_in_scoring(dk, dv, H, G, 
     clear = ~O.ambiguous_rows(sel.view(1, G, H // G, T, -1).sum(2), n)
     assert clear.float().mean().item() > 0.9
     assert torch.equal(ids_lse.cpu().long()[clear], ref[clear]), "rows without a near-tie select other blocks than the oracle"
+
+
+def test_sliding_window_alone_at_its_benchmark_configuration():
+    """The sliding-window branch alone at the size the project's second benchmark configuration names (B=4, H=64, G=4,
+    T=8192, dk=192, dv=128, window 512, bf16, forward + backward): output rows and statistics against the CPU oracle's
+    per-row attention on sampled positions (first rows, around the window length, tile edges, last row), gradients
+    against the stride-generic kernels (which the small cases above pin to the oracle)."""
+    from nsa import ops
+    B, H, G, T, dk, dv, w = 4, 64, 4, 8192, 192, 128, 512
+    q, k, v, do = (t.to(DEV) for t in _inputs(B, H, G, T, dk, dv, seed=21))
+    scale = dk ** -0.5
+    o, L, M = ops.sliding_fwd(q, k, v, w, scale)
+    dq, dkey, dval = ops.sliding_bwd(q, k, v, o, do, L, M, w, scale)
+    gen = ops.sliding_bwd(q, k, v, o, do, L, M, w, scale, generic=True)
+    torch.cuda.synchronize()
+    _no_timeouts()
+    hpg = H // G
+    pos = sorted({0, 1, 63, 64, 127, 128, 510, 511, 512, 513, 1023, 1024, 4095, 4096, 4097, T - 129, T - 128, T - 1} |
+                 {int(x) for x in torch.randint(0, T, (24,), generator=torch.Generator().manual_seed(3))})
+    qc, kc, vc = q.float().cpu(), k.float().cpu(), v.float().cpu()
+    worst_o, worst_lse = 0.0, 0.0
+    for t in pos:
+        lo = max(0, t - w + 1)
+        for g in range(G):
+            s = torch.einsum("bhd,bdn->bhn", qc[:, g * hpg:(g + 1) * hpg, t], kc[:, g, :, lo:t + 1]) * scale
+            ref = torch.softmax(s, -1) @ vc[:, g, lo:t + 1]
+            got = o[:, g * hpg:(g + 1) * hpg, t].float().cpu()
+            worst_o = max(worst_o, (got - ref).abs().max().item())
+            lse = (M + L)[:, g * hpg:(g + 1) * hpg, t].cpu()
+            worst_lse = max(worst_lse, (lse - torch.logsumexp(s, -1)).abs().max().item())
+    assert worst_o < 2e-2 and worst_lse < 2e-2, (worst_o, worst_lse)
+    for a, b_, n in zip((dq, dkey, dval), gen, ("dq", "dk", "dv")):
+        _grad_close(a, b_.float().cpu(), "sliding window at B=4 T=8192: " + n)
