@@ -388,18 +388,18 @@ def test_layer_bf16_forward_backward(nsa_mod):
 
 
 @pytest.mark.timeout(1200)
-@pytest.mark.parametrize("T", [2048, 4096])
-def test_layer_bf16_at_the_benchmarked_head_configuration(nsa_mod, T):
+@pytest.mark.parametrize("B,T", [(1, 2048), (1, 4096), (2, 2048)])
+def test_layer_bf16_at_the_benchmarked_head_configuration(nsa_mod, B, T):
     """H=64 query heads in G=4 groups, dk=192, dv=128, keys with per-block offsets (BASELINE configs 3-5), bf16, through the
     single autograd node the benchmark uses (dQ of the three branches summed in the selection backward, row sums handed
     over by the gate/mix backward): outputs and all twelve gradients against the oracle."""
     from nsa._lib import lib
-    c = dict(B=1, H=64, G=4, T=T, dk=192, dv=128, d_model=512, l=32, d=16, l_prime=64, n=16, w=512)
+    c = dict(B=B, H=64, G=4, T=T, dk=192, dv=128, d_model=512, l=32, d=16, l_prime=64, n=16, w=512)
     inp = O.make_inputs(c["B"], c["H"], c["G"], T, c["dk"], c["dv"], c["d_model"], c["l"], seed=23, block_offset_std=0.5,
                         l_prime=c["l_prime"], dtype=torch.bfloat16)
     O.LOW_MEMORY = True
     try:
-        check_layer_against_oracle(f"layer bf16 H=64 G=4 dk=192 dv=128 T={T}", nsa_mod, c, inp, torch.bfloat16)
+        check_layer_against_oracle(f"layer bf16 B={B} H=64 G=4 dk=192 dv=128 T={T}", nsa_mod, c, inp, torch.bfloat16)
     finally:
         O.LOW_MEMORY = False
     assert lib.nsa_device_timeouts(0) == 0
