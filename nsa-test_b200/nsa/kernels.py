@@ -223,6 +223,9 @@ class _BranchesAndMix(torch.autograd.Function):
         ctx.scale, ctx.l_prime, ctx.w, ctx.blocks = scale, config.l_prime, config.w, blocks
         ctx.gate_mode, ctx.ldtype = config.gate_mode, gate_logits.dtype
         ctx.q_pos0, ctx.win = q_pos0, (lo, hi, pad, tuple(k_win.shape), tuple(v_win.shape))
+        # one k/v pair feeding both the selection and the sliding-window branch: their dK/dV are summed in the backward
+        ctx.shared_win = (k_win.data_ptr() == k_slc.data_ptr() and v_win.data_ptr() == v_slc.data_ptr()
+                          and k_win.shape == k_slc.shape and v_win.shape == v_slc.shape)
         ctx.mark_non_differentiable(gates, o_cmp, o_slc, o_win, indices)
         return out, gates, o_cmp, o_slc, o_win, indices
 
@@ -245,14 +248,21 @@ class _BranchesAndMix(torch.autograd.Function):
         dq_w, dkw, dvw = ops.sliding_bwd(qw, kw_s, vw_s, o_wp, d_wp, Lw, Mw, ctx.w, ctx.scale, row_delta=delta_w)
         if pad:
             dq_w = dq_w[:, :, pad:].contiguous()
-        dkw = dkw.transpose(-1, -2)
-        if (lo, hi) != (0, kshape[-1]):
-            full_k, full_v = dkw.new_zeros(kshape), dvw.new_zeros(vshape)
-            full_k[..., lo:hi] = dkw
-            full_v[:, :, lo:hi] = dvw
-            dkw, dvw = full_k, full_v
         dq, dks, dvs = ops.slc_bwd(q, k_slc, v_slc, idx, o_slc, d_slc, Ls, Ms, ctx.l_prime, ctx.scale, ctx.q_pos0,
                                    dq_addends=(dq_c, dq_w), row_delta=delta[1])
+        if ctx.shared_win:
+            # the window's gradients (time-major, for the key slice [lo, hi)) go straight into the selection branch's
+            # full-length buffers: no zero-filled full-length copies, no separate full-length additions by autograd
+            dks[:, :, lo:hi] += dkw
+            dvs[:, :, lo:hi] += dvw
+            dkw = dvw = None
+        else:
+            dkw = dkw.transpose(-1, -2)
+            if (lo, hi) != (0, kshape[-1]):
+                full_k, full_v = dkw.new_zeros(kshape), dvw.new_zeros(vshape)
+                full_k[..., lo:hi] = dkw
+                full_v[:, :, lo:hi] = dvw
+                dkw, dvw = full_k, full_v
         return (dq, dkc.transpose(-1, -2), dvc, None, dks.transpose(-1, -2), dvs, None, dkw, dvw,
                 dlogits.to(ctx.ldtype), None, None, None, None, None, None)
 

@@ -94,13 +94,19 @@ class _AllGatherSeq(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         big = max(ctx.sizes)
+        dim = ctx.dim
+        # A gradient whose last two dimensions are swapped in memory (dK arrives as the transposed view of a time-major
+        # buffer) is split, widened and summed in that layout: every pass then reads and writes whole lines.
+        swapped = (not g.is_contiguous()) and g.dim() >= 2 and dim == g.dim() - 1 and g.transpose(-1, -2).is_contiguous()
+        if swapped:
+            g, dim = g.transpose(-1, -2), dim - 1
         chunks = []
-        for c in g.split(ctx.sizes, dim=ctx.dim):
+        for c in g.split(ctx.sizes, dim=dim):
             c = c.float()
-            if c.shape[ctx.dim] < big:
+            if c.shape[dim] < big:
                 pad_shape = list(c.shape)
-                pad_shape[ctx.dim] = big - c.shape[ctx.dim]
-                c = torch.cat([c, c.new_zeros(pad_shape)], dim=ctx.dim)
+                pad_shape[dim] = big - c.shape[dim]
+                c = torch.cat([c, c.new_zeros(pad_shape)], dim=dim)
             chunks.append(c.contiguous())
         if dist.get_backend(ctx.group) == "nccl":
             out = torch.empty_like(chunks[ctx.rank])
@@ -109,7 +115,8 @@ class _AllGatherSeq(torch.autograd.Function):
             full = torch.stack(chunks)
             dist.all_reduce(full, op=dist.ReduceOp.SUM, group=ctx.group)
             out = full[ctx.rank]
-        return out.narrow(ctx.dim, 0, ctx.sizes[ctx.rank]).to(g.dtype), None, None, None
+        out = out.narrow(dim, 0, ctx.sizes[ctx.rank]).to(g.dtype)
+        return (out.transpose(-1, -2) if swapped else out), None, None, None
 
 
 def all_gather_seq(x: torch.Tensor, dim: int, group: Optional[dist.ProcessGroup] = None, sizes=None) -> torch.Tensor:
@@ -150,7 +157,9 @@ def sharded_compress(k_full, v_full, compress_fn, bounds: List[int], rank: int, 
     dv = v_full.shape[-1]
     if cnt > 0:
         lo, hi = b0 * d, (b1 - 1) * d + l
-        kc, vc = compress_fn(k_full[..., lo:hi].transpose(-1, -2), v_full[:, :, lo:hi])
+        # (slice of the transposed view: the slice's backward then builds its zero-filled full-length gradient in the
+        # time-major memory layout the attention branches' dK has, so autograd adds the two without a strided pass)
+        kc, vc = compress_fn(k_full.transpose(-1, -2)[:, :, lo:hi], v_full[:, :, lo:hi])
         kc, vc = kc[..., :cnt], vc[:, :, :cnt]
     else:
         kc = k_full.new_zeros(B, G, dk, 0, dtype=torch.float32)
