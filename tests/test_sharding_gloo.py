@@ -84,7 +84,15 @@ def _gather_worker(rank, world, port, ret):
         want = base * sum(r + 1 for r in range(world))              # gradient summed over the ranks' losses
         ok_fwd = ok_fwd and torch.equal(yu.detach(), full)
         err_u = (xu.grad - want[..., bounds[rank]:bounds[rank + 1]]).abs().max().item()
-        ret[rank] = (ok_fwd, max((x.grad - want[..., t0:t1]).abs().max().item(), err_u), (t1 - t0) == step)
+        # an upstream gradient whose last two dimensions are swapped in memory (how dK reaches the exchange: the transposed
+        # view of a time-major buffer): the reduce-scatter works in that layout and hands back a view of the same kind
+        xs = full[..., bounds[rank]:bounds[rank + 1]].clone().requires_grad_(True)
+        ys = all_gather_seq(xs, -1, None, [384, 128])
+        g_tm = (wgt.transpose(-1, -2).contiguous()).transpose(-1, -2)       # values of wgt, time-major memory
+        assert not g_tm.is_contiguous() and g_tm.transpose(-1, -2).is_contiguous()
+        torch.autograd.backward([ys], [g_tm])
+        err_s = (xs.grad - want[..., bounds[rank]:bounds[rank + 1]]).abs().max().item()
+        ret[rank] = (ok_fwd, max((x.grad - want[..., t0:t1]).abs().max().item(), err_u, err_s), (t1 - t0) == step)
     finally:
         dist.destroy_process_group()
 
